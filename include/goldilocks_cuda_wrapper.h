@@ -1,0 +1,110 @@
+/*
+ * C-ABI of libgoldilocks_cuda_wrapper: Goldilocks (p = 2^64 - 2^32 + 1) hot path
+ * on B200 (sm_100a).
+ *
+ * Every function returns int: 0 success, -1 CUDA error, -2 rejected argument,
+ * -3 unsupported configuration. Pointers named d_* are device memory that the
+ * caller owns (obtained from cuda_malloc, returned with cuda_free); h_* are host
+ * memory. Inputs may be any u64 representative of a residue; everything
+ * written out is canonical (< p). Calls run on the calling thread's stream
+ * and return when their result is ready.
+ *
+ * Each declaration cites the reference interface it replaces: the Rust
+ * `extern "C"` block in goldilocks-cuda-rs/src/ffi.rs (declaration) and
+ * goldilocks-cuda-rs/cuda/wrapper.cu (definition). Entries marked "addition"
+ * have no reference counterpart.
+ */
+#ifndef GOLDILOCKS_CUDA_WRAPPER_H
+#define GOLDILOCKS_CUDA_WRAPPER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- initialisation: ffi.rs:10-11, :549 (wrapper.cu:27-46) ---- */
+int goldilocks_cuda_init(void);
+int poseidon2_cuda_init(void);
+int monolith_cuda_init(void);
+
+/* ---- memory: ffi.rs:17-25 (wrapper.cu:52-98) ---- */
+int cuda_malloc(void** ptr, size_t size);
+int cuda_free(void* ptr);
+int cuda_memcpy_htod(void* dst, const void* src, size_t size);
+int cuda_memcpy_dtoh(void* dst, const void* src, size_t size);
+int cuda_memcpy_dtod(void* dst, const void* src, size_t size);
+int cuda_device_synchronize(void);
+int cuda_get_last_error(void);
+int cuda_peek_at_last_error(void);
+int cuda_mem_get_info(size_t* free_bytes, size_t* total_bytes);
+/* ffi.rs:102 */
+int gl_memset_zero(uint64_t* d_buf, size_t n_u64);
+
+/* ---- device info: ffi.rs:305-308 ---- */
+int cuda_set_device(int device);
+int cuda_get_device(int* device);
+int cuda_get_device_count(int* count);
+int cuda_get_device_name(int device, char* name, int max_len);
+
+/* ---- sumcheck, base field: ffi.rs:588-604 (wrapper.cu:1716-1749) ----
+ * d tables of `original_size` u64 each, poly-major; `half` = live length / 2.
+ * round_message writes num_blocks*(d+1) partial sums, d_partial[block*(d+1)+c];
+ * the caller adds the rows. fold writes d_output[i*original_size + y]. */
+int sumcheck_round_message_ffi(const uint64_t* d_polys, uint64_t* d_partial, int d, size_t original_size,
+                               size_t half, int num_blocks);
+int sumcheck_fold_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge, int d,
+                      size_t original_size, size_t half);
+
+/* ---- sumcheck, extension field: ffi.rs:610-627 (wrapper.cu:1751-1785) ----
+ * Elements are (c0, c1) pairs; original_size counts extension elements. */
+int sumcheck_round_message_ext2_ffi(const uint64_t* d_polys, uint64_t* d_partial, int d, size_t original_size,
+                                    size_t half, int num_blocks);
+int sumcheck_fold_ext2_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                           uint64_t challenge_c1, int d, size_t original_size, size_t half);
+
+/* ---- additions: fold fused with the next round's message ----
+ * One pass folds every table on the challenge and accumulates the message of
+ * the following round, so a round streams the tables through HBM once.
+ * `quarter` = live length / 4. Partials as in round_message (extension). */
+int sumcheck_fold_round_ext2_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                                 uint64_t challenge_c1, int d, size_t original_size, size_t quarter,
+                                 uint64_t* d_partial, int num_blocks);
+/* base-field tables in, extension tables out */
+int sumcheck_fold_round_mixed_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                                  uint64_t challenge_c1, int d, size_t original_size, size_t quarter,
+                                  uint64_t* d_partial, int num_blocks);
+int sumcheck_fold_mixed_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                            uint64_t challenge_c1, int d, size_t original_size, size_t half);
+
+/* ---- additions: whole sumcheck proof (host layer) ----
+ * The loop of GpuLinearSumcheckProver::prove (zk-torch-3/src/sumcheck/gpu_prover.rs:37-90)
+ * with the transcript of zk-torch-3/src/transcript.rs started as Transcript::new(label).
+ * Outputs (host): round_msgs[num_var][d+1][2], challenges[num_var][2],
+ * final_evals[d][2], final_eval[2], transcript_state[8] (may be NULL). */
+int gl_sumcheck_prove_device_ffi(const uint64_t* d_tables, int d, int num_var, int base_field,
+                                 const uint8_t* label, size_t label_len, uint64_t* round_msgs,
+                                 uint64_t* challenges, uint64_t* final_evals, uint64_t* final_eval,
+                                 uint64_t* transcript_state);
+int gl_sumcheck_prove_host_ffi(const uint64_t* h_tables, int d, int num_var, int base_field,
+                               const uint8_t* label, size_t label_len, uint64_t* round_msgs,
+                               uint64_t* challenges, uint64_t* final_evals, uint64_t* final_eval,
+                               uint64_t* transcript_state);
+
+/* ---- additions: pinned memory, stream and timing helpers ---- */
+int mb_host_alloc(void** ptr, size_t size);
+int mb_host_free(void* ptr);
+int mb_memcpy_htod_async(void* dst, const void* src, size_t size);
+int mb_memcpy_dtoh_async(void* dst, const void* src, size_t size);
+int mb_stream_sync(void);
+int mb_event_create(void** ev);
+int mb_event_record(void* ev);
+int mb_event_sync(void* ev);
+int mb_event_elapsed_ms(void* start, void* stop, float* ms);
+int mb_event_destroy(void* ev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,133 @@
+// Poseidon2 permutation, width 8 over Goldilocks (4 + 22 + 4 rounds, x^7),
+// plus the leaf / node hash forms used by the Merkle trees.
+//
+// Same function as the reference's poseidon2_permute_8 (cuda/poseidon2.cuh:322-358,
+// CPU twin goldilocks-cuda-rs/src/cpu_poseidon2.rs:120-141) with the same round
+// constants (cuda/poseidon2.cuh:50-94). State words are loose residues in
+// [0, 2^64); callers canonicalise what they write out.
+#pragma once
+#include "gl_field.cuh"
+
+namespace gl {
+
+#define GLP2_RC_EXT_INIT                                                                              \
+    {                                                                                                 \
+        {0xdd5743e7f2a5a5d9ULL, 0xcb3a864e58ada44bULL, 0xd5a3726889dedc0dULL, 0x79365a7f967583c1ULL,  \
+         0xb7820c177b0a3c30ULL, 0x68a60479943b7240ULL, 0x0a22eeab67b97c41ULL, 0xbee9d90e037fa7d4ULL}, \
+        {0xf1dda5b9259dfcb4ULL, 0x27515210be112d59ULL, 0x654a4db8f15f6c3aULL, 0x5a9bfff8c29db0c4ULL,  \
+         0xb72f2628c95a885bULL, 0xffcb54fc166beaddULL, 0xe32f91d59c463772ULL, 0x9e0ff2a9bbea79dbULL}, \
+        {0xce57d6245ddca6b2ULL, 0xb1fc8d402bba1eb1ULL, 0x64df974fb666d528ULL, 0x59e4e5b237e52e78ULL,  \
+         0x5e255e2742caa8fcULL, 0xc4a17304e330ef9aULL, 0x60e3a513cdd9f0b1ULL, 0xbf29a6a5a0c9c8baULL}, \
+        {0xcea721cce82fb11bULL, 0xe5b55eb8098ece81ULL, 0x4ec66bfb89f7c380ULL, 0xc33be12b6ef7e4faULL,  \
+         0xa41b5f5b84c57d7dULL, 0xb526206b2138a936ULL, 0x9f7a5ac62f16eb4eULL, 0x7de77f405f683aa5ULL}, \
+        {0x014ef1197d341346ULL, 0x9725e20825d07394ULL, 0xc8ff2a22516f3604ULL, 0xde1b51f7cf493493ULL,  \
+         0xa7e3af1a53eadb78ULL, 0x9b7b7ee0ddf9f229ULL, 0xf0a460f2dc649e7dULL, 0xdc4448d02c2cb823ULL}, \
+        {0xaa62c88e0b294011ULL, 0x058eb9d810ce9f74ULL, 0x4e3d7a5403566d24ULL, 0xe8ae66da2f8b7a63ULL,  \
+         0x3fdad3b08dae2e0bULL, 0xec81e61303dd409bULL, 0x3cbaa1cd35d31fc4ULL, 0x847f7806eec88ffaULL}, \
+        {0x98ae09a325893803ULL, 0xf8a6475077968838ULL, 0xdf55b7419443de5bULL, 0xdbe15699e696ca70ULL,  \
+         0x8e54a27d8db00424ULL, 0x7679a45cd9d1e12aULL, 0x2844f52be73e0e2fULL, 0xd41f8eb31ada34f8ULL}, \
+        {0xe9dd318bae1f3961ULL, 0xf7462137299efe1aULL, 0x6dbbe06779e1d573ULL, 0xfe35b05cbe707632ULL,  \
+         0x5d8896b12654fd8cULL, 0x6f96ef47c32d4ae2ULL, 0xb0caa221dbbfc0daULL, 0x0bc2a5bf1f238d3fULL}, \
+    }
+#define GLP2_RC_INT_INIT                                                                             \
+    {                                                                                                \
+        0x488897d85ff51f56ULL, 0x1140737ccb162218ULL, 0xa7eeb9215866ed35ULL, 0x9bd2976fee49fcc9ULL,  \
+        0xc0c8f0de580a3fccULL, 0x4fb2dae6ee8fc793ULL, 0x343a89f35f37395bULL, 0x223b525a77ca72c8ULL,  \
+        0x56ccb62574aaa918ULL, 0xc4d507d8027af9edULL, 0xa080673cf0b7e95cULL, 0xf0184884eb70dcf8ULL,  \
+        0x044f10b0cb3d5c69ULL, 0xe9e3f7993938f186ULL, 0x1b761c80e772f459ULL, 0x606cec607a1b5facULL,  \
+        0x14a0c2e1d45f03cdULL, 0x4eace8855398574fULL, 0xf905ca7103eff3e6ULL, 0xf8c8f8d20862c059ULL,  \
+        0xb524fe8bdd678e5aULL, 0xfbb7865901a1ec41ULL,                                                \
+    }
+#define GLP2_DIAG_INIT                                                                               \
+    {                                                                                                \
+        0xa98811a1fed4e3a5ULL, 0x1cc48b54f377e2a0ULL, 0xe40cd4f6c5609a26ULL, 0x11de79ebca97a4a3ULL,  \
+        0x9177c73d8b7e929cULL, 0x2a6fe8085797e791ULL, 0x3de6e93329f8d5adULL, 0x3f7af9125da962feULL,  \
+    }
+
+// All table entries are below p. Statically initialised __constant__ data is
+// loaded with the module on every device that runs it; no init call is needed.
+static const uint64_t h_p2_rc_ext[8][8] = GLP2_RC_EXT_INIT;
+static const uint64_t h_p2_rc_int[22] = GLP2_RC_INT_INIT;
+static const uint64_t h_p2_diag[8] = GLP2_DIAG_INIT;
+#ifdef __CUDACC__
+__constant__ uint64_t d_p2_rc_ext[8][8] = GLP2_RC_EXT_INIT;
+__constant__ uint64_t d_p2_rc_int[22] = GLP2_RC_INT_INIT;
+__constant__ uint64_t d_p2_diag[8] = GLP2_DIAG_INIT;
+#endif
+
+GLF uint64_t p2_rc_ext(int r, int i) {
+#ifdef __CUDA_ARCH__
+    return d_p2_rc_ext[r][i];
+#else
+    return h_p2_rc_ext[r][i];
+#endif
+}
+GLF uint64_t p2_rc_int(int r) {
+#ifdef __CUDA_ARCH__
+    return d_p2_rc_int[r];
+#else
+    return h_p2_rc_int[r];
+#endif
+}
+GLF uint64_t p2_diag(int i) {
+#ifdef __CUDA_ARCH__
+    return d_p2_diag[i];
+#else
+    return h_p2_diag[i];
+#endif
+}
+
+GLF uint64_t sbox7(uint64_t x) {
+    uint64_t x2 = sqr(x), x4 = sqr(x2), x3 = mul(x2, x);
+    return mul(x4, x3);
+}
+
+// [2 3 1 1; 1 2 3 1; 1 1 2 3; 3 1 1 2] on four words.
+GLF void mds4(uint64_t& s0, uint64_t& s1, uint64_t& s2, uint64_t& s3) {
+    uint64_t t01 = add(s0, s1), t23 = add(s2, s3);
+    uint64_t t0123 = add(t01, t23);
+    uint64_t t01123 = add(t0123, s1), t01233 = add(t0123, s3);
+    uint64_t n0 = add(t01123, t01);
+    uint64_t n1 = add(t01123, add(s2, s2));
+    uint64_t n2 = add(t01233, t23);
+    uint64_t n3 = add(t01233, add(s0, s0));
+    s0 = n0; s1 = n1; s2 = n2; s3 = n3;
+}
+
+GLF void mds_light_8(uint64_t* s) {
+    mds4(s[0], s[1], s[2], s[3]);
+    mds4(s[4], s[5], s[6], s[7]);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint64_t sum = add(s[i], s[i + 4]);
+        s[i] = add(s[i], sum);
+        s[i + 4] = add(s[i + 4], sum);
+    }
+}
+
+GLF void p2_full_round(uint64_t* s, int r) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = sbox7(add_c(s[i], p2_rc_ext(r, i)));
+    mds_light_8(s);
+}
+
+GLF void p2_partial_round(uint64_t* s, int r) {
+    s[0] = sbox7(add_c(s[0], p2_rc_int(r)));
+    uint64_t sum = s[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) sum = add(sum, s[i]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = add(mul(s[i], p2_diag(i)), sum);
+}
+
+// In place; loose in, loose out.
+GLF void poseidon2_permute(uint64_t* s) {
+#pragma unroll 1
+    for (int r = 0; r < 4; r++) p2_full_round(s, r);
+#pragma unroll 1
+    for (int r = 0; r < 22; r++) p2_partial_round(s, r);
+#pragma unroll 1
+    for (int r = 4; r < 8; r++) p2_full_round(s, r);
+}
+
+}  // namespace gl

@@ -1,0 +1,298 @@
+// Multilinear sumcheck kernels, generic over the field (a traits class).
+//
+// Work per round of the linear sumcheck (reference kernels
+// cuda/sumcheck_prover.cuh:37-151,171-292 and the almost-Goldilocks twins
+// cuda_almost_goldilocks/almost_sumcheck_prover.cuh:24-218):
+//   message  P(c) = sum_y prod_i (a_i + c (b_i - a_i)),  c = 0..D,
+//            a_i = T_i[2y], b_i = T_i[2y+1]
+//   fold     T_i'[y] = a_i + r (b_i - a_i)
+// The reference launches these as two kernels per round, so every table is read
+// twice. Here the fold on challenge r_k is fused with the message of round k+1:
+// one pass reads four consecutive elements per table, writes the two folded
+// ones and accumulates the next message from them, so each round streams the
+// tables through HBM once (read S, write S/2).
+//
+// Tables are poly-major with a fixed stride (the original table length), the
+// layout of GpuSumcheckState (goldilocks-cuda-rs/src/sumcheck_prover.rs:20-28).
+// Everything written to global memory is canonical.
+#pragma once
+#include "common.cuh"
+#include "gl_field.cuh"
+
+namespace mb {
+namespace sc {
+
+constexpr int BLOCK = 256;
+constexpr int MAX_D = 8;  // cuda/sumcheck_prover.cuh:18-19
+
+// ---- field traits ---------------------------------------------------------
+// WordAdd / WordCanon act on single u64 residues of the base field; block
+// reductions use them on the flattened words of an element.
+struct GlAdd {
+    __device__ __forceinline__ uint64_t operator()(uint64_t a, uint64_t b) const { return gl::add(a, b); }
+};
+struct GlCanon {
+    __device__ __forceinline__ uint64_t operator()(uint64_t a) const { return gl::canon(a); }
+};
+
+struct GlBase {
+    using T = uint64_t;
+    using WordAdd = GlAdd;
+    using WordCanon = GlCanon;
+    static constexpr int NW = 1;
+    static __device__ __forceinline__ T load(const uint64_t* p, size_t i) { return p[i]; }
+    static __device__ __forceinline__ void load2(const uint64_t* p, size_t i, T& a, T& b) {
+        ulonglong2 v = *reinterpret_cast<const ulonglong2*>(p + i);
+        a = v.x; b = v.y;
+    }
+    static __device__ __forceinline__ void store(uint64_t* p, size_t i, T v) { p[i] = gl::canon(v); }
+    static __device__ __forceinline__ void store2(uint64_t* p, size_t i, T a, T b) {
+        *reinterpret_cast<ulonglong2*>(p + i) = make_ulonglong2(gl::canon(a), gl::canon(b));
+    }
+    static __device__ __forceinline__ T add(T a, T b) { return gl::add(a, b); }
+    static __device__ __forceinline__ T sub(T a, T b) { return gl::sub(a, b); }
+    static __device__ __forceinline__ T mul(T a, T b) { return gl::mul(a, b); }
+    static __device__ __forceinline__ T zero() { return 0; }
+    static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v; }
+};
+
+struct GlExt2 {
+    using T = gl::E2;
+    using WordAdd = GlAdd;
+    using WordCanon = GlCanon;
+    static constexpr int NW = 2;
+    static __device__ __forceinline__ T load(const uint64_t* p, size_t i) { return gl::e2_load(p + 2 * i); }
+    static __device__ __forceinline__ void load2(const uint64_t* p, size_t i, T& a, T& b) {
+        a = gl::e2_load(p + 2 * i);
+        b = gl::e2_load(p + 2 * i + 2);
+    }
+    static __device__ __forceinline__ void store(uint64_t* p, size_t i, T v) {
+        gl::e2_store(p + 2 * i, gl::e2_canon(v));
+    }
+    static __device__ __forceinline__ void store2(uint64_t* p, size_t i, T a, T b) {
+        store(p, i, a);
+        store(p, i + 1, b);
+    }
+    static __device__ __forceinline__ T add(T a, T b) { return gl::e2_add(a, b); }
+    static __device__ __forceinline__ T sub(T a, T b) { return gl::e2_sub(a, b); }
+    static __device__ __forceinline__ T mul(T a, T b) { return gl::e2_mul(a, b); }
+    static __device__ __forceinline__ T zero() { return gl::E2{0, 0}; }
+    static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
+};
+
+// ---- block-wide sum of NV residues per thread -------------------------------
+// Warp shuffles, then one shared-memory hop across warps. Thread 0 writes the
+// canonical totals to out[0..NV). blockDim.x must be a multiple of 32.
+template <int NV, class AddFn, class CanonFn>
+__device__ __forceinline__ void block_sum_store(uint64_t (&v)[NV], uint64_t* out, AddFn addf, CanonFn canonf) {
+    __shared__ uint64_t sm[32][NV];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int k = 0; k < NV; k++) v[k] = addf(v[k], __shfl_down_sync(0xffffffffu, v[k], off));
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < NV; k++) sm[warp][k] = v[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+#pragma unroll
+        for (int k = 0; k < NV; k++) v[k] = lane < nw ? sm[lane][k] : 0;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (int k = 0; k < NV; k++) v[k] = addf(v[k], __shfl_down_sync(0xffffffffu, v[k], off));
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < NV; k++) out[k] = canonf(v[k]);
+        }
+    }
+}
+
+// acc[c] += prod_i (val_i + c * diff_i) for c = 0..D; consumes val.
+template <class F, int D>
+__device__ __forceinline__ void accumulate_pair(typename F::T (&val)[D], const typename F::T (&diff)[D],
+                                                typename F::T (&acc)[D + 1]) {
+#pragma unroll
+    for (int c = 0; c <= D; c++) {
+        typename F::T prod = val[0];
+#pragma unroll
+        for (int i = 1; i < D; i++) prod = F::mul(prod, val[i]);
+        acc[c] = F::add(acc[c], prod);
+        if (c < D) {
+#pragma unroll
+            for (int i = 0; i < D; i++) val[i] = F::add(val[i], diff[i]);
+        }
+    }
+}
+
+// Block partial -> global row; optionally the last block to finish adds all rows
+// up ("last block done" pattern: a fence, one atomic ticket per block) and
+// writes the (D+1)*NW canonical totals to final_out, so no second launch and no
+// host-side summation is needed. `counter` must be zero on entry and is reset
+// to zero by the last block. Rows written by other blocks are read with
+// cache-global loads, which never hit a stale L1 line.
+template <class F, int D>
+__device__ __forceinline__ void store_partials(typename F::T (&acc)[D + 1], uint64_t* partial,
+                                                unsigned int* counter, uint64_t* final_out) {
+    constexpr int NV = (D + 1) * F::NW;
+    uint64_t v[NV];
+#pragma unroll
+    for (int c = 0; c <= D; c++) F::to_words(acc[c], v + c * F::NW);
+    block_sum_store<NV>(v, partial + (size_t)blockIdx.x * NV, typename F::WordAdd(), typename F::WordCanon());
+    if (final_out == nullptr) return;
+    __shared__ bool is_last;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        unsigned int ticket = atomicAdd(counter, 1u);
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+#pragma unroll
+    for (int k = 0; k < NV; k++) v[k] = 0;
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+#pragma unroll
+        for (int k = 0; k < NV; k++) v[k] = typename F::WordAdd()(v[k], __ldcg(partial + (size_t)b * NV + k));
+    }
+    block_sum_store<NV>(v, final_out, typename F::WordAdd(), typename F::WordCanon());
+    if (threadIdx.x == 0) *counter = 0;
+}
+
+// ---- round message ----------------------------------------------------------
+// partial[(blockIdx.x * (D+1) + c) * NW ...] = this block's share of P(c).
+template <class F, int D>
+__global__ void __launch_bounds__(D <= 3 ? 1024 : 256)
+round_message_kernel(const uint64_t* __restrict__ polys, size_t stride, size_t half, uint64_t* __restrict__ partial,
+                     unsigned int* counter, uint64_t* final_out) {
+    using T = typename F::T;
+    T acc[D + 1];
+#pragma unroll
+    for (int c = 0; c <= D; c++) acc[c] = F::zero();
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
+        T val[D], diff[D];
+#pragma unroll
+        for (int i = 0; i < D; i++) {
+            T a, b;
+            F::load2(polys + (size_t)i * stride * F::NW, 2 * y, a, b);
+            val[i] = a;
+            diff[i] = F::sub(b, a);
+        }
+        accumulate_pair<F, D>(val, diff, acc);
+    }
+    store_partials<F, D>(acc, partial, counter, final_out);
+}
+
+// ---- plain fold (out of place) ------------------------------------------------
+// out[i*stride + y] = a + r (b - a); blockIdx.y selects the table.
+template <class F>
+__global__ void fold_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, typename F::T r,
+                            size_t stride, size_t half) {
+    using T = typename F::T;
+    const uint64_t* pin = in + (size_t)blockIdx.y * stride * F::NW;
+    uint64_t* pout = out + (size_t)blockIdx.y * stride * F::NW;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
+        T a, b;
+        F::load2(pin, 2 * y, a, b);
+        F::store(pout, y, F::add(a, F::mul(r, F::sub(b, a))));
+    }
+}
+
+// ---- fused fold + next message ---------------------------------------------------
+// Input tables hold 4*quarter live elements each; the fold on r writes
+// 2*quarter elements per table and the message of the following round is
+// accumulated from them. FIn is the input field; the output and the message are
+// always in FOut (a base-field input is lifted by the extension challenge).
+template <class FIn, class FOut>
+struct FoldOp;
+
+template <class F>
+struct FoldOp<F, F> {
+    static __device__ __forceinline__ typename F::T apply(typename F::T a, typename F::T b, typename F::T r) {
+        return F::add(a, F::mul(r, F::sub(b, a)));
+    }
+};
+template <>
+struct FoldOp<GlBase, GlExt2> {
+    static __device__ __forceinline__ gl::E2 apply(uint64_t a, uint64_t b, gl::E2 r) {
+        uint64_t d = gl::sub(b, a);
+        return gl::E2{gl::add(a, gl::mul(r.c0, d)), gl::mul(r.c1, d)};
+    }
+};
+
+template <class FIn, class FOut, int D>
+__global__ void __launch_bounds__(BLOCK)
+fold_message_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, typename FOut::T r_val,
+                    const uint64_t* __restrict__ r_ptr, size_t stride_in, size_t stride_out, size_t quarter,
+                    uint64_t* __restrict__ partial, unsigned int* counter, uint64_t* final_out) {
+    using TI = typename FIn::T;
+    using TO = typename FOut::T;
+    TO r = r_val;
+    if (r_ptr != nullptr) r = FOut::load(r_ptr, 0);
+    TO acc[D + 1];
+#pragma unroll
+    for (int c = 0; c <= D; c++) acc[c] = FOut::zero();
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < quarter; y += step) {
+        TO val[D], diff[D];
+#pragma unroll
+        for (int i = 0; i < D; i++) {
+            TI e0, e1, e2, e3;
+            const uint64_t* pin = in + (size_t)i * stride_in * FIn::NW;
+            FIn::load2(pin, 4 * y, e0, e1);
+            FIn::load2(pin, 4 * y + 2, e2, e3);
+            TO f0 = FoldOp<FIn, FOut>::apply(e0, e1, r);
+            TO f1 = FoldOp<FIn, FOut>::apply(e2, e3, r);
+            FOut::store2(out + (size_t)i * stride_out * FOut::NW, 2 * y, f0, f1);
+            val[i] = f0;
+            diff[i] = FOut::sub(f1, f0);
+        }
+        accumulate_pair<FOut, D>(val, diff, acc);
+    }
+    store_partials<FOut, D>(acc, partial, counter, final_out);
+}
+
+// Last fold of a base-field table pair by an extension challenge (no message).
+template <class FIn, class FOut>
+__global__ void fold_lift_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, typename FOut::T r_val,
+                                 const uint64_t* __restrict__ r_ptr, size_t stride_in, size_t stride_out, size_t half) {
+    typename FOut::T r = r_val;
+    if (r_ptr != nullptr) r = FOut::load(r_ptr, 0);
+    const uint64_t* pin = in + (size_t)blockIdx.y * stride_in * FIn::NW;
+    uint64_t* pout = out + (size_t)blockIdx.y * stride_out * FOut::NW;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
+        typename FIn::T a, b;
+        FIn::load2(pin, 2 * y, a, b);
+        FOut::store(pout, y, FoldOp<FIn, FOut>::apply(a, b, r));
+    }
+}
+
+// Sum `nblocks` block partials of NV words each into out[0..NV): one block.
+template <int BLOCKDIM, class AddFn, class CanonFn>
+__global__ void reduce_partials_kernel(const uint64_t* __restrict__ partial, int nblocks, int nv,
+                                       uint64_t* __restrict__ out) {
+    __shared__ uint64_t sm[BLOCKDIM];
+    for (int k = 0; k < nv; k++) {
+        uint64_t s = 0;
+        for (int b = threadIdx.x; b < nblocks; b += BLOCKDIM) s = AddFn()(s, partial[(size_t)b * nv + k]);
+        sm[threadIdx.x] = s;
+        __syncthreads();
+        for (int off = BLOCKDIM / 2; off > 0; off >>= 1) {
+            if (threadIdx.x < off) sm[threadIdx.x] = AddFn()(sm[threadIdx.x], sm[threadIdx.x + off]);
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) out[k] = CanonFn()(sm[0]);
+        __syncthreads();
+    }
+}
+
+}  // namespace sc
+}  // namespace mb

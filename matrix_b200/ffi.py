@@ -1,0 +1,136 @@
+"""ctypes bindings of the C-ABI (see include/*.h for the declarations)."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIBDIR = os.path.join(HERE, "lib")
+
+c_u64 = ctypes.c_uint64
+c_u64p = ctypes.POINTER(ctypes.c_uint64)
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_size_t = ctypes.c_size_t
+
+
+class LibraryMissing(RuntimeError):
+    """The CUDA library has not been built; there is no fallback."""
+
+
+def _load(name):
+    path = os.path.join(LIBDIR, name)
+    if not os.path.exists(path):
+        raise LibraryMissing(
+            "%s not found: build it with `python -m matrix_b200.build` (needs nvcc). "
+            "This package has no CPU fallback." % path)
+    return ctypes.CDLL(path)
+
+
+_GL = None
+
+# name -> (restype, argtypes); pointers to device memory are passed as integers (c_void_p)
+_GL_SIGNATURES = {
+    "goldilocks_cuda_init": (c_int, []),
+    "poseidon2_cuda_init": (c_int, []),
+    "monolith_cuda_init": (c_int, []),
+    "cuda_malloc": (c_int, [ctypes.POINTER(c_void_p), c_size_t]),
+    "cuda_free": (c_int, [c_void_p]),
+    "cuda_memcpy_htod": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "cuda_memcpy_dtoh": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "cuda_memcpy_dtod": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "cuda_device_synchronize": (c_int, []),
+    "cuda_get_last_error": (c_int, []),
+    "cuda_peek_at_last_error": (c_int, []),
+    "cuda_mem_get_info": (c_int, [ctypes.POINTER(c_size_t), ctypes.POINTER(c_size_t)]),
+    "cuda_set_device": (c_int, [c_int]),
+    "cuda_get_device": (c_int, [ctypes.POINTER(c_int)]),
+    "cuda_get_device_count": (c_int, [ctypes.POINTER(c_int)]),
+    "cuda_get_device_name": (c_int, [c_int, ctypes.c_char_p, c_int]),
+    "gl_memset_zero": (c_int, [c_void_p, c_size_t]),
+    "mb_host_alloc": (c_int, [ctypes.POINTER(c_void_p), c_size_t]),
+    "mb_host_free": (c_int, [c_void_p]),
+    "mb_memcpy_htod_async": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "mb_memcpy_dtoh_async": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "mb_stream_sync": (c_int, []),
+    "mb_event_create": (c_int, [ctypes.POINTER(c_void_p)]),
+    "mb_event_record": (c_int, [c_void_p]),
+    "mb_event_sync": (c_int, [c_void_p]),
+    "mb_event_elapsed_ms": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_float)]),
+    "mb_event_destroy": (c_int, [c_void_p]),
+    "sumcheck_round_message_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int]),
+    "sumcheck_fold_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_size_t, c_size_t]),
+    "sumcheck_round_message_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int]),
+    "sumcheck_fold_ext2_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t]),
+    "sumcheck_fold_round_ext2_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t, c_void_p, c_int]),
+    "sumcheck_fold_round_mixed_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t, c_void_p, c_int]),
+    "sumcheck_fold_mixed_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t]),
+    "gl_sumcheck_prove_device_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
+                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "gl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+}
+
+
+def load_gl():
+    """The Goldilocks library with argument types set. Raises LibraryMissing if it was not built."""
+    global _GL
+    if _GL is None:
+        lib = _load("libgoldilocks_cuda_wrapper.so")
+        for name, (res, args) in _GL_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _GL = lib
+    return _GL
+
+
+def gl_signatures():
+    return dict(_GL_SIGNATURES)
+
+
+class DeviceBuffer:
+    """A caller-owned device allocation obtained from the library's cuda_malloc
+    (the role of DeviceBuffer<u64> in goldilocks-cuda-rs/src/memory.rs)."""
+
+    def __init__(self, lib, nbytes):
+        self.lib = lib
+        self.nbytes = int(nbytes)
+        p = c_void_p()
+        if self.nbytes > 0:
+            rc = lib.cuda_malloc(ctypes.byref(p), self.nbytes)
+            if rc != 0:
+                raise MemoryError("cuda_malloc(%d) failed: %d" % (self.nbytes, rc))
+        self.ptr = p.value or 0
+
+    @classmethod
+    def from_numpy(cls, lib, arr):
+        import numpy as np
+        arr = np.ascontiguousarray(arr)
+        buf = cls(lib, arr.nbytes)
+        if arr.nbytes:
+            rc = lib.cuda_memcpy_htod(buf.ptr, arr.ctypes.data, arr.nbytes)
+            if rc != 0:
+                raise RuntimeError("cuda_memcpy_htod failed: %d" % rc)
+        return buf
+
+    def to_numpy(self, dtype="uint64", count=None, offset_bytes=0):
+        import numpy as np
+        dt = np.dtype(dtype)
+        if count is None:
+            count = (self.nbytes - offset_bytes) // dt.itemsize
+        out = np.empty(count, dtype=dt)
+        if out.nbytes:
+            rc = self.lib.cuda_memcpy_dtoh(out.ctypes.data, self.ptr + offset_bytes, out.nbytes)
+            if rc != 0:
+                raise RuntimeError("cuda_memcpy_dtoh failed: %d" % rc)
+        return out
+
+    def free(self):
+        if self.ptr:
+            self.lib.cuda_free(self.ptr)
+            self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

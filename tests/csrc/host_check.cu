@@ -1,0 +1,34 @@
+// Test-only shim: exposes the host-callable instantiations of the library's
+// field, Poseidon2 and transcript code so they can be compared with the CPU
+// oracle on a machine without a GPU. Not part of the product libraries.
+#include "gl_field.cuh"
+#include "gl_poseidon2.cuh"
+#include "host/gl_transcript.hpp"
+
+extern "C" {
+uint64_t hc_gl_add(uint64_t a, uint64_t b) { return gl::add(a, b); }
+uint64_t hc_gl_sub(uint64_t a, uint64_t b) { return gl::sub(a, b); }
+uint64_t hc_gl_mul(uint64_t a, uint64_t b) { return gl::mul(a, b); }
+uint64_t hc_gl_mul_small(uint64_t a, uint32_t k) { return gl::mul_small(a, k); }
+uint64_t hc_gl_inv(uint64_t a) { return gl::inv(a); }
+void hc_e2_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) {
+    gl::E2 r = gl::e2_mul(gl::E2{a[0], a[1]}, gl::E2{b[0], b[1]});
+    o[0] = r.c0; o[1] = r.c1;
+}
+void hc_e2_inv(const uint64_t* a, uint64_t* o) {
+    gl::E2 r = gl::e2_inv(gl::E2{a[0], a[1]});
+    o[0] = r.c0; o[1] = r.c1;
+}
+void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
+
+// Replays a script of transcript operations: op 0 = absorb(v), 1 = squeeze -> out.
+int hc_transcript_script(const uint8_t* label, size_t n, const int* ops, const uint64_t* vals, int nops, uint64_t* out) {
+    mbhost::Transcript t(label, n);
+    int k = 0;
+    for (int i = 0; i < nops; i++) {
+        if (ops[i] == 0) t.absorb(vals[i]);
+        else out[k++] = t.squeeze();
+    }
+    return k;
+}
+}

@@ -1,0 +1,53 @@
+"""The built libraries load and export every symbol that include/*.h declares
+(no compute calls, so this runs without a GPU)."""
+import ctypes
+import os
+import re
+
+from .conftest import ROOT
+
+HEADERS = {
+    "goldilocks_cuda_wrapper.h": "libgoldilocks_cuda_wrapper.so",
+    "almost_goldilocks_cuda_wrapper.h": "libalmost_goldilocks_cuda_wrapper.so",
+}
+
+
+def _declared(header_path):
+    text = open(header_path).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"^\s*(?:int|void|const char\s*\*)\s+(\w+)\s*\(", text, flags=re.M)
+
+
+def test_every_declared_symbol_is_exported():
+    import matrix_b200.build as b
+    b.build()
+    seen = 0
+    for header, libname in HEADERS.items():
+        hp = os.path.join(ROOT, "include", header)
+        if not os.path.exists(hp):
+            continue
+        lib = ctypes.CDLL(os.path.join(ROOT, "matrix_b200", "lib", libname))
+        names = _declared(hp)
+        assert len(names) > 10
+        for n in names:
+            assert hasattr(lib, n), "%s declares %s but %s does not export it" % (header, n, libname)
+            seen += 1
+    assert seen > 0
+
+
+def test_python_bindings_cover_header():
+    from matrix_b200 import ffi
+    names = set(_declared(os.path.join(ROOT, "include", "goldilocks_cuda_wrapper.h")))
+    bound = set(ffi.gl_signatures())
+    assert bound <= names, bound - names
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    from matrix_b200 import ffi
+    monkeypatch.setattr(ffi, "LIBDIR", str(tmp_path))
+    monkeypatch.setattr(ffi, "_GL", None)
+    try:
+        ffi.load_gl()
+        raise AssertionError("expected LibraryMissing")
+    except ffi.LibraryMissing:
+        pass

@@ -1,0 +1,89 @@
+"""The library's own field / Poseidon2 / transcript code, compiled for the host,
+against the oracle and Python integers (no GPU needed)."""
+import ctypes
+import random
+
+import numpy as np
+
+from .conftest import GL_P
+
+P = GL_P
+u64 = ctypes.c_uint64
+
+
+def _setup(hc):
+    for name in ("hc_gl_add", "hc_gl_sub", "hc_gl_mul", "hc_gl_inv"):
+        getattr(hc, name).restype = u64
+        getattr(hc, name).argtypes = [u64, u64] if name != "hc_gl_inv" else [u64]
+    hc.hc_gl_mul_small.restype = u64
+    hc.hc_gl_mul_small.argtypes = [u64, ctypes.c_uint32]
+
+
+def test_loose_arithmetic_is_correct_mod_p(hostcheck):
+    _setup(hostcheck)
+    rnd = random.Random(7)
+    edge = [0, 1, P - 1, P, P + 1, 2**64 - 1, 2**64 - 2, 2**32 - 1, 2**32, 2**63, 0xFFFFFFFF00000000]
+    vals = edge + [rnd.randrange(2**64) for _ in range(300)]
+    for a in vals:
+        for b in edge + [rnd.randrange(2**64) for _ in range(20)]:
+            assert hostcheck.hc_gl_add(a, b) % P == (a + b) % P
+            assert hostcheck.hc_gl_sub(a, b) % P == (a - b) % P
+            assert hostcheck.hc_gl_mul(a, b) % P == (a * b) % P
+        assert hostcheck.hc_gl_mul_small(a, 7) % P == (a * 7) % P
+        assert hostcheck.hc_gl_mul_small(a, 2**32 - 1) % P == (a * (2**32 - 1)) % P
+    for a in vals[:40]:
+        inv = hostcheck.hc_gl_inv(a) % P
+        assert (inv * a) % P == (1 if a % P else 0)
+
+
+def test_ext2_mul_inv(hostcheck):
+    rnd = random.Random(8)
+    for _ in range(500):
+        a = [rnd.randrange(2**64), rnd.randrange(2**64)]
+        b = [rnd.randrange(2**64), rnd.randrange(2**64)]
+        A, B, O = (u64 * 2)(*a), (u64 * 2)(*b), (u64 * 2)()
+        hostcheck.hc_e2_mul(A, B, O)
+        assert O[0] % P == (a[0] * b[0] + 7 * a[1] * b[1]) % P
+        assert O[1] % P == (a[0] * b[1] + a[1] * b[0]) % P
+    for _ in range(20):
+        a = [rnd.randrange(P), rnd.randrange(P)]
+        A, I, O = (u64 * 2)(*a), (u64 * 2)(), (u64 * 2)()
+        hostcheck.hc_e2_inv(A, I)
+        hostcheck.hc_e2_mul(A, I, O)
+        assert (O[0] % P, O[1] % P) == (1, 0)
+
+
+def test_poseidon2_matches_oracle(hostcheck, oracle):
+    rnd = random.Random(9)
+    for k in range(50):
+        inp = list(range(8)) if k == 0 else [rnd.randrange(P) for _ in range(8)]
+        a, b = (u64 * 8)(*inp), (u64 * 8)(*inp)
+        hostcheck.hc_poseidon2(a)
+        oracle.gl_poseidon2_permute(b)
+        assert [x % P for x in a] == list(b)
+
+
+def test_transcript_matches_oracle(hostcheck, oracle):
+    # Random scripts of absorbs and squeezes against the oracle's transcript.
+    class T(ctypes.Structure):
+        _fields_ = [("sponge", u64 * 8), ("in_buf", u64 * 4), ("out_buf", u64 * 4),
+                    ("in_count", ctypes.c_int), ("out_count", ctypes.c_int), ("perms", u64)]
+    oracle.gl_transcript_squeeze.restype = u64
+    oracle.gl_transcript_absorb.argtypes = [ctypes.c_void_p, u64]
+    rnd = random.Random(10)
+    for trial in range(20):
+        nops = rnd.randrange(1, 60)
+        ops = [rnd.choice([0, 0, 1]) for _ in range(nops)]
+        vals = [rnd.randrange(P) for _ in range(nops)]
+        label = bytes(rnd.randrange(256) for _ in range(rnd.randrange(0, 9)))
+        out = (u64 * nops)()
+        k = hostcheck.hc_transcript_script(label, len(label), (ctypes.c_int * nops)(*ops), (u64 * nops)(*vals), nops, out)
+        t = T()
+        oracle.gl_transcript_new(ctypes.byref(t), label, len(label))
+        exp = []
+        for o, v in zip(ops, vals):
+            if o == 0:
+                oracle.gl_transcript_absorb(ctypes.byref(t), v)
+            else:
+                exp.append(oracle.gl_transcript_squeeze(ctypes.byref(t)))
+        assert list(out[:k]) == exp

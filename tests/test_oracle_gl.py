@@ -1,0 +1,106 @@
+"""CPU tests of the Goldilocks oracle: field arithmetic against Python integers,
+Poseidon2 against the vector produced by the reference's own code, and the
+sumcheck prover against the tiny cases of the reference's tests."""
+import ctypes
+import json
+import os
+import random
+
+import numpy as np
+
+from .conftest import GL_P, ROOT, field_elems
+
+P = GL_P
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def test_field_ops_match_python_ints(oracle):
+    rnd = random.Random(1)
+    edge = [0, 1, 2, P - 1, P - 2, 2**32, 2**32 - 1, 2**63, P // 2]
+    vals = edge + [rnd.randrange(P) for _ in range(2000)]
+    for a in vals[:60]:
+        assert oracle.gl_inv(a) == (pow(a, P - 2, P))
+    for _ in range(3000):
+        a, e = rnd.choice(vals), rnd.randrange(1, 50)
+        assert oracle.gl_pow(a, e) == pow(a, e, P)
+
+
+def test_poseidon2_matches_reference_code_vector(oracle):
+    # tests/golden/gl_poseidon2.json holds outputs of the reference's own
+    # poseidon2_permute_8 (cuda/poseidon2.cuh:322-358) compiled host-side.
+    vec = json.load(open(os.path.join(GOLDEN, "gl_poseidon2.json")))
+    for case in vec["permute"]:
+        s = (ctypes.c_uint64 * 8)(*case["in"])
+        oracle.gl_poseidon2_permute(s)
+        assert list(s) == case["out"]
+
+
+def _py_round_message(polys, d, n):
+    half = n // 2
+    out = []
+    for c in range(d + 1):
+        acc = 0
+        for y in range(half):
+            prod = 1
+            for i in range(d):
+                a, b = int(polys[i * n + 2 * y]), int(polys[i * n + 2 * y + 1])
+                prod = prod * ((a + c * (b - a)) % P) % P
+            acc = (acc + prod) % P
+        out.append(acc)
+    return out
+
+
+def test_base_round_and_fold_match_python(oracle):
+    # The deterministic inputs of the reference's test_gpu_sumcheck_vs_cpu_large
+    # (goldilocks-cuda-rs/src/sumcheck_prover.rs:527-556), at 6 variables.
+    nv, d = 6, 3
+    n = 1 << nv
+    polys = np.array([(i * m + k) % P for (m, k) in ((37, 1), (53, 7), (71, 13)) for i in range(n)], dtype=np.uint64)
+    cur = polys.copy()
+    size = n
+    for rnd_i in range(nv):
+        half = size // 2
+        msg = np.zeros(d + 1, dtype=np.uint64)
+        oracle.oracle_gl_round_message(cur.ctypes.data, d, n, half, msg.ctypes.data)
+        live = np.concatenate([cur[i * n:i * n + size] for i in range(d)])
+        assert list(map(int, msg)) == _py_round_message(live, d, size)
+        r = rnd_i * 11 + 5
+        nxt = np.zeros_like(cur)
+        oracle.oracle_gl_fold(cur.ctypes.data, nxt.ctypes.data, r, d, n, half)
+        for i in range(d):
+            for y in range(half):
+                a, b = int(cur[i * n + 2 * y]), int(cur[i * n + 2 * y + 1])
+                assert int(nxt[i * n + y]) == (a + r * (b - a)) % P
+        cur, size = nxt, half
+
+
+def test_sumcheck_tiny_claim_and_verifier(oracle):
+    # Tables 1..4 and 5..8 (zk-torch-3/src/sumcheck/cpu_ext2_prover.rs:120-140):
+    # sum of products = 5 + 12 + 21 + 32 = 70.
+    from oracle import pyoracle
+    polys = np.array([1, 2, 3, 4, 5, 6, 7, 8], dtype=np.uint64)
+    res = pyoracle.sumcheck_prove(polys, 2, 2, True, b"test")
+    m0 = res["round_msgs"][0]
+    assert (int(m0[0][0]) + int(m0[1][0])) % P == 70 and int(m0[0][1]) == 0 and int(m0[1][1]) == 0
+    claim = np.array([70, 0], dtype=np.uint64)
+    rc = oracle.oracle_gl_sumcheck_verify(2, 2, b"test", 4, claim.ctypes.data, res["round_msgs"].ctypes.data,
+                                          res["final_eval"].ctypes.data)
+    assert rc == 0
+    bad = res["round_msgs"].copy()
+    bad[1, 2, 0] ^= np.uint64(1)
+    rc = oracle.oracle_gl_sumcheck_verify(2, 2, b"test", 4, claim.ctypes.data, bad.ctypes.data,
+                                          res["final_eval"].ctypes.data)
+    assert rc != 0
+
+
+def test_sumcheck_random_prover_verifier_roundtrip(oracle):
+    from oracle import pyoracle
+    for nv, d, base in ((1, 1, True), (3, 2, True), (5, 3, False), (7, 2, False), (4, 4, True)):
+        n = 1 << nv
+        polys = field_elems(100 + nv, n * d * (1 if base else 2))
+        res = pyoracle.sumcheck_prove(polys, d, nv, base, b"bench")
+        m0 = res["round_msgs"][0]
+        claim = np.array([(int(m0[0][0]) + int(m0[1][0])) % P, (int(m0[0][1]) + int(m0[1][1])) % P], dtype=np.uint64)
+        rc = oracle.oracle_gl_sumcheck_verify(d, nv, b"bench", 5, claim.ctypes.data, res["round_msgs"].ctypes.data,
+                                              res["final_eval"].ctypes.data)
+        assert rc == 0
