@@ -70,3 +70,67 @@ def sumcheck_prove(polys, d, num_var, base_field, label=b"bench"):
     if rc != 0:
         raise RuntimeError("oracle_gl_sumcheck_prove: %d" % rc)
     return dict(round_msgs=rm, challenges=ch, final_evals=fes, final_eval=fe, state=st)
+
+
+# ---- Basefold -------------------------------------------------------------
+_SIGS.update({
+    "oracle_bf_query_words": (sz, [ci, ci]),
+    "oracle_bf_proof_words": (sz, [ci, ci, ci]),
+    "oracle_bf_table_entries": (sz, [ci, ci, ci]),
+    "oracle_bf_table_generate": (None, [ci, ci, ci, u64, vp]),
+    "oracle_bf_bit_reverse_gl": (None, [vp, ci]),
+    "oracle_bf_bit_reverse_ext2": (None, [vp, ci]),
+    "oracle_bf_bhc_interpolate": (None, [vp, vp, vp, ci]),
+    "oracle_bf_encode": (None, [vp, vp, ci, ci]),
+    "oracle_bf_merkle_tree": (None, [vp, sz, ci, vp]),
+    "oracle_bf_commit": (None, [vp, ci, ci, vp, vp, vp]),
+    "oracle_gl_eq_ext2": (None, [vp, ci, vp]),
+    "oracle_gl_eq_base": (None, [vp, ci, vp]),
+    "oracle_bf_open_ext2": (ci, [vp, vp, vp, ci, ci, vp, vp, ctypes.c_char_p, sz, ci, vp, vp]),
+    "oracle_bf_verify_ext2": (ci, [vp, ci, ci, vp, vp, ctypes.c_char_p, sz, ci, vp]),
+})
+
+
+def bf_table(nv, lr, seed=42):
+    """(point, weight) entries of the folding table, levels back to back."""
+    import numpy as np
+    lib = load()
+    total = lib.oracle_bf_table_entries(nv, lr, nv)
+    out = np.zeros(2 * total, dtype=np.uint64)
+    lib.oracle_bf_table_generate(nv, lr, nv, seed, out.ctypes.data)
+    return out
+
+
+def bf_commit(evals, nv, lr):
+    """Returns (codeword, bh_evals, tree) as uint64 arrays."""
+    import numpy as np
+    lib = load()
+    evals = np.ascontiguousarray(evals, dtype=np.uint64)
+    cw = np.zeros(1 << (nv + lr), dtype=np.uint64)
+    bh = np.zeros(1 << nv, dtype=np.uint64)
+    tree = np.zeros(4 * ((1 << (nv + lr)) - 1), dtype=np.uint64)
+    lib.oracle_bf_commit(evals.ctypes.data, nv, lr, cw.ctypes.data, bh.ctypes.data, tree.ctypes.data)
+    return cw, bh, tree
+
+
+def bf_open(cw, bh, tree, nv, lr, point, table, num_queries, label=b"bench"):
+    """Returns (proof words, transcript state)."""
+    import numpy as np
+    lib = load()
+    proof = np.zeros(lib.oracle_bf_proof_words(nv, lr, num_queries), dtype=np.uint64)
+    st = np.zeros(8, dtype=np.uint64)
+    point = np.ascontiguousarray(point, dtype=np.uint64)
+    rc = lib.oracle_bf_open_ext2(cw.ctypes.data, bh.ctypes.data, tree.ctypes.data, nv, lr, point.ctypes.data,
+                                 table.ctypes.data, label, len(label), num_queries, proof.ctypes.data, st.ctypes.data)
+    if rc != 0:
+        raise RuntimeError("oracle_bf_open_ext2: %d" % rc)
+    return proof, st
+
+
+def bf_verify(root, nv, lr, point, table, num_queries, proof, label=b"bench"):
+    import numpy as np
+    lib = load()
+    root = np.ascontiguousarray(root, dtype=np.uint64)
+    point = np.ascontiguousarray(point, dtype=np.uint64)
+    return lib.oracle_bf_verify_ext2(root.ctypes.data, nv, lr, point.ctypes.data, table.ctypes.data, label, len(label),
+                                     num_queries, proof.ctypes.data)
