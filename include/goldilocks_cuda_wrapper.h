@@ -92,6 +92,81 @@ int gl_sumcheck_prove_host_ffi(const uint64_t* h_tables, int d, int num_var, int
                                uint64_t* challenges, uint64_t* final_evals, uint64_t* final_eval,
                                uint64_t* transcript_state);
 
+/* ---- Poseidon2: ffi.rs:287-300 (wrapper.cu:863-964) ----
+ * hash_batch permutes n width-8 states (8 words in, 8 out); compress_batch and
+ * merkle_layer write permute(left || right)[0..4]. */
+int poseidon2_hash_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+int poseidon2_compress_batch_ffi(const uint64_t* d_left, const uint64_t* d_right, uint64_t* d_output, int n);
+int poseidon2_merkle_layer_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+
+/* ---- Merkle trees: ffi.rs:549-561 (wrapper.cu:1604-1713) ----
+ * d_tree holds (2 * num_leaves - 1) digests: leaves, each layer, root last. */
+int poseidon2_merkle_tree_gl_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
+int poseidon2_merkle_tree_ext2_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
+
+/* ---- eq tables: ffi.rs:396-410 (wrapper.cu:2040-2110) ----
+ * eq(r, x) for all x, bit i of x <-> r[i]; *d_result is set to the buffer that
+ * holds the table (always d_buf_a here; d_buf_b is scratch). */
+int eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
+int ext2_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
+
+/* ---- Basefold kernels: ffi.rs:416-543 (wrapper.cu:1216-1590) ---- */
+int basefold_bit_reverse_gl_ffi(uint64_t* d_data, int log_n);
+int basefold_bit_reverse_ext2_ffi(uint64_t* d_data, int log_n);
+int basefold_bhc_interpolate_ffi(const uint64_t* d_evals, uint64_t* d_coeffs, uint64_t* d_bh_evals, int num_vars);
+int basefold_encode_ffi(const uint64_t* d_coeffs, uint64_t* d_codeword, int num_vars, int log_rate);
+int basefold_fold_gl_ffi(const uint64_t* d_codeword, const uint64_t* d_table, uint64_t challenge, uint64_t* d_output,
+                         int pair_count);
+int basefold_fold_mixed_ffi(const uint64_t* d_codeword, const uint64_t* d_table, uint64_t challenge_c0,
+                            uint64_t challenge_c1, uint64_t* d_output, int pair_count);
+int basefold_fold_ext2_ffi(const uint64_t* d_codeword, const uint64_t* d_table, uint64_t challenge_c0,
+                           uint64_t challenge_c1, uint64_t* d_output, int pair_count);
+int basefold_sumcheck_interp_gl_ffi(uint64_t* d_data, int pair_count);
+int basefold_sumcheck_interp_ext2_ffi(uint64_t* d_data, int pair_count);
+int basefold_sumcheck_product_gl_ffi(const uint64_t* d_eq, const uint64_t* d_bh, uint64_t* d_partial_c0,
+                                     uint64_t* d_partial_c1, uint64_t* d_partial_c2, int pair_count, int num_blocks);
+int basefold_sumcheck_product_mixed_ffi(const uint64_t* d_eq, const uint64_t* d_bh, uint64_t* d_partial_c0,
+                                        uint64_t* d_partial_c1, uint64_t* d_partial_c2, int pair_count, int num_blocks);
+int basefold_sumcheck_product_ext2_ffi(const uint64_t* d_eq, const uint64_t* d_bh, uint64_t* d_partial_c0,
+                                       uint64_t* d_partial_c1, uint64_t* d_partial_c2, int pair_count, int num_blocks);
+int basefold_sumcheck_eval_gl_ffi(const uint64_t* d_data, uint64_t challenge, uint64_t* d_output, int pair_count);
+int basefold_sumcheck_eval_mixed_ffi(const uint64_t* d_data, uint64_t challenge_c0, uint64_t challenge_c1,
+                                     uint64_t* d_output, int pair_count);
+int basefold_sumcheck_eval_ext2_ffi(const uint64_t* d_data, uint64_t challenge_c0, uint64_t challenge_c1,
+                                    uint64_t* d_output, int pair_count);
+int fused_sumcheck_round_ext2_ffi(const uint64_t* d_eq_in, const uint64_t* d_bh_in, uint64_t challenge_c0,
+                                  uint64_t challenge_c1, uint64_t* d_eq_out, uint64_t* d_bh_out,
+                                  uint64_t* d_partial_c0, uint64_t* d_partial_c1, uint64_t* d_partial_c2,
+                                  int pair_count, int num_blocks);
+int basefold_dot_product_gl_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_partial, int n, int num_blocks);
+int basefold_dot_product_mixed_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_partial, int n,
+                                   int num_blocks);
+
+/* ---- additions: Basefold host layer ----
+ * The objects the reference keeps in Rust: BasefoldTable (basefold.rs:267-362),
+ * BasefoldCommitment::commit_device (:382-414) and open_ext2 (:578-863) with
+ * the Poseidon2 transcript of zk-torch-3/src/transcript.rs. Handles are opaque.
+ * Proof layout (u64 words): eval[2] | oracles[nv][3][2] | folded_roots[nv-1][4] |
+ * final_codeword[2^lr][2] | per query: index, nv value pairs [2][2], sibling
+ * digests of the commitment tree bottom-up, then of each folded tree. */
+size_t basefold_proof_words(int num_vars, int log_rate, int num_queries);
+int basefold_table_create(int num_vars, int log_rate, int num_rounds, uint64_t seed, void** table);
+int basefold_table_destroy(void* table);
+size_t basefold_table_entries(const void* table);
+int basefold_table_download(const void* table, uint64_t* h_entries);
+const uint64_t* basefold_table_level_ptr(const void* table, int level);
+int basefold_commit_device(const uint64_t* d_evals, int num_vars, int log_rate, void** commitment, uint64_t* h_root);
+int basefold_commit_host(const uint64_t* h_evals, int num_vars, int log_rate, void** commitment, uint64_t* h_root);
+int basefold_commitment_destroy(void* commitment);
+const uint64_t* basefold_commitment_codeword(const void* commitment);
+const uint64_t* basefold_commitment_bh_evals(const void* commitment);
+const uint64_t* basefold_commitment_tree(const void* commitment);
+int basefold_open_ext2(const void* commitment, const uint64_t* h_point, const void* table, const uint8_t* label,
+                       size_t label_len, int num_queries, uint64_t* h_proof, uint64_t* h_transcript_state);
+int basefold_prove_host(const uint64_t* h_evals, int num_vars, int log_rate, const uint64_t* h_point,
+                        const void* table, const uint8_t* label, size_t label_len, int num_queries, uint64_t* h_root,
+                        uint64_t* h_proof);
+
 /* ---- additions: pinned memory, stream and timing helpers ---- */
 int mb_host_alloc(void** ptr, size_t size);
 int mb_host_free(void* ptr);

@@ -28,7 +28,10 @@ LIBRARIES = {
     "libgoldilocks_cuda_wrapper.so": [
         "gl_memory.cu",
         "gl_sumcheck.cu",
+        "gl_merkle.cu",
+        "gl_basefold.cu",
         "host/gl_sumcheck_prover.cu",
+        "host/gl_basefold_prover.cu",
     ],
 }
 

@@ -1,0 +1,73 @@
+// eq(r, x) tables for all x in {0,1}^n, bit i of x <-> r[i]
+// (reference: cuda/eq_lagrange.cuh:22-158, convention pinned by the CPU loop in
+// cuda/eq_lagrange_kernels.cu:31-53).
+//
+// The reference doubles the table n times with one launch per variable. The
+// table is a tensor product, so here two small tables (low and high variables)
+// are built by one launch of two blocks and a single write-only pass forms
+// out[x] = lo[x & mask] * hi[x >> n_lo]: one multiplication per element and no
+// re-reading of partial tables. Products of the same factors give the same
+// residue in any order, so the result is bit-identical.
+#pragma once
+#include "sumcheck_kernels.cuh"
+
+namespace mb {
+namespace eq {
+
+// Block b builds the table over variables [lo_b, lo_b + nbits_b) into out_b,
+// doubling in place: out[j + half] = a r, out[j] = a - a r.
+template <class F>
+__global__ void small_tables_kernel(const uint64_t* __restrict__ r, int nbits0, uint64_t* out0, int nbits1,
+                                    uint64_t* out1) {
+    using T = typename F::T;
+    const int var_lo = blockIdx.x == 0 ? 0 : nbits0;
+    const int nbits = blockIdx.x == 0 ? nbits0 : nbits1;
+    uint64_t* out = blockIdx.x == 0 ? out0 : out1;
+    if (threadIdx.x == 0) {
+        uint64_t one[2] = {1, 0};
+        for (int w = 0; w < F::NW; w++) out[w] = one[w];
+    }
+    __syncthreads();
+    for (int i = 0; i < nbits; i++) {
+        T ri = F::load(r, var_lo + i);
+        const size_t half = (size_t)1 << i;
+        for (size_t j = threadIdx.x; j < half; j += blockDim.x) {
+            T a = F::load(out, j);
+            T ar = F::mul(a, ri);
+            F::store(out, j, F::sub(a, ar));
+            F::store(out, j + half, ar);
+        }
+        __syncthreads();
+    }
+}
+
+template <class F>
+__global__ void outer_product_kernel(const uint64_t* __restrict__ lo, const uint64_t* __restrict__ hi, int n_lo,
+                                     uint64_t* __restrict__ out, size_t n) {
+    const size_t mask = ((size_t)1 << n_lo) - 1;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t x = (size_t)blockIdx.x * blockDim.x + threadIdx.x; x < n; x += step)
+        F::store(out, x, F::mul(F::load(lo, x & mask), F::load(hi, x >> n_lo)));
+}
+
+// Builds the table in d_out (2^log_n elements). d_scratch needs room for
+// 2^(log_n/2) + 2^(log_n - log_n/2) elements when log_n > 12 (unused otherwise).
+template <class F>
+inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int log_n, cudaStream_t st) {
+    if (log_n < 0 || log_n > 40 || !d_out || (log_n > 0 && !d_r)) return MB_ERR_ARG;
+    if (log_n <= 12) {
+        small_tables_kernel<F><<<1, 256, 0, st>>>(d_r, log_n, d_out, 0, d_out);
+        return finish_async();
+    }
+    if (!d_scratch) return MB_ERR_ARG;
+    int n_lo = log_n / 2, n_hi = log_n - n_lo;
+    uint64_t* lo = d_scratch;
+    uint64_t* hi = d_scratch + ((size_t)F::NW << n_lo);
+    small_tables_kernel<F><<<2, 1024, 0, st>>>(d_r, n_lo, lo, n_hi, hi);
+    size_t n = (size_t)1 << log_n;
+    outer_product_kernel<F><<<grid_for(n, 256, 8), 256, 0, st>>>(lo, hi, n_lo, d_out, n);
+    return finish_async();
+}
+
+}  // namespace eq
+}  // namespace mb

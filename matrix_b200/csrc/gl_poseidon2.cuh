@@ -50,9 +50,9 @@ static const uint64_t h_p2_rc_ext[8][8] = GLP2_RC_EXT_INIT;
 static const uint64_t h_p2_rc_int[22] = GLP2_RC_INT_INIT;
 static const uint64_t h_p2_diag[8] = GLP2_DIAG_INIT;
 #ifdef __CUDACC__
-__constant__ uint64_t d_p2_rc_ext[8][8] = GLP2_RC_EXT_INIT;
-__constant__ uint64_t d_p2_rc_int[22] = GLP2_RC_INT_INIT;
-__constant__ uint64_t d_p2_diag[8] = GLP2_DIAG_INIT;
+static __constant__ uint64_t d_p2_rc_ext[8][8] = GLP2_RC_EXT_INIT;
+static __constant__ uint64_t d_p2_rc_int[22] = GLP2_RC_INT_INIT;
+static __constant__ uint64_t d_p2_diag[8] = GLP2_DIAG_INIT;
 #endif
 
 GLF uint64_t p2_rc_ext(int r, int i) {

@@ -1,0 +1,537 @@
+// Host layer above the C-ABI for Basefold over Goldilocks: folding table,
+// commitment and extension-field opening, written in C++ where the reference has
+// Rust (no Rust toolchain on the build machine).
+//
+//   BasefoldTable        goldilocks-cuda-rs/src/basefold.rs:267-362
+//   DeviceMerkleTree     goldilocks-cuda-rs/src/merkle.rs:20-160
+//   BasefoldCommitment   goldilocks-cuda-rs/src/basefold.rs:368-414 (commit_device)
+//   open_ext2            goldilocks-cuda-rs/src/basefold.rs:578-863
+//   extract_ext2_queries goldilocks-cuda-rs/src/basefold.rs:2310-2402
+//
+// The protocol order, every transcript interaction and every value that enters
+// the proof are the reference's. The work between them is organised for the
+// B200: the claimed value is read off the first oracle (eval = p(0) + p(1), one
+// pass fewer), the inner sumcheck keeps its tables as plain values and folds
+// them in the same pass that accumulates the next oracle, partial sums are
+// finished on the device, each round issues its sumcheck pass, codeword fold and
+// Merkle tree back to back and synchronises once, and the query phase is one
+// gather kernel and one copy.
+#include <cstring>
+#include <memory>
+#include <vector>
+#include "../basefold_kernels.cuh"
+#include "../eq_kernels.cuh"
+#include "../merkle_kernels.cuh"
+#include "gl_transcript.hpp"
+
+using namespace mb;
+
+namespace mb {
+namespace bf {
+int interpolate_async(const uint64_t*, uint64_t*, uint64_t*, int, cudaStream_t);
+int encode_async(const uint64_t*, uint64_t*, uint64_t*, int, int, cudaStream_t);
+}  // namespace bf
+}  // namespace mb
+
+namespace mbhost {
+
+// ---- small RAII device buffer ----------------------------------------------------
+struct DevBuf {
+    uint64_t* p = nullptr;
+    size_t words = 0;
+    DevBuf() = default;
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+    ~DevBuf() { release(); }
+    int alloc(size_t w) {
+        release();
+        words = w;
+        if (w == 0) return MB_OK;
+        return cudaMalloc(&p, w * sizeof(uint64_t)) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        words = 0;
+    }
+};
+
+// ---- kernels private to the host layer ---------------------------------------------
+
+// weights[k] = 1 / weights[k] for the (point, weight) table.
+__global__ void table_invert_kernel(uint64_t* table, size_t entries) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < entries; k += step)
+        table[2 * k + 1] = gl::canon(gl::inv(table[2 * k + 1]));
+}
+
+// Oracle of the opening's inner sumcheck from tables in value form:
+// with e = (eq[2j], eq[2j+1] - eq[2j]) and b likewise,
+// c0 = sum e0 b0, c1 = sum (e0 b1 + e1 b0), c2 = sum e1 b1
+// (the coefficients cuda/basefold.cuh:334-383 computes after its in-place
+// interp step). BH_BASE: bh holds base-field values.
+template <bool BH_BASE>
+__device__ __forceinline__ void oracle_accumulate(gl::E2 q0, gl::E2 q1, gl::E2 b0, gl::E2 b1, gl::E2& a0, gl::E2& a1,
+                                                  gl::E2& a2) {
+    gl::E2 qd = gl::e2_sub(q1, q0), bd = gl::e2_sub(b1, b0);
+    if (BH_BASE) {
+        a0 = gl::e2_add(a0, gl::e2_mul_base(q0, b0.c0));
+        a1 = gl::e2_add(a1, gl::e2_add(gl::e2_mul_base(q0, bd.c0), gl::e2_mul_base(qd, b0.c0)));
+        a2 = gl::e2_add(a2, gl::e2_mul_base(qd, bd.c0));
+    } else {
+        a0 = gl::e2_add(a0, gl::e2_mul(q0, b0));
+        a1 = gl::e2_add(a1, gl::e2_add(gl::e2_mul(q0, bd), gl::e2_mul(qd, b0)));
+        a2 = gl::e2_add(a2, gl::e2_mul(qd, bd));
+    }
+}
+
+// Block partials, then the last block to finish adds them up into final_out[6].
+__device__ __forceinline__ void oracle_finish(gl::E2 a0, gl::E2 a1, gl::E2 a2, uint64_t* partial, unsigned int* counter,
+                                              uint64_t* final_out) {
+    uint64_t v[6] = {a0.c0, a0.c1, a1.c0, a1.c1, a2.c0, a2.c1};
+    sc::block_sum_store<6>(v, partial + 6 * (size_t)blockIdx.x, sc::GlAdd(), sc::GlCanon());
+    __shared__ bool is_last;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        is_last = (atomicAdd(counter, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+#pragma unroll
+    for (int k = 0; k < 6; k++) v[k] = 0;
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += blockDim.x)
+#pragma unroll
+        for (int k = 0; k < 6; k++) v[k] = gl::add(v[k], __ldcg(partial + 6 * (size_t)b + k));
+    sc::block_sum_store<6>(v, final_out, sc::GlAdd(), sc::GlCanon());
+    if (threadIdx.x == 0) *counter = 0;
+}
+
+// First oracle: eq (extension) x bh (base), both of length 2 * pairs.
+__global__ void __launch_bounds__(256)
+oracle0_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ bh, size_t pairs, uint64_t* partial,
+               unsigned int* counter, uint64_t* final_out) {
+    gl::E2 a0{0, 0}, a1{0, 0}, a2{0, 0};
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < pairs; j += step) {
+        gl::E2 q0 = gl::e2_load(eq + 4 * j), q1 = gl::e2_load(eq + 4 * j + 2);
+        ulonglong2 b = *reinterpret_cast<const ulonglong2*>(bh + 2 * j);
+        oracle_accumulate<true>(q0, q1, gl::E2{b.x, 0}, gl::E2{b.y, 0}, a0, a1, a2);
+    }
+    oracle_finish(a0, a1, a2, partial, counter, final_out);
+}
+
+// One round: fold eq and bh on r (four inputs -> two outputs each) and
+// accumulate the oracle of the folded tables. BH_BASE: bh_in is base field
+// (round 0); outputs are always extension elements.
+template <bool BH_BASE>
+__global__ void __launch_bounds__(256)
+open_round_kernel(const uint64_t* __restrict__ eq_in, const uint64_t* __restrict__ bh_in, gl::E2 r,
+                  uint64_t* __restrict__ eq_out, uint64_t* __restrict__ bh_out, size_t quarter, uint64_t* partial,
+                  unsigned int* counter, uint64_t* final_out) {
+    gl::E2 a0{0, 0}, a1{0, 0}, a2{0, 0};
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < quarter; y += step) {
+        const uint64_t* pe = eq_in + 8 * y;
+        gl::E2 e0 = gl::e2_load(pe), e1 = gl::e2_load(pe + 2), e2 = gl::e2_load(pe + 4), e3 = gl::e2_load(pe + 6);
+        gl::E2 q0 = gl::e2_add(e0, gl::e2_mul(r, gl::e2_sub(e1, e0)));
+        gl::E2 q1 = gl::e2_add(e2, gl::e2_mul(r, gl::e2_sub(e3, e2)));
+        gl::E2 b0, b1;
+        if (BH_BASE) {
+            ulonglong2 u = *reinterpret_cast<const ulonglong2*>(bh_in + 4 * y);
+            ulonglong2 w = *reinterpret_cast<const ulonglong2*>(bh_in + 4 * y + 2);
+            uint64_t d0 = gl::sub(u.y, u.x), d1 = gl::sub(w.y, w.x);
+            b0 = gl::E2{gl::add(u.x, gl::mul(r.c0, d0)), gl::mul(r.c1, d0)};
+            b1 = gl::E2{gl::add(w.x, gl::mul(r.c0, d1)), gl::mul(r.c1, d1)};
+        } else {
+            const uint64_t* pb = bh_in + 8 * y;
+            gl::E2 f0 = gl::e2_load(pb), f1 = gl::e2_load(pb + 2), f2 = gl::e2_load(pb + 4), f3 = gl::e2_load(pb + 6);
+            b0 = gl::e2_add(f0, gl::e2_mul(r, gl::e2_sub(f1, f0)));
+            b1 = gl::e2_add(f2, gl::e2_mul(r, gl::e2_sub(f3, f2)));
+        }
+        q0 = gl::e2_canon(q0); q1 = gl::e2_canon(q1); b0 = gl::e2_canon(b0); b1 = gl::e2_canon(b1);
+        gl::e2_store(eq_out + 4 * y, q0);
+        gl::e2_store(eq_out + 4 * y + 2, q1);
+        gl::e2_store(bh_out + 4 * y, b0);
+        gl::e2_store(bh_out + 4 * y + 2, b1);
+        oracle_accumulate<false>(q0, q1, b0, b1, a0, a1, a2);
+    }
+    oracle_finish(a0, a1, a2, partial, counter, final_out);
+}
+
+// Query phase: every value pair and authentication path of every query in
+// one launch. Block q handles query q; out is the per-query part of the proof.
+struct QueryLevels {
+    int nv, lr;
+    const uint64_t* commit_cw;    // base-field codeword
+    const uint64_t* commit_tree;  // its tree
+    const uint64_t* fcw[40];      // folded codewords (extension)
+    const uint64_t* ftree[40];    // their trees
+};
+
+__device__ __forceinline__ void copy_path(const uint64_t* tree, size_t num_leaves, size_t leaf, uint64_t* out) {
+    // layer l starts at 4 * (2 * num_leaves - (num_leaves >> (l - 1))) for l >= 1
+    int depth = 0;
+    for (size_t s = num_leaves; s > 1; s >>= 1) depth++;
+    for (int t = threadIdx.x; t < depth * 4; t += blockDim.x) {
+        int l = t >> 2, w = t & 3;
+        size_t off = 2 * num_leaves - ((2 * num_leaves) >> l);  // digests before layer l
+        size_t sib = (leaf >> l) ^ 1;
+        out[t] = tree[4 * (off + sib) + w];
+    }
+}
+
+__global__ void query_gather_kernel(QueryLevels lv, const uint64_t* __restrict__ leaf_idx, uint64_t* __restrict__ out,
+                                    size_t qwords) {
+    const int nv = lv.nv, lr = lv.lr;
+    uint64_t* pq = out + (size_t)blockIdx.x * qwords;
+    const size_t leaf = (size_t)leaf_idx[blockIdx.x];
+    uint64_t* vals = pq + 1;
+    if (threadIdx.x == 0) {
+        pq[0] = leaf;
+        vals[0] = lv.commit_cw[2 * leaf];
+        vals[1] = 0;
+        vals[2] = lv.commit_cw[2 * leaf + 1];
+        vals[3] = 0;
+    }
+    for (int t = threadIdx.x; t < (nv - 1) * 4; t += blockDim.x) {
+        int i = t >> 2, w = t & 3;
+        size_t idx = leaf >> (i + 1);
+        vals[4 * (i + 1) + w] = lv.fcw[i][4 * idx + w];
+    }
+    uint64_t* pp = vals + 4 * nv;
+    size_t leaves = (size_t)1 << (nv + lr - 1);
+    copy_path(lv.commit_tree, leaves, leaf, pp);
+    pp += 4 * (nv + lr - 1);
+    for (int i = 0; i <= nv - 2; i++) {
+        size_t fl = (size_t)1 << (nv + lr - 2 - i);
+        copy_path(lv.ftree[i], fl, leaf >> (i + 1), pp);
+        pp += 4 * (nv + lr - 2 - i);
+    }
+}
+
+// ---- BasefoldTable ------------------------------------------------------------------
+class BasefoldTable {
+public:
+    // basefold.rs:281-321: xorshift64 (13, 7, 17) mod p; x1 redrawn while equal
+    // to x0; weight = 1 / (x1 - x0). The stream is sequential and runs on the
+    // host; the inversions run on the device.
+    int generate(int nv, int lr, int num_rounds, uint64_t seed) {
+        if (nv < 1 || lr < 0 || num_rounds < 1 || num_rounds > nv || nv + lr > 34) return MB_ERR_ARG;
+        num_vars = nv; log_rate = lr; rounds = num_rounds;
+        level_offsets.clear(); level_sizes.clear();
+        size_t total = 0;
+        for (int i = 0; i < num_rounds; i++) {
+            level_offsets.push_back(total);
+            level_sizes.push_back((size_t)1 << (nv + lr - i - 1));
+            total += level_sizes.back();
+        }
+        entries = total;
+        uint64_t* h = nullptr;
+        MB_CUDA(cudaMallocHost(&h, total * 2 * sizeof(uint64_t)));
+        uint64_t s = seed;
+        auto next = [&s]() { s ^= s << 13; s ^= s >> 7; s ^= s << 17; return s % gl::P; };
+        for (size_t k = 0; k < total; k++) {
+            uint64_t x0 = next(), x1 = next();
+            while (x1 == x0) x1 = next();
+            h[2 * k] = x0;
+            h[2 * k + 1] = x1 >= x0 ? x1 - x0 : x1 + (gl::P - x0);
+        }
+        int rc = d_entries.alloc(total * 2);
+        if (rc == MB_OK && cudaMemcpyAsync(d_entries.p, h, total * 2 * sizeof(uint64_t), cudaMemcpyHostToDevice,
+                                           MB_STREAM) != cudaSuccess)
+            rc = MB_ERR_CUDA;
+        if (rc == MB_OK) {
+            table_invert_kernel<<<grid_for(total, 256, 8), 256, 0, MB_STREAM>>>(d_entries.p, total);
+            rc = finish_sync();
+        }
+        cudaFreeHost(h);
+        return rc;
+    }
+    const uint64_t* device_level_ptr(int level) const { return d_entries.p + 2 * level_offsets[level]; }
+
+    int num_vars = 0, log_rate = 0, rounds = 0;
+    size_t entries = 0;
+    std::vector<size_t> level_offsets, level_sizes;
+    DevBuf d_entries;
+};
+
+// ---- BasefoldCommitment -----------------------------------------------------------------
+class BasefoldCommitment {
+public:
+    // commit_device (basefold.rs:382-414): interpolate, encode, Merkle tree.
+    int commit_device(const uint64_t* d_evals, int nv, int lr) {
+        if (nv < 1 || lr < 0 || nv + lr > 32 || !d_evals) return MB_ERR_ARG;
+        num_vars = nv; log_rate = lr;
+        size_t n = (size_t)1 << nv, cw_len = (size_t)1 << (nv + lr);
+        DevBuf coeffs;
+        int rc = coeffs.alloc(n);
+        if (rc == MB_OK) rc = d_bh_evals.alloc(n);
+        if (rc == MB_OK) rc = d_codeword.alloc(cw_len);
+        if (rc == MB_OK) rc = d_tree.alloc(4 * (cw_len - 1));
+        if (rc != MB_OK) return rc;
+        rc = bf::interpolate_async(d_evals, coeffs.p, d_bh_evals.p, nv, MB_STREAM);
+        if (rc == MB_OK) rc = bf::encode_async(coeffs.p, coeffs.p, d_codeword.p, nv, lr, MB_STREAM);
+        if (rc == MB_OK) rc = mk::build_tree<false>(d_codeword.p, d_tree.p, cw_len / 2, MB_STREAM);
+        if (rc != MB_OK) return rc;
+        MB_CUDA(cudaMemcpyAsync(root, d_tree.p + 4 * (cw_len - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        return MB_OK;
+    }
+    uint64_t root[4] = {0, 0, 0, 0};
+    int num_vars = 0, log_rate = 0;
+    DevBuf d_codeword, d_bh_evals, d_tree;
+};
+
+size_t query_words(int nv, int lr) {
+    size_t w = 1 + (size_t)nv * 4 + 4 * (size_t)(nv + lr - 1);
+    for (int i = 0; i <= nv - 2; i++) w += 4 * (size_t)(nv + lr - 2 - i);
+    return w;
+}
+size_t proof_words(int nv, int lr, int nq) {
+    return 2 + (size_t)nv * 6 + (size_t)(nv - 1) * 4 + ((size_t)2 << lr) + (size_t)nq * query_words(nv, lr);
+}
+
+// open_ext2 (basefold.rs:578-863). Writes the proof as
+//   eval[2] | oracles[nv][3][2] | folded_roots[nv-1][4] | final_codeword[2^lr][2] |
+//   per query: index, nv value pairs [2][2], path in the commitment tree,
+//   paths in the nv-1 folded trees (sibling digests bottom-up).
+int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const BasefoldTable& table, Transcript& t,
+              int num_queries, uint64_t* proof) {
+    const int nv = cm.num_vars, lr = cm.log_rate;
+    if (nv < 2 || nv > 38 || table.num_vars != nv || table.log_rate != lr || table.rounds < nv || num_queries < 0)
+        return MB_ERR_ARG;
+    const size_t n = (size_t)1 << nv, cw_len = (size_t)1 << (nv + lr);
+    uint64_t* p_eval = proof;
+    uint64_t* p_oracles = proof + 2;
+    uint64_t* p_roots = p_oracles + (size_t)nv * 6;
+    uint64_t* p_final = p_roots + (size_t)(nv - 1) * 4;
+    uint64_t* p_queries = p_final + ((size_t)2 << lr);
+
+    t.observe_hash(cm.root);
+    for (int i = 0; i < nv; i++) t.observe_ext2(Ext2{point[2 * i], point[2 * i + 1]});
+
+    // device state
+    DevBuf eq_a, eq_b, bh_fp, bh_a, bh_b, d_point, partial, small, stage;
+    const int grid_max = grid_for(n / 2, 256, 4);
+    int rc = eq_a.alloc(2 * n);
+    if (rc == MB_OK) rc = eq_b.alloc(n);
+    if (rc == MB_OK) rc = bh_fp.alloc(n);
+    if (rc == MB_OK) rc = bh_a.alloc(n);
+    if (rc == MB_OK) rc = bh_b.alloc(n / 2 > 2 ? n / 2 : 2);
+    if (rc == MB_OK) rc = d_point.alloc(2 * (size_t)nv);
+    if (rc == MB_OK) rc = partial.alloc(6 * (size_t)grid_max);
+    if (rc == MB_OK) rc = small.alloc(16);  // [0..6) oracle words, [8] ticket counter
+    if (rc != MB_OK) return rc;
+    unsigned int* counter = reinterpret_cast<unsigned int*>(small.p + 8);
+    MB_CUDA(cudaMemsetAsync(small.p, 0, 16 * sizeof(uint64_t), MB_STREAM));
+    uint64_t* h_small = nullptr;  // pinned landing zone: 6 oracle words + 4 root words
+    MB_CUDA(cudaMallocHost(&h_small, 16 * sizeof(uint64_t)));
+    struct PinnedGuard { uint64_t* p; ~PinnedGuard() { cudaFreeHost(p); } } guard{h_small};
+
+    MB_CUDA(cudaMemcpyAsync(d_point.p, point, sizeof(uint64_t) * 2 * nv, cudaMemcpyHostToDevice, MB_STREAM));
+    // eq table; bh_a doubles as scratch for the two small tables (free until round 0 writes it)
+    rc = eq::build<sc::GlExt2>(d_point.p, eq_a.p, bh_a.p, nv, MB_STREAM);
+    if (rc != MB_OK) return rc;
+    // evaluations back in natural order (basefold.rs:600-602)
+    if (nv >= 12) {
+        size_t tiles = (size_t)1 << (nv - 12);
+        int g = (int)(tiles < (size_t)sm_count() * 4 ? tiles : (size_t)sm_count() * 4);
+        bf::bit_reverse_tiled_kernel<<<g, 256, 0, MB_STREAM>>>(cm.d_bh_evals.p, bh_fp.p, nv, 1);
+    } else {
+        bf::bit_reverse_copy_kernel<<<grid_for(n, 256, 8), 256, 0, MB_STREAM>>>(cm.d_bh_evals.p, bh_fp.p, nv, 1);
+    }
+
+    // oracle 0 and the claimed value eval = p(0) + p(1) = 2 c0 + c1 + c2
+    oracle0_kernel<<<grid_for(n / 2, 256, 4), 256, 0, MB_STREAM>>>(eq_a.p, bh_fp.p, n / 2, partial.p, counter, small.p);
+    MB_CUDA(cudaMemcpyAsync(h_small, small.p, 48, cudaMemcpyDeviceToHost, MB_STREAM));
+    MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+    std::memcpy(p_oracles, h_small, 48);
+    {
+        gl::E2 c0{h_small[0], h_small[1]}, c1{h_small[2], h_small[3]}, c2{h_small[4], h_small[5]};
+        gl::E2 ev = gl::e2_canon(gl::e2_add(gl::e2_add(c0, c0), gl::e2_add(c1, c2)));
+        p_eval[0] = ev.c0;
+        p_eval[1] = ev.c1;
+    }
+    for (int k = 0; k < 3; k++) t.observe_ext2(Ext2{p_oracles[2 * k], p_oracles[2 * k + 1]});
+
+    // folded codewords and trees, kept for the query phase
+    std::vector<std::unique_ptr<DevBuf>> fcw(nv), ftree(nv - 1);
+    {
+        size_t len = cw_len / 2;
+        for (int i = 0; i < nv; i++) {
+            fcw[i].reset(new DevBuf);
+            rc = fcw[i]->alloc(2 * len);
+            if (rc != MB_OK) return rc;
+            if (i < nv - 1) {
+                ftree[i].reset(new DevBuf);
+                rc = ftree[i]->alloc(4 * (len - 1 > 0 ? len - 1 : 1));
+                if (rc != MB_OK) return rc;
+            }
+            len /= 2;
+        }
+    }
+
+    const uint64_t *eq_cur = eq_a.p, *bh_cur = bh_fp.p;
+    uint64_t *eq_nxt = eq_b.p, *bh_nxt = bh_a.p;
+    size_t live = n;            // current length of the sumcheck tables
+    size_t cw_pairs = cw_len / 2;
+    for (int round = 0; round < nv - 1; round++) {
+        Ext2 ch = t.sample_challenge_ext2();
+        gl::E2 r{ch.c0, ch.c1};
+        size_t quarter = live / 4;
+        int g = grid_for(quarter, 256, 4);
+        if (round == 0) {
+            open_round_kernel<true><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
+                                                              counter, small.p);
+        } else {
+            open_round_kernel<false><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
+                                                               counter, small.p);
+        }
+        if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+        MB_CUDA(cudaMemcpyAsync(h_small, small.p, 48, cudaMemcpyDeviceToHost, MB_STREAM));
+        // codeword fold with this round's table level, then its tree
+        const uint64_t* level = table.device_level_ptr(round);
+        int gf = grid_for(cw_pairs, 256, 8);
+        if (round == 0) {
+            bf::fold_mixed_kernel<<<gf, 256, 0, MB_STREAM>>>(cm.d_codeword.p, level, r, fcw[0]->p, cw_pairs);
+        } else {
+            bf::fold_ext2_kernel<<<gf, 256, 0, MB_STREAM>>>(fcw[round - 1]->p, level, r, fcw[round]->p, cw_pairs);
+        }
+        if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+        rc = mk::build_tree<true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM);
+        if (rc != MB_OK) return rc;
+        MB_CUDA(cudaMemcpyAsync(h_small + 8, ftree[round]->p + 4 * (cw_pairs - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        uint64_t* po = p_oracles + 6 * (size_t)(round + 1);
+        std::memcpy(po, h_small, 48);
+        std::memcpy(p_roots + 4 * (size_t)round, h_small + 8, 32);
+        for (int k = 0; k < 3; k++) t.observe_ext2(Ext2{po[2 * k], po[2 * k + 1]});
+        t.observe_hash(p_roots + 4 * (size_t)round);
+
+        // ping-pong: eq between eq_b and eq_a, bh between bh_a and bh_b
+        eq_cur = eq_nxt;
+        bh_cur = bh_nxt;
+        eq_nxt = (eq_nxt == eq_b.p) ? eq_a.p : eq_b.p;
+        bh_nxt = (bh_nxt == bh_a.p) ? bh_b.p : bh_a.p;
+        live /= 2;
+        cw_pairs /= 2;
+    }
+
+    // last challenge: final fold, no tree
+    {
+        Ext2 ch = t.sample_challenge_ext2();
+        gl::E2 r{ch.c0, ch.c1};
+        bf::fold_ext2_kernel<<<grid_for(cw_pairs, 256, 8), 256, 0, MB_STREAM>>>(
+            fcw[nv - 2]->p, table.device_level_ptr(nv - 1), r, fcw[nv - 1]->p, cw_pairs);
+        if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+        MB_CUDA(cudaMemcpyAsync(p_final, fcw[nv - 1]->p, sizeof(uint64_t) * ((size_t)2 << lr), cudaMemcpyDeviceToHost,
+                                MB_STREAM));
+    }
+
+    // queries: all indices first (basefold.rs:2321-2326), then one gather
+    if (num_queries > 0) {
+        std::vector<uint64_t> idx(num_queries);
+        for (int q = 0; q < num_queries; q++) idx[q] = t.sample_challenge() % (uint64_t)(cw_len / 2);
+        size_t qw = query_words(nv, lr);
+        DevBuf d_idx, d_q;
+        rc = d_idx.alloc(num_queries);
+        if (rc == MB_OK) rc = d_q.alloc(qw * num_queries);
+        if (rc != MB_OK) return rc;
+        MB_CUDA(cudaMemcpyAsync(d_idx.p, idx.data(), sizeof(uint64_t) * num_queries, cudaMemcpyHostToDevice, MB_STREAM));
+        QueryLevels lv;
+        lv.nv = nv; lv.lr = lr;
+        lv.commit_cw = cm.d_codeword.p;
+        lv.commit_tree = cm.d_tree.p;
+        for (int i = 0; i <= nv - 2; i++) { lv.fcw[i] = fcw[i]->p; lv.ftree[i] = ftree[i]->p; }
+        query_gather_kernel<<<num_queries, 128, 0, MB_STREAM>>>(lv, d_idx.p, d_q.p, qw);
+        if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+        MB_CUDA(cudaMemcpyAsync(p_queries, d_q.p, sizeof(uint64_t) * qw * num_queries, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+    } else {
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+    }
+    return MB_OK;
+}
+
+}  // namespace mbhost
+
+// ---- C-ABI of the host layer -----------------------------------------------------------
+using mbhost::BasefoldCommitment;
+using mbhost::BasefoldTable;
+
+extern "C" {
+
+size_t basefold_proof_words(int num_vars, int log_rate, int num_queries) {
+    return mbhost::proof_words(num_vars, log_rate, num_queries);
+}
+
+int basefold_table_create(int num_vars, int log_rate, int num_rounds, uint64_t seed, void** table) {
+    if (!table) return MB_ERR_ARG;
+    auto* t = new BasefoldTable;
+    int rc = t->generate(num_vars, log_rate, num_rounds, seed);
+    if (rc != MB_OK) { delete t; return rc; }
+    *table = t;
+    return MB_OK;
+}
+int basefold_table_destroy(void* table) { delete static_cast<BasefoldTable*>(table); return MB_OK; }
+size_t basefold_table_entries(const void* table) { return static_cast<const BasefoldTable*>(table)->entries; }
+// (point, weight) pairs, levels back to back, to host memory.
+int basefold_table_download(const void* table, uint64_t* h_entries) {
+    auto* t = static_cast<const BasefoldTable*>(table);
+    MB_CUDA(cudaMemcpyAsync(h_entries, t->d_entries.p, t->entries * 16, cudaMemcpyDeviceToHost, MB_STREAM));
+    return cudaStreamSynchronize(MB_STREAM) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+}
+const uint64_t* basefold_table_level_ptr(const void* table, int level) {
+    return static_cast<const BasefoldTable*>(table)->device_level_ptr(level);
+}
+
+int basefold_commit_device(const uint64_t* d_evals, int num_vars, int log_rate, void** commitment, uint64_t* h_root) {
+    if (!commitment) return MB_ERR_ARG;
+    auto* c = new BasefoldCommitment;
+    int rc = c->commit_device(d_evals, num_vars, log_rate);
+    if (rc != MB_OK) { delete c; return rc; }
+    if (h_root) std::memcpy(h_root, c->root, 32);
+    *commitment = c;
+    return MB_OK;
+}
+int basefold_commit_host(const uint64_t* h_evals, int num_vars, int log_rate, void** commitment, uint64_t* h_root) {
+    if (num_vars < 1 || num_vars > 32 || !h_evals) return MB_ERR_ARG;
+    mbhost::DevBuf ev;
+    int rc = ev.alloc((size_t)1 << num_vars);
+    if (rc != MB_OK) return rc;
+    MB_CUDA(cudaMemcpyAsync(ev.p, h_evals, sizeof(uint64_t) << num_vars, cudaMemcpyHostToDevice, MB_STREAM));
+    return basefold_commit_device(ev.p, num_vars, log_rate, commitment, h_root);
+}
+int basefold_commitment_destroy(void* commitment) { delete static_cast<BasefoldCommitment*>(commitment); return MB_OK; }
+// Device pointers of the commitment's parts (owned by the commitment).
+const uint64_t* basefold_commitment_codeword(const void* c) { return static_cast<const BasefoldCommitment*>(c)->d_codeword.p; }
+const uint64_t* basefold_commitment_bh_evals(const void* c) { return static_cast<const BasefoldCommitment*>(c)->d_bh_evals.p; }
+const uint64_t* basefold_commitment_tree(const void* c) { return static_cast<const BasefoldCommitment*>(c)->d_tree.p; }
+
+// Opening at an extension-field point (h_point: num_vars (c0, c1) pairs) with
+// the transcript started as Transcript::new(label). h_proof must hold
+// basefold_proof_words(...) words; h_transcript_state (8 words) may be NULL.
+int basefold_open_ext2(const void* commitment, const uint64_t* h_point, const void* table, const uint8_t* label,
+                       size_t label_len, int num_queries, uint64_t* h_proof, uint64_t* h_transcript_state) {
+    if (!commitment || !h_point || !table || !h_proof) return MB_ERR_ARG;
+    mbhost::Transcript t(label, label_len);
+    int rc = mbhost::open_ext2(*static_cast<const BasefoldCommitment*>(commitment), h_point,
+                               *static_cast<const BasefoldTable*>(table), t, num_queries, h_proof);
+    if (rc == MB_OK && h_transcript_state) std::memcpy(h_transcript_state, t.state(), 64);
+    return rc;
+}
+
+// Commit + open from host evaluations in one call; the commitment is dropped
+// afterwards. h_root receives the commitment root.
+int basefold_prove_host(const uint64_t* h_evals, int num_vars, int log_rate, const uint64_t* h_point, const void* table,
+                        const uint8_t* label, size_t label_len, int num_queries, uint64_t* h_root, uint64_t* h_proof) {
+    void* c = nullptr;
+    int rc = basefold_commit_host(h_evals, num_vars, log_rate, &c, h_root);
+    if (rc != MB_OK) return rc;
+    rc = basefold_open_ext2(c, h_point, table, label, label_len, num_queries, h_proof, nullptr);
+    basefold_commitment_destroy(c);
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+// Poseidon2 Merkle trees over Goldilocks codewords.
+//
+// Tree buffer layout (goldilocks-cuda-rs/src/merkle.rs:266-280): the leaf
+// digests, then every layer above them, the root last; 4 words per digest.
+// Leaf k hashes the codeword pair k: permute([v0, v1, 0^6])[0..4] for base-field
+// pairs, permute([a.c0, a.c1, b.c0, b.c1, 0^4])[0..4] for extension pairs; a node
+// is permute(left || right)[0..4] (goldilocks-cuda-rs/src/cpu_poseidon2.rs:145-183,
+// device twins goldilocks-cuda-rs/cuda/wrapper.cu:1604-1713). Digests are
+// written canonical.
+//
+// Hashing is bound by the integer pipes (about 520 modular multiplications for
+// every 32-byte digest), not by HBM, so every layer is one fully parallel launch
+// with one permutation per thread; only the last few layers, too small to fill
+// the machine, are finished by a single block.
+#pragma once
+#include "common.cuh"
+#include "gl_poseidon2.cuh"
+
+namespace mb {
+namespace mk {
+
+constexpr int BLOCK = 128;
+constexpr int TAIL_NODES = 1024;  // layers of at most this many nodes are finished by one block
+
+__device__ __forceinline__ void store_digest(uint64_t* out, const uint64_t* s) {
+    *reinterpret_cast<ulonglong2*>(out) = make_ulonglong2(gl::canon(s[0]), gl::canon(s[1]));
+    *reinterpret_cast<ulonglong2*>(out + 2) = make_ulonglong2(gl::canon(s[2]), gl::canon(s[3]));
+}
+
+template <bool EXT2>
+__global__ void __launch_bounds__(BLOCK)
+hash_leaves_kernel(const uint64_t* __restrict__ cw, uint64_t* __restrict__ digests, size_t num_leaves) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < num_leaves; k += step) {
+        uint64_t s[8];
+        if (EXT2) {
+            ulonglong2 a = *reinterpret_cast<const ulonglong2*>(cw + 4 * k);
+            ulonglong2 b = *reinterpret_cast<const ulonglong2*>(cw + 4 * k + 2);
+            s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y;
+        } else {
+            ulonglong2 a = *reinterpret_cast<const ulonglong2*>(cw + 2 * k);
+            s[0] = a.x; s[1] = a.y; s[2] = 0; s[3] = 0;
+        }
+        s[4] = s[5] = s[6] = s[7] = 0;
+        gl::poseidon2_permute(s);
+        store_digest(digests + 4 * k, s);
+    }
+}
+
+__device__ __forceinline__ void compress_node(const uint64_t* in, uint64_t* out) {
+    uint64_t s[8];
+    const ulonglong2* p = reinterpret_cast<const ulonglong2*>(in);
+    ulonglong2 a = p[0], b = p[1], c = p[2], d = p[3];
+    s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y;
+    s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
+    gl::poseidon2_permute(s);
+    store_digest(out, s);
+}
+
+// out[k] = compress(in[2k], in[2k+1]) for k < n
+static __global__ void __launch_bounds__(BLOCK)
+compress_layer_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += step) compress_node(in + 8 * k, out + 4 * k);
+}
+
+// Left and right children in separate arrays (poseidon2_compress_batch_ffi).
+static __global__ void __launch_bounds__(BLOCK)
+compress_pairs_kernel(const uint64_t* __restrict__ left, const uint64_t* __restrict__ right,
+                      uint64_t* __restrict__ out, size_t n) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += step) {
+        uint64_t s[8];
+        ulonglong2 a = *reinterpret_cast<const ulonglong2*>(left + 4 * k);
+        ulonglong2 b = *reinterpret_cast<const ulonglong2*>(left + 4 * k + 2);
+        ulonglong2 c = *reinterpret_cast<const ulonglong2*>(right + 4 * k);
+        ulonglong2 d = *reinterpret_cast<const ulonglong2*>(right + 4 * k + 2);
+        s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y;
+        s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
+        gl::poseidon2_permute(s);
+        store_digest(out + 4 * k, s);
+    }
+}
+
+// One block walks every remaining layer above `layer` (of `size` nodes) up to
+// the root; layers are contiguous in the tree buffer.
+static __global__ void __launch_bounds__(BLOCK)
+tree_tail_kernel(uint64_t* layer, size_t size) {
+    while (size > 1) {
+        uint64_t* next = layer + 4 * size;
+        size_t half = size / 2;
+        for (size_t k = threadIdx.x; k < half; k += blockDim.x) compress_node(layer + 8 * k, next + 4 * k);
+        __syncthreads();
+        layer = next;
+        size = half;
+    }
+}
+
+// Full permutation of n width-8 states (poseidon2_hash_batch_ffi).
+static __global__ void __launch_bounds__(BLOCK)
+permute_batch_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += step) {
+        uint64_t s[8];
+        const ulonglong2* p = reinterpret_cast<const ulonglong2*>(in + 8 * k);
+        ulonglong2 a = p[0], b = p[1], c = p[2], d = p[3];
+        s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y;
+        s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
+        gl::poseidon2_permute(s);
+        store_digest(out + 8 * k, s);
+        store_digest(out + 8 * k + 4, s + 4);
+    }
+}
+
+// Layers above the digests already present in tree[0 .. 4*num_leaves).
+inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
+    uint64_t* layer = d_tree;
+    size_t size = num_leaves;
+    while (size > TAIL_NODES) {
+        size_t half = size / 2;
+        compress_layer_kernel<<<grid_for(half, BLOCK, 16), BLOCK, 0, st>>>(layer, layer + 4 * size, half);
+        layer += 4 * size;
+        size = half;
+    }
+    if (size > 1) tree_tail_kernel<<<1, BLOCK, 0, st>>>(layer, size);
+    return finish_async();
+}
+
+template <bool EXT2>
+inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
+    if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
+    hash_leaves_kernel<EXT2><<<grid_for(num_leaves, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, num_leaves);
+    return build_layers(d_tree, num_leaves, st);
+}
+
+}  // namespace mk
+}  // namespace mb

@@ -63,6 +63,47 @@ _GL_SIGNATURES = {
     "sumcheck_fold_round_ext2_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t, c_void_p, c_int]),
     "sumcheck_fold_round_mixed_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t, c_void_p, c_int]),
     "sumcheck_fold_mixed_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t]),
+    "poseidon2_hash_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "poseidon2_compress_batch_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "poseidon2_merkle_layer_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "poseidon2_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "poseidon2_merkle_tree_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "ext2_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "basefold_bit_reverse_gl_ffi": (c_int, [c_void_p, c_int]),
+    "basefold_bit_reverse_ext2_ffi": (c_int, [c_void_p, c_int]),
+    "basefold_bhc_interpolate_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "basefold_encode_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "basefold_fold_gl_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_void_p, c_int]),
+    "basefold_fold_mixed_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_void_p, c_int]),
+    "basefold_fold_ext2_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_void_p, c_int]),
+    "basefold_sumcheck_interp_gl_ffi": (c_int, [c_void_p, c_int]),
+    "basefold_sumcheck_interp_ext2_ffi": (c_int, [c_void_p, c_int]),
+    "basefold_sumcheck_product_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "basefold_sumcheck_product_mixed_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "basefold_sumcheck_product_ext2_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "basefold_sumcheck_eval_gl_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
+    "basefold_sumcheck_eval_mixed_ffi": (c_int, [c_void_p, c_u64, c_u64, c_void_p, c_int]),
+    "basefold_sumcheck_eval_ext2_ffi": (c_int, [c_void_p, c_u64, c_u64, c_void_p, c_int]),
+    "fused_sumcheck_round_ext2_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int]),
+    "basefold_dot_product_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "basefold_dot_product_mixed_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "basefold_proof_words": (c_size_t, [c_int, c_int, c_int]),
+    "basefold_table_create": (c_int, [c_int, c_int, c_int, c_u64, ctypes.POINTER(c_void_p)]),
+    "basefold_table_destroy": (c_int, [c_void_p]),
+    "basefold_table_entries": (c_size_t, [c_void_p]),
+    "basefold_table_download": (c_int, [c_void_p, c_void_p]),
+    "basefold_table_level_ptr": (c_void_p, [c_void_p, c_int]),
+    "basefold_commit_device": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_void_p]),
+    "basefold_commit_host": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_void_p]),
+    "basefold_commitment_destroy": (c_int, [c_void_p]),
+    "basefold_commitment_codeword": (c_void_p, [c_void_p]),
+    "basefold_commitment_bh_evals": (c_void_p, [c_void_p]),
+    "basefold_commitment_tree": (c_void_p, [c_void_p]),
+    "basefold_open_ext2": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int, c_void_p, c_void_p]),
+    "basefold_prove_host": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int,
+                                    c_void_p, c_void_p]),
     "gl_sumcheck_prove_device_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
