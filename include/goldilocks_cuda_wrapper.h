@@ -179,6 +179,15 @@ int mb_event_sync(void* ev);
 int mb_event_elapsed_ms(void* start, void* stop, float* ms);
 int mb_event_destroy(void* ev);
 
+/* ---- additions: launch accounting and per-kernel stopwatch ----
+ * mb_launch_count: kernels this library launched in the process so far.
+ * With profiling on, every launch is bracketed by CUDA events on its stream;
+ * the report holds "name launches total_ms" lines (returns bytes needed). */
+uint64_t mb_launch_count(void);
+int mb_prof_enable(int on);
+int mb_prof_reset(void);
+size_t mb_prof_report(char* buf, size_t cap);
+
 #ifdef __cplusplus
 }
 #endif

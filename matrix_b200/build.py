@@ -27,6 +27,7 @@ FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--default-stream", "per-thread",
 LIBRARIES = {
     "libgoldilocks_cuda_wrapper.so": [
         "gl_memory.cu",
+        "prof.cu",
         "gl_sumcheck.cu",
         "gl_merkle.cu",
         "gl_basefold.cu",

@@ -27,6 +27,8 @@
         if (_e != cudaSuccess) return MB_ERR_CUDA;      \
     } while (0)
 
+#include "prof.cuh"
+
 namespace mb {
 
 // Launch status, then completion of the caller's stream: the reference's entry

@@ -56,16 +56,25 @@ template <class F>
 inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int log_n, cudaStream_t st) {
     if (log_n < 0 || log_n > 40 || !d_out || (log_n > 0 && !d_r)) return MB_ERR_ARG;
     if (log_n <= 12) {
-        small_tables_kernel<F><<<1, 256, 0, st>>>(d_r, log_n, d_out, 0, d_out);
+        {
+            MB_KERNEL_ON("small_tables", st);
+            small_tables_kernel<F><<<1, 256, 0, st>>>(d_r, log_n, d_out, 0, d_out);
+        }
         return finish_async();
     }
     if (!d_scratch) return MB_ERR_ARG;
     int n_lo = log_n / 2, n_hi = log_n - n_lo;
     uint64_t* lo = d_scratch;
     uint64_t* hi = d_scratch + ((size_t)F::NW << n_lo);
-    small_tables_kernel<F><<<2, 1024, 0, st>>>(d_r, n_lo, lo, n_hi, hi);
+    {
+        MB_KERNEL_ON("small_tables", st);
+        small_tables_kernel<F><<<2, 1024, 0, st>>>(d_r, n_lo, lo, n_hi, hi);
+    }
     size_t n = (size_t)1 << log_n;
-    outer_product_kernel<F><<<grid_for(n, 256, 8), 256, 0, st>>>(lo, hi, n_lo, d_out, n);
+    {
+        MB_KERNEL_ON("outer_product", st);
+        outer_product_kernel<F><<<grid_for(n, 256, 8), 256, 0, st>>>(lo, hi, n_lo, d_out, n);
+    }
     return finish_async();
 }
 

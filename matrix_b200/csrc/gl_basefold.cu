@@ -33,7 +33,10 @@ int run_layers(const uint64_t* in, uint64_t* out, int log_n, int first_bit, int 
         size_t tiles = (size_t)1 << (log_n - nbits - cbits);
         size_t smem = sizeof(uint64_t) << (nbits + cbits);
         int grid = (int)(tiles < (size_t)sm_count() * 4 ? tiles : (size_t)sm_count() * 4);
-        bit_layers_kernel<Op><<<grid, BLOCK, smem, st>>>(src, out, log_n, bit, nbits, cbits);
+        {
+            MB_KERNEL_ON("bit_layers", st);
+            bit_layers_kernel<Op><<<grid, BLOCK, smem, st>>>(src, out, log_n, bit, nbits, cbits);
+        }
         src = out;
         bit += nbits;
         left -= nbits;
@@ -46,9 +49,15 @@ int bit_reverse_out_of_place(const uint64_t* in, uint64_t* out, int log_n, int c
     if (log_n >= 12) {
         size_t tiles = (size_t)1 << (log_n - 12);
         int grid = (int)(tiles < (size_t)sm_count() * 4 ? tiles : (size_t)sm_count() * 4);
-        bit_reverse_tiled_kernel<<<grid, 256, 0, st>>>(in, out, log_n, copies);
+        {
+            MB_KERNEL_ON("bit_reverse_tiled", st);
+            bit_reverse_tiled_kernel<<<grid, 256, 0, st>>>(in, out, log_n, copies);
+        }
     } else {
-        bit_reverse_copy_kernel<<<gs(n), BLOCK, 0, st>>>(in, out, log_n, copies);
+        {
+            MB_KERNEL_ON("bit_reverse_copy", st);
+            bit_reverse_copy_kernel<<<gs(n), BLOCK, 0, st>>>(in, out, log_n, copies);
+        }
     }
     return finish_async();
 }
@@ -85,12 +94,18 @@ extern "C" {
 
 int basefold_bit_reverse_gl_ffi(uint64_t* d_data, int log_n) {
     if (log_n < 0 || log_n > 40 || !d_data) return MB_ERR_ARG;
-    bit_reverse_inplace_kernel<1><<<gs((size_t)1 << log_n), BLOCK, 0, MB_STREAM>>>(d_data, log_n);
+    {
+        MB_KERNEL_ON("bit_reverse_inplace", MB_STREAM);
+        bit_reverse_inplace_kernel<1><<<gs((size_t)1 << log_n), BLOCK, 0, MB_STREAM>>>(d_data, log_n);
+    }
     return finish_sync();
 }
 int basefold_bit_reverse_ext2_ffi(uint64_t* d_data, int log_n) {
     if (log_n < 0 || log_n > 40 || !d_data) return MB_ERR_ARG;
-    bit_reverse_inplace_kernel<2><<<gs((size_t)1 << log_n), BLOCK, 0, MB_STREAM>>>(d_data, log_n);
+    {
+        MB_KERNEL_ON("bit_reverse_inplace", MB_STREAM);
+        bit_reverse_inplace_kernel<2><<<gs((size_t)1 << log_n), BLOCK, 0, MB_STREAM>>>(d_data, log_n);
+    }
     return finish_sync();
 }
 
@@ -117,32 +132,47 @@ int basefold_encode_ffi(const uint64_t* d_coeffs, uint64_t* d_codeword, int num_
 int basefold_fold_gl_ffi(const uint64_t* d_codeword, const uint64_t* d_table, uint64_t challenge, uint64_t* d_output,
                          int pair_count) {
     if (pair_count < 1 || !d_codeword || !d_table || !d_output) return MB_ERR_ARG;
-    fold_gl_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_codeword, d_table, gl::canon(challenge), d_output, pair_count);
+    {
+        MB_KERNEL_ON("fold_gl", MB_STREAM);
+        fold_gl_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_codeword, d_table, gl::canon(challenge), d_output, pair_count);
+    }
     return finish_sync();
 }
 int basefold_fold_mixed_ffi(const uint64_t* d_codeword, const uint64_t* d_table, uint64_t c0, uint64_t c1,
                             uint64_t* d_output, int pair_count) {
     if (pair_count < 1 || !d_codeword || !d_table || !d_output) return MB_ERR_ARG;
-    fold_mixed_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_codeword, d_table, gl::E2{gl::canon(c0), gl::canon(c1)},
-                                                             d_output, pair_count);
+    {
+        MB_KERNEL_ON("fold_mixed", MB_STREAM);
+        fold_mixed_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_codeword, d_table, gl::E2{gl::canon(c0), gl::canon(c1)},
+                                                                 d_output, pair_count);
+    }
     return finish_sync();
 }
 int basefold_fold_ext2_ffi(const uint64_t* d_codeword, const uint64_t* d_table, uint64_t c0, uint64_t c1,
                            uint64_t* d_output, int pair_count) {
     if (pair_count < 1 || !d_codeword || !d_table || !d_output) return MB_ERR_ARG;
-    fold_ext2_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_codeword, d_table, gl::E2{gl::canon(c0), gl::canon(c1)},
-                                                            d_output, pair_count);
+    {
+        MB_KERNEL_ON("fold_ext2", MB_STREAM);
+        fold_ext2_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_codeword, d_table, gl::E2{gl::canon(c0), gl::canon(c1)},
+                                                                d_output, pair_count);
+    }
     return finish_sync();
 }
 
 int basefold_sumcheck_interp_gl_ffi(uint64_t* d_data, int pair_count) {
     if (pair_count < 1 || !d_data) return MB_ERR_ARG;
-    sc_interp_kernel<1><<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, pair_count);
+    {
+        MB_KERNEL_ON("sc_interp", MB_STREAM);
+        sc_interp_kernel<1><<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, pair_count);
+    }
     return finish_sync();
 }
 int basefold_sumcheck_interp_ext2_ffi(uint64_t* d_data, int pair_count) {
     if (pair_count < 1 || !d_data) return MB_ERR_ARG;
-    sc_interp_kernel<2><<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, pair_count);
+    {
+        MB_KERNEL_ON("sc_interp", MB_STREAM);
+        sc_interp_kernel<2><<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, pair_count);
+    }
     return finish_sync();
 }
 
@@ -150,7 +180,7 @@ int basefold_sumcheck_interp_ext2_ffi(uint64_t* d_data, int pair_count) {
     int NAME(const uint64_t* d_eq, const uint64_t* d_bh, uint64_t* p0, uint64_t* p1, uint64_t* p2, int pair_count, \
              int num_blocks) {                                                                                \
         if (pair_count < 1 || num_blocks < 1 || !d_eq || !d_bh || !p0 || !p1 || !p2) return MB_ERR_ARG;       \
-        KERNEL<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_eq, d_bh, p0, p1, p2, (size_t)pair_count);             \
+        { MB_KERNEL(#KERNEL); KERNEL<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_eq, d_bh, p0, p1, p2, (size_t)pair_count); } \
         return finish_sync();                                                                                 \
     }
 MB_PRODUCT_FFI(basefold_sumcheck_product_gl_ffi, sc_product_gl_kernel)
@@ -159,19 +189,28 @@ MB_PRODUCT_FFI(basefold_sumcheck_product_ext2_ffi, sc_product_ext2_kernel)
 
 int basefold_sumcheck_eval_gl_ffi(const uint64_t* d_data, uint64_t challenge, uint64_t* d_output, int pair_count) {
     if (pair_count < 1 || !d_data || !d_output) return MB_ERR_ARG;
-    sc_eval_gl_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, gl::canon(challenge), d_output, pair_count);
+    {
+        MB_KERNEL_ON("sc_eval_gl", MB_STREAM);
+        sc_eval_gl_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, gl::canon(challenge), d_output, pair_count);
+    }
     return finish_sync();
 }
 int basefold_sumcheck_eval_mixed_ffi(const uint64_t* d_data, uint64_t c0, uint64_t c1, uint64_t* d_output, int pair_count) {
     if (pair_count < 1 || !d_data || !d_output) return MB_ERR_ARG;
-    sc_eval_mixed_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, gl::E2{gl::canon(c0), gl::canon(c1)}, d_output,
-                                                                pair_count);
+    {
+        MB_KERNEL_ON("sc_eval_mixed", MB_STREAM);
+        sc_eval_mixed_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, gl::E2{gl::canon(c0), gl::canon(c1)}, d_output,
+                                                                    pair_count);
+    }
     return finish_sync();
 }
 int basefold_sumcheck_eval_ext2_ffi(const uint64_t* d_data, uint64_t c0, uint64_t c1, uint64_t* d_output, int pair_count) {
     if (pair_count < 1 || !d_data || !d_output) return MB_ERR_ARG;
-    sc_eval_ext2_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, gl::E2{gl::canon(c0), gl::canon(c1)}, d_output,
-                                                               pair_count);
+    {
+        MB_KERNEL_ON("sc_eval_ext2", MB_STREAM);
+        sc_eval_ext2_kernel<<<gs(pair_count), BLOCK, 0, MB_STREAM>>>(d_data, gl::E2{gl::canon(c0), gl::canon(c1)}, d_output,
+                                                                   pair_count);
+    }
     return finish_sync();
 }
 
@@ -180,19 +219,28 @@ int fused_sumcheck_round_ext2_ffi(const uint64_t* d_eq_in, const uint64_t* d_bh_
                                   int pair_count, int num_blocks) {
     if (pair_count < 1 || num_blocks < 1 || !d_eq_in || !d_bh_in || !d_eq_out || !d_bh_out || !p0 || !p1 || !p2)
         return MB_ERR_ARG;
-    sc_fused_round_ext2_kernel<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_eq_in, d_bh_in, gl::E2{gl::canon(c0), gl::canon(c1)},
-                                                                   d_eq_out, d_bh_out, p0, p1, p2, (size_t)pair_count);
+    {
+        MB_KERNEL_ON("sc_fused_round_ext2", MB_STREAM);
+        sc_fused_round_ext2_kernel<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_eq_in, d_bh_in, gl::E2{gl::canon(c0), gl::canon(c1)},
+                                                                       d_eq_out, d_bh_out, p0, p1, p2, (size_t)pair_count);
+    }
     return finish_sync();
 }
 
 int basefold_dot_product_gl_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_partial, int n, int num_blocks) {
     if (n < 0 || num_blocks < 1 || !d_a || !d_b || !d_partial) return MB_ERR_ARG;
-    dot_gl_kernel<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_a, d_b, d_partial, (size_t)n);
+    {
+        MB_KERNEL_ON("dot_gl", MB_STREAM);
+        dot_gl_kernel<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_a, d_b, d_partial, (size_t)n);
+    }
     return finish_sync();
 }
 int basefold_dot_product_mixed_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_partial, int n, int num_blocks) {
     if (n < 0 || num_blocks < 1 || !d_a || !d_b || !d_partial) return MB_ERR_ARG;
-    dot_mixed_kernel<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_a, d_b, d_partial, (size_t)n);
+    {
+        MB_KERNEL_ON("dot_mixed", MB_STREAM);
+        dot_mixed_kernel<<<num_blocks, BLOCK, 0, MB_STREAM>>>(d_a, d_b, d_partial, (size_t)n);
+    }
     return finish_sync();
 }
 

@@ -12,14 +12,20 @@ extern "C" {
 int poseidon2_hash_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n) {
     if (n < 0 || !d_input || !d_output) return MB_ERR_ARG;
     if (n == 0) return MB_OK;
-    permute_batch_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_input, d_output, (size_t)n);
+    {
+        MB_KERNEL_ON("permute_batch", MB_STREAM);
+        permute_batch_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_input, d_output, (size_t)n);
+    }
     return finish_sync();
 }
 
 int poseidon2_compress_batch_ffi(const uint64_t* d_left, const uint64_t* d_right, uint64_t* d_output, int n) {
     if (n < 0 || !d_left || !d_right || !d_output) return MB_ERR_ARG;
     if (n == 0) return MB_OK;
-    compress_pairs_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_left, d_right, d_output, (size_t)n);
+    {
+        MB_KERNEL_ON("compress_pairs", MB_STREAM);
+        compress_pairs_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_left, d_right, d_output, (size_t)n);
+    }
     return finish_sync();
 }
 
@@ -27,7 +33,10 @@ int poseidon2_compress_batch_ffi(const uint64_t* d_left, const uint64_t* d_right
 int poseidon2_merkle_layer_ffi(const uint64_t* d_input, uint64_t* d_output, int n) {
     if (n < 0 || !d_input || !d_output) return MB_ERR_ARG;
     if (n == 0) return MB_OK;
-    compress_layer_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_input, d_output, (size_t)n);
+    {
+        MB_KERNEL_ON("compress_layer", MB_STREAM);
+        compress_layer_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_input, d_output, (size_t)n);
+    }
     return finish_sync();
 }
 

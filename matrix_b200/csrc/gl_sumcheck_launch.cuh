@@ -42,6 +42,7 @@ int launch_round_message(const uint64_t* d_polys, uint64_t* d_partial, int d, si
     if (!aligned16(d_polys) || ((stride * F::NW) & 1)) return MB_ERR_ARG;
     int threads = threads_for(half, num_blocks);
     if (d > 3 && threads > 256) threads = 256;
+    MB_KERNEL_ON("sumcheck_round_message", st);
     MB_DISPATCH_D(d, (round_message_kernel<F, D><<<num_blocks, threads, 0, st>>>(d_polys, stride, half, d_partial,
                                                                                      d_counter, d_final)));
     return finish_async();
@@ -54,7 +55,10 @@ int launch_fold(const uint64_t* d_in, uint64_t* d_out, typename F::T r, int d, s
     if (half < 1 || 2 * half > stride) return MB_ERR_ARG;
     if (!aligned16(d_in) || ((stride * F::NW) & 1)) return MB_ERR_ARG;
     dim3 grid(grid_for(half, BLOCK, 8), d);
-    fold_kernel<F><<<grid, BLOCK, 0, st>>>(d_in, d_out, r, stride, half);
+    {
+        MB_KERNEL_ON("fold", st);
+        fold_kernel<F><<<grid, BLOCK, 0, st>>>(d_in, d_out, r, stride, half);
+    }
     return finish_async();
 }
 
@@ -67,6 +71,7 @@ int launch_fold_message(const uint64_t* d_in, uint64_t* d_out, typename FOut::T 
     if (quarter < 1 || 4 * quarter > stride_in || 2 * quarter > stride_out) return MB_ERR_ARG;
     if (!aligned16(d_in) || !aligned16(d_out) || ((stride_in * FIn::NW) & 1) || ((stride_out * FOut::NW) & 1))
         return MB_ERR_ARG;
+    MB_KERNEL_ON("sumcheck_fold_message", st);
     MB_DISPATCH_D(d, (fold_message_kernel<FIn, FOut, D><<<num_blocks, BLOCK, 0, st>>>(
                          d_in, d_out, r, d_r, stride_in, stride_out, quarter, d_partial, d_counter, d_final)));
     return finish_async();
@@ -79,7 +84,10 @@ int launch_fold_lift(const uint64_t* d_in, uint64_t* d_out, typename FOut::T r, 
     if (half < 1 || 2 * half > stride_in || half > stride_out) return MB_ERR_ARG;
     if (!aligned16(d_in) || ((stride_in * FIn::NW) & 1)) return MB_ERR_ARG;
     dim3 grid(grid_for(half, BLOCK, 8), d);
-    fold_lift_kernel<FIn, FOut><<<grid, BLOCK, 0, st>>>(d_in, d_out, r, d_r, stride_in, stride_out, half);
+    {
+        MB_KERNEL_ON("fold_lift", st);
+        fold_lift_kernel<FIn, FOut><<<grid, BLOCK, 0, st>>>(d_in, d_out, r, d_r, stride_in, stride_out, half);
+    }
     return finish_async();
 }
 

@@ -242,7 +242,10 @@ public:
                                            MB_STREAM) != cudaSuccess)
             rc = MB_ERR_CUDA;
         if (rc == MB_OK) {
-            table_invert_kernel<<<grid_for(total, 256, 8), 256, 0, MB_STREAM>>>(d_entries.p, total);
+            {
+                MB_KERNEL_ON("table_invert", MB_STREAM);
+                table_invert_kernel<<<grid_for(total, 256, 8), 256, 0, MB_STREAM>>>(d_entries.p, total);
+            }
             rc = finish_sync();
         }
         cudaFreeHost(h);
@@ -337,13 +340,22 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
     if (nv >= 12) {
         size_t tiles = (size_t)1 << (nv - 12);
         int g = (int)(tiles < (size_t)sm_count() * 4 ? tiles : (size_t)sm_count() * 4);
-        bf::bit_reverse_tiled_kernel<<<g, 256, 0, MB_STREAM>>>(cm.d_bh_evals.p, bh_fp.p, nv, 1);
+        {
+            MB_KERNEL_ON("bit_reverse_tiled", MB_STREAM);
+            bf::bit_reverse_tiled_kernel<<<g, 256, 0, MB_STREAM>>>(cm.d_bh_evals.p, bh_fp.p, nv, 1);
+        }
     } else {
-        bf::bit_reverse_copy_kernel<<<grid_for(n, 256, 8), 256, 0, MB_STREAM>>>(cm.d_bh_evals.p, bh_fp.p, nv, 1);
+        {
+            MB_KERNEL_ON("bit_reverse_copy", MB_STREAM);
+            bf::bit_reverse_copy_kernel<<<grid_for(n, 256, 8), 256, 0, MB_STREAM>>>(cm.d_bh_evals.p, bh_fp.p, nv, 1);
+        }
     }
 
     // oracle 0 and the claimed value eval = p(0) + p(1) = 2 c0 + c1 + c2
-    oracle0_kernel<<<grid_for(n / 2, 256, 4), 256, 0, MB_STREAM>>>(eq_a.p, bh_fp.p, n / 2, partial.p, counter, small.p);
+    {
+        MB_KERNEL_ON("oracle0", MB_STREAM);
+        oracle0_kernel<<<grid_for(n / 2, 256, 4), 256, 0, MB_STREAM>>>(eq_a.p, bh_fp.p, n / 2, partial.p, counter, small.p);
+    }
     MB_CUDA(cudaMemcpyAsync(h_small, small.p, 48, cudaMemcpyDeviceToHost, MB_STREAM));
     MB_CUDA(cudaStreamSynchronize(MB_STREAM));
     std::memcpy(p_oracles, h_small, 48);
@@ -382,11 +394,17 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
         size_t quarter = live / 4;
         int g = grid_for(quarter, 256, 4);
         if (round == 0) {
-            open_round_kernel<true><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
-                                                              counter, small.p);
+            {
+                MB_KERNEL_ON("open_round", MB_STREAM);
+                open_round_kernel<true><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
+                                                                  counter, small.p);
+            }
         } else {
-            open_round_kernel<false><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
-                                                               counter, small.p);
+            {
+                MB_KERNEL_ON("open_round", MB_STREAM);
+                open_round_kernel<false><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
+                                                                   counter, small.p);
+            }
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
         MB_CUDA(cudaMemcpyAsync(h_small, small.p, 48, cudaMemcpyDeviceToHost, MB_STREAM));
@@ -394,9 +412,15 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
         const uint64_t* level = table.device_level_ptr(round);
         int gf = grid_for(cw_pairs, 256, 8);
         if (round == 0) {
-            bf::fold_mixed_kernel<<<gf, 256, 0, MB_STREAM>>>(cm.d_codeword.p, level, r, fcw[0]->p, cw_pairs);
+            {
+                MB_KERNEL_ON("fold_mixed", MB_STREAM);
+                bf::fold_mixed_kernel<<<gf, 256, 0, MB_STREAM>>>(cm.d_codeword.p, level, r, fcw[0]->p, cw_pairs);
+            }
         } else {
-            bf::fold_ext2_kernel<<<gf, 256, 0, MB_STREAM>>>(fcw[round - 1]->p, level, r, fcw[round]->p, cw_pairs);
+            {
+                MB_KERNEL_ON("fold_ext2", MB_STREAM);
+                bf::fold_ext2_kernel<<<gf, 256, 0, MB_STREAM>>>(fcw[round - 1]->p, level, r, fcw[round]->p, cw_pairs);
+            }
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
         rc = mk::build_tree<true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM);
@@ -422,8 +446,11 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
     {
         Ext2 ch = t.sample_challenge_ext2();
         gl::E2 r{ch.c0, ch.c1};
-        bf::fold_ext2_kernel<<<grid_for(cw_pairs, 256, 8), 256, 0, MB_STREAM>>>(
-            fcw[nv - 2]->p, table.device_level_ptr(nv - 1), r, fcw[nv - 1]->p, cw_pairs);
+        {
+            MB_KERNEL_ON("fold_ext2", MB_STREAM);
+            bf::fold_ext2_kernel<<<grid_for(cw_pairs, 256, 8), 256, 0, MB_STREAM>>>(
+                fcw[nv - 2]->p, table.device_level_ptr(nv - 1), r, fcw[nv - 1]->p, cw_pairs);
+        }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
         MB_CUDA(cudaMemcpyAsync(p_final, fcw[nv - 1]->p, sizeof(uint64_t) * ((size_t)2 << lr), cudaMemcpyDeviceToHost,
                                 MB_STREAM));
@@ -444,7 +471,10 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
         lv.commit_cw = cm.d_codeword.p;
         lv.commit_tree = cm.d_tree.p;
         for (int i = 0; i <= nv - 2; i++) { lv.fcw[i] = fcw[i]->p; lv.ftree[i] = ftree[i]->p; }
-        query_gather_kernel<<<num_queries, 128, 0, MB_STREAM>>>(lv, d_idx.p, d_q.p, qw);
+        {
+            MB_KERNEL_ON("query_gather", MB_STREAM);
+            query_gather_kernel<<<num_queries, 128, 0, MB_STREAM>>>(lv, d_idx.p, d_q.p, qw);
+        }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
         MB_CUDA(cudaMemcpyAsync(p_queries, d_q.p, sizeof(uint64_t) * qw * num_queries, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));

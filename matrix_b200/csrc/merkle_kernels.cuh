@@ -118,7 +118,10 @@ inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
     size_t size = num_leaves;
     while (size > TAIL_NODES) {
         size_t half = size / 2;
-        compress_layer_kernel<<<grid_for(half, BLOCK, 16), BLOCK, 0, st>>>(layer, layer + 4 * size, half);
+        {
+            MB_KERNEL_ON("compress_layer", st);
+            compress_layer_kernel<<<grid_for(half, BLOCK, 16), BLOCK, 0, st>>>(layer, layer + 4 * size, half);
+        }
         layer += 4 * size;
         size = half;
     }
@@ -129,7 +132,10 @@ inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
 template <bool EXT2>
 inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
     if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
-    hash_leaves_kernel<EXT2><<<grid_for(num_leaves, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, num_leaves);
+    {
+        MB_KERNEL_ON("hash_leaves", st);
+        hash_leaves_kernel<EXT2><<<grid_for(num_leaves, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, num_leaves);
+    }
     return build_layers(d_tree, num_leaves, st);
 }
 

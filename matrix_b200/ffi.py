@@ -56,6 +56,10 @@ _GL_SIGNATURES = {
     "mb_event_sync": (c_int, [c_void_p]),
     "mb_event_elapsed_ms": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_float)]),
     "mb_event_destroy": (c_int, [c_void_p]),
+    "mb_launch_count": (c_u64, []),
+    "mb_prof_enable": (c_int, [c_int]),
+    "mb_prof_reset": (c_int, []),
+    "mb_prof_report": (c_size_t, [ctypes.c_char_p, c_size_t]),
     "sumcheck_round_message_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int]),
     "sumcheck_fold_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_size_t, c_size_t]),
     "sumcheck_round_message_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int]),

@@ -15,7 +15,7 @@ HEADERS = {
 def _declared(header_path):
     text = open(header_path).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return re.findall(r"^\s*(?:int|void|size_t|const char\s*\*|const uint64_t\s*\*)\s+(\w+)\s*\(", text, flags=re.M)
+    return re.findall(r"^\s*(?:int|void|size_t|uint64_t|const char\s*\*|const uint64_t\s*\*)\s+(\w+)\s*\(", text, flags=re.M)
 
 
 def test_every_declared_symbol_is_exported():
