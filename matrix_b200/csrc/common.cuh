@@ -53,6 +53,42 @@ inline int sm_count() {
     return cached;
 }
 
+// Scratch and result buffers the library allocates for itself come from the
+// device's stream-ordered pool on the caller's stream. The pool keeps freed
+// memory (release threshold raised once per device), so repeated calls reuse
+// their buffers instead of paying cudaMalloc / cudaFree every time; the role of
+// the caching allocator in almost-goldilocks-cuda-rs/cuda/wrapper.cu:145-235.
+inline void pool_setup_once() {
+    static thread_local int ready_dev = -1;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev == ready_dev) return;
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+        unsigned long long keep = ~0ULL;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    ready_dev = dev;
+}
+inline cudaError_t pool_alloc(void** p, size_t bytes) {
+    pool_setup_once();
+    return cudaMallocAsync(p, bytes, MB_STREAM);
+}
+inline void pool_free(void* p) {
+    if (p) cudaFreeAsync(p, MB_STREAM);
+}
+
+// Small pinned host landing zone, one per host thread, for results that are
+// read back every round (round polynomials, roots).
+inline uint64_t* pinned_scratch() {
+    struct Holder {
+        uint64_t* p = nullptr;
+        ~Holder() { if (p) cudaFreeHost(p); }
+    };
+    static thread_local Holder h;
+    if (!h.p && cudaMallocHost(&h.p, 64 * sizeof(uint64_t)) != cudaSuccess) h.p = nullptr;
+    return h.p;
+}
+
 // Grid for a grid-stride kernel: enough blocks to cover `items`, capped at
 // `per_sm` resident blocks on every SM.
 inline int grid_for(size_t items, int block, int per_sm) {

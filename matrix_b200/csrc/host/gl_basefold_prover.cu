@@ -47,10 +47,10 @@ struct DevBuf {
         release();
         words = w;
         if (w == 0) return MB_OK;
-        return cudaMalloc(&p, w * sizeof(uint64_t)) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+        return pool_alloc(reinterpret_cast<void**>(&p), w * sizeof(uint64_t)) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
     }
     void release() {
-        if (p) cudaFree(p);
+        pool_free(p);
         p = nullptr;
         words = 0;
     }
@@ -275,7 +275,7 @@ public:
         if (rc != MB_OK) return rc;
         rc = bf::interpolate_async(d_evals, coeffs.p, d_bh_evals.p, nv, MB_STREAM);
         if (rc == MB_OK) rc = bf::encode_async(coeffs.p, coeffs.p, d_codeword.p, nv, lr, MB_STREAM);
-        if (rc == MB_OK) rc = mk::build_tree<false>(d_codeword.p, d_tree.p, cw_len / 2, MB_STREAM);
+        if (rc == MB_OK) rc = mk::build_tree_periodic(d_codeword.p, d_tree.p, cw_len / 2, (size_t)1 << lr, MB_STREAM);
         if (rc != MB_OK) return rc;
         MB_CUDA(cudaMemcpyAsync(root, d_tree.p + 4 * (cw_len - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
@@ -328,9 +328,8 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
     if (rc != MB_OK) return rc;
     unsigned int* counter = reinterpret_cast<unsigned int*>(small.p + 8);
     MB_CUDA(cudaMemsetAsync(small.p, 0, 16 * sizeof(uint64_t), MB_STREAM));
-    uint64_t* h_small = nullptr;  // pinned landing zone: 6 oracle words + 4 root words
-    MB_CUDA(cudaMallocHost(&h_small, 16 * sizeof(uint64_t)));
-    struct PinnedGuard { uint64_t* p; ~PinnedGuard() { cudaFreeHost(p); } } guard{h_small};
+    uint64_t* h_small = pinned_scratch();  // landing zone: 6 oracle words + 4 root words
+    if (!h_small) return MB_ERR_CUDA;
 
     MB_CUDA(cudaMemcpyAsync(d_point.p, point, sizeof(uint64_t) * 2 * nv, cudaMemcpyHostToDevice, MB_STREAM));
     // eq table; bh_a doubles as scratch for the two small tables (free until round 0 writes it)

@@ -41,14 +41,15 @@ public:
         size_t cap_a = n_ >= 2 ? n_ / 2 : 1, cap_b = n_ >= 4 ? n_ / 4 : 1;
         stride_a_ = cap_a;
         stride_b_ = cap_b;
-        MB_CUDA(cudaMalloc(&buf_a_, sizeof(uint64_t) * 2 * cap_a * d));
-        MB_CUDA(cudaMalloc(&buf_b_, sizeof(uint64_t) * 2 * cap_b * d));
+        MB_CUDA(pool_alloc((void**)&buf_a_, sizeof(uint64_t) * 2 * cap_a * d));
+        MB_CUDA(pool_alloc((void**)&buf_b_, sizeof(uint64_t) * 2 * cap_b * d));
         max_blocks_ = prover_grid(n_ / 2 > 0 ? n_ / 2 : 1);
-        MB_CUDA(cudaMalloc(&partial_, sizeof(uint64_t) * 2 * (d + 1) * (size_t)max_blocks_));
-        MB_CUDA(cudaMalloc(&msg_dev_, sizeof(uint64_t) * 2 * (MAX_D + 1)));
-        MB_CUDA(cudaMalloc(&counter_, sizeof(unsigned int)));
+        MB_CUDA(pool_alloc((void**)&partial_, sizeof(uint64_t) * 2 * (d + 1) * (size_t)max_blocks_));
+        MB_CUDA(pool_alloc((void**)&msg_dev_, sizeof(uint64_t) * 2 * (MAX_D + 1)));
+        MB_CUDA(pool_alloc((void**)&counter_, sizeof(unsigned int)));
         MB_CUDA(cudaMemsetAsync(counter_, 0, sizeof(unsigned int), MB_STREAM));
-        MB_CUDA(cudaMallocHost(&msg_host_, sizeof(uint64_t) * 2 * (MAX_D + 1)));
+        msg_host_ = pinned_scratch();
+        if (!msg_host_) return MB_ERR_CUDA;
         have_msg_ = false;
         return MB_OK;
     }
@@ -148,12 +149,11 @@ public:
 
 private:
     void release() {
-        cudaFree(buf_a_);
-        cudaFree(buf_b_);
-        cudaFree(partial_);
-        cudaFree(msg_dev_);
-        cudaFree(counter_);
-        if (msg_host_) cudaFreeHost(msg_host_);
+        pool_free(buf_a_);
+        pool_free(buf_b_);
+        pool_free(partial_);
+        pool_free(msg_dev_);
+        pool_free(counter_);
         buf_a_ = buf_b_ = partial_ = msg_dev_ = nullptr;
         counter_ = nullptr;
         msg_host_ = nullptr;
@@ -238,14 +238,14 @@ int gl_sumcheck_prove_host_ffi(const uint64_t* h_tables, int d, int num_var, int
     if (d < 1 || d > MAX_D || num_var < 0 || num_var > 40 || !h_tables) return MB_ERR_ARG;
     size_t words = ((size_t)1 << num_var) * (size_t)d * (base_field ? 1 : 2);
     uint64_t* d_tables = nullptr;
-    MB_CUDA(cudaMalloc(&d_tables, words * sizeof(uint64_t)));
+    MB_CUDA(pool_alloc((void**)&d_tables, words * sizeof(uint64_t)));
     int rc = MB_OK;
     if (cudaMemcpyAsync(d_tables, h_tables, words * sizeof(uint64_t), cudaMemcpyHostToDevice, MB_STREAM) != cudaSuccess)
         rc = MB_ERR_CUDA;
     if (rc == MB_OK)
         rc = gl_sumcheck_prove_device_ffi(d_tables, d, num_var, base_field, label, label_len, round_msgs, challenges,
                                           final_evals, final_eval, transcript_state);
-    cudaFree(d_tables);
+    pool_free(d_tables);
     return rc;
 }
 

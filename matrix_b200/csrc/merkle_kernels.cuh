@@ -139,5 +139,68 @@ inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_l
     return build_layers(d_tree, num_leaves, st);
 }
 
+// dst[c * words + i] = src[i] for c = 1 .. copies-1 (dst = src: in-place replication of a prefix).
+static __global__ void replicate_kernel(uint64_t* base, size_t words, size_t copies) {
+    const size_t pairs = words / 2, total = pairs * (copies - 1);
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    ulonglong2* b = reinterpret_cast<ulonglong2*>(base);
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step) {
+        size_t c = t / pairs + 1, i = t % pairs;
+        b[c * pairs + i] = b[i];
+    }
+}
+
+// Tree over a base-field codeword that consists of `copies` equal blocks (what
+// the foldable-code encoder produces: goldilocks-cuda-rs/cuda/wrapper.cu:1277-1312
+// repeats every coefficient 2^log_rate times and its butterflies never mix the
+// copies, so after the bit reversal block c equals block 0). Every layer of the
+// tree is then periodic too: only the first size/copies nodes of each layer are
+// hashed, the rest are copied. The buffer ends up identical to build_tree's.
+inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, size_t copies,
+                               cudaStream_t st) {
+    if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
+    if (copies < 2 || num_leaves / copies < 2 * (size_t)TAIL_NODES) return build_tree<false>(d_codeword, d_tree, num_leaves, st);
+    size_t uniq = num_leaves / copies;
+    {
+        MB_KERNEL_ON("hash_leaves", st);
+        hash_leaves_kernel<false><<<grid_for(uniq, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, uniq);
+    }
+    {
+        MB_KERNEL_ON("replicate", st);
+        replicate_kernel<<<grid_for(uniq * 2 * (copies - 1), 256, 8), 256, 0, st>>>(d_tree, 4 * uniq, copies);
+    }
+    uint64_t* layer = d_tree;
+    size_t size = num_leaves;
+    while (size > TAIL_NODES && size / copies >= 2) {
+        size_t half = size / 2, u = half / copies;
+        uint64_t* next = layer + 4 * size;
+        {
+            MB_KERNEL_ON("compress_layer", st);
+            compress_layer_kernel<<<grid_for(u, BLOCK, 16), BLOCK, 0, st>>>(layer, next, u);
+        }
+        {
+            MB_KERNEL_ON("replicate", st);
+            replicate_kernel<<<grid_for(u * 2 * (copies - 1), 256, 8), 256, 0, st>>>(next, 4 * u, copies);
+        }
+        layer = next;
+        size = half;
+    }
+    // the remaining layers are small: ordinary path on the fully populated layer
+    while (size > TAIL_NODES) {
+        size_t half = size / 2;
+        {
+            MB_KERNEL_ON("compress_layer", st);
+            compress_layer_kernel<<<grid_for(half, BLOCK, 16), BLOCK, 0, st>>>(layer, layer + 4 * size, half);
+        }
+        layer += 4 * size;
+        size = half;
+    }
+    if (size > 1) {
+        MB_KERNEL_ON("tree_tail", st);
+        tree_tail_kernel<<<1, BLOCK, 0, st>>>(layer, size);
+    }
+    return finish_async();
+}
+
 }  // namespace mk
 }  // namespace mb

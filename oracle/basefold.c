@@ -304,7 +304,14 @@ int oracle_bf_open_ext2(const uint64_t *codeword, const uint64_t *bh_evals, cons
 
     /* eval = <bh, eq> */
     ext2_t eval = e2(0, 0);
-    for (size_t i = 0; i < n; i++) eval = e2_add(eval, e2_mul_base(e2(eq[2 * i], eq[2 * i + 1]), bh_evals[i]));
+#pragma omp parallel
+    {
+        ext2_t loc = e2(0, 0);
+#pragma omp for schedule(static) nowait
+        for (size_t i = 0; i < n; i++) loc = e2_add(loc, e2_mul_base(e2(eq[2 * i], eq[2 * i + 1]), bh_evals[i]));
+#pragma omp critical
+        eval = e2_add(eval, loc);
+    }
     p_eval[0] = eval.c0; p_eval[1] = eval.c1;
 
     compute_oracle(bh_evals, 1, eq, n, p_oracles);
@@ -312,14 +319,19 @@ int oracle_bf_open_ext2(const uint64_t *codeword, const uint64_t *bh_evals, cons
 
     ext2_t r = sample_ext2(&t);
     size_t sc = n / 2;
+    uint64_t *eq2 = (uint64_t *)malloc(sizeof(uint64_t) * n);      /* ping-pong partners so the folds can run in parallel */
+    uint64_t *bh2 = (uint64_t *)malloc(sizeof(uint64_t) * (n / 2 > 2 ? n / 2 : 2));
+    if (!eq2 || !bh2) { free(eq); free(bh); free(bhv); free(eq2); free(bh2); return -1; }
+#pragma omp parallel for schedule(static)
     for (size_t j = 0; j < sc; j++) {
         ext2_t lo = e2(bh_evals[2 * j], 0), hi = e2(bh_evals[2 * j + 1], 0);
         ext2_t v = e2_add(lo, e2_mul(r, e2_sub(hi, lo)));
         bh[2 * j] = v.c0; bh[2 * j + 1] = v.c1;
         ext2_t ql = e2(eq[4 * j], eq[4 * j + 1]), qh = e2(eq[4 * j + 2], eq[4 * j + 3]);
         ext2_t q = e2_add(ql, e2_mul(r, e2_sub(qh, ql)));
-        eq[2 * j] = q.c0; eq[2 * j + 1] = q.c1;
+        eq2[2 * j] = q.c0; eq2[2 * j + 1] = q.c1;
     }
+    { uint64_t *tmp = eq; eq = eq2; eq2 = tmp; }
     compute_oracle(bh, 2, eq, sc, p_oracles + 6);
     for (int k = 0; k < 3; k++) observe_ext2(&t, p_oracles[6 + 2 * k], p_oracles[6 + 2 * k + 1]);
 
@@ -341,14 +353,16 @@ int oracle_bf_open_ext2(const uint64_t *codeword, const uint64_t *bh_evals, cons
     for (int round = 1; round < nv - 1; round++) {
         r = sample_ext2(&t);
         size_t half = sc / 2;
+#pragma omp parallel for schedule(static)
         for (size_t j = 0; j < half; j++) {
             ext2_t ql = e2(eq[4 * j], eq[4 * j + 1]), qh = e2(eq[4 * j + 2], eq[4 * j + 3]);
             ext2_t q = e2_add(ql, e2_mul(r, e2_sub(qh, ql)));
             ext2_t bl = e2(bh[4 * j], bh[4 * j + 1]), bhh = e2(bh[4 * j + 2], bh[4 * j + 3]);
             ext2_t b = e2_add(bl, e2_mul(r, e2_sub(bhh, bl)));
-            eq[2 * j] = q.c0; eq[2 * j + 1] = q.c1;
-            bh[2 * j] = b.c0; bh[2 * j + 1] = b.c1;
+            eq2[2 * j] = q.c0; eq2[2 * j + 1] = q.c1;
+            bh2[2 * j] = b.c0; bh2[2 * j + 1] = b.c1;
         }
+        { uint64_t *tmp = eq; eq = eq2; eq2 = tmp; tmp = bh; bh = bh2; bh2 = tmp; }
         sc = half;
         uint64_t *po = p_oracles + (size_t)(round + 1) * 6;
         compute_oracle(bh, 2, eq, sc, po);
@@ -390,7 +404,7 @@ int oracle_bf_open_ext2(const uint64_t *codeword, const uint64_t *bh_evals, cons
     }
     if (transcript_state_out) memcpy(transcript_state_out, t.sponge, 64);
     for (int i = 0; i < nv; i++) { free(fcw[i]); free(ftree[i]); }
-    free(fcw); free(ftree); free(flen); free(eq); free(bh); free(bhv);
+    free(fcw); free(ftree); free(flen); free(eq); free(bh); free(bhv); free(eq2); free(bh2);
     return 0;
 }
 
