@@ -82,52 +82,84 @@ GLF uint64_t sbox7(uint64_t x) {
     return mul(x4, x3);
 }
 
-// [2 3 1 1; 1 2 3 1; 1 1 2 3; 3 1 1 2] on four words.
-GLF void mds4(uint64_t& s0, uint64_t& s1, uint64_t& s2, uint64_t& s3) {
-    uint64_t t01 = add(s0, s1), t23 = add(s2, s3);
-    uint64_t t0123 = add(t01, t23);
-    uint64_t t01123 = add(t0123, s1), t01233 = add(t0123, s3);
-    uint64_t n0 = add(t01123, t01);
-    uint64_t n1 = add(t01123, add(s2, s2));
-    uint64_t n2 = add(t01233, t23);
-    uint64_t n3 = add(t01233, add(s0, s0));
-    s0 = n0; s1 = n1; s2 = n2; s3 = n3;
-}
-
-GLF void mds_light_8(uint64_t* s) {
-    mds4(s[0], s[1], s[2], s[3]);
-    mds4(s[4], s[5], s[6], s[7]);
+// External linear layer: y = M x with M = [[2 M4, M4], [M4, 2 M4]],
+// M4 = [2 3 1 1; 1 2 3 1; 1 1 2 3; 3 1 1 2] (the 4x4 map on each half followed
+// by the cross-half sums of mds_light_8 in the reference), plus the next
+// round's constants. Instead of a chain of modular additions, the low and high
+// 32-bit halves of the eight inputs are accumulated separately with their small
+// integer weights (row sum 21, so both sums stay below 2^37) and each output is
+// reduced once.
+template <bool HAS_RC>
+GLF void p2_external_linear(uint64_t* s, int next_round) {
+    constexpr uint32_t M[8][8] = {{4, 6, 2, 2, 2, 3, 1, 1}, {2, 4, 6, 2, 1, 2, 3, 1}, {2, 2, 4, 6, 1, 1, 2, 3},
+                                  {6, 2, 2, 4, 3, 1, 1, 2}, {2, 3, 1, 1, 4, 6, 2, 2}, {1, 2, 3, 1, 2, 4, 6, 2},
+                                  {1, 1, 2, 3, 2, 2, 4, 6}, {3, 1, 1, 2, 6, 2, 2, 4}};
+    uint64_t y[8];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint64_t sum = add(s[i], s[i + 4]);
-        s[i] = add(s[i], sum);
-        s[i + 4] = add(s[i + 4], sum);
+    for (int i = 0; i < 8; i++) {
+        uint64_t L = 0, H = 0;
+        if (HAS_RC) {
+            uint64_t rc = p2_rc_ext(next_round, i);
+            L = lo32(rc);
+            H = hi32(rc);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            L = madwide(lo32(s[j]), M[i][j], L);
+            H = madwide(hi32(s[j]), M[i][j], H);
+        }
+        y[i] = reduce_limb_sums(L, H);
     }
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = y[i];
 }
 
-GLF void p2_full_round(uint64_t* s, int r) {
+// Internal linear layer: s_i = d_i s_i + sum(s); `rc0` (the next round's
+// constant for lane 0, or 0) rides along in lane 0's sum.
+GLF void p2_internal_linear(uint64_t* s, uint64_t rc0) {
+    uint64_t SL = 0, SH = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) s[i] = sbox7(add_c(s[i], p2_rc_ext(r, i)));
-    mds_light_8(s);
+    for (int i = 0; i < 8; i++) {
+        SL = madwide(lo32(s[i]), 1u, SL);
+        SH = madwide(hi32(s[i]), 1u, SH);
+    }
+    uint64_t sum = reduce_limb_sums(SL, SH);
+    s[0] = mul_add(s[0], p2_diag(0), add_c(sum, rc0));
+#pragma unroll
+    for (int i = 1; i < 8; i++) s[i] = mul_add(s[i], p2_diag(i), sum);
 }
 
-GLF void p2_partial_round(uint64_t* s, int r) {
-    s[0] = sbox7(add_c(s[0], p2_rc_int(r)));
-    uint64_t sum = s[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) sum = add(sum, s[i]);
-#pragma unroll
-    for (int i = 0; i < 8; i++) s[i] = add(mul(s[i], p2_diag(i)), sum);
-}
-
-// In place; loose in, loose out.
+// In place; loose in, loose out. Round constants are added by the linear layer
+// that precedes the S-boxes using them, so only the first external and the
+// first internal / terminal constants need explicit additions.
 GLF void poseidon2_permute(uint64_t* s) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = add_c(s[i], p2_rc_ext(0, i));
 #pragma unroll 1
-    for (int r = 0; r < 4; r++) p2_full_round(s, r);
+    for (int r = 0; r < 4; r++) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) s[i] = sbox7(s[i]);
+        if (r < 3) {
+            p2_external_linear<true>(s, r + 1);
+        } else {
+            p2_external_linear<false>(s, 0);
+            s[0] = add_c(s[0], p2_rc_int(0));
+        }
+    }
 #pragma unroll 1
-    for (int r = 0; r < 22; r++) p2_partial_round(s, r);
+    for (int r = 0; r < 22; r++) {
+        s[0] = sbox7(s[0]);
+        p2_internal_linear(s, r < 21 ? p2_rc_int(r + 1) : 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) s[i] = add_c(s[i], p2_rc_ext(4, i));
 #pragma unroll 1
-    for (int r = 4; r < 8; r++) p2_full_round(s, r);
+    for (int r = 4; r < 8; r++) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) s[i] = sbox7(s[i]);
+        if (r < 7) p2_external_linear<true>(s, r + 1);
+        else p2_external_linear<false>(s, 0);
+    }
 }
 
 }  // namespace gl

@@ -19,6 +19,9 @@ void hc_e2_inv(const uint64_t* a, uint64_t* o) {
     gl::E2 r = gl::e2_inv(gl::E2{a[0], a[1]});
     o[0] = r.c0; o[1] = r.c1;
 }
+uint64_t hc_gl_mul_add(uint64_t a, uint64_t b, uint64_t c) { return gl::mul_add(a, b, c); }
+uint64_t hc_gl_reduce_limb_sums(uint64_t L, uint64_t H) { return gl::reduce_limb_sums(L, H); }
+uint64_t hc_gl_reduce_limbs(uint32_t z0, uint32_t z1, uint32_t z2, uint32_t z3) { return gl::reduce_limbs(z0, z1, z2, z3); }
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
 
 // Replays a script of transcript operations: op 0 = absorb(v), 1 = squeeze -> out.

@@ -36,6 +36,37 @@ def test_loose_arithmetic_is_correct_mod_p(hostcheck):
         assert (inv * a) % P == (1 if a % P else 0)
 
 
+def test_limb_reductions(hostcheck):
+    _setup(hostcheck)
+    hostcheck.hc_gl_mul_add.restype = u64
+    hostcheck.hc_gl_mul_add.argtypes = [u64, u64, u64]
+    hostcheck.hc_gl_reduce_limb_sums.restype = u64
+    hostcheck.hc_gl_reduce_limb_sums.argtypes = [u64, u64]
+    hostcheck.hc_gl_reduce_limbs.restype = u64
+    hostcheck.hc_gl_reduce_limbs.argtypes = [ctypes.c_uint32] * 4
+    rnd = random.Random(11)
+    edge32 = [0, 1, 2, 0xFFFFFFFF, 0xFFFFFFFE, 0x80000000, 0x7FFFFFFF]
+    for z0 in edge32:
+        for z1 in edge32:
+            for z2 in edge32:
+                for z3 in edge32:
+                    v = z0 + (z1 << 32) + (z2 << 64) + (z3 << 96)
+                    assert hostcheck.hc_gl_reduce_limbs(z0, z1, z2, z3) % P == v % P
+    for _ in range(3000):
+        z = [rnd.randrange(2**32) for _ in range(4)]
+        v = z[0] + (z[1] << 32) + (z[2] << 64) + (z[3] << 96)
+        assert hostcheck.hc_gl_reduce_limbs(*z) % P == v % P
+    edge64 = [0, 1, P - 1, P, 2**64 - 1, 2**64 - 2**32, 2**32 - 1, 2**32]
+    for a in edge64 + [rnd.randrange(2**64) for _ in range(40)]:
+        for b in edge64 + [rnd.randrange(2**64) for _ in range(10)]:
+            for c in edge64 + [rnd.randrange(2**64) for _ in range(4)]:
+                assert hostcheck.hc_gl_mul_add(a, b, c) % P == (a * b + c) % P
+    edge40 = [0, 1, 2**32 - 1, 2**32, 2**40 - 1, 2**37, 21 * (2**32 - 1)]
+    for L in edge40 + [rnd.randrange(2**40) for _ in range(60)]:
+        for H in edge40 + [rnd.randrange(2**40) for _ in range(60)]:
+            assert hostcheck.hc_gl_reduce_limb_sums(L, H) % P == (L + (H << 32)) % P
+
+
 def test_ext2_mul_inv(hostcheck):
     rnd = random.Random(8)
     for _ in range(500):
