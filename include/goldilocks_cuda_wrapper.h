@@ -103,6 +103,9 @@ int poseidon2_merkle_layer_ffi(const uint64_t* d_input, uint64_t* d_output, int 
  * d_tree holds (2 * num_leaves - 1) digests: leaves, each layer, root last. */
 int poseidon2_merkle_tree_gl_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
 int poseidon2_merkle_tree_ext2_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
+/* addition, tuning hook: one layer with an explicit kernel (0: permutation per thread, 1: eight lanes per
+ * permutation); asynchronous on the caller's stream */
+int mb_merkle_layer_variant(const uint64_t* d_input, uint64_t* d_output, int n, int variant);
 
 /* ---- eq tables: ffi.rs:396-410 (wrapper.cu:2040-2110) ----
  * eq(r, x) for all x, bit i of x <-> r[i]; *d_result is set to the buffer that

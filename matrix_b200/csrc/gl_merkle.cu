@@ -53,4 +53,18 @@ int poseidon2_merkle_tree_ext2_ffi(const uint64_t* d_codeword, uint64_t* d_tree,
     return rc != MB_OK ? rc : finish_sync();
 }
 
+// Tuning hook: one Merkle layer with an explicit kernel choice
+// (0 = one permutation per thread, 1 = eight lanes per permutation). No sync.
+int mb_merkle_layer_variant(const uint64_t* d_input, uint64_t* d_output, int n, int variant) {
+    if (n < 1 || !d_input || !d_output) return MB_ERR_ARG;
+    if (variant == 1) {
+        MB_KERNEL("compress_layer_coop");
+        compress_layer_coop_kernel<<<grid_for((size_t)n * 8, 256, 8), 256, 0, MB_STREAM>>>(d_input, d_output, (size_t)n);
+    } else {
+        MB_KERNEL("compress_layer");
+        compress_layer_kernel<<<grid_for((size_t)n, BLOCK, 16), BLOCK, 0, MB_STREAM>>>(d_input, d_output, (size_t)n);
+    }
+    return finish_async();
+}
+
 }  // extern "C"

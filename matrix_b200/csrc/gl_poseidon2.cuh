@@ -162,4 +162,67 @@ GLF void poseidon2_permute(uint64_t* s) {
     }
 }
 
+#ifdef __CUDACC__
+// ---- one permutation spread over 8 lanes ----------------------------------------
+// Layers near the top of a Merkle tree (and a transcript) have too few
+// permutations to fill the machine; what matters there is the latency of one
+// permutation. Eight consecutive lanes of a warp hold one state word each: the
+// S-boxes of an external round run in parallel, the linear layers exchange
+// halves with warp shuffles, and in the internal rounds lane 0 runs the S-box
+// while the sum is formed by a three-step butterfly. Per-lane constants come
+// from global copies of the tables (a divergent index into __constant__ memory
+// would serialise). All 32 lanes of the warp must call; `lane8` = lane & 7.
+static __device__ const uint64_t g_p2_rc_ext[8][8] = GLP2_RC_EXT_INIT;
+static __device__ const uint64_t g_p2_diag[8] = GLP2_DIAG_INIT;
+
+__device__ __forceinline__ uint64_t p2_coop_external(uint64_t x, const uint32_t (&w)[8], uint64_t rc) {
+    uint64_t L = lo32(rc), H = hi32(rc);
+    const uint32_t xl = lo32(x), xh = hi32(x);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        L = madwide(__shfl_sync(0xffffffffu, xl, j, 8), w[j], L);
+        H = madwide(__shfl_sync(0xffffffffu, xh, j, 8), w[j], H);
+    }
+    return reduce_limb_sums(L, H);
+}
+
+__device__ __forceinline__ uint64_t poseidon2_permute_coop8(uint64_t x, int lane8) {
+    // row lane8 of M = [[2 M4, M4], [M4, 2 M4]]
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        int d = ((j & 3) - (lane8 & 3)) & 3;  // M4 is circulant: first row 2 3 1 1
+        uint32_t m4 = d == 0 ? 2u : (d == 1 ? 3u : 1u);
+        w[j] = ((j >> 2) == (lane8 >> 2)) ? 2u * m4 : m4;
+    }
+    const uint64_t diag = g_p2_diag[lane8];
+    x = add_c(x, g_p2_rc_ext[0][lane8]);
+#pragma unroll 1
+    for (int r = 0; r < 4; r++) {
+        x = sbox7(x);
+        x = p2_coop_external(x, w, r < 3 ? g_p2_rc_ext[r + 1][lane8] : (lane8 == 0 ? p2_rc_int(0) : 0));
+    }
+#pragma unroll 1
+    for (int r = 0; r < 22; r++) {
+        if (lane8 == 0) x = sbox7(x);
+        uint64_t SL = lo32(x), SH = hi32(x);
+#pragma unroll
+        for (int off = 1; off < 8; off <<= 1) {
+            SL += __shfl_xor_sync(0xffffffffu, SL, off, 8);
+            SH += __shfl_xor_sync(0xffffffffu, SH, off, 8);
+        }
+        uint64_t sum = reduce_limb_sums(SL, SH);
+        if (lane8 == 0 && r < 21) sum = add_c(sum, p2_rc_int(r + 1));
+        x = mul_add(x, diag, sum);
+    }
+    x = add_c(x, g_p2_rc_ext[4][lane8]);
+#pragma unroll 1
+    for (int r = 4; r < 8; r++) {
+        x = sbox7(x);
+        x = p2_coop_external(x, w, r < 7 ? g_p2_rc_ext[r + 1][lane8] : 0);
+    }
+    return x;
+}
+#endif
+
 }  // namespace gl

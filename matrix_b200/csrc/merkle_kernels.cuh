@@ -10,8 +10,9 @@
 //
 // Hashing is bound by the integer pipes (about 520 modular multiplications for
 // every 32-byte digest), not by HBM, so every layer is one fully parallel launch
-// with one permutation per thread; only the last few layers, too small to fill
-// the machine, are finished by a single block.
+// with one permutation per thread while the layer can fill the machine. Smaller
+// layers are bound by the latency of one permutation: they spread each
+// permutation over 8 lanes, and the last six are finished by a single block.
 #pragma once
 #include "common.cuh"
 #include "gl_poseidon2.cuh"
@@ -20,7 +21,7 @@ namespace mb {
 namespace mk {
 
 constexpr int BLOCK = 128;
-constexpr int TAIL_NODES = 1024;  // layers of at most this many nodes are finished by one block
+constexpr int TAIL_NODES = 64;  // layers of at most this many nodes are finished by one block
 
 __device__ __forceinline__ void store_digest(uint64_t* out, const uint64_t* s) {
     *reinterpret_cast<ulonglong2*>(out) = make_ulonglong2(gl::canon(s[0]), gl::canon(s[1]));
@@ -82,14 +83,56 @@ compress_pairs_kernel(const uint64_t* __restrict__ left, const uint64_t* __restr
     }
 }
 
-// One block walks every remaining layer above `layer` (of `size` nodes) up to
-// the root; layers are contiguous in the tree buffer.
-static __global__ void __launch_bounds__(BLOCK)
-tree_tail_kernel(uint64_t* layer, size_t size) {
+// ---- latency-oriented variants: 8 lanes per permutation ---------------------------
+// Node k of the output layer is handled by 8 consecutive threads: thread l loads
+// word l of the 64-byte input pair and threads 0..3 store the digest.
+static __global__ void __launch_bounds__(256)
+compress_layer_coop_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
+    const int l = threadIdx.x & 7;
+    const size_t groups = ((size_t)gridDim.x * blockDim.x) >> 3;
+    const size_t rounds = (n + groups - 1) / groups;  // every lane of a warp runs the same trip count
+    size_t k = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    for (size_t it = 0; it < rounds; it++, k += groups) {
+        const bool live = k < n;
+        uint64_t x = live ? in[8 * k + l] : 0;
+        x = gl::poseidon2_permute_coop8(x, l);
+        if (live && l < 4) out[4 * k + l] = gl::canon(x);
+    }
+}
+
+template <bool EXT2>
+__global__ void __launch_bounds__(256)
+hash_leaves_coop_kernel(const uint64_t* __restrict__ cw, uint64_t* __restrict__ digests, size_t num_leaves) {
+    constexpr int W = EXT2 ? 4 : 2;
+    const int l = threadIdx.x & 7;
+    const size_t groups = ((size_t)gridDim.x * blockDim.x) >> 3;
+    const size_t rounds = (num_leaves + groups - 1) / groups;
+    size_t k = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    for (size_t it = 0; it < rounds; it++, k += groups) {
+        const bool live = k < num_leaves;
+        uint64_t x = (live && l < W) ? cw[W * k + l] : 0;
+        x = gl::poseidon2_permute_coop8(x, l);
+        if (live && l < 4) digests[4 * k + l] = gl::canon(x);
+    }
+}
+
+// One block (256 threads = 32 permutations at a time) walks every remaining
+// layer above `layer` (of `size` <= 64 nodes) up to the root.
+static __global__ void __launch_bounds__(256)
+tree_tail_coop_kernel(uint64_t* layer, size_t size) {
+    const int l = threadIdx.x & 7;
+    const size_t groups = blockDim.x >> 3;
     while (size > 1) {
         uint64_t* next = layer + 4 * size;
-        size_t half = size / 2;
-        for (size_t k = threadIdx.x; k < half; k += blockDim.x) compress_node(layer + 8 * k, next + 4 * k);
+        const size_t half = size / 2;
+        const size_t rounds = (half + groups - 1) / groups;
+        size_t k = threadIdx.x >> 3;
+        for (size_t it = 0; it < rounds; it++, k += groups) {
+            const bool live = k < half;
+            uint64_t x = live ? layer[8 * k + l] : 0;
+            x = gl::poseidon2_permute_coop8(x, l);
+            if (live && l < 4) next[4 * k + l] = gl::canon(x);
+        }
         __syncthreads();
         layer = next;
         size = half;
@@ -112,30 +155,53 @@ permute_batch_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out
     }
 }
 
+// Measured on B200: a layer of up to 2^12 nodes takes 16.6 us with 8 lanes per
+// permutation and 22.7 us with one permutation per thread (both are the latency
+// of a single permutation); from 2^13 nodes up the per-thread kernel wins.
+constexpr size_t COOP_NODES = (size_t)1 << 12;
+
+inline void launch_compress_layer(const uint64_t* in, uint64_t* out, size_t n, cudaStream_t st) {
+    if (n <= COOP_NODES) {
+        MB_KERNEL_ON("compress_layer_coop", st);
+        compress_layer_coop_kernel<<<grid_for(n * 8, 256, 8), 256, 0, st>>>(in, out, n);
+    } else {
+        MB_KERNEL_ON("compress_layer", st);
+        compress_layer_kernel<<<grid_for(n, BLOCK, 16), BLOCK, 0, st>>>(in, out, n);
+    }
+}
+
+template <bool EXT2>
+inline void launch_hash_leaves(const uint64_t* cw, uint64_t* digests, size_t n, cudaStream_t st) {
+    if (n <= COOP_NODES) {
+        MB_KERNEL_ON("hash_leaves_coop", st);
+        hash_leaves_coop_kernel<EXT2><<<grid_for(n * 8, 256, 8), 256, 0, st>>>(cw, digests, n);
+    } else {
+        MB_KERNEL_ON("hash_leaves", st);
+        hash_leaves_kernel<EXT2><<<grid_for(n, BLOCK, 16), BLOCK, 0, st>>>(cw, digests, n);
+    }
+}
+
 // Layers above the digests already present in tree[0 .. 4*num_leaves).
 inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
     uint64_t* layer = d_tree;
     size_t size = num_leaves;
     while (size > TAIL_NODES) {
         size_t half = size / 2;
-        {
-            MB_KERNEL_ON("compress_layer", st);
-            compress_layer_kernel<<<grid_for(half, BLOCK, 16), BLOCK, 0, st>>>(layer, layer + 4 * size, half);
-        }
+        launch_compress_layer(layer, layer + 4 * size, half, st);
         layer += 4 * size;
         size = half;
     }
-    if (size > 1) tree_tail_kernel<<<1, BLOCK, 0, st>>>(layer, size);
+    if (size > 1) {
+        MB_KERNEL_ON("tree_tail", st);
+        tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size);
+    }
     return finish_async();
 }
 
 template <bool EXT2>
 inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
     if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
-    {
-        MB_KERNEL_ON("hash_leaves", st);
-        hash_leaves_kernel<EXT2><<<grid_for(num_leaves, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, num_leaves);
-    }
+    launch_hash_leaves<EXT2>(d_codeword, d_tree, num_leaves, st);
     return build_layers(d_tree, num_leaves, st);
 }
 
@@ -174,10 +240,7 @@ inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, siz
     while (size > TAIL_NODES && size / copies >= 2) {
         size_t half = size / 2, u = half / copies;
         uint64_t* next = layer + 4 * size;
-        {
-            MB_KERNEL_ON("compress_layer", st);
-            compress_layer_kernel<<<grid_for(u, BLOCK, 16), BLOCK, 0, st>>>(layer, next, u);
-        }
+        launch_compress_layer(layer, next, u, st);
         {
             MB_KERNEL_ON("replicate", st);
             replicate_kernel<<<grid_for(u * 2 * (copies - 1), 256, 8), 256, 0, st>>>(next, 4 * u, copies);
@@ -188,16 +251,13 @@ inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, siz
     // the remaining layers are small: ordinary path on the fully populated layer
     while (size > TAIL_NODES) {
         size_t half = size / 2;
-        {
-            MB_KERNEL_ON("compress_layer", st);
-            compress_layer_kernel<<<grid_for(half, BLOCK, 16), BLOCK, 0, st>>>(layer, layer + 4 * size, half);
-        }
+        launch_compress_layer(layer, layer + 4 * size, half, st);
         layer += 4 * size;
         size = half;
     }
     if (size > 1) {
         MB_KERNEL_ON("tree_tail", st);
-        tree_tail_kernel<<<1, BLOCK, 0, st>>>(layer, size);
+        tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size);
     }
     return finish_async();
 }

@@ -72,6 +72,7 @@ _GL_SIGNATURES = {
     "poseidon2_merkle_layer_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "poseidon2_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "poseidon2_merkle_tree_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "mb_merkle_layer_variant": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
     "ext2_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
     "basefold_bit_reverse_gl_ffi": (c_int, [c_void_p, c_int]),
