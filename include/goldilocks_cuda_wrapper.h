@@ -78,6 +78,18 @@ int sumcheck_fold_round_mixed_ffi(const uint64_t* d_input, uint64_t* d_output, u
 int sumcheck_fold_mixed_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
                             uint64_t challenge_c1, int d, size_t original_size, size_t half);
 
+/* ---- addition: a round message that allocates nothing ----
+ * No counterpart in the reference. For hosts that cannot let the library
+ * allocate (all device memory owned by their own arena, or a loop that must not
+ * take the driver's allocation lock): the per-block partial sums live in a fixed
+ * array inside the library image (about 85 KB per GPU, held until exit).
+ * d_message receives the d + 1 evaluations P(0..d), canonical. Limits: d <= 8,
+ * half <= 2^30 (-3 beyond). First call per device resolves the array's address
+ * (do it before any stream capture). Calls on one device share the array and
+ * must not overlap. */
+int sumcheck_round_message_ext2_noalloc_ffi(const uint64_t* d_polys, uint64_t* d_message, int d,
+                                            size_t original_size, size_t half);
+
 /* ---- additions: whole sumcheck proof (host layer) ----
  * The loop of GpuLinearSumcheckProver::prove (zk-torch-3/src/sumcheck/gpu_prover.rs:37-90)
  * with the transcript of zk-torch-3/src/transcript.rs started as Transcript::new(label).

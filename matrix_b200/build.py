@@ -29,6 +29,7 @@ LIBRARIES = {
         "gl_memory.cu",
         "prof.cu",
         "gl_sumcheck.cu",
+        "gl_noalloc.cu",
         "gl_merkle.cu",
         "gl_basefold.cu",
         "host/gl_sumcheck_prover.cu",

@@ -109,6 +109,7 @@ _GL_SIGNATURES = {
     "basefold_open_ext2": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int, c_void_p, c_void_p]),
     "basefold_prove_host": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int,
                                     c_void_p, c_void_p]),
+    "sumcheck_round_message_ext2_noalloc_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t]),
     "gl_sumcheck_prove_device_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
