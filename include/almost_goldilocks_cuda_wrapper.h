@@ -1,0 +1,83 @@
+/*
+ * C-ABI of libalmost_goldilocks_cuda_wrapper: almost-Goldilocks
+ * (q = 2^64 - 2^32 - 31, extension X^2 = 3) hot path on B200 (sm_100a).
+ *
+ * Conventions as in goldilocks_cuda_wrapper.h: int return (0 ok, -1 CUDA error,
+ * -2 rejected argument, -3 unsupported size), d_* device pointers owned by the
+ * caller, loose u64 inputs, canonical outputs, calls run on the calling thread's
+ * stream and return when done. Each declaration cites the reference interface it
+ * replaces: almost-goldilocks-cuda-rs/src/ffi.rs (declaration) and
+ * almost-goldilocks-cuda-rs/cuda/wrapper.cu (definition).
+ */
+#ifndef ALMOST_GOLDILOCKS_CUDA_WRAPPER_H
+#define ALMOST_GOLDILOCKS_CUDA_WRAPPER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- init, memory, device: ffi.rs:77-100 (wrapper.cu:111-116, 205-330) ---- */
+int almost_goldilocks_cuda_init(void);
+int cuda_malloc(void** ptr, size_t size);
+int cuda_free(void* ptr);
+int cuda_memcpy_htod(void* dst, const void* src, size_t size);
+int cuda_memcpy_dtoh(void* dst, const void* src, size_t size);
+int cuda_memcpy_dtod(void* dst, const void* src, size_t size);
+int cuda_device_synchronize(void);
+int cuda_get_last_error(void);
+int cuda_peek_at_last_error(void);
+int cuda_mem_get_info(size_t* free_bytes, size_t* total_bytes);
+int cuda_set_device(int device);
+int cuda_get_device(int* device);
+int cuda_get_device_count(int* count);
+
+/* ---- field batches: ffi.rs:103-135 ---- */
+int agl_batch_add_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int agl_batch_sub_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int agl_batch_mul_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int agl_batch_inverse_ffi(const uint64_t* a, uint64_t* r, int n);
+int aext2_batch_mul_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int aext2_batch_inverse_ffi(const uint64_t* a, uint64_t* r, int n);
+
+/* ---- sumcheck: ffi.rs:221-263 (wrapper.cu:812-860); layouts as the Goldilocks twins ---- */
+int agl_sumcheck_round_message_ffi(const uint64_t* d_polys, uint64_t* d_partial, int d, size_t original_size,
+                                   size_t half, int num_blocks);
+int agl_sumcheck_fold_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge, int d,
+                          size_t original_size, size_t half);
+int aext2_sumcheck_round_message_ffi(const uint64_t* d_polys, uint64_t* d_partial, int d, size_t original_size,
+                                     size_t half, int num_blocks);
+int aext2_sumcheck_fold_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                            uint64_t challenge_c1, int d, size_t original_size, size_t half);
+/* additions: fold fused with the next round's message */
+int aext2_sumcheck_fold_round_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                                  uint64_t challenge_c1, int d, size_t original_size, size_t quarter,
+                                  uint64_t* d_partial, int num_blocks);
+int aext2_sumcheck_fold_round_mixed_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0,
+                                        uint64_t challenge_c1, int d, size_t original_size, size_t quarter,
+                                        uint64_t* d_partial, int num_blocks);
+
+/* ---- eq tables: ffi.rs (agl_eq_dp_all_ffi, aext2_eq_dp_all_ffi), wrapper.cu:640-700 ---- */
+int agl_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
+int aext2_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
+
+/* ---- partial evaluation: wrapper.cu:713-749 ---- */
+int agl_partial_eval_ffi(uint64_t* d_data, const uint64_t* d_r, int log_n, int m);
+int agl_partial_eval_ext2_from_base_ffi(const uint64_t* d_input, uint64_t* d_output, const uint64_t* d_r, int log_n,
+                                        int m);
+
+/* ---- additions shared with the Goldilocks library ---- */
+int mb_event_create(void** ev);
+int mb_event_record(void* ev);
+int mb_event_sync(void* ev);
+int mb_event_elapsed_ms(void* start, void* stop, float* ms);
+int mb_event_destroy(void* ev);
+int mb_stream_sync(void);
+uint64_t mb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

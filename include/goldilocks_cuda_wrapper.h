@@ -125,6 +125,13 @@ int mb_merkle_layer_variant(const uint64_t* d_input, uint64_t* d_output, int n, 
 int eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
 int ext2_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
 
+/* ---- partial evaluation: ffi.rs:377-390 (cuda/partial_eval.cuh:113-219) ----
+ * Fixes the m low variables at d_r[0..m). In place for the base field (results
+ * at the start of d_data); base table in, extension challenges and output for
+ * the second form. */
+int partial_eval_gl_ffi(uint64_t* d_data, const uint64_t* d_r, int log_n, int m);
+int partial_eval_ext2_from_gl_ffi(const uint64_t* d_input, uint64_t* d_output, const uint64_t* d_r, int log_n, int m);
+
 /* ---- Basefold kernels: ffi.rs:416-543 (wrapper.cu:1216-1590) ---- */
 int basefold_bit_reverse_gl_ffi(uint64_t* d_data, int log_n);
 int basefold_bit_reverse_ext2_ffi(uint64_t* d_data, int log_n);

@@ -6,4 +6,4 @@ The product is the pair of CUDA shared libraries under ``matrix_b200/lib``
 benchmarks; it contains no CPU implementation of any kernel and raises if a
 library is missing.
 """
-from .ffi import load_gl, LibraryMissing  # noqa: F401
+from .ffi import load_gl, load_agl, LibraryMissing  # noqa: F401

@@ -35,6 +35,11 @@ LIBRARIES = {
         "host/gl_sumcheck_prover.cu",
         "host/gl_basefold_prover.cu",
     ],
+    "libalmost_goldilocks_cuda_wrapper.so": [
+        "gl_memory.cu",
+        "prof.cu",
+        "agl_wrapper.cu",
+    ],
 }
 
 

@@ -1,0 +1,107 @@
+// Almost-Goldilocks field q = 2^64 - 2^32 - 31 and its quadratic extension
+// F_q[X]/(X^2 - 3) for sm_100a device code (same field as the reference's
+// cuda_almost_goldilocks/almost_goldilocks.cuh:32 and almost_extension.cuh:32).
+//
+// 2^64 = c = 2^32 + 31 (mod q). Values travel as loose residues in [0, 2^64)
+// and are made canonical where they are written out. The reduction works on
+// 32-bit limbs: with 2^96 = 2^37 + 31 (mod q),
+//   z0 + z1 2^32 + z2 2^64 + z3 2^96 = (z0 + 31 z2 + 31 z3) + 2^32 (z1 + z2 + 32 z3),
+// two limb sums below 2^39 that are folded once (the reference's
+// agl_reduce128, almost_goldilocks.cuh:176-193, runs three multiply passes).
+#pragma once
+#include "gl_field.cuh"
+
+namespace agl {
+
+using gl::add_carry;
+using gl::hi32;
+using gl::lo32;
+using gl::madwide;
+using gl::pack64;
+using gl::umulhi;
+
+constexpr uint64_t P = 0xFFFFFFFEFFFFFFE1ULL;  // q
+constexpr uint64_t C = 0x000000010000001FULL;  // 2^64 mod q = 2^32 + 31
+
+GLF uint64_t canon(uint64_t x) { return x >= P ? x - P : x; }
+
+GLF uint64_t add(uint64_t a, uint64_t b) {
+    uint64_t s = a + b;
+    if (s < a) {
+        s += C;
+        if (s < C) s += C;
+    }
+    return s;
+}
+GLF uint64_t sub(uint64_t a, uint64_t b) {
+    uint64_t d = a - b;
+    if (a < b) {
+        uint64_t e = d - C;
+        d = (d < C) ? e - C : e;
+    }
+    return d;
+}
+GLF uint64_t neg(uint64_t a) { return sub(0, a); }
+
+// L + H 2^32 mod q for L, H < 2^40, loose result. W = (A_lo : L_lo) with
+// A = L_hi + H_lo; the weight k = A_c + H_hi < 2^9 of 2^64 is worth k c < 2^42;
+// one carry fix-up, and the wrapped value is below k c so it cannot carry again.
+GLF uint64_t reduce_limb_sums(uint64_t L, uint64_t H) {
+    uint64_t A = madwide(hi32(L), 1u, (uint64_t)lo32(H));
+    uint32_t k = hi32(A) + hi32(H);
+    uint64_t W = pack64(lo32(L), lo32(A));
+    uint64_t kc = madwide(k, 31u, (uint64_t)k << 32);
+    uint32_t carry;
+    uint64_t s = add_carry(W, kc, carry);
+    return madwide(carry, 31u, s) + ((uint64_t)carry << 32);
+}
+
+GLF uint64_t reduce_limbs(uint32_t z0, uint32_t z1, uint32_t z2, uint32_t z3) {
+    uint64_t L = madwide(z3, 31u, madwide(z2, 31u, (uint64_t)z0));
+    uint64_t H = madwide(z3, 32u, madwide(z2, 1u, (uint64_t)z1));
+    return reduce_limb_sums(L, H);
+}
+GLF uint64_t reduce128(uint64_t lo, uint64_t hi) { return reduce_limbs(lo32(lo), hi32(lo), lo32(hi), hi32(hi)); }
+
+GLF uint64_t mul(uint64_t a, uint64_t b) { return reduce128(a * b, umulhi(a, b)); }
+GLF uint64_t sqr(uint64_t a) { return mul(a, a); }
+GLF uint64_t mul_small(uint64_t a, uint32_t k) {
+    uint64_t lo = a * (uint64_t)k, hi = umulhi(a, (uint64_t)k);
+    return reduce128(lo, hi);
+}
+GLF uint64_t pw(uint64_t a, uint64_t e) {
+    uint64_t r = 1;
+    while (e) {
+        if (e & 1) r = mul(r, a);
+        a = sqr(a);
+        e >>= 1;
+    }
+    return r;
+}
+GLF uint64_t inv(uint64_t a) { return pw(a, P - 2); }
+
+// Quadratic extension, X^2 = 3.
+struct E2 {
+    uint64_t c0, c1;
+};
+GLF E2 e2_add(E2 a, E2 b) { return E2{add(a.c0, b.c0), add(a.c1, b.c1)}; }
+GLF E2 e2_sub(E2 a, E2 b) { return E2{sub(a.c0, b.c0), sub(a.c1, b.c1)}; }
+GLF E2 e2_canon(E2 a) { return E2{canon(a.c0), canon(a.c1)}; }
+GLF E2 e2_mul(E2 a, E2 b) {
+    uint64_t m0 = mul(a.c0, b.c0), m1 = mul(a.c1, b.c1);
+    uint64_t x = mul(add(a.c0, a.c1), add(b.c0, b.c1));
+    return E2{add(m0, mul_small(m1, 3)), sub(sub(x, m0), m1)};
+}
+GLF E2 e2_mul_base(E2 a, uint64_t b) { return E2{mul(a.c0, b), mul(a.c1, b)}; }
+GLF E2 e2_inv(E2 a) {
+    uint64_t n = sub(sqr(a.c0), mul_small(sqr(a.c1), 3));
+    uint64_t ni = inv(n);
+    return E2{mul(a.c0, ni), mul(neg(a.c1), ni)};
+}
+GLF E2 e2_load(const uint64_t* p) {
+    ulonglong2 v = *reinterpret_cast<const ulonglong2*>(p);
+    return E2{v.x, v.y};
+}
+GLF void e2_store(uint64_t* p, E2 v) { *reinterpret_cast<ulonglong2*>(p) = make_ulonglong2(v.c0, v.c1); }
+
+}  // namespace agl

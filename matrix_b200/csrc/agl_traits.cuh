@@ -1,0 +1,69 @@
+// Field traits of almost-Goldilocks for the generic sumcheck / eq / partial
+// evaluation kernels (the Goldilocks traits live in sumcheck_kernels.cuh).
+#pragma once
+#include "agl_field.cuh"
+#include "sumcheck_kernels.cuh"
+
+namespace mb {
+namespace sc {
+
+struct AglAdd {
+    __device__ __forceinline__ uint64_t operator()(uint64_t a, uint64_t b) const { return agl::add(a, b); }
+};
+struct AglCanon {
+    __device__ __forceinline__ uint64_t operator()(uint64_t a) const { return agl::canon(a); }
+};
+
+struct AglBase {
+    using T = uint64_t;
+    using WordAdd = AglAdd;
+    using WordCanon = AglCanon;
+    static constexpr int NW = 1;
+    static __device__ __forceinline__ T load(const uint64_t* p, size_t i) { return p[i]; }
+    static __device__ __forceinline__ void load2(const uint64_t* p, size_t i, T& a, T& b) {
+        ulonglong2 v = *reinterpret_cast<const ulonglong2*>(p + i);
+        a = v.x; b = v.y;
+    }
+    static __device__ __forceinline__ void store(uint64_t* p, size_t i, T v) { p[i] = agl::canon(v); }
+    static __device__ __forceinline__ void store2(uint64_t* p, size_t i, T a, T b) {
+        *reinterpret_cast<ulonglong2*>(p + i) = make_ulonglong2(agl::canon(a), agl::canon(b));
+    }
+    static __device__ __forceinline__ T add(T a, T b) { return agl::add(a, b); }
+    static __device__ __forceinline__ T sub(T a, T b) { return agl::sub(a, b); }
+    static __device__ __forceinline__ T mul(T a, T b) { return agl::mul(a, b); }
+    static __device__ __forceinline__ T zero() { return 0; }
+    static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v; }
+};
+
+struct AglExt2 {
+    using T = agl::E2;
+    using WordAdd = AglAdd;
+    using WordCanon = AglCanon;
+    static constexpr int NW = 2;
+    static __device__ __forceinline__ T load(const uint64_t* p, size_t i) { return agl::e2_load(p + 2 * i); }
+    static __device__ __forceinline__ void load2(const uint64_t* p, size_t i, T& a, T& b) {
+        a = agl::e2_load(p + 2 * i);
+        b = agl::e2_load(p + 2 * i + 2);
+    }
+    static __device__ __forceinline__ void store(uint64_t* p, size_t i, T v) { agl::e2_store(p + 2 * i, agl::e2_canon(v)); }
+    static __device__ __forceinline__ void store2(uint64_t* p, size_t i, T a, T b) {
+        store(p, i, a);
+        store(p, i + 1, b);
+    }
+    static __device__ __forceinline__ T add(T a, T b) { return agl::e2_add(a, b); }
+    static __device__ __forceinline__ T sub(T a, T b) { return agl::e2_sub(a, b); }
+    static __device__ __forceinline__ T mul(T a, T b) { return agl::e2_mul(a, b); }
+    static __device__ __forceinline__ T zero() { return agl::E2{0, 0}; }
+    static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
+};
+
+template <>
+struct FoldOp<AglBase, AglExt2> {
+    static __device__ __forceinline__ agl::E2 apply(uint64_t a, uint64_t b, agl::E2 r) {
+        uint64_t d = agl::sub(b, a);
+        return agl::E2{agl::add(a, agl::mul(r.c0, d)), agl::mul(r.c1, d)};
+    }
+};
+
+}  // namespace sc
+}  // namespace mb

@@ -3,6 +3,7 @@
 // goldilocks-cuda-rs/cuda/wrapper.cu:1216-1590 and :2040-2110).
 #include "basefold_kernels.cuh"
 #include "eq_kernels.cuh"
+#include "peval_kernels.cuh"
 
 using namespace mb;
 using namespace mb::bf;
@@ -259,6 +260,36 @@ int ext2_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b
     if (rc != MB_OK) return rc;
     *d_result = d_buf_a;
     return finish_sync();
+}
+
+// ---- partial evaluation: ffi.rs:377-390 (cuda/partial_eval.cuh:113-219) ----
+// In place: the 2^(log_n - m) results end up at the start of d_data.
+int partial_eval_gl_ffi(uint64_t* d_data, const uint64_t* d_r, int log_n, int m) {
+    if (log_n < 0 || log_n > 40 || m < 0 || m > log_n || !d_data) return MB_ERR_ARG;
+    if (m == 0) return MB_OK;
+    size_t n = (size_t)1 << log_n;
+    uint64_t *t0 = nullptr, *t1 = nullptr;
+    MB_CUDA(pool_alloc((void**)&t0, sizeof(uint64_t) * (n >> 1)));
+    if (pool_alloc((void**)&t1, sizeof(uint64_t) * (n >> 1)) != cudaSuccess) { pool_free(t0); return MB_ERR_CUDA; }
+    int rc = pe::partial_eval<sc::GlBase, sc::GlBase>(d_data, t0, t1, d_r, log_n, m, MB_STREAM);
+    if (rc == MB_OK &&
+        cudaMemcpyAsync(d_data, t0, sizeof(uint64_t) << (log_n - m), cudaMemcpyDeviceToDevice, MB_STREAM) != cudaSuccess)
+        rc = MB_ERR_CUDA;
+    if (rc == MB_OK) rc = finish_sync();
+    pool_free(t0);
+    pool_free(t1);
+    return rc;
+}
+// Base-field table in, extension challenges (m pairs), 2^(log_n - m) extension elements out.
+int partial_eval_ext2_from_gl_ffi(const uint64_t* d_input, uint64_t* d_output, const uint64_t* d_r, int log_n, int m) {
+    if (log_n < 1 || log_n > 40 || m < 1 || m > log_n || !d_input || !d_output) return MB_ERR_ARG;
+    size_t n = (size_t)1 << log_n;
+    uint64_t* tmp = nullptr;
+    MB_CUDA(pool_alloc((void**)&tmp, 2 * sizeof(uint64_t) * (n >> 1)));
+    int rc = pe::partial_eval<sc::GlBase, sc::GlExt2>(d_input, d_output, tmp, d_r, log_n, m, MB_STREAM);
+    if (rc == MB_OK) rc = finish_sync();
+    pool_free(tmp);
+    return rc;
 }
 
 }  // extern "C"

@@ -75,6 +75,8 @@ _GL_SIGNATURES = {
     "mb_merkle_layer_variant": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
     "ext2_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "partial_eval_gl_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "partial_eval_ext2_from_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "basefold_bit_reverse_gl_ffi": (c_int, [c_void_p, c_int]),
     "basefold_bit_reverse_ext2_ffi": (c_int, [c_void_p, c_int]),
     "basefold_bhc_interpolate_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
@@ -128,6 +130,52 @@ def load_gl():
             fn.argtypes = args
         _GL = lib
     return _GL
+
+
+_AGL = None
+_MEM = ["cuda_malloc", "cuda_free", "cuda_memcpy_htod", "cuda_memcpy_dtoh", "cuda_memcpy_dtod", "cuda_device_synchronize",
+        "cuda_get_last_error", "cuda_peek_at_last_error", "cuda_mem_get_info", "cuda_set_device", "cuda_get_device",
+        "cuda_get_device_count", "mb_event_create", "mb_event_record", "mb_event_sync", "mb_event_elapsed_ms",
+        "mb_event_destroy", "mb_stream_sync", "mb_launch_count"]
+_AGL_SIGNATURES = {
+    "almost_goldilocks_cuda_init": (c_int, []),
+    "agl_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "agl_batch_sub_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "agl_batch_mul_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "agl_batch_inverse_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "aext2_batch_mul_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "aext2_batch_inverse_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "agl_sumcheck_round_message_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int]),
+    "agl_sumcheck_fold_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_size_t, c_size_t]),
+    "aext2_sumcheck_round_message_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int]),
+    "aext2_sumcheck_fold_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t]),
+    "aext2_sumcheck_fold_round_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t, c_void_p, c_int]),
+    "aext2_sumcheck_fold_round_mixed_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_size_t, c_size_t, c_void_p, c_int]),
+    "agl_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "aext2_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "agl_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "agl_partial_eval_ext2_from_base_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
+}
+
+
+def load_agl():
+    """The almost-Goldilocks library with argument types set. Raises LibraryMissing if it was not built."""
+    global _AGL
+    if _AGL is None:
+        lib = _load("libalmost_goldilocks_cuda_wrapper.so")
+        sigs = dict(_AGL_SIGNATURES)
+        for name in _MEM:
+            sigs[name] = _GL_SIGNATURES[name]
+        for name, (res, args) in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _AGL = lib
+    return _AGL
+
+
+def agl_signatures():
+    return dict(_AGL_SIGNATURES)
 
 
 def gl_signatures():

@@ -134,3 +134,22 @@ def bf_verify(root, nv, lr, point, table, num_queries, proof, label=b"bench"):
     point = np.ascontiguousarray(point, dtype=np.uint64)
     return lib.oracle_bf_verify_ext2(root.ctypes.data, nv, lr, point.ctypes.data, table.ctypes.data, label, len(label),
                                      num_queries, proof.ctypes.data)
+
+
+# ---- almost-Goldilocks and partial evaluation ------------------------------------
+_SIGS.update({
+    "oracle_agl_mul": (u64, [u64, u64]),
+    "oracle_agl_inv": (u64, [u64]),
+    "oracle_aext2_mul": (None, [vp, vp, vp]),
+    "oracle_agl_round_message": (None, [vp, ci, sz, sz, vp]),
+    "oracle_agl_fold": (None, [vp, vp, u64, ci, sz, sz]),
+    "oracle_aext2_round_message": (None, [vp, ci, sz, sz, vp]),
+    "oracle_aext2_fold": (None, [vp, vp, u64, u64, ci, sz, sz]),
+    "oracle_aext2_fold_mixed": (None, [vp, vp, u64, u64, ci, sz, sz, sz]),
+    "oracle_agl_eq_base": (None, [vp, ci, vp]),
+    "oracle_agl_eq_ext2": (None, [vp, ci, vp]),
+    "oracle_agl_partial_eval": (None, [vp, vp, vp, ci, ci]),
+    "oracle_agl_partial_eval_ext2_from_base": (None, [vp, vp, vp, ci, ci]),
+    "oracle_gl_partial_eval": (None, [vp, vp, vp, ci, ci]),
+    "oracle_gl_partial_eval_ext2_from_base": (None, [vp, vp, vp, ci, ci]),
+})

@@ -212,3 +212,29 @@ int oracle_gl_sumcheck_verify(int d, int num_var, const uint8_t *label, size_t l
     }
     return (claim.c0 == final_eval[0] && claim.c1 == final_eval[1]) ? 0 : -1000;
 }
+
+/* Partial evaluation over Goldilocks (cuda/partial_eval.cuh:31-93): fix the m low variables. */
+void oracle_gl_partial_eval(const uint64_t *in, uint64_t *out, const uint64_t *r, int log_n, int m) {
+    size_t n = (size_t)1 << log_n;
+    uint64_t *cur = (uint64_t *)malloc(sizeof(uint64_t) * n);
+    for (size_t i = 0; i < n; i++) cur[i] = gl_canon(in[i]);
+    for (int i = 0; i < m; i++) {
+        n /= 2;
+        uint64_t ri = gl_canon(r[i]);
+        for (size_t y = 0; y < n; y++) cur[y] = gl_add(cur[2 * y], gl_mul(ri, gl_sub(cur[2 * y + 1], cur[2 * y])));
+    }
+    memcpy(out, cur, sizeof(uint64_t) * n);
+    free(cur);
+}
+void oracle_gl_partial_eval_ext2_from_base(const uint64_t *in, uint64_t *out, const uint64_t *r, int log_n, int m) {
+    size_t n = (size_t)1 << log_n;
+    ext2_t *cur = (ext2_t *)malloc(sizeof(ext2_t) * n);
+    for (size_t i = 0; i < n; i++) cur[i] = e2(gl_canon(in[i]), 0);
+    for (int i = 0; i < m; i++) {
+        n /= 2;
+        ext2_t ri = e2(gl_canon(r[2 * i]), gl_canon(r[2 * i + 1]));
+        for (size_t y = 0; y < n; y++) cur[y] = e2_add(cur[2 * y], e2_mul(ri, e2_sub(cur[2 * y + 1], cur[2 * y])));
+    }
+    for (size_t y = 0; y < n; y++) { out[2 * y] = cur[y].c0; out[2 * y + 1] = cur[y].c1; }
+    free(cur);
+}

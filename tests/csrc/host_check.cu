@@ -3,6 +3,7 @@
 // oracle on a machine without a GPU. Not part of the product libraries.
 #include "gl_field.cuh"
 #include "gl_poseidon2.cuh"
+#include "agl_field.cuh"
 #include "host/gl_transcript.hpp"
 
 extern "C" {
@@ -22,6 +23,14 @@ void hc_e2_inv(const uint64_t* a, uint64_t* o) {
 uint64_t hc_gl_mul_add(uint64_t a, uint64_t b, uint64_t c) { return gl::mul_add(a, b, c); }
 uint64_t hc_gl_reduce_limb_sums(uint64_t L, uint64_t H) { return gl::reduce_limb_sums(L, H); }
 uint64_t hc_gl_reduce_limbs(uint32_t z0, uint32_t z1, uint32_t z2, uint32_t z3) { return gl::reduce_limbs(z0, z1, z2, z3); }
+uint64_t hc_agl_add(uint64_t a, uint64_t b) { return agl::add(a, b); }
+uint64_t hc_agl_sub(uint64_t a, uint64_t b) { return agl::sub(a, b); }
+uint64_t hc_agl_mul(uint64_t a, uint64_t b) { return agl::mul(a, b); }
+uint64_t hc_agl_inv(uint64_t a) { return agl::inv(a); }
+void hc_aext2_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) {
+    agl::E2 r = agl::e2_mul(agl::E2{a[0], a[1]}, agl::E2{b[0], b[1]});
+    o[0] = r.c0; o[1] = r.c1;
+}
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
 
 // Replays a script of transcript operations: op 0 = absorb(v), 1 = squeeze -> out.

@@ -118,3 +118,26 @@ def test_transcript_matches_oracle(hostcheck, oracle):
             else:
                 exp.append(oracle.gl_transcript_squeeze(ctypes.byref(t)))
         assert list(out[:k]) == exp
+
+
+def test_almost_goldilocks_loose_arithmetic(hostcheck):
+    Q = 0xFFFFFFFEFFFFFFE1
+    for name in ("hc_agl_add", "hc_agl_sub", "hc_agl_mul"):
+        getattr(hostcheck, name).restype = u64
+        getattr(hostcheck, name).argtypes = [u64, u64]
+    hostcheck.hc_agl_inv.restype = u64
+    hostcheck.hc_agl_inv.argtypes = [u64]
+    rnd = random.Random(12)
+    edge = [0, 1, Q - 1, Q, Q + 1, 2**64 - 1, 2**64 - 2, 2**32 + 31, 2**32 + 30, 2**32, 2**63, 0xFFFFFFFF00000000]
+    vals = edge + [rnd.randrange(2**64) for _ in range(300)]
+    for a in vals:
+        for b in edge + [rnd.randrange(2**64) for _ in range(20)]:
+            assert hostcheck.hc_agl_add(a, b) % Q == (a + b) % Q
+            assert hostcheck.hc_agl_sub(a, b) % Q == (a - b) % Q
+            assert hostcheck.hc_agl_mul(a, b) % Q == (a * b) % Q
+    for a in vals[:30]:
+        assert (hostcheck.hc_agl_inv(a) * a) % Q == (1 if a % Q else 0)
+    # (1 + 2X)(3 + 4X) = 27 + 10X with X^2 = 3 (almost-goldilocks-cuda-rs/tests/integration.rs:141-146)
+    A, B, O = (u64 * 2)(1, 2), (u64 * 2)(3, 4), (u64 * 2)()
+    hostcheck.hc_aext2_mul(A, B, O)
+    assert (O[0] % Q, O[1] % Q) == (27, 10)
