@@ -68,6 +68,25 @@ int agl_partial_eval_ffi(uint64_t* d_data, const uint64_t* d_r, int log_n, int m
 int agl_partial_eval_ext2_from_base_ffi(const uint64_t* d_input, uint64_t* d_output, const uint64_t* d_r, int log_n,
                                         int m);
 
+/* ---- Ajtai ring commitment: ffi.rs:426-433, 500-508, 595-617 (wrapper.cu:1095-1204, 1663-1670) ----
+ * c_i = sum_j M[i][col_offset + j] * z_j in F_q[X]/(X^64 + 1), i < 42; M from
+ * ChaCha8 keyed by d_key (8 u32). Dense: d_z[b*N + j] bit masks, d_out[b][42][64],
+ * B in {1,2,4,8,16} (else -2). Wide: d_z_wide[j*64 + l] field coefficients,
+ * d_out[42][64]. chunk in {64,128,256,1024,4096} (else -3); it is the
+ * reference's tuning knob and does not change the result. */
+int ajtai_commit_dense_batched_ffi(const uint32_t* d_key, const uint64_t* d_z, uint64_t N, int B, int chunk,
+                                   uint64_t* d_out);
+int ajtai_commit_dense_batched_at_ffi(const uint32_t* d_key, const uint64_t* d_z, uint64_t N, int B, int chunk,
+                                      uint64_t col_offset, uint64_t* d_out);
+int ajtai_commit_wide_ffi(const uint32_t* d_key, const uint64_t* d_z_wide, uint64_t N, uint64_t col_offset, int chunk,
+                          uint64_t* d_out);
+/* d_M[j][i][k], j < N (42 * 64 * 8 bytes per column) */
+int ajtai_materialize_m_ffi(const uint32_t* d_chacha_key, uint64_t* d_M, uint64_t N);
+/* addition: signed 8-bit digit planes d_digits[(p*N + j)*64 + l] in [-128, 127], d_out[p][42][64];
+ * scalar path, exact for any N */
+int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes,
+                               uint64_t col_offset, uint64_t* d_out);
+
 /* ---- additions shared with the Goldilocks library ---- */
 int mb_event_create(void** ev);
 int mb_event_record(void* ev);

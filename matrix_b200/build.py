@@ -39,6 +39,7 @@ LIBRARIES = {
         "gl_memory.cu",
         "prof.cu",
         "agl_wrapper.cu",
+        "agl_ajtai.cu",
     ],
 }
 

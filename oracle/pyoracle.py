@@ -153,3 +153,40 @@ _SIGS.update({
     "oracle_gl_partial_eval": (None, [vp, vp, vp, ci, ci]),
     "oracle_gl_partial_eval_ext2_from_base": (None, [vp, vp, vp, ci, ci]),
 })
+
+
+# ---- Ajtai ------------------------------------------------------------------------
+_SIGS.update({
+    "oracle_chacha8_block": (None, [vp, ctypes.c_uint32, vp, vp]),
+    "oracle_ajtai_ring_elem": (None, [vp, ctypes.c_uint32, u64, vp]),
+    "oracle_ajtai_commit": (None, [vp, vp, ci, u64, ci, u64, vp]),
+})
+
+AJTAI_KAPPA, AJTAI_D = 42, 64
+
+
+def ajtai_commit(key, z, kind, n_ring, planes, col_offset=0):
+    """out[planes][42][64]; kind 0 = u64 bit planes, 1 = int8 digits, 2 = u64 field coefficients."""
+    import numpy as np
+    lib = load()
+    key = np.ascontiguousarray(key, dtype=np.uint32)
+    z = np.ascontiguousarray(z)
+    out = np.zeros(planes * AJTAI_KAPPA * AJTAI_D, dtype=np.uint64)
+    lib.oracle_ajtai_commit(key.ctypes.data, z.ctypes.data, kind, n_ring, planes, col_offset, out.ctypes.data)
+    return out
+
+
+def load_ref(name):
+    """A library built from the reference's own sources (oracle/_ref), or None if absent."""
+    path = os.path.join(HERE, "_ref", name)
+    if not os.path.exists(path):
+        return None
+    lib = ctypes.CDLL(path)
+    if name == "libajtai_ref.so":
+        lib.ref_ajtai_commit_dense.argtypes = [vp, vp, u64, ci, vp]
+        lib.ref_ajtai_ring_elem.argtypes = [vp, ci, u64, vp]
+        lib.ref_ring_mul.argtypes = [vp, vp, vp]
+        lib.ref_chacha8_block.argtypes = [vp, ctypes.c_uint32, vp, vp]
+        lib.ref_agl_mul.argtypes = [u64, u64]
+        lib.ref_agl_mul.restype = u64
+    return lib

@@ -31,6 +31,35 @@ def main():
               open(os.path.join(HERE, "gl_poseidon2.json"), "w"), indent=1)
     print("wrote gl_poseidon2.json")
 
+    # Ajtai: the reference's own cpu_ajtai_commit_batched / cpu_prg_ring_elem / cpu_ring_mul
+    import hashlib
+    import numpy as np
+    aj = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libajtai_ref.so"))
+    vp, u64 = ctypes.c_void_p, ctypes.c_uint64
+    aj.ref_ajtai_commit_dense.argtypes = [vp, vp, u64, ctypes.c_int, vp]
+    aj.ref_ajtai_ring_elem.argtypes = [vp, ctypes.c_int, u64, vp]
+    key = np.arange(1, 9, dtype=np.uint32)
+    cases = []
+    rng = np.random.default_rng(20240602)
+    for (n, b) in ((4, 1), (16, 2), (33, 4)):
+        if n == 4:
+            z = np.array([0x123456789abcdef0, 0xFFFFFFFFFFFFFFFF, 0, 1], dtype=np.uint64)
+        else:
+            z = rng.integers(0, 2**63, size=n * b, dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, size=n * b, dtype=np.uint64)
+        out = np.zeros(b * 42 * 64, dtype=np.uint64)
+        aj.ref_ajtai_commit_dense(key.ctypes.data, z.ctypes.data, n, b, out.ctypes.data)
+        cases.append({"N": n, "B": b, "z": [int(x) for x in z], "first": int(out[0]), "last": int(out[-1]),
+                      "sha256": hashlib.sha256(out.tobytes()).hexdigest()})
+    elems = []
+    for (row, j) in ((0, 0), (41, 5), (7, (1 << 32) + 3)):
+        e = np.zeros(64, dtype=np.uint64)
+        aj.ref_ajtai_ring_elem(key.ctypes.data, row, j, e.ctypes.data)
+        elems.append({"row": row, "j": j, "coeffs": [int(x) for x in e]})
+    json.dump({"source": "cuda_almost_goldilocks/ajtai_cpu_reference.cuh cpu_ajtai_commit_batched<64,42>, cpu_prg_ring_elem<64>; key = 1..8",
+               "key": [int(k) for k in key], "dense": cases, "ring_elems": elems},
+              open(os.path.join(HERE, "ajtai_ref.json"), "w"), indent=1)
+    print("wrote ajtai_ref.json")
+
 
 if __name__ == "__main__":
     main()

@@ -1,0 +1,94 @@
+"""GPU parity of the Ajtai commitment against the CPU oracle (itself pinned to the
+reference's CPU code), through the C-ABI. Bit-exact."""
+import numpy as np
+import pytest
+
+from matrix_b200.ffi import DeviceBuffer, load_agl
+from matrix_b200.inputs import AGL_Q, field_elems
+
+pytestmark = pytest.mark.gpu
+Q = AGL_Q
+KEY = np.arange(1, 9, dtype=np.uint32)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    lib = load_agl()
+    assert lib.almost_goldilocks_cuda_init() == 0
+    return lib
+
+
+def test_reference_regression_vector(lib):
+    # key 1..8, z = {0x123456789abcdef0, ~0, 0, 1}: values produced by the reference's cpu_ajtai_commit
+    z = np.array([0x123456789abcdef0, 0xFFFFFFFFFFFFFFFF, 0, 1], dtype=np.uint64)
+    d_k, d_z, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, z), DeviceBuffer(lib, 42 * 64 * 8)
+    assert lib.ajtai_commit_dense_batched_ffi(d_k.ptr, d_z.ptr, 4, 1, 64, d_o.ptr) == 0
+    out = d_o.to_numpy()
+    assert int(out[0]) == 0x0d35295c35dc119b and int(out[41 * 64 + 63]) == 0x233af51a4cee11e2
+
+
+@pytest.mark.parametrize("n,b,off", [(1, 1, 0), (5, 2, 0), (37, 4, 11), (64, 8, 1 << 33), (300, 16, 5), (1500, 1, 0)])
+def test_dense_planes_match_oracle(lib, n, b, off):
+    from oracle import pyoracle
+    rng = np.random.default_rng(n + b)
+    z = rng.integers(0, 2**63, size=n * b, dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, size=n * b, dtype=np.uint64)
+    z[::7] = 0  # empty ring elements are skipped
+    d_k, d_z, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, z), DeviceBuffer(lib, b * 42 * 64 * 8)
+    assert lib.ajtai_commit_dense_batched_at_ffi(d_k.ptr, d_z.ptr, n, b, 256, off, d_o.ptr) == 0
+    assert np.array_equal(d_o.to_numpy(), pyoracle.ajtai_commit(KEY, z, 0, n, b, off))
+
+
+def test_column_shards_sum_to_the_whole(lib):
+    # the reference's test_multi_gpu_split_simulation (tests/ajtai_integration.rs:296-328): j-range shards add up
+    n = 96
+    rng = np.random.default_rng(1)
+    z = rng.integers(0, 2**63, size=n, dtype=np.uint64)
+    d_k, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer(lib, 42 * 64 * 8)
+    d_z = DeviceBuffer.from_numpy(lib, z)
+    assert lib.ajtai_commit_dense_batched_ffi(d_k.ptr, d_z.ptr, n, 1, 64, d_o.ptr) == 0
+    whole = d_o.to_numpy()
+    acc = np.zeros(42 * 64, dtype=object)
+    for lo, hi in ((0, 32), (32, 80), (80, 96)):
+        d_s = DeviceBuffer.from_numpy(lib, z[lo:hi].copy())
+        assert lib.ajtai_commit_dense_batched_at_ffi(d_k.ptr, d_s.ptr, hi - lo, 1, 64, lo, d_o.ptr) == 0
+        acc = (acc + d_o.to_numpy().astype(object)) % Q
+    assert [int(x) for x in acc] == [int(x) for x in whole]
+
+
+@pytest.mark.parametrize("n,planes,off", [(1, 1, 0), (9, 3, 2), (70, 8, 0), (200, 3, 77)])
+def test_signed_digits_match_oracle(lib, n, planes, off):
+    from oracle import pyoracle
+    rng = np.random.default_rng(n * 3 + planes)
+    dig = rng.integers(-128, 128, size=planes * n * 64, dtype=np.int8)
+    dig[:64] = 127
+    dig[64:128] = -128
+    d_k, d_z = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, dig)
+    d_o = DeviceBuffer(lib, planes * 42 * 64 * 8)
+    assert lib.ajtai_commit_s8_scalar_ffi(d_k.ptr, d_z.ptr, n, planes, off, d_o.ptr) == 0
+    assert np.array_equal(d_o.to_numpy(), pyoracle.ajtai_commit(KEY, dig, 1, n, planes, off))
+
+
+@pytest.mark.parametrize("n,off", [(1, 0), (20, 3), (130, 0)])
+def test_wide_matches_oracle(lib, n, off):
+    from oracle import pyoracle
+    w = field_elems(50 + n, n * 64, Q)
+    w[:3] = [0, Q - 1, 1]
+    d_k, d_z, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, w), DeviceBuffer(lib, 42 * 64 * 8)
+    assert lib.ajtai_commit_wide_ffi(d_k.ptr, d_z.ptr, n, off, 128, d_o.ptr) == 0
+    assert np.array_equal(d_o.to_numpy(), pyoracle.ajtai_commit(KEY, w, 2, n, 1, off))
+
+
+def test_materialised_matrix_and_argument_checks(lib):
+    n = 3
+    d_k, d_m = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer(lib, n * 42 * 64 * 8)
+    assert lib.ajtai_materialize_m_ffi(d_k.ptr, d_m.ptr, n) == 0
+    m = d_m.to_numpy().reshape(n, 42, 64)
+    from oracle import pyoracle
+    o = pyoracle.load()
+    for (j, i) in ((0, 0), (2, 41), (1, 17)):
+        e = np.zeros(64, dtype=np.uint64)
+        o.oracle_ajtai_ring_elem(KEY.ctypes.data, i, j, e.ctypes.data)
+        assert np.array_equal(m[j, i], e)
+    d_z, d_o = DeviceBuffer(lib, 64), DeviceBuffer(lib, 16 * 42 * 64 * 8)
+    assert lib.ajtai_commit_dense_batched_ffi(d_k.ptr, d_z.ptr, 1, 3, 64, d_o.ptr) == -2   # B not a power of two <= 16
+    assert lib.ajtai_commit_dense_batched_ffi(d_k.ptr, d_z.ptr, 1, 1, 100, d_o.ptr) == -3  # unsupported chunk
