@@ -87,6 +87,11 @@ int ajtai_materialize_m_ffi(const uint32_t* d_chacha_key, uint64_t* d_M, uint64_
 int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes,
                                uint64_t col_offset, uint64_t* d_out);
 
+/* addition: the signed-digit commit on the tensor cores (tcgen05 kind::i8, exact s32 accumulation, byte-plane
+ * recombination mod q); digits in [-127, 127] (-3 if a -128 is present), any number of planes */
+int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
+                        uint64_t* d_out);
+
 /* ---- additions shared with the Goldilocks library ---- */
 int mb_event_create(void** ev);
 int mb_event_record(void* ev);

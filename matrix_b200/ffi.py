@@ -157,6 +157,7 @@ _AGL_SIGNATURES = {
     "ajtai_commit_dense_batched_at_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_int, c_u64, c_void_p]),
     "ajtai_commit_wide_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_void_p]),
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
+    "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "agl_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "agl_partial_eval_ext2_from_base_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),

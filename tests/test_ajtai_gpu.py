@@ -68,6 +68,31 @@ def test_signed_digits_match_oracle(lib, n, planes, off):
     assert np.array_equal(d_o.to_numpy(), pyoracle.ajtai_commit(KEY, dig, 1, n, planes, off))
 
 
+@pytest.mark.parametrize("n,planes,off", [(1, 1, 0), (4, 1, 0), (5, 3, 9), (70, 4, 0), (130, 8, 3), (600, 3, 1 << 20)])
+def test_tensor_core_digits_match_oracle(lib, n, planes, off):
+    # tcgen05 path: exact integer accumulation, so the result must equal the CPU oracle bit for bit;
+    # n = 600 crosses the 512-column drain boundary, planes = 8 runs two plane groups
+    from oracle import pyoracle
+    rng = np.random.default_rng(n * 5 + planes)
+    dig = rng.integers(-127, 128, size=planes * n * 64, dtype=np.int8)
+    dig[:64] = 127
+    dig[-64:] = -127
+    d_k, d_z = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, dig)
+    d_o = DeviceBuffer(lib, planes * 42 * 64 * 8)
+    assert lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n, planes, off, d_o.ptr) == 0
+    got = d_o.to_numpy()
+    exp = pyoracle.ajtai_commit(KEY, dig, 1, n, planes, off)
+    bad = np.nonzero(got != exp)[0]
+    assert len(bad) == 0, "%d of %d words differ, first at %d" % (len(bad), len(exp), bad[0])
+
+
+def test_tensor_core_rejects_minus_128(lib):
+    dig = np.zeros(64, dtype=np.int8)
+    dig[5] = -128
+    d_k, d_z, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, dig), DeviceBuffer(lib, 42 * 64 * 8)
+    assert lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, 1, 1, 0, d_o.ptr) == -3
+
+
 @pytest.mark.parametrize("n,off", [(1, 0), (20, 3), (130, 0)])
 def test_wide_matches_oracle(lib, n, off):
     from oracle import pyoracle
