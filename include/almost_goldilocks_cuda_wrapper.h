@@ -68,6 +68,12 @@ int agl_partial_eval_ffi(uint64_t* d_data, const uint64_t* d_r, int log_n, int m
 int agl_partial_eval_ext2_from_base_ffi(const uint64_t* d_input, uint64_t* d_output, const uint64_t* d_r, int log_n,
                                         int m);
 
+/* ---- fused bit-permutation + partial evaluation: wrapper.cu:755-800 ----
+ * out[j] = sum_b evals[lo_lut[x & (2^half - 1)] | hi_lut[x >> half]] * eq[b], x = j 2^m + b; base-field
+ * evals, extension eq table and output; smem_bytes is accepted for compatibility and ignored. */
+int agl_fused_permute_partial_eval_ffi(const uint64_t* d_evals, uint64_t* d_output, const uint64_t* d_eq_table, const uint32_t* d_lo_lut,
+       const uint32_t* d_hi_lut, int n, int m, int half, int output_size, int smem_bytes);
+
 /* ---- Ajtai ring commitment: ffi.rs:426-433, 500-508, 595-617 (wrapper.cu:1095-1204, 1663-1670) ----
  * c_i = sum_j M[i][col_offset + j] * z_j in F_q[X]/(X^64 + 1), i < 42; M from
  * ChaCha8 keyed by d_key (8 u32). Dense: d_z[b*N + j] bit masks, d_out[b][42][64],

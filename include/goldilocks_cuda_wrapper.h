@@ -125,12 +125,36 @@ int mb_merkle_layer_variant(const uint64_t* d_input, uint64_t* d_output, int n, 
 int eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
 int ext2_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result);
 
+/* ---- Fiat-Shamir challenger: ffi.rs:315-371 (wrapper.cu:1004-1110, cuda/challenger.cuh:42-366) ----
+ * n independent duplex sponges (Poseidon2 width 8, rate 4). d_states is opaque
+ * (challenger_state_size() bytes each; challenger_alloc_states returns memory to
+ * release with cuda_free). observe: d_values[i] (or [i*count + k], or (c0, c1)
+ * pairs); sample: d_outputs[i] (or [i*count + k]). */
+int challenger_state_size(void);
+int challenger_alloc_states(void** d_states, int n);
+int challenger_init_states(void* d_states, int n);
+int challenger_observe_ffi(void* d_states, const uint64_t* d_values, int n);
+int challenger_observe_slice_ffi(void* d_states, const uint64_t* d_values, int count, int n);
+int challenger_sample_ffi(void* d_states, uint64_t* d_outputs, int n);
+int challenger_sample_array_ffi(void* d_states, uint64_t* d_outputs, int count, int n);
+int challenger_sample_ext2_ffi(void* d_states, uint64_t* d_outputs, int n);
+int challenger_sample_ext5_ffi(void* d_states, uint64_t* d_outputs, int n);
+int challenger_observe_ext2_ffi(void* d_states, const uint64_t* d_values, int n);
+int challenger_copy_state_to_host(void* h_state, const void* d_state);
+int challenger_copy_state_to_device(void* d_state, const void* h_state);
+
 /* ---- partial evaluation: ffi.rs:377-390 (cuda/partial_eval.cuh:113-219) ----
  * Fixes the m low variables at d_r[0..m). In place for the base field (results
  * at the start of d_data); base table in, extension challenges and output for
  * the second form. */
 int partial_eval_gl_ffi(uint64_t* d_data, const uint64_t* d_r, int log_n, int m);
 int partial_eval_ext2_from_gl_ffi(const uint64_t* d_input, uint64_t* d_output, const uint64_t* d_r, int log_n, int m);
+
+/* ---- fused bit-permutation + partial evaluation: ffi.rs:657-668 (cuda/fused_permute_peval.cuh:31-120) ----
+ * out[j] = sum_b evals[lo_lut[x & (2^half - 1)] | hi_lut[x >> half]] * eq[b], x = j 2^m + b; base-field
+ * evals, extension eq table and output; smem_bytes is accepted for compatibility and ignored. */
+int fused_permute_partial_eval_ffi(const uint64_t* d_evals, uint64_t* d_output, const uint64_t* d_eq_table, const uint32_t* d_lo_lut,
+       const uint32_t* d_hi_lut, int n, int m, int half, int output_size, int smem_bytes);
 
 /* ---- Basefold kernels: ffi.rs:416-543 (wrapper.cu:1216-1590) ---- */
 int basefold_bit_reverse_gl_ffi(uint64_t* d_data, int log_n);

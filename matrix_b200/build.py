@@ -32,6 +32,7 @@ LIBRARIES = {
         "gl_noalloc.cu",
         "gl_merkle.cu",
         "gl_basefold.cu",
+        "gl_challenger.cu",
         "host/gl_sumcheck_prover.cu",
         "host/gl_basefold_prover.cu",
     ],

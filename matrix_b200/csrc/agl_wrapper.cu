@@ -7,6 +7,7 @@
 #include "eq_kernels.cuh"
 #include "gl_sumcheck_launch.cuh"
 #include "peval_kernels.cuh"
+#include "fused_peval_kernels.cuh"
 
 using namespace mb;
 using namespace mb::sc;
@@ -170,6 +171,16 @@ int agl_partial_eval_ext2_from_base_ffi(const uint64_t* d_input, uint64_t* d_out
     if (rc == MB_OK) rc = finish_sync();
     pool_free(tmp);
     return rc;
+}
+
+// ---- fused permute + partial evaluation: wrapper.cu:755-800 ----
+int agl_fused_permute_partial_eval_ffi(const uint64_t* d_evals, uint64_t* d_output, const uint64_t* d_eq_table,
+                                       const uint32_t* d_lo_lut, const uint32_t* d_hi_lut, int n, int m, int half,
+                                       int output_size, int smem_bytes) {
+    (void)smem_bytes;
+    int rc = fp::launch<AglBase, AglExt2>(d_evals, d_output, d_eq_table, d_lo_lut, d_hi_lut, n, m, half, output_size,
+                                          MB_STREAM);
+    return rc != MB_OK ? rc : finish_sync();
 }
 
 }  // extern "C"

@@ -4,6 +4,7 @@
 #include "basefold_kernels.cuh"
 #include "eq_kernels.cuh"
 #include "peval_kernels.cuh"
+#include "fused_peval_kernels.cuh"
 
 using namespace mb;
 using namespace mb::bf;
@@ -260,6 +261,17 @@ int ext2_eq_dp_all_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b
     if (rc != MB_OK) return rc;
     *d_result = d_buf_a;
     return finish_sync();
+}
+
+// ---- fused permute + partial evaluation: ffi.rs:657-668 (cuda/fused_permute_peval.cuh:31-120) ----
+// smem_bytes is the reference's launch parameter; the library sizes its own shared memory.
+int fused_permute_partial_eval_ffi(const uint64_t* d_evals, uint64_t* d_output, const uint64_t* d_eq_table,
+                                   const uint32_t* d_lo_lut, const uint32_t* d_hi_lut, int n, int m, int half,
+                                   int output_size, int smem_bytes) {
+    (void)smem_bytes;
+    int rc = fp::launch<sc::GlBase, sc::GlExt2>(d_evals, d_output, d_eq_table, d_lo_lut, d_hi_lut, n, m, half, output_size,
+                                                MB_STREAM);
+    return rc != MB_OK ? rc : finish_sync();
 }
 
 // ---- partial evaluation: ffi.rs:377-390 (cuda/partial_eval.cuh:113-219) ----

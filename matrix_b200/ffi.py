@@ -75,6 +75,19 @@ _GL_SIGNATURES = {
     "mb_merkle_layer_variant": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
     "ext2_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "challenger_state_size": (c_int, []),
+    "challenger_alloc_states": (c_int, [ctypes.POINTER(c_void_p), c_int]),
+    "challenger_init_states": (c_int, [c_void_p, c_int]),
+    "challenger_observe_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "challenger_observe_slice_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "challenger_sample_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "challenger_sample_array_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "challenger_sample_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "challenger_sample_ext5_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "challenger_observe_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "challenger_copy_state_to_host": (c_int, [c_void_p, c_void_p]),
+    "challenger_copy_state_to_device": (c_int, [c_void_p, c_void_p]),
+    "fused_permute_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "partial_eval_gl_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "partial_eval_ext2_from_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "basefold_bit_reverse_gl_ffi": (c_int, [c_void_p, c_int]),
@@ -159,6 +172,7 @@ _AGL_SIGNATURES = {
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
+    "agl_fused_permute_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "agl_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "agl_partial_eval_ext2_from_base_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
 }

@@ -176,3 +176,44 @@ def test_partial_eval_both_fields(lib, oracle, log_n, m):
             exp2 = np.zeros(2 * (n >> m), dtype=np.uint64)
             opex(data.ctypes.data, exp2.ctypes.data, r.ctypes.data, log_n, m)
             assert np.array_equal(d_out.to_numpy()[:2 * (n >> m)], exp2), field
+
+
+def _split_luts(n, new_var_order, half):
+    # almost-goldilocks-cuda-rs/src/partial_eval.rs:283-321
+    inv = list(new_var_order)  # new position -> old variable
+    lo = np.zeros(1 << half, dtype=np.uint32)
+    for x in range(1 << half):
+        lo[x] = sum(1 << inv[bit] for bit in range(half) if x >> bit & 1)
+    hi = np.zeros(1 << (n - half), dtype=np.uint32)
+    for x in range(1 << (n - half)):
+        hi[x] = sum(1 << inv[half + bit] for bit in range(n - half) if x >> bit & 1)
+    return lo, hi
+
+
+@pytest.mark.parametrize("n,m,half", [(4, 2, 2), (10, 4, 5), (13, 6, 6), (16, 9, 8), (17, 0, 9)])
+def test_fused_permute_partial_eval_both_fields(lib, oracle, n, m, half):
+    gl = load_gl()
+    rng = np.random.default_rng(n)
+    order = list(rng.permutation(n))
+    lo, hi = _split_luts(n, order, half)
+    perm = np.array([int(lo[x & ((1 << half) - 1)]) | int(hi[x >> half]) for x in range(1 << n)], dtype=np.int64)
+    for L, mod, fn, eqfn, pex in (
+            (lib, Q, lib.agl_fused_permute_partial_eval_ffi, oracle.oracle_agl_eq_ext2, oracle.oracle_agl_partial_eval_ext2_from_base),
+            (gl, GL_P, gl.fused_permute_partial_eval_ffi, oracle.oracle_gl_eq_ext2, oracle.oracle_gl_partial_eval_ext2_from_base)):
+        evals = field_elems(900 + n, 1 << n, mod)
+        r = field_elems(901 + n, 2 * max(m, 1), mod)
+        eq = np.zeros(2 << m, dtype=np.uint64)
+        eqfn(r.ctypes.data, m, eq.ctypes.data)
+        out_size = 1 << (n - m)
+        d_e, d_q = DeviceBuffer.from_numpy(L, evals), DeviceBuffer.from_numpy(L, eq)
+        d_lo, d_hi = DeviceBuffer.from_numpy(L, lo), DeviceBuffer.from_numpy(L, hi)
+        d_o = DeviceBuffer(L, 16 * out_size)
+        assert fn(d_e.ptr, d_o.ptr, d_q.ptr, d_lo.ptr, d_hi.ptr, n, m, half, out_size, 0) == 0
+        # expected: permute on the host, then the oracle's partial evaluation of the m low variables
+        permuted = evals[perm]
+        exp = np.zeros(2 * out_size, dtype=np.uint64)
+        if m == 0:
+            exp[0::2] = permuted
+        else:
+            pex(permuted.ctypes.data, exp.ctypes.data, r.ctypes.data, n, m)
+        assert np.array_equal(d_o.to_numpy(), exp)
