@@ -213,6 +213,31 @@ int basefold_prove_host(const uint64_t* h_evals, int num_vars, int log_rate, con
                         const void* table, const uint8_t* label, size_t label_len, int num_queries, uint64_t* h_root,
                         uint64_t* h_proof);
 
+/* ---- additions: batched degree-3 sumcheck with a shared eq table, one shard ----
+ * S = sum_k alpha^k sum_x eq(t, x) a_k(x) b_k(x). d_a, d_b: [K][2^n_loc] base-field
+ * slices of this shard; h_point_low: n_loc (c0, c1) pairs; h_eq_scale: eq of the
+ * sharded (top) coordinates at this shard's index, (1, 0) for a single shard.
+ * claims: K local shares of the per-instance sums; round_message: local share of
+ * m(0..3) (4 extension elements); fold binds the low variable on the challenge;
+ * finals (after n_loc folds): eq, alpha^k a_k (K), b_k (K). The caller adds the
+ * shards' shares and runs the transcript (matrix_b200/sharded.py). */
+int gl_batched_state_create(const uint64_t* d_a, const uint64_t* d_b, const uint64_t* h_point_low,
+                            const uint64_t* h_eq_scale, int K, int n_loc, void** state);
+int gl_batched_state_destroy(void* state);
+int gl_batched_state_claims(void* state, uint64_t* h_claims);
+int gl_batched_state_set_alpha(void* state, uint64_t c0, uint64_t c1);
+int gl_batched_state_round_message(void* state, uint64_t* h_msg);
+int gl_batched_state_fold(void* state, uint64_t c0, uint64_t c1);
+int gl_batched_state_finals(void* state, uint64_t* h_out);
+
+/* ---- additions: the host transcript (zk-torch-3/src/transcript.rs:174-350) ---- */
+int gl_transcript_create(const uint8_t* label, size_t label_len, void** transcript);
+int gl_transcript_destroy(void* transcript);
+int gl_transcript_append_u64(void* transcript, const char* label, uint64_t v);
+int gl_transcript_append_ext2(void* transcript, const char* label, uint64_t c0, uint64_t c1);
+int gl_transcript_challenge_ext2(void* transcript, const char* label, uint64_t* out2);
+int gl_transcript_state(const void* transcript, uint64_t* out8);
+
 /* ---- additions: pinned memory, stream and timing helpers ---- */
 int mb_host_alloc(void** ptr, size_t size);
 int mb_host_free(void* ptr);

@@ -16,16 +16,18 @@ namespace eq {
 
 // Block b builds the table over variables [lo_b, lo_b + nbits_b) into out_b,
 // doubling in place: out[j + half] = a r, out[j] = a - a r.
+// `init` (may be null) points at one element that replaces the initial 1 of block 0's
+// table, which scales the whole eq table by it.
 template <class F>
 __global__ void small_tables_kernel(const uint64_t* __restrict__ r, int nbits0, uint64_t* out0, int nbits1,
-                                    uint64_t* out1) {
+                                    uint64_t* out1, const uint64_t* __restrict__ init = nullptr) {
     using T = typename F::T;
     const int var_lo = blockIdx.x == 0 ? 0 : nbits0;
     const int nbits = blockIdx.x == 0 ? nbits0 : nbits1;
     uint64_t* out = blockIdx.x == 0 ? out0 : out1;
     if (threadIdx.x == 0) {
         uint64_t one[2] = {1, 0};
-        for (int w = 0; w < F::NW; w++) out[w] = one[w];
+        for (int w = 0; w < F::NW; w++) out[w] = (init != nullptr && blockIdx.x == 0) ? init[w] : one[w];
     }
     __syncthreads();
     for (int i = 0; i < nbits; i++) {
@@ -53,12 +55,13 @@ __global__ void outer_product_kernel(const uint64_t* __restrict__ lo, const uint
 // Builds the table in d_out (2^log_n elements). d_scratch needs room for
 // 2^(log_n/2) + 2^(log_n - log_n/2) elements when log_n > 12 (unused otherwise).
 template <class F>
-inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int log_n, cudaStream_t st) {
+inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int log_n, cudaStream_t st,
+                 const uint64_t* d_init = nullptr) {
     if (log_n < 0 || log_n > 40 || !d_out || (log_n > 0 && !d_r)) return MB_ERR_ARG;
     if (log_n <= 12) {
         {
             MB_KERNEL_ON("small_tables", st);
-            small_tables_kernel<F><<<1, 256, 0, st>>>(d_r, log_n, d_out, 0, d_out);
+            small_tables_kernel<F><<<1, 256, 0, st>>>(d_r, log_n, d_out, 0, d_out, d_init);
         }
         return finish_async();
     }
@@ -68,7 +71,7 @@ inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int 
     uint64_t* hi = d_scratch + ((size_t)F::NW << n_lo);
     {
         MB_KERNEL_ON("small_tables", st);
-        small_tables_kernel<F><<<2, 1024, 0, st>>>(d_r, n_lo, lo, n_hi, hi);
+        small_tables_kernel<F><<<2, 1024, 0, st>>>(d_r, n_lo, lo, n_hi, hi, d_init);
     }
     size_t n = (size_t)1 << log_n;
     {

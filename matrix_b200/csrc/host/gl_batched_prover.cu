@@ -1,0 +1,229 @@
+// Host layer for the batched degree-3 sumcheck (shared eq table, K instances
+// combined with powers of alpha) over Goldilocks, one shard of the hypercube.
+//
+// A shard holds the slice of every table whose top index bits equal the shard
+// number: a_k, b_k slices of 2^n_loc base-field elements, and the eq slice
+// eq(t_low, x_low) * eq(t_top, shard) (the scalar is passed in). The per-round
+// API mirrors the reference's state objects (compute message, then fold on the
+// challenge; almost-goldilocks-cuda-rs/src/sumcheck_prover.rs:127-436): the
+// caller adds the shards' messages, runs the transcript and broadcasts the
+// challenge. With one shard it is the whole prover. The C-ABI below also exposes
+// the host transcript (zk-torch-3/src/transcript.rs:174-350) so that callers in
+// any language run the same Fiat-Shamir.
+#include <cstring>
+#include <vector>
+#include "../batched_kernels.cuh"
+#include "../eq_kernels.cuh"
+#include "gl_transcript.hpp"
+
+using namespace mb;
+using namespace mb::sc;
+
+namespace mbhost {
+
+class BatchedEqAbState {
+public:
+    ~BatchedEqAbState() { release(); }
+
+    int init(const uint64_t* d_a, const uint64_t* d_b, const uint64_t* h_point_low, const uint64_t* h_eq_scale, int K,
+             int n_loc) {
+        if (!d_a || !d_b || !h_eq_scale || K < 1 || K > bt::MAX_K || n_loc < 1 || n_loc > 34) return MB_ERR_ARG;
+        if (n_loc > 0 && !h_point_low) return MB_ERR_ARG;
+        K_ = K; n_loc_ = n_loc; n_ = (size_t)1 << n_loc; round_ = 0; have_msg_ = false; have_alpha_ = false;
+        // tables: [K][2][n] base (copied so that the caller's buffers stay untouched and contiguous)
+        MB_CUDA(pool_alloc((void**)&ab_base_, sizeof(uint64_t) * 2 * K * n_));
+        for (int k = 0; k < K; k++) {
+            MB_CUDA(cudaMemcpyAsync(ab_base_ + (size_t)(2 * k) * n_, d_a + (size_t)k * n_, 8 * n_, cudaMemcpyDeviceToDevice, MB_STREAM));
+            MB_CUDA(cudaMemcpyAsync(ab_base_ + (size_t)(2 * k + 1) * n_, d_b + (size_t)k * n_, 8 * n_, cudaMemcpyDeviceToDevice, MB_STREAM));
+        }
+        size_t half = n_ / 2, quarter = n_ >= 4 ? n_ / 4 : 1;
+        MB_CUDA(pool_alloc((void**)&eq0_, 16 * n_));
+        MB_CUDA(pool_alloc((void**)&eq_a_, 16 * half));
+        MB_CUDA(pool_alloc((void**)&eq_b_, 16 * quarter));
+        MB_CUDA(pool_alloc((void**)&ab_a_, 16 * 2 * K * half));
+        MB_CUDA(pool_alloc((void**)&ab_b_, 16 * 2 * K * quarter));
+        grid_max_ = grid_for(half, 256, 4);
+        MB_CUDA(pool_alloc((void**)&partial_, sizeof(uint64_t) * 2 * (size_t)(K > bt::NC ? K : bt::NC) * grid_max_));
+        MB_CUDA(pool_alloc((void**)&small_, sizeof(uint64_t) * (16 + 2 * bt::MAX_K + 2 * 40 + 2)));
+        msg_dev_ = small_;                      // 8 words
+        counter_ = reinterpret_cast<unsigned int*>(small_ + 8);
+        alpha_dev_ = small_ + 16;               // 2 * MAX_K words
+        uint64_t* point_dev = alpha_dev_ + 2 * bt::MAX_K;  // 2 * 40 words
+        uint64_t* scale_dev = point_dev + 80;               // 2 words
+        MB_CUDA(cudaMemsetAsync(small_, 0, 16 * sizeof(uint64_t), MB_STREAM));
+        MB_CUDA(cudaMemcpyAsync(point_dev, h_point_low, 16 * (size_t)n_loc, cudaMemcpyHostToDevice, MB_STREAM));
+        MB_CUDA(cudaMemcpyAsync(scale_dev, h_eq_scale, 16, cudaMemcpyHostToDevice, MB_STREAM));
+        // eq slice scaled by eq(t_top, shard); ab_a_ is free until the first fold and serves as scratch
+        int rc = eq::build<GlExt2>(point_dev, eq0_, ab_a_, n_loc, MB_STREAM, scale_dev);
+        if (rc != MB_OK) return rc;
+        h_ = pinned_scratch();
+        return h_ ? MB_OK : MB_ERR_CUDA;
+    }
+
+    // Local share of the per-instance claims s_k (K extension elements).
+    int claims(uint64_t* h_out) {
+        int grid = grid_for(n_, 256, 2);
+        if (grid > grid_max_) grid = grid_max_;
+        {
+            MB_KERNEL("batched_claims");
+            bt::claims_kernel<GlBase, GlExt2><<<grid, 256, 0, MB_STREAM>>>(eq0_, ab_base_, K_, n_, n_, partial_);
+        }
+        uint64_t* d_out = nullptr;
+        MB_CUDA(pool_alloc((void**)&d_out, 16 * (size_t)K_));
+        {
+            MB_KERNEL("reduce_partials");
+            reduce_partials_kernel<256, GlAdd, GlCanon><<<1, 256, 0, MB_STREAM>>>(partial_, grid, 2 * K_, d_out);
+        }
+        MB_CUDA(cudaMemcpyAsync(h_out, d_out, 16 * (size_t)K_, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        pool_free(d_out);
+        return MB_OK;
+    }
+
+    int set_alpha(Ext2 alpha) {
+        std::vector<uint64_t> pows(2 * K_);
+        gl::E2 p{1, 0}, a{gl::canon(alpha.c0), gl::canon(alpha.c1)};
+        for (int k = 0; k < K_; k++) {
+            pows[2 * k] = p.c0;
+            pows[2 * k + 1] = p.c1;
+            p = gl::e2_canon(gl::e2_mul(p, a));
+        }
+        MB_CUDA(cudaMemcpyAsync(alpha_dev_, pows.data(), 16 * (size_t)K_, cudaMemcpyHostToDevice, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        have_alpha_ = true;
+        return MB_OK;
+    }
+
+    // Local share of m(0..3) for the current round.
+    int round_message(uint64_t* h_msg) {
+        if (!have_alpha_ || round_ >= n_loc_) return MB_ERR_ARG;
+        if (!have_msg_) {
+            size_t half = n_ / 2;
+            MB_KERNEL("batched_round0");
+            bt::round0_message_kernel<GlBase, GlExt2><<<grid_for(half, 256, 4), 256, 0, MB_STREAM>>>(
+                eq0_, ab_base_, alpha_dev_, K_, n_, half, partial_, counter_, msg_dev_);
+        }
+        MB_CUDA(cudaMemcpyAsync(h_, msg_dev_, 64, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        std::memcpy(h_msg, h_, 64);
+        return MB_OK;
+    }
+
+    int fold(Ext2 ch) {
+        if (!have_alpha_ || round_ >= n_loc_) return MB_ERR_ARG;
+        gl::E2 r{gl::canon(ch.c0), gl::canon(ch.c1)};
+        size_t live = n_ >> round_, quarter = live / 4;
+        bool first = round_ == 0;
+        const uint64_t* eq_in = first ? eq0_ : eq_cur_;
+        const uint64_t* ab_in = first ? ab_base_ : ab_cur_;
+        size_t stride_in = first ? n_ : ab_stride_;
+        bool to_a = first || ab_cur_ == ab_b_;
+        uint64_t* eq_out = to_a ? eq_a_ : eq_b_;
+        uint64_t* ab_out = to_a ? ab_a_ : ab_b_;
+        size_t stride_out = to_a ? n_ / 2 : (n_ >= 4 ? n_ / 4 : 1);
+        if (quarter >= 1) {
+            int grid = grid_for(quarter, 256, 4);
+            MB_KERNEL("batched_fold_message");
+            if (first)
+                bt::fold_message_kernel<GlBase, GlExt2, true><<<grid, 256, 0, MB_STREAM>>>(
+                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+            else
+                bt::fold_message_kernel<GlBase, GlExt2, false><<<grid, 256, 0, MB_STREAM>>>(
+                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+            have_msg_ = true;
+        } else {
+            MB_KERNEL("batched_final_fold");
+            int threads = 2 * K_ + 1;
+            if (first)
+                bt::final_fold_kernel<GlBase, GlExt2, true><<<(threads + 127) / 128, 128, 0, MB_STREAM>>>(
+                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out);
+            else
+                bt::final_fold_kernel<GlBase, GlExt2, false><<<(threads + 127) / 128, 128, 0, MB_STREAM>>>(
+                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out);
+            have_msg_ = false;
+        }
+        if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+        eq_cur_ = eq_out;
+        ab_cur_ = ab_out;
+        ab_stride_ = stride_out;
+        round_++;
+        return MB_OK;
+    }
+
+    // After n_loc folds: eq, then alpha^k a_k, b_k for every k: (2K + 1) extension elements.
+    int finals(uint64_t* h_out) {
+        if (round_ != n_loc_) return MB_ERR_ARG;
+        MB_CUDA(cudaMemcpyAsync(h_out, eq_cur_, 16, cudaMemcpyDeviceToHost, MB_STREAM));
+        for (int t = 0; t < 2 * K_; t++) {
+            int k = t >> 1, which = t & 1;  // output order: a'_0 .. a'_{K-1}, b_0 .. b_{K-1}
+            uint64_t* dst = h_out + 2 + 2 * (size_t)(which * K_ + k);
+            MB_CUDA(cudaMemcpyAsync(dst, ab_cur_ + (size_t)t * ab_stride_ * 2, 16, cudaMemcpyDeviceToHost, MB_STREAM));
+        }
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        return MB_OK;
+    }
+
+private:
+    void release() {
+        pool_free(ab_base_); pool_free(eq0_); pool_free(eq_a_); pool_free(eq_b_); pool_free(ab_a_); pool_free(ab_b_);
+        pool_free(partial_); pool_free(small_);
+        ab_base_ = eq0_ = eq_a_ = eq_b_ = ab_a_ = ab_b_ = partial_ = small_ = nullptr;
+    }
+    int K_ = 0, n_loc_ = 0, round_ = 0, grid_max_ = 0;
+    size_t n_ = 0, ab_stride_ = 0;
+    bool have_msg_ = false, have_alpha_ = false;
+    uint64_t *ab_base_ = nullptr, *eq0_ = nullptr, *eq_a_ = nullptr, *eq_b_ = nullptr, *ab_a_ = nullptr, *ab_b_ = nullptr;
+    uint64_t *partial_ = nullptr, *small_ = nullptr, *msg_dev_ = nullptr, *alpha_dev_ = nullptr, *eq_cur_ = nullptr, *ab_cur_ = nullptr;
+    unsigned int* counter_ = nullptr;
+    uint64_t* h_ = nullptr;
+};
+
+}  // namespace mbhost
+
+using mbhost::BatchedEqAbState;
+using mbhost::Ext2;
+using mbhost::Transcript;
+
+extern "C" {
+
+// ---- one shard of the batched eq * a_k * b_k sumcheck ----
+// d_a, d_b: [K][2^n_loc] base-field slices; h_point_low: n_loc (c0, c1) pairs (the
+// shard-local coordinates of the eq point); h_eq_scale: eq of the top coordinates
+// at this shard's index ((1, 0) for a single shard).
+int gl_batched_state_create(const uint64_t* d_a, const uint64_t* d_b, const uint64_t* h_point_low,
+                            const uint64_t* h_eq_scale, int K, int n_loc, void** state) {
+    if (!state) return MB_ERR_ARG;
+    auto* s = new BatchedEqAbState;
+    int rc = s->init(d_a, d_b, h_point_low, h_eq_scale, K, n_loc);
+    if (rc != MB_OK) { delete s; return rc; }
+    *state = s;
+    return MB_OK;
+}
+int gl_batched_state_destroy(void* state) { delete static_cast<BatchedEqAbState*>(state); return MB_OK; }
+int gl_batched_state_claims(void* state, uint64_t* h_claims) { return static_cast<BatchedEqAbState*>(state)->claims(h_claims); }
+int gl_batched_state_set_alpha(void* state, uint64_t c0, uint64_t c1) { return static_cast<BatchedEqAbState*>(state)->set_alpha(Ext2{c0, c1}); }
+int gl_batched_state_round_message(void* state, uint64_t* h_msg) { return static_cast<BatchedEqAbState*>(state)->round_message(h_msg); }
+int gl_batched_state_fold(void* state, uint64_t c0, uint64_t c1) { return static_cast<BatchedEqAbState*>(state)->fold(Ext2{c0, c1}); }
+int gl_batched_state_finals(void* state, uint64_t* h_out) { return static_cast<BatchedEqAbState*>(state)->finals(h_out); }
+
+// ---- host transcript ----
+int gl_transcript_create(const uint8_t* label, size_t label_len, void** transcript) {
+    if (!transcript) return MB_ERR_ARG;
+    *transcript = new Transcript(label, label_len);
+    return MB_OK;
+}
+int gl_transcript_destroy(void* t) { delete static_cast<Transcript*>(t); return MB_OK; }
+int gl_transcript_append_u64(void* t, const char* label, uint64_t v) { static_cast<Transcript*>(t)->append_u64(label, v); return MB_OK; }
+int gl_transcript_append_ext2(void* t, const char* label, uint64_t c0, uint64_t c1) {
+    static_cast<Transcript*>(t)->append_ext2(label, Ext2{c0, c1});
+    return MB_OK;
+}
+int gl_transcript_challenge_ext2(void* t, const char* label, uint64_t* out2) {
+    Ext2 r = static_cast<Transcript*>(t)->challenge_ext2(label);
+    out2[0] = r.c0;
+    out2[1] = r.c1;
+    return MB_OK;
+}
+int gl_transcript_state(const void* t, uint64_t* out8) { std::memcpy(out8, static_cast<const Transcript*>(t)->state(), 64); return MB_OK; }
+
+}  // extern "C"

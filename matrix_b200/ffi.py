@@ -125,6 +125,19 @@ _GL_SIGNATURES = {
     "basefold_prove_host": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int,
                                     c_void_p, c_void_p]),
     "sumcheck_round_message_ext2_noalloc_ffi": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t]),
+    "gl_batched_state_create": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(c_void_p)]),
+    "gl_batched_state_destroy": (c_int, [c_void_p]),
+    "gl_batched_state_claims": (c_int, [c_void_p, c_void_p]),
+    "gl_batched_state_set_alpha": (c_int, [c_void_p, c_u64, c_u64]),
+    "gl_batched_state_round_message": (c_int, [c_void_p, c_void_p]),
+    "gl_batched_state_fold": (c_int, [c_void_p, c_u64, c_u64]),
+    "gl_batched_state_finals": (c_int, [c_void_p, c_void_p]),
+    "gl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
+    "gl_transcript_destroy": (c_int, [c_void_p]),
+    "gl_transcript_append_u64": (c_int, [c_void_p, ctypes.c_char_p, c_u64]),
+    "gl_transcript_append_ext2": (c_int, [c_void_p, ctypes.c_char_p, c_u64, c_u64]),
+    "gl_transcript_challenge_ext2": (c_int, [c_void_p, ctypes.c_char_p, c_void_p]),
+    "gl_transcript_state": (c_int, [c_void_p, c_void_p]),
     "gl_sumcheck_prove_device_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,

@@ -1,0 +1,233 @@
+"""Batched degree-3 sumcheck (shared eq table, K instances combined with powers
+of alpha) sharded over the top hypercube variables, one shard per rank.
+
+    S = sum_k alpha^k sum_x eq(t, x) a_k(x) b_k(x),   x in {0,1}^nv
+
+Rank g of G = 2^g_bits holds the slices of a_k, b_k whose top g_bits index bits
+equal g. The sumcheck binds the low variable first, so the first nv - g_bits
+rounds are local: every rank computes its share of the round polynomial on its
+GPU, the shares (4 extension elements = 64 bytes per rank) are exchanged with
+one all-gather and added mod p, every rank runs the same transcript and folds
+on the same challenge. After the local rounds each rank is left with one value
+per table; these are all-gathered and the last g_bits rounds are finished on the
+host, identically on every rank. There is no other data-path communication.
+
+The reference runs this kernel family on one GPU per task and adds partial sums
+on the host (almost-goldilocks-cuda-rs/src/sumcheck_prover.rs:351-385); sharding
+one sumcheck over several GPUs has no reference counterpart.
+"""
+import ctypes
+
+import numpy as np
+
+GL_P = 0xFFFFFFFF00000001
+W = 7  # X^2 = 7
+
+
+# ---- extension-field helpers on Python integers (a few dozen values per round) ----
+def e2_add(a, b):
+    return ((a[0] + b[0]) % GL_P, (a[1] + b[1]) % GL_P)
+
+
+def e2_sub(a, b):
+    return ((a[0] - b[0]) % GL_P, (a[1] - b[1]) % GL_P)
+
+
+def e2_mul(a, b):
+    return ((a[0] * b[0] + W * a[1] * b[1]) % GL_P, (a[0] * b[1] + a[1] * b[0]) % GL_P)
+
+
+def e2_inv(a):
+    n = (a[0] * a[0] - W * a[1] * a[1]) % GL_P
+    ni = pow(n, GL_P - 2, GL_P)
+    return (a[0] * ni % GL_P, (-a[1]) * ni % GL_P)
+
+
+def eq_scale(point_top, shard):
+    """eq(t_top, bits of shard): bit i of the shard index pairs with point_top[i]."""
+    s = (1, 0)
+    for i, t in enumerate(point_top):
+        s = e2_mul(s, t if (shard >> i) & 1 else e2_sub((1, 0), t))
+    return s
+
+
+class SingleComm:
+    """All `world` shards live in this process (one GPU simulating several ranks, or world = 1)."""
+
+    def __init__(self, world=1):
+        self.world = world
+        self.local_ranks = list(range(world))
+
+    def allgather(self, arrs):
+        return [np.array(a, dtype=np.uint64) for a in arrs]
+
+
+class TorchComm:
+    """All-gather of small uint64 arrays over torch.distributed (NCCL between GPUs, gloo on CPU)."""
+
+    def __init__(self, device=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.local_ranks = [self.rank]
+        self.device = device
+
+    def allgather(self, arrs):
+        import torch
+        t = torch.from_numpy(np.ascontiguousarray(arrs[0], dtype=np.uint64).view(np.int64).copy())
+        if self.device is not None:
+            t = t.to(self.device)
+        outs = [torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(outs, t)
+        return [o.cpu().numpy().view(np.uint64) for o in outs]
+
+
+class LibTranscript:
+    """The library's host transcript (zk-torch-3/src/transcript.rs semantics) through the C-ABI."""
+
+    def __init__(self, lib, label):
+        self.lib = lib
+        self.h = ctypes.c_void_p()
+        assert lib.gl_transcript_create(label, len(label), ctypes.byref(self.h)) == 0
+
+    def append_u64(self, label, v):
+        self.lib.gl_transcript_append_u64(self.h, label, int(v))
+
+    def append_ext2(self, label, v):
+        self.lib.gl_transcript_append_ext2(self.h, label, int(v[0]), int(v[1]))
+
+    def challenge_ext2(self, label):
+        out = (ctypes.c_uint64 * 2)()
+        self.lib.gl_transcript_challenge_ext2(self.h, label, out)
+        return (int(out[0]), int(out[1]))
+
+    def state(self):
+        out = np.zeros(8, dtype=np.uint64)
+        self.lib.gl_transcript_state(self.h, out.ctypes.data)
+        return out
+
+    def __del__(self):
+        try:
+            self.lib.gl_transcript_destroy(self.h)
+        except Exception:
+            pass
+
+
+class GpuShard:
+    """One shard on the current CUDA device through the C-ABI (gl_batched_state_*)."""
+
+    def __init__(self, lib, d_a_ptr, d_b_ptr, point_low, scale, K, n_loc):
+        self.lib, self.K = lib, K
+        self.h = ctypes.c_void_p()
+        pl = np.array([c for t in point_low for c in t], dtype=np.uint64)
+        sc = np.array(scale, dtype=np.uint64)
+        rc = lib.gl_batched_state_create(d_a_ptr, d_b_ptr, pl.ctypes.data, sc.ctypes.data, K, n_loc, ctypes.byref(self.h))
+        if rc != 0:
+            raise RuntimeError("gl_batched_state_create: %d" % rc)
+
+    def claims(self):
+        out = np.zeros(2 * self.K, dtype=np.uint64)
+        assert self.lib.gl_batched_state_claims(self.h, out.ctypes.data) == 0
+        return out
+
+    def set_alpha(self, alpha):
+        assert self.lib.gl_batched_state_set_alpha(self.h, alpha[0], alpha[1]) == 0
+
+    def round_message(self):
+        out = np.zeros(8, dtype=np.uint64)
+        assert self.lib.gl_batched_state_round_message(self.h, out.ctypes.data) == 0
+        return out
+
+    def fold(self, r):
+        assert self.lib.gl_batched_state_fold(self.h, r[0], r[1]) == 0
+
+    def finals(self):
+        out = np.zeros(2 * (2 * self.K + 1), dtype=np.uint64)
+        assert self.lib.gl_batched_state_finals(self.h, out.ctypes.data) == 0
+        return out
+
+    def close(self):
+        if self.h:
+            self.lib.gl_batched_state_destroy(self.h)
+            self.h = None
+
+
+def _sum_shares(shares, width):
+    """Adds the ranks' arrays of `width` extension elements mod p."""
+    tot = [(0, 0)] * width
+    for s in shares:
+        tot = [e2_add(t, (int(s[2 * i]), int(s[2 * i + 1]))) for i, t in enumerate(tot)]
+    return tot
+
+
+def prove_sharded(make_shard, transcript, comm, point, K, nv, g_bits):
+    """Runs the protocol. `make_shard(rank, point_low, scale)` builds the shard object of a
+    rank this process owns (GpuShard or a test double with the same methods); `transcript`
+    follows LibTranscript; `point` is a list of nv (c0, c1) pairs. Returns the same
+    dictionary on every process."""
+    assert comm.world == 1 << g_bits and nv - g_bits >= 1
+    n_loc = nv - g_bits
+    shards = [make_shard(g, point[:n_loc], eq_scale(point[n_loc:], g)) for g in comm.local_ranks]
+    transcript.append_u64(b"sp_num_var", nv)
+    transcript.append_u64(b"sp_num_inst", K)
+    claims = _sum_shares(comm.allgather([s.claims() for s in shards]), K)
+    for c in claims:
+        transcript.append_ext2(b"sp_y_i", c)
+    alpha = transcript.challenge_ext2(b"sp_alpha")
+    for s in shards:
+        s.set_alpha(alpha)
+    round_msgs, challenges = [], []
+    for _ in range(n_loc):
+        msg = _sum_shares(comm.allgather([s.round_message() for s in shards]), 4)
+        for m in msg:
+            transcript.append_ext2(b"sp_round_msg", m)
+        r = transcript.challenge_ext2(b"sp_round_challenge")
+        round_msgs.append(msg)
+        challenges.append(r)
+        for s in shards:
+            s.fold(r)
+    # one value per table and rank: eq, alpha^k a_k, b_k; finish the top variables on the host
+    gathered = comm.allgather([s.finals() for s in shards])
+    T = 2 * K + 1
+    tables = [[(int(g[2 * i]), int(g[2 * i + 1])) for g in gathered] for i in range(T)]
+    size = comm.world
+    while size > 1:
+        half = size // 2
+        msg = []
+        for c in range(4):
+            tot = (0, 0)
+            cc = (c, 0)
+            for y in range(half):
+                def at(tab):
+                    lo, hi = tab[2 * y], tab[2 * y + 1]
+                    return e2_add(lo, e2_mul(cc, e2_sub(hi, lo)))
+                inner = (0, 0)
+                for k in range(K):
+                    inner = e2_add(inner, e2_mul(at(tables[1 + k]), at(tables[1 + K + k])))
+                tot = e2_add(tot, e2_mul(at(tables[0]), inner))
+            msg.append(tot)
+        for m in msg:
+            transcript.append_ext2(b"sp_round_msg", m)
+        r = transcript.challenge_ext2(b"sp_round_challenge")
+        round_msgs.append(msg)
+        challenges.append(r)
+        tables = [[e2_add(t[2 * y], e2_mul(r, e2_sub(t[2 * y + 1], t[2 * y]))) for y in range(half)] for t in tables]
+        size = half
+    # report a_k(R) without the alpha^k factor the shards carry
+    finals = [tables[0][0]]
+    pw, acc = (1, 0), (0, 0)
+    for k in range(K):
+        finals.append(e2_mul(tables[1 + k][0], e2_inv(pw)))
+        acc = e2_add(acc, e2_mul(tables[1 + k][0], tables[1 + K + k][0]))
+        pw = e2_mul(pw, alpha)
+    finals += [tables[1 + K + k][0] for k in range(K)]
+    for f in finals:
+        transcript.append_ext2(b"sp_f_eval", f)
+    final_eval = e2_mul(tables[0][0], acc)
+    for s in shards:
+        if hasattr(s, "close"):
+            s.close()
+    return dict(claims=np.array(claims, dtype=np.uint64), alpha=np.array(alpha, dtype=np.uint64),
+                round_msgs=np.array(round_msgs, dtype=np.uint64), challenges=np.array(challenges, dtype=np.uint64),
+                finals=np.array(finals, dtype=np.uint64), final_eval=np.array(final_eval, dtype=np.uint64),
+                state=transcript.state())

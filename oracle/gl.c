@@ -199,3 +199,6 @@ void gl_compress(const uint64_t l[4], const uint64_t r[4], uint64_t out[4]) {
     gl_poseidon2_permute(s);
     memcpy(out, s, 32);
 }
+
+/* flat wrappers for tests */
+void oracle_gl_e2_inv(const uint64_t *a, uint64_t *out) { ext2_t r = e2_inv(e2(a[0], a[1])); out[0] = r.c0; out[1] = r.c1; }

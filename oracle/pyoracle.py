@@ -190,3 +190,31 @@ def load_ref(name):
         lib.ref_agl_mul.argtypes = [u64, u64]
         lib.ref_agl_mul.restype = u64
     return lib
+
+
+# ---- batched eq * a * b sumcheck ---------------------------------------------------
+_SIGS.update({
+    "oracle_gl_batched_message": (None, [vp, vp, vp, ci, sz, sz, vp]),
+    "oracle_gl_batched_fold": (None, [vp, vp, u64, u64, ci, sz, sz]),
+    "oracle_gl_batched_claims": (None, [vp, vp, ci, sz, sz, vp]),
+    "oracle_gl_batched_prove": (ci, [vp, vp, vp, ci, ci, ctypes.c_char_p, sz, vp, vp, vp, vp, vp, vp, vp]),
+    "oracle_gl_e2_inv": (None, [vp, vp]),
+})
+
+
+def batched_prove(a, b, point, K, nv, label=b"bench"):
+    """Whole batched eq*a*b sumcheck on the CPU; a, b: [K * 2^nv] base field."""
+    import numpy as np
+    lib = load()
+    a, b, point = (np.ascontiguousarray(x, dtype=np.uint64) for x in (a, b, point))
+    out = dict(claims=np.zeros((K, 2), dtype=np.uint64), alpha=np.zeros(2, dtype=np.uint64),
+               round_msgs=np.zeros((nv, 4, 2), dtype=np.uint64), challenges=np.zeros((nv, 2), dtype=np.uint64),
+               finals=np.zeros((2 * K + 1, 2), dtype=np.uint64), final_eval=np.zeros(2, dtype=np.uint64),
+               state=np.zeros(8, dtype=np.uint64))
+    rc = lib.oracle_gl_batched_prove(a.ctypes.data, b.ctypes.data, point.ctypes.data, K, nv, label, len(label),
+                                     out["claims"].ctypes.data, out["alpha"].ctypes.data, out["round_msgs"].ctypes.data,
+                                     out["challenges"].ctypes.data, out["finals"].ctypes.data,
+                                     out["final_eval"].ctypes.data, out["state"].ctypes.data)
+    if rc != 0:
+        raise RuntimeError("oracle_gl_batched_prove: %d" % rc)
+    return out
