@@ -158,6 +158,139 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_batched(args):
+    """Config 4: K instances of eq*a*b over 2^nv points, combined with powers of alpha, sharded over
+    the top log2(N) variables; one all-gather of 64 bytes per rank and round."""
+    rank, world, local = dist_env()
+    from matrix_b200 import load_gl
+    from matrix_b200.ffi import DeviceBuffer
+    from matrix_b200.inputs import GL_P, field_elems
+    from matrix_b200.sharded import GpuShard, LibTranscript, SingleComm, TorchComm, prove_sharded
+    lib = load_gl()
+    assert lib.cuda_set_device(local) == 0
+    nv = args.num_vars if args.num_vars != 24 else 26
+    K = args.instances
+    g_bits = world.bit_length() - 1
+    assert world == 1 << g_bits, "the number of ranks must be a power of two"
+    comm = SingleComm(1)
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        comm = TorchComm(device=torch.device("cuda", local))
+    n_loc = nv - g_bits
+    m = 1 << n_loc
+    # this rank's slices, made on the device: instance k, table a / b, entries [rank * m, (rank + 1) * m)
+    d_a, d_b = DeviceBuffer(lib, 8 * K * m), DeviceBuffer(lib, 8 * K * m)
+    for k in range(K):
+        # seeds 100 + k / 200 + k; the slice of a longer stream starts at element rank * m
+        off = (rank * m * 0x9E3779B97F4A7C15) & (2**64 - 1)
+        assert lib.mb_fill_splitmix(d_a.ptr + 8 * k * m, m, (100 + k + off) & (2**64 - 1), GL_P) == 0
+        assert lib.mb_fill_splitmix(d_b.ptr + 8 * k * m, m, (200 + k + off) & (2**64 - 1), GL_P) == 0
+    pt = field_elems(6, 2 * nv)
+    point = [(int(pt[2 * i]), int(pt[2 * i + 1])) for i in range(nv)]
+
+    def step():
+        return prove_sharded(lambda g, pl, sc: GpuShard(lib, d_a.ptr, d_b.ptr, pl, sc, K, n_loc),
+                             LibTranscript(lib, LABEL), comm, point, K, nv, g_bits)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        lib.cuda_device_synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    a, b = ctypes.c_void_p(), ctypes.c_void_p()
+    lib.mb_event_create(ctypes.byref(a)); lib.mb_event_create(ctypes.byref(b))
+    sampler = ClockSampler(local)
+    lib.mb_prof_reset(); lib.mb_prof_enable(1)
+    launches0 = lib.mb_launch_count()
+    sampler.start()
+    barrier()
+    lib.mb_event_record(a)
+    for _ in range(args.steps):
+        proof = step()
+    lib.mb_event_record(b); lib.mb_event_sync(b)
+    barrier()
+    clocks = sampler.stop()
+    ms = ctypes.c_float(); lib.mb_event_elapsed_ms(a, b, ctypes.byref(ms))
+    val = ms.value
+    if dist is not None:
+        import torch
+        t = torch.tensor([val], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        val = float(t.item())
+    launches = lib.mb_launch_count() - launches0
+    lib.mb_prof_enable(0)
+    need = lib.mb_prof_report(None, 0)
+    buf = ctypes.create_string_buffer(need + 16)
+    lib.mb_prof_report(buf, need + 16)
+    kernels = {l.split()[0]: (int(l.split()[1]), float(l.split()[2])) for l in buf.value.decode().splitlines()}
+    elems = 2 * K * (1 << nv)  # field elements of the 2K witness tables (eq is derived, not counted)
+    peak, peak_kind = measured_peaks()
+    # algorithmic bytes of the dominant pass (fold of round 0 fused with message 1): read 8 B, write 8 B per element
+    roofline = None
+    if "batched_fold_message" in kernels:
+        cnt, kms = kernels["batched_fold_message"]
+        # per step and rank: round 0 fold reads 2K*m*8 + eq m*16, writes (2K+1)*m/2*16; later rounds halve: read S, write S/2
+        first = 2 * K * m * 8 + m * 16 + (2 * K + 1) * (m // 2) * 16
+        later = sum((2 * K + 1) * (m >> r) * 16 * 1.5 for r in range(1, n_loc - 1))
+        total_bytes = (first + later) * args.steps
+        ach = total_bytes / (kms * 1e-3) / 1e9
+        roofline = {"kernel": "batched_fold_message", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+                    "frac": ach / peak, "traffic": None, "peak_kind": peak_kind, "launches": cnt,
+                    "avg_launch_ms": kms / cnt, "note": "per rank; all rounds' fold+message launches together"}
+    line = {"metric": "field-elems/s: batched degree-3 sumcheck eq*a*b, %d instances, 2^%d points" % (K, nv),
+            "value": elems * args.steps / (val * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": val / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": {"workload": "batched_sumcheck nv=%d instances=%d" % (nv, K), "sharding": "top %d variables" % g_bits,
+                       "collective": "one all-gather of 64 B per rank and round (NCCL)", "l2": "tables larger than L2"},
+            "roofline": roofline,
+            "kernel_times_ms": {k: {"launches": c, "ms": round(x, 4)} for k, (c, x) in sorted(kernels.items())},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "final_eval": [int(x) for x in proof["final_eval"]]}
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_reference_batched(args):
+    """CPU arm of the batched sumcheck: the oracle prover on a bounded sample (2^ref_num_vars points)."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from matrix_b200.inputs import field_elems
+    from oracle import pyoracle
+    nv, K = args.ref_num_vars, args.instances
+    n = 1 << nv
+    a = np.concatenate([field_elems(100 + k, n) for k in range(K)])
+    b = np.concatenate([field_elems(200 + k, n) for k in range(K)])
+    pt = field_elems(6, 2 * nv)
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        pyoracle.batched_prove(a, b, pt, K, nv, LABEL)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = 2 * K * n * args.steps / total
+    cores = os.cpu_count() or 1
+    print(json.dumps({"impl": "reference", "metric": "field-elems/s: batched degree-3 sumcheck eq*a*b, %d instances" % K,
+                      "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "strong",
+                      "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                      "config": {"workload": "batched_sumcheck instances=%d (sampled at nv=%d)" % (K, nv)},
+                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                                       "sample": "CPU oracle batched prover at 2^%d points per step" % nv},
+                      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,7 +300,17 @@ def main():
     ap.add_argument("--num-vars", type=int, default=24)
     ap.add_argument("--ref-num-vars", type=int, default=20, help="sample size of the CPU arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck"],
+                    help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
+                         "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
+    ap.add_argument("--instances", type=int, default=16)
     args = ap.parse_args()
+    if args.workload == "batched_sumcheck":
+        if args.impl == "reference":
+            run_reference_batched(args)
+        else:
+            run_batched(args)
+        return
 
     if args.impl == "reference":
         run_reference(args)

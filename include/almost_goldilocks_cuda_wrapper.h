@@ -99,6 +99,8 @@ int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t 
                         uint64_t* d_out);
 
 /* ---- additions shared with the Goldilocks library ---- */
+/* d_out[i] = splitmix64(seed) output i + 1 mod modulus: seeded synthetic inputs made on the device */
+int mb_fill_splitmix(uint64_t* d_out, size_t n, uint64_t seed, uint64_t modulus);
 int mb_event_create(void** ev);
 int mb_event_record(void* ev);
 int mb_event_sync(void* ev);

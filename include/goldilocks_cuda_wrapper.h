@@ -244,6 +244,8 @@ int mb_host_free(void* ptr);
 int mb_memcpy_htod_async(void* dst, const void* src, size_t size);
 int mb_memcpy_dtoh_async(void* dst, const void* src, size_t size);
 int mb_stream_sync(void);
+/* d_out[i] = splitmix64(seed) output i + 1 mod modulus: seeded synthetic inputs made on the device */
+int mb_fill_splitmix(uint64_t* d_out, size_t n, uint64_t seed, uint64_t modulus);
 int mb_event_create(void** ev);
 int mb_event_record(void* ev);
 int mb_event_sync(void* ev);

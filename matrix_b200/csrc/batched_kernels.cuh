@@ -44,11 +44,11 @@ __device__ __forceinline__ void finish_message(typename FE::T (&m)[NC], uint64_t
     if (threadIdx.x == 0) *counter = 0;
 }
 
-// Round 0 message from base-field tables. ab: [K][2][stride] base elements
-// (a_k then b_k); eq: extension; alpha_pows: K extension elements in global memory.
+// Round 0 message from the caller's base-field tables a0, b0: [K][stride] each;
+// eq: extension; alpha_pows: K extension elements in global memory.
 template <class FB, class FE>
 __global__ void __launch_bounds__(256)
-round0_message_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ ab,
+round0_message_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ a0p, const uint64_t* __restrict__ b0p,
                       const uint64_t* __restrict__ alpha_pows, int K, size_t stride, size_t half, uint64_t* partial,
                       unsigned int* counter, uint64_t* final_out) {
     using TE = typename FE::T;
@@ -62,8 +62,8 @@ round0_message_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restric
         for (int c = 0; c < NC; c++) inner[c] = FE::zero();
         for (int k = 0; k < K; k++) {
             uint64_t a0, a1, b0, b1;
-            FB::load2(ab + (size_t)(2 * k) * stride, 2 * y, a0, a1);
-            FB::load2(ab + (size_t)(2 * k + 1) * stride, 2 * y, b0, b1);
+            FB::load2(a0p + (size_t)k * stride, 2 * y, a0, a1);
+            FB::load2(b0p + (size_t)k * stride, 2 * y, b0, b1);
             const TE w = FE::load(alpha_pows, k);
             uint64_t da = FB::sub(a1, a0), db = FB::sub(b1, b0), va = a0, vb = b0;
 #pragma unroll
@@ -90,14 +90,15 @@ round0_message_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restric
 // partial[(block * K + k) * 2 ...]; summed by reduce_partials_kernel.
 template <class FB, class FE>
 __global__ void __launch_bounds__(256)
-claims_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ ab, int K, size_t stride, size_t n,
+claims_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ a0p, const uint64_t* __restrict__ b0p, int K,
+              size_t stride, size_t n,
               uint64_t* __restrict__ partial) {
     using TE = typename FE::T;
     const size_t step = (size_t)gridDim.x * blockDim.x;
     for (int k = 0; k < K; k++) {
         TE acc = FE::zero();
         for (size_t x = (size_t)blockIdx.x * blockDim.x + threadIdx.x; x < n; x += step) {
-            uint64_t pr = FB::mul(ab[(size_t)(2 * k) * stride + x], ab[(size_t)(2 * k + 1) * stride + x]);
+            uint64_t pr = FB::mul(a0p[(size_t)k * stride + x], b0p[(size_t)k * stride + x]);
             TE e = FE::load(eq, x);
             acc = FE::add(acc, TE{FB::mul(e.c0, pr), FB::mul(e.c1, pr)});
         }
@@ -109,11 +110,13 @@ claims_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ ab, 
 
 // Fold every table on r and accumulate the next message. FIRST: inputs a, b are
 // base field and the folded a_k is multiplied by alpha^k; otherwise all tables
-// are extension tables (a_k already scaled). quarter = live length / 4.
+// are extension tables (a_k already scaled). quarter = live length / 4. With
+// FIRST, ab_in / b_first are the caller's [K][stride] base tables a and b;
+// otherwise ab_in is [K][2][stride] extension tables and b_first is unused.
 template <class FB, class FE, bool FIRST>
 __global__ void __launch_bounds__(256)
 fold_message_kernel(const uint64_t* __restrict__ eq_in, uint64_t* __restrict__ eq_out, const uint64_t* __restrict__ ab_in,
-                    uint64_t* __restrict__ ab_out, const uint64_t* __restrict__ alpha_pows, typename FE::T r, int K,
+                    const uint64_t* __restrict__ b_first, uint64_t* __restrict__ ab_out, const uint64_t* __restrict__ alpha_pows, typename FE::T r, int K,
                     size_t stride_in, size_t stride_out, size_t quarter, uint64_t* partial, unsigned int* counter,
                     uint64_t* final_out) {
     using TE = typename FE::T;
@@ -129,13 +132,13 @@ fold_message_kernel(const uint64_t* __restrict__ eq_in, uint64_t* __restrict__ e
             TE fa0, fa1, fb0, fb1;
             if (FIRST) {
                 uint64_t x0, x1, x2, x3;
-                const uint64_t* pa = ab_in + (size_t)(2 * k) * stride_in;
+                const uint64_t* pa = ab_in + (size_t)k * stride_in;
                 FB::load2(pa, 4 * y, x0, x1);
                 FB::load2(pa, 4 * y + 2, x2, x3);
                 const TE w = FE::load(alpha_pows, k);
                 fa0 = FE::mul(w, sc::FoldOp<FB, FE>::apply(x0, x1, r));
                 fa1 = FE::mul(w, sc::FoldOp<FB, FE>::apply(x2, x3, r));
-                const uint64_t* pb = ab_in + (size_t)(2 * k + 1) * stride_in;
+                const uint64_t* pb = b_first + (size_t)k * stride_in;
                 FB::load2(pb, 4 * y, x0, x1);
                 FB::load2(pb, 4 * y + 2, x2, x3);
                 fb0 = sc::FoldOp<FB, FE>::apply(x0, x1, r);
@@ -181,7 +184,8 @@ fold_message_kernel(const uint64_t* __restrict__ eq_in, uint64_t* __restrict__ e
 // Last fold (two live elements per table): no message.
 template <class FB, class FE, bool FIRST>
 __global__ void final_fold_kernel(const uint64_t* __restrict__ eq_in, uint64_t* __restrict__ eq_out,
-                                  const uint64_t* __restrict__ ab_in, uint64_t* __restrict__ ab_out,
+                                  const uint64_t* __restrict__ ab_in, const uint64_t* __restrict__ b_first,
+                                  uint64_t* __restrict__ ab_out,
                                   const uint64_t* __restrict__ alpha_pows, typename FE::T r, int K, size_t stride_in,
                                   size_t stride_out) {
     using TE = typename FE::T;
@@ -196,7 +200,7 @@ __global__ void final_fold_kernel(const uint64_t* __restrict__ eq_in, uint64_t* 
     TE f;
     if (FIRST) {
         uint64_t x0, x1;
-        FB::load2(ab_in + (size_t)t * stride_in, 0, x0, x1);
+        FB::load2(((t & 1) ? b_first : ab_in) + (size_t)(t >> 1) * stride_in, 0, x0, x1);
         f = sc::FoldOp<FB, FE>::apply(x0, x1, r);
         if ((t & 1) == 0) f = FE::mul(FE::load(alpha_pows, t >> 1), f);
     } else {

@@ -8,7 +8,30 @@
 #include "common.cuh"
 #include <cstring>
 
+namespace {
+// out[i] = splitmix64 output number i + 1 started at `seed`, reduced mod `modulus`
+// (the generator of matrix_b200/inputs.py, so device-made inputs equal host-made ones).
+__global__ void fill_splitmix_kernel(uint64_t* __restrict__ out, size_t n, uint64_t seed, uint64_t modulus) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+        uint64_t z = seed + (uint64_t)(i + 1) * 0x9E3779B97F4A7C15ULL;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+        z = z ^ (z >> 31);
+        out[i] = z % modulus;
+    }
+}
+}  // namespace
+
 extern "C" {
+
+// Synthetic inputs made on the device (benchmarks of sizes the host should not stage).
+int mb_fill_splitmix(uint64_t* d_out, size_t n, uint64_t seed, uint64_t modulus) {
+    if (!d_out || modulus == 0) return MB_ERR_ARG;
+    if (n == 0) return MB_OK;
+    fill_splitmix_kernel<<<mb::grid_for(n, 256, 8), 256, 0, MB_STREAM>>>(d_out, n, seed, modulus);
+    return mb::finish_sync();
+}
 
 // The reference uploads field and hash constants here, once per device. This
 // library's tables are statically initialised __constant__ data, present on

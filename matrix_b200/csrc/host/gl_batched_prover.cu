@@ -30,12 +30,8 @@ public:
         if (!d_a || !d_b || !h_eq_scale || K < 1 || K > bt::MAX_K || n_loc < 1 || n_loc > 34) return MB_ERR_ARG;
         if (n_loc > 0 && !h_point_low) return MB_ERR_ARG;
         K_ = K; n_loc_ = n_loc; n_ = (size_t)1 << n_loc; round_ = 0; have_msg_ = false; have_alpha_ = false;
-        // tables: [K][2][n] base (copied so that the caller's buffers stay untouched and contiguous)
-        MB_CUDA(pool_alloc((void**)&ab_base_, sizeof(uint64_t) * 2 * K * n_));
-        for (int k = 0; k < K; k++) {
-            MB_CUDA(cudaMemcpyAsync(ab_base_ + (size_t)(2 * k) * n_, d_a + (size_t)k * n_, 8 * n_, cudaMemcpyDeviceToDevice, MB_STREAM));
-            MB_CUDA(cudaMemcpyAsync(ab_base_ + (size_t)(2 * k + 1) * n_, d_b + (size_t)k * n_, 8 * n_, cudaMemcpyDeviceToDevice, MB_STREAM));
-        }
+        a0_ = d_a;  // the caller's tables are read in place during round 0 and never written
+        b0_ = d_b;
         size_t half = n_ / 2, quarter = n_ >= 4 ? n_ / 4 : 1;
         MB_CUDA(pool_alloc((void**)&eq0_, 16 * n_));
         MB_CUDA(pool_alloc((void**)&eq_a_, 16 * half));
@@ -66,7 +62,7 @@ public:
         if (grid > grid_max_) grid = grid_max_;
         {
             MB_KERNEL("batched_claims");
-            bt::claims_kernel<GlBase, GlExt2><<<grid, 256, 0, MB_STREAM>>>(eq0_, ab_base_, K_, n_, n_, partial_);
+            bt::claims_kernel<GlBase, GlExt2><<<grid, 256, 0, MB_STREAM>>>(eq0_, a0_, b0_, K_, n_, n_, partial_);
         }
         uint64_t* d_out = nullptr;
         MB_CUDA(pool_alloc((void**)&d_out, 16 * (size_t)K_));
@@ -101,7 +97,7 @@ public:
             size_t half = n_ / 2;
             MB_KERNEL("batched_round0");
             bt::round0_message_kernel<GlBase, GlExt2><<<grid_for(half, 256, 4), 256, 0, MB_STREAM>>>(
-                eq0_, ab_base_, alpha_dev_, K_, n_, half, partial_, counter_, msg_dev_);
+                eq0_, a0_, b0_, alpha_dev_, K_, n_, half, partial_, counter_, msg_dev_);
         }
         MB_CUDA(cudaMemcpyAsync(h_, msg_dev_, 64, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
@@ -115,7 +111,7 @@ public:
         size_t live = n_ >> round_, quarter = live / 4;
         bool first = round_ == 0;
         const uint64_t* eq_in = first ? eq0_ : eq_cur_;
-        const uint64_t* ab_in = first ? ab_base_ : ab_cur_;
+        const uint64_t* ab_in = first ? a0_ : ab_cur_;
         size_t stride_in = first ? n_ : ab_stride_;
         bool to_a = first || ab_cur_ == ab_b_;
         uint64_t* eq_out = to_a ? eq_a_ : eq_b_;
@@ -126,20 +122,20 @@ public:
             MB_KERNEL("batched_fold_message");
             if (first)
                 bt::fold_message_kernel<GlBase, GlExt2, true><<<grid, 256, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+                    eq_in, eq_out, ab_in, b0_, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
             else
                 bt::fold_message_kernel<GlBase, GlExt2, false><<<grid, 256, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+                    eq_in, eq_out, ab_in, b0_, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
             have_msg_ = true;
         } else {
             MB_KERNEL("batched_final_fold");
             int threads = 2 * K_ + 1;
             if (first)
                 bt::final_fold_kernel<GlBase, GlExt2, true><<<(threads + 127) / 128, 128, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out);
+                    eq_in, eq_out, ab_in, b0_, ab_out, alpha_dev_, r, K_, stride_in, stride_out);
             else
                 bt::final_fold_kernel<GlBase, GlExt2, false><<<(threads + 127) / 128, 128, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, ab_out, alpha_dev_, r, K_, stride_in, stride_out);
+                    eq_in, eq_out, ab_in, b0_, ab_out, alpha_dev_, r, K_, stride_in, stride_out);
             have_msg_ = false;
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
@@ -165,14 +161,15 @@ public:
 
 private:
     void release() {
-        pool_free(ab_base_); pool_free(eq0_); pool_free(eq_a_); pool_free(eq_b_); pool_free(ab_a_); pool_free(ab_b_);
+        pool_free(eq0_); pool_free(eq_a_); pool_free(eq_b_); pool_free(ab_a_); pool_free(ab_b_);
         pool_free(partial_); pool_free(small_);
-        ab_base_ = eq0_ = eq_a_ = eq_b_ = ab_a_ = ab_b_ = partial_ = small_ = nullptr;
+        eq0_ = eq_a_ = eq_b_ = ab_a_ = ab_b_ = partial_ = small_ = nullptr;
     }
     int K_ = 0, n_loc_ = 0, round_ = 0, grid_max_ = 0;
     size_t n_ = 0, ab_stride_ = 0;
     bool have_msg_ = false, have_alpha_ = false;
-    uint64_t *ab_base_ = nullptr, *eq0_ = nullptr, *eq_a_ = nullptr, *eq_b_ = nullptr, *ab_a_ = nullptr, *ab_b_ = nullptr;
+    const uint64_t *a0_ = nullptr, *b0_ = nullptr;
+    uint64_t *eq0_ = nullptr, *eq_a_ = nullptr, *eq_b_ = nullptr, *ab_a_ = nullptr, *ab_b_ = nullptr;
     uint64_t *partial_ = nullptr, *small_ = nullptr, *msg_dev_ = nullptr, *alpha_dev_ = nullptr, *eq_cur_ = nullptr, *ab_cur_ = nullptr;
     unsigned int* counter_ = nullptr;
     uint64_t* h_ = nullptr;
@@ -187,7 +184,7 @@ using mbhost::Transcript;
 extern "C" {
 
 // ---- one shard of the batched eq * a_k * b_k sumcheck ----
-// d_a, d_b: [K][2^n_loc] base-field slices; h_point_low: n_loc (c0, c1) pairs (the
+// d_a, d_b: [K][2^n_loc] base-field slices (read in place until the first fold, never written); h_point_low: n_loc (c0, c1) pairs (the
 // shard-local coordinates of the eq point); h_eq_scale: eq of the top coordinates
 // at this shard's index ((1, 0) for a single shard).
 int gl_batched_state_create(const uint64_t* d_a, const uint64_t* d_b, const uint64_t* h_point_low,

@@ -51,6 +51,7 @@ _GL_SIGNATURES = {
     "mb_memcpy_htod_async": (c_int, [c_void_p, c_void_p, c_size_t]),
     "mb_memcpy_dtoh_async": (c_int, [c_void_p, c_void_p, c_size_t]),
     "mb_stream_sync": (c_int, []),
+    "mb_fill_splitmix": (c_int, [c_void_p, c_size_t, c_u64, c_u64]),
     "mb_event_create": (c_int, [ctypes.POINTER(c_void_p)]),
     "mb_event_record": (c_int, [c_void_p]),
     "mb_event_sync": (c_int, [c_void_p]),
@@ -162,7 +163,7 @@ _AGL = None
 _MEM = ["cuda_malloc", "cuda_free", "cuda_memcpy_htod", "cuda_memcpy_dtoh", "cuda_memcpy_dtod", "cuda_device_synchronize",
         "cuda_get_last_error", "cuda_peek_at_last_error", "cuda_mem_get_info", "cuda_set_device", "cuda_get_device",
         "cuda_get_device_count", "mb_event_create", "mb_event_record", "mb_event_sync", "mb_event_elapsed_ms",
-        "mb_event_destroy", "mb_stream_sync", "mb_launch_count"]
+        "mb_event_destroy", "mb_stream_sync", "mb_launch_count", "mb_fill_splitmix"]
 _AGL_SIGNATURES = {
     "almost_goldilocks_cuda_init": (c_int, []),
     "agl_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),

@@ -1,0 +1,48 @@
+"""One rank of the multi-GPU test: the sharded batched sumcheck with a GPU shard
+per rank and NCCL for the per-round exchange. Started by test_multigpu.py."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from matrix_b200 import load_gl  # noqa: E402
+from matrix_b200.ffi import DeviceBuffer  # noqa: E402
+from matrix_b200.sharded import GpuShard, LibTranscript, TorchComm, prove_sharded  # noqa: E402
+from oracle import pyoracle  # noqa: E402
+from tests.sharded_helpers import assert_same_proof, inputs, shard_slices  # noqa: E402
+
+
+def main():
+    out_path = sys.argv[1]
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = load_gl()
+    assert lib.cuda_set_device(local) == 0
+    comm = TorchComm(device=torch.device("cuda", local))
+    g_bits = comm.world.bit_length() - 1
+    K, nv = 4, 14
+    a, b, point = inputs(K, nv)
+    keep = []
+
+    def make_shard(g, point_low, scale):
+        sa, sb = shard_slices(a, b, K, nv, g_bits, g)
+        d_a, d_b = DeviceBuffer.from_numpy(lib, sa), DeviceBuffer.from_numpy(lib, sb)
+        keep.extend([d_a, d_b])
+        return GpuShard(lib, d_a.ptr, d_b.ptr, point_low, scale, K, nv - g_bits)
+
+    got = prove_sharded(make_shard, LibTranscript(lib, b"bench"), comm, point, K, nv, g_bits)
+    exp = pyoracle.batched_prove(a, b, np.array([c for t in point for c in t], dtype=np.uint64), K, nv)
+    assert_same_proof(got, exp)
+    with open("%s.%d" % (out_path, comm.rank), "w") as f:
+        f.write("ok")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
