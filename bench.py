@@ -111,12 +111,13 @@ def dist_env():
     return rank, world, local
 
 
-def cpu_oracle_sample(num_vars, threads=None):
+def cpu_oracle_sample(num_vars, threads=None, merkle_hash="poseidon2"):
     """One commit + open of the CPU oracle at 2^num_vars; returns seconds and thread count."""
     from matrix_b200.inputs import field_elems
     from oracle import pyoracle
     if threads:
         os.environ["OMP_NUM_THREADS"] = str(threads)
+    pyoracle.load().oracle_set_merkle_hash(1 if merkle_hash == "monolith" else 0)
     evals = field_elems(3, 1 << num_vars)
     point = field_elems(4, 2 * num_vars)
     table = pyoracle.bf_table(num_vars, LOG_RATE)  # key material, untimed
@@ -135,18 +136,20 @@ def run_reference(args):
     cores = os.cpu_count() or 1
     nv = args.ref_num_vars
     for _ in range(args.warmup):
-        cpu_oracle_sample(min(nv, 16))
+        cpu_oracle_sample(min(nv, 16), merkle_hash=args.hash)
     times = []
     for _ in range(args.steps):
-        dt, _ = cpu_oracle_sample(nv)
+        dt, _ = cpu_oracle_sample(nv, merkle_hash=args.hash)
         times.append(dt)
     total = sum(times)
     value = (1 << nv) * args.steps / total
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference",
+        "metric": METRIC if args.hash == "poseidon2" else METRIC.replace("Poseidon2 Merkle", "Monolith Merkle"),
+        "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-        "config": {"workload": "basefold_commit_open nv=24 lr=1 queries=100 poseidon2 (sampled at nv=%d)" % nv,
+        "config": {"workload": "basefold_commit_open nv=24 lr=1 queries=100 %s (sampled at nv=%d)" % (args.hash, nv),
                    "num_vars": 24, "log_rate": LOG_RATE, "num_queries": NUM_QUERIES},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": "CPU oracle (C restatement of the reference's CPU prover, OpenMP) commit+open at "
@@ -304,6 +307,9 @@ def main():
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
+    ap.add_argument("--hash", default="poseidon2", choices=["poseidon2", "monolith"],
+                    help="Merkle hash of the basefold workload (the transcript is Poseidon2 either way); the headline "
+                         "metric names Poseidon2, the reference's default cargo features select Monolith")
     args = ap.parse_args()
     if args.workload == "batched_sumcheck":
         if args.impl == "reference":
@@ -322,6 +328,7 @@ def main():
     from matrix_b200.inputs import field_elems
 
     lib = load_gl()  # raises when the CUDA library is missing: there is no CPU path
+    assert lib.basefold_set_merkle_hash(1 if args.hash == "monolith" else 0) == 0
     if lib.cuda_set_device(local) != 0:
         raise SystemExit("cuda_set_device(%d) failed" % local)
 
@@ -410,6 +417,7 @@ def main():
     kernels = {}
     for line in buf.value.decode().splitlines():
         name, cnt, ms = line.split()
+        name = name[len("monolith_"):] if name.startswith("monolith_") else name
         kernels[name] = (int(cnt), float(ms))
 
     # e2e: host buffers in, proof out
@@ -448,16 +456,18 @@ def main():
             roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                         "launches": cnt, "avg_launch_ms": ms / cnt, "share_of_kernel_time": ms / total_kernel_ms,
-                        "note": "Poseidon2 hashing: ~520 modular multiplications per 32-byte digest, bound by the "
-                                "integer pipes, not HBM; permutations/s is the meaningful rate",
+                        "note": ("Poseidon2 hashing: ~520 modular multiplications per 32-byte digest, bound by the "
+                                 "integer pipes, not HBM; permutations/s is the meaningful rate") if args.hash == "poseidon2"
+                        else "Monolith hashing: bound by the integer pipes, not HBM; permutations/s is the meaningful rate",
                         "permutations_per_s": (leaves_commit + leaves_folded + nodes_per_step) * args.steps /
                                               ((kernels.get("hash_leaves", (0, 0))[1] + kernels.get("compress_layer", (0, 0))[1]
                                                 + kernels.get("tree_tail", (0, 0))[1]) * 1e-3)}
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.hash == "poseidon2" else METRIC.replace("Poseidon2 Merkle", "Monolith Merkle"),
+        "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
         "data": "synthetic",
-        "config": {"workload": "basefold_commit_open nv=%d lr=%d queries=%d poseidon2" % (nv, lr, nq),
+        "config": {"workload": "basefold_commit_open nv=%d lr=%d queries=%d %s" % (nv, lr, nq, args.hash),
                    "num_vars": nv, "log_rate": lr, "num_queries": nq, "per_gpu": "one polynomial per rank",
                    "l2": "inputs larger than L2 (codeword 256 MiB, trees > 1 GiB per step)"},
         "roofline": roofline,
@@ -470,7 +480,7 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         snv = args.ref_num_vars
-        dt, _ = cpu_oracle_sample(snv)
+        dt, _ = cpu_oracle_sample(snv, merkle_hash=args.hash)
         line["cpu_baseline"] = {"value": (1 << snv) / dt, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": "CPU oracle commit+open at 2^%d evaluations (%.2f s), OpenMP on all cores; "
                                           "table generation excluded on both sides" % (snv, dt)}

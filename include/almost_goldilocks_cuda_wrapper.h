@@ -98,6 +98,29 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
 int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
                         uint64_t* d_out);
 
+/* ---- host side: Monolith over almost-Goldilocks and the transcript on it ----
+ * The reference keeps these in Rust: permutation and SHA-256-derived round constants
+ * zk-torch-4/src/crypto/monolith.rs:66-208, transcript zk-torch-4/src/transcript.rs:22-243 (width 12,
+ * rate 8, overwrite mode, LIFO outputs; a label is absorbed as its length then its bytes, an empty label
+ * absorbs nothing; the constructor absorbs its label bytes without a length; appended values are
+ * reduced mod q). No device work. */
+int agl_monolith_permute_host(uint64_t* state12);
+int agl_monolith_round_constants(uint64_t* out84); /* [7][12] */
+int agl_transcript_create(const uint8_t* label, size_t label_len, void** transcript);
+int agl_transcript_destroy(void* transcript);
+/* transcript.rs:168-173: a copy that has absorbed the family label and the branch id */
+int agl_transcript_fork(const void* transcript, const uint8_t* family, size_t family_len, uint64_t branch_id,
+                        void** forked);
+int agl_transcript_append_scalar(void* transcript, const uint8_t* label, size_t label_len, uint64_t v);
+int agl_transcript_append_u64(void* transcript, const uint8_t* label, size_t label_len, uint64_t v);
+int agl_transcript_append_u64_slice(void* transcript, const uint8_t* label, size_t label_len, const uint64_t* values,
+                                    size_t n);
+int agl_transcript_append_ext2(void* transcript, const uint8_t* label, size_t label_len, uint64_t c0, uint64_t c1);
+int agl_transcript_challenge_scalar(void* transcript, const uint8_t* label, size_t label_len, uint64_t* out);
+/* n = 2 is challenge_ext2 (c0 then c1) */
+int agl_transcript_challenge_vector(void* transcript, const uint8_t* label, size_t label_len, uint64_t* out, size_t n);
+int agl_transcript_state(const void* transcript, uint64_t* out12);
+
 /* ---- additions shared with the Goldilocks library ---- */
 /* d_out[i] = splitmix64(seed) output i + 1 mod modulus: seeded synthetic inputs made on the device */
 int mb_fill_splitmix(uint64_t* d_out, size_t n, uint64_t seed, uint64_t modulus);

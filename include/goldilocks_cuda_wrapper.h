@@ -115,6 +115,17 @@ int poseidon2_merkle_layer_ffi(const uint64_t* d_input, uint64_t* d_output, int 
  * d_tree holds (2 * num_leaves - 1) digests: leaves, each layer, root last. */
 int poseidon2_merkle_tree_gl_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
 int poseidon2_merkle_tree_ext2_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
+
+/* ---- Monolith width 12 Merkle trees: ffi.rs:565-582 (wrapper.cu:1889-2012); CPU twins
+ * goldilocks-cuda-rs/src/cpu_monolith.rs:137-211. Same tree layout and leaf inputs as above, zero-padded
+ * to 12 words; digest = first four words. ---- */
+int monolith_merkle_tree_gl_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
+int monolith_merkle_tree_ext2_ffi(const uint64_t* d_codeword, uint64_t* d_tree, int num_leaves);
+/* one permutation of a host state on the device (host pointers, 12 words each) */
+int monolith_permute_test_ffi(const uint64_t* h_input, uint64_t* h_output);
+/* addition: n width-12 states on the device, permuted out of place, canonical outputs */
+int monolith_permute_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+
 /* addition, tuning hook: one layer with an explicit kernel (0: permutation per thread, 1: eight lanes per
  * permutation); asynchronous on the caller's stream */
 int mb_merkle_layer_variant(const uint64_t* d_input, uint64_t* d_output, int n, int variant);
@@ -196,6 +207,10 @@ int basefold_dot_product_mixed_ffi(const uint64_t* d_a, const uint64_t* d_b, uin
  * final_codeword[2^lr][2] | per query: index, nv value pairs [2][2], sibling
  * digests of the commitment tree bottom-up, then of each folded tree. */
 size_t basefold_proof_words(int num_vars, int log_rate, int num_queries);
+/* Merkle hash of commitments made after the call: 0 Poseidon2 (default), 1 Monolith. The reference fixes it
+ * at build time (cargo feature "monolith", goldilocks-cuda-rs/src/basefold.rs:11-14, merkle.rs:44-47); a
+ * commitment is opened with the hash it was built with. */
+int basefold_set_merkle_hash(int hash);
 int basefold_table_create(int num_vars, int log_rate, int num_rounds, uint64_t seed, void** table);
 int basefold_table_destroy(void* table);
 size_t basefold_table_entries(const void* table);

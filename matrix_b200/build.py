@@ -42,6 +42,7 @@ LIBRARIES = {
         "prof.cu",
         "agl_wrapper.cu",
         "agl_ajtai.cu",
+        "host/agl_transcript.cu",
     ],
 }
 

@@ -18,6 +18,7 @@
 // gather kernel and one copy.
 #include <cstring>
 #include <memory>
+#include <atomic>
 #include <vector>
 #include "../basefold_kernels.cuh"
 #include "../eq_kernels.cuh"
@@ -259,6 +260,12 @@ public:
     DevBuf d_entries;
 };
 
+// Merkle hash of commitments made from now on: 0 = Poseidon2, 1 = Monolith. The
+// reference fixes this at build time (cargo feature "monolith", default on:
+// goldilocks-cuda-rs/src/basefold.rs:11-14); a commitment remembers the hash it
+// was built with and its openings use the same one.
+static std::atomic<int> g_merkle_hash{0};
+
 // ---- BasefoldCommitment -----------------------------------------------------------------
 class BasefoldCommitment {
 public:
@@ -266,6 +273,7 @@ public:
     int commit_device(const uint64_t* d_evals, int nv, int lr) {
         if (nv < 1 || lr < 0 || nv + lr > 32 || !d_evals) return MB_ERR_ARG;
         num_vars = nv; log_rate = lr;
+        hash = g_merkle_hash.load();
         size_t n = (size_t)1 << nv, cw_len = (size_t)1 << (nv + lr);
         DevBuf coeffs;
         int rc = coeffs.alloc(n);
@@ -275,14 +283,16 @@ public:
         if (rc != MB_OK) return rc;
         rc = bf::interpolate_async(d_evals, coeffs.p, d_bh_evals.p, nv, MB_STREAM);
         if (rc == MB_OK) rc = bf::encode_async(coeffs.p, coeffs.p, d_codeword.p, nv, lr, MB_STREAM);
-        if (rc == MB_OK) rc = mk::build_tree_periodic(d_codeword.p, d_tree.p, cw_len / 2, (size_t)1 << lr, MB_STREAM);
+        if (rc == MB_OK)
+            rc = hash ? mk::build_tree_periodic<mk::HashMonolith>(d_codeword.p, d_tree.p, cw_len / 2, (size_t)1 << lr, MB_STREAM)
+                      : mk::build_tree_periodic<mk::HashPoseidon2>(d_codeword.p, d_tree.p, cw_len / 2, (size_t)1 << lr, MB_STREAM);
         if (rc != MB_OK) return rc;
         MB_CUDA(cudaMemcpyAsync(root, d_tree.p + 4 * (cw_len - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         return MB_OK;
     }
     uint64_t root[4] = {0, 0, 0, 0};
-    int num_vars = 0, log_rate = 0;
+    int num_vars = 0, log_rate = 0, hash = 0;
     DevBuf d_codeword, d_bh_evals, d_tree;
 };
 
@@ -422,7 +432,8 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
             }
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        rc = mk::build_tree<true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM);
+        rc = cm.hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM)
+                     : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM);
         if (rc != MB_OK) return rc;
         MB_CUDA(cudaMemcpyAsync(h_small + 8, ftree[round]->p + 4 * (cw_pairs - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
@@ -490,6 +501,13 @@ using mbhost::BasefoldCommitment;
 using mbhost::BasefoldTable;
 
 extern "C" {
+
+// Selects the Merkle hash of later commitments: 0 Poseidon2 (default), 1 Monolith.
+int basefold_set_merkle_hash(int hash) {
+    if (hash != 0 && hash != 1) return MB_ERR_ARG;
+    mbhost::g_merkle_hash.store(hash);
+    return MB_OK;
+}
 
 size_t basefold_proof_words(int num_vars, int log_rate, int num_queries) {
     return mbhost::proof_words(num_vars, log_rate, num_queries);

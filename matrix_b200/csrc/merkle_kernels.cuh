@@ -1,12 +1,16 @@
-// Poseidon2 Merkle trees over Goldilocks codewords.
+// Merkle trees over Goldilocks codewords, hashed with Poseidon2 (width 8) or
+// Monolith (width 12); the reference picks one at build time (cargo feature
+// "monolith", goldilocks-cuda-rs/src/merkle.rs:44-47), here the hash is a
+// template policy and both sets of entry points exist side by side.
 //
 // Tree buffer layout (goldilocks-cuda-rs/src/merkle.rs:266-280): the leaf
 // digests, then every layer above them, the root last; 4 words per digest.
 // Leaf k hashes the codeword pair k: permute([v0, v1, 0^6])[0..4] for base-field
 // pairs, permute([a.c0, a.c1, b.c0, b.c1, 0^4])[0..4] for extension pairs; a node
 // is permute(left || right)[0..4] (goldilocks-cuda-rs/src/cpu_poseidon2.rs:145-183,
-// device twins goldilocks-cuda-rs/cuda/wrapper.cu:1604-1713). Digests are
-// written canonical.
+// device twins goldilocks-cuda-rs/cuda/wrapper.cu:1604-1713). Monolith pads
+// the same inputs with zeros to 12 words (goldilocks-cuda-rs/src/cpu_monolith.rs:150-211,
+// wrapper.cu:1894-1987). Digests are written canonical.
 //
 // Hashing is bound by the integer pipes (about 520 modular multiplications for
 // every 32-byte digest), not by HBM, so every layer is one fully parallel launch
@@ -16,6 +20,7 @@
 #pragma once
 #include "common.cuh"
 #include "gl_poseidon2.cuh"
+#include "gl_monolith.cuh"
 
 namespace mb {
 namespace mk {
@@ -23,17 +28,33 @@ namespace mk {
 constexpr int BLOCK = 128;
 constexpr int TAIL_NODES = 64;  // layers of at most this many nodes are finished by one block
 
+// Hash policies. COOP: an 8-lanes-per-permutation variant exists for small layers.
+struct HashPoseidon2 {
+    static constexpr int WIDTH = 8;
+    static constexpr bool COOP = true;
+    static __device__ __forceinline__ void permute(uint64_t* s) { gl::poseidon2_permute(s); }
+    static const char* leaves_name() { return "hash_leaves"; }
+    static const char* layer_name() { return "compress_layer"; }
+};
+struct HashMonolith {
+    static constexpr int WIDTH = 12;
+    static constexpr bool COOP = false;
+    static __device__ __forceinline__ void permute(uint64_t* s) { gl::monolith_permute(s); }
+    static const char* leaves_name() { return "monolith_hash_leaves"; }
+    static const char* layer_name() { return "monolith_compress_layer"; }
+};
+
 __device__ __forceinline__ void store_digest(uint64_t* out, const uint64_t* s) {
     *reinterpret_cast<ulonglong2*>(out) = make_ulonglong2(gl::canon(s[0]), gl::canon(s[1]));
     *reinterpret_cast<ulonglong2*>(out + 2) = make_ulonglong2(gl::canon(s[2]), gl::canon(s[3]));
 }
 
-template <bool EXT2>
+template <class H, bool EXT2>
 __global__ void __launch_bounds__(BLOCK)
 hash_leaves_kernel(const uint64_t* __restrict__ cw, uint64_t* __restrict__ digests, size_t num_leaves) {
     const size_t step = (size_t)gridDim.x * blockDim.x;
     for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < num_leaves; k += step) {
-        uint64_t s[8];
+        uint64_t s[H::WIDTH];
         if (EXT2) {
             ulonglong2 a = *reinterpret_cast<const ulonglong2*>(cw + 4 * k);
             ulonglong2 b = *reinterpret_cast<const ulonglong2*>(cw + 4 * k + 2);
@@ -42,27 +63,32 @@ hash_leaves_kernel(const uint64_t* __restrict__ cw, uint64_t* __restrict__ diges
             ulonglong2 a = *reinterpret_cast<const ulonglong2*>(cw + 2 * k);
             s[0] = a.x; s[1] = a.y; s[2] = 0; s[3] = 0;
         }
-        s[4] = s[5] = s[6] = s[7] = 0;
-        gl::poseidon2_permute(s);
+#pragma unroll
+        for (int i = 4; i < H::WIDTH; i++) s[i] = 0;
+        H::permute(s);
         store_digest(digests + 4 * k, s);
     }
 }
 
+template <class H>
 __device__ __forceinline__ void compress_node(const uint64_t* in, uint64_t* out) {
-    uint64_t s[8];
+    uint64_t s[H::WIDTH];
     const ulonglong2* p = reinterpret_cast<const ulonglong2*>(in);
     ulonglong2 a = p[0], b = p[1], c = p[2], d = p[3];
     s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y;
     s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
-    gl::poseidon2_permute(s);
+#pragma unroll
+    for (int i = 8; i < H::WIDTH; i++) s[i] = 0;
+    H::permute(s);
     store_digest(out, s);
 }
 
 // out[k] = compress(in[2k], in[2k+1]) for k < n
-static __global__ void __launch_bounds__(BLOCK)
+template <class H>
+__global__ void __launch_bounds__(BLOCK)
 compress_layer_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
     const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += step) compress_node(in + 8 * k, out + 4 * k);
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += step) compress_node<H>(in + 8 * k, out + 4 * k);
 }
 
 // Left and right children in separate arrays (poseidon2_compress_batch_ffi).
@@ -80,6 +106,35 @@ compress_pairs_kernel(const uint64_t* __restrict__ left, const uint64_t* __restr
         s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
         gl::poseidon2_permute(s);
         store_digest(out + 4 * k, s);
+    }
+}
+
+// One block finishes every layer above `layer` (of `size` <= TAIL_NODES nodes),
+// one permutation per thread (hashes without an 8-lane variant).
+template <class H>
+__global__ void __launch_bounds__(TAIL_NODES / 2)
+tree_tail_kernel(uint64_t* layer, size_t size) {
+    while (size > 1) {
+        uint64_t* next = layer + 4 * size;
+        const size_t half = size / 2;
+        if (threadIdx.x < half) compress_node<H>(layer + 8 * threadIdx.x, next + 4 * threadIdx.x);
+        __syncthreads();
+        layer = next;
+        size = half;
+    }
+}
+
+// Full Monolith permutation of n width-12 states, canonical outputs.
+static __global__ void __launch_bounds__(BLOCK)
+monolith_permute_batch_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += step) {
+        uint64_t s[12];
+#pragma unroll
+        for (int i = 0; i < 12; i++) s[i] = in[12 * k + i];
+        gl::monolith_permute(s);
+#pragma unroll
+        for (int i = 0; i < 12; i++) out[12 * k + i] = gl::canon(s[i]);
     }
 }
 
@@ -160,49 +215,59 @@ permute_batch_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out
 // of a single permutation); from 2^13 nodes up the per-thread kernel wins.
 constexpr size_t COOP_NODES = (size_t)1 << 12;
 
+template <class H>
 inline void launch_compress_layer(const uint64_t* in, uint64_t* out, size_t n, cudaStream_t st) {
-    if (n <= COOP_NODES) {
-        MB_KERNEL_ON("compress_layer_coop", st);
-        compress_layer_coop_kernel<<<grid_for(n * 8, 256, 8), 256, 0, st>>>(in, out, n);
-    } else {
-        MB_KERNEL_ON("compress_layer", st);
-        compress_layer_kernel<<<grid_for(n, BLOCK, 16), BLOCK, 0, st>>>(in, out, n);
+    if constexpr (H::COOP) {
+        if (n <= COOP_NODES) {
+            MB_KERNEL_ON("compress_layer_coop", st);
+            compress_layer_coop_kernel<<<grid_for(n * 8, 256, 8), 256, 0, st>>>(in, out, n);
+            return;
+        }
     }
+    MB_KERNEL_ON(H::layer_name(), st);
+    compress_layer_kernel<H><<<grid_for(n, BLOCK, 16), BLOCK, 0, st>>>(in, out, n);
 }
 
-template <bool EXT2>
+template <class H, bool EXT2>
 inline void launch_hash_leaves(const uint64_t* cw, uint64_t* digests, size_t n, cudaStream_t st) {
-    if (n <= COOP_NODES) {
-        MB_KERNEL_ON("hash_leaves_coop", st);
-        hash_leaves_coop_kernel<EXT2><<<grid_for(n * 8, 256, 8), 256, 0, st>>>(cw, digests, n);
-    } else {
-        MB_KERNEL_ON("hash_leaves", st);
-        hash_leaves_kernel<EXT2><<<grid_for(n, BLOCK, 16), BLOCK, 0, st>>>(cw, digests, n);
+    if constexpr (H::COOP) {
+        if (n <= COOP_NODES) {
+            MB_KERNEL_ON("hash_leaves_coop", st);
+            hash_leaves_coop_kernel<EXT2><<<grid_for(n * 8, 256, 8), 256, 0, st>>>(cw, digests, n);
+            return;
+        }
     }
+    MB_KERNEL_ON(H::leaves_name(), st);
+    hash_leaves_kernel<H, EXT2><<<grid_for(n, BLOCK, 16), BLOCK, 0, st>>>(cw, digests, n);
+}
+
+template <class H>
+inline void launch_tree_tail(uint64_t* layer, size_t size, cudaStream_t st) {
+    MB_KERNEL_ON("tree_tail", st);
+    if constexpr (H::COOP) tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size);
+    else tree_tail_kernel<H><<<1, TAIL_NODES / 2, 0, st>>>(layer, size);
 }
 
 // Layers above the digests already present in tree[0 .. 4*num_leaves).
+template <class H>
 inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
     uint64_t* layer = d_tree;
     size_t size = num_leaves;
     while (size > TAIL_NODES) {
         size_t half = size / 2;
-        launch_compress_layer(layer, layer + 4 * size, half, st);
+        launch_compress_layer<H>(layer, layer + 4 * size, half, st);
         layer += 4 * size;
         size = half;
     }
-    if (size > 1) {
-        MB_KERNEL_ON("tree_tail", st);
-        tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size);
-    }
+    if (size > 1) launch_tree_tail<H>(layer, size, st);
     return finish_async();
 }
 
-template <bool EXT2>
+template <class H, bool EXT2>
 inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
     if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
-    launch_hash_leaves<EXT2>(d_codeword, d_tree, num_leaves, st);
-    return build_layers(d_tree, num_leaves, st);
+    launch_hash_leaves<H, EXT2>(d_codeword, d_tree, num_leaves, st);
+    return build_layers<H>(d_tree, num_leaves, st);
 }
 
 // dst[c * words + i] = src[i] for c = 1 .. copies-1 (dst = src: in-place replication of a prefix).
@@ -222,14 +287,15 @@ static __global__ void replicate_kernel(uint64_t* base, size_t words, size_t cop
 // copies, so after the bit reversal block c equals block 0). Every layer of the
 // tree is then periodic too: only the first size/copies nodes of each layer are
 // hashed, the rest are copied. The buffer ends up identical to build_tree's.
+template <class H>
 inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, size_t copies,
                                cudaStream_t st) {
     if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
-    if (copies < 2 || num_leaves / copies < 2 * (size_t)TAIL_NODES) return build_tree<false>(d_codeword, d_tree, num_leaves, st);
+    if (copies < 2 || num_leaves / copies < 2 * (size_t)TAIL_NODES) return build_tree<H, false>(d_codeword, d_tree, num_leaves, st);
     size_t uniq = num_leaves / copies;
     {
-        MB_KERNEL_ON("hash_leaves", st);
-        hash_leaves_kernel<false><<<grid_for(uniq, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, uniq);
+        MB_KERNEL_ON(H::leaves_name(), st);
+        hash_leaves_kernel<H, false><<<grid_for(uniq, BLOCK, 16), BLOCK, 0, st>>>(d_codeword, d_tree, uniq);
     }
     {
         MB_KERNEL_ON("replicate", st);
@@ -240,7 +306,7 @@ inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, siz
     while (size > TAIL_NODES && size / copies >= 2) {
         size_t half = size / 2, u = half / copies;
         uint64_t* next = layer + 4 * size;
-        launch_compress_layer(layer, next, u, st);
+        launch_compress_layer<H>(layer, next, u, st);
         {
             MB_KERNEL_ON("replicate", st);
             replicate_kernel<<<grid_for(u * 2 * (copies - 1), 256, 8), 256, 0, st>>>(next, 4 * u, copies);
@@ -251,14 +317,11 @@ inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, siz
     // the remaining layers are small: ordinary path on the fully populated layer
     while (size > TAIL_NODES) {
         size_t half = size / 2;
-        launch_compress_layer(layer, layer + 4 * size, half, st);
+        launch_compress_layer<H>(layer, layer + 4 * size, half, st);
         layer += 4 * size;
         size = half;
     }
-    if (size > 1) {
-        MB_KERNEL_ON("tree_tail", st);
-        tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size);
-    }
+    if (size > 1) launch_tree_tail<H>(layer, size, st);
     return finish_async();
 }
 

@@ -73,6 +73,10 @@ _GL_SIGNATURES = {
     "poseidon2_merkle_layer_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "poseidon2_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "poseidon2_merkle_tree_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "monolith_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "monolith_merkle_tree_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "monolith_permute_test_ffi": (c_int, [c_void_p, c_void_p]),
+    "monolith_permute_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "mb_merkle_layer_variant": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
     "ext2_eq_dp_all_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
@@ -111,6 +115,7 @@ _GL_SIGNATURES = {
     "basefold_dot_product_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "basefold_dot_product_mixed_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "basefold_proof_words": (c_size_t, [c_int, c_int, c_int]),
+    "basefold_set_merkle_hash": (c_int, [c_int]),
     "basefold_table_create": (c_int, [c_int, c_int, c_int, c_u64, ctypes.POINTER(c_void_p)]),
     "basefold_table_destroy": (c_int, [c_void_p]),
     "basefold_table_entries": (c_size_t, [c_void_p]),
@@ -186,6 +191,18 @@ _AGL_SIGNATURES = {
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
+    "agl_monolith_permute_host": (c_int, [c_void_p]),
+    "agl_monolith_round_constants": (c_int, [c_void_p]),
+    "agl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
+    "agl_transcript_destroy": (c_int, [c_void_p]),
+    "agl_transcript_fork": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_u64, ctypes.POINTER(c_void_p)]),
+    "agl_transcript_append_scalar": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_u64]),
+    "agl_transcript_append_u64": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_u64]),
+    "agl_transcript_append_u64_slice": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_void_p, c_size_t]),
+    "agl_transcript_append_ext2": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_u64, c_u64]),
+    "agl_transcript_challenge_scalar": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, ctypes.POINTER(ctypes.c_uint64)]),
+    "agl_transcript_challenge_vector": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_void_p, c_size_t]),
+    "agl_transcript_state": (c_int, [c_void_p, c_void_p]),
     "agl_fused_permute_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "agl_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "agl_partial_eval_ext2_from_base_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),

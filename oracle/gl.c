@@ -182,17 +182,28 @@ ext2_t gl_transcript_challenge_ext2(gl_transcript_t *t, const char *label) {
 /* Merkle hashing: cpu_poseidon2.rs:145-183                            */
 /* ------------------------------------------------------------------ */
 
+/* The reference chooses the Merkle hash at build time (cargo feature
+ * "monolith", goldilocks-cuda-rs/src/merkle.rs:44-47, basefold.rs:11-14); the
+ * oracle chooses at run time: 0 = Poseidon2, 1 = Monolith. Set before use, not
+ * while another thread hashes. */
+static int g_merkle_hash = 0;
+void oracle_set_merkle_hash(int h) { g_merkle_hash = h; }
+int oracle_get_merkle_hash(void) { return g_merkle_hash; }
+
 void gl_hash_gl_leaf(uint64_t a, uint64_t b, uint64_t out[4]) {
+    if (g_merkle_hash) { gl_monolith_hash_gl_leaf(a, b, out); return; }
     uint64_t s[8] = { a, b, 0, 0, 0, 0, 0, 0 };
     gl_poseidon2_permute(s);
     memcpy(out, s, 32);
 }
 void gl_hash_ext2_leaf(ext2_t a, ext2_t b, uint64_t out[4]) {
+    if (g_merkle_hash) { gl_monolith_hash_ext2_leaf(a, b, out); return; }
     uint64_t s[8] = { a.c0, a.c1, b.c0, b.c1, 0, 0, 0, 0 };
     gl_poseidon2_permute(s);
     memcpy(out, s, 32);
 }
 void gl_compress(const uint64_t l[4], const uint64_t r[4], uint64_t out[4]) {
+    if (g_merkle_hash) { gl_monolith_compress(l, r, out); return; }
     uint64_t s[8];
     memcpy(s, l, 32);
     memcpy(s + 4, r, 32);

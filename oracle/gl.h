@@ -95,6 +95,15 @@ ext2_t gl_transcript_challenge_ext2(gl_transcript_t *t, const char *label);
 void gl_hash_gl_leaf(uint64_t a, uint64_t b, uint64_t out[4]);
 void gl_hash_ext2_leaf(ext2_t a, ext2_t b, uint64_t out[4]);
 void gl_compress(const uint64_t l[4], const uint64_t r[4], uint64_t out[4]);
+/* 0 = Poseidon2 (default), 1 = Monolith for the three functions above */
+void oracle_set_merkle_hash(int h);
+int oracle_get_merkle_hash(void);
+
+/* Monolith width 12: goldilocks-cuda-rs/src/cpu_monolith.rs:18-211 */
+void gl_monolith_permute(uint64_t state[12]);
+void gl_monolith_hash_gl_leaf(uint64_t a, uint64_t b, uint64_t out[4]);
+void gl_monolith_hash_ext2_leaf(ext2_t a, ext2_t b, uint64_t out[4]);
+void gl_monolith_compress(const uint64_t l[4], const uint64_t r[4], uint64_t out[4]);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,276 @@
+/*
+ * CPU oracle (test infrastructure, not the product): the Monolith permutation
+ * (width 12, 4 bars, 6 rounds, 8-bit lookups) over Goldilocks and over
+ * almost-Goldilocks, the Merkle hash functions built on the Goldilocks one and
+ * the almost-Goldilocks duplex transcript built on the other.
+ *
+ *   Goldilocks Monolith   goldilocks-cuda-rs/src/cpu_monolith.rs:18-211
+ *   AGL Monolith          zk-torch-4/src/crypto/monolith.rs:66-200
+ *   AGL transcript        zk-torch-4/src/transcript.rs:34-260
+ *
+ * Pinned by the reference's known-answer tests: cpu_monolith.rs:237-254
+ * (permutation of 0..11), crypto/monolith.rs:379-392 (the same for AGL),
+ * :403-408 (round constants 1,0..3) and transcript.rs:358-371 (golden squeeze).
+ *
+ * The AGL round constants come from SHA-256 (the reference uses the sha2 crate,
+ * version 0.10.8 in zk-torch-4/Cargo.lock); SHA-256 is restated here from
+ * FIPS 180-4.
+ */
+#include "gl.h"
+#include "agl.h"
+#include <string.h>
+
+#define MW 12
+#define MROUNDS 6
+
+/* first row of the circulant MDS matrix (cpu_monolith.rs:46-59): row i is row 0 rotated right by i */
+static const uint64_t MDS_ROW[MW] = { 7, 23, 8, 26, 13, 10, 9, 7, 6, 22, 21, 8 };
+
+/* cpu_monolith.rs:22-44 */
+static const uint64_t GL_RC[MROUNDS + 1][MW] = {
+    { 0 },
+    { 13596126580325903823ULL, 5676126986831820406ULL, 11349149288412960427ULL, 3368797843020733411ULL,
+      16240671731749717664ULL, 9273190757374900239ULL, 14446552112110239438ULL, 4033077683985131644ULL,
+      4291229347329361293ULL, 13231607645683636062ULL, 1383651072186713277ULL, 8898815177417587567ULL },
+    { 2383619671172821638ULL, 6065528368924797662ULL, 16737578966352303081ULL, 2661700069680749654ULL,
+      7414030722730336790ULL, 18124970299993404776ULL, 9169923000283400738ULL, 15832813151034110977ULL,
+      16245117847613094506ULL, 11056181639108379773ULL, 10546400734398052938ULL, 8443860941261719174ULL },
+    { 15799082741422909885ULL, 13421235861052008152ULL, 15448208253823605561ULL, 2540286744040770964ULL,
+      2895626806801935918ULL, 8644593510196221619ULL, 17722491003064835823ULL, 5166255496419771636ULL,
+      1015740739405252346ULL, 4400043467547597488ULL, 5176473243271652644ULL, 4517904634837939508ULL },
+    { 18341030605319882173ULL, 13366339881666916534ULL, 6291492342503367536ULL, 10004214885638819819ULL,
+      4748655089269860551ULL, 1520762444865670308ULL, 8393589389936386108ULL, 11025183333304586284ULL,
+      5993305003203422738ULL, 458912836931247573ULL, 5947003897778655410ULL, 17184667486285295106ULL },
+    { 15710528677110011358ULL, 8929476121507374707ULL, 2351989866172789037ULL, 11264145846854799752ULL,
+      14924075362538455764ULL, 10107004551857451916ULL, 18325221206052792232ULL, 16751515052585522105ULL,
+      15305034267720085905ULL, 15639149412312342017ULL, 14624541102106656564ULL, 3542311898554959098ULL },
+    { 0 },
+};
+
+/* The byte S-box applied to all eight bytes at once (cpu_monolith.rs:97-103):
+ * y = rotl8(x ^ (rotl8(~x, 1) & rotl8(x, 2) & rotl8(x, 3)), 1) per byte. */
+static inline uint64_t bar_64(uint64_t x) {
+    uint64_t l1 = ((~x & 0x8080808080808080ULL) >> 7) | ((~x & 0x7F7F7F7F7F7F7F7FULL) << 1);
+    uint64_t l2 = ((x & 0xC0C0C0C0C0C0C0C0ULL) >> 6) | ((x & 0x3F3F3F3F3F3F3F3FULL) << 2);
+    uint64_t l3 = ((x & 0xE0E0E0E0E0E0E0E0ULL) >> 5) | ((x & 0x1F1F1F1F1F1F1F1FULL) << 3);
+    uint64_t t = x ^ (l1 & l2 & l3);
+    return ((t & 0x8080808080808080ULL) >> 7) | ((t & 0x7F7F7F7F7F7F7F7FULL) << 1);
+}
+
+/* cpu_monolith.rs:120-131: MDS times state plus round constants, reduced from 128 bits */
+static void gl_concrete(uint64_t *s, int round) {
+    uint64_t out[MW];
+    for (int row = 0; row < MW; row++) {
+        u128 acc = GL_RC[round][row];
+        for (int col = 0; col < MW; col++) acc += (u128)s[col] * MDS_ROW[(col - row + MW) % MW];
+        out[row] = (uint64_t)(acc % GL_P);
+    }
+    memcpy(s, out, sizeof(out));
+}
+
+/* cpu_monolith.rs:137-144. The bars act on the canonical words the preceding
+ * concrete layer left; their outputs may exceed p and are reduced by the
+ * arithmetic that follows (:111-117 bricks, top index first). */
+void gl_monolith_permute(uint64_t s[MW]) {
+    gl_concrete(s, 0);
+    for (int r = 1; r <= MROUNDS; r++) {
+        for (int i = 0; i < 4; i++) s[i] = bar_64(s[i]);
+        for (int i = MW - 1; i >= 1; i--) {
+            uint64_t prev = s[i - 1] % GL_P;
+            s[i] = gl_add(s[i] % GL_P, gl_mul(prev, prev));
+        }
+        gl_concrete(s, r);
+    }
+}
+
+void oracle_gl_monolith_permute(uint64_t *s) { gl_monolith_permute(s); }
+
+/* cpu_monolith.rs:150-211: leaf and node hashes, digest = first four words */
+void gl_monolith_hash_gl_leaf(uint64_t a, uint64_t b, uint64_t out[4]) {
+    uint64_t s[MW] = { a, b };
+    gl_monolith_permute(s);
+    memcpy(out, s, 32);
+}
+void gl_monolith_hash_ext2_leaf(ext2_t a, ext2_t b, uint64_t out[4]) {
+    uint64_t s[MW] = { a.c0, a.c1, b.c0, b.c1 };
+    gl_monolith_permute(s);
+    memcpy(out, s, 32);
+}
+void gl_monolith_compress(const uint64_t l[4], const uint64_t r[4], uint64_t out[4]) {
+    uint64_t s[MW] = { 0 };
+    memcpy(s, l, 32);
+    memcpy(s + 4, r, 32);
+    gl_monolith_permute(s);
+    memcpy(out, s, 32);
+}
+
+/* ------------------------------------------------------------------ */
+/* SHA-256 (FIPS 180-4), single-shot, short messages                   */
+/* ------------------------------------------------------------------ */
+static const uint32_t SHA_K[64] = {
+    0x428a2f98, 0x71374491, 0xb5c0fbcf, 0xe9b5dba5, 0x3956c25b, 0x59f111f1, 0x923f82a4, 0xab1c5ed5,
+    0xd807aa98, 0x12835b01, 0x243185be, 0x550c7dc3, 0x72be5d74, 0x80deb1fe, 0x9bdc06a7, 0xc19bf174,
+    0xe49b69c1, 0xefbe4786, 0x0fc19dc6, 0x240ca1cc, 0x2de92c6f, 0x4a7484aa, 0x5cb0a9dc, 0x76f988da,
+    0x983e5152, 0xa831c66d, 0xb00327c8, 0xbf597fc7, 0xc6e00bf3, 0xd5a79147, 0x06ca6351, 0x14292967,
+    0x27b70a85, 0x2e1b2138, 0x4d2c6dfc, 0x53380d13, 0x650a7354, 0x766a0abb, 0x81c2c92e, 0x92722c85,
+    0xa2bfe8a1, 0xa81a664b, 0xc24b8b70, 0xc76c51a3, 0xd192e819, 0xd6990624, 0xf40e3585, 0x106aa070,
+    0x19a4c116, 0x1e376c08, 0x2748774c, 0x34b0bcb5, 0x391c0cb3, 0x4ed8aa4a, 0x5b9cca4f, 0x682e6ff3,
+    0x748f82ee, 0x78a5636f, 0x84c87814, 0x8cc70208, 0x90befffa, 0xa4506ceb, 0xbef9a3f7, 0xc67178f2,
+};
+static inline uint32_t rotr(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
+
+void oracle_sha256(const uint8_t *msg, size_t len, uint8_t out[32]) {
+    uint32_t h[8] = { 0x6a09e667, 0xbb67ae85, 0x3c6ef372, 0xa54ff53a, 0x510e527f, 0x9b05688c, 0x1f83d9ab, 0x5be0cd19 };
+    size_t total = ((len + 9 + 63) / 64) * 64;
+    for (size_t off = 0; off < total; off += 64) {
+        uint8_t blk[64];
+        for (int i = 0; i < 64; i++) {
+            size_t p = off + i;
+            if (p < len) blk[i] = msg[p];
+            else if (p == len) blk[i] = 0x80;
+            else if (p >= total - 8) blk[i] = (uint8_t)(((uint64_t)len * 8) >> (8 * (total - 1 - p)));
+            else blk[i] = 0;
+        }
+        uint32_t w[64];
+        for (int i = 0; i < 16; i++)
+            w[i] = ((uint32_t)blk[4 * i] << 24) | ((uint32_t)blk[4 * i + 1] << 16) | ((uint32_t)blk[4 * i + 2] << 8) | blk[4 * i + 3];
+        for (int i = 16; i < 64; i++) {
+            uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+            uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+            w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+        }
+        uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+        for (int i = 0; i < 64; i++) {
+            uint32_t S1 = rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25);
+            uint32_t ch = (e & f) ^ (~e & g);
+            uint32_t t1 = hh + S1 + ch + SHA_K[i] + w[i];
+            uint32_t S0 = rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22);
+            uint32_t mj = (a & b) ^ (a & c) ^ (b & c);
+            uint32_t t2 = S0 + mj;
+            hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+        }
+        h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+    }
+    for (int i = 0; i < 8; i++)
+        for (int j = 0; j < 4; j++) out[4 * i + j] = (uint8_t)(h[i] >> (24 - 8 * j));
+}
+
+/* ------------------------------------------------------------------ */
+/* AGL Monolith                                                        */
+/* ------------------------------------------------------------------ */
+static uint64_t AGL_RC[MROUNDS + 1][MW];
+static int agl_rc_ready;
+
+/* crypto/monolith.rs:66-107: SHA-256("AGL-Monolith-RC-v1" || round || pos || salt as
+ * little-endian u32), first 8 bytes little-endian, salt incremented until below q;
+ * rounds 1..5 only, rounds 0 and 6 stay zero. */
+static void agl_rc_init(void) {
+    if (agl_rc_ready) return;
+    static const char TAG[] = "AGL-Monolith-RC-v1";
+    for (uint32_t r = 1; r < MROUNDS; r++) {
+        for (uint32_t i = 0; i < MW; i++) {
+            for (uint32_t salt = 0;; salt++) {
+                uint8_t msg[18 + 12], dg[32];
+                memcpy(msg, TAG, 18);
+                uint32_t f[3] = { r, i, salt };
+                for (int k = 0; k < 3; k++)
+                    for (int b = 0; b < 4; b++) msg[18 + 4 * k + b] = (uint8_t)(f[k] >> (8 * b));
+                oracle_sha256(msg, sizeof(msg), dg);
+                uint64_t v = 0;
+                for (int b = 7; b >= 0; b--) v = (v << 8) | dg[b];
+                if (v < AGL_Q) { AGL_RC[r][i] = v; break; }
+            }
+        }
+    }
+    agl_rc_ready = 1;
+}
+
+void oracle_agl_monolith_rc(uint64_t *out) {
+    agl_rc_init();
+    memcpy(out, AGL_RC, sizeof(AGL_RC));
+}
+
+/* crypto/monolith.rs:177-193 */
+static void agl_concrete(uint64_t *s, int round) {
+    uint64_t out[MW];
+    for (int row = 0; row < MW; row++) {
+        agl_u128 acc = AGL_RC[round][row];
+        for (int col = 0; col < MW; col++) acc += (agl_u128)(s[col] % AGL_Q) * MDS_ROW[(col - row + MW) % MW];
+        out[row] = (uint64_t)(acc % AGL_Q);
+    }
+    memcpy(s, out, sizeof(out));
+}
+
+/* crypto/monolith.rs:201-208 */
+void agl_monolith_permute(uint64_t s[MW]) {
+    agl_rc_init();
+    agl_concrete(s, 0);
+    for (int r = 1; r <= MROUNDS; r++) {
+        for (int i = 0; i < 4; i++) s[i] = bar_64(s[i]);
+        for (int i = MW - 1; i >= 1; i--) {
+            uint64_t prev = s[i - 1] % AGL_Q;
+            s[i] = agl_add(s[i] % AGL_Q, agl_mul(prev, prev));
+        }
+        agl_concrete(s, r);
+    }
+}
+void oracle_agl_monolith_permute(uint64_t *s) { agl_monolith_permute(s); }
+
+/* ------------------------------------------------------------------ */
+/* AGL transcript: width 12, rate 8, overwrite mode, LIFO outputs       */
+/* ------------------------------------------------------------------ */
+typedef struct {
+    uint64_t sponge[MW];
+    uint64_t in_buf[8];
+    uint64_t out_buf[8];
+    int in_count, out_count;
+} agl_transcript_t;
+
+/* transcript.rs:209-222 */
+static void agl_duplexing(agl_transcript_t *t) {
+    for (int i = 0; i < t->in_count; i++) t->sponge[i] = t->in_buf[i];
+    for (int i = t->in_count; i < 8; i++) t->sponge[i] = 0;
+    t->in_count = 0;
+    agl_monolith_permute(t->sponge);
+    for (int i = 0; i < 8; i++) t->out_buf[7 - i] = t->sponge[i];
+    t->out_count = 8;
+}
+/* transcript.rs:224-235 */
+static void agl_absorb(agl_transcript_t *t, uint64_t v) {
+    t->out_count = 0;
+    t->in_buf[t->in_count++] = v;
+    if (t->in_count == 8) agl_duplexing(t);
+}
+/* transcript.rs:237-243 */
+static uint64_t agl_squeeze(agl_transcript_t *t) {
+    if (t->out_count == 0) agl_duplexing(t);
+    return t->out_buf[--t->out_count];
+}
+/* transcript.rs:60-68 */
+static void agl_absorb_label(agl_transcript_t *t, const uint8_t *label, size_t n) {
+    if (n == 0) return;
+    agl_absorb(t, (uint64_t)n);
+    for (size_t i = 0; i < n; i++) agl_absorb(t, label[i]);
+}
+
+/* A scripted run for the tests: ops[i] = kind (0 append one word, 1 challenge
+ * scalar, 2 fork with branch id = value), label i = labels + label_off[i] with
+ * length label_len[i]; appended values are reduced mod q (transcript.rs:70-113),
+ * challenges are written to out in order. A fork (transcript.rs:168-173)
+ * continues on the forked copy. Returns the number of challenges. */
+size_t oracle_agl_transcript_run(const uint8_t *init_label, size_t init_len, size_t n_ops, const int *ops,
+                                 const uint8_t *labels, const size_t *label_off, const size_t *label_len,
+                                 const uint64_t *values, uint64_t *out, uint64_t *state_out) {
+    agl_transcript_t t;
+    memset(&t, 0, sizeof(t));
+    for (size_t i = 0; i < init_len; i++) agl_absorb(&t, init_label[i]); /* transcript.rs:34-47 */
+    size_t n_out = 0;
+    for (size_t i = 0; i < n_ops; i++) {
+        agl_absorb_label(&t, labels + label_off[i], label_len[i]);
+        if (ops[i] == 0) agl_absorb(&t, values[i] % AGL_Q);
+        else if (ops[i] == 1) out[n_out++] = agl_squeeze(&t);
+        else agl_absorb(&t, values[i]);
+    }
+    if (state_out) memcpy(state_out, t.sponge, sizeof(t.sponge));
+    return n_out;
+}

@@ -218,3 +218,50 @@ def batched_prove(a, b, point, K, nv, label=b"bench"):
     if rc != 0:
         raise RuntimeError("oracle_gl_batched_prove: %d" % rc)
     return out
+
+
+# ---- Monolith (both fields) and the almost-Goldilocks transcript ---------------------
+_SIGS.update({
+    "oracle_gl_monolith_permute": (None, [vp]),
+    "oracle_agl_monolith_permute": (None, [vp]),
+    "oracle_agl_monolith_rc": (None, [vp]),
+    "oracle_set_merkle_hash": (None, [ci]),
+    "oracle_get_merkle_hash": (ci, []),
+    "oracle_sha256": (None, [ctypes.c_char_p, sz, vp]),
+    "oracle_agl_transcript_run": (sz, [ctypes.c_char_p, sz, sz, vp, ctypes.c_char_p, vp, vp, vp, vp, vp]),
+})
+
+APPEND, CHALLENGE, FORK = 0, 1, 2
+
+
+def agl_transcript_run(init_label, ops):
+    """Runs a scripted almost-Goldilocks transcript: ops = [(APPEND | CHALLENGE | FORK, label, value)].
+    Returns (challenges in order, final 12-word sponge state)."""
+    import numpy as np
+    lib = load()
+    kinds = np.array([o[0] for o in ops], dtype=np.int32)
+    labels = b"".join(o[1] for o in ops)
+    lens = np.array([len(o[1]) for o in ops], dtype=np.uint64)
+    offs = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.uint64) if len(ops) else np.zeros(0, dtype=np.uint64)
+    vals = np.array([o[2] for o in ops], dtype=np.uint64)
+    out = np.zeros(max(1, len(ops)), dtype=np.uint64)
+    state = np.zeros(12, dtype=np.uint64)
+    n = lib.oracle_agl_transcript_run(init_label, len(init_label), len(ops), kinds.ctypes.data, labels,
+                                      offs.ctypes.data, lens.ctypes.data, vals.ctypes.data, out.ctypes.data,
+                                      state.ctypes.data)
+    return out[:n].copy(), state
+
+
+class merkle_hash:
+    """Context manager: the oracle's Merkle hash (0 Poseidon2, 1 Monolith) inside the block."""
+
+    def __init__(self, h):
+        self.h = h
+
+    def __enter__(self):
+        lib = load()
+        self.prev = lib.oracle_get_merkle_hash()
+        lib.oracle_set_merkle_hash(self.h)
+
+    def __exit__(self, *a):
+        load().oracle_set_merkle_hash(self.prev)

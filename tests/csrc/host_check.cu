@@ -5,6 +5,8 @@
 #include "gl_poseidon2.cuh"
 #include "agl_field.cuh"
 #include "host/gl_transcript.hpp"
+#include "gl_monolith.cuh"
+#include "host/agl_transcript.hpp"
 
 extern "C" {
 uint64_t hc_gl_add(uint64_t a, uint64_t b) { return gl::add(a, b); }
@@ -32,6 +34,12 @@ void hc_aext2_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) {
     o[0] = r.c0; o[1] = r.c1;
 }
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
+void hc_gl_monolith(uint64_t* s) {
+    gl::monolith_permute(s);
+    for (int i = 0; i < 12; i++) s[i] = gl::canon(s[i]);
+}
+void hc_agl_monolith(uint64_t* s) { mbhost::aglm::permute(s); }
+uint64_t hc_agl_reduce_limb_sums(uint64_t L, uint64_t H) { return agl::reduce_limb_sums(L, H); }
 
 // Replays a script of transcript operations: op 0 = absorb(v), 1 = squeeze -> out.
 int hc_transcript_script(const uint8_t* label, size_t n, const int* ops, const uint64_t* vals, int nops, uint64_t* out) {
