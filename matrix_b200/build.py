@@ -31,6 +31,7 @@ LIBRARIES = {
         "gl_sumcheck.cu",
         "gl_noalloc.cu",
         "gl_merkle.cu",
+        "gl_batch.cu",
         "gl_basefold.cu",
         "gl_challenger.cu",
         "host/gl_sumcheck_prover.cu",
@@ -42,6 +43,7 @@ LIBRARIES = {
         "prof.cu",
         "agl_wrapper.cu",
         "agl_ajtai.cu",
+        "agl_batch.cu",
         "host/agl_transcript.cu",
     ],
 }

@@ -180,6 +180,81 @@ GLF uint64_t pw(uint64_t a, uint64_t e) {
 // Fermat inverse; inv(0) = 0.
 GLF uint64_t inv(uint64_t a) { return pw(a, P - 2); }
 
+// ---- lazily reduced sums of products ------------------------------------------
+// A sum of a few 128-bit products (and 64-bit addends) is kept exact in 160 bits
+// and reduced once: per product that is five multiply-adds for the product and
+// five additions with carry, against a full reduction and a modular addition
+// when every product is reduced on its own.
+
+// x * y as (hi : lo), from four 32 x 32 products. No step overflows:
+// (2^32 - 1)^2 + 2 (2^32 - 1) = 2^64 - 1.
+GLF void mul128(uint64_t x, uint64_t y, uint64_t& lo, uint64_t& hi) {
+#ifdef __CUDA_ARCH__
+    const uint32_t x0 = lo32(x), x1 = hi32(x), y0 = lo32(y), y1 = hi32(y);
+    uint64_t p00 = madwide(x0, y0, 0);
+    uint64_t p01 = madwide(x0, y1, (uint64_t)hi32(p00));
+    uint64_t p10 = madwide(x1, y0, (uint64_t)lo32(p01));
+    uint64_t p11 = madwide(x1, y1, (uint64_t)hi32(p01));
+    lo = pack64(lo32(p00), lo32(p10));
+    hi = madwide(hi32(p10), 1u, p11);
+#else
+    unsigned __int128 f = (unsigned __int128)x * y;
+    lo = (uint64_t)f;
+    hi = (uint64_t)(f >> 64);
+#endif
+}
+
+// top : hi : lo, top < 2^32 (room for 2^32 products).
+struct Acc {
+    uint64_t lo, hi;
+    uint32_t top;
+};
+GLF Acc acc_zero() { return Acc{0, 0, 0}; }
+GLF void acc_add128(Acc& s, uint64_t lo, uint64_t hi) {
+#ifdef __CUDA_ARCH__
+    asm("add.cc.u64 %0, %0, %3;\n\taddc.cc.u64 %1, %1, %4;\n\taddc.u32 %2, %2, 0;"
+        : "+l"(s.lo), "+l"(s.hi), "+r"(s.top)
+        : "l"(lo), "l"(hi));
+#else
+    unsigned __int128 cur = ((unsigned __int128)s.hi << 64) | s.lo, add = ((unsigned __int128)hi << 64) | lo;
+    unsigned __int128 r = cur + add;
+    if (r < cur) s.top++;
+    s.lo = (uint64_t)r;
+    s.hi = (uint64_t)(r >> 64);
+#endif
+}
+GLF void acc_add(Acc& s, uint64_t v) { acc_add128(s, v, 0); }
+GLF void acc_mul(Acc& s, uint64_t x, uint64_t y) {
+    uint64_t lo, hi;
+    mul128(x, y, lo, hi);
+    acc_add128(s, lo, hi);
+}
+// s mod p for top < 2^8, loose result. 2^128 = -2^32 (mod p), so the top limb joins
+// the subtrahend of reduce_limbs: B = z2 + z3 + 2^32 top < 2^41, and the repair
+// of a borrow still cannot underflow (the wrapped value exceeds 2^64 - 2^41).
+GLF uint64_t acc_reduce(const Acc& s) {
+    const uint32_t z0 = lo32(s.lo), z1 = hi32(s.lo), z2 = lo32(s.hi), z3 = hi32(s.hi);
+    uint64_t A = madwide(z2, 1u, (uint64_t)z1);
+    uint64_t B0 = madwide(z3, 1u, (uint64_t)z2);
+    uint64_t B = pack64(lo32(B0), hi32(B0) + s.top);
+    uint64_t W = madwide(hi32(A), 0xFFFFFFFFu, pack64(z0, lo32(A)));
+    uint32_t m;
+    uint64_t R = sub_borrow(W, B, m);
+    return R - (uint64_t)m;
+}
+
+// s mod p for any top limb (long-running accumulators): top 2^128 = -top 2^32.
+GLF uint64_t acc_reduce_wide(const Acc& s) {
+    return sub(reduce128(s.lo, s.hi), (uint64_t)s.top << 32);
+}
+
+// a - b for canonical a, b; canonical result (one borrow repair: + p = - EPS mod 2^64).
+GLF uint64_t sub_canon(uint64_t a, uint64_t b) {
+    uint32_t m;
+    uint64_t d = sub_borrow(a, b, m);
+    return d - (uint64_t)m;
+}
+
 // ---------------------------------------------------------------------------
 // Quadratic extension, X^2 = 7. Stored as (c0, c1), two consecutive u64.
 // ---------------------------------------------------------------------------
@@ -199,6 +274,53 @@ GLF E2 e2_mul(E2 a, E2 b) {
 }
 
 GLF E2 e2_mul_base(E2 a, uint64_t b) { return E2{mul(a.c0, b), mul(a.c1, b)}; }
+
+// A loop-invariant extension factor with 7 c1 precomputed: r * d needs four
+// products and two reductions, no modular additions.
+struct E2Pre {
+    uint64_t c0, c1, c1w;
+};
+GLF E2Pre e2_pre(E2 r) { return E2Pre{canon(r.c0), canon(r.c1), canon(mul_small(canon(r.c1), 7))}; }
+// a + r * d
+GLF E2 e2_fma_pre(E2Pre r, E2 d, E2 a) {
+    Acc s0 = Acc{a.c0, 0, 0}, s1 = Acc{a.c1, 0, 0};
+    acc_mul(s0, r.c0, d.c0);
+    acc_mul(s0, r.c1w, d.c1);
+    acc_mul(s1, r.c0, d.c1);
+    acc_mul(s1, r.c1, d.c0);
+    return E2{acc_reduce(s0), acc_reduce(s1)};
+}
+GLF E2 e2_mul_pre(E2Pre r, E2 d) { return e2_fma_pre(r, d, E2{0, 0}); }
+// a + r * d for a base-field d
+GLF E2 e2_fma_pre_base(E2Pre r, uint64_t d, uint64_t a) {
+    Acc s0 = Acc{a, 0, 0}, s1 = acc_zero();
+    acc_mul(s0, r.c0, d);
+    acc_mul(s1, r.c1, d);
+    return E2{acc_reduce(s0), acc_reduce(s1)};
+}
+
+// Lazy accumulator of extension products: sum a_k b_k as three exact sums.
+struct E2Acc {
+    Acc s00, s11, s01;
+};
+GLF E2Acc e2acc_zero() { return E2Acc{acc_zero(), acc_zero(), acc_zero()}; }
+GLF void e2acc_mul(E2Acc& q, E2 a, E2 b) {
+    acc_mul(q.s00, a.c0, b.c0);
+    acc_mul(q.s11, a.c1, b.c1);
+    acc_mul(q.s01, a.c0, b.c1);
+    acc_mul(q.s01, a.c1, b.c0);
+}
+// one product through the lazy sums: four multiplications, three reductions
+GLF E2 e2_mul_lazy(E2 a, E2 b);
+// at most 64 products accumulated (top limbs below 2^8)
+GLF E2 e2acc_reduce(const E2Acc& q) {
+    return E2{add(acc_reduce(q.s00), mul_small(acc_reduce(q.s11), 7)), acc_reduce(q.s01)};
+}
+GLF E2 e2_mul_lazy(E2 a, E2 b) {
+    E2Acc q = e2acc_zero();
+    e2acc_mul(q, a, b);
+    return e2acc_reduce(q);
+}
 
 GLF E2 e2_inv(E2 a) {
     uint64_t n = sub(sqr(a.c0), mul_small(sqr(a.c1), 7));

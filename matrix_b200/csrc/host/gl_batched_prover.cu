@@ -29,7 +29,7 @@ public:
              int n_loc) {
         if (!d_a || !d_b || !h_eq_scale || K < 1 || K > bt::MAX_K || n_loc < 1 || n_loc > 34) return MB_ERR_ARG;
         if (n_loc > 0 && !h_point_low) return MB_ERR_ARG;
-        K_ = K; n_loc_ = n_loc; n_ = (size_t)1 << n_loc; round_ = 0; have_msg_ = false; have_alpha_ = false;
+        K_ = K; n_loc_ = n_loc; n_ = (size_t)1 << n_loc; round_ = 0; have_msg_ = false; have_alpha_ = false; have_inst_ = false;
         a0_ = d_a;  // the caller's tables are read in place during round 0 and never written
         b0_ = d_b;
         size_t half = n_ / 2, quarter = n_ >= 4 ? n_ / 4 : 1;
@@ -39,13 +39,22 @@ public:
         MB_CUDA(pool_alloc((void**)&ab_a_, 16 * 2 * K * half));
         MB_CUDA(pool_alloc((void**)&ab_b_, 16 * 2 * K * quarter));
         grid_max_ = grid_for(half, 256, 4);
-        MB_CUDA(pool_alloc((void**)&partial_, sizeof(uint64_t) * 2 * (size_t)(K > bt::NC ? K : bt::NC) * grid_max_));
-        MB_CUDA(pool_alloc((void**)&small_, sizeof(uint64_t) * (16 + 2 * bt::MAX_K + 2 * 40 + 2)));
+        // round-0 kernel: lane groups of Kp lanes, two output pairs per lane and step
+        Kp_ = 1;
+        while (Kp_ < K && Kp_ < 32) Kp_ *= 2;
+        const size_t per_step = (size_t)2 * (32 / Kp_);
+        grid_inst_ = grid_for(((half + per_step - 1) / per_step) * 32, 256, 3);
+        size_t partial_words = 2 * (size_t)bt::NC * (size_t)grid_max_;
+        if (partial_words < 2 * (size_t)bt::NC * K * grid_inst_) partial_words = 2 * (size_t)bt::NC * K * grid_inst_;
+        MB_CUDA(pool_alloc((void**)&partial_, sizeof(uint64_t) * partial_words));
+        MB_CUDA(pool_alloc((void**)&small_, sizeof(uint64_t) * (16 + 2 * bt::MAX_K + 2 * 40 + 2 + 4 * bt::MAX_K + 8 * bt::MAX_K)));
         msg_dev_ = small_;                      // 8 words
         counter_ = reinterpret_cast<unsigned int*>(small_ + 8);
         alpha_dev_ = small_ + 16;               // 2 * MAX_K words
         uint64_t* point_dev = alpha_dev_ + 2 * bt::MAX_K;  // 2 * 40 words
         uint64_t* scale_dev = point_dev + 80;               // 2 words
+        wtab_dev_ = scale_dev + 2;                          // 4 * MAX_K words
+        inst_dev_ = wtab_dev_ + 4 * bt::MAX_K;              // 8 * MAX_K words
         MB_CUDA(cudaMemsetAsync(small_, 0, 16 * sizeof(uint64_t), MB_STREAM));
         MB_CUDA(cudaMemcpyAsync(point_dev, h_point_low, 16 * (size_t)n_loc, cudaMemcpyHostToDevice, MB_STREAM));
         MB_CUDA(cudaMemcpyAsync(scale_dev, h_eq_scale, 16, cudaMemcpyHostToDevice, MB_STREAM));
@@ -56,28 +65,40 @@ public:
         return h_ ? MB_OK : MB_ERR_CUDA;
     }
 
-    // Local share of the per-instance claims s_k (K extension elements).
-    int claims(uint64_t* h_out) {
-        int grid = grid_for(n_, 256, 2);
-        if (grid > grid_max_) grid = grid_max_;
+    // Per-instance round-0 messages m_k(0..3) of this shard, one pass over the caller's tables.
+    int instance_messages() {
+        if (have_inst_) return MB_OK;
+        const size_t half = n_ / 2;
+        dim3 grid(grid_inst_, (K_ + 31) / 32);
+        const size_t smem = sizeof(uint64_t) * 8 * (size_t)(2 * (32 / Kp_)) * 8;
         {
-            MB_KERNEL("batched_claims");
-            bt::claims_kernel<GlBase, GlExt2><<<grid, 256, 0, MB_STREAM>>>(eq0_, a0_, b0_, K_, n_, n_, partial_);
+            MB_KERNEL("batched_instance_messages");
+            bt::instance_messages_kernel<<<grid, 256, smem, MB_STREAM>>>(eq0_, a0_, b0_, K_, Kp_, n_, half, partial_);
         }
-        uint64_t* d_out = nullptr;
-        MB_CUDA(pool_alloc((void**)&d_out, 16 * (size_t)K_));
         {
             MB_KERNEL("reduce_partials");
-            reduce_partials_kernel<256, GlAdd, GlCanon><<<1, 256, 0, MB_STREAM>>>(partial_, grid, 2 * K_, d_out);
+            reduce_partials_kernel<256, GlAdd, GlCanon><<<1, 256, 0, MB_STREAM>>>(partial_, grid_inst_, 2 * bt::NC * K_, inst_dev_);
         }
-        MB_CUDA(cudaMemcpyAsync(h_out, d_out, 16 * (size_t)K_, cudaMemcpyDeviceToHost, MB_STREAM));
+        inst_.resize(2 * (size_t)bt::NC * K_);
+        MB_CUDA(cudaMemcpyAsync(inst_.data(), inst_dev_, sizeof(uint64_t) * inst_.size(), cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
-        pool_free(d_out);
+        have_inst_ = true;
+        return MB_OK;
+    }
+
+    // Local share of the per-instance claims s_k = m_k(0) + m_k(1) (K extension elements).
+    int claims(uint64_t* h_out) {
+        int rc = instance_messages();
+        if (rc != MB_OK) return rc;
+        for (int k = 0; k < K_; k++)
+            for (int comp = 0; comp < 2; comp++)
+                h_out[2 * k + comp] = gl::canon(gl::add(inst_[8 * (size_t)k + comp], inst_[8 * (size_t)k + 2 + comp]));
         return MB_OK;
     }
 
     int set_alpha(Ext2 alpha) {
-        std::vector<uint64_t> pows(2 * K_);
+        std::vector<uint64_t>& pows = pows_;
+        pows.resize(2 * (size_t)K_);
         gl::E2 p{1, 0}, a{gl::canon(alpha.c0), gl::canon(alpha.c1)};
         for (int k = 0; k < K_; k++) {
             pows[2 * k] = p.c0;
@@ -93,12 +114,22 @@ public:
     // Local share of m(0..3) for the current round.
     int round_message(uint64_t* h_msg) {
         if (!have_alpha_ || round_ >= n_loc_) return MB_ERR_ARG;
-        if (!have_msg_) {
-            size_t half = n_ / 2;
-            MB_KERNEL("batched_round0");
-            bt::round0_message_kernel<GlBase, GlExt2><<<grid_for(half, 256, 4), 256, 0, MB_STREAM>>>(
-                eq0_, a0_, b0_, alpha_dev_, K_, n_, half, partial_, counter_, msg_dev_);
+        if (round_ == 0) {
+            // sum_k alpha^k m_k(c) from the per-instance messages
+            int rc = instance_messages();
+            if (rc != MB_OK) return rc;
+            for (int c = 0; c < bt::NC; c++) {
+                gl::E2 acc{0, 0};
+                for (int k = 0; k < K_; k++)
+                    acc = gl::e2_add(acc, gl::e2_mul(gl::E2{pows_[2 * k], pows_[2 * k + 1]},
+                                                     gl::E2{inst_[8 * (size_t)k + 2 * c], inst_[8 * (size_t)k + 2 * c + 1]}));
+                acc = gl::e2_canon(acc);
+                h_msg[2 * c] = acc.c0;
+                h_msg[2 * c + 1] = acc.c1;
+            }
+            return MB_OK;
         }
+        if (!have_msg_) return MB_ERR_ARG;
         MB_CUDA(cudaMemcpyAsync(h_, msg_dev_, 64, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         std::memcpy(h_msg, h_, 64);
@@ -119,13 +150,23 @@ public:
         size_t stride_out = to_a ? n_ / 2 : (n_ >= 4 ? n_ / 4 : 1);
         if (quarter >= 1) {
             int grid = grid_for(quarter, 256, 4);
+            if (first) {
+                // per instance: alpha^k and alpha^k r
+                std::vector<uint64_t> wt(4 * (size_t)K_);
+                for (int k = 0; k < K_; k++) {
+                    gl::E2 w{pows_[2 * k], pows_[2 * k + 1]}, wr = gl::e2_canon(gl::e2_mul(w, r));
+                    wt[4 * k] = w.c0; wt[4 * k + 1] = w.c1; wt[4 * k + 2] = wr.c0; wt[4 * k + 3] = wr.c1;
+                }
+                MB_CUDA(cudaMemcpyAsync(wtab_dev_, wt.data(), sizeof(uint64_t) * wt.size(), cudaMemcpyHostToDevice, MB_STREAM));
+                MB_CUDA(cudaStreamSynchronize(MB_STREAM));  // wt leaves scope
+            }
             MB_KERNEL("batched_fold_message");
             if (first)
-                bt::fold_message_kernel<GlBase, GlExt2, true><<<grid, 256, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, b0_, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+                bt::fold_message_kernel<true><<<grid, 256, 0, MB_STREAM>>>(
+                    eq_in, eq_out, ab_in, b0_, ab_out, wtab_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
             else
-                bt::fold_message_kernel<GlBase, GlExt2, false><<<grid, 256, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, b0_, ab_out, alpha_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+                bt::fold_message_kernel<false><<<grid, 256, 0, MB_STREAM>>>(
+                    eq_in, eq_out, ab_in, b0_, ab_out, wtab_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
             have_msg_ = true;
         } else {
             MB_KERNEL("batched_final_fold");
@@ -165,7 +206,10 @@ private:
         pool_free(partial_); pool_free(small_);
         eq0_ = eq_a_ = eq_b_ = ab_a_ = ab_b_ = partial_ = small_ = nullptr;
     }
-    int K_ = 0, n_loc_ = 0, round_ = 0, grid_max_ = 0;
+    int K_ = 0, Kp_ = 1, n_loc_ = 0, round_ = 0, grid_max_ = 0, grid_inst_ = 0;
+    bool have_inst_ = false;
+    std::vector<uint64_t> inst_, pows_;
+    uint64_t *wtab_dev_ = nullptr, *inst_dev_ = nullptr;
     size_t n_ = 0, ab_stride_ = 0;
     bool have_msg_ = false, have_alpha_ = false;
     const uint64_t *a0_ = nullptr, *b0_ = nullptr;

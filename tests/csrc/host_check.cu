@@ -34,6 +34,25 @@ void hc_aext2_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) {
     o[0] = r.c0; o[1] = r.c1;
 }
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
+// sum_i x[i] * y[i] + c through the lazy accumulator
+uint64_t hc_gl_dot(const uint64_t* x, const uint64_t* y, int n, uint64_t c) {
+    gl::Acc s = gl::Acc{c, 0, 0};
+    for (int i = 0; i < n; i++) gl::acc_mul(s, x[i], y[i]);
+    return gl::canon(gl::acc_reduce(s));
+}
+uint64_t hc_gl_sub_canon(uint64_t a, uint64_t b) { return gl::sub_canon(a, b); }
+// a + r * d with the precomputed-factor form
+void hc_e2_fma_pre(const uint64_t* r, const uint64_t* d, const uint64_t* a, uint64_t* o) {
+    gl::E2 v = gl::e2_canon(gl::e2_fma_pre(gl::e2_pre(gl::E2{r[0], r[1]}), gl::E2{d[0], d[1]}, gl::E2{a[0], a[1]}));
+    o[0] = v.c0; o[1] = v.c1;
+}
+// sum_i a[i] * b[i] over the extension through the lazy accumulator
+void hc_e2_dot(const uint64_t* a, const uint64_t* b, int n, uint64_t* o) {
+    gl::E2Acc q = gl::e2acc_zero();
+    for (int i = 0; i < n; i++) gl::e2acc_mul(q, gl::E2{a[2 * i], a[2 * i + 1]}, gl::E2{b[2 * i], b[2 * i + 1]});
+    gl::E2 v = gl::e2_canon(gl::e2acc_reduce(q));
+    o[0] = v.c0; o[1] = v.c1;
+}
 void hc_gl_monolith(uint64_t* s) {
     gl::monolith_permute(s);
     for (int i = 0; i < 12; i++) s[i] = gl::canon(s[i]);

@@ -141,3 +141,46 @@ def test_almost_goldilocks_loose_arithmetic(hostcheck):
     A, B, O = (u64 * 2)(1, 2), (u64 * 2)(3, 4), (u64 * 2)()
     hostcheck.hc_aext2_mul(A, B, O)
     assert (O[0] % Q, O[1] % Q) == (27, 10)
+
+
+def test_lazy_accumulators(hostcheck):
+    """Sums of products kept exact in 160 bits and reduced once: base dot products of up to
+    128 terms of all-ones words, the precomputed-factor multiply-add, extension dot products."""
+    hc = hostcheck
+    hc.hc_gl_dot.restype = u64
+    hc.hc_gl_dot.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, u64]
+    hc.hc_gl_sub_canon.restype = u64
+    hc.hc_gl_sub_canon.argtypes = [u64, u64]
+    rnd = random.Random(21)
+    for n in (0, 1, 2, 3, 16, 64, 128):
+        for mode in ("max", "rand", "mixed"):
+            if mode == "max":
+                x, y = [2**64 - 1] * n, [2**64 - 1] * n
+            elif mode == "rand":
+                x, y = [rnd.randrange(2**64) for _ in range(n)], [rnd.randrange(2**64) for _ in range(n)]
+            else:
+                x = [rnd.choice([0, 1, P - 1, P, 2**64 - 1, 2**32, 2**32 - 1]) for _ in range(n)]
+                y = [rnd.choice([0, 1, P - 1, P, 2**64 - 1, 2**32, 2**32 - 1]) for _ in range(n)]
+            c = rnd.choice([0, 2**64 - 1, rnd.randrange(2**64)])
+            X, Y = np.array(x, dtype=np.uint64), np.array(y, dtype=np.uint64)
+            got = hc.hc_gl_dot(X.ctypes.data, Y.ctypes.data, n, c)
+            assert got == (sum(a * b for a, b in zip(x, y)) + c) % P
+    edge = [0, 1, 2, P - 1, P - 2, 2**32, 2**32 - 1, 2**63]
+    for a in edge + [rnd.randrange(P) for _ in range(100)]:
+        for b in edge + [rnd.randrange(P) for _ in range(10)]:
+            assert hc.hc_gl_sub_canon(a, b) == (a - b) % P
+    for _ in range(400):
+        r, d, a = ([rnd.choice([rnd.randrange(2**64), 2**64 - 1, P - 1, 0]) for _ in range(2)] for _ in range(3))
+        R, D, A, O = (u64 * 2)(*r), (u64 * 2)(*d), (u64 * 2)(*a), (u64 * 2)()
+        hc.hc_e2_fma_pre(R, D, A, O)
+        assert O[0] == (a[0] + r[0] * d[0] + 7 * r[1] * d[1]) % P
+        assert O[1] == (a[1] + r[0] * d[1] + r[1] * d[0]) % P
+    for n in (1, 5, 16, 64):
+        for mode in ("max", "rand"):
+            v = [2**64 - 1] * (4 * n) if mode == "max" else [rnd.randrange(2**64) for _ in range(4 * n)]
+            a, b = np.array(v[:2 * n], dtype=np.uint64), np.array(v[2 * n:], dtype=np.uint64)
+            O = (u64 * 2)()
+            hc.hc_e2_dot(a.ctypes.data, b.ctypes.data, n, O)
+            c0 = sum(int(a[2 * i]) * int(b[2 * i]) + 7 * int(a[2 * i + 1]) * int(b[2 * i + 1]) for i in range(n)) % P
+            c1 = sum(int(a[2 * i]) * int(b[2 * i + 1]) + int(a[2 * i + 1]) * int(b[2 * i]) for i in range(n)) % P
+            assert (O[0], O[1]) == (c0, c1)
