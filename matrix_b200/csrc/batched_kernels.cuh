@@ -6,19 +6,26 @@
 // linear prover zk-torch-4/src/sumcheck/cpu_ext2_prover.rs:21-100; low variable
 // first).
 //
+// Every round polynomial factors: the eq table of a round is
+// C eq(t_i, x_i) eq(t_rest, y), so with E(y) = eq[2y] + eq[2y + 1] = C eq(t_rest, y)
+//   m(c) = lambda(c) T(c),  lambda(c) = (1 - t_i) + c (2 t_i - 1),
+//   T(c) = sum_y E(y) Q_y(c),  Q_y(c) = sum_k alpha^k a_k(c, y) b_k(c, y),
+// and T is quadratic: the kernels return T(0), T(1) and its leading coefficient
+// T2 (three extension elements); the host forms T(2) = 2 T(1) + 2 T2 - T(0),
+// T(3) = 3 T(1) + 6 T2 - 2 T(0) and multiplies by lambda. The results are the same
+// field elements as the direct sums over eq(c, y) a(c, y) b(c, y).
+//
 // Round 0 works on the caller's base-field tables and is independent of alpha:
-// one pass produces, per instance, m_k(0..3) = sum_y eq(c, y) a_k(c, y) b_k(c, y);
-// the claims are s_k = m_k(0) + m_k(1) and the round-0 message is
-// sum_k alpha^k m_k(c), combined on the host. The first fold lifts the tables to
-// the extension and multiplies a_k by alpha^k once; every later pass folds the
-// 2K + 1 tables and accumulates the next message in the same sweep.
+// one pass produces T_k(0), T_k(1), T2_k per instance; the claims are
+// s_k = m_k(0) + m_k(1) and the round-0 message is sum_k alpha^k m_k(c), combined
+// on the host. The first fold lifts the tables to the extension and multiplies
+// a_k by alpha^k once; every later pass folds the 2K + 1 tables and accumulates
+// the next message in the same sweep.
 //
 // Arithmetic: all multiplications feed exact 160-bit sums that are reduced once
-// (gl::Acc). Per instance and output pair the inner polynomial
-// Q(c) = sum_k a_k(c) b_k(c) is quadratic, so three lazily accumulated
-// extension products (at c = 0, c = 1 and the leading coefficient) replace four
-// reduced ones; Q(2), Q(3) follow by additions and eq(c) Q(c) is formed once
-// per pair, not once per instance.
+// (gl::Acc); Q_y(0), Q_y(1) and the leading coefficient of Q_y are three lazily
+// accumulated extension products per instance, and E Q is formed once per pair,
+// not once per instance.
 #pragma once
 #include "sumcheck_kernels.cuh"
 
@@ -26,7 +33,7 @@ namespace mb {
 namespace bt {
 
 constexpr int MAX_K = 64;
-constexpr int NC = 4;  // evaluation points c = 0..3
+constexpr int NC = 3;  // T(0), T(1) and the leading coefficient of T
 
 // Block partial rows of 8 words, last block sums them (same pattern as the linear prover).
 template <class FE>
@@ -53,66 +60,98 @@ __device__ __forceinline__ void finish_message(typename FE::T (&m)[NC], uint64_t
     if (threadIdx.x == 0) *counter = 0;
 }
 
-// ---- round 0: per-instance messages from the base-field tables ----------------------
+// ---- round 0: per-instance T_k(0), T_k(1), T2_k from the base-field tables ---------------
 // Lane l of a warp owns instance k = kbase + (l & (Kp - 1)) for the whole
-// launch, so its eight exact sums (4 points x 2 components) are reduced only
-// once at the end; the 32 / Kp lane groups of a warp take consecutive pairs of
-// output pairs y, and the eq values eq(c, y), c = 0..3, of the warp's current
-// pairs are computed once by the warp and shared through shared memory.
+// launch, so its six exact sums are reduced only once at the end; the 32 / Kp
+// lane groups of a warp take consecutive pairs of output pairs y, and the
+// weights E(y) of the warp's current pairs are shared through shared memory.
+// The loads of step i + 1 are issued before the arithmetic of step i.
 // eq: canonical extension table; a0p, b0p: [K][stride] (any representatives);
-// half = number of pairs; partial: [gridDim.x][K][8] canonical words. Dynamic
-// shared memory: warps * (64 / Kp) * 8 words.
+// half = number of pairs; partial: [gridDim.x][K][6] canonical words. Dynamic
+// shared memory: warps * 2 * (64 / Kp) * 2 words.
 static __global__ void __launch_bounds__(256)
 instance_messages_kernel(const uint64_t* __restrict__ eq, const uint64_t* __restrict__ a0p,
                          const uint64_t* __restrict__ b0p, int K, int Kp, size_t stride, size_t half,
                          uint64_t* __restrict__ partial) {
-    extern __shared__ uint64_t dyn[];
+    extern __shared__ __align__(16) uint64_t dyn[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int G = 32 / Kp, g = lane / Kp;
     const int k = blockIdx.y * 32 + (lane & (Kp - 1));
     const bool live_k = k < K;
     const int ys_per_iter = 2 * G;
-    uint64_t* ev = dyn + (size_t)warp * ys_per_iter * 8;  // [y][c][component]
+    const int nev = ys_per_iter * 2;  // weight words per step; one per lane when Kp >= 4
+    uint64_t* ev = dyn + (size_t)warp * nev * 2;  // two buffers of [y][component]
     const uint64_t* pa = a0p + (size_t)(live_k ? k : 0) * stride;
     const uint64_t* pb = b0p + (size_t)(live_k ? k : 0) * stride;
     gl::Acc A[NC][2];
 #pragma unroll
     for (int c = 0; c < NC; c++) A[c][0] = A[c][1] = gl::acc_zero();
     const size_t warps_total = (size_t)gridDim.x * nwarp, wg = (size_t)blockIdx.x * nwarp + warp;
-    for (size_t ybase = wg * ys_per_iter; ybase < half; ybase += warps_total * ys_per_iter) {
-        // eq(c, y) = e0 + c (e1 - e0) for the warp's pairs, one value per lane and step
-        for (int j = lane; j < ys_per_iter * 8; j += 32) {
-            const size_t y = ybase + (j >> 3);
-            const int c = (j >> 1) & 3, comp = j & 1;
-            uint64_t v = 0;
-            if (y < half) {
-                const uint64_t e0 = eq[4 * y + comp], e1 = eq[4 * y + 2 + comp];
-                gl::Acc s = gl::Acc{e0, 0, 0};
-                gl::acc_mul(s, (uint64_t)c, gl::sub_canon(e1, e0));
-                v = gl::acc_reduce(s);
-            }
-            ev[j] = v;
+    const size_t ystep = warps_total * ys_per_iter;
+
+    auto weight_fill = [&](size_t ybase, uint64_t* dst) {  // unpipelined form, any Kp
+        for (int j = lane; j < nev; j += 32) {
+            const size_t y = ybase + (j >> 1);
+            dst[j] = y < half ? gl::add_c(eq[4 * y + (j & 1)], eq[4 * y + 2 + (j & 1)]) : 0;
         }
-        __syncwarp();
+    };
+    const bool one_per_lane = nev <= 32;
+    ulonglong2 ca[2], cb[2], na[2], nb[2];
+    uint64_t ne0 = 0, ne1 = 0;
+    auto load_pairs = [&](size_t ybase, ulonglong2 (&ta)[2], ulonglong2 (&tb)[2]) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const size_t y = ybase + 2 * g + h;
+            ta[h] = tb[h] = make_ulonglong2(0, 0);
+            if (y < half && live_k) {
+                ta[h] = *reinterpret_cast<const ulonglong2*>(pa + 2 * y);
+                tb[h] = *reinterpret_cast<const ulonglong2*>(pb + 2 * y);
+            }
+        }
+    };
+    size_t ybase = wg * ys_per_iter;
+    int buf = 0;
+    if (ybase < half) {
+        weight_fill(ybase, ev);
+        load_pairs(ybase, ca, cb);
+    }
+    __syncwarp();
+    for (; ybase < half; ybase += ystep, buf ^= 1) {
+        const size_t ynext = ybase + ystep;
+        const bool more = ynext < half;
+        if (more) {
+            load_pairs(ynext, na, nb);
+            if (one_per_lane && lane < nev) {
+                const size_t y = ynext + (lane >> 1);
+                if (y < half) {
+                    ne0 = eq[4 * y + (lane & 1)];
+                    ne1 = eq[4 * y + 2 + (lane & 1)];
+                }
+            }
+        }
+        const uint64_t* evc = ev + buf * nev;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const size_t y = ybase + 2 * g + h;
             if (y < half && live_k) {
-                const ulonglong2 av2 = *reinterpret_cast<const ulonglong2*>(pa + 2 * y);
-                const ulonglong2 bv2 = *reinterpret_cast<const ulonglong2*>(pb + 2 * y);
-                const uint64_t a0 = gl::canon(av2.x), a1 = gl::canon(av2.y), b0 = gl::canon(bv2.x), b1 = gl::canon(bv2.y);
-                const uint64_t da = gl::sub_canon(a1, a0), db = gl::sub_canon(b1, b0);
-                uint64_t va = a0, vb = b0;
-                const uint64_t* e = ev + (2 * g + h) * 8;
-#pragma unroll
-                for (int c = 0; c < NC; c++) {
-                    const uint64_t pr = gl::mul(va, vb);
-                    gl::acc_mul(A[c][0], e[2 * c], pr);
-                    gl::acc_mul(A[c][1], e[2 * c + 1], pr);
-                    va = c == 0 ? a1 : gl::add_c(va, da);
-                    vb = c == 0 ? b1 : gl::add_c(vb, db);
-                }
+                const uint64_t a0 = gl::canon(ca[h].x), a1 = gl::canon(ca[h].y), b0 = gl::canon(cb[h].x), b1 = gl::canon(cb[h].y);
+                const ulonglong2 E = *reinterpret_cast<const ulonglong2*>(evc + (2 * g + h) * 2);
+                const uint64_t p0 = gl::mul(a0, b0), p1 = gl::mul(a1, b1);
+                const uint64_t p2 = gl::mul(gl::sub_canon(a1, a0), gl::sub_canon(b1, b0));
+                gl::acc_mul(A[0][0], E.x, p0); gl::acc_mul(A[0][1], E.y, p0);
+                gl::acc_mul(A[1][0], E.x, p1); gl::acc_mul(A[1][1], E.y, p1);
+                gl::acc_mul(A[2][0], E.x, p2); gl::acc_mul(A[2][1], E.y, p2);
             }
+        }
+        if (more) {
+            uint64_t* evn = ev + (buf ^ 1) * nev;
+            if (one_per_lane) {
+                if (lane < nev) evn[lane] = (ynext + (lane >> 1)) < half ? gl::add_c(ne0, ne1) : 0;
+            } else {
+                weight_fill(ynext, evn);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) { ca[h] = na[h]; cb[h] = nb[h]; }
         }
         __syncwarp();
     }
@@ -215,12 +254,7 @@ fold_message_kernel(const uint64_t* __restrict__ eq_in, uint64_t* __restrict__ e
             gl::e2acc_mul(q2, E2{gl::sub_canon(fa1.c0, fa0.c0), gl::sub_canon(fa1.c1, fa0.c1)},
                           E2{gl::sub_canon(fb1.c0, fb0.c0), gl::sub_canon(fb1.c1, fb0.c1)});
         }
-        // Q(c) = Q(0) + c L + c^2 Q2 with L = Q(1) - Q(0) - Q2
         const E2 Q0 = gl::e2acc_reduce(q0), Q1 = gl::e2acc_reduce(q1), Q2 = gl::e2acc_reduce(q2);
-        const E2 t = gl::e2_add(Q1, Q2);                        // Q1 + Q2
-        const E2 u = gl::e2_add(t, Q2);                         // Q1 + 2 Q2
-        const E2 Qc2 = gl::e2_sub(gl::e2_add(t, t), Q0);        // 2 Q1 + 2 Q2 - Q0
-        const E2 Qc3 = gl::e2_sub(gl::e2_sub(gl::e2_add(gl::e2_add(u, u), u), Q0), Q0);  // 3 Q1 + 6 Q2 - 2 Q0
         const ulonglong2* pe = reinterpret_cast<const ulonglong2*>(eq_in + 8 * y);
         const ulonglong2 e0 = pe[0], e1 = pe[1], e2v = pe[2], e3 = pe[3];
         const E2 g0 = gl::e2_canon(gl::e2_fma_pre(rp, E2{gl::sub_canon(e1.x, e0.x), gl::sub_canon(e1.y, e0.y)}, E2{e0.x, e0.y}));
@@ -228,12 +262,10 @@ fold_message_kernel(const uint64_t* __restrict__ eq_in, uint64_t* __restrict__ e
         ulonglong2* oe = reinterpret_cast<ulonglong2*>(eq_out + 4 * y);
         oe[0] = make_ulonglong2(g0.c0, g0.c1);
         oe[1] = make_ulonglong2(g1.c0, g1.c1);
-        const E2 de = E2{gl::sub_canon(g1.c0, g0.c0), gl::sub_canon(g1.c1, g0.c1)};
-        const E2 ve2 = gl::e2_add(g1, de), ve3 = gl::e2_add(ve2, de);
-        m[0] = gl::e2_add(m[0], gl::e2_mul_lazy(g0, Q0));
-        m[1] = gl::e2_add(m[1], gl::e2_mul_lazy(g1, Q1));
-        m[2] = gl::e2_add(m[2], gl::e2_mul_lazy(ve2, Qc2));
-        m[3] = gl::e2_add(m[3], gl::e2_mul_lazy(ve3, Qc3));
+        const E2 Ew = E2{gl::add_c(g0.c0, g1.c0), gl::add_c(g0.c1, g1.c1)};
+        m[0] = gl::e2_add(m[0], gl::e2_mul_lazy(Ew, Q0));
+        m[1] = gl::e2_add(m[1], gl::e2_mul_lazy(Ew, Q1));
+        m[2] = gl::e2_add(m[2], gl::e2_mul_lazy(Ew, Q2));
     }
     finish_message<FE>(m, partial, counter, final_out);
 }

@@ -28,39 +28,82 @@ GLF uint64_t umulhi(uint64_t a, uint64_t b) {
 constexpr uint64_t P = 0xFFFFFFFF00000001ULL;
 constexpr uint64_t EPS = 0xFFFFFFFFULL;  // 2^64 mod p
 
-GLF uint64_t canon(uint64_t x) { return x >= P ? x - P : x; }
+// The integer datapath of an SM issues about one 32-bit operation per lane every
+// two cycles whatever the operation, so the cost of field arithmetic is its
+// instruction count (measured: 0.57 warp instructions per cycle and scheduler for
+// any mix of additions, logic and multiply-adds). The device forms below use the
+// carry flag and one multiply-add for the +-EPS repair: canon 4 instructions,
+// add_c 4, add 8, sub_c 5, sub 9, where the comparison forms compile to 9 - 19.
+#ifdef __CUDA_ARCH__
+// carry of a + b and the wrapped sum
+__device__ __forceinline__ uint64_t add_cc(uint64_t a, uint64_t b, uint32_t& carry) {
+    uint64_t r;
+    asm("add.cc.u64 %0, %2, %3;\n\taddc.u32 %1, 0, 0;" : "=l"(r), "=r"(carry) : "l"(a), "l"(b));
+    return r;
+}
+// x + k * EPS mod 2^64 (one multiply-add)
+__device__ __forceinline__ uint64_t plus_eps(uint64_t x, uint32_t k) {
+    uint64_t r;
+    asm("mad.wide.u32 %0, %1, 0xFFFFFFFF, %2;" : "=l"(r) : "r"(k), "l"(x));
+    return r;
+}
+#endif
 
-// a + b for loose a, b. Each wrap past 2^64 is worth +EPS; a second wrap is only
-// possible when both operands are at or above p.
+// x >= p exactly when x + EPS wraps; then x - p = x + EPS - 2^64.
+GLF uint64_t canon(uint64_t x) {
+#ifdef __CUDA_ARCH__
+    uint32_t c;
+    (void)add_cc(x, EPS, c);
+    return plus_eps(x, c);
+#else
+    return x >= P ? x - P : x;
+#endif
+}
+
+// a + b where b < p: one wrap at most, and the repaired sum stays below 2^64.
+GLF uint64_t add_c(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint32_t c;
+    uint64_t s = add_cc(a, b, c);
+    return plus_eps(s, c);
+#else
+    uint64_t s = a + b;
+    return s < a ? s + EPS : s;
+#endif
+}
+
+// a + b for loose a, b. The wrapped sum is made canonical first, so the repair
+// of the wrap (+ EPS) cannot wrap again.
 GLF uint64_t add(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint32_t c;
+    uint64_t s = add_cc(a, b, c);
+    return plus_eps(canon(s), c);
+#else
     uint64_t s = a + b;
     if (s < a) {
         s += EPS;
         if (s < EPS) s += EPS;
     }
     return s;
+#endif
 }
 
-// a + b where b < p: one correction suffices.
-GLF uint64_t add_c(uint64_t a, uint64_t b) {
-    uint64_t s = a + b;
-    return s < a ? s + EPS : s;
-}
-
-GLF uint64_t sub(uint64_t a, uint64_t b) {
-    uint64_t d = a - b;
-    if (a < b) {
-        uint64_t e = d - EPS;
-        d = (d < EPS) ? e - EPS : e;
-    }
-    return d;
-}
-
-// a - b where b < p.
+// a - b where b < p: a borrow is repaired by - EPS, which cannot underflow
+// because the wrapped difference exceeds 2^64 - p = EPS.
 GLF uint64_t sub_c(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint64_t r;
+    uint32_t m;
+    asm("sub.cc.u64 %0, %2, %3;\n\tsubc.u32 %1, 0, 0;" : "=l"(r), "=r"(m) : "l"(a), "l"(b));
+    return r - (uint64_t)m;
+#else
     uint64_t d = a - b;
     return a < b ? d - EPS : d;
+#endif
 }
+
+GLF uint64_t sub(uint64_t a, uint64_t b) { return sub_c(a, canon(b)); }
 
 GLF uint64_t neg(uint64_t a) { return sub(0, a); }
 
@@ -204,56 +247,71 @@ GLF void mul128(uint64_t x, uint64_t y, uint64_t& lo, uint64_t& hi) {
 #endif
 }
 
-// top : hi : lo, top < 2^32 (room for 2^32 products).
+// Five 32-bit limbs, a4 the top (room for 2^32 products).
 struct Acc {
-    uint64_t lo, hi;
-    uint32_t top;
+    uint32_t a0, a1, a2, a3, a4;
 };
-GLF Acc acc_zero() { return Acc{0, 0, 0}; }
+GLF Acc acc_zero() { return Acc{0, 0, 0, 0, 0}; }
+GLF Acc acc_from(uint64_t v) { return Acc{lo32(v), hi32(v), 0, 0, 0}; }
 GLF void acc_add128(Acc& s, uint64_t lo, uint64_t hi) {
 #ifdef __CUDA_ARCH__
-    asm("add.cc.u64 %0, %0, %3;\n\taddc.cc.u64 %1, %1, %4;\n\taddc.u32 %2, %2, 0;"
-        : "+l"(s.lo), "+l"(s.hi), "+r"(s.top)
-        : "l"(lo), "l"(hi));
+    asm("add.cc.u32 %0, %0, %5;\n\taddc.cc.u32 %1, %1, %6;\n\taddc.cc.u32 %2, %2, %7;\n\taddc.cc.u32 %3, %3, %8;\n\t"
+        "addc.u32 %4, %4, 0;"
+        : "+r"(s.a0), "+r"(s.a1), "+r"(s.a2), "+r"(s.a3), "+r"(s.a4)
+        : "r"(lo32(lo)), "r"(hi32(lo)), "r"(lo32(hi)), "r"(hi32(hi)));
 #else
-    unsigned __int128 cur = ((unsigned __int128)s.hi << 64) | s.lo, add = ((unsigned __int128)hi << 64) | lo;
+    unsigned __int128 cur = ((unsigned __int128)pack64(s.a2, s.a3) << 64) | pack64(s.a0, s.a1);
+    unsigned __int128 add = ((unsigned __int128)hi << 64) | lo;
     unsigned __int128 r = cur + add;
-    if (r < cur) s.top++;
-    s.lo = (uint64_t)r;
-    s.hi = (uint64_t)(r >> 64);
+    if (r < cur) s.a4++;
+    s.a0 = (uint32_t)r; s.a1 = (uint32_t)(r >> 32); s.a2 = (uint32_t)(r >> 64); s.a3 = (uint32_t)(r >> 96);
 #endif
 }
 GLF void acc_add(Acc& s, uint64_t v) { acc_add128(s, v, 0); }
+// s += x * y: the even columns x0 y0, x1 y1 in one carry chain, then the two
+// cross products (13 multiply-adds and carry additions in all).
 GLF void acc_mul(Acc& s, uint64_t x, uint64_t y) {
+#ifdef __CUDA_ARCH__
+    asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
+        "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
+        "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
+        "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
+        "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
+        "addc.cc.u32 %3, %3, 0;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
+        "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
+        "addc.cc.u32 %3, %3, 0;\n\t"
+        "addc.u32 %4, %4, 0;"
+        : "+r"(s.a0), "+r"(s.a1), "+r"(s.a2), "+r"(s.a3), "+r"(s.a4)
+        : "r"(lo32(x)), "r"(hi32(x)), "r"(lo32(y)), "r"(hi32(y)));
+#else
     uint64_t lo, hi;
     mul128(x, y, lo, hi);
     acc_add128(s, lo, hi);
+#endif
 }
-// s mod p for top < 2^8, loose result. 2^128 = -2^32 (mod p), so the top limb joins
-// the subtrahend of reduce_limbs: B = z2 + z3 + 2^32 top < 2^41, and the repair
-// of a borrow still cannot underflow (the wrapped value exceeds 2^64 - 2^41).
+// s mod p for a top limb below 2^8, loose result. 2^128 = -2^32 (mod p), so the top
+// limb joins the subtrahend of reduce_limbs: B = z2 + z3 + 2^32 top < 2^41, and the
+// repair of a borrow still cannot underflow (the wrapped value exceeds 2^64 - 2^41).
 GLF uint64_t acc_reduce(const Acc& s) {
-    const uint32_t z0 = lo32(s.lo), z1 = hi32(s.lo), z2 = lo32(s.hi), z3 = hi32(s.hi);
-    uint64_t A = madwide(z2, 1u, (uint64_t)z1);
-    uint64_t B0 = madwide(z3, 1u, (uint64_t)z2);
-    uint64_t B = pack64(lo32(B0), hi32(B0) + s.top);
-    uint64_t W = madwide(hi32(A), 0xFFFFFFFFu, pack64(z0, lo32(A)));
+    uint64_t A = madwide(s.a2, 1u, (uint64_t)s.a1);
+    uint64_t B0 = madwide(s.a3, 1u, (uint64_t)s.a2);
+    uint64_t B = pack64(lo32(B0), hi32(B0) + s.a4);
+    uint64_t W = madwide(hi32(A), 0xFFFFFFFFu, pack64(s.a0, lo32(A)));
     uint32_t m;
     uint64_t R = sub_borrow(W, B, m);
     return R - (uint64_t)m;
 }
-
 // s mod p for any top limb (long-running accumulators): top 2^128 = -top 2^32.
 GLF uint64_t acc_reduce_wide(const Acc& s) {
-    return sub(reduce128(s.lo, s.hi), (uint64_t)s.top << 32);
+    return sub(reduce_limbs(s.a0, s.a1, s.a2, s.a3), (uint64_t)s.a4 << 32);
 }
 
 // a - b for canonical a, b; canonical result (one borrow repair: + p = - EPS mod 2^64).
-GLF uint64_t sub_canon(uint64_t a, uint64_t b) {
-    uint32_t m;
-    uint64_t d = sub_borrow(a, b, m);
-    return d - (uint64_t)m;
-}
+GLF uint64_t sub_canon(uint64_t a, uint64_t b) { return sub_c(a, b); }
 
 // ---------------------------------------------------------------------------
 // Quadratic extension, X^2 = 7. Stored as (c0, c1), two consecutive u64.
@@ -283,7 +341,7 @@ struct E2Pre {
 GLF E2Pre e2_pre(E2 r) { return E2Pre{canon(r.c0), canon(r.c1), canon(mul_small(canon(r.c1), 7))}; }
 // a + r * d
 GLF E2 e2_fma_pre(E2Pre r, E2 d, E2 a) {
-    Acc s0 = Acc{a.c0, 0, 0}, s1 = Acc{a.c1, 0, 0};
+    Acc s0 = acc_from(a.c0), s1 = acc_from(a.c1);
     acc_mul(s0, r.c0, d.c0);
     acc_mul(s0, r.c1w, d.c1);
     acc_mul(s1, r.c0, d.c1);
@@ -293,7 +351,7 @@ GLF E2 e2_fma_pre(E2Pre r, E2 d, E2 a) {
 GLF E2 e2_mul_pre(E2Pre r, E2 d) { return e2_fma_pre(r, d, E2{0, 0}); }
 // a + r * d for a base-field d
 GLF E2 e2_fma_pre_base(E2Pre r, uint64_t d, uint64_t a) {
-    Acc s0 = Acc{a, 0, 0}, s1 = acc_zero();
+    Acc s0 = acc_from(a), s1 = acc_zero();
     acc_mul(s0, r.c0, d);
     acc_mul(s1, r.c1, d);
     return E2{acc_reduce(s0), acc_reduce(s1)};

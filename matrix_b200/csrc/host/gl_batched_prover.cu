@@ -30,6 +30,7 @@ public:
         if (!d_a || !d_b || !h_eq_scale || K < 1 || K > bt::MAX_K || n_loc < 1 || n_loc > 34) return MB_ERR_ARG;
         if (n_loc > 0 && !h_point_low) return MB_ERR_ARG;
         K_ = K; n_loc_ = n_loc; n_ = (size_t)1 << n_loc; round_ = 0; have_msg_ = false; have_alpha_ = false; have_inst_ = false;
+        pt_.assign(h_point_low, h_point_low + 2 * (size_t)n_loc);
         a0_ = d_a;  // the caller's tables are read in place during round 0 and never written
         b0_ = d_b;
         size_t half = n_ / 2, quarter = n_ >= 4 ? n_ / 4 : 1;
@@ -70,7 +71,9 @@ public:
         if (have_inst_) return MB_OK;
         const size_t half = n_ / 2;
         dim3 grid(grid_inst_, (K_ + 31) / 32);
-        const size_t smem = sizeof(uint64_t) * 8 * (size_t)(2 * (32 / Kp_)) * 8;
+        const size_t smem = sizeof(uint64_t) * 8 * 2 * (size_t)(2 * (32 / Kp_)) * 2;
+        if (smem > 48 * 1024)
+            MB_CUDA(cudaFuncSetAttribute(bt::instance_messages_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         {
             MB_KERNEL("batched_instance_messages");
             bt::instance_messages_kernel<<<grid, 256, smem, MB_STREAM>>>(eq0_, a0_, b0_, K_, Kp_, n_, half, partial_);
@@ -86,13 +89,34 @@ public:
         return MB_OK;
     }
 
+    // m(0..3) = lambda(c) T(c) from T(0), T(1) and the leading coefficient T2 (six words) for the
+    // variable bound in `round`: lambda(c) = (1 - t) + c (2 t - 1), T(2) = 2 T(1) + 2 T2 - T(0),
+    // T(3) = 3 T(1) + 6 T2 - 2 T(0).
+    void expand_message(const uint64_t* t6, int round, gl::E2 (&out)[4]) const {
+        const gl::E2 T0{t6[0], t6[1]}, T1{t6[2], t6[3]}, T2{t6[4], t6[5]};
+        const gl::E2 t{gl::canon(pt_[2 * (size_t)round]), gl::canon(pt_[2 * (size_t)round + 1])};
+        const gl::E2 s12 = gl::e2_add(T1, T2), s122 = gl::e2_add(s12, T2);
+        gl::E2 T[4] = {T0, T1, gl::e2_sub(gl::e2_add(s12, s12), T0),
+                       gl::e2_sub(gl::e2_sub(gl::e2_add(gl::e2_add(s122, s122), s122), T0), T0)};
+        gl::E2 lam = gl::e2_sub(gl::E2{1, 0}, t);                 // lambda(0) = 1 - t
+        const gl::E2 step = gl::e2_sub(gl::e2_add(t, t), gl::E2{1, 0});  // 2 t - 1
+        for (int c = 0; c < 4; c++) {
+            out[c] = gl::e2_canon(gl::e2_mul(lam, T[c]));
+            lam = gl::e2_add(lam, step);
+        }
+    }
+
     // Local share of the per-instance claims s_k = m_k(0) + m_k(1) (K extension elements).
     int claims(uint64_t* h_out) {
         int rc = instance_messages();
         if (rc != MB_OK) return rc;
-        for (int k = 0; k < K_; k++)
-            for (int comp = 0; comp < 2; comp++)
-                h_out[2 * k + comp] = gl::canon(gl::add(inst_[8 * (size_t)k + comp], inst_[8 * (size_t)k + 2 + comp]));
+        for (int k = 0; k < K_; k++) {
+            gl::E2 m[4];
+            expand_message(inst_.data() + 2 * bt::NC * (size_t)k, 0, m);
+            const gl::E2 s = gl::e2_canon(gl::e2_add(m[0], m[1]));
+            h_out[2 * k] = s.c0;
+            h_out[2 * k + 1] = s.c1;
+        }
         return MB_OK;
     }
 
@@ -118,21 +142,29 @@ public:
             // sum_k alpha^k m_k(c) from the per-instance messages
             int rc = instance_messages();
             if (rc != MB_OK) return rc;
-            for (int c = 0; c < bt::NC; c++) {
-                gl::E2 acc{0, 0};
-                for (int k = 0; k < K_; k++)
-                    acc = gl::e2_add(acc, gl::e2_mul(gl::E2{pows_[2 * k], pows_[2 * k + 1]},
-                                                     gl::E2{inst_[8 * (size_t)k + 2 * c], inst_[8 * (size_t)k + 2 * c + 1]}));
-                acc = gl::e2_canon(acc);
-                h_msg[2 * c] = acc.c0;
-                h_msg[2 * c + 1] = acc.c1;
+            gl::E2 acc[4] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+            for (int k = 0; k < K_; k++) {
+                gl::E2 m[4];
+                expand_message(inst_.data() + 2 * bt::NC * (size_t)k, 0, m);
+                const gl::E2 w{pows_[2 * k], pows_[2 * k + 1]};
+                for (int c = 0; c < 4; c++) acc[c] = gl::e2_add(acc[c], gl::e2_mul(w, m[c]));
+            }
+            for (int c = 0; c < 4; c++) {
+                acc[c] = gl::e2_canon(acc[c]);
+                h_msg[2 * c] = acc[c].c0;
+                h_msg[2 * c + 1] = acc[c].c1;
             }
             return MB_OK;
         }
         if (!have_msg_) return MB_ERR_ARG;
-        MB_CUDA(cudaMemcpyAsync(h_, msg_dev_, 64, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaMemcpyAsync(h_, msg_dev_, 16 * bt::NC, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
-        std::memcpy(h_msg, h_, 64);
+        gl::E2 m[4];
+        expand_message(h_, round_, m);
+        for (int c = 0; c < 4; c++) {
+            h_msg[2 * c] = m[c].c0;
+            h_msg[2 * c + 1] = m[c].c1;
+        }
         return MB_OK;
     }
 
@@ -208,7 +240,7 @@ private:
     }
     int K_ = 0, Kp_ = 1, n_loc_ = 0, round_ = 0, grid_max_ = 0, grid_inst_ = 0;
     bool have_inst_ = false;
-    std::vector<uint64_t> inst_, pows_;
+    std::vector<uint64_t> inst_, pows_, pt_;
     uint64_t *wtab_dev_ = nullptr, *inst_dev_ = nullptr;
     size_t n_ = 0, ab_stride_ = 0;
     bool have_msg_ = false, have_alpha_ = false;

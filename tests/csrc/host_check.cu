@@ -36,7 +36,7 @@ void hc_aext2_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) {
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
 // sum_i x[i] * y[i] + c through the lazy accumulator
 uint64_t hc_gl_dot(const uint64_t* x, const uint64_t* y, int n, uint64_t c) {
-    gl::Acc s = gl::Acc{c, 0, 0};
+    gl::Acc s = gl::acc_from(c);
     for (int i = 0; i < n; i++) gl::acc_mul(s, x[i], y[i]);
     return gl::canon(gl::acc_reduce(s));
 }

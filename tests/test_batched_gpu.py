@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("K,nv,g_bits", [(1, 1, 0), (1, 2, 0), (2, 3, 0), (3, 6, 0), (16, 10, 0), (5, 14, 0),
-                                         (2, 5, 1), (3, 9, 2), (16, 12, 3), (4, 4, 3)])
+                                         (2, 5, 1), (3, 9, 2), (16, 12, 3), (4, 4, 3),
+                                         (33, 8, 0), (64, 7, 1), (8, 17, 0), (1, 15, 0), (16, 18, 1)])
 def test_batched_sumcheck_matches_oracle(K, nv, g_bits):
     from oracle import pyoracle
     lib = load_gl()
