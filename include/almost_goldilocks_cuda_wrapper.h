@@ -41,6 +41,43 @@ int agl_batch_mul_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
 int agl_batch_inverse_ffi(const uint64_t* a, uint64_t* r, int n);
 int aext2_batch_mul_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
 int aext2_batch_inverse_ffi(const uint64_t* a, uint64_t* r, int n);
+/* ffi.rs:106-138,687: the remaining element-wise operations, asynchronous on the caller's stream */
+int agl_batch_div_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int agl_batch_neg_ffi(const uint64_t* a, uint64_t* r, int n);
+int agl_batch_square_ffi(const uint64_t* a, uint64_t* r, int n);
+int agl_batch_double_ffi(const uint64_t* a, uint64_t* r, int n);
+int agl_batch_mul_scalar_ffi(uint64_t scalar, const uint64_t* a, uint64_t* r, int n);
+int agl_batch_exp_ffi(const uint64_t* a, uint64_t exp, uint64_t* r, int n);
+int aext2_batch_add_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int aext2_batch_sub_ffi(const uint64_t* a, const uint64_t* b, uint64_t* r, int n);
+int aext2_batch_neg_ffi(const uint64_t* a, uint64_t* r, int n);
+int aext2_batch_square_ffi(const uint64_t* a, uint64_t* r, int n);
+int aext2_batch_frobenius_ffi(const uint64_t* a, uint64_t* r, int n);
+int aext2_batch_conjugate_ffi(const uint64_t* a, uint64_t* r, int n);
+int aext2_batch_mul_scalar_ffi(uint64_t scalar, const uint64_t* a, uint64_t* r, int n);
+int aext2_batch_exp_ffi(const uint64_t* a, uint64_t exp, uint64_t* r, int n);
+int aext2_scale_accumulate_ffi(uint64_t scalar_c0, uint64_t scalar_c1, const uint64_t* src, uint64_t* acc, int n);
+int agl_to_aext2_batch_ffi(const uint64_t* input, uint64_t* output, int n);
+int aext2_to_agl_batch_ffi(const uint64_t* input, uint64_t* output, int n);
+int agl_zero_buffer_ffi(uint64_t* d_buf, size_t n);
+int agl_bit_permute_ffi(const uint64_t* d_input, uint64_t* d_output, const int* d_perm_map, int n_bits, int total);
+
+/* ---- streams, copies, pool: ffi.rs:61-64,77-100,342-350 (wrapper.cu:259-411) ---- */
+const char* agl_cuda_error_string(int code);
+int cuda_memset(void* dst, int value, size_t size);
+int cuda_sync_mine(void); /* the caller's own per-thread stream only */
+int cuda_stream_create(void** stream);
+int cuda_stream_destroy(void* stream);
+int cuda_stream_synchronize(void* stream);
+int cuda_memcpy_dtod_async(void* dst, const void* src, size_t size, void* stream);
+int cuda_memcpy_htod_async(void* dst, const void* src, size_t size, void* stream);
+int cuda_memcpy_peer(void* dst, int dst_dev, const void* src, int src_dev, size_t size);
+int cuda_enable_peer_access(int peer);
+int cuda_pool_trim(size_t min_bytes_to_keep);
+size_t agl_cached_bytes(void);
+/* pageable host memory through two pinned 64 MiB buffers per device */
+int agl_d2h_staged(void* h_dst, const void* d_src, size_t bytes);
+int agl_h2d_staged(void* d_dst, const void* h_src, size_t bytes);
 
 /* ---- sumcheck: ffi.rs:221-263 (wrapper.cu:812-860); layouts as the Goldilocks twins ---- */
 int agl_sumcheck_round_message_ffi(const uint64_t* d_polys, uint64_t* d_partial, int d, size_t original_size,

@@ -29,6 +29,37 @@ int goldilocks_cuda_init(void);
 int poseidon2_cuda_init(void);
 int monolith_cuda_init(void);
 
+/* ---- element-wise batch operations: ffi.rs:31-58,165-285,629-655 (wrapper.cu:100-575,1807-1860,2446-2460).
+ * Device pointers, n elements (extension elements are two consecutive words), canonical outputs,
+ * asynchronous on the caller's stream like the reference's. Division and inversion map 0 to 0. ---- */
+int gl_batch_add(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int gl_batch_sub(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int gl_batch_mul(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int gl_batch_div(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int gl_batch_inverse(const uint64_t* d_a, uint64_t* d_result, int n);
+int gl_batch_neg(const uint64_t* d_a, uint64_t* d_result, int n);
+int gl_batch_square(const uint64_t* d_a, uint64_t* d_result, int n);
+int gl_batch_double(const uint64_t* d_a, uint64_t* d_result, int n);
+int gl_batch_mul_scalar(uint64_t scalar, const uint64_t* d_a, uint64_t* d_result, int n);
+int gl_batch_exp(const uint64_t* d_a, uint64_t exp, uint64_t* d_result, int n);
+int ext2_batch_add_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int ext2_batch_sub_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int ext2_batch_mul_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int ext2_batch_inverse_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext2_batch_neg_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext2_batch_square_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext2_batch_frobenius_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext2_batch_conjugate_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext2_batch_mul_scalar_ffi(uint64_t scalar, const uint64_t* d_a, uint64_t* d_result, int n);
+int ext2_batch_exp_ffi(const uint64_t* d_a, uint64_t exp, uint64_t* d_result, int n);
+/* acc[i] += scalar * src[i] */
+int ext2_scale_accumulate_ffi(uint64_t scalar_c0, uint64_t scalar_c1, const uint64_t* d_src, uint64_t* d_acc, int n);
+int gl_to_ext2_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+int ext2_to_gl_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+int gl_zero_buffer(uint64_t* d_buf, int n);
+/* out[new] = in[old] where bit b of new is bit d_perm_map[b] of old (wrapper.cu:1843-1860) */
+int bit_permute_gl_ffi(const uint64_t* d_input, uint64_t* d_output, const int* d_perm_map, int n_bits, int total);
+
 /* ---- memory: ffi.rs:17-25 (wrapper.cu:52-98) ---- */
 int cuda_malloc(void** ptr, size_t size);
 int cuda_free(void* ptr);

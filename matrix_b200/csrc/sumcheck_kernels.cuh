@@ -75,7 +75,7 @@ struct GlExt2 {
     }
     static __device__ __forceinline__ T add(T a, T b) { return gl::e2_add(a, b); }
     static __device__ __forceinline__ T sub(T a, T b) { return gl::e2_sub(a, b); }
-    static __device__ __forceinline__ T mul(T a, T b) { return gl::e2_mul(a, b); }
+    static __device__ __forceinline__ T mul(T a, T b) { return gl::e2_mul_lazy(a, b); }
     static __device__ __forceinline__ T zero() { return gl::E2{0, 0}; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
 };
@@ -219,11 +219,18 @@ struct FoldOp<F, F> {
         return F::add(a, F::mul(r, F::sub(b, a)));
     }
 };
+// Goldilocks: a + r (b - a) as two exact sums of products (the factor r with
+// 7 r.c1 precomputed is loop invariant), one reduction per component.
 template <>
 struct FoldOp<GlBase, GlExt2> {
     static __device__ __forceinline__ gl::E2 apply(uint64_t a, uint64_t b, gl::E2 r) {
-        uint64_t d = gl::sub(b, a);
-        return gl::E2{gl::add(a, gl::mul(r.c0, d)), gl::mul(r.c1, d)};
+        return gl::e2_fma_pre_base(gl::e2_pre(r), gl::sub(b, a), a);
+    }
+};
+template <>
+struct FoldOp<GlExt2, GlExt2> {
+    static __device__ __forceinline__ gl::E2 apply(gl::E2 a, gl::E2 b, gl::E2 r) {
+        return gl::e2_fma_pre(gl::e2_pre(r), gl::e2_sub(b, a), a);
     }
 };
 

@@ -73,6 +73,31 @@ _GL_SIGNATURES = {
     "poseidon2_merkle_layer_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "poseidon2_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "poseidon2_merkle_tree_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "gl_batch_add": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "gl_batch_sub": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "gl_batch_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "gl_batch_div": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "ext2_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "ext2_batch_sub_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "ext2_batch_mul_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "gl_batch_inverse": (c_int, [c_void_p, c_void_p, c_int]),
+    "gl_batch_neg": (c_int, [c_void_p, c_void_p, c_int]),
+    "gl_batch_square": (c_int, [c_void_p, c_void_p, c_int]),
+    "gl_batch_double": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext2_batch_inverse_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext2_batch_neg_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext2_batch_square_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext2_batch_frobenius_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext2_batch_conjugate_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "gl_to_ext2_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext2_to_gl_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "gl_batch_mul_scalar": (c_int, [c_u64, c_void_p, c_void_p, c_int]),
+    "ext2_batch_mul_scalar_ffi": (c_int, [c_u64, c_void_p, c_void_p, c_int]),
+    "gl_batch_exp": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
+    "ext2_batch_exp_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
+    "ext2_scale_accumulate_ffi": (c_int, [c_u64, c_u64, c_void_p, c_void_p, c_int]),
+    "gl_zero_buffer": (c_int, [c_void_p, c_int]),
+    "bit_permute_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "monolith_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "monolith_merkle_tree_ext2_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "monolith_permute_test_ffi": (c_int, [c_void_p, c_void_p]),
@@ -191,6 +216,39 @@ _AGL_SIGNATURES = {
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
+    "agl_batch_div_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "aext2_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "aext2_batch_sub_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "agl_batch_neg_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "agl_batch_square_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "agl_batch_double_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "aext2_batch_neg_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "aext2_batch_square_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "aext2_batch_frobenius_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "aext2_batch_conjugate_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "agl_to_aext2_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "aext2_to_agl_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "agl_batch_mul_scalar_ffi": (c_int, [c_u64, c_void_p, c_void_p, c_int]),
+    "aext2_batch_mul_scalar_ffi": (c_int, [c_u64, c_void_p, c_void_p, c_int]),
+    "agl_batch_exp_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
+    "aext2_batch_exp_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
+    "aext2_scale_accumulate_ffi": (c_int, [c_u64, c_u64, c_void_p, c_void_p, c_int]),
+    "agl_zero_buffer_ffi": (c_int, [c_void_p, c_size_t]),
+    "agl_bit_permute_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "agl_cuda_error_string": (ctypes.c_char_p, [c_int]),
+    "cuda_memset": (c_int, [c_void_p, c_int, c_size_t]),
+    "cuda_sync_mine": (c_int, []),
+    "cuda_stream_create": (c_int, [ctypes.POINTER(c_void_p)]),
+    "cuda_stream_destroy": (c_int, [c_void_p]),
+    "cuda_stream_synchronize": (c_int, [c_void_p]),
+    "cuda_memcpy_dtod_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "cuda_memcpy_htod_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "cuda_memcpy_peer": (c_int, [c_void_p, c_int, c_void_p, c_int, c_size_t]),
+    "cuda_enable_peer_access": (c_int, [c_int]),
+    "cuda_pool_trim": (c_int, [c_size_t]),
+    "agl_cached_bytes": (c_size_t, []),
+    "agl_d2h_staged": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "agl_h2d_staged": (c_int, [c_void_p, c_void_p, c_size_t]),
     "agl_monolith_permute_host": (c_int, [c_void_p]),
     "agl_monolith_round_constants": (c_int, [c_void_p]),
     "agl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
