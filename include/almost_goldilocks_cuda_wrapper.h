@@ -135,6 +135,20 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
 int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
                         uint64_t* d_out);
 
+/* ---- K = F_q[Theta]/(Theta^8 - 3) product sumcheck and table helpers: ffi.rs:65-75 (wrapper.cu:3815-3905;
+ * kernels cuda_almost_goldilocks/morpheus_piop.cuh:140-282; CPU zk-torch-4/src/morpheus/piop/mod.rs:785-840,
+ * field zk-torch-4/src/morpheus/field8.rs). Elements are 8 canonical words; tables live on the device,
+ * h_tabs / h_outs are host arrays of device pointers, challenges / points / sums are host words.
+ * -3: more than 6 tables or degree above 6 (or len < 4 for the fused form). ---- */
+int agl_mpiop_sc_round(const uint64_t* const* h_tabs, int ntab, uint64_t len, int d, uint64_t* h_out);
+int agl_mpiop_sc_fold(const uint64_t* d_in, uint64_t* d_out, uint64_t len, const uint64_t* h_r);
+int agl_mpiop_sc_fold_round(const uint64_t* const* h_tabs, uint64_t* const* h_outs, int ntab, uint64_t len,
+                            const uint64_t* h_r, int d, uint64_t* h_out);
+int agl_mpiop_eq(const uint64_t* h_point, int n, uint64_t* d_out);
+int agl_mpiop_eq_outer(const uint64_t* d_lo, int nlo, const uint64_t* d_hi, int nhi, uint64_t* d_out);
+int agl_mpiop_axpy(uint64_t* d_out, const uint64_t* d_in, uint64_t n, const uint64_t* h_c);
+int agl_mpiop_lift(const uint64_t* d_in, uint64_t n, uint64_t* d_out);
+
 /* ---- host side: Monolith over almost-Goldilocks and the transcript on it ----
  * The reference keeps these in Rust: permutation and SHA-256-derived round constants
  * zk-torch-4/src/crypto/monolith.rs:66-208, transcript zk-torch-4/src/transcript.rs:22-243 (width 12,

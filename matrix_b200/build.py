@@ -44,6 +44,7 @@ LIBRARIES = {
         "agl_wrapper.cu",
         "agl_ajtai.cu",
         "agl_batch.cu",
+        "agl_k8.cu",
         "host/agl_transcript.cu",
     ],
 }

@@ -63,6 +63,15 @@ GLF uint64_t reduce_limbs(uint32_t z0, uint32_t z1, uint32_t z2, uint32_t z3) {
 }
 GLF uint64_t reduce128(uint64_t lo, uint64_t hi) { return reduce_limbs(lo32(lo), hi32(lo), lo32(hi), hi32(hi)); }
 
+// An exact 160-bit sum of products (gl::Acc: the accumulation is integer
+// arithmetic, the same for both fields) mod q, top limb below 2^8, loose result:
+// 2^128 = c^2 = 63 2^32 + 992 (mod q) joins the two limb sums of reduce_limbs.
+GLF uint64_t acc_reduce(const gl::Acc& s) {
+    uint64_t L = madwide(s.a4, 992u, madwide(s.a3, 31u, madwide(s.a2, 31u, (uint64_t)s.a0)));
+    uint64_t H = madwide(s.a4, 63u, madwide(s.a3, 32u, madwide(s.a2, 1u, (uint64_t)s.a1)));
+    return reduce_limb_sums(L, H);
+}
+
 GLF uint64_t mul(uint64_t a, uint64_t b) { return reduce128(a * b, umulhi(a, b)); }
 GLF uint64_t sqr(uint64_t a) { return mul(a, a); }
 GLF uint64_t mul_small(uint64_t a, uint32_t k) {

@@ -1,0 +1,168 @@
+// C-ABI: the K = F_q[Theta]/(Theta^8 - 3) product sumcheck and its table helpers
+// (reference: almost-goldilocks-cuda-rs/src/ffi.rs:65-75, definitions
+// almost-goldilocks-cuda-rs/cuda/wrapper.cu:3815-3905; Rust callers
+// zk-torch-4/src/morpheus/piop/gpu.rs). Tables are device arrays of 64-byte
+// elements; challenges, points and sums are host arrays of 8 words per element.
+// The sums come back through one pinned copy; everything runs on the caller's
+// per-thread stream.
+#include <cstring>
+#include "agl_k8.cuh"
+
+using namespace mb;
+using namespace mb::k8;
+
+namespace {
+
+struct Scratch {
+    uint64_t* partial = nullptr;  // [grid][MAXTAB + 1][8]
+    uint64_t* sums = nullptr;     // [(MAXTAB + 1) * 8]
+    unsigned int* counter = nullptr;
+    int grid_cap = 0;
+    ~Scratch() {}
+};
+
+// Per host thread and device: partial rows for the largest grid, the sums and the ticket counter.
+int scratch_for(int grid, Scratch** out) {
+    static thread_local Scratch s[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MB_ERR_CUDA;
+    Scratch& sc = s[dev];
+    if (grid > sc.grid_cap) {
+        if (sc.partial) { pool_free(sc.partial); pool_free(sc.sums); }
+        const int cap = sm_count() * 8;
+        sc.grid_cap = grid > cap ? grid : cap;
+        const size_t row = (size_t)(MAXTAB + 1) * 8;
+        if (pool_alloc((void**)&sc.partial, sizeof(uint64_t) * row * sc.grid_cap) != cudaSuccess) return MB_ERR_CUDA;
+        if (pool_alloc((void**)&sc.sums, sizeof(uint64_t) * (row + 2)) != cudaSuccess) return MB_ERR_CUDA;
+        sc.counter = reinterpret_cast<unsigned int*>(sc.sums + row);
+        if (cudaMemsetAsync(sc.counter, 0, 2 * sizeof(uint64_t), MB_STREAM) != cudaSuccess) return MB_ERR_CUDA;
+    }
+    *out = &sc;
+    return MB_OK;
+}
+
+int fetch_sums(Scratch* sc, int d, uint64_t* h_out) {
+    uint64_t* h = pinned_scratch();  // 64 words; (d + 1) * 8 <= 56
+    if (!h) return MB_ERR_CUDA;
+    MB_CUDA(cudaMemcpyAsync(h, sc->sums, sizeof(uint64_t) * (size_t)(d + 1) * 8, cudaMemcpyDeviceToHost, MB_STREAM));
+    MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+    std::memcpy(h_out, h, sizeof(uint64_t) * (size_t)(d + 1) * 8);
+    return MB_OK;
+}
+
+Elem elem_from(const uint64_t* h) {
+    Elem e;
+    for (int i = 0; i < 8; i++) e.c[i] = h[i];
+    return e;
+}
+
+}  // namespace
+
+extern "C" {
+
+// h_out[(d + 1) * 8]: s[t] = sum_k prod_j (T_j[2k] + t (T_j[2k+1] - T_j[2k])), t = 0..d. -3: too many tables / degree.
+int agl_mpiop_sc_round(const uint64_t* const* h_tabs, int ntab, uint64_t len, int d, uint64_t* h_out) {
+    if (!h_tabs || !h_out || ntab < 1 || d < 0 || len < 2 || (len & 1)) return MB_ERR_ARG;
+    if (ntab > MAXTAB || d > MAXTAB) return -3;
+    Tabs T;
+    T.ntab = ntab;
+    for (int j = 0; j < MAXTAB; j++) T.t[j] = j < ntab ? h_tabs[j] : nullptr;
+    const uint64_t npairs = len / 2;
+    const int grid = grid_for(npairs * 8, 256, 4);
+    Scratch* sc;
+    int rc = scratch_for(grid, &sc);
+    if (rc != MB_OK) return rc;
+    {
+        MB_KERNEL("k8_sc_round");
+        sc_round_kernel<<<grid, 256, 0, MB_STREAM>>>(T, npairs, d, sc->partial, sc->counter, sc->sums);
+    }
+    if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+    return fetch_sums(sc, d, h_out);
+}
+
+// d_out[k] = d_in[2k] + r (d_in[2k+1] - d_in[2k]), k < len / 2.
+int agl_mpiop_sc_fold(const uint64_t* d_in, uint64_t* d_out, uint64_t len, const uint64_t* h_r) {
+    if (!d_in || !d_out || !h_r || len < 2 || (len & 1)) return MB_ERR_ARG;
+    const uint64_t nout = len / 2;
+    {
+        MB_KERNEL("k8_sc_fold");
+        sc_fold_kernel<<<grid_for(nout * 8, 256, 4), 256, 0, MB_STREAM>>>(d_in, d_out, nout, elem_from(h_r));
+    }
+    return finish_async();
+}
+
+// Folds the ntab tables (length len) with r into h_outs (length len / 2) and returns the d + 1 sums of the
+// next round over the folded tables.
+int agl_mpiop_sc_fold_round(const uint64_t* const* h_tabs, uint64_t* const* h_outs, int ntab, uint64_t len,
+                            const uint64_t* h_r, int d, uint64_t* h_out) {
+    if (!h_tabs || !h_outs || !h_r || !h_out || ntab < 1 || d < 0) return MB_ERR_ARG;
+    if (ntab > MAXTAB || d > MAXTAB || len < 4 || (len & 3)) return -3;
+    Tabs T;
+    OutTabs O;
+    T.ntab = ntab;
+    for (int j = 0; j < MAXTAB; j++) {
+        T.t[j] = j < ntab ? h_tabs[j] : nullptr;
+        O.t[j] = j < ntab ? h_outs[j] : nullptr;
+    }
+    const uint64_t nquads = len / 4;
+    const int grid = grid_for(nquads * 8, 256, 4);
+    Scratch* sc;
+    int rc = scratch_for(grid, &sc);
+    if (rc != MB_OK) return rc;
+    {
+        MB_KERNEL("k8_sc_fold_round");
+        sc_fold_round_kernel<<<grid, 256, 0, MB_STREAM>>>(T, O, nquads, elem_from(h_r), d, sc->partial, sc->counter, sc->sums);
+    }
+    if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
+    return fetch_sums(sc, d, h_out);
+}
+
+// d_out[2^n] = eq(x, point), bit j of the index matching point[j] (field8.rs:160-182).
+int agl_mpiop_eq(const uint64_t* h_point, int n, uint64_t* d_out) {
+    if (!d_out || n < 0 || n > 30 || (n > 0 && !h_point)) return MB_ERR_ARG;
+    const uint64_t one[8] = {1, 0, 0, 0, 0, 0, 0, 0};
+    uint64_t* tmp = nullptr;
+    if (n > 0 && pool_alloc((void**)&tmp, ((size_t)1 << n) * 64) != cudaSuccess) return MB_ERR_CUDA;
+    uint64_t* bufs[2] = {d_out, tmp};
+    int cur = (n % 2 == 0) ? 0 : 1;  // the last step lands in d_out
+    int rc = MB_OK;
+    if (cudaMemcpyAsync(bufs[cur], one, 64, cudaMemcpyHostToDevice, MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
+    if (cudaStreamSynchronize(MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;  // `one` is on this stack frame
+    uint64_t half = 1;
+    for (int j = n - 1; j >= 0 && rc == MB_OK; j--) {
+        MB_KERNEL("k8_eq_double");
+        eq_double_kernel<<<grid_for(half * 8, 256, 4), 256, 0, MB_STREAM>>>(bufs[cur], bufs[cur ^ 1], half, elem_from(h_point + 8 * j));
+        cur ^= 1;
+        half <<= 1;
+    }
+    if (rc == MB_OK) rc = finish_async();
+    pool_free(tmp);
+    return rc;
+}
+
+int agl_mpiop_eq_outer(const uint64_t* d_lo, int nlo, const uint64_t* d_hi, int nhi, uint64_t* d_out) {
+    if (!d_lo || !d_hi || !d_out || nlo < 0 || nhi < 0 || nlo + nhi > 30) return MB_ERR_ARG;
+    const uint64_t n = (uint64_t)1 << (nlo + nhi);
+    MB_KERNEL("k8_eq_outer");
+    eq_outer_kernel<<<grid_for(n * 8, 256, 4), 256, 0, MB_STREAM>>>(d_lo, nlo, d_hi, n, d_out);
+    return finish_async();
+}
+
+// d_out[x] += c * d_in[x]
+int agl_mpiop_axpy(uint64_t* d_out, const uint64_t* d_in, uint64_t n, const uint64_t* h_c) {
+    if (!d_out || !d_in || !h_c) return MB_ERR_ARG;
+    if (n == 0) return MB_OK;
+    MB_KERNEL("k8_axpy");
+    axpy_kernel<<<grid_for(n * 8, 256, 4), 256, 0, MB_STREAM>>>(d_out, d_in, n, elem_from(h_c));
+    return finish_async();
+}
+
+int agl_mpiop_lift(const uint64_t* d_in, uint64_t n, uint64_t* d_out) {
+    if (!d_in || !d_out) return MB_ERR_ARG;
+    if (n == 0) return MB_OK;
+    MB_KERNEL("k8_lift");
+    lift_kernel<<<grid_for(n * 8, 256, 8), 256, 0, MB_STREAM>>>(d_in, n, d_out);
+    return finish_async();
+}
+
+}  // extern "C"

@@ -249,6 +249,13 @@ _AGL_SIGNATURES = {
     "agl_cached_bytes": (c_size_t, []),
     "agl_d2h_staged": (c_int, [c_void_p, c_void_p, c_size_t]),
     "agl_h2d_staged": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "agl_mpiop_sc_round": (c_int, [c_void_p, c_int, c_u64, c_int, c_void_p]),
+    "agl_mpiop_sc_fold": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
+    "agl_mpiop_sc_fold_round": (c_int, [c_void_p, c_void_p, c_int, c_u64, c_void_p, c_int, c_void_p]),
+    "agl_mpiop_eq": (c_int, [c_void_p, c_int, c_void_p]),
+    "agl_mpiop_eq_outer": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "agl_mpiop_axpy": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
+    "agl_mpiop_lift": (c_int, [c_void_p, c_u64, c_void_p]),
     "agl_monolith_permute_host": (c_int, [c_void_p]),
     "agl_monolith_round_constants": (c_int, [c_void_p]),
     "agl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),

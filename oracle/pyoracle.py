@@ -265,3 +265,33 @@ class merkle_hash:
 
     def __exit__(self, *a):
         load().oracle_set_merkle_hash(self.prev)
+
+
+# ---- K = F_q[Theta]/(Theta^8 - 3) and its product sumcheck -----------------------------
+_SIGS.update({
+    "oracle_k8_add": (None, [vp, vp, vp]),
+    "oracle_k8_sub": (None, [vp, vp, vp]),
+    "oracle_k8_mul": (None, [vp, vp, vp]),
+    "oracle_k8_eq_table": (None, [vp, ci, vp]),
+    "oracle_k8_sc_round": (None, [vp, ci, sz, ci, vp]),
+    "oracle_k8_sc_fold": (None, [vp, sz, vp, vp]),
+    "oracle_k8_axpy": (None, [vp, vp, sz, vp]),
+})
+
+
+def k8_sc_round(tabs, d):
+    """tabs: list of uint64 arrays [len * 8]; returns the (d + 1) x 8 words of the round sums."""
+    import numpy as np
+    lib = load()
+    ptrs = (ctypes.c_void_p * len(tabs))(*[t.ctypes.data for t in tabs])
+    out = np.zeros((d + 1) * 8, dtype=np.uint64)
+    lib.oracle_k8_sc_round(ptrs, len(tabs), len(tabs[0]) // 8, d, out.ctypes.data)
+    return out
+
+
+def k8_sc_fold(tab, r):
+    import numpy as np
+    lib = load()
+    out = np.zeros(len(tab) // 2, dtype=np.uint64)
+    lib.oracle_k8_sc_fold(tab.ctypes.data, len(tab) // 8, np.ascontiguousarray(r, dtype=np.uint64).ctypes.data, out.ctypes.data)
+    return out
