@@ -125,6 +125,20 @@ int ajtai_commit_wide_ffi(const uint32_t* d_key, const uint64_t* d_z_wide, uint6
                           uint64_t* d_out);
 /* d_M[j][i][k], j < N (42 * 64 * 8 bytes per column) */
 int ajtai_materialize_m_ffi(const uint32_t* d_chacha_key, uint64_t* d_M, uint64_t N);
+/* ffi.rs:603-625: 13 ternary planes given as bit masks of the +1 / -1 coefficients, d_pos / d_neg[i * N_ring + j];
+ * d_out[13][42][64] (kernel cuda_almost_goldilocks/ajtai.cuh:1262-1370). The premat form reads a matrix made by
+ * ajtai_materialize_m_ffi. `chunk` is validated (-3) and otherwise ignored. */
+int ajtai_commit_ternary_ffi(const uint32_t* d_key, const uint64_t* d_pos, const uint64_t* d_neg, uint64_t N_ring, int chunk,
+                             uint64_t* d_out);
+int ajtai_commit_ternary_premat_ffi(const uint64_t* d_M, const uint64_t* d_pos, const uint64_t* d_neg, uint64_t N_ring,
+                                    int chunk, uint64_t* d_out);
+/* ffi.rs:649-655: K positions p in [0, 64 N), c_i = sum_p X^(p mod 64) M[i][p / 64]; d_out[42][64]
+ * (CPU twin cuda_almost_goldilocks/ajtai_cpu_reference.cuh:192-219) */
+int ajtai_commit_sparse_ffi(const uint32_t* d_key, const uint64_t* d_positions, uint64_t K, int chunk, uint64_t* d_out);
+/* ffi.rs:352-359: signed 16-bit coefficients d_wide[n_ring][64] to k_chunks <= 16 ternary planes (bit i of |v| goes to
+ * plane i of pos or neg by sign); *d_err = 1 when a coefficient needs more bits (almost_sumcheck_prover.cuh:447-478) */
+int aext2_wide_to_ternary_ffi(const int16_t* d_wide, uint64_t* d_pos, uint64_t* d_neg, int* d_err, size_t n_ring, int k_chunks);
+
 /* addition: signed 8-bit digit planes d_digits[(p*N + j)*64 + l] in [-128, 127], d_out[p][42][64];
  * scalar path, exact for any N */
 int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes,

@@ -19,8 +19,9 @@ uint64_t pick_cols_per_chunk(uint64_t N, int planes) {
 }
 
 template <int KIND>
-int commit_scalar(const uint32_t* d_key, const void* d_z, uint64_t N, int planes, uint64_t col_offset, uint64_t* d_out) {
-    if (!d_key || !d_z || !d_out || planes < 1 || planes > 64) return MB_ERR_ARG;
+int commit_scalar(const uint32_t* d_key, const void* d_z, uint64_t N, int planes, uint64_t col_offset, uint64_t* d_out,
+                  const uint64_t* d_premat = nullptr) {
+    if ((!d_key && !d_premat) || !d_z || !d_out || planes < 1 || planes > 64) return MB_ERR_ARG;
     const size_t width = (size_t)planes * KAPPA * D;
     if (N == 0) {
         MB_CUDA(cudaMemsetAsync(d_out, 0, width * sizeof(uint64_t), MB_STREAM));
@@ -33,7 +34,7 @@ int commit_scalar(const uint32_t* d_key, const void* d_z, uint64_t N, int planes
     {
         MB_KERNEL("ajtai_commit_scalar");
         dim3 grid((unsigned)chunks, (unsigned)planes);
-        commit_scalar_kernel<KIND><<<grid, 384, 0, MB_STREAM>>>(d_key, d_z, N, col_offset, cpc, partial);
+        commit_scalar_kernel<KIND><<<grid, 384, 0, MB_STREAM>>>(d_key, d_z, N, col_offset, cpc, partial, d_premat);
     }
     {
         MB_KERNEL("ajtai_reduce_chunks");
@@ -138,6 +139,86 @@ int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t 
     if (h_err == TC_ERR_TIMEOUT) return MB_ERR_CUDA;
     if (h_err == TC_ERR_DIGIT_RANGE) return MB_ERR_UNSUPPORTED;
     return MB_OK;
+}
+
+// ---- ternary planes, sparse positions (ffi.rs:352-359,603-625,649-655; wrapper.cu:959-969,1642-1699,1741-1758) ----
+namespace {
+constexpr int SPLIT_K = 13;  // ternary planes per witness (cuda_almost_goldilocks/ajtai.cuh commit_ternary_kernel)
+
+int expand_ternary(const uint64_t* d_pos, const uint64_t* d_neg, uint64_t N_ring, int8_t** d_digits) {
+    const size_t words = (size_t)SPLIT_K * N_ring;
+    if (pool_alloc((void**)d_digits, words * 64) != cudaSuccess) return MB_ERR_CUDA;
+    MB_KERNEL("ajtai_ternary_expand");
+    ternary_expand_kernel<<<grid_for(words * 4, 256, 8), 256, 0, MB_STREAM>>>(d_pos, d_neg, words, *d_digits);
+    return finish_async();
+}
+}  // namespace
+
+// 13 ternary planes: d_pos / d_neg[i * N_ring + j] are the bit masks of the +1 / -1 coefficients of ring
+// element j of plane i; d_out[13][42][64]. The planes are expanded to signed digits and committed on the
+// tensor cores (one matrix generation per four planes).
+int ajtai_commit_ternary_ffi(const uint32_t* d_key, const uint64_t* d_pos, const uint64_t* d_neg, uint64_t N_ring, int chunk,
+                             uint64_t* d_out) {
+    if (!valid_chunk(chunk)) return MB_ERR_UNSUPPORTED;
+    if (!d_key || !d_pos || !d_neg || !d_out) return MB_ERR_ARG;
+    if (N_ring == 0) return ajtai_commit_s8_ffi(d_key, reinterpret_cast<const int8_t*>(d_pos), 0, SPLIT_K, 0, d_out);
+    int8_t* d_digits = nullptr;
+    int rc = expand_ternary(d_pos, d_neg, N_ring, &d_digits);
+    if (rc == MB_OK) rc = ajtai_commit_s8_ffi(d_key, d_digits, N_ring, SPLIT_K, 0, d_out);
+    pool_free(d_digits);
+    return rc;
+}
+
+// The same against a matrix materialised by ajtai_materialize_m_ffi (d_M[j][i][k]).
+int ajtai_commit_ternary_premat_ffi(const uint64_t* d_M, const uint64_t* d_pos, const uint64_t* d_neg, uint64_t N_ring,
+                                    int chunk, uint64_t* d_out) {
+    if (!valid_chunk(chunk)) return MB_ERR_UNSUPPORTED;
+    if (!d_M || !d_pos || !d_neg || !d_out) return MB_ERR_ARG;
+    if (N_ring == 0) return commit_scalar<KIND_S8>(nullptr, d_pos, 0, SPLIT_K, 0, d_out, d_M);
+    int8_t* d_digits = nullptr;
+    int rc = expand_ternary(d_pos, d_neg, N_ring, &d_digits);
+    if (rc == MB_OK) rc = commit_scalar<KIND_S8>(nullptr, d_digits, N_ring, SPLIT_K, 0, d_out, d_M);
+    pool_free(d_digits);
+    return rc;
+}
+
+// d_wide[n_ring][64] signed 16-bit coefficients to k_chunks ternary planes; *d_err is set when a
+// coefficient does not fit k_chunks bits. More than 16 planes: -1 as in the reference.
+int aext2_wide_to_ternary_ffi(const int16_t* d_wide, uint64_t* d_pos, uint64_t* d_neg, int* d_err, size_t n_ring, int k_chunks) {
+    if (k_chunks > 16) return MB_ERR_CUDA;
+    if (!d_wide || !d_pos || !d_neg || !d_err || k_chunks < 1) return MB_ERR_ARG;
+    if (n_ring == 0) return MB_OK;
+    MB_KERNEL("wide_to_ternary");
+    wide_to_ternary_kernel<<<grid_for(n_ring, 128, 8), 128, 0, MB_STREAM>>>(d_wide, d_pos, d_neg, d_err, n_ring, k_chunks);
+    return finish_async();
+}
+
+// K positions p in [0, 64 N): c_i = sum_p X^(p mod 64) M[i][p / 64]; d_out[42][64].
+int ajtai_commit_sparse_ffi(const uint32_t* d_key, const uint64_t* d_positions, uint64_t K, int chunk, uint64_t* d_out) {
+    if (!valid_chunk(chunk)) return MB_ERR_UNSUPPORTED;
+    if (!d_key || !d_out || (!d_positions && K)) return MB_ERR_ARG;
+    const size_t width = (size_t)KAPPA * D;
+    if (K == 0) {
+        MB_CUDA(cudaMemsetAsync(d_out, 0, width * sizeof(uint64_t), MB_STREAM));
+        return finish_sync();
+    }
+    uint64_t blocks = (uint64_t)sm_count() * 4;
+    if (blocks > K) blocks = K;
+    const uint64_t per_chunk = (K + blocks - 1) / blocks;
+    const uint64_t chunks = (K + per_chunk - 1) / per_chunk;
+    uint64_t* partial = nullptr;
+    MB_CUDA(pool_alloc((void**)&partial, chunks * width * sizeof(uint64_t)));
+    {
+        MB_KERNEL("ajtai_commit_sparse");
+        commit_sparse_kernel<<<(unsigned)chunks, 384, 0, MB_STREAM>>>(d_key, d_positions, K, per_chunk, partial);
+    }
+    {
+        MB_KERNEL("ajtai_reduce_chunks");
+        reduce_chunks_kernel<<<grid_for(width, 256, 4), 256, 0, MB_STREAM>>>(partial, chunks, width, d_out);
+    }
+    int rc = finish_sync();
+    pool_free(partial);
+    return rc;
 }
 
 }  // extern "C"

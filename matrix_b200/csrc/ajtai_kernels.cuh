@@ -95,13 +95,13 @@ enum Kind { KIND_BITS = 0, KIND_S8 = 1, KIND_WIDE = 2 };
 template <int KIND>
 __global__ void __launch_bounds__(384)
 commit_scalar_kernel(const uint32_t* __restrict__ d_key, const void* __restrict__ z, uint64_t N, uint64_t col_offset,
-                     uint64_t cols_per_chunk, uint64_t* __restrict__ partial) {
+                     uint64_t cols_per_chunk, uint64_t* __restrict__ partial, const uint64_t* __restrict__ premat = nullptr) {
     __shared__ uint64_t M_sh[KAPPA * D];
     __shared__ uint64_t zw_sh[D];   // wide coefficients / bit mask in [0]
     __shared__ int8_t zd_sh[D];
     uint32_t key[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) key[k] = d_key[k];
+    for (int k = 0; k < 8; k++) key[k] = premat ? 0u : d_key[k];
     const int t = threadIdx.x, p = blockIdx.y;
     const uint64_t j0 = (uint64_t)blockIdx.x * cols_per_chunk;
     const uint64_t j1 = j0 + cols_per_chunk < N ? j0 + cols_per_chunk : N;
@@ -110,7 +110,10 @@ commit_scalar_kernel(const uint32_t* __restrict__ d_key, const void* __restrict_
     for (int q = 0; q < 7; q++) acc[q] = 0;
     for (uint64_t j = j0; j < j1; j++) {
         __syncthreads();
-        if (t < BLOCKS_PER_COL) {
+        if (premat) {  // a matrix materialised earlier: [column][row][coefficient]
+#pragma unroll
+            for (int q = 0; q < 7; q++) M_sh[t + 384 * q] = agl::canon(premat[(col_offset + j) * (uint64_t)(KAPPA * D) + t + 384 * q]);
+        } else if (t < BLOCKS_PER_COL) {
             uint64_t c[8];
             prg_ring_block(key, (uint32_t)(t >> 3), col_offset + j, (uint32_t)(t & 7), c);
 #pragma unroll
@@ -174,6 +177,103 @@ static __global__ void reduce_chunks_kernel(const uint64_t* __restrict__ partial
         for (size_t c = 0; c < chunks; c++) a = agl::add(a, partial[c * width + k]);
         out[k] = agl::canon(a);
     }
+}
+
+// Ternary planes to signed digits: digits[(p * N + j) * 64 + l] = +1 / -1 / 0 from the bit
+// masks pos[p * N + j], neg[p * N + j] (disjoint; cuda_almost_goldilocks/ajtai.cuh:1262-1270).
+static __global__ void ternary_expand_kernel(const uint64_t* __restrict__ pos, const uint64_t* __restrict__ neg,
+                                             size_t words, int8_t* __restrict__ digits) {
+    const size_t total = words * 4, step = (size_t)gridDim.x * blockDim.x;  // 16 digits per thread and step
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step) {
+        const size_t w = t >> 2;
+        const int part = (int)(t & 3);
+        const uint32_t pm = (uint32_t)(pos[w] >> (16 * part)) & 0xFFFFu, nm = (uint32_t)(neg[w] >> (16 * part)) & 0xFFFFu;
+        uint32_t v[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int l = 4 * q + b;
+                const uint32_t d = ((pm >> l) & 1u) ? 1u : (((nm >> l) & 1u) ? 0xFFu : 0u);
+                word |= d << (8 * b);
+            }
+            v[q] = word;
+        }
+        *reinterpret_cast<uint4*>(digits + w * 64 + 16 * part) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// Signed 16-bit coefficients to ternary bit planes: plane i holds bit i of |v|, in pos when v >= 0,
+// in neg otherwise; |v| >= 2^k_chunks raises *err (almost_sumcheck_prover.cuh:447-478).
+static __global__ void wide_to_ternary_kernel(const int16_t* __restrict__ wide, uint64_t* __restrict__ pos,
+                                              uint64_t* __restrict__ neg, int* err, size_t n_ring, int k_chunks) {
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < n_ring; j += step) {
+        uint64_t p[16], n[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) p[i] = n[i] = 0;
+        bool bad = false;
+        for (int k = 0; k < 64; k++) {
+            const int v = wide[j * 64 + k];
+            const uint32_t a = (uint32_t)(v < 0 ? -v : v);
+            bad |= (a >> k_chunks) != 0;
+            const uint64_t bit = 1ULL << k;
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+                if (i < k_chunks && ((a >> i) & 1u)) {
+                    if (v < 0) n[i] |= bit; else p[i] |= bit;
+                }
+        }
+        if (bad) atomicExch(err, 1);
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i < k_chunks) {
+                pos[(size_t)i * n_ring + j] = p[i];
+                neg[(size_t)i * n_ring + j] = n[i];
+            }
+    }
+}
+
+// Sparse commit: c_i = sum over positions p of X^(p mod 64) M[i][p / 64] (ajtai_cpu_reference.cuh:192-219).
+// One block per chunk of positions; the column's 42 ring elements are regenerated only when the column
+// changes, so sorted position lists cost one generation per distinct column. partial[chunk][42 * 64].
+static __global__ void __launch_bounds__(384)
+commit_sparse_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ positions, uint64_t K,
+                     uint64_t per_chunk, uint64_t* __restrict__ partial) {
+    __shared__ uint64_t M_sh[KAPPA * D];
+    uint32_t key[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) key[k] = d_key[k];
+    const int t = threadIdx.x;
+    const uint64_t k0 = (uint64_t)blockIdx.x * per_chunk, k1 = k0 + per_chunk < K ? k0 + per_chunk : K;
+    uint64_t acc[7];
+#pragma unroll
+    for (int q = 0; q < 7; q++) acc[q] = 0;
+    uint64_t have = ~0ULL;
+    for (uint64_t k = k0; k < k1; k++) {
+        const uint64_t pidx = positions[k], j = pidx >> 6;
+        const int ell = (int)(pidx & 63);
+        if (j != have) {
+            __syncthreads();
+            if (t < BLOCKS_PER_COL) {
+                uint64_t c[8];
+                prg_ring_block(key, (uint32_t)(t >> 3), j, (uint32_t)(t & 7), c);
+#pragma unroll
+                for (int q = 0; q < 8; q++) M_sh[(t >> 3) * D + (t & 7) * 8 + q] = c[q];
+            }
+            __syncthreads();
+            have = j;
+        }
+#pragma unroll
+        for (int q = 0; q < 7; q++) {
+            const int o = t + 384 * q, i = o >> 6, r = o & 63;
+            const uint64_t mv = M_sh[i * D + ((r - ell) & 63)];
+            acc[q] = r >= ell ? agl::add(acc[q], mv) : agl::sub(acc[q], mv);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 7; q++) partial[(size_t)blockIdx.x * (KAPPA * D) + t + 384 * q] = agl::canon(acc[q]);
 }
 
 // M[j][i][k] for j < N (the layout of ajtai_materialize_m_ffi, cuda_almost_goldilocks/ajtai_premat.cuh:41-84).

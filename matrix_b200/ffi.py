@@ -216,6 +216,10 @@ _AGL_SIGNATURES = {
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
+    "ajtai_commit_ternary_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_int, c_void_p]),
+    "ajtai_commit_ternary_premat_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_int, c_void_p]),
+    "ajtai_commit_sparse_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_void_p]),
+    "aext2_wide_to_ternary_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int]),
     "agl_batch_div_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "aext2_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "aext2_batch_sub_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),

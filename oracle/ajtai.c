@@ -95,3 +95,24 @@ void oracle_ajtai_commit(const uint32_t key[8], const void *z, int kind, uint64_
         }
     }
 }
+
+/* Sparse commit (ajtai_cpu_reference.cuh:192-219): position p = 64 j + l contributes X^l M[i][j]. */
+void oracle_ajtai_commit_sparse(const uint32_t key[8], const uint64_t *positions, uint64_t K, uint64_t *out) {
+    memset(out, 0, sizeof(uint64_t) * AJ_KAPPA * AJ_D);
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < AJ_KAPPA; i++) {
+        uint64_t m[AJ_D];
+        uint64_t have = ~0ULL;
+        for (uint64_t k = 0; k < K; k++) {
+            uint64_t j = positions[k] >> 6;
+            int l = (int)(positions[k] & 63);
+            if (j != have) { oracle_ajtai_ring_elem(key, (uint32_t)i, j, m); have = j; }
+            uint64_t *c = out + (size_t)i * AJ_D;
+            for (int r = 0; r < AJ_D; r++) {
+                uint64_t v = m[(r - l) & 63];
+                c[r] = r >= l ? agl_add(c[r], v) : agl_sub(c[r], v);
+            }
+        }
+    }
+}
+

@@ -160,6 +160,7 @@ _SIGS.update({
     "oracle_chacha8_block": (None, [vp, ctypes.c_uint32, vp, vp]),
     "oracle_ajtai_ring_elem": (None, [vp, ctypes.c_uint32, u64, vp]),
     "oracle_ajtai_commit": (None, [vp, vp, ci, u64, ci, u64, vp]),
+    "oracle_ajtai_commit_sparse": (None, [vp, vp, u64, vp]),
 })
 
 AJTAI_KAPPA, AJTAI_D = 42, 64

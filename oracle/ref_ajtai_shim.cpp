@@ -19,6 +19,13 @@ void ref_ajtai_commit_dense(const uint32_t* key, const uint64_t* z, uint64_t N, 
         for (int r = 0; r < 64; r++) out[k * 64 + r] = res[k][r];
 }
 
+// cpu_ajtai_commit_sparse over a position list; out[i][r]
+void ref_ajtai_commit_sparse(const uint32_t* key, const uint64_t* positions, uint64_t K, uint64_t* out) {
+    auto res = ajtai_cpu::cpu_ajtai_commit_sparse<64, 42>(key, positions, K);
+    for (size_t k = 0; k < res.size(); k++)
+        for (int r = 0; r < 64; r++) out[k * 64 + r] = res[k][r];
+}
+
 void ref_ajtai_ring_elem(const uint32_t* key, int row, uint64_t j, uint64_t* out) {
     auto e = ajtai_cpu::cpu_prg_ring_elem<64>(key, row, j);
     for (int r = 0; r < 64; r++) out[r] = e[r];

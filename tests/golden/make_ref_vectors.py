@@ -55,8 +55,17 @@ def main():
         e = np.zeros(64, dtype=np.uint64)
         aj.ref_ajtai_ring_elem(key.ctypes.data, row, j, e.ctypes.data)
         elems.append({"row": row, "j": j, "coeffs": [int(x) for x in e]})
-    json.dump({"source": "cuda_almost_goldilocks/ajtai_cpu_reference.cuh cpu_ajtai_commit_batched<64,42>, cpu_prg_ring_elem<64>; key = 1..8",
-               "key": [int(k) for k in key], "dense": cases, "ring_elems": elems},
+    # sparse commit over a seeded position list (repeated columns, unsorted order)
+    aj.ref_ajtai_commit_sparse.argtypes = [vp, vp, u64, vp]
+    pos = rng.integers(0, 64 * 40, size=200, dtype=np.uint64)
+    pos[:4] = [0, 63, 64, 64 * 39 + 63]
+    sp = np.zeros(42 * 64, dtype=np.uint64)
+    aj.ref_ajtai_commit_sparse(key.ctypes.data, pos.ctypes.data, len(pos), sp.ctypes.data)
+    sparse = {"positions": [int(x) for x in pos], "first": int(sp[0]), "last": int(sp[-1]),
+              "sha256": hashlib.sha256(sp.tobytes()).hexdigest()}
+    json.dump({"source": "cuda_almost_goldilocks/ajtai_cpu_reference.cuh cpu_ajtai_commit_batched<64,42>, cpu_prg_ring_elem<64>, "
+                         "cpu_ajtai_commit_sparse<64,42>; key = 1..8",
+               "key": [int(k) for k in key], "dense": cases, "ring_elems": elems, "sparse": sparse},
               open(os.path.join(HERE, "ajtai_ref.json"), "w"), indent=1)
     print("wrote ajtai_ref.json")
 

@@ -117,3 +117,96 @@ def test_materialised_matrix_and_argument_checks(lib):
     d_z, d_o = DeviceBuffer(lib, 64), DeviceBuffer(lib, 16 * 42 * 64 * 8)
     assert lib.ajtai_commit_dense_batched_ffi(d_k.ptr, d_z.ptr, 1, 3, 64, d_o.ptr) == -2   # B not a power of two <= 16
     assert lib.ajtai_commit_dense_batched_ffi(d_k.ptr, d_z.ptr, 1, 1, 100, d_o.ptr) == -3  # unsupported chunk
+
+
+def _ternary_planes(rng, n_ring, planes=13):
+    """Random disjoint pos / neg masks [planes][n_ring] and the digits they stand for."""
+    pos = rng.integers(0, 2**63, size=planes * n_ring, dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, size=planes * n_ring, dtype=np.uint64)
+    neg = rng.integers(0, 2**63, size=planes * n_ring, dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, size=planes * n_ring, dtype=np.uint64)
+    neg &= ~pos
+    pos[::5] = 0
+    neg[1::7] = 0
+    shifts = np.arange(64, dtype=np.uint64)
+    digits = (((pos[:, None] >> shifts) & np.uint64(1)).astype(np.int8) - ((neg[:, None] >> shifts) & np.uint64(1)).astype(np.int8))
+    return pos, neg, np.ascontiguousarray(digits.reshape(-1))
+
+
+@pytest.mark.parametrize("n_ring", [1, 3, 70, 260])
+def test_ternary_commit_matches_oracle(lib, n_ring):
+    from oracle import pyoracle
+    pos, neg, digits = _ternary_planes(np.random.default_rng(40 + n_ring), n_ring)
+    exp = pyoracle.ajtai_commit(KEY, digits, 1, n_ring, 13)
+    d_k, d_p, d_n = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, pos), DeviceBuffer.from_numpy(lib, neg)
+    d_o = DeviceBuffer(lib, 13 * 42 * 64 * 8)
+    assert lib.ajtai_commit_ternary_ffi(d_k.ptr, d_p.ptr, d_n.ptr, n_ring, 256, d_o.ptr) == 0
+    assert np.array_equal(d_o.to_numpy(), exp)
+    # against a materialised matrix
+    d_m = DeviceBuffer(lib, 8 * 42 * 64 * n_ring)
+    assert lib.ajtai_materialize_m_ffi(d_k.ptr, d_m.ptr, n_ring) == 0
+    d_o2 = DeviceBuffer(lib, 13 * 42 * 64 * 8)
+    assert lib.ajtai_commit_ternary_premat_ffi(d_m.ptr, d_p.ptr, d_n.ptr, n_ring, 64, d_o2.ptr) == 0
+    assert np.array_equal(d_o2.to_numpy(), exp)
+    assert lib.ajtai_commit_ternary_ffi(d_k.ptr, d_p.ptr, d_n.ptr, n_ring, 100, d_o.ptr) == -3
+    assert lib.ajtai_commit_ternary_ffi(d_k.ptr, d_p.ptr, d_n.ptr, 0, 64, d_o.ptr) == 0
+    assert not d_o.to_numpy().any()
+
+
+@pytest.mark.parametrize("n_ring,k_chunks", [(1, 13), (50, 13), (300, 8), (64, 16)])
+def test_wide_to_ternary_and_back(lib, n_ring, k_chunks):
+    """Planes recombine to the coefficients (sum_i 2^i (pos_i - neg_i)); a coefficient that needs more bits
+    raises the flag; committing the planes and recombining equals the commit of the signed coefficients."""
+    from oracle import pyoracle
+    rng = np.random.default_rng(n_ring)
+    lim = min(2**k_chunks - 1, 32767)
+    wide = rng.integers(-lim, lim + 1, size=n_ring * 64, dtype=np.int16)
+    wide[:4] = [lim, -lim, 0, 1]
+    d_w = DeviceBuffer.from_numpy(lib, wide)
+    d_p, d_n = DeviceBuffer(lib, 8 * k_chunks * n_ring), DeviceBuffer(lib, 8 * k_chunks * n_ring)
+    d_e = DeviceBuffer.from_numpy(lib, np.zeros(1, dtype=np.int32))
+    assert lib.aext2_wide_to_ternary_ffi(d_w.ptr, d_p.ptr, d_n.ptr, d_e.ptr, n_ring, k_chunks) == 0
+    lib.cuda_device_synchronize()
+    pos, neg = d_p.to_numpy().reshape(k_chunks, n_ring), d_n.to_numpy().reshape(k_chunks, n_ring)
+    assert int(d_e.to_numpy(dtype="int32")[0]) == 0
+    assert not (pos & neg).any()
+    shifts = np.arange(64, dtype=np.uint64)
+    rec = np.zeros((n_ring, 64), dtype=np.int64)
+    for i in range(k_chunks):
+        rec += (((pos[i][:, None] >> shifts) & np.uint64(1)).astype(np.int64) - ((neg[i][:, None] >> shifts) & np.uint64(1)).astype(np.int64)) << i
+    assert np.array_equal(rec.reshape(-1), wide.astype(np.int64))
+    if k_chunks < 15:
+        wide[7] = 2**k_chunks
+        d_w2 = DeviceBuffer.from_numpy(lib, wide)
+        assert lib.aext2_wide_to_ternary_ffi(d_w2.ptr, d_p.ptr, d_n.ptr, d_e.ptr, n_ring, k_chunks) == 0
+        lib.cuda_device_synchronize()
+        assert int(d_e.to_numpy(dtype="int32")[0]) == 1
+    assert lib.aext2_wide_to_ternary_ffi(d_w.ptr, d_p.ptr, d_n.ptr, d_e.ptr, n_ring, 17) == -1
+
+
+@pytest.mark.parametrize("k,cols", [(1, 1), (200, 40), (5000, 300), (3000, 5)])
+def test_sparse_commit_matches_oracle(lib, k, cols):
+    from oracle import pyoracle
+    rng = np.random.default_rng(k)
+    pos = rng.integers(0, 64 * cols, size=k, dtype=np.uint64)
+    if k > 100:
+        pos[: k // 2] = np.sort(pos[: k // 2])  # runs that reuse a column, then arbitrary order
+    exp = np.zeros(42 * 64, dtype=np.uint64)
+    pyoracle.load().oracle_ajtai_commit_sparse(KEY.ctypes.data, pos.ctypes.data, k, exp.ctypes.data)
+    d_k, d_p, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, pos), DeviceBuffer(lib, 42 * 64 * 8)
+    assert lib.ajtai_commit_sparse_ffi(d_k.ptr, d_p.ptr, k, 1024, d_o.ptr) == 0
+    assert np.array_equal(d_o.to_numpy(), exp)
+    assert lib.ajtai_commit_sparse_ffi(d_k.ptr, d_p.ptr, 0, 64, d_o.ptr) == 0
+    assert not d_o.to_numpy().any()
+    assert lib.ajtai_commit_sparse_ffi(d_k.ptr, d_p.ptr, k, 7, d_o.ptr) == -3
+
+
+def test_sparse_commit_reference_vector(lib):
+    """The position list whose commitment the reference's cpu_ajtai_commit_sparse produced (tests/golden/ajtai_ref.json)."""
+    import hashlib, json, os
+    from .conftest import ROOT
+    sp = json.load(open(os.path.join(ROOT, "tests", "golden", "ajtai_ref.json")))["sparse"]
+    pos = np.array(sp["positions"], dtype=np.uint64)
+    d_k, d_p, d_o = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, pos), DeviceBuffer(lib, 42 * 64 * 8)
+    assert lib.ajtai_commit_sparse_ffi(d_k.ptr, d_p.ptr, len(pos), 256, d_o.ptr) == 0
+    out = d_o.to_numpy()
+    assert int(out[0]) == sp["first"] and int(out[-1]) == sp["last"]
+    assert hashlib.sha256(out.tobytes()).hexdigest() == sp["sha256"]
