@@ -540,6 +540,11 @@ def main():
     nodes_per_step = leaves_commit + sum(max((cw_len >> (i + 2)) - 1, 0) for i in range(nv - 1))
     alg_bytes = {"hash_leaves": (leaves_commit * 48 + leaves_folded * 64) * args.steps}
     roofline = None
+    hash_ms = sum(kernels.get(k, (0, 0))[1] for k in ("hash_leaves", "compress_layer", "tree_tail", "compress_layer_coop",
+                                                       "hash_leaves_coop"))
+    perms_per_s = (leaves_commit + leaves_folded + nodes_per_step) * args.steps / (hash_ms * 1e-3) if hash_ms else 0.0
+    inst_per_perm = 15550.0 if args.hash == "poseidon2" else 6900.0  # thread instructions per permutation (ncu)
+    sm_hz = 1e6 * (clocks.get("sm_mhz") or 1965.0)
     if dom is not None:
         cnt, ms = kernels[dom]
         if dom == "hash_leaves":
@@ -564,9 +569,15 @@ def main():
                         "note": ("Poseidon2 hashing: ~520 modular multiplications per 32-byte digest, bound by the "
                                  "integer pipes, not HBM; permutations/s is the meaningful rate") if args.hash == "poseidon2"
                         else "Monolith hashing: bound by the integer pipes, not HBM; permutations/s is the meaningful rate",
-                        "permutations_per_s": (leaves_commit + leaves_folded + nodes_per_step) * args.steps /
-                                              ((kernels.get("hash_leaves", (0, 0))[1] + kernels.get("compress_layer", (0, 0))[1]
-                                                + kernels.get("tree_tail", (0, 0))[1]) * 1e-3)}
+                        "permutations_per_s": perms_per_s,
+                        # the bound that applies: warp instructions issued against the issue slots of the machine
+                        # (instructions per permutation from the ncu capture in profiles/; 148 SMs x 4 schedulers)
+                        "issue": {"warp_inst_per_permutation": inst_per_perm / 32.0,
+                                  "achieved_warp_inst_per_s": perms_per_s * inst_per_perm / 32.0,
+                                  "peak_warp_inst_per_s": 148 * 4 * sm_hz,
+                                  "frac": perms_per_s * inst_per_perm / 32.0 / (148 * 4 * sm_hz),
+                                  "note": "integer additions, logic and multiply-adds share one 16-lane datapath per "
+                                          "scheduler: 0.57 of the issue slots is the measured ceiling for this mix"}}
     line = {
         "metric": METRIC if args.hash == "poseidon2" else METRIC.replace("Poseidon2 Merkle", "Monolith Merkle"),
         "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -71,15 +71,31 @@ class TorchComm:
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.local_ranks = [self.rank]
         self.device = device
+        self._bufs = {}
 
     def allgather(self, arrs):
+        """Every rank's array, in rank order. Staging buffers (pinned host, device) are kept per length."""
         import torch
-        t = torch.from_numpy(np.ascontiguousarray(arrs[0], dtype=np.uint64).view(np.int64).copy())
+        a = np.ascontiguousarray(arrs[0], dtype=np.uint64)
+        n = a.size
+        buf = self._bufs.get(n)
+        if buf is None:
+            pin = self.device is not None
+            h_in = torch.empty(n, dtype=torch.int64, pin_memory=pin)
+            h_out = torch.empty(n * self.world, dtype=torch.int64, pin_memory=pin)
+            d_in = torch.empty(n, dtype=torch.int64, device=self.device) if pin else h_in
+            d_out = torch.empty(n * self.world, dtype=torch.int64, device=self.device) if pin else h_out
+            buf = self._bufs[n] = (h_in, h_out, d_in, d_out)
+        h_in, h_out, d_in, d_out = buf
+        h_in.numpy()[:] = a.view(np.int64)
         if self.device is not None:
-            t = t.to(self.device)
-        outs = [torch.empty_like(t) for _ in range(self.world)]
-        self.dist.all_gather(outs, t)
-        return [o.cpu().numpy().view(np.uint64) for o in outs]
+            d_in.copy_(h_in, non_blocking=True)
+        self.dist.all_gather_into_tensor(d_out, d_in)
+        if self.device is not None:
+            h_out.copy_(d_out, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+        res = h_out.numpy().view(np.uint64).reshape(self.world, n)
+        return [res[g].copy() for g in range(self.world)]
 
 
 class LibTranscript:
