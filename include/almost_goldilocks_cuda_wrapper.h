@@ -149,6 +149,50 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
 int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
                         uint64_t* d_out);
 
+/* ---- batched same-point sumcheck family (sum_x eq(x) f(x) per leaf, messages at c = 0, 1, 2): ffi.rs:177-195,265-423
+ * (wrapper.cu:674-707,851-1060; kernels cuda_almost_goldilocks/almost_sumcheck_prover.cuh:233-1007). Tables are Ext2
+ * (two words per element) with stride original_size elements; folds bind the low variable; message kernels write
+ * d_partial[block][leaf][c][2] for the caller to add; all calls are asynchronous on the caller's stream. ---- */
+/* interleaved layout: d_polys[leaf] = eq table, then f table */
+int aext2_sumcheck_batched_round_message_ffi(const uint64_t* d_polys, uint64_t* d_partial, size_t original_size, size_t half,
+                                             int num_leaves, int num_blocks_x);
+int aext2_sumcheck_batched_fold_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0, uint64_t challenge_c1,
+                                    size_t original_size, size_t half, int num_leaves);
+/* round 0 with f still binary (packed bits, packed_size_u64 words per leaf): no lift, f' in {0, 1, r, 1 - r} */
+int aext2_sumcheck_batched_round0_binary_msg_ffi(const uint64_t* d_polys, const uint64_t* d_packed, uint64_t* d_partial,
+                                                 size_t original_size, size_t half, int num_leaves, int num_blocks_x,
+                                                 size_t packed_size_u64);
+int aext2_sumcheck_batched_round0_binary_fold_ffi(const uint64_t* d_polys, const uint64_t* d_packed, uint64_t* d_output,
+                                                  uint64_t challenge_c0, uint64_t challenge_c1, size_t original_size, size_t half,
+                                                  int num_leaves, size_t packed_size_u64);
+/* shared eq: eq tables of the distinct points in d_eq, f tables in d_f, leaf -> point map */
+int aext2_sharedeq_msg_ffi(const uint64_t* d_eq, const uint64_t* d_f, const int* d_leaf_to_unique, uint64_t* d_partial,
+                           size_t original_size, size_t half, int num_leaves, int num_blocks_x);
+int aext2_fold_single_ffi(const uint64_t* d_in, uint64_t* d_out, uint64_t challenge_c0, uint64_t challenge_c1, size_t original_size,
+                          size_t half, int count);
+/* factored eq: suffix tables eqsuf_t (element offset 2^(log_n - t) - 1 inside each point's region) built once;
+ * a round returns d_partial[block][point][A, B][2], A = sum_y eqsuf[y] F[2y], B = sum_y eqsuf[y] F[2y + 1] */
+int aext2_eq_suffix_dp_ffi(const uint64_t* d_r_all, uint64_t* d_eqsuf, int log_n, int num_unique, size_t eqsuf_stride_u64);
+int aext2_sharedeq_factored_msg_ffi(const uint64_t* d_eqsuf, const uint64_t* d_fu, uint64_t* d_partial, size_t eqsuf_off_elems,
+                                    size_t eqsuf_stride_u64, size_t poly_stride_u64, size_t half, int num_unique, int num_blocks_x);
+/* F_u[x] = sum over the leaves of point u of alpha_leaf f_leaf[x]; leaves sorted by point, offsets[num_unique + 1] */
+int aext2_build_fu_ffi(const uint64_t* d_packed, const uint64_t* d_alphas, const int* d_leaf_idx_sorted, const int* d_unique_offsets,
+                       uint64_t* d_Fu, size_t original_size, int num_unique, size_t packed_size_u64);
+int aext2_build_fu_ternary_ffi(const uint64_t* d_pos, const uint64_t* d_neg, const uint64_t* d_alphas, const int* d_leaf_idx_sorted,
+                               const int* d_unique_offsets, uint64_t* d_Fu, size_t original_size, int num_unique, size_t packed_size_u64);
+/* packed planes to Ext2 tables: into the f slot of the interleaved layout, a contiguous array, or pos - neg */
+int aext2_batched_lift_binary_ffi(const uint64_t* d_packed, uint64_t* d_polys, size_t original_size, int num_leaves, size_t packed_size_u64);
+int aext2_lift_binary_contig_ffi(const uint64_t* d_packed, uint64_t* d_f, size_t original_size, int num_leaves, size_t packed_size_u64);
+int aext2_batched_lift_ternary_single_ffi(const uint64_t* d_pos, const uint64_t* d_neg, uint64_t* d_polys, size_t original_size,
+                                          int num_leaves, size_t packed_size_u64);
+/* d_partial[block][plane][2]: sum of eq[i] over the set bits of each plane */
+int aext2_selective_add_batched_planes_ffi(const uint64_t* d_eq, const uint64_t* d_packed_planes, uint64_t* d_partial, size_t total,
+                                           int n_planes, size_t packed_size_u64, int num_blocks_x);
+/* eq tables on a caller stream; the table is returned in d_buf_a (d_buf_b is scratch) */
+int aext2_eq_dp_all_stream_ffi(const uint64_t* d_r, uint64_t* d_buf_a, uint64_t* d_buf_b, int log_n, uint64_t** d_result, void* stream);
+int aext2_eq_dp_all_batched_ffi(const uint64_t* d_r_all, uint64_t* d_buf_a_all, uint64_t* d_buf_b_all, int log_n, int num_leaves,
+                                size_t leaf_stride, uint64_t** d_result, void* stream);
+
 /* ---- K = F_q[Theta]/(Theta^8 - 3) product sumcheck and table helpers: ffi.rs:65-75 (wrapper.cu:3815-3905;
  * kernels cuda_almost_goldilocks/morpheus_piop.cuh:140-282; CPU zk-torch-4/src/morpheus/piop/mod.rs:785-840,
  * field zk-torch-4/src/morpheus/field8.rs). Elements are 8 canonical words; tables live on the device,

@@ -45,6 +45,7 @@ LIBRARIES = {
         "agl_ajtai.cu",
         "agl_batch.cu",
         "agl_k8.cu",
+        "agl_batched.cu",
         "host/agl_transcript.cu",
     ],
 }

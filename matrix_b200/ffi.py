@@ -253,6 +253,22 @@ _AGL_SIGNATURES = {
     "agl_cached_bytes": (c_size_t, []),
     "agl_d2h_staged": (c_int, [c_void_p, c_void_p, c_size_t]),
     "agl_h2d_staged": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "aext2_sumcheck_batched_round_message_ffi": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_int]),
+    "aext2_sumcheck_batched_fold_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t, c_int]),
+    "aext2_sumcheck_batched_round0_binary_msg_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_int, c_size_t]),
+    "aext2_sumcheck_batched_round0_binary_fold_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t, c_int, c_size_t]),
+    "aext2_sharedeq_msg_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_int]),
+    "aext2_fold_single_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t, c_int]),
+    "aext2_eq_suffix_dp_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int, c_size_t]),
+    "aext2_sharedeq_factored_msg_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_int, c_int]),
+    "aext2_build_fu_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_size_t]),
+    "aext2_build_fu_ternary_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_size_t]),
+    "aext2_batched_lift_binary_ffi": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_size_t]),
+    "aext2_lift_binary_contig_ffi": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_size_t]),
+    "aext2_batched_lift_ternary_single_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_size_t]),
+    "aext2_selective_add_batched_planes_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_size_t, c_int]),
+    "aext2_eq_dp_all_stream_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p), c_void_p]),
+    "aext2_eq_dp_all_batched_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "agl_mpiop_sc_round": (c_int, [c_void_p, c_int, c_u64, c_int, c_void_p]),
     "agl_mpiop_sc_fold": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "agl_mpiop_sc_fold_round": (c_int, [c_void_p, c_void_p, c_int, c_u64, c_void_p, c_int, c_void_p]),
