@@ -139,6 +139,35 @@ int ajtai_commit_sparse_ffi(const uint32_t* d_key, const uint64_t* d_positions, 
  * plane i of pos or neg by sign); *d_err = 1 when a coefficient needs more bits (almost_sumcheck_prover.cuh:447-478) */
 int aext2_wide_to_ternary_ffi(const int16_t* d_wide, uint64_t* d_pos, uint64_t* d_neg, int* d_err, size_t n_ring, int k_chunks);
 
+/* ---- folding of witnesses and commitments by ring challenges: ffi.rs:435-492,635-647 (wrapper.cu:1468-1629,1717-1739;
+ * kernels cuda_almost_goldilocks/ajtai.cuh:700-1255, ajtai_tc.cuh:44-411). Products are negacyclic (X^64 = -1);
+ * challenges are 64 signed bytes (the protocol uses {-1, 0, 1, 2}). ---- */
+/* d_out[N_ring][64] = z1 + r z2 as canonical field elements; z1, z2 bit masks; r_coeffs on the HOST */
+int ajtai_fold_witness_ffi(const uint64_t* d_z1, const uint64_t* d_z2, const int8_t* r_coeffs, uint64_t N_ring, int chunk,
+                           uint64_t* d_out);
+/* d_out[42][64] = c1 + r c2; r_coeffs on the HOST */
+int ajtai_fold_commitment_ffi(const uint64_t* d_c1, const uint64_t* d_c2, const int8_t* r_coeffs, uint64_t* d_out);
+/* d_out[42][64] = sum_m r_m c_m; d_c_packed[m][42][64], d_r_all[m][64] on the device */
+int ajtai_multifold_commitment_ffi(const uint64_t* d_c_packed, const int8_t* d_r_all, int num_instances, uint64_t* d_out);
+/* d_out[N_ring][64] (16-bit) = sum_i r_i z_i: binary masks d_z[i * N_ring + j], then ternary (pos, neg) pairs; challenges in
+ * that order on the device. All four run the tcgen05 int8 kernel (exact); chunk_size is ignored. */
+int ajtai_multifold_witness_ffi(const uint64_t* d_z_packed, const int8_t* d_r_all, int16_t* d_out, int num_instances, uint64_t N_ring,
+                                uint64_t chunk_size);
+int ajtai_multifold_mixed_witness_ffi(const uint64_t* d_z_bin_packed, const uint64_t* d_pos_packed, const uint64_t* d_neg_packed,
+                                      const int8_t* d_r_all, int16_t* d_out, int num_binary, int num_ternary, uint64_t N_ring,
+                                      uint64_t chunk_size);
+int ajtai_multifold_mixed_witness_tc_ffi(const uint64_t* d_z_bin_packed, const uint64_t* d_pos_packed, const uint64_t* d_neg_packed,
+                                         const int8_t* d_r_all, int16_t* d_out, int num_binary, int num_ternary, uint64_t N_ring);
+int ajtai_multifold_mixed_witness_tc_fused_ffi(const uint64_t* d_z_bin_packed, const uint64_t* d_pos_packed,
+                                               const uint64_t* d_neg_packed, const int8_t* d_r_all, int16_t* d_out, int num_binary,
+                                               int num_ternary, uint64_t N_ring);
+/* addition: the scalar form of the same fold, an independent check of the tensor-core path */
+int ajtai_multifold_mixed_witness_scalar_ffi(const uint64_t* d_z_bin_packed, const uint64_t* d_pos_packed,
+                                             const uint64_t* d_neg_packed, const int8_t* d_r_all, int16_t* d_out, int num_binary,
+                                             int num_ternary, uint64_t N_ring);
+/* 16-bit coefficients d_z_wide[N_ring][64] to 13 ternary planes d_pos / d_neg[i * N_ring + j] */
+int ajtai_split_witness_ffi(const int16_t* d_z_wide, uint64_t* d_pos_chunks, uint64_t* d_neg_chunks, uint64_t N_ring);
+
 /* addition: signed 8-bit digit planes d_digits[(p*N + j)*64 + l] in [-128, 127], d_out[p][42][64];
  * scalar path, exact for any N */
 int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes,

@@ -68,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 // grid = (column chunks, 3 row groups); block = 256 threads; dynamic shared memory.
 // d_digits: [planes][N][64] s8 (this CTA uses planes p0 .. p0 + np - 1).
 // partial[((chunk * 3 + group) * np + p) * 14 * 64 + i_local * 64 + r] = canonical chunk sum.
-__global__ void __launch_bounds__(TC_THREADS)
+static __global__ void __launch_bounds__(TC_THREADS)
 commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ d_digits, uint64_t N, int p0, int np,
                  uint64_t col_offset, uint64_t* __restrict__ partial, int* __restrict__ d_error) {
     extern __shared__ __align__(1024) uint8_t smem[];

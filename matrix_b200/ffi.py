@@ -216,6 +216,15 @@ _AGL_SIGNATURES = {
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
+    "ajtai_fold_witness_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_int, c_void_p]),
+    "ajtai_fold_commitment_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ajtai_multifold_commitment_ffi": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
+    "ajtai_multifold_witness_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_u64, c_u64]),
+    "ajtai_multifold_mixed_witness_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_u64, c_u64]),
+    "ajtai_multifold_mixed_witness_tc_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_u64]),
+    "ajtai_multifold_mixed_witness_tc_fused_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_u64]),
+    "ajtai_multifold_mixed_witness_scalar_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_u64]),
+    "ajtai_split_witness_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64]),
     "ajtai_commit_ternary_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_int, c_void_p]),
     "ajtai_commit_ternary_premat_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_int, c_void_p]),
     "ajtai_commit_sparse_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_void_p]),
