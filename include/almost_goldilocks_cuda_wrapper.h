@@ -235,6 +235,15 @@ int agl_mpiop_eq(const uint64_t* h_point, int n, uint64_t* d_out);
 int agl_mpiop_eq_outer(const uint64_t* d_lo, int nlo, const uint64_t* d_hi, int nhi, uint64_t* d_out);
 int agl_mpiop_axpy(uint64_t* d_out, const uint64_t* d_in, uint64_t n, const uint64_t* h_c);
 int agl_mpiop_lift(const uint64_t* d_in, uint64_t n, uint64_t* d_out);
+/* ffi.rs:65-68 (wrapper.cu:3753-3837; kernels morpheus_piop.cuh:20-172): helpers over base-field tables.
+ * pe: d_out[r] = sum_f d_vals[deposit(r, rest_pos) | deposit(f, fix_pos)] d_e[f] (bit j of r / f goes to bit pos[j];
+ * rest_pos, fix_pos are host arrays); mle: h_out[8] = sum_x d_vals[x] eq(x, h_point); gather: d_out[x] = d_in[idx],
+ * bit j of idx = bit pos[j] of x; sel_lookup: d_out[i] = d_table[(d_sel[i] >> shift) & mask]. */
+int agl_mpiop_pe(const uint64_t* d_vals, const int* rest_pos, int nrest_v, const int* fix_pos, int nfix_v, const uint64_t* d_e,
+                 uint64_t* d_out);
+int agl_mpiop_mle(const uint64_t* d_vals, const uint64_t* h_point, int n, uint64_t* h_out);
+int agl_mpiop_gather(const uint64_t* d_in, const int* pos, int nv, uint64_t n, uint64_t* d_out);
+int agl_mpiop_sel_lookup(const uint64_t* d_sel, uint64_t n, int shift, uint64_t mask, const uint64_t* d_table, uint64_t* d_out);
 
 /* ---- host side: Monolith over almost-Goldilocks and the transcript on it ----
  * The reference keeps these in Rust: permutation and SHA-256-derived round constants

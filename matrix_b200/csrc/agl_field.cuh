@@ -23,24 +23,67 @@ using gl::umulhi;
 constexpr uint64_t P = 0xFFFFFFFEFFFFFFE1ULL;  // q
 constexpr uint64_t C = 0x000000010000001FULL;  // 2^64 mod q = 2^32 + 31
 
-GLF uint64_t canon(uint64_t x) { return x >= P ? x - P : x; }
+// Device forms use the carry flag and one multiply-add for the +-c repair, like the Goldilocks
+// primitives (the cost of this arithmetic is its instruction count).
+#ifdef __CUDA_ARCH__
+// x + k c mod 2^64 for k in {0, 1}: c = 2^32 + 31
+__device__ __forceinline__ uint64_t plus_c(uint64_t x, uint32_t k) {
+    return madwide(k, 31u, x) + ((uint64_t)k << 32);
+}
+#endif
 
+// x >= q exactly when x + c wraps; then x - q = x + c - 2^64.
+GLF uint64_t canon(uint64_t x) {
+#ifdef __CUDA_ARCH__
+    uint32_t carry;
+    (void)gl::add_cc(x, C, carry);
+    return plus_c(x, carry);
+#else
+    return x >= P ? x - P : x;
+#endif
+}
+
+// a + b where b < q: one wrap at most, and the repaired sum stays below 2^64.
+GLF uint64_t add_c(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint32_t carry;
+    uint64_t s = gl::add_cc(a, b, carry);
+    return plus_c(s, carry);
+#else
+    uint64_t s = a + b;
+    return s < a ? s + C : s;
+#endif
+}
+
+// a + b for loose a, b: the wrapped sum is made canonical first, so the repair cannot wrap again.
 GLF uint64_t add(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint32_t carry;
+    uint64_t s = gl::add_cc(a, b, carry);
+    return plus_c(canon(s), carry);
+#else
     uint64_t s = a + b;
     if (s < a) {
         s += C;
         if (s < C) s += C;
     }
     return s;
+#endif
 }
-GLF uint64_t sub(uint64_t a, uint64_t b) {
+
+// a - b where b < q: a borrow is repaired by - c, which cannot underflow (the wrapped difference exceeds c).
+GLF uint64_t sub_c(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint64_t r;
+    uint32_t m;
+    asm("sub.cc.u64 %0, %2, %3;\n\tsubc.u32 %1, 0, 0;" : "=l"(r), "=r"(m) : "l"(a), "l"(b));
+    return r - ((uint64_t)(m & 1u) << 32) - (uint64_t)(m & 31u);
+#else
     uint64_t d = a - b;
-    if (a < b) {
-        uint64_t e = d - C;
-        d = (d < C) ? e - C : e;
-    }
-    return d;
+    return a < b ? d - C : d;
+#endif
 }
+GLF uint64_t sub(uint64_t a, uint64_t b) { return sub_c(a, canon(b)); }
 GLF uint64_t neg(uint64_t a) { return sub(0, a); }
 
 // L + H 2^32 mod q for L, H < 2^40, loose result. W = (A_lo : L_lo) with
@@ -70,6 +113,13 @@ GLF uint64_t acc_reduce(const gl::Acc& s) {
     uint64_t L = madwide(s.a4, 992u, madwide(s.a3, 31u, madwide(s.a2, 31u, (uint64_t)s.a0)));
     uint64_t H = madwide(s.a4, 63u, madwide(s.a3, 32u, madwide(s.a2, 1u, (uint64_t)s.a1)));
     return reduce_limb_sums(L, H);
+}
+
+// The same for any top limb (long-running accumulators): top 2^128 = top (63 2^32 + 992) mod q.
+GLF uint64_t mul(uint64_t a, uint64_t b);
+GLF uint64_t acc_reduce_wide(const gl::Acc& s) {
+    const uint64_t low = reduce_limbs(s.a0, s.a1, s.a2, s.a3);
+    return add(low, mul((uint64_t)s.a4, 63ULL * (1ULL << 32) + 992ULL));
 }
 
 GLF uint64_t mul(uint64_t a, uint64_t b) { return reduce128(a * b, umulhi(a, b)); }

@@ -165,4 +165,105 @@ int agl_mpiop_lift(const uint64_t* d_in, uint64_t n, uint64_t* d_out) {
     return finish_async();
 }
 
+// ---- helpers over base-field tables (wrapper.cu:3753-3837) ----
+namespace {
+VarMap make_map(const int* pos, int n) {
+    VarMap m;
+    m.n = n;
+    for (int j = 0; j < MAXV; j++) m.pos[j] = j < n ? pos[j] : 0;
+    return m;
+}
+// out (device, nrest elements) = partial evaluation; `e` is a device K table of 2^nfix_v elements
+int run_pe(const uint64_t* d_vals, const VarMap& rest, const VarMap& fix, const uint64_t* d_e, uint64_t* d_out) {
+    const uint64_t nrest = (uint64_t)1 << rest.n, nfix = (uint64_t)1 << fix.n;
+    uint64_t want = (uint64_t)sm_count() * 8;
+    uint64_t gx = nrest < want ? nrest : want;
+    uint64_t gy = (want + gx - 1) / gx;
+    const uint64_t max_gy = (nfix + 31) / 32;
+    if (gy > max_gy) gy = max_gy;
+    if (gy > 65535) gy = 65535;
+    if (gy < 1) gy = 1;
+    uint64_t* partial = nullptr;
+    MB_CUDA(pool_alloc((void**)&partial, sizeof(uint64_t) * 8 * nrest * gy));
+    {
+        MB_KERNEL("k8_pe");
+        dim3 grid((unsigned)gx, (unsigned)gy);
+        pe_kernel<<<grid, 256, 0, MB_STREAM>>>(d_vals, rest, fix, d_e, nrest, nfix, partial);
+    }
+    {
+        MB_KERNEL("k8_sum_rows");
+        sum_rows_kernel<<<grid_for(nrest * 8, 256, 4), 256, 0, MB_STREAM>>>(partial, nrest, (int)gy, d_out);
+    }
+    int rc = finish_async();
+    pool_free(partial);
+    return rc;
+}
+}  // namespace
+
+// d_out[r] = sum_f d_vals[deposit(r, rest_pos) | deposit(f, fix_pos)] d_e[f]; rest_pos / fix_pos are host arrays of bit positions.
+int agl_mpiop_pe(const uint64_t* d_vals, const int* rest_pos, int nrest_v, const int* fix_pos, int nfix_v, const uint64_t* d_e,
+                 uint64_t* d_out) {
+    if (!d_vals || !d_e || !d_out || nrest_v < 0 || nfix_v < 0 || nrest_v > MAXV || nfix_v > MAXV || nrest_v + nfix_v > 40 ||
+        (nrest_v && !rest_pos) || (nfix_v && !fix_pos))
+        return MB_ERR_ARG;
+    return run_pe(d_vals, make_map(rest_pos, nrest_v), make_map(fix_pos, nfix_v), d_e, d_out);
+}
+
+// h_out[8] = sum_x d_vals[x] eq(x, h_point): the multilinear extension of a base-field table at a K point.
+// The point is split in two: T[h] = sum_l eq_lo[l] vals[h 2^nlo + l], then sum_h eq_hi[h] T[h].
+int agl_mpiop_mle(const uint64_t* d_vals, const uint64_t* h_point, int n, uint64_t* h_out) {
+    if (!d_vals || !h_out || n < 0 || n > 40 || (n && !h_point)) return MB_ERR_ARG;
+    const int nlo = n / 2, nhi = n - nlo;
+    uint64_t *e_lo = nullptr, *e_hi = nullptr, *T = nullptr, *partial = nullptr;
+    MB_CUDA(pool_alloc((void**)&e_lo, (size_t)64 << nlo));
+    int rc = MB_OK;
+    if (pool_alloc((void**)&e_hi, (size_t)64 << nhi) != cudaSuccess) rc = MB_ERR_CUDA;
+    if (rc == MB_OK && pool_alloc((void**)&T, (size_t)64 << nhi) != cudaSuccess) rc = MB_ERR_CUDA;
+    const uint64_t nh = (uint64_t)1 << nhi;
+    const int grid = grid_for(nh * 8, 256, 4);
+    if (rc == MB_OK && pool_alloc((void**)&partial, sizeof(uint64_t) * 8 * (size_t)(grid + 1)) != cudaSuccess) rc = MB_ERR_CUDA;
+    if (rc == MB_OK) rc = agl_mpiop_eq(h_point, nlo, e_lo);
+    if (rc == MB_OK) rc = agl_mpiop_eq(h_point ? h_point + 8 * nlo : nullptr, nhi, e_hi);
+    if (rc == MB_OK) {
+        int lo_pos[MAXV], hi_pos[MAXV];
+        for (int j = 0; j < nlo; j++) lo_pos[j] = j;
+        for (int j = 0; j < nhi; j++) hi_pos[j] = nlo + j;
+        rc = run_pe(d_vals, make_map(hi_pos, nhi), make_map(lo_pos, nlo), e_lo, T);
+    }
+    if (rc == MB_OK) {
+        {
+            MB_KERNEL("k8_dot");
+            dot_kernel<<<grid, 256, 0, MB_STREAM>>>(e_hi, T, nh, partial);
+        }
+        {
+            MB_KERNEL("k8_sum_rows");
+            sum_rows_kernel<<<1, 32, 0, MB_STREAM>>>(partial, 1, grid, partial + 8 * (size_t)grid);
+        }
+        uint64_t* h = pinned_scratch();
+        if (!h || cudaMemcpyAsync(h, partial + 8 * (size_t)grid, 64, cudaMemcpyDeviceToHost, MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
+        if (rc == MB_OK) rc = finish_sync();
+        if (rc == MB_OK) std::memcpy(h_out, h, 64);
+    }
+    pool_free(e_lo); pool_free(e_hi); pool_free(T); pool_free(partial);
+    return rc;
+}
+
+// d_out[x] = d_in[sum_j ((x >> pos[j]) & 1) << j], x < n; pos is a host array of nv bit positions.
+int agl_mpiop_gather(const uint64_t* d_in, const int* pos, int nv, uint64_t n, uint64_t* d_out) {
+    if (!d_in || !d_out || nv < 0 || nv > MAXV || (nv && !pos)) return MB_ERR_ARG;
+    if (n == 0) return MB_OK;
+    MB_KERNEL("k8_gather");
+    gather_kernel<<<grid_for(n * 8, 256, 8), 256, 0, MB_STREAM>>>(d_in, make_map(pos, nv), n, d_out);
+    return finish_async();
+}
+
+// d_out[i] = d_table[(d_sel[i] >> shift) & mask]
+int agl_mpiop_sel_lookup(const uint64_t* d_sel, uint64_t n, int shift, uint64_t mask, const uint64_t* d_table, uint64_t* d_out) {
+    if (!d_sel || !d_table || !d_out || shift < 0 || shift > 63) return MB_ERR_ARG;
+    if (n == 0) return MB_OK;
+    MB_KERNEL("k8_sel_lookup");
+    sel_lookup_kernel<<<grid_for(n * 8, 256, 8), 256, 0, MB_STREAM>>>(d_sel, n, shift, mask, d_table, d_out);
+    return finish_async();
+}
+
 }  // extern "C"

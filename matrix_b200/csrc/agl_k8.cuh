@@ -267,5 +267,100 @@ static __global__ void lift_kernel(const uint64_t* __restrict__ in, uint64_t n, 
         out[t] = (t & 7) == 0 ? agl::canon(in[t >> 3]) : 0;
 }
 
+// ---- helpers over base-field tables (morpheus_piop.cuh:20-140,160-172) ---------------------------
+constexpr int MAXV = 32;
+struct VarMap {
+    int n;
+    int pos[MAXV];
+};
+// bit j of x goes to bit pos[j]
+__device__ __forceinline__ uint64_t deposit(uint64_t x, const VarMap& m) {
+    uint64_t r = 0;
+    for (int j = 0; j < m.n; j++) r |= ((x >> j) & 1ULL) << m.pos[j];
+    return r;
+}
+
+// Partial evaluation of a base-field table against a K table e over the `fix` variables:
+//   out[r] = sum_f vals[deposit(r, rest) | deposit(f, fix)] e[f].
+// A block handles output r = blockIdx.x (grid-stride) and the slice blockIdx.y of f: 32 sub-lanes times the
+// eight coefficient lanes; partial[(r * gridDim.y + blockIdx.y) * 8 + c], summed by sum_rows_kernel.
+static __global__ void __launch_bounds__(256)
+pe_kernel(const uint64_t* __restrict__ vals, VarMap rest, VarMap fix, const uint64_t* __restrict__ e, uint64_t nrest,
+          uint64_t nfix, uint64_t* __restrict__ partial) {
+    __shared__ uint64_t red[32][8];
+    const int c = threadIdx.x & 7, sub = threadIdx.x >> 3;
+    const uint64_t per = (nfix + gridDim.y - 1) / gridDim.y;
+    const uint64_t f0 = (uint64_t)blockIdx.y * per, f1 = f0 + per < nfix ? f0 + per : nfix;
+    for (uint64_t r = blockIdx.x; r < nrest; r += gridDim.x) {
+        const uint64_t ro = deposit(r, rest);
+        gl::Acc acc = gl::acc_zero();
+        for (uint64_t f = f0 + sub; f < f1; f += 32) {
+            const uint64_t v = vals[ro | deposit(f, fix)];
+            if (v) gl::acc_mul(acc, agl::canon(v), e[8 * f + c]);
+        }
+        red[sub][c] = agl::acc_reduce_wide(acc);
+        __syncthreads();
+        if (sub == 0) {
+            uint64_t s = 0;
+            for (int k = 0; k < 32; k++) s = agl::add(s, red[k][c]);
+            partial[(r * gridDim.y + blockIdx.y) * 8 + c] = agl::canon(s);
+        }
+        __syncthreads();
+    }
+}
+// out[r * 8 + c] = sum over `rows` partial rows
+static __global__ void sum_rows_kernel(const uint64_t* __restrict__ partial, uint64_t nout, int rows, uint64_t* __restrict__ out) {
+    const uint64_t total = nout * 8, step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step) {
+        const uint64_t r = t >> 3;
+        const int c = (int)(t & 7);
+        uint64_t s = 0;
+        for (int k = 0; k < rows; k++) s = agl::add(s, partial[(r * rows + k) * 8 + c]);
+        out[t] = agl::canon(s);
+    }
+}
+
+// sum_x a[x] b[x] over K: partial[blockIdx.x * 8 + c] (block sums; eight lanes per element).
+static __global__ void __launch_bounds__(256)
+dot_kernel(const uint64_t* __restrict__ a, const uint64_t* __restrict__ b, uint64_t n, uint64_t* __restrict__ partial) {
+    __shared__ uint64_t red[8][8];
+    const int c = threadIdx.x & 7, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t groups = ((uint64_t)gridDim.x * blockDim.x) >> 3;
+    const uint64_t rounds = (n + groups - 1) / groups;
+    uint64_t x = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3, s = 0;
+    for (uint64_t it = 0; it < rounds; it++, x += groups) {
+        const bool live = x < n;
+        const uint64_t av = live ? a[8 * x + c] : 0, bv = live ? b[8 * x + c] : 0;
+        s = agl::add(s, mul_lane(av, bv, c));
+    }
+    s = agl::add(s, __shfl_xor_sync(0xffffffffu, s, 8));
+    s = agl::add(s, __shfl_xor_sync(0xffffffffu, s, 16));
+    if (lane < 8) red[warp][lane] = s;
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        uint64_t v = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) v = agl::add(v, red[w][threadIdx.x]);
+        partial[(uint64_t)blockIdx.x * 8 + threadIdx.x] = agl::canon(v);
+    }
+}
+
+// out[x] = in[sum_j ((x >> pos[j]) & 1) << j]  (morpheus_piop.cuh:166-172)
+static __global__ void gather_kernel(const uint64_t* __restrict__ in, VarMap m, uint64_t n, uint64_t* __restrict__ out) {
+    const uint64_t total = n * 8, step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step) {
+        const uint64_t x = t >> 3;
+        uint64_t idx = 0;
+        for (int j = 0; j < m.n; j++) idx |= ((x >> m.pos[j]) & 1ULL) << j;
+        out[t] = in[8 * idx + (t & 7)];
+    }
+}
+// out[i] = table[(sel[i] >> shift) & mask]  (morpheus_piop.cuh:160-164)
+static __global__ void sel_lookup_kernel(const uint64_t* __restrict__ sel, uint64_t n, int shift, uint64_t mask,
+                                         const uint64_t* __restrict__ table, uint64_t* __restrict__ out) {
+    const uint64_t total = n * 8, step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step)
+        out[t] = table[8 * ((sel[t >> 3] >> shift) & mask) + (t & 7)];
+}
+
 }  // namespace k8
 }  // namespace mb

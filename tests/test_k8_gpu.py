@@ -138,3 +138,65 @@ def test_eq_outer_axpy_lift(lib):
     lib.cuda_device_synchronize()
     got = d_k.to_numpy().reshape(n, 8)
     assert np.array_equal(got[:, 0], base % np.uint64(Q)) and not got[:, 1:].any()
+
+
+def _py_kmul_base(e, v):
+    return [(int(x) * int(v)) % Q for x in e]
+
+
+def test_partial_eval_mle_gather_lookup(lib):
+    oracle = pyoracle.load()
+    rng = np.random.default_rng(3)
+    # partial evaluation over a permuted split of 9 variables: 4 stay, 5 are bound
+    n = 9
+    perm = rng.permutation(n)
+    rest_pos, fix_pos = np.array(perm[:4], dtype=np.int32), np.array(perm[4:], dtype=np.int32)
+    vals = field_elems(50, 1 << n, Q)
+    vals[::3] = 0
+    vals[1::5] = 1
+    point = field_elems(51, 8 * 5, Q)
+    e = np.zeros(8 << 5, dtype=np.uint64)
+    oracle.oracle_k8_eq_table(point.ctypes.data, 5, e.ctypes.data)
+    d_v, d_e, d_o = DeviceBuffer.from_numpy(lib, vals), DeviceBuffer.from_numpy(lib, e), DeviceBuffer(lib, 64 << 4)
+    assert lib.agl_mpiop_pe(d_v.ptr, rest_pos.ctypes.data, 4, fix_pos.ctypes.data, 5, d_e.ptr, d_o.ptr) == 0
+    lib.cuda_device_synchronize()
+    got = d_o.to_numpy().reshape(16, 8)
+    dep = lambda x, pos: sum(((x >> j) & 1) << int(pos[j]) for j in range(len(pos)))
+    for r in range(16):
+        acc = [0] * 8
+        for f in range(32):
+            v = int(vals[dep(r, rest_pos) | dep(f, fix_pos)])
+            acc = [(a + int(x) * v) % Q for a, x in zip(acc, e[8 * f:8 * f + 8])]
+        assert [int(x) for x in got[r]] == acc
+    # multilinear extension at a K point, several sizes (n = 0, odd, even)
+    for nn in (0, 1, 7, 12):
+        vv = field_elems(60 + nn, 1 << nn, Q)
+        pt = field_elems(70 + nn, 8 * max(nn, 1), Q)
+        table = np.zeros(8 << nn, dtype=np.uint64)
+        oracle.oracle_k8_eq_table(pt.ctypes.data, nn, table.ctypes.data)
+        exp = [0] * 8
+        for x in range(1 << nn):
+            exp = [(a + int(t) * int(vv[x])) % Q for a, t in zip(exp, table[8 * x:8 * x + 8])]
+        d_vv = DeviceBuffer.from_numpy(lib, vv)
+        out = np.zeros(8, dtype=np.uint64)
+        assert lib.agl_mpiop_mle(d_vv.ptr, pt.ctypes.data, nn, out.ctypes.data) == 0
+        assert [int(x) for x in out] == exp
+    # gather and selector lookup
+    src = field_elems(80, 8 << 6, Q)
+    pos = np.array([5, 0, 9, 3, 7, 2], dtype=np.int32)
+    nout = 1 << 10
+    d_s, d_g = DeviceBuffer.from_numpy(lib, src), DeviceBuffer(lib, 64 * nout)
+    assert lib.agl_mpiop_gather(d_s.ptr, pos.ctypes.data, 6, nout, d_g.ptr) == 0
+    lib.cuda_device_synchronize()
+    g = d_g.to_numpy().reshape(nout, 8)
+    for x in range(0, nout, 37):
+        idx = sum(((x >> int(pos[j])) & 1) << j for j in range(6))
+        assert np.array_equal(g[x], src[8 * idx:8 * idx + 8])
+    sel = rng.integers(0, 2**63, size=500, dtype=np.uint64)
+    d_sel, d_l = DeviceBuffer.from_numpy(lib, sel), DeviceBuffer(lib, 64 * 500)
+    assert lib.agl_mpiop_sel_lookup(d_sel.ptr, 500, 7, 63, d_s.ptr, d_l.ptr) == 0
+    lib.cuda_device_synchronize()
+    look = d_l.to_numpy().reshape(500, 8)
+    for i in range(0, 500, 13):
+        k = (int(sel[i]) >> 7) & 63
+        assert np.array_equal(look[i], src[8 * k:8 * k + 8])
