@@ -247,3 +247,34 @@ def prove_sharded(make_shard, transcript, comm, point, K, nv, g_bits):
                 round_msgs=np.array(round_msgs, dtype=np.uint64), challenges=np.array(challenges, dtype=np.uint64),
                 finals=np.array(finals, dtype=np.uint64), final_eval=np.array(final_eval, dtype=np.uint64),
                 state=transcript.state())
+
+
+# ---- Ajtai commitment sharded by column ranges -------------------------------------------------
+AGL_Q = 0xFFFFFFFEFFFFFFE1
+
+
+def column_range(n_ring, world, rank):
+    """Ring columns [lo, hi) of `rank`: contiguous, as even as possible."""
+    base, extra = divmod(n_ring, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def commit_sharded(commit_columns, comm, n_ring, planes):
+    """c = sum_j M[:, j] z_j is a sum over columns: every rank commits its own column range against the
+    matching window of the matrix (`col_offset`, the reference's ajtai_commit_dense_batched_at_ffi,
+    almost-goldilocks-cuda-rs/src/ffi.rs:500-508; sharding design almost-goldilocks-cuda-rs tests
+    ajtai_integration.rs:296-328), the partial commitments (planes x 42 x 64 words) are all-gathered and added
+    mod q. `commit_columns(lo, hi)` returns this rank's partial commitment as a uint64 array (zeros for an
+    empty range). Returns the same array on every process."""
+    parts = []
+    for g in comm.local_ranks:
+        lo, hi = column_range(n_ring, comm.world, g)
+        part = np.ascontiguousarray(commit_columns(lo, hi), dtype=np.uint64)
+        assert part.size == planes * 42 * 64
+        parts.append(part)
+    gathered = comm.allgather(parts)
+    total = np.zeros(planes * 42 * 64, dtype=object)
+    for p in gathered:
+        total = (total + p.astype(object)) % AGL_Q
+    return np.array(total, dtype=np.uint64)
