@@ -35,7 +35,7 @@ constexpr int TC_THREADS = 256;
 constexpr uint32_t TC_CORE = 128;       // bytes of one 8 x 16 core matrix
 constexpr uint32_t TC_SBO = (TC_STAGE_K / 16) * TC_CORE;  // 2048: next 8-row group
 constexpr uint32_t TC_A_BYTES = 16 * TC_SBO;              // 128 rows
-constexpr int TC_V_STRIDE = 144;        // bytes per shifted copy of the reversed digit window
+constexpr int TC_V_STRIDE = 144;        // bytes per reversed digit window (128 + padding, 16-byte multiple)
 
 enum TcError { TC_OK = 0, TC_ERR_DIGIT_RANGE = 1, TC_ERR_TIMEOUT = 2 };
 
@@ -75,8 +75,8 @@ commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ 
     const int n_cols = 64 * np;                       // UMMA N
     uint8_t* A_sh = smem;                             // 32 KB
     uint8_t* B_sh = smem + TC_A_BYTES;                // (n_cols / 8) * 2048
-    uint8_t* V_sh = B_sh + (size_t)(n_cols / 8) * TC_SBO;  // [4 cols][np][4 copies][144]
-    int8_t* Z_sh = reinterpret_cast<int8_t*>(V_sh + TC_STAGE_COLS * TC_MAX_PLANES * 4 * TC_V_STRIDE);  // [4][np][64]
+    uint8_t* V_sh = B_sh + (size_t)(n_cols / 8) * TC_SBO;  // [4 cols][np][144]
+    int8_t* Z_sh = reinterpret_cast<int8_t*>(V_sh + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE);  // [4][np][64]
     __shared__ __align__(8) uint64_t mbar;
     __shared__ uint32_t tmem_base_sh;
 
@@ -130,37 +130,44 @@ commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ 
             prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
             uint32_t kk = (uint32_t)(jj * D + 8 * blk);
             uint8_t* dst = A_sh + il * TC_SBO + (kk >> 4) * TC_CORE + (kk & 15);
+            // Two lanes fill one 128-byte core (8 plane rows x 16 bytes). The plane order is rotated by the
+            // lane pair so that the lanes of a store instruction spread over the rows (banks) instead of
+            // all writing the same row of different cores.
+            const int rot = (t >> 1) & 3;
 #pragma unroll
             for (int b = 0; b < 8; b++) {
+                const int bp = (b & 4) | ((b + rot) & 3);
                 uint32_t w[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) w[x] = b < 4 ? (uint32_t)c[x] : (uint32_t)(c[x] >> 32);
-                const uint32_t sel = (uint32_t)(b & 3) | ((4u + (uint32_t)(b & 3)) << 4);
+                const uint32_t sel = (uint32_t)(bp & 3) | ((4u + (uint32_t)(bp & 3)) << 4);
                 uint32_t lo = __byte_perm(__byte_perm(w[0], w[1], sel), __byte_perm(w[2], w[3], sel), 0x5410);
                 uint32_t hi = __byte_perm(__byte_perm(w[4], w[5], sel), __byte_perm(w[6], w[7], sel), 0x5410);
-                *reinterpret_cast<uint2*>(dst + b * 16) = make_uint2(lo, hi);
+                *reinterpret_cast<uint2*>(dst + bp * 16) = make_uint2(lo, hi);
             }
         }
         __syncthreads();
-        // ---- v: reversed, sign-wrapped digit windows, four byte-shifted copies ----
-        // v[s + 63] = z[-s] for s <= 0, -z[64 - s] for s > 0, s in [-63, 63]; copy a holds v shifted by a bytes
-        for (int x = t; x < TC_STAGE_COLS * np * 4 * 128; x += TC_THREADS) {
-            int y = x & 127, a = (x >> 7) & 3, cp = x >> 9;  // cp = jj * np + p
-            int s = y + a - 63;
-            int8_t val = 0;
-            if (s >= -63 && s <= 63) {
-                const int8_t* z = Z_sh + cp * D;
-                val = s <= 0 ? z[-s] : (int8_t)(-z[64 - s]);
-            }
-            V_sh[(cp * 4 + a) * TC_V_STRIDE + y] = (uint8_t)val;
+        // ---- w: the reversed, sign-wrapped digit window of every (column, plane): w[i] = z[63 - i] for i < 64,
+        // -z[127 - i] for 64 <= i < 128, one word (four digits) per thread and step; word 32 is padding ----
+        for (int x = t; x < TC_STAGE_COLS * np * 33; x += TC_THREADS) {
+            const int cp = x / 33, q = x % 33;  // cp = jj * np + p
+            const uint32_t* zw = reinterpret_cast<const uint32_t*>(Z_sh + cp * D);
+            uint32_t v = 0;
+            if (q < 16) v = __byte_perm(zw[15 - q], 0, 0x0123);
+            else if (q < 32) v = __vneg4(__byte_perm(zw[31 - q], 0, 0x0123));
+            reinterpret_cast<uint32_t*>(V_sh + cp * TC_V_STRIDE)[q] = v;
         }
         __syncthreads();
-        // ---- B[(p, r)][(jj, k)] = v[k - r + 63], 16-byte chunks along k ----
+        // ---- B[(p, r)][(jj, k)] = w[63 - r + k], 16-byte chunks along k cut out of w at any byte offset
+        // (five aligned words, funnel shifts). Consecutive lanes take consecutive rows of one core (16 bytes
+        // apart): a store instruction covers whole 128-byte cores. ----
         for (int x = t; x < n_cols * 16; x += TC_THREADS) {
-            int n = x >> 4, kc = x & 15, p = n >> 6, r = n & 63, jj = kc >> 2, cq = kc & 3;
-            int w0 = 16 * cq - r + 63, a = w0 & 3, base = w0 - a;
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(V_sh + ((jj * np + p) * 4 + a) * TC_V_STRIDE + base);
-            uint4 v = make_uint4(src[0], src[1], src[2], src[3]);
+            int n = ((x >> 7) << 3) | (x & 7), kc = (x >> 3) & 15, p = n >> 6, r = n & 63, jj = kc >> 2, cq = kc & 3;
+            const int s0 = 63 - r + 16 * cq, sh = 8 * (s0 & 3);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(V_sh + (jj * np + p) * TC_V_STRIDE) + (s0 >> 2);
+            const uint32_t w0 = src[0], w1 = src[1], w2 = src[2], w3 = src[3], w4 = src[4];
+            uint4 v = make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                                 __funnelshift_r(w3, w4, sh));
             *reinterpret_cast<uint4*>(B_sh + (n >> 3) * TC_SBO + kc * TC_CORE + (n & 7) * 16) = v;
         }
         // generic-proxy writes -> visible to the tensor core (async proxy)
@@ -243,7 +250,7 @@ static __global__ void reduce_tc_partials_kernel(const uint64_t* __restrict__ pa
 }
 
 inline size_t tc_smem_bytes(int np) {
-    return TC_A_BYTES + (size_t)(64 * np / 8) * TC_SBO + TC_STAGE_COLS * TC_MAX_PLANES * 4 * TC_V_STRIDE +
+    return TC_A_BYTES + (size_t)(64 * np / 8) * TC_SBO + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE +
            TC_STAGE_COLS * TC_MAX_PLANES * D;
 }
 
