@@ -183,6 +183,13 @@ def run_batched(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         comm = TorchComm(device=torch.device("cuda", local))
+        if args.exchange == "shm":
+            from matrix_b200.sharded import ShmComm
+            path = "/dev/shm/matrix_b200_mailbox_%s" % os.environ.get("MASTER_PORT", "0")
+            if rank == 0 and os.path.exists(path):
+                os.remove(path)
+            dist.barrier()
+            comm = ShmComm(path, rank, world)
     n_loc = nv - g_bits
     m = 1 << n_loc
     # this rank's slices, made on the device: instance k, table a / b, entries [rank * m, (rank + 1) * m)
@@ -251,7 +258,8 @@ def run_batched(args):
             "warmup": args.warmup, "ms_per_step": val / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": "batched_sumcheck nv=%d instances=%d" % (nv, K), "sharding": "top %d variables" % g_bits,
-                       "collective": "one all-gather of 64 B per rank and round (NCCL)", "l2": "tables larger than L2"},
+                       "collective": "one all-gather of 48 B per rank and round (%s)" % ("NCCL" if args.exchange == "nccl" else "host shared memory"),
+                       "l2": "tables larger than L2"},
             "roofline": roofline,
             "kernel_times_ms": {k: {"launches": c, "ms": round(x, 4)} for k, (c, x) in sorted(kernels.items())},
             "gpu_launches": int(launches), "clocks": clocks,
@@ -451,6 +459,9 @@ def main():
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "shm"],
+                    help="batched_sumcheck at N > 1: how the ranks exchange their round messages (48 bytes per rank and "
+                         "round): an NCCL all-gather, or a mailbox file in host shared memory (one node)")
     ap.add_argument("--hash", default="poseidon2", choices=["poseidon2", "monolith"],
                     help="Merkle hash of the basefold workload (the transcript is Poseidon2 either way); the headline "
                          "metric names Poseidon2, the reference's default cargo features select Monolith")

@@ -46,3 +46,15 @@ def test_two_gloo_ranks(tmp_path):
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=280)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert os.path.exists(out + ".0") and os.path.exists(out + ".1")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_shared_memory_exchange(tmp_path, world):
+    """The host mailbox exchange between processes of one node: 200 ordered calls, then a whole sharded proof."""
+    path = str(tmp_path / "mailbox")
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "shm_worker.py"), path, str(r), str(world)],
+                              cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = [p.communicate(timeout=280)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\\n".join(o[-1500:] for o in outs)
+    assert all(os.path.exists("%s.ok.%d" % (path, r)) for r in range(world))
