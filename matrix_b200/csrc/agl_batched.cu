@@ -27,7 +27,7 @@ constexpr int BLK = 256;
 
 __device__ __forceinline__ E2 ld(const uint64_t* p) { return agl::e2_load(p); }
 __device__ __forceinline__ void st(uint64_t* p, E2 v) { agl::e2_store(p, agl::e2_canon(v)); }
-__device__ __forceinline__ E2 fold2(E2 a, E2 b, E2 r) { return agl::e2_add(a, agl::e2_mul(r, agl::e2_sub(b, a))); }
+__device__ __forceinline__ E2 fold2(E2 a, E2 b, E2 r) { return agl::e2_fma_pre(agl::e2_pre(r), agl::e2_sub(b, a), a); }
 __device__ __forceinline__ uint64_t bit_at(const uint64_t* packed, size_t i) { return (packed[i >> 6] >> (i & 63)) & 1ULL; }
 
 // partial[(blockIdx.x * gridDim.y + blockIdx.y) * 2 NV ...] = this block's sums
@@ -54,9 +54,9 @@ eqf_message_kernel(const uint64_t* __restrict__ eq_base, size_t eq_stride, const
         const E2 e2 = agl::e2_sub(agl::e2_add(e1, e1), e0);
         if (F_MODE == 0) {
             const E2 f0 = ld(f + 4 * y), f1 = ld(f + 4 * y + 2);
-            acc[0] = agl::e2_add(acc[0], agl::e2_mul(e0, f0));
-            acc[1] = agl::e2_add(acc[1], agl::e2_mul(e1, f1));
-            acc[2] = agl::e2_add(acc[2], agl::e2_mul(e2, agl::e2_sub(agl::e2_add(f1, f1), f0)));
+            acc[0] = agl::e2_add(acc[0], agl::e2_mul_lazy(e0, f0));
+            acc[1] = agl::e2_add(acc[1], agl::e2_mul_lazy(e1, f1));
+            acc[2] = agl::e2_add(acc[2], agl::e2_mul_lazy(e2, agl::e2_sub(agl::e2_add(f1, f1), f0)));
         } else {
             const uint64_t word = f[(2 * y) >> 6];
             const int f0 = (int)((word >> ((2 * y) & 63)) & 1), f1 = (int)((word >> ((2 * y + 1) & 63)) & 1);
@@ -82,8 +82,8 @@ factored_message_kernel(const uint64_t* __restrict__ eqsuf, size_t eqsuf_stride,
     const size_t step = (size_t)gridDim.x * blockDim.x;
     for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
         const E2 w = ld(e + 2 * y);
-        acc[0] = agl::e2_add(acc[0], agl::e2_mul(w, ld(f + 4 * y)));
-        acc[1] = agl::e2_add(acc[1], agl::e2_mul(w, ld(f + 4 * y + 2)));
+        acc[0] = agl::e2_add(acc[0], agl::e2_mul_lazy(w, ld(f + 4 * y)));
+        acc[1] = agl::e2_add(acc[1], agl::e2_mul_lazy(w, ld(f + 4 * y + 2)));
     }
     store_block_sums<2>(acc, partial);
 }

@@ -152,6 +152,36 @@ GLF E2 e2_mul(E2 a, E2 b) {
     return E2{add(m0, mul_small(m1, 3)), sub(sub(x, m0), m1)};
 }
 GLF E2 e2_mul_base(E2 a, uint64_t b) { return E2{mul(a.c0, b), mul(a.c1, b)}; }
+
+// Products through exact 160-bit sums reduced once (gl::Acc), as for Goldilocks.
+// One product: four multiplications, three reductions, no modular additions inside.
+GLF E2 e2_mul_lazy(E2 a, E2 b) {
+    gl::Acc s00 = gl::acc_zero(), s11 = gl::acc_zero(), s01 = gl::acc_zero();
+    gl::acc_mul(s00, a.c0, b.c0);
+    gl::acc_mul(s11, a.c1, b.c1);
+    gl::acc_mul(s01, a.c0, b.c1);
+    gl::acc_mul(s01, a.c1, b.c0);
+    return E2{add(agl::acc_reduce(s00), mul_small(agl::acc_reduce(s11), 3)), agl::acc_reduce(s01)};
+}
+// A loop-invariant factor with 3 c1 precomputed: a + r d needs four products and two reductions.
+struct E2Pre {
+    uint64_t c0, c1, c1w;
+};
+GLF E2Pre e2_pre(E2 r) { return E2Pre{canon(r.c0), canon(r.c1), canon(mul_small(canon(r.c1), 3))}; }
+GLF E2 e2_fma_pre(E2Pre r, E2 d, E2 a) {
+    gl::Acc s0 = gl::acc_from(a.c0), s1 = gl::acc_from(a.c1);
+    gl::acc_mul(s0, r.c0, d.c0);
+    gl::acc_mul(s0, r.c1w, d.c1);
+    gl::acc_mul(s1, r.c0, d.c1);
+    gl::acc_mul(s1, r.c1, d.c0);
+    return E2{agl::acc_reduce(s0), agl::acc_reduce(s1)};
+}
+GLF E2 e2_fma_pre_base(E2Pre r, uint64_t d, uint64_t a) {
+    gl::Acc s0 = gl::acc_from(a), s1 = gl::acc_zero();
+    gl::acc_mul(s0, r.c0, d);
+    gl::acc_mul(s1, r.c1, d);
+    return E2{agl::acc_reduce(s0), agl::acc_reduce(s1)};
+}
 GLF E2 e2_inv(E2 a) {
     uint64_t n = sub(sqr(a.c0), mul_small(sqr(a.c1), 3));
     uint64_t ni = inv(n);

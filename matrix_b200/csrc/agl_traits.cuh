@@ -52,7 +52,7 @@ struct AglExt2 {
     }
     static __device__ __forceinline__ T add(T a, T b) { return agl::e2_add(a, b); }
     static __device__ __forceinline__ T sub(T a, T b) { return agl::e2_sub(a, b); }
-    static __device__ __forceinline__ T mul(T a, T b) { return agl::e2_mul(a, b); }
+    static __device__ __forceinline__ T mul(T a, T b) { return agl::e2_mul_lazy(a, b); }
     static __device__ __forceinline__ T zero() { return agl::E2{0, 0}; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
 };
@@ -60,8 +60,13 @@ struct AglExt2 {
 template <>
 struct FoldOp<AglBase, AglExt2> {
     static __device__ __forceinline__ agl::E2 apply(uint64_t a, uint64_t b, agl::E2 r) {
-        uint64_t d = agl::sub(b, a);
-        return agl::E2{agl::add(a, agl::mul(r.c0, d)), agl::mul(r.c1, d)};
+        return agl::e2_fma_pre_base(agl::e2_pre(r), agl::sub(b, a), a);
+    }
+};
+template <>
+struct FoldOp<AglExt2, AglExt2> {
+    static __device__ __forceinline__ agl::E2 apply(agl::E2 a, agl::E2 b, agl::E2 r) {
+        return agl::e2_fma_pre(agl::e2_pre(r), agl::e2_sub(b, a), a);
     }
 };
 

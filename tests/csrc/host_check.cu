@@ -7,6 +7,7 @@
 #include "host/gl_transcript.hpp"
 #include "gl_monolith.cuh"
 #include "host/agl_transcript.hpp"
+#include "agl_mcommit.cuh"
 
 extern "C" {
 uint64_t hc_gl_add(uint64_t a, uint64_t b) { return gl::add(a, b); }
@@ -32,6 +33,24 @@ uint64_t hc_agl_inv(uint64_t a) { return agl::inv(a); }
 void hc_aext2_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) {
     agl::E2 r = agl::e2_mul(agl::E2{a[0], a[1]}, agl::E2{b[0], b[1]});
     o[0] = r.c0; o[1] = r.c1;
+}
+void hc_aext2_mul_lazy(const uint64_t* a, const uint64_t* b, uint64_t* o) {
+    agl::E2 r = agl::e2_mul_lazy(agl::E2{a[0], a[1]}, agl::E2{b[0], b[1]});
+    o[0] = agl::canon(r.c0); o[1] = agl::canon(r.c1);
+}
+void hc_aext2_fma_pre(const uint64_t* r, const uint64_t* d, const uint64_t* a, uint64_t* o) {
+    agl::E2 v = agl::e2_fma_pre(agl::e2_pre(agl::E2{r[0], r[1]}), agl::E2{d[0], d[1]}, agl::E2{a[0], a[1]});
+    o[0] = agl::canon(v.c0); o[1] = agl::canon(v.c1);
+}
+void hc_aext2_fma_pre_base(const uint64_t* r, uint64_t d, uint64_t a, uint64_t* o) {
+    agl::E2 v = agl::e2_fma_pre_base(agl::e2_pre(agl::E2{r[0], r[1]}), d, a);
+    o[0] = agl::canon(v.c0); o[1] = agl::canon(v.c1);
+}
+void hc_mcm_shake(const uint32_t* seed, uint32_t counter, const uint32_t* nonce, uint32_t* out) {
+    mcm::shake_key_block(seed, counter, nonce, out);
+}
+void hc_mcm_key_block(const uint32_t* seed, uint32_t kind, uint32_t row, uint64_t col, uint32_t b, uint64_t* vals) {
+    mcm::key_block8(seed, kind, row, col, b, vals);
 }
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
 // sum_i x[i] * y[i] + c through the lazy accumulator

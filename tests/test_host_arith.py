@@ -184,3 +184,21 @@ def test_lazy_accumulators(hostcheck):
             c0 = sum(int(a[2 * i]) * int(b[2 * i]) + 7 * int(a[2 * i + 1]) * int(b[2 * i + 1]) for i in range(n)) % P
             c1 = sum(int(a[2 * i]) * int(b[2 * i + 1]) + int(a[2 * i + 1]) * int(b[2 * i]) for i in range(n)) % P
             assert (O[0], O[1]) == (c0, c1)
+
+
+def test_almost_goldilocks_extension_lazy_forms(hostcheck):
+    """Products of F_q[X]/(X^2 - 3) through exact sums reduced once, loose inputs."""
+    hc = hostcheck
+    Q = 2**64 - 2**32 - 31
+    hc.hc_aext2_fma_pre_base.argtypes = [ctypes.c_void_p, u64, u64, ctypes.c_void_p]
+    rnd = random.Random(33)
+    pick = lambda: rnd.choice([rnd.randrange(2**64), 2**64 - 1, Q - 1, Q, Q + 1, 0, 1])
+    for _ in range(600):
+        r, d, a = ([pick() for _ in range(2)] for _ in range(3))
+        R, D, A, O = (u64 * 2)(*r), (u64 * 2)(*d), (u64 * 2)(*a), (u64 * 2)()
+        hc.hc_aext2_mul_lazy(R, D, O)
+        assert (O[0], O[1]) == ((r[0] * d[0] + 3 * r[1] * d[1]) % Q, (r[0] * d[1] + r[1] * d[0]) % Q)
+        hc.hc_aext2_fma_pre(R, D, A, O)
+        assert (O[0], O[1]) == ((a[0] + r[0] * d[0] + 3 * r[1] * d[1]) % Q, (a[1] + r[0] * d[1] + r[1] * d[0]) % Q)
+        hc.hc_aext2_fma_pre_base(R, d[0], a[0], O)
+        assert (O[0], O[1]) == ((a[0] + r[0] * d[0]) % Q, (r[1] * d[0]) % Q)
