@@ -245,6 +245,23 @@ int agl_mpiop_mle(const uint64_t* d_vals, const uint64_t* h_point, int n, uint64
 int agl_mpiop_gather(const uint64_t* d_in, const int* pos, int nv, uint64_t n, uint64_t* d_out);
 int agl_mpiop_sel_lookup(const uint64_t* d_sel, uint64_t n, int shift, uint64_t mask, const uint64_t* d_table, uint64_t* d_out);
 
+/* ---- exact module commitment over F_q[Y]/(Y^4096 + 1) ----
+ * Replaces almost-goldilocks-cuda-rs/src/ffi.rs:18-21 (definitions cuda/wrapper.cu:3129-3229; kernels
+ * cuda_almost_goldilocks/morpheus_commit.cuh; CPU definition zk-torch-4/src/morpheus/commit.rs:48-83,
+ * ring.rs, keys.rs:48-93; Rust caller zk-torch-4/src/morpheus/commit_gpu.rs:27-97).
+ * C[v][row] = sum_c centre(A_kind[row][col_c]) * x[v][c] as integer negacyclic products, reduced mod q
+ * at the end, exact while twice the largest |coefficient| stays below the product of the first k of the
+ * five 31-bit primes 2147377153, 2147352577, 2147295233, 2147205121, 2147196929 (k = 3 for ternary
+ * inputs, 5 for 37-bit ones). Buffers between the calls: d_key u32 [k][ncols][rows][4096], d_acc u32
+ * [V][k][rows][4096]; their contents are transform-domain residues in this library's own order (a cache
+ * built with k primes serves calls with fewer). rows <= 16, V <= 8, x_bytes 1 (int8) or 8 (int64). */
+int agl_mcommit_keygen(const uint32_t* h_seed, uint32_t kind, int rows, uint64_t col0, int ncols, int k, uint32_t* d_key);
+int agl_mcommit_partial(const uint32_t* d_key, int kcols, int rows, int k, const void* d_x, int x_bytes, int V, int C,
+                        uint64_t x_vstride, const uint32_t* d_colidx, uint32_t* d_acc);
+int agl_mcommit_add(uint32_t* d_dst, const uint32_t* d_src, int V, int k, int rows);
+/* d_out u64 [V][rows][4096] canonical; d_err int64 [V][rows][4096] or null is added; d_acc is left unchanged. */
+int agl_mcommit_finish(uint32_t* d_acc, int V, int k, int rows, const int64_t* d_err, uint64_t* d_out);
+
 /* ---- host side: Monolith over almost-Goldilocks and the transcript on it ----
  * The reference keeps these in Rust: permutation and SHA-256-derived round constants
  * zk-torch-4/src/crypto/monolith.rs:66-208, transcript zk-torch-4/src/transcript.rs:22-243 (width 12,

@@ -45,6 +45,7 @@ LIBRARIES = {
         "agl_ajtai.cu",
         "agl_batch.cu",
         "agl_k8.cu",
+        "agl_mcommit.cu",
         "agl_batched.cu",
         "agl_ajtai_fold.cu",
         "host/agl_transcript.cu",

@@ -289,6 +289,10 @@ _AGL_SIGNATURES = {
     "agl_mpiop_mle": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "agl_mpiop_gather": (c_int, [c_void_p, c_void_p, c_int, c_u64, c_void_p]),
     "agl_mpiop_sel_lookup": (c_int, [c_void_p, c_u64, c_int, c_u64, c_void_p, c_void_p]),
+    "agl_mcommit_keygen": (c_int, [c_void_p, ctypes.c_uint32, c_int, c_u64, c_int, c_int, c_void_p]),
+    "agl_mcommit_partial": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_u64, c_void_p, c_void_p]),
+    "agl_mcommit_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int]),
+    "agl_mcommit_finish": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "agl_monolith_permute_host": (c_int, [c_void_p]),
     "agl_monolith_round_constants": (c_int, [c_void_p]),
     "agl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),

@@ -296,3 +296,42 @@ def k8_sc_fold(tab, r):
     out = np.zeros(len(tab) // 2, dtype=np.uint64)
     lib.oracle_k8_sc_fold(tab.ctypes.data, len(tab) // 8, np.ascontiguousarray(r, dtype=np.uint64).ctypes.data, out.ctypes.data)
     return out
+
+
+# ---- module commitment over F_q[Y]/(Y^4096 + 1) ----------------------------------------
+_SIGS.update({
+    "oracle_shake256_short": (None, [vp, sz, vp, sz]),
+    "oracle_mcommit_shake_block": (None, [vp, ctypes.c_uint32, vp, vp]),
+    "oracle_mcommit_key_element": (None, [vp, ctypes.c_uint32, ctypes.c_uint32, u64, vp]),
+    "oracle_mcommit_commit": (None, [vp, ctypes.c_uint32, ci, vp, ci, vp, vp, vp]),
+})
+
+
+def mcommit_shake_block(seed, counter, nonce):
+    import numpy as np
+    s = np.ascontiguousarray(seed, dtype=np.uint32)
+    n = np.ascontiguousarray(nonce, dtype=np.uint32)
+    out = np.zeros(16, dtype=np.uint32)
+    load().oracle_mcommit_shake_block(s.ctypes.data, counter, n.ctypes.data, out.ctypes.data)
+    return out
+
+
+def mcommit_key_element(seed, kind, row, col):
+    import numpy as np
+    s = np.ascontiguousarray(seed, dtype=np.uint32)
+    out = np.zeros(4096, dtype=np.uint64)
+    load().oracle_mcommit_key_element(s.ctypes.data, kind, row, col, out.ctypes.data)
+    return out
+
+
+def mcommit_commit(seed, kind, rows, cols, x, err=None):
+    """x: int64 [len(cols)][4096]; err: int64 [rows][4096] or None; returns uint64 [rows][4096]."""
+    import numpy as np
+    s = np.ascontiguousarray(seed, dtype=np.uint32)
+    c = np.ascontiguousarray(cols, dtype=np.uint64)
+    xx = np.ascontiguousarray(x, dtype=np.int64).reshape(len(c), 4096)
+    e = None if err is None else np.ascontiguousarray(err, dtype=np.int64).reshape(rows, 4096)
+    out = np.zeros((rows, 4096), dtype=np.uint64)
+    load().oracle_mcommit_commit(s.ctypes.data, kind, rows, c.ctypes.data, len(c), xx.ctypes.data,
+                                 None if e is None else e.ctypes.data, out.ctypes.data)
+    return out
