@@ -313,6 +313,31 @@ def column_range(n_ring, world, rank):
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+def _sum_column_shards(commit_columns, comm, ncols, words):
+    """All-gathers the ranks' partial results over their column ranges and adds them mod q."""
+    parts = []
+    for g in comm.local_ranks:
+        lo, hi = column_range(ncols, comm.world, g)
+        part = np.ascontiguousarray(commit_columns(lo, hi), dtype=np.uint64).reshape(-1)
+        assert part.size == words
+        parts.append(part)
+    gathered = comm.allgather(parts)
+    total = np.zeros(words, dtype=object)
+    for p in gathered:
+        total = (total + p.astype(object)) % AGL_Q
+    return np.array(total, dtype=np.uint64)
+
+
+def module_commit_sharded(commit_columns, comm, ncols, vectors, rows):
+    """The module commitment over F_q[Y]/(Y^4096 + 1) is a sum over key columns
+    (zk-torch-4/src/morpheus/commit_gpu.rs:1-8: partial per column range and GPU, then add): every rank
+    builds the key cache of its own column range (`col0` of agl_mcommit_keygen), commits its columns and
+    finishes; each shard's integer is exact on its own, so the finished words (vectors x rows x 4096) add
+    mod q. `commit_columns(lo, hi)` returns this rank's finished partial commitment (zeros for an empty
+    range, without the identity error, which the caller adds once). Same array on every process."""
+    return _sum_column_shards(commit_columns, comm, ncols, vectors * rows * 4096)
+
+
 def commit_sharded(commit_columns, comm, n_ring, planes):
     """c = sum_j M[:, j] z_j is a sum over columns: every rank commits its own column range against the
     matching window of the matrix (`col_offset`, the reference's ajtai_commit_dense_batched_at_ffi,
@@ -320,14 +345,4 @@ def commit_sharded(commit_columns, comm, n_ring, planes):
     ajtai_integration.rs:296-328), the partial commitments (planes x 42 x 64 words) are all-gathered and added
     mod q. `commit_columns(lo, hi)` returns this rank's partial commitment as a uint64 array (zeros for an
     empty range). Returns the same array on every process."""
-    parts = []
-    for g in comm.local_ranks:
-        lo, hi = column_range(n_ring, comm.world, g)
-        part = np.ascontiguousarray(commit_columns(lo, hi), dtype=np.uint64)
-        assert part.size == planes * 42 * 64
-        parts.append(part)
-    gathered = comm.allgather(parts)
-    total = np.zeros(planes * 42 * 64, dtype=object)
-    for p in gathered:
-        total = (total + p.astype(object)) % AGL_Q
-    return np.array(total, dtype=np.uint64)
+    return _sum_column_shards(commit_columns, comm, n_ring, planes * 42 * 64)

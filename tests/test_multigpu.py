@@ -44,3 +44,16 @@ def test_column_sharded_ajtai_over_nccl(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     for g in range(n):
         assert os.path.exists("%s.%d" % (out, g))
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs at least two GPUs")
+def test_column_sharded_module_commit_over_nccl(tmp_path):
+    n = min(_gpu_count(), 8)
+    out = str(tmp_path / "done")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr",
+           "127.0.0.1", "--master-port", "29549", os.path.join(ROOT, "tests", "sharded_mcommit_worker.py"), out, "gpu"]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    for g in range(n):
+        assert os.path.exists("%s.%d" % (out, g))
