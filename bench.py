@@ -319,7 +319,10 @@ def _event_timer(lib):
 def run_simple(args):
     """Single-GPU lines for the two other kernels of the path (parity cases in tests/, not the headline):
     sumcheck: one sumcheck of f * g over 2^20 points (base-field tables, extension challenges), tables resident;
-    ajtai:    ring commit, 2^18 ring columns (2^24 coefficients), signed 8-bit digit planes on the tensor cores."""
+    ajtai:    ring commit, 2^18 ring columns (2^24 coefficients), signed 8-bit digit planes on the tensor cores;
+    mcommit:  exact module commitment over F_q[Y]/(Y^4096+1): 8192 ternary columns x 16 rows against a resident
+              transform-domain key cache, three primes (the shape of the reference's own throughput test,
+              zk-torch-4/src/morpheus/commit_gpu.rs:170-186); columns split across the ranks."""
     rank, world, local = dist_env()
     if args.workload == "sumcheck" and rank != 0:
         return
@@ -346,6 +349,58 @@ def run_simple(args):
         alg_bytes = d * n * 8 * (1 + 1 + 1.5 * 2)  # round 0 read; fold read + half-size ext write; later rounds halve
         h2d, d2h = polys.nbytes, rm.nbytes + fe.nbytes
         scaling = "weak"
+    elif args.workload == "mcommit":
+        from matrix_b200 import load_agl
+        from matrix_b200.sharded import SingleComm, TorchComm, column_range, module_commit_sharded
+        lib = load_agl()
+        assert lib.cuda_set_device(local) == 0
+        comm = SingleComm(1)
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            comm = TorchComm(device=torch.device("cuda", local))
+        ncols, rows, kp, NR = (args.num_vars if args.num_vars != 24 else 8192), 16, 3, 4096
+        lo, hi = column_range(ncols, world, rank)
+        cols = hi - lo
+        seed = np.ones(8, dtype=np.uint32)
+        d_key = DeviceBuffer(lib, kp * cols * rows * NR * 4)
+        assert lib.agl_mcommit_keygen(seed.ctypes.data, 1, rows, lo, cols, kp, d_key.ptr) == 0   # key material: untimed
+        x = np.random.default_rng(5 + rank).integers(-1, 2, size=cols * NR, dtype=np.int8)
+        d_x = DeviceBuffer.from_numpy(lib, x)
+        d_acc, d_o = DeviceBuffer(lib, kp * rows * NR * 4), DeviceBuffer(lib, rows * NR * 8)
+        out = np.zeros(rows * NR, dtype=np.uint64)
+
+        def device_commit():
+            rc = lib.agl_mcommit_partial(d_key.ptr, cols, rows, kp, d_x.ptr, 1, 1, cols, 0, None, d_acc.ptr)
+            return rc or lib.agl_mcommit_finish(d_acc.ptr, 1, kp, rows, None, d_o.ptr)
+
+        def local_commit(a, b):
+            assert device_commit() == 0
+            lib.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
+            return out
+
+        def step():
+            if world == 1:
+                return device_commit()
+            module_commit_sharded(local_commit, comm, ncols, 1, rows)
+            return 0
+
+        def step_e2e():
+            lib.cuda_memcpy_htod(d_x.ptr, x.ctypes.data, x.nbytes)
+            if world == 1:
+                device_commit()
+                lib.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
+            else:
+                module_commit_sharded(local_commit, comm, ncols, 1, rows)
+        units = ncols * NR
+        metric = "field-elems/s: module commitment over F_q[Y]/(Y^4096+1), 16 rows, ternary columns, almost-Goldilocks"
+        workload = "mcommit cols=%d rows=16 primes=3 int8" % ncols
+        # the key cache is read once (16 KB per prime, column and row); the transformed inputs are written and read once
+        alg_bytes = float(kp * cols * rows * NR * 4 + 2 * kp * cols * NR * 4 + cols * NR)
+        h2d, d2h = x.nbytes, out.nbytes
+        scaling = "strong"
     else:
         # the witness columns are split across the ranks (strong scaling); partial commitments are all-gathered
         # (planes x 42 x 64 words per rank) and added mod q
@@ -424,7 +479,9 @@ def run_simple(args):
     ms_e2e = timed_max(step_e2e, args.steps)
     line = {"metric": metric, "value": units * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling,
-            "vs_baseline": None, "dtype": "u64" if args.workload == "sumcheck" else "s8 x u8 -> s32, u64 recombination",
+            "vs_baseline": None,
+            "dtype": {"sumcheck": "u64", "mcommit": "u32 residues mod five 31-bit primes, u64 recombination"}.get(
+                args.workload, "s8 x u8 -> s32, u64 recombination"),
             "data": "synthetic", "config": {"workload": workload},
             "e2e": {"value": units * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
@@ -432,14 +489,27 @@ def run_simple(args):
     if alg_bytes is not None:
         ach = alg_bytes * args.steps / (ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                            "peak_kind": peak_kind, "note": "whole proof (all rounds, host transcript between them) against "
-                                                            "the bytes its passes must move; small tables are latency bound"}
+                            "peak_kind": peak_kind,
+                            "note": ("whole call (input transforms, streaming accumulate, finish) against the bytes of this "
+                                     "rank's key cache and transformed inputs; the accumulate kernel alone runs near the copy peak")
+                            if args.workload == "mcommit" else
+                            "whole proof (all rounds, host transcript between them) against the bytes its passes must move; "
+                            "small tables are latency bound"}
     else:
         macs = 2688.0 * units * 8 * 3
         line["roofline"] = {"bound": "tensor", "achieved": 2 * macs * args.steps / (ms * 1e-3) / 1e12, "peak": None,
                             "unit": "int8 TOP/s", "frac": None, "traffic": None,
                             "note": "the matrix is regenerated from the ChaCha8 stream in every pass; generation and the "
                                     "operand build bound the kernel, not the tensor pipe"}
+    if args.workload == "mcommit" and rank == 0 and not args.no_cpu_baseline:
+        # the oracle's schoolbook products (what the reference's CPU test compares with, commit.rs:92-131) on two columns
+        from oracle import pyoracle
+        xs = np.random.default_rng(1).integers(-1, 2, size=(2, 4096)).astype(np.int64)
+        t0 = time.perf_counter()
+        pyoracle.mcommit_commit([1] * 8, 1, 16, [0, 1], xs)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 2 * 4096 / dt, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                                "sample": "2 columns x 16 rows, schoolbook negacyclic products with key expansion (OpenMP over rows)"}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
@@ -455,7 +525,7 @@ def main():
     ap.add_argument("--num-vars", type=int, default=24)
     ap.add_argument("--ref-num-vars", type=int, default=20, help="sample size of the CPU arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai"],
+    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit"],
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
@@ -472,7 +542,7 @@ def main():
         else:
             run_batched(args)
         return
-    if args.workload in ("sumcheck", "ajtai"):
+    if args.workload in ("sumcheck", "ajtai", "mcommit"):
         run_simple(args)
         return
 

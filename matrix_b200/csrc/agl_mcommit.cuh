@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(NT, sizeof(TX) == 1 ? 3 : 2) input_ntt_kernel(
 // part[chunk][v][prime][row][j] = sum over the chunk's columns of key[prime][col(c)][row][j] * xh[v][prime][c][j].
 // Thread = (prime, j, group of R rows); block (128, rows / R); grid (k * 4096 / 128, chunks).
 template <int V, int R>
-__global__ void __launch_bounds__(128 * (MAXROWS / R)) mac_kernel(const uint32_t* __restrict__ key, int kcols, int rows,
+__global__ void __launch_bounds__(128 * (MAXROWS / R), V == 1 ? 6 : V == 2 ? 5 : V <= 4 ? 2 : 1) mac_kernel(const uint32_t* __restrict__ key, int kcols, int rows,
                                                                   const uint32_t* __restrict__ xh, const uint32_t* __restrict__ colidx,
                                                                   int C, int k, int chunk_cols, uint32_t* __restrict__ part) {
     const int j = blockIdx.x * 128 + threadIdx.x;
