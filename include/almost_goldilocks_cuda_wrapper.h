@@ -262,6 +262,49 @@ int agl_mcommit_add(uint32_t* d_dst, const uint32_t* d_src, int V, int k, int ro
 /* d_out u64 [V][rows][4096] canonical; d_err int64 [V][rows][4096] or null is added; d_acc is left unchanged. */
 int agl_mcommit_finish(uint32_t* d_acc, int V, int k, int rows, const int64_t* d_err, uint64_t* d_out);
 
+/* ---- packed link sumcheck ----
+ * Replaces almost-goldilocks-cuda-rs/src/ffi.rs:511-593 (definitions cuda/wrapper.cu:1213-1440, kernels
+ * cuda_almost_goldilocks/link_sumcheck.cuh; CPU definition zk-torch-4/src/pcs/link.rs:284-357).
+ * Extension elements are two u64; tables are rows of `stride` elements per commitment; the HIGH index bit is
+ * bound first (pairs (idx, half + idx)). Round messages: d_out = [S(0..3), E(0..2)], seven canonical elements,
+ * S(k) = sum_e tag_e sum_idx eq[idx] R(w_e(k)[idx]) with R(u) = u^3 - u, E(k) = sum_e sum_idx omega_e(k)[idx]
+ * w_e(k)[idx]; with first_round != 0 (and in the round0_bits forms) S(0) = S(1) = 0. d_partial is scratch of
+ * n_commit * chunks * 7 elements; chunks = grid width per commitment. Support lists: d_list slices
+ * [d_list_off[e], + d_list_len[e]) of pair indices, eq then indexed by list position. Interleaved layout: block
+ * b = idx & block_mask, weight = scale[e][b] * eq(idx >> block_bits, pts[e][b][round .. leaf_arity)). */
+int link_round_message_ffi(const uint64_t* d_w, const uint64_t* d_omega, const uint64_t* d_eq_suffix, const uint64_t* d_tags,
+                           uint64_t stride, uint64_t omega_stride, uint64_t half, uint64_t n_commit, int first_round,
+                           uint64_t* d_partial, uint64_t chunks, uint64_t* d_out);
+int link_round_message_sparse_ffi(const uint64_t* d_w, const uint64_t* d_omega, const uint64_t* d_eq_suffix, const uint64_t* d_tags,
+                                  const uint32_t* d_list, const uint64_t* d_list_off, const uint64_t* d_list_len, uint64_t stride,
+                                  uint64_t omega_stride, uint64_t half, uint64_t n_commit, int first_round, uint64_t* d_partial,
+                                  uint64_t chunks, uint64_t* d_out);
+int link_round0_bits_ffi(const uint64_t* d_bits, const uint64_t* d_omega, const uint64_t* d_eq, const uint64_t* d_tags, uint64_t stride,
+                         uint64_t half, uint64_t n_commit, uint64_t* d_partial, uint64_t chunks, uint64_t* d_out);
+int link_round0_bits_sparse_ffi(const uint64_t* d_bits, const uint64_t* d_omega, const uint64_t* d_eq, const uint64_t* d_tags,
+                                const uint32_t* d_list, const uint64_t* d_list_off, const uint64_t* d_list_len, uint64_t stride,
+                                uint64_t half, uint64_t n_commit, uint64_t* d_partial, uint64_t chunks, uint64_t* d_out);
+int link_round_interleaved_ffi(const uint64_t* d_bits, const uint64_t* d_w, const uint64_t* d_pts, const uint64_t* d_scale,
+                               const uint64_t* d_eq, const uint64_t* d_tags, const uint32_t* d_list, const uint64_t* d_list_off,
+                               const uint64_t* d_list_len, uint64_t w_stride, uint64_t bits_stride_words, uint64_t half,
+                               uint64_t n_commit, uint32_t block_mask, int block_bits, int leaf_arity, int round, int first_round,
+                               uint64_t* d_partial, uint64_t chunks, uint64_t* d_out);
+/* t[i] = lo + r (hi - lo), in place on both tables (rows of stride / omega_stride). */
+int link_fold_ffi(uint64_t* d_w, uint64_t* d_omega, uint64_t stride, uint64_t omega_stride, uint64_t half, uint64_t n_commit,
+                  uint64_t r_c0, uint64_t r_c1);
+int link_fold_sparse_ffi(uint64_t* d_w, uint64_t* d_omega, const uint32_t* d_list, const uint64_t* d_list_off,
+                         const uint64_t* d_list_len, uint64_t stride, uint64_t half, uint64_t n_commit, uint64_t r_c0, uint64_t r_c1);
+/* bits in (rows of stride bits), d_w_out rows of `half` elements, d_omega (rows of stride) folded in place. */
+int link_fold0_bits_ffi(const uint64_t* d_bits, uint64_t* d_w_out, uint64_t* d_omega, uint64_t stride, uint64_t half, uint64_t n_commit,
+                        uint64_t r_c0, uint64_t r_c1);
+int link_fold_w_ffi(const uint64_t* d_bits, const uint64_t* d_w_in, uint64_t* d_w_out, uint64_t in_stride, uint64_t bits_stride_words,
+                    uint64_t out_stride, uint64_t half, uint64_t n_commit, int first_round, uint64_t r_c0, uint64_t r_c1);
+/* table[i], table[span + i] = v (1 - r), v r for i < span. */
+int link_eq_expand_ffi(uint64_t* d_table, uint64_t span, uint64_t r_c0, uint64_t r_c1);
+int link_omega_expand_ffi(uint64_t* d_omega, const uint64_t* d_bases, const uint64_t* d_rs, uint64_t span, uint64_t n_active);
+int link_expand_bits_ffi(const uint64_t* d_bits, uint64_t* d_out, uint64_t n_words);
+int link_eq_gather_ffi(const uint64_t* d_alpha, uint64_t n_vars, const uint32_t* d_list, uint64_t* d_out, uint64_t total);
+
 /* ---- host side: Monolith over almost-Goldilocks and the transcript on it ----
  * The reference keeps these in Rust: permutation and SHA-256-derived round constants
  * zk-torch-4/src/crypto/monolith.rs:66-208, transcript zk-torch-4/src/transcript.rs:22-243 (width 12,

@@ -46,6 +46,7 @@ LIBRARIES = {
         "agl_batch.cu",
         "agl_k8.cu",
         "agl_mcommit.cu",
+        "agl_link.cu",
         "agl_batched.cu",
         "agl_ajtai_fold.cu",
         "host/agl_transcript.cu",

@@ -1,0 +1,468 @@
+// C-ABI: the packed link sumcheck over the almost-Goldilocks extension (reference declarations
+// almost-goldilocks-cuda-rs/src/ffi.rs:511-593, definitions almost-goldilocks-cuda-rs/cuda/wrapper.cu:1213-1440,
+// kernels cuda_almost_goldilocks/link_sumcheck.cuh:59-787; CPU definition zk-torch-4/src/pcs/link.rs:284-357).
+//
+// Per round, with R(u) = u^3 - u and the HIGH index bit bound first (pairs (idx, half + idx)):
+//     S(k) = sum_e tag_e sum_idx eq[idx] R(w_e(k)[idx])       k = 0..3
+//     E(k) = sum_e       sum_idx omega_e(k)[idx] w_e(k)[idx]   k = 0..2
+// out = [S(0..3), E(0..2)]: seven extension elements, canonical. In the first round S(0), S(1) are zero
+// by definition (committed coefficients lie in {-1, 0, 1}).
+//
+// One kernel template covers every form: witness from a table or from packed bits, index set dense or a
+// support list, weights from a table or evaluated on demand for the interleaved layout.
+//
+// Bit-packed witnesses need no multiplication at all: with (lo, hi) in {0, 1}^2 the interpolants are small
+// integers, R(w(2)) = 6 and R(w(3)) = 24 on (0, 1), R(w(3)) = -6 on (1, 0), zero otherwise, and the weight
+// products are signed selections, so the round is additions of eq and omega values and is bound by the
+// reads of omega; the small factors are applied once per block.
+#include "agl_field.cuh"
+#include "common.cuh"
+#include "prof.cuh"
+
+using namespace mb;
+
+namespace {
+
+using agl::E2;
+constexpr int SLOTS = 7, NORM = 4, BLOCK = 256;
+
+__device__ __forceinline__ E2 ld(const uint64_t* p, uint64_t i) { return agl::e2_load(p + 2 * i); }
+__device__ __forceinline__ void st(uint64_t* p, uint64_t i, E2 v) { agl::e2_store(p + 2 * i, agl::e2_canon(v)); }
+__device__ __forceinline__ E2 zero() { return E2{0, 0}; }
+__device__ __forceinline__ bool is_zero(E2 v) { return (agl::canon(v.c0) | agl::canon(v.c1)) == 0; }
+__device__ __forceinline__ unsigned bit_at(const uint64_t* bits, uint64_t i) { return (unsigned)((bits[i >> 6] >> (i & 63)) & 1ULL); }
+__device__ __forceinline__ E2 range_poly(E2 u) { return agl::e2_sub(agl::e2_mul_lazy(agl::e2_mul_lazy(u, u), u), u); }
+__device__ __forceinline__ E2 fold2(E2 lo, E2 hi, agl::E2Pre r) { return agl::e2_fma_pre(r, agl::e2_sub(hi, lo), lo); }
+__device__ __forceinline__ E2 mul_small(E2 a, uint32_t k) { return E2{agl::mul_small(a.c0, k), agl::mul_small(a.c1, k)}; }
+
+// eq(l, pt[0..m)) with pt most significant variable first.
+__device__ __forceinline__ E2 eq_pointwise(const uint64_t* pt, uint64_t l, int m) {
+    E2 acc{1, 0};
+    for (int k = 0; k < m; k++) {
+        const E2 r = ld(pt, k);
+        acc = agl::e2_mul_lazy(acc, ((l >> (m - 1 - k)) & 1ULL) ? r : agl::e2_sub(E2{1, 0}, r));
+    }
+    return acc;
+}
+
+struct RoundArgs {
+    const uint64_t* bits;      // witness bits, rows of bits_stride_words (BITS)
+    const uint64_t* w;         // witness table, rows of w_stride (!BITS)
+    const uint64_t* omega;     // weight table, rows of omega_stride (!ONDEMAND)
+    const uint64_t* pts;       // [n_commit][blocks][leaf_arity] (ONDEMAND)
+    const uint64_t* scale;     // [n_commit][blocks] (ONDEMAND)
+    const uint64_t* eq;        // by idx (dense) or by list position (LISTED)
+    const uint64_t* tags;
+    const uint32_t* list;
+    const uint64_t* list_off;
+    const uint64_t* list_len;
+    uint64_t w_stride, bits_stride_words, omega_stride, half;
+    uint32_t block_mask;
+    int block_bits, leaf_arity, round, first_round;
+    uint64_t* partial;         // [n_commit][chunks][7]
+};
+
+// grid (chunks, n_commit), 256 threads.
+template <bool BITS, bool LISTED, bool ONDEMAND>
+__global__ void __launch_bounds__(BLOCK) link_round_kernel(RoundArgs a) {
+    const uint64_t e = blockIdx.y, chunk = blockIdx.x, nchunk = gridDim.x;
+    const int tid = threadIdx.x;
+    const uint64_t* be = BITS ? a.bits + e * a.bits_stride_words : nullptr;
+    const uint64_t* we = BITS ? nullptr : a.w + 2 * e * a.w_stride;
+    const uint64_t* oe = ONDEMAND ? nullptr : a.omega + 2 * e * a.omega_stride;
+    const uint64_t loff = LISTED ? a.list_off[e] : 0;
+    const uint64_t n = LISTED ? a.list_len[e] : a.half;
+    const uint64_t blocks = (uint64_t)a.block_mask + 1;
+    const int m = a.leaf_arity - a.round;
+
+    // BITS: acc[0] = sum of eq over (0,1) pairs, acc[1] = over (1,0) pairs, acc[4..6] as defined.
+    E2 acc[SLOTS];
+#pragma unroll
+    for (int k = 0; k < SLOTS; k++) acc[k] = zero();
+
+    for (uint64_t t = chunk * BLOCK + tid; t < n; t += nchunk * BLOCK) {
+        const uint64_t idx = LISTED ? (uint64_t)a.list[loff + t] : t;
+        unsigned blo = 0, bhi = 0;
+        E2 w_lo = zero(), w_hi = zero();
+        if (BITS) {
+            blo = bit_at(be, idx);
+            bhi = bit_at(be, a.half + idx);
+            if (!(blo | bhi)) continue;
+        } else {
+            w_lo = ld(we, idx);
+            w_hi = ld(we, a.half + idx);
+            if (!LISTED && is_zero(w_lo) && is_zero(w_hi)) continue;
+        }
+        E2 o_lo, o_hi;
+        if (ONDEMAND) {
+            const uint64_t b = idx & a.block_mask;
+            const uint64_t* ptb = a.pts + 2 * ((e * blocks + b) * (uint64_t)a.leaf_arity + (uint64_t)a.round);
+            const E2 sc = ld(a.scale, e * blocks + b);
+            o_lo = agl::e2_mul_lazy(sc, eq_pointwise(ptb, idx >> a.block_bits, m));
+            o_hi = agl::e2_mul_lazy(sc, eq_pointwise(ptb, (a.half + idx) >> a.block_bits, m));
+        } else {
+            o_lo = ld(oe, idx);
+            o_hi = ld(oe, a.half + idx);
+        }
+        const E2 eqs = ld(a.eq, LISTED ? loff + t : idx);
+        if (BITS) {
+            if (blo != bhi) acc[blo ? 1 : 0] = agl::e2_add(acc[blo ? 1 : 0], eqs);
+            if (blo) acc[4] = agl::e2_add(acc[4], o_lo);
+            if (bhi) acc[5] = agl::e2_add(acc[5], o_hi);
+            const E2 o2 = agl::e2_sub(agl::e2_add(o_hi, o_hi), o_lo);   // omega(2); w(2) = 2 hi - lo in {-1, 1, 2}
+            if (blo && !bhi) acc[6] = agl::e2_sub(acc[6], o2);
+            else if (!blo) acc[6] = agl::e2_add(acc[6], agl::e2_add(o2, o2));
+            else acc[6] = agl::e2_add(acc[6], o2);
+        } else {
+            const E2 w_d = agl::e2_sub(w_hi, w_lo), o_d = agl::e2_sub(o_hi, o_lo);
+            const E2 w1 = agl::e2_add(w_lo, w_d), w2 = agl::e2_add(w1, w_d), w3 = agl::e2_add(w2, w_d);
+            if (!a.first_round) {
+                acc[0] = agl::e2_add(acc[0], agl::e2_mul_lazy(eqs, range_poly(w_lo)));
+                acc[1] = agl::e2_add(acc[1], agl::e2_mul_lazy(eqs, range_poly(w1)));
+            }
+            acc[2] = agl::e2_add(acc[2], agl::e2_mul_lazy(eqs, range_poly(w2)));
+            acc[3] = agl::e2_add(acc[3], agl::e2_mul_lazy(eqs, range_poly(w3)));
+            const E2 o1 = agl::e2_add(o_lo, o_d), o2 = agl::e2_add(o1, o_d);
+            acc[4] = agl::e2_add(acc[4], agl::e2_mul_lazy(o_lo, w_lo));
+            acc[5] = agl::e2_add(acc[5], agl::e2_mul_lazy(o1, w1));
+            acc[6] = agl::e2_add(acc[6], agl::e2_mul_lazy(o2, w2));
+        }
+    }
+    if (BITS) {
+        const E2 s01 = acc[0], s10 = acc[1];
+        acc[0] = zero();
+        acc[1] = zero();
+        acc[2] = mul_small(s01, 6);
+        acc[3] = agl::e2_sub(mul_small(s01, 24), mul_small(s10, 6));
+    }
+
+    // block sum: shuffles inside a warp, one shared-memory step across the eight warps
+    __shared__ uint64_t sh[BLOCK / 32][SLOTS][2];
+#pragma unroll
+    for (int k = 0; k < SLOTS; k++) {
+        E2 v = acc[k];
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            const E2 o{__shfl_down_sync(0xffffffffu, v.c0, off), __shfl_down_sync(0xffffffffu, v.c1, off)};
+            v = agl::e2_add(v, o);
+        }
+        if ((tid & 31) == 0) {
+            sh[tid >> 5][k][0] = v.c0;
+            sh[tid >> 5][k][1] = v.c1;
+        }
+    }
+    __syncthreads();
+    if (tid < SLOTS) {
+        E2 v = zero();
+        for (int wp = 0; wp < BLOCK / 32; wp++) v = agl::e2_add(v, E2{sh[wp][tid][0], sh[wp][tid][1]});
+        if (tid < NORM) v = agl::e2_mul_lazy(ld(a.tags, e), v);
+        st(a.partial, (e * nchunk + chunk) * SLOTS + tid, v);
+    }
+}
+
+// out[k] = sum of partial[b][k]; one block per slot.
+__global__ void __launch_bounds__(BLOCK) link_reduce_kernel(const uint64_t* __restrict__ partial, uint64_t n_blocks, uint64_t* __restrict__ out) {
+    const int k = blockIdx.x, tid = threadIdx.x;
+    E2 v = zero();
+    for (uint64_t b = tid; b < n_blocks; b += BLOCK) v = agl::e2_add(v, ld(partial, b * SLOTS + k));
+    __shared__ uint64_t sh[BLOCK / 32][2];
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+        const E2 o{__shfl_down_sync(0xffffffffu, v.c0, off), __shfl_down_sync(0xffffffffu, v.c1, off)};
+        v = agl::e2_add(v, o);
+    }
+    if ((tid & 31) == 0) {
+        sh[tid >> 5][0] = v.c0;
+        sh[tid >> 5][1] = v.c1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        E2 s = zero();
+        for (int wp = 0; wp < BLOCK / 32; wp++) s = agl::e2_add(s, E2{sh[wp][0], sh[wp][1]});
+        st(out, k, s);
+    }
+}
+
+// In-place fold of rows of two tables: t[i] = lo + r (hi - lo). `tb` may be null.
+__global__ void link_fold_kernel(uint64_t* __restrict__ ta, uint64_t* __restrict__ tb, uint64_t stride_a, uint64_t stride_b, uint64_t half,
+                                 uint64_t n_commit, E2 r) {
+    const agl::E2Pre rp = agl::e2_pre(r);
+    const uint64_t total = half * n_commit;
+    for (uint64_t t = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t e = t / half, i = t - e * half;
+        uint64_t* pa = ta + 2 * e * stride_a;
+        st(pa, i, fold2(ld(pa, i), ld(pa, half + i), rp));
+        if (tb) {
+            uint64_t* pb = tb + 2 * e * stride_b;
+            st(pb, i, fold2(ld(pb, i), ld(pb, half + i), rp));
+        }
+    }
+}
+
+// Same over support lists; grid (x, n_commit).
+__global__ void link_fold_sparse_kernel(uint64_t* __restrict__ w, uint64_t* __restrict__ omega, const uint32_t* __restrict__ list,
+                                        const uint64_t* __restrict__ list_off, const uint64_t* __restrict__ list_len, uint64_t stride,
+                                        uint64_t half, E2 r) {
+    const agl::E2Pre rp = agl::e2_pre(r);
+    const uint64_t e = blockIdx.y, n = list_len[e];
+    const uint32_t* le = list + list_off[e];
+    uint64_t *pw = w + 2 * e * stride, *po = omega + 2 * e * stride;
+    for (uint64_t t = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; t < n; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t i = le[t];
+        st(pw, i, fold2(ld(pw, i), ld(pw, half + i), rp));
+        st(po, i, fold2(ld(po, i), ld(po, half + i), rp));
+    }
+}
+
+// Witness fold out of place, from bits (a selection among 0, 1, r, 1 - r) or from a table; omega, when given, in place.
+template <bool BITS>
+__global__ void link_fold_w_kernel(const uint64_t* __restrict__ bits, const uint64_t* __restrict__ w_in, uint64_t* __restrict__ w_out,
+                                   uint64_t* __restrict__ omega, uint64_t in_stride, uint64_t bits_stride_words, uint64_t out_stride,
+                                   uint64_t omega_stride, uint64_t half, uint64_t n_commit, E2 r) {
+    const agl::E2Pre rp = agl::e2_pre(r);
+    const E2 rc = agl::e2_canon(r), omr = agl::e2_canon(agl::e2_sub(E2{1, 0}, r));
+    const uint64_t total = half * n_commit;
+    for (uint64_t t = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t e = t / half, i = t - e * half;
+        E2 v;
+        if (BITS) {
+            const uint64_t* be = bits + e * bits_stride_words;
+            const unsigned lo = bit_at(be, i), hi = bit_at(be, half + i);
+            v = lo ? (hi ? E2{1, 0} : omr) : (hi ? rc : zero());
+        } else {
+            const uint64_t* pi = w_in + 2 * e * in_stride;
+            v = fold2(ld(pi, i), ld(pi, half + i), rp);
+        }
+        st(w_out + 2 * e * out_stride, i, v);
+        if (omega) {
+            uint64_t* po = omega + 2 * e * omega_stride;
+            st(po, i, fold2(ld(po, i), ld(po, half + i), rp));
+        }
+    }
+}
+
+// table[i], table[span + i] = v (1 - r), v r for i < span; grid.y selects (base, r) pairs when given.
+__global__ void link_expand_kernel(uint64_t* __restrict__ table, const uint64_t* __restrict__ bases, const uint64_t* __restrict__ rs,
+                                   uint64_t span, E2 r_one) {
+    const uint64_t q = blockIdx.y;
+    uint64_t* tb = bases ? table + 2 * bases[q] : table;
+    const E2 r = rs ? ld(rs, q) : r_one;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < span; i += (uint64_t)gridDim.x * blockDim.x) {
+        const E2 v = ld(tb, i), vr = agl::e2_mul_lazy(v, r);
+        st(tb, i, agl::e2_sub(v, vr));
+        st(tb, span + i, vr);
+    }
+}
+
+// One thread per output pair of elements: 64 elements per input word.
+__global__ void link_expand_bits_kernel(const uint64_t* __restrict__ bits, uint64_t* __restrict__ out, uint64_t n_elems) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n_elems; i += (uint64_t)gridDim.x * blockDim.x)
+        agl::e2_store(out + 2 * i, E2{(uint64_t)bit_at(bits, i), 0});
+}
+
+__global__ void link_eq_gather_kernel(const uint64_t* __restrict__ alpha, uint64_t n_vars, const uint32_t* __restrict__ list,
+                                      uint64_t* __restrict__ out, uint64_t total) {
+    for (uint64_t t = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x)
+        st(out, t, eq_pointwise(alpha, list[t], (int)n_vars));
+}
+
+template <bool BITS, bool LISTED, bool ONDEMAND>
+int run_round(const RoundArgs& a, uint64_t n_commit, uint64_t chunks, uint64_t* d_out) {
+    if (!a.eq || !a.tags || !a.partial || !d_out || chunks == 0 || chunks > 0x7fffffffULL || n_commit > 65535) return MB_ERR_ARG;
+    if (n_commit == 0) {
+        MB_CUDA(cudaMemsetAsync(d_out, 0, SLOTS * 16, MB_STREAM));
+        return finish_sync();
+    }
+    {
+        MB_KERNEL("link_round");
+        dim3 grid((unsigned)chunks, (unsigned)n_commit);
+        link_round_kernel<BITS, LISTED, ONDEMAND><<<grid, BLOCK, 0, MB_STREAM>>>(a);
+    }
+    {
+        MB_KERNEL("link_reduce");
+        link_reduce_kernel<<<SLOTS, BLOCK, 0, MB_STREAM>>>(a.partial, n_commit * chunks, d_out);
+    }
+    return finish_sync();
+}
+
+RoundArgs base_args(const uint64_t* eq, const uint64_t* tags, uint64_t half, int first_round, uint64_t* partial) {
+    RoundArgs a{};
+    a.eq = eq;
+    a.tags = tags;
+    a.half = half;
+    a.first_round = first_round;
+    a.partial = partial;
+    return a;
+}
+
+}  // namespace
+
+extern "C" {
+
+int link_round_message_ffi(const uint64_t* d_w, const uint64_t* d_omega, const uint64_t* d_eq_suffix, const uint64_t* d_tags, uint64_t stride,
+                           uint64_t omega_stride, uint64_t half, uint64_t n_commit, int first_round, uint64_t* d_partial, uint64_t chunks,
+                           uint64_t* d_out) {
+    if (!d_w || !d_omega) return MB_ERR_ARG;
+    RoundArgs a = base_args(d_eq_suffix, d_tags, half, first_round, d_partial);
+    a.w = d_w;
+    a.omega = d_omega;
+    a.w_stride = stride;
+    a.omega_stride = omega_stride;
+    return run_round<false, false, false>(a, n_commit, chunks, d_out);
+}
+
+int link_round_message_sparse_ffi(const uint64_t* d_w, const uint64_t* d_omega, const uint64_t* d_eq_suffix, const uint64_t* d_tags,
+                                  const uint32_t* d_list, const uint64_t* d_list_off, const uint64_t* d_list_len, uint64_t stride,
+                                  uint64_t omega_stride, uint64_t half, uint64_t n_commit, int first_round, uint64_t* d_partial,
+                                  uint64_t chunks, uint64_t* d_out) {
+    if (!d_w || !d_omega || !d_list || !d_list_off || !d_list_len) return MB_ERR_ARG;
+    RoundArgs a = base_args(d_eq_suffix, d_tags, half, first_round, d_partial);
+    a.w = d_w;
+    a.omega = d_omega;
+    a.w_stride = stride;
+    a.omega_stride = omega_stride;
+    a.list = d_list;
+    a.list_off = d_list_off;
+    a.list_len = d_list_len;
+    return run_round<false, true, false>(a, n_commit, chunks, d_out);
+}
+
+int link_round0_bits_ffi(const uint64_t* d_bits, const uint64_t* d_omega, const uint64_t* d_eq, const uint64_t* d_tags, uint64_t stride,
+                         uint64_t half, uint64_t n_commit, uint64_t* d_partial, uint64_t chunks, uint64_t* d_out) {
+    if (!d_bits || !d_omega || (stride & 63)) return MB_ERR_ARG;
+    RoundArgs a = base_args(d_eq, d_tags, half, 1, d_partial);
+    a.bits = d_bits;
+    a.omega = d_omega;
+    a.bits_stride_words = stride >> 6;
+    a.omega_stride = stride;
+    return run_round<true, false, false>(a, n_commit, chunks, d_out);
+}
+
+int link_round0_bits_sparse_ffi(const uint64_t* d_bits, const uint64_t* d_omega, const uint64_t* d_eq, const uint64_t* d_tags,
+                                const uint32_t* d_list, const uint64_t* d_list_off, const uint64_t* d_list_len, uint64_t stride,
+                                uint64_t half, uint64_t n_commit, uint64_t* d_partial, uint64_t chunks, uint64_t* d_out) {
+    if (!d_bits || !d_omega || !d_list || !d_list_off || !d_list_len || (stride & 63)) return MB_ERR_ARG;
+    RoundArgs a = base_args(d_eq, d_tags, half, 1, d_partial);
+    a.bits = d_bits;
+    a.omega = d_omega;
+    a.bits_stride_words = stride >> 6;
+    a.omega_stride = stride;
+    a.list = d_list;
+    a.list_off = d_list_off;
+    a.list_len = d_list_len;
+    return run_round<true, true, false>(a, n_commit, chunks, d_out);
+}
+
+// Interleaved layout (block index in the low bits): weights scale[e][b] * eq(leaf index, pts[e][b][round..]).
+int link_round_interleaved_ffi(const uint64_t* d_bits, const uint64_t* d_w, const uint64_t* d_pts, const uint64_t* d_scale,
+                               const uint64_t* d_eq, const uint64_t* d_tags, const uint32_t* d_list, const uint64_t* d_list_off,
+                               const uint64_t* d_list_len, uint64_t w_stride, uint64_t bits_stride_words, uint64_t half, uint64_t n_commit,
+                               uint32_t block_mask, int block_bits, int leaf_arity, int round, int first_round, uint64_t* d_partial,
+                               uint64_t chunks, uint64_t* d_out) {
+    if (!d_pts || !d_scale || !d_list || !d_list_off || !d_list_len || round < 0 || round > leaf_arity || block_bits < 0 || block_bits > 31 ||
+        (first_round ? !d_bits : !d_w))
+        return MB_ERR_ARG;
+    RoundArgs a = base_args(d_eq, d_tags, half, first_round, d_partial);
+    a.bits = d_bits;
+    a.w = d_w;
+    a.pts = d_pts;
+    a.scale = d_scale;
+    a.w_stride = w_stride;
+    a.bits_stride_words = bits_stride_words;
+    a.list = d_list;
+    a.list_off = d_list_off;
+    a.list_len = d_list_len;
+    a.block_mask = block_mask;
+    a.block_bits = block_bits;
+    a.leaf_arity = leaf_arity;
+    a.round = round;
+    return first_round ? run_round<true, true, true>(a, n_commit, chunks, d_out) : run_round<false, true, true>(a, n_commit, chunks, d_out);
+}
+
+int link_fold_ffi(uint64_t* d_w, uint64_t* d_omega, uint64_t stride, uint64_t omega_stride, uint64_t half, uint64_t n_commit, uint64_t r_c0,
+                  uint64_t r_c1) {
+    if (!d_w || !d_omega) return MB_ERR_ARG;
+    if (half * n_commit == 0) return MB_OK;
+    MB_KERNEL("link_fold");
+    link_fold_kernel<<<grid_for(half * n_commit, BLOCK, 8), BLOCK, 0, MB_STREAM>>>(d_w, d_omega, stride, omega_stride, half, n_commit,
+                                                                                  E2{r_c0, r_c1});
+    return finish_sync();
+}
+
+int link_fold_sparse_ffi(uint64_t* d_w, uint64_t* d_omega, const uint32_t* d_list, const uint64_t* d_list_off, const uint64_t* d_list_len,
+                         uint64_t stride, uint64_t half, uint64_t n_commit, uint64_t r_c0, uint64_t r_c1) {
+    if (!d_w || !d_omega || !d_list || !d_list_off || !d_list_len || n_commit > 65535) return MB_ERR_ARG;
+    if (n_commit == 0) return MB_OK;
+    MB_KERNEL("link_fold_sparse");
+    dim3 grid((unsigned)(sm_count() * 8 / (n_commit < 8 ? n_commit : 8) + 1), (unsigned)n_commit);
+    link_fold_sparse_kernel<<<grid, BLOCK, 0, MB_STREAM>>>(d_w, d_omega, d_list, d_list_off, d_list_len, stride, half, E2{r_c0, r_c1});
+    return finish_sync();
+}
+
+// Round-0 fold: bits in, half-size table out (rows of `half`), omega folded in place (rows of `stride`).
+int link_fold0_bits_ffi(const uint64_t* d_bits, uint64_t* d_w_out, uint64_t* d_omega, uint64_t stride, uint64_t half, uint64_t n_commit,
+                        uint64_t r_c0, uint64_t r_c1) {
+    if (!d_bits || !d_w_out || !d_omega || (stride & 63)) return MB_ERR_ARG;
+    if (half * n_commit == 0) return MB_OK;
+    MB_KERNEL("link_fold0_bits");
+    link_fold_w_kernel<true><<<grid_for(half * n_commit, BLOCK, 8), BLOCK, 0, MB_STREAM>>>(d_bits, nullptr, d_w_out, d_omega, 0, stride >> 6, half,
+                                                                                          stride, half, n_commit, E2{r_c0, r_c1});
+    return finish_sync();
+}
+
+// Witness-only fold of the interleaved layout.
+int link_fold_w_ffi(const uint64_t* d_bits, const uint64_t* d_w_in, uint64_t* d_w_out, uint64_t in_stride, uint64_t bits_stride_words,
+                    uint64_t out_stride, uint64_t half, uint64_t n_commit, int first_round, uint64_t r_c0, uint64_t r_c1) {
+    if (!d_w_out || (first_round ? !d_bits : !d_w_in)) return MB_ERR_ARG;
+    if (half * n_commit == 0) return MB_OK;
+    MB_KERNEL("link_fold_w");
+    const int grid = grid_for(half * n_commit, BLOCK, 8);
+    if (first_round)
+        link_fold_w_kernel<true><<<grid, BLOCK, 0, MB_STREAM>>>(d_bits, nullptr, d_w_out, nullptr, 0, bits_stride_words, out_stride, 0, half,
+                                                                n_commit, E2{r_c0, r_c1});
+    else
+        link_fold_w_kernel<false><<<grid, BLOCK, 0, MB_STREAM>>>(nullptr, d_w_in, d_w_out, nullptr, in_stride, 0, out_stride, 0, half, n_commit,
+                                                                 E2{r_c0, r_c1});
+    return finish_sync();
+}
+
+// One variable of an eq table built most-significant variable first: the live span doubles.
+int link_eq_expand_ffi(uint64_t* d_table, uint64_t span, uint64_t r_c0, uint64_t r_c1) {
+    if (!d_table) return MB_ERR_ARG;
+    if (span == 0) return MB_OK;
+    MB_KERNEL("link_eq_expand");
+    link_expand_kernel<<<dim3((unsigned)grid_for(span, BLOCK, 8), 1), BLOCK, 0, MB_STREAM>>>(d_table, nullptr, nullptr, span, E2{r_c0, r_c1});
+    return finish_sync();
+}
+
+// The same step for n_active weight slices at once: slice q starts at element d_bases[q], challenge d_rs[q].
+int link_omega_expand_ffi(uint64_t* d_omega, const uint64_t* d_bases, const uint64_t* d_rs, uint64_t span, uint64_t n_active) {
+    if (!d_omega || !d_bases || !d_rs || n_active > 65535) return MB_ERR_ARG;
+    if (span == 0 || n_active == 0) return MB_OK;
+    MB_KERNEL("link_omega_expand");
+    unsigned gx = (unsigned)((span + BLOCK - 1) / BLOCK);
+    const unsigned cap = (unsigned)(sm_count() * 8 / (n_active < 8 ? n_active : 8) + 1);
+    if (gx > cap) gx = cap;
+    link_expand_kernel<<<dim3(gx, (unsigned)n_active), BLOCK, 0, MB_STREAM>>>(d_omega, d_bases, d_rs, span, E2{0, 0});
+    return finish_sync();
+}
+
+// d_out[n_words * 64] extension elements (bit, 0).
+int link_expand_bits_ffi(const uint64_t* d_bits, uint64_t* d_out, uint64_t n_words) {
+    if (!d_bits || !d_out) return MB_ERR_ARG;
+    if (n_words == 0) return MB_OK;
+    MB_KERNEL("link_expand_bits");
+    link_expand_bits_kernel<<<grid_for(n_words * 64, BLOCK, 8), BLOCK, 0, MB_STREAM>>>(d_bits, d_out, n_words * 64);
+    return finish_sync();
+}
+
+// d_out[t] = eq(d_list[t], alpha), alpha = n_vars extension elements, most significant variable first.
+int link_eq_gather_ffi(const uint64_t* d_alpha, uint64_t n_vars, const uint32_t* d_list, uint64_t* d_out, uint64_t total) {
+    if (!d_alpha || !d_list || !d_out || n_vars > 32) return MB_ERR_ARG;
+    if (total == 0) return MB_OK;
+    MB_KERNEL("link_eq_gather");
+    link_eq_gather_kernel<<<grid_for(total, BLOCK, 8), BLOCK, 0, MB_STREAM>>>(d_alpha, n_vars, d_list, d_out, total);
+    return finish_sync();
+}
+
+}  // extern "C"

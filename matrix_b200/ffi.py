@@ -293,6 +293,23 @@ _AGL_SIGNATURES = {
     "agl_mcommit_partial": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_u64, c_void_p, c_void_p]),
     "agl_mcommit_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int]),
     "agl_mcommit_finish": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "link_round_message_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64, c_u64, c_int, c_void_p, c_u64, c_void_p]),
+    "link_round_message_sparse_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64,
+                                              c_u64, c_int, c_void_p, c_u64, c_void_p]),
+    "link_round0_bits_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64, c_void_p, c_u64, c_void_p]),
+    "link_round0_bits_sparse_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64,
+                                            c_void_p, c_u64, c_void_p]),
+    "link_round_interleaved_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_u64, c_u64, c_u64, c_u64, ctypes.c_uint32, c_int, c_int, c_int, c_int, c_void_p, c_u64,
+                                           c_void_p]),
+    "link_fold_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_u64, c_u64, c_u64, c_u64]),
+    "link_fold_sparse_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64, c_u64, c_u64]),
+    "link_fold0_bits_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64, c_u64, c_u64]),
+    "link_fold_w_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_u64, c_u64, c_u64, c_int, c_u64, c_u64]),
+    "link_eq_expand_ffi": (c_int, [c_void_p, c_u64, c_u64, c_u64]),
+    "link_omega_expand_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64]),
+    "link_expand_bits_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
+    "link_eq_gather_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_void_p, c_u64]),
     "agl_monolith_permute_host": (c_int, [c_void_p]),
     "agl_monolith_round_constants": (c_int, [c_void_p]),
     "agl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),

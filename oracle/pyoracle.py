@@ -335,3 +335,68 @@ def mcommit_commit(seed, kind, rows, cols, x, err=None):
     load().oracle_mcommit_commit(s.ctypes.data, kind, rows, c.ctypes.data, len(c), xx.ctypes.data,
                                  None if e is None else e.ctypes.data, out.ctypes.data)
     return out
+
+
+# ---- packed link sumcheck ---------------------------------------------------------------
+u32 = ctypes.c_uint32
+_SIGS.update({
+    "oracle_link_round": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, u32, ci, ci, ci, ci, vp]),
+    "oracle_link_fold_rows": (None, [vp, u64, u64, u64, vp, vp, vp, u64, u64]),
+    "oracle_link_fold_w": (None, [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64]),
+    "oracle_link_eq_expand": (None, [vp, u64, u64, u64]),
+    "oracle_link_expand_bits": (None, [vp, vp, u64]),
+    "oracle_link_eq_gather": (None, [vp, u64, vp, vp, u64]),
+})
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data
+
+
+def link_round(eq, tags, half, n_commit, first_round, bits=None, w=None, omega=None, pts=None, scale=None, lists=None,
+               w_stride=0, bits_stride_words=0, omega_stride=0, block_mask=0, block_bits=0, leaf_arity=0, rnd=0):
+    """lists: (list u32, off u64, len u64) or None. Returns the 14 words [S(0..3), E(0..2)]."""
+    import numpy as np
+    out = np.zeros(14, dtype=np.uint64)
+    l, lo, ll = lists if lists is not None else (None, None, None)
+    load().oracle_link_round(_p(bits), _p(w), _p(omega), _p(pts), _p(scale), _p(eq), _p(tags), _p(l), _p(lo), _p(ll), w_stride,
+                             bits_stride_words, omega_stride, half, n_commit, block_mask, block_bits, leaf_arity, rnd,
+                             first_round, out.ctypes.data)
+    return out
+
+
+def link_fold_rows(tab, stride, half, n_commit, r, lists=None):
+    import numpy as np
+    t = np.array(tab, dtype=np.uint64, copy=True)
+    l, lo, ll = lists if lists is not None else (None, None, None)
+    load().oracle_link_fold_rows(t.ctypes.data, stride, half, n_commit, _p(l), _p(lo), _p(ll), int(r[0]), int(r[1]))
+    return t
+
+
+def link_fold_w(bits, w_in, in_stride, bits_stride_words, out_stride, half, n_commit, r):
+    import numpy as np
+    out = np.zeros(2 * n_commit * out_stride, dtype=np.uint64)
+    load().oracle_link_fold_w(_p(bits), _p(w_in), out.ctypes.data, in_stride, bits_stride_words, out_stride, half, n_commit,
+                              int(r[0]), int(r[1]))
+    return out
+
+
+def link_eq_expand(table, span, r):
+    import numpy as np
+    t = np.array(table, dtype=np.uint64, copy=True)
+    load().oracle_link_eq_expand(t.ctypes.data, span, int(r[0]), int(r[1]))
+    return t
+
+
+def link_expand_bits(bits):
+    import numpy as np
+    out = np.zeros(len(bits) * 128, dtype=np.uint64)
+    load().oracle_link_expand_bits(bits.ctypes.data, out.ctypes.data, len(bits))
+    return out
+
+
+def link_eq_gather(alpha, n_vars, lst):
+    import numpy as np
+    out = np.zeros(2 * len(lst), dtype=np.uint64)
+    load().oracle_link_eq_gather(alpha.ctypes.data, n_vars, lst.ctypes.data, out.ctypes.data, len(lst))
+    return out
