@@ -473,10 +473,19 @@ def run_simple(args):
     launches0 = lib.mb_launch_count()
     sampler.start()
     ms = timed_max(step, args.steps)
-    clocks = sampler.stop()
     launches = lib.mb_launch_count() - launches0
     step_e2e()
     ms_e2e = timed_max(step_e2e, args.steps)
+    # a timed region of a few milliseconds ends before nvidia-smi prints its first sample: keep the same
+    # step running (untimed) until one has arrived, so that the clocks are read under this load
+    if world == 1:
+        t_end = time.perf_counter() + 2.0
+        while not sampler.lines and time.perf_counter() < t_end:
+            step()
+    else:
+        for _ in range(20):   # the same count on every rank: the steps hold collectives
+            step()
+    clocks = sampler.stop()
     line = {"metric": metric, "value": units * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None,
