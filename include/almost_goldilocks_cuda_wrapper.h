@@ -262,6 +262,24 @@ int agl_mcommit_add(uint32_t* d_dst, const uint32_t* d_src, int V, int k, int ro
 /* d_out u64 [V][rows][4096] canonical; d_err int64 [V][rows][4096] or null is added; d_acc is left unchanged. */
 int agl_mcommit_finish(uint32_t* d_acc, int V, int k, int rows, const int64_t* d_err, uint64_t* d_out);
 
+/* ---- sparse boolean-check sumcheck ----
+ * Replaces almost-goldilocks-cuda-rs/src/ffi.rs:140-158 (definitions cuda/wrapper.cu:2650-2981; Rust state
+ * almost-goldilocks-cuda-rs/src/sumcheck_prover.rs:2186-2340). sum_t w_t sum_x eq(x) v_t(x) (v_t(x) - 1) over sorted
+ * (position u32, value ext) entry lists, term t owning entries [d_term_off[t], d_term_off[t + 1]); a round binds the low
+ * position bit. round_msg fills d_flags (1 = entry opens a group) and d_gid (exclusive prefix sum of the flags), returns
+ * the four evaluations at 0..3 in h_msg (8 canonical words) and the number of groups in *h_total; d_eq is the eq table of
+ * the current size. d_partial, grid_x and the scan scratch are accepted for signature compatibility and not used.
+ * fold writes `total` merged entries and n_terms + 1 new offsets. n < 2^32 - 4096. */
+int agl_bool_init_val_ffi(uint64_t* d_val, size_t n);
+int agl_bool_round_msg_ffi(const uint32_t* d_idx, const uint64_t* d_val, const uint32_t* d_term_off, const uint64_t* d_w,
+                           const uint64_t* d_eq, int n_terms, size_t n, uint32_t* d_flags, uint32_t* d_gid, uint64_t* d_partial,
+                           int grid_x, uint32_t* d_scan_scratch, size_t scan_scratch_len, uint64_t* h_msg, uint32_t* h_total);
+int agl_bool_fold_ffi(const uint32_t* d_idx, const uint64_t* d_val, const uint32_t* d_flags, const uint32_t* d_gid,
+                      const uint32_t* d_term_off, int n_terms, size_t n, uint64_t r0, uint64_t r1, uint32_t total, int grid_x,
+                      uint32_t* d_out_idx, uint64_t* d_out_val, uint32_t* d_new_off);
+int agl_bool_finish_ffi(const uint32_t* d_idx, const uint64_t* d_val, const uint32_t* d_term_off, int n_terms, size_t n,
+                        uint64_t* d_out);
+
 /* ---- packed link sumcheck ----
  * Replaces almost-goldilocks-cuda-rs/src/ffi.rs:511-593 (definitions cuda/wrapper.cu:1213-1440, kernels
  * cuda_almost_goldilocks/link_sumcheck.cuh; CPU definition zk-torch-4/src/pcs/link.rs:284-357).

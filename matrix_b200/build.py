@@ -47,6 +47,7 @@ LIBRARIES = {
         "agl_k8.cu",
         "agl_mcommit.cu",
         "agl_link.cu",
+        "agl_bool.cu",
         "agl_batched.cu",
         "agl_ajtai_fold.cu",
         "host/agl_transcript.cu",

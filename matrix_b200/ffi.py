@@ -310,6 +310,12 @@ _AGL_SIGNATURES = {
     "link_omega_expand_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64]),
     "link_expand_bits_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "link_eq_gather_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_void_p, c_u64]),
+    "agl_bool_init_val_ffi": (c_int, [c_void_p, c_size_t]),
+    "agl_bool_round_msg_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_int,
+                                       c_void_p, c_size_t, c_void_p, c_void_p]),
+    "agl_bool_fold_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_u64, c_u64, ctypes.c_uint32, c_int,
+                                  c_void_p, c_void_p, c_void_p]),
+    "agl_bool_finish_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p]),
     "agl_monolith_permute_host": (c_int, [c_void_p]),
     "agl_monolith_round_constants": (c_int, [c_void_p]),
     "agl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),

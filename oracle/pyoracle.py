@@ -400,3 +400,32 @@ def link_eq_gather(alpha, n_vars, lst):
     out = np.zeros(2 * len(lst), dtype=np.uint64)
     load().oracle_link_eq_gather(alpha.ctypes.data, n_vars, lst.ctypes.data, out.ctypes.data, len(lst))
     return out
+
+
+# ---- sparse boolean-check sumcheck ------------------------------------------------------
+_SIGS.update({
+    "oracle_bool_round": (u32, [vp, vp, vp, vp, vp, ci, u32, vp, vp, vp]),
+    "oracle_bool_fold": (None, [vp, vp, vp, vp, vp, ci, u32, u64, u64, u32, vp, vp, vp]),
+})
+
+
+def bool_round(idx, val, term_off, w, eq):
+    """Returns (flags, gid, msg[8], total)."""
+    import numpy as np
+    n, n_terms = len(idx), len(term_off) - 1
+    flags, gid = np.zeros(max(n, 1), dtype=np.uint32), np.zeros(max(n, 1), dtype=np.uint32)
+    msg = np.zeros(8, dtype=np.uint64)
+    total = load().oracle_bool_round(idx.ctypes.data, val.ctypes.data, term_off.ctypes.data, w.ctypes.data, eq.ctypes.data, n_terms, n,
+                                     flags.ctypes.data, gid.ctypes.data, msg.ctypes.data)
+    return flags[:n], gid[:n], msg, int(total)
+
+
+def bool_fold(idx, val, flags, gid, term_off, r, total):
+    """Returns (out_idx, out_val, new_off)."""
+    import numpy as np
+    n, n_terms = len(idx), len(term_off) - 1
+    out_idx, out_val = np.zeros(max(total, 1), dtype=np.uint32), np.zeros(2 * max(total, 1), dtype=np.uint64)
+    new_off = np.zeros(n_terms + 1, dtype=np.uint32)
+    load().oracle_bool_fold(idx.ctypes.data, val.ctypes.data, flags.ctypes.data, gid.ctypes.data, term_off.ctypes.data, n_terms, n,
+                            int(r[0]), int(r[1]), total, out_idx.ctypes.data, out_val.ctypes.data, new_off.ctypes.data)
+    return out_idx[:total], out_val[:2 * total], new_off
