@@ -45,6 +45,71 @@ __device__ __forceinline__ E2 eq_pointwise(const uint64_t* pt, uint64_t l, int m
     return acc;
 }
 
+// Block sum of the seven slots (shuffles inside a warp, one shared-memory step across the eight warps), tag on the
+// norm half, one partial per block.
+__device__ __forceinline__ void block_sum_store(const E2 acc[SLOTS], const uint64_t* tags, uint64_t* partial, uint64_t e, uint64_t chunk,
+                                                uint64_t nchunk) {
+    const int tid = threadIdx.x;
+    __shared__ uint64_t sh[BLOCK / 32][SLOTS][2];
+#pragma unroll
+    for (int k = 0; k < SLOTS; k++) {
+        E2 v = acc[k];
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            const E2 o{__shfl_down_sync(0xffffffffu, v.c0, off), __shfl_down_sync(0xffffffffu, v.c1, off)};
+            v = agl::e2_add(v, o);
+        }
+        if ((tid & 31) == 0) {
+            sh[tid >> 5][k][0] = v.c0;
+            sh[tid >> 5][k][1] = v.c1;
+        }
+    }
+    __syncthreads();
+    if (tid < SLOTS) {
+        E2 v = zero();
+        for (int wp = 0; wp < BLOCK / 32; wp++) v = agl::e2_add(v, E2{sh[wp][tid][0], sh[wp][tid][1]});
+        if (tid < NORM) v = agl::e2_mul_lazy(ld(tags, e), v);
+        st(partial, (e * nchunk + chunk) * SLOTS + tid, v);
+    }
+}
+
+// The bit-packed terms of one pair: s01 / s10 collect eq over (0,1) / (1,0) pairs, acc[4..6] the weight sums.
+__device__ __forceinline__ void bit_pair_terms(E2& s01, E2& s10, E2 acc[SLOTS], unsigned blo, unsigned bhi, E2 o_lo, E2 o_hi, E2 eqs) {
+    if (blo && !bhi) s10 = agl::e2_add(s10, eqs);
+    if (bhi && !blo) s01 = agl::e2_add(s01, eqs);
+    if (blo) acc[4] = agl::e2_add(acc[4], o_lo);
+    if (bhi) acc[5] = agl::e2_add(acc[5], o_hi);
+    const E2 o2 = agl::e2_sub(agl::e2_add(o_hi, o_hi), o_lo);   // omega(2); w(2) = 2 hi - lo in {-1, 1, 2}
+    if (blo && !bhi) acc[6] = agl::e2_sub(acc[6], o2);
+    else if (!blo) acc[6] = agl::e2_add(acc[6], agl::e2_add(o2, o2));
+    else acc[6] = agl::e2_add(acc[6], o2);
+}
+
+// Position of the n-th (1-based) set bit of a 64-bit word.
+__device__ __forceinline__ unsigned nth_set_bit(uint64_t m, unsigned n) {
+    const unsigned lo = (unsigned)m, c = __popc(lo);
+    return n <= c ? __fns(lo, 0, (int)n) : 32u + __fns((unsigned)(m >> 32), 0, (int)(n - c));
+}
+
+// Exact 96-bit sums of 64-bit words (no reduction per addition): up to 2^32 terms.
+struct Raw {
+    uint64_t lo;
+    uint32_t hi;
+};
+struct RawE2 {
+    Raw c0, c1;
+};
+__device__ __forceinline__ void raw_add(Raw& a, uint64_t x) {
+    asm("add.cc.u64 %0, %0, %2;\n\taddc.u32 %1, %1, 0;" : "+l"(a.lo), "+r"(a.hi) : "l"(x));
+}
+__device__ __forceinline__ void raw_add(RawE2& a, E2 x) {
+    raw_add(a.c0, x.c0);
+    raw_add(a.c1, x.c1);
+}
+__device__ __forceinline__ E2 raw_reduce(const RawE2& a) {
+    return E2{agl::reduce128(a.c0.lo, (uint64_t)a.c0.hi), agl::reduce128(a.c1.lo, (uint64_t)a.c1.hi)};
+}
+
 struct RoundArgs {
     const uint64_t* bits;      // witness bits, rows of bits_stride_words (BITS)
     const uint64_t* w;         // witness table, rows of w_stride (!BITS)
@@ -106,13 +171,7 @@ __global__ void __launch_bounds__(BLOCK) link_round_kernel(RoundArgs a) {
         }
         const E2 eqs = ld(a.eq, LISTED ? loff + t : idx);
         if (BITS) {
-            if (blo != bhi) acc[blo ? 1 : 0] = agl::e2_add(acc[blo ? 1 : 0], eqs);
-            if (blo) acc[4] = agl::e2_add(acc[4], o_lo);
-            if (bhi) acc[5] = agl::e2_add(acc[5], o_hi);
-            const E2 o2 = agl::e2_sub(agl::e2_add(o_hi, o_hi), o_lo);   // omega(2); w(2) = 2 hi - lo in {-1, 1, 2}
-            if (blo && !bhi) acc[6] = agl::e2_sub(acc[6], o2);
-            else if (!blo) acc[6] = agl::e2_add(acc[6], agl::e2_add(o2, o2));
-            else acc[6] = agl::e2_add(acc[6], o2);
+            bit_pair_terms(acc[0], acc[1], acc, blo, bhi, o_lo, o_hi, eqs);
         } else {
             const E2 w_d = agl::e2_sub(w_hi, w_lo), o_d = agl::e2_sub(o_hi, o_lo);
             const E2 w1 = agl::e2_add(w_lo, w_d), w2 = agl::e2_add(w1, w_d), w3 = agl::e2_add(w2, w_d);
@@ -136,28 +195,98 @@ __global__ void __launch_bounds__(BLOCK) link_round_kernel(RoundArgs a) {
         acc[3] = agl::e2_sub(mul_small(s01, 24), mul_small(s10, 6));
     }
 
-    // block sum: shuffles inside a warp, one shared-memory step across the eight warps
-    __shared__ uint64_t sh[BLOCK / 32][SLOTS][2];
+    block_sum_store(acc, a.tags, a.partial, e, chunk, nchunk);
+}
+
+// Round 0 off bits, dense index set, half a multiple of 64. A warp takes 32 word pairs (2048 index pairs) at a
+// time, counts the live pairs (lo | hi), and hands them out one per lane in compact order, so the work and the
+// weight reads follow the number of live pairs at any density, with 32 independent pairs in flight per warp;
+// batches that are mostly live are swept a word at a time instead (one lane per bit position).
+__global__ void __launch_bounds__(BLOCK) link_round0_words_kernel(RoundArgs a) {
+    const uint64_t e = blockIdx.y, chunk = blockIdx.x, nchunk = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const uint64_t* be = a.bits + e * a.bits_stride_words;
+    const uint64_t* oe = a.omega + 2 * e * a.omega_stride;
+    const uint64_t words = a.half >> 6;
+    const uint64_t warp = chunk * (BLOCK / 32) + (tid >> 5), nwarps = nchunk * (BLOCK / 32);
+    // raw sums by pair type (lo, hi) = (1,0), (0,1), (1,1): weights at idx (L) and at half + idx (H), eq for the mixed types
+    RawE2 L10{}, L01{}, L11{}, H10{}, H01{}, H11{}, S10{}, S01{};
+    for (uint64_t wb = warp * 32; wb < words; wb += nwarps * 32) {
+        const uint64_t wi = wb + lane;
+        const uint64_t lo = wi < words ? be[wi] : 0, hi = wi < words ? be[words + wi] : 0;
+        const uint64_t act = lo | hi;
+        const unsigned cnt = __popcll(act);
+        unsigned inc = cnt;
 #pragma unroll
-    for (int k = 0; k < SLOTS; k++) {
-        E2 v = acc[k];
-#pragma unroll
-        for (int off = 16; off; off >>= 1) {
-            const E2 o{__shfl_down_sync(0xffffffffu, v.c0, off), __shfl_down_sync(0xffffffffu, v.c1, off)};
-            v = agl::e2_add(v, o);
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned u = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += u;
         }
-        if ((tid & 31) == 0) {
-            sh[tid >> 5][k][0] = v.c0;
-            sh[tid >> 5][k][1] = v.c1;
+        const unsigned pre = inc - cnt, total = __shfl_sync(0xffffffffu, inc, 31);
+        auto consume = [&](uint64_t idx, unsigned blo, unsigned bhi) {
+            const E2 o_lo = ld(oe, idx), o_hi = ld(oe, a.half + idx);
+            if (blo & bhi) {
+                raw_add(L11, o_lo);
+                raw_add(H11, o_hi);
+            } else {
+                const E2 eqs = ld(a.eq, idx);
+                if (blo) {
+                    raw_add(L10, o_lo);
+                    raw_add(H10, o_hi);
+                    raw_add(S10, eqs);
+                } else {
+                    raw_add(L01, o_lo);
+                    raw_add(H01, o_hi);
+                    raw_add(S01, eqs);
+                }
+            }
+        };
+        if (total >= 768) {
+            // mostly live: a lane per bit position, 32 consecutive pairs per step (coalesced weight reads)
+            for (int j = 0; j < 32; j++) {
+                const uint64_t wlo = __shfl_sync(0xffffffffu, lo, j), whi = __shfl_sync(0xffffffffu, hi, j);
+                if (!(wlo | whi)) continue;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const unsigned bit = lane + 32 * h;
+                    const unsigned blo = (unsigned)(wlo >> bit) & 1u, bhi = (unsigned)(whi >> bit) & 1u;
+                    if (blo | bhi) consume(((wb + j) << 6) + bit, blo, bhi);
+                }
+            }
+            continue;
+        }
+        for (unsigned k0 = 0; k0 < total; k0 += 32) {
+            const bool live = k0 + lane < total;
+            const unsigned r = live ? k0 + lane : total - 1;
+            int j = 0;   // the lane whose word holds live pair r: last j with pre_j <= r
+#pragma unroll
+            for (int step = 16; step; step >>= 1) {
+                const unsigned pc = __shfl_sync(0xffffffffu, pre, (j + step) & 31);
+                if (j + step < 32 && pc <= r) j += step;
+            }
+            const uint64_t wlo = __shfl_sync(0xffffffffu, lo, j), whi = __shfl_sync(0xffffffffu, hi, j);
+            const unsigned pj = __shfl_sync(0xffffffffu, pre, j);
+            if (live) {
+                const unsigned bit = nth_set_bit(wlo | whi, r - pj + 1);
+                consume(((wb + j) << 6) + bit, (unsigned)(wlo >> bit) & 1u, (unsigned)(whi >> bit) & 1u);
+            }
         }
     }
-    __syncthreads();
-    if (tid < SLOTS) {
-        E2 v = zero();
-        for (int wp = 0; wp < BLOCK / 32; wp++) v = agl::e2_add(v, E2{sh[wp][tid][0], sh[wp][tid][1]});
-        if (tid < NORM) v = agl::e2_mul_lazy(ld(a.tags, e), v);
-        st(a.partial, (e * nchunk + chunk) * SLOTS + tid, v);
-    }
+    // E(0) = sum lo omega_lo, E(1) = sum hi omega_hi, E(2) = sum (2 hi - lo)(2 omega_hi - omega_lo); S(2) = 6 s01, S(3) = 24 s01 - 6 s10
+    const E2 l10 = raw_reduce(L10), l01 = raw_reduce(L01), l11 = raw_reduce(L11);
+    const E2 h10 = raw_reduce(H10), h01 = raw_reduce(H01), h11 = raw_reduce(H11);
+    const E2 s10 = raw_reduce(S10), s01 = raw_reduce(S01);
+    E2 acc[SLOTS];
+    acc[0] = zero();
+    acc[1] = zero();
+    acc[2] = mul_small(s01, 6);
+    acc[3] = agl::e2_sub(mul_small(s01, 24), mul_small(s10, 6));
+    acc[4] = agl::e2_add(l10, l11);
+    acc[5] = agl::e2_add(h01, h11);
+    const E2 t11 = agl::e2_sub(agl::e2_add(h11, h11), l11), t01 = agl::e2_sub(agl::e2_add(h01, h01), l01),
+             t10 = agl::e2_sub(agl::e2_add(h10, h10), l10);
+    acc[6] = agl::e2_sub(agl::e2_add(t11, agl::e2_add(t01, t01)), t10);
+    block_sum_store(acc, a.tags, a.partial, e, chunk, nchunk);
 }
 
 // out[k] = sum of partial[b][k]; one block per slot.
@@ -335,7 +464,17 @@ int link_round0_bits_ffi(const uint64_t* d_bits, const uint64_t* d_omega, const 
     a.omega = d_omega;
     a.bits_stride_words = stride >> 6;
     a.omega_stride = stride;
-    return run_round<true, false, false>(a, n_commit, chunks, d_out);
+    if ((half & 63) || n_commit == 0) return run_round<true, false, false>(a, n_commit, chunks, d_out);
+    if (!a.eq || !a.tags || !a.partial || !d_out || chunks == 0 || chunks > 0x7fffffffULL || n_commit > 65535) return MB_ERR_ARG;
+    {
+        MB_KERNEL("link_round0_words");
+        link_round0_words_kernel<<<dim3((unsigned)chunks, (unsigned)n_commit), BLOCK, 0, MB_STREAM>>>(a);
+    }
+    {
+        MB_KERNEL("link_reduce");
+        link_reduce_kernel<<<SLOTS, BLOCK, 0, MB_STREAM>>>(a.partial, n_commit * chunks, d_out);
+    }
+    return finish_sync();
 }
 
 int link_round0_bits_sparse_ffi(const uint64_t* d_bits, const uint64_t* d_omega, const uint64_t* d_eq, const uint64_t* d_tags,

@@ -82,7 +82,7 @@ def test_listed_round_message(lib, log_half, nc, density, first):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("log_half,nc,density", [(6, 1, 0.5), (10, 3, 0.1), (14, 2, 0.003)])
+@pytest.mark.parametrize("log_half,nc,density", [(5, 2, 0.5), (6, 1, 0.5), (10, 3, 0.1), (14, 2, 0.003), (12, 2, 1.0)])
 def test_bit_packed_round_zero(lib, log_half, nc, density):
     half = 1 << log_half
     stride = 2 * half
