@@ -525,6 +525,88 @@ def run_simple(args):
         dist.destroy_process_group()
 
 
+def run_link(args):
+    """The two largest rounds of the packed link sumcheck on one GPU: round 0 off the bit-packed witness
+    (message, then fold to a half-size table with the weights folded in place) and round 1 on the tables
+    (message, fold). 8 commitments of 2^24 coefficients, 5 % of the bits set (one-hot style advice is sparser,
+    committed weights denser); weights, eq and tags are seeded field elements."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    from matrix_b200 import load_agl
+    from matrix_b200.ffi import DeviceBuffer
+    from matrix_b200.inputs import AGL_Q, field_elems
+    lib = load_agl()
+    assert lib.cuda_set_device(local) == 0
+    peak, peak_kind = measured_peaks()
+    log_n, nc = (args.num_vars if args.num_vars != 24 else 24), 8
+    n, half = 1 << log_n, 1 << (log_n - 1)
+    rng = np.random.default_rng(7)
+    bits = rng.random(nc * n) < 0.05
+    words = np.ascontiguousarray(np.packbits(bits.reshape(-1, 64)[:, ::-1], axis=1).view(">u8").astype(np.uint64).reshape(-1))
+
+    def dev_rand(seed, elems):   # seeded field elements tiled on the device (the host holds one 32 MB tile)
+        buf, tile = DeviceBuffer(lib, elems * 16), field_elems(seed, 1 << 22, AGL_Q)
+        for off in range(0, 2 * elems, 1 << 22):
+            lib.cuda_memcpy_htod(buf.ptr + off * 8, tile.ctypes.data, min(1 << 22, 2 * elems - off) * 8)
+        return buf
+    d_bits, d_om0, d_eq, d_tags = DeviceBuffer.from_numpy(lib, words), dev_rand(1, nc * n), dev_rand(2, half), dev_rand(3, nc)
+    d_om, d_w = DeviceBuffer(lib, nc * n * 16), DeviceBuffer(lib, nc * half * 16)
+    chunks = 148 * 8 // nc
+    d_part, d_out = DeviceBuffer(lib, nc * chunks * 7 * 16), DeviceBuffer(lib, 7 * 16)
+    msg = np.zeros(14, dtype=np.uint64)
+
+    def step():
+        lib.cuda_memcpy_dtod(d_om.ptr, d_om0.ptr, nc * n * 16)   # the folds work in place: restore the weights
+        rc = lib.link_round0_bits_ffi(d_bits.ptr, d_om.ptr, d_eq.ptr, d_tags.ptr, n, half, nc, d_part.ptr, chunks, d_out.ptr)
+        rc |= lib.link_fold0_bits_ffi(d_bits.ptr, d_w.ptr, d_om.ptr, n, half, nc, 5, 7)
+        rc |= lib.link_round_message_ffi(d_w.ptr, d_om.ptr, d_eq.ptr, d_tags.ptr, half, n, half // 2, nc, 0, d_part.ptr, chunks, d_out.ptr)
+        rc |= lib.link_fold_ffi(d_w.ptr, d_om.ptr, half, n, half // 2, nc, 11, 13)
+        return rc
+
+    def step_e2e():
+        lib.cuda_memcpy_htod(d_bits.ptr, words.ctypes.data, words.nbytes)
+        step()
+        lib.cuda_memcpy_dtoh(msg.ctypes.data, d_out.ptr, msg.nbytes)
+    timed = _event_timer(lib)
+    for _ in range(max(args.warmup, 3)):
+        assert step() == 0
+    lib.mb_prof_enable(1)
+    lib.mb_prof_reset()
+    sampler = ClockSampler(local)
+    launches0 = lib.mb_launch_count()
+    sampler.start()
+    lib.cuda_device_synchronize()
+    ms = timed(step, args.steps)
+    launches = lib.mb_launch_count() - launches0
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.mb_prof_report(buf, len(buf))
+    kernels = {l.split()[0]: float(l.split()[2]) / args.steps for l in buf.value.decode().splitlines() if len(l.split()) == 3}
+    lib.mb_prof_enable(0)
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    t_end = time.perf_counter() + 2.0
+    while not sampler.lines and time.perf_counter() < t_end:
+        step()
+    clocks = sampler.stop()
+    units = nc * n
+    fold_bytes = 1.5 * nc * half * 32.0   # link_fold: both tables, read 2 halves, write 1
+    ach = fold_bytes / (kernels.get("link_fold", float("nan")) * 1e-3) / 1e9
+    line = {"metric": "field-elems/s: packed link sumcheck, rounds 0 and 1 (8 commitments x 2^%d bit-packed coefficients), "
+                      "almost-Goldilocks" % log_n,
+            "value": units * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
+            "data": "synthetic", "config": {"workload": "link rounds 0-1, n_commit=8, 2^%d coefficients, 5%% of bits set" % log_n,
+                                            "l2": "tables larger than L2"},
+            "e2e": {"value": units * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(words.nbytes), "d2h_bytes_per_step": int(msg.nbytes)},
+            "gpu_launches": int(launches), "clocks": clocks, "kernel_ms_per_step": kernels,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "peak_kind": peak_kind, "note": "link_fold (the streaming kernel of the step); the bit round is a gather "
+                                                         "over live pairs, the table round is bound by the integer pipe"}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -534,7 +616,7 @@ def main():
     ap.add_argument("--num-vars", type=int, default=24)
     ap.add_argument("--ref-num-vars", type=int, default=20, help="sample size of the CPU arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit"],
+    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit", "link"],
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
@@ -553,6 +635,9 @@ def main():
         return
     if args.workload in ("sumcheck", "ajtai", "mcommit"):
         run_simple(args)
+        return
+    if args.workload == "link":
+        run_link(args)
         return
 
     if args.impl == "reference":

@@ -289,6 +289,59 @@ __global__ void __launch_bounds__(BLOCK) link_round0_words_kernel(RoundArgs a) {
     block_sum_store(acc, a.tags, a.partial, e, chunk, nchunk);
 }
 
+// Table witness, dense index set: a warp sweeps 32 pairs at a time (coalesced reads of both halves), queues the
+// indices of the live ones in shared memory and runs the arithmetic only on full groups of 32 live pairs, so a
+// sparse table costs its live pairs plus one pass over the witness, whatever the spacing of the live entries
+// (skipping inside the sweep alone would be bounded by the warp width). half <= 2^32.
+__global__ void __launch_bounds__(BLOCK) link_round_dense_kernel(RoundArgs a) {
+    __shared__ uint32_t queue[BLOCK / 32][64];
+    const uint64_t e = blockIdx.y, chunk = blockIdx.x, nchunk = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const uint64_t* we = a.w + 2 * e * a.w_stride;
+    const uint64_t* oe = a.omega + 2 * e * a.omega_stride;
+    E2 acc[SLOTS];
+#pragma unroll
+    for (int k = 0; k < SLOTS; k++) acc[k] = zero();
+    auto process = [&](uint64_t idx) {
+        const E2 w_lo = ld(we, idx), w_hi = ld(we, a.half + idx);
+        const E2 o_lo = ld(oe, idx), o_hi = ld(oe, a.half + idx), eqs = ld(a.eq, idx);
+        const E2 w_d = agl::e2_sub(w_hi, w_lo), o_d = agl::e2_sub(o_hi, o_lo);
+        const E2 w1 = agl::e2_add(w_lo, w_d), w2 = agl::e2_add(w1, w_d), w3 = agl::e2_add(w2, w_d);
+        if (!a.first_round) {
+            acc[0] = agl::e2_add(acc[0], agl::e2_mul_lazy(eqs, range_poly(w_lo)));
+            acc[1] = agl::e2_add(acc[1], agl::e2_mul_lazy(eqs, range_poly(w1)));
+        }
+        acc[2] = agl::e2_add(acc[2], agl::e2_mul_lazy(eqs, range_poly(w2)));
+        acc[3] = agl::e2_add(acc[3], agl::e2_mul_lazy(eqs, range_poly(w3)));
+        const E2 o1 = agl::e2_add(o_lo, o_d), o2 = agl::e2_add(o1, o_d);
+        acc[4] = agl::e2_add(acc[4], agl::e2_mul_lazy(o_lo, w_lo));
+        acc[5] = agl::e2_add(acc[5], agl::e2_mul_lazy(o1, w1));
+        acc[6] = agl::e2_add(acc[6], agl::e2_mul_lazy(o2, w2));
+    };
+    unsigned qn = 0;   // queued indices of this warp, the same value in every lane
+    const uint64_t warp = chunk * (BLOCK / 32) + wp, nwarps = nchunk * (BLOCK / 32);
+    uint64_t base = warp * 32;
+    for (;;) {
+        while (qn < 32 && base < a.half) {   // sweep until a full group is queued or the range ends
+            const uint64_t idx = base + lane;
+            bool live = false;
+            if (idx < a.half) live = !(is_zero(ld(we, idx)) && is_zero(ld(we, a.half + idx)));
+            const unsigned mask = __ballot_sync(0xffffffffu, live);
+            if (live) queue[wp][qn + __popc(mask & ((1u << lane) - 1u))] = (uint32_t)idx;
+            qn += __popc(mask);
+            base += nwarps * 32;
+        }
+        if (qn == 0) break;
+        __syncwarp();
+        const unsigned take = qn < 32 ? qn : 32;
+        qn -= take;
+        const uint32_t mine = queue[wp][qn + (lane < take ? lane : 0)];
+        __syncwarp();
+        if (lane < take) process(mine);
+    }
+    block_sum_store(acc, a.tags, a.partial, e, chunk, nchunk);
+}
+
 // out[k] = sum of partial[b][k]; one block per slot.
 __global__ void __launch_bounds__(BLOCK) link_reduce_kernel(const uint64_t* __restrict__ partial, uint64_t n_blocks, uint64_t* __restrict__ out) {
     const int k = blockIdx.x, tid = threadIdx.x;
@@ -437,7 +490,17 @@ int link_round_message_ffi(const uint64_t* d_w, const uint64_t* d_omega, const u
     a.omega = d_omega;
     a.w_stride = stride;
     a.omega_stride = omega_stride;
-    return run_round<false, false, false>(a, n_commit, chunks, d_out);
+    if (half > 0xffffffffULL || n_commit == 0) return run_round<false, false, false>(a, n_commit, chunks, d_out);
+    if (!a.eq || !a.tags || !a.partial || !d_out || chunks == 0 || chunks > 0x7fffffffULL || n_commit > 65535) return MB_ERR_ARG;
+    {
+        MB_KERNEL("link_round_dense");
+        link_round_dense_kernel<<<dim3((unsigned)chunks, (unsigned)n_commit), BLOCK, 0, MB_STREAM>>>(a);
+    }
+    {
+        MB_KERNEL("link_reduce");
+        link_reduce_kernel<<<SLOTS, BLOCK, 0, MB_STREAM>>>(a.partial, n_commit * chunks, d_out);
+    }
+    return finish_sync();
 }
 
 int link_round_message_sparse_ffi(const uint64_t* d_w, const uint64_t* d_omega, const uint64_t* d_eq_suffix, const uint64_t* d_tags,

@@ -328,6 +328,15 @@ def _sum_column_shards(commit_columns, comm, ncols, words):
     return np.array(total, dtype=np.uint64)
 
 
+def link_round_sharded(round_commitments, comm, n_commit):
+    """The link round message is a sum over commitments (cuda_almost_goldilocks/link_sumcheck.cuh:16-19: a
+    partition of the commitment axis with a 7-element all-reduce): every rank forms the message of its own
+    range of commitments, the 14 words per rank are all-gathered and added mod q. `round_commitments(lo, hi)`
+    returns [S(0..3), E(0..2)] over commitments lo..hi (zeros for an empty range). Same array everywhere;
+    the ranks then fold their own tables with the same challenge, no further exchange."""
+    return _sum_column_shards(round_commitments, comm, n_commit, 14)
+
+
 def module_commit_sharded(commit_columns, comm, ncols, vectors, rows):
     """The module commitment over F_q[Y]/(Y^4096 + 1) is a sum over key columns
     (zk-torch-4/src/morpheus/commit_gpu.rs:1-8: partial per column range and GPU, then add): every rank
