@@ -177,6 +177,17 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
  * recombination mod q); digits in [-127, 127] (-3 if a -128 is present), any number of planes */
 int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
                         uint64_t* d_out);
+/* Addition (no reference counterpart for signed digits): the same commit against the matrix materialised by
+ * ajtai_materialize_m_ffi (d_M[j][i][k], columns 0 .. N - 1); the tensor-core kernel streams d_M instead of
+ * regenerating the matrix. ajtai_commit_ternary_premat_ffi (the reference's entry point) runs through it. */
+int ajtai_commit_s8_premat_ffi(const uint64_t* d_M, const int8_t* d_digits, uint64_t N, int planes, uint64_t* d_out);
+/* Additions (no reference counterpart): the matrix as unsigned byte planes in the order of the tensor-core operand
+ * (per four columns and group of 14 rows one 28 KB image). ajtai_tc_matrix_bytes(N): size of d_T for N columns;
+ * ajtai_materialize_tc_ffi: fill it for columns col_offset .. col_offset + N - 1; ajtai_commit_s8_tiled_ffi: the
+ * signed-digit commit against it (the kernel copies the images; its work is the digit windows and the MMAs). */
+uint64_t ajtai_tc_matrix_bytes(uint64_t N);
+int ajtai_materialize_tc_ffi(const uint32_t* d_key, uint8_t* d_T, uint64_t N, uint64_t col_offset);
+int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int planes, uint64_t* d_out);
 
 /* ---- batched same-point sumcheck family (sum_x eq(x) f(x) per leaf, messages at c = 0, 1, 2): ffi.rs:177-195,265-423
  * (wrapper.cu:674-707,851-1060; kernels cuda_almost_goldilocks/almost_sumcheck_prover.cuh:233-1007). Tables are Ext2

@@ -91,13 +91,27 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
     return commit_scalar<KIND_S8>(d_key, d_digits, N, planes, col_offset, d_out);
 }
 
-// Addition: the same signed-digit commit on the tensor cores (tcgen05 kind::i8).
-// Digits must lie in [-127, 127] (-3 if a -128 is met: its negation, needed by
-// the negacyclic wrap, is not an s8; use the scalar entry point then). Planes
-// are processed four at a time.
-int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
-                        uint64_t* d_out) {
-    if (!d_key || !d_digits || !d_out || planes < 1 || planes > 64) return MB_ERR_ARG;
+}  // extern "C"
+
+namespace {
+constexpr bool TC_WIDE = true;   // one MMA over all planes of a pass (N = 64 np, four planes) rather than one per plane
+constexpr int TC_PASS_PLANES = TC_WIDE ? TC_MAX_PLANES : TCP_MAX_PLANES;
+
+template <int SRC>
+int launch_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0, int np,
+              uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks) {
+    const size_t smem = tc_pipe_smem_bytes(np, TC_WIDE);
+    if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC, TC_WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
+    dim3 grid((unsigned)chunks, 3);
+    commit_tc_pipe_kernel<SRC, TC_WIDE><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, np, col_offset, partial, d_err, materialize);
+    return MB_OK;
+}
+
+// Signed 8-bit digit planes on the tensor cores, eight planes per pass; the matrix comes from the key stream
+// (d_key), from 64-bit coefficients (d_M) or from byte planes in operand order (d_T).
+int commit_s8_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int planes,
+                 uint64_t col_offset, uint64_t* d_out) {
+    if (!d_digits || !d_out || planes < 1 || planes > 64) return MB_ERR_ARG;
     const size_t plane_words = (size_t)KAPPA * D;
     if (N == 0) {
         MB_CUDA(cudaMemsetAsync(d_out, 0, planes * plane_words * sizeof(uint64_t), MB_STREAM));
@@ -106,22 +120,19 @@ int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t 
     const size_t chunks = (N + TC_CHUNK_COLS - 1) / TC_CHUNK_COLS;
     uint64_t* partial = nullptr;
     int* d_err = nullptr;
-    MB_CUDA(pool_alloc((void**)&partial, chunks * 3 * TC_MAX_PLANES * TC_ROWS * D * sizeof(uint64_t)));
+    MB_CUDA(pool_alloc((void**)&partial, chunks * 3 * TCP_MAX_PLANES * TC_ROWS * D * sizeof(uint64_t)));
     if (pool_alloc((void**)&d_err, sizeof(int)) != cudaSuccess) { pool_free(partial); return MB_ERR_CUDA; }
     int rc = MB_OK;
     if (cudaMemsetAsync(d_err, 0, sizeof(int), MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
-    for (int p0 = 0; p0 < planes && rc == MB_OK; p0 += TC_MAX_PLANES) {
-        int np = planes - p0 < TC_MAX_PLANES ? planes - p0 : TC_MAX_PLANES;
-        size_t smem = tc_smem_bytes(np);
-        if (cudaFuncSetAttribute(commit_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            rc = MB_ERR_CUDA;
-            break;
-        }
+    for (int p0 = 0; p0 < planes && rc == MB_OK; p0 += TC_PASS_PLANES) {
+        const int np = planes - p0 < TC_PASS_PLANES ? planes - p0 : TC_PASS_PLANES;
         {
-            MB_KERNEL("ajtai_commit_tc");
-            dim3 grid((unsigned)chunks, 3);
-            commit_tc_kernel<<<grid, TC_THREADS, smem, MB_STREAM>>>(d_key, d_digits, N, p0, np, col_offset, partial, d_err);
+            MB_KERNEL(d_T ? "ajtai_commit_tc_tiled" : d_M ? "ajtai_commit_tc_premat" : "ajtai_commit_tc");
+            if (d_T) rc = launch_tc<TC_SRC_TILED>(nullptr, nullptr, d_T, d_digits, N, p0, np, 0, partial, d_err, nullptr, chunks);
+            else if (d_M) rc = launch_tc<TC_SRC_COEFFS>(nullptr, d_M, nullptr, d_digits, N, p0, np, 0, partial, d_err, nullptr, chunks);
+            else rc = launch_tc<TC_SRC_CHACHA>(d_key, nullptr, nullptr, d_digits, N, p0, np, col_offset, partial, d_err, nullptr, chunks);
         }
+        if (rc != MB_OK) break;
         {
             MB_KERNEL("ajtai_reduce_tc");
             reduce_tc_partials_kernel<<<grid_for((size_t)np * plane_words, 256, 4), 256, 0, MB_STREAM>>>(
@@ -139,6 +150,54 @@ int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t 
     if (h_err == TC_ERR_TIMEOUT) return MB_ERR_CUDA;
     if (h_err == TC_ERR_DIGIT_RANGE) return MB_ERR_UNSUPPORTED;
     return MB_OK;
+}
+}  // namespace
+
+extern "C" {
+
+// Addition: the same signed-digit commit on the tensor cores (tcgen05 kind::i8).
+// Digits must lie in [-127, 127] (-3 if a -128 is met: its negation, needed by
+// the negacyclic wrap, is not an s8; use the scalar entry point then). Planes
+// are processed eight at a time.
+int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
+                        uint64_t* d_out) {
+    if (!d_key) return MB_ERR_ARG;
+    return commit_s8_tc(d_key, nullptr, nullptr, d_digits, N, planes, col_offset, d_out);
+}
+
+// The same against a matrix materialised by ajtai_materialize_m_ffi (d_M[j][i][k], columns 0 .. N - 1): the
+// tensor-core kernel streams the matrix instead of regenerating it. No reference counterpart for signed digits
+// (the reference's premat entry point takes ternary planes, ajtai_commit_ternary_premat_ffi below).
+int ajtai_commit_s8_premat_ffi(const uint64_t* d_M, const int8_t* d_digits, uint64_t N, int planes, uint64_t* d_out) {
+    if (!d_M) return MB_ERR_ARG;
+    return commit_s8_tc(nullptr, d_M, nullptr, d_digits, N, planes, 0, d_out);
+}
+
+// Additions (no reference counterpart): the matrix as byte planes in the order the tensor-core operand wants
+// them. ajtai_tc_matrix_bytes(N) = size of that buffer for N columns; ajtai_materialize_tc_ffi fills it for
+// columns col_offset .. col_offset + N - 1; ajtai_commit_s8_tiled_ffi commits against it (the kernel then only
+// copies 28 KB per four columns and row group: its remaining work is the digit windows and the MMAs).
+uint64_t ajtai_tc_matrix_bytes(uint64_t N) { return ((N + TC_STAGE_COLS - 1) / TC_STAGE_COLS) * 3 * (uint64_t)TCP_A_IMAGE; }
+
+int ajtai_materialize_tc_ffi(const uint32_t* d_key, uint8_t* d_T, uint64_t N, uint64_t col_offset) {
+    if (!d_key || (!d_T && N)) return MB_ERR_ARG;
+    if (N == 0) return MB_OK;
+    const size_t chunks = (N + TC_CHUNK_COLS - 1) / TC_CHUNK_COLS;
+    int* d_err = nullptr;
+    MB_CUDA(pool_alloc((void**)&d_err, sizeof(int)));
+    int rc = cudaMemsetAsync(d_err, 0, sizeof(int), MB_STREAM) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+    if (rc == MB_OK) {
+        MB_KERNEL("ajtai_materialize_tc");
+        rc = launch_tc<TC_SRC_CHACHA>(d_key, nullptr, nullptr, nullptr, N, 0, 1, col_offset, nullptr, d_err, d_T, chunks);
+    }
+    if (rc == MB_OK) rc = finish_sync();
+    pool_free(d_err);
+    return rc;
+}
+
+int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int planes, uint64_t* d_out) {
+    if (!d_T) return MB_ERR_ARG;
+    return commit_s8_tc(nullptr, nullptr, d_T, d_digits, N, planes, 0, d_out);
 }
 
 // ---- ternary planes, sparse positions (ffi.rs:352-359,603-625,649-655; wrapper.cu:959-969,1642-1699,1741-1758) ----
@@ -177,7 +236,7 @@ int ajtai_commit_ternary_premat_ffi(const uint64_t* d_M, const uint64_t* d_pos, 
     if (N_ring == 0) return commit_scalar<KIND_S8>(nullptr, d_pos, 0, SPLIT_K, 0, d_out, d_M);
     int8_t* d_digits = nullptr;
     int rc = expand_ternary(d_pos, d_neg, N_ring, &d_digits);
-    if (rc == MB_OK) rc = commit_scalar<KIND_S8>(nullptr, d_digits, N_ring, SPLIT_K, 0, d_out, d_M);
+    if (rc == MB_OK) rc = commit_s8_tc(nullptr, d_M, nullptr, d_digits, N_ring, SPLIT_K, 0, d_out);
     pool_free(d_digits);
     return rc;
 }

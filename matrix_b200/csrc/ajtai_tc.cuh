@@ -68,9 +68,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 // grid = (column chunks, 3 row groups); block = 256 threads; dynamic shared memory.
 // d_digits: [planes][N][64] s8 (this CTA uses planes p0 .. p0 + np - 1).
 // partial[((chunk * 3 + group) * np + p) * 14 * 64 + i_local * 64 + r] = canonical chunk sum.
+// PREMAT: the coefficients come from d_M[j][i][k] (the layout of ajtai_materialize_m_ffi, column j relative to
+// the first column of this call) instead of the ChaCha8 stream: the kernel then streams 28 KB of the matrix per
+// stage and its cost is the operand build and the reads of d_M, not the generation.
+template <bool PREMAT>
 static __global__ void __launch_bounds__(TC_THREADS)
-commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ d_digits, uint64_t N, int p0, int np,
-                 uint64_t col_offset, uint64_t* __restrict__ partial, int* __restrict__ d_error) {
+commit_tc_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const int8_t* __restrict__ d_digits, uint64_t N,
+                 int p0, int np, uint64_t col_offset, uint64_t* __restrict__ partial, int* __restrict__ d_error) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int n_cols = 64 * np;                       // UMMA N
     uint8_t* A_sh = smem;                             // 32 KB
@@ -86,7 +90,7 @@ commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ 
     const uint64_t j1 = j0 + TC_CHUNK_COLS < N ? j0 + TC_CHUNK_COLS : N;
     uint32_t key[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) key[k] = d_key[k];
+    for (int k = 0; k < 8; k++) key[k] = PREMAT ? 0u : d_key[k];
 
     // zero the padding rows 112..127 of A (row groups 14, 15) once
     for (int x = t; x < (int)(2 * TC_SBO / 16); x += TC_THREADS)
@@ -127,7 +131,23 @@ commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ 
         for (int job = t; job < TC_STAGE_COLS * TC_ROWS * 8; job += TC_THREADS) {
             int jj = job / (TC_ROWS * 8), rem = job % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
             uint64_t c[8];
-            prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
+            if (PREMAT) {
+                if (js + jj < j1) {
+                    const ulonglong2* src = reinterpret_cast<const ulonglong2*>(
+                        d_M + ((js + jj) * (uint64_t)KAPPA + (uint64_t)(group * TC_ROWS + il)) * D + 8 * blk);
+#pragma unroll
+                    for (int x = 0; x < 4; x++) {
+                        const ulonglong2 v = __ldcs(src + x);
+                        c[2 * x] = v.x;
+                        c[2 * x + 1] = v.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 8; x++) c[x] = 0;
+                }
+            } else {
+                prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
+            }
             uint32_t kk = (uint32_t)(jj * D + 8 * blk);
             uint8_t* dst = A_sh + il * TC_SBO + (kk >> 4) * TC_CORE + (kk & 15);
             // Two lanes fill one 128-byte core (8 plane rows x 16 bytes). The plane order is rotated by the
@@ -232,6 +252,309 @@ commit_tc_kernel(const uint32_t* __restrict__ d_key, const int8_t* __restrict__ 
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u));
     if (failed && t == 0) atomicMax(d_error, (int)TC_ERR_TIMEOUT);
     if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Pipelined form of the kernel above with a compact B operand: two operand buffers, so the MMAs of stage s run while the threads
+// build stage s + 1, and what a stage reads from global memory (digits; matrix coefficients when PREMAT) is
+// loaded into registers one stage ahead. One CTA per SM (2 x 96 KB of operands), 256 TMEM columns.
+// Barrier b = s & 1 is committed by stage s; a buffer is rewritten at stage s only after the commit of
+// stage s - 2 has completed (its (s >> 1)-th completion, parity ((s >> 1) - 1) & 1).
+//
+// B without the Toeplitz blow-up. With the output rows reversed (n = 63 - r) the operand of one (column, plane)
+// is B[n][k] = w[n + k], so the 8 x 16 core matrix at (row group nb, K block kq) depends on nb + 2 kq only. Stored
+// once per value d = nb + 2 kq (14 cores instead of 32), core d at byte 128 d, the matrix is exactly "the 16-byte
+// window of w at every byte offset o = 0..111, at address 16 o"; a K = 32 MMA over K blocks kq0, kq0 + 1 reads it
+// through a descriptor with start = base + 256 kq0, stride 128 between row groups and 256 between K blocks, one
+// MMA (N = 64) per plane. A thread produces seven consecutive windows of one alignment class with one funnel
+// shift per window.
+constexpr int TCP_THREADS = 512;                   // sixteen warps hide the latencies of the build
+constexpr int TC_BWIN = 112;                       // windows per (column, plane)
+constexpr uint32_t TC_BCP_BYTES = TC_BWIN * 16;    // 1792
+//
+// Where the matrix comes from (SRC): the ChaCha8 stream; d_M[j][i][k] as 64-bit coefficients (split into byte
+// planes here); or d_T, the byte planes already in operand order: for every stage of four columns and row group
+// the 28 KB image of the A buffer, [stage][group][14 x 2048] (ajtai_materialize_tc_ffi), which is copied as is.
+// With the last source and up to eight planes per pass (512 TMEM columns) the kernel's work is the B windows,
+// the copies and the MMAs.
+// materialize != nullptr: no digits, no MMAs; the A images of this CTA's stages are written there instead.
+enum TcSource { TC_SRC_CHACHA = 0, TC_SRC_COEFFS = 1, TC_SRC_TILED = 2 };
+constexpr int TCP_MAX_PLANES = 8;
+constexpr uint32_t TCP_A_IMAGE = 14 * TC_SBO;       // 28672 bytes: the rows that hold data
+
+// WIDE: the B operand is stored in full (every core matrix of the Toeplitz expansion, rows in natural order), so
+// that one MMA covers all planes of the pass (N = 64 np <= 256) instead of one MMA per plane: instructions of
+// N = 64 run far below the rate of the tensor pipe. The windows are still produced once per byte offset and
+// alignment class; each is stored to every (row, K block) that uses it.
+template <int SRC, bool WIDE>
+static __global__ void __launch_bounds__(TCP_THREADS, 1)
+commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const uint8_t* __restrict__ d_T,
+                      const int8_t* __restrict__ d_digits, uint64_t N, int p0, int np, uint64_t col_offset, uint64_t* __restrict__ partial,
+                      int* __restrict__ d_error, uint8_t* __restrict__ materialize) {
+    constexpr bool PREMAT = SRC == TC_SRC_COEFFS;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int n_cols = 64 * np;
+    const size_t b_bytes = WIDE ? (size_t)(n_cols / 8) * TC_SBO : (size_t)TC_STAGE_COLS * np * TC_BCP_BYTES, buf_bytes = TC_A_BYTES + b_bytes;
+    uint8_t* V_sh = smem + 2 * buf_bytes;
+    __shared__ __align__(8) uint64_t mbar[2];
+    __shared__ uint32_t tmem_base_sh;
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int group = blockIdx.y;
+    const uint64_t j0 = (uint64_t)blockIdx.x * TC_CHUNK_COLS;
+    const uint64_t j1 = j0 + TC_CHUNK_COLS < N ? j0 + TC_CHUNK_COLS : N;
+    uint32_t key[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) key[k] = SRC == TC_SRC_CHACHA ? d_key[k] : 0u;
+    const uint32_t tmem_cols = np > 4 ? 512u : 256u;
+
+    for (int x = t; x < TC_STAGE_COLS * TCP_MAX_PLANES * TC_V_STRIDE / 4; x += TCP_THREADS) reinterpret_cast<uint32_t*>(V_sh)[x] = 0;
+    for (int b = 0; b < 2; b++)   // zero padding rows 112..127 of both A buffers
+        for (int x = t; x < (int)(2 * TC_SBO / 16); x += TCP_THREADS)
+            reinterpret_cast<uint4*>(smem + b * buf_bytes + 14 * TC_SBO)[x] = make_uint4(0, 0, 0, 0);
+    if (t == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[1])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;");
+    const uint32_t tmem = tmem_base_sh;
+    const uint32_t idesc = umma_idesc_i8(WIDE ? n_cols : 64);
+    bool failed = false;
+    int bad_digit = 0;
+
+    // what one thread fetches for a stage: four digits, and the 8 coefficients of up to two (column, row, block) jobs
+    constexpr int JOBS = TC_STAGE_COLS * TC_ROWS * 8;   // 448
+    uint32_t zreg = 0;
+    ulonglong2 creg[4];
+    uint4 treg[4];   // TILED: 1792 16-byte pieces of the A image over 512 threads
+    auto fetch = [&](uint64_t js) {
+        const int x4 = 4 * t;   // digits x4 .. x4 + 3 of the stage's [col][plane][64] block
+        zreg = 0;
+        if (!materialize && x4 < TC_STAGE_COLS * np * D) {
+            const int jj = x4 / (np * D), rem = x4 % (np * D), p = rem / D, l = rem % D;
+            if (js + jj < j1) zreg = *reinterpret_cast<const uint32_t*>(d_digits + ((size_t)(p0 + p) * N + js + jj) * D + l);
+        }
+        if (SRC == TC_SRC_TILED) {
+            const uint4* src = reinterpret_cast<const uint4*>(d_T + ((js / TC_STAGE_COLS) * 3 + (uint64_t)group) * TCP_A_IMAGE);
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int piece = t + x * TCP_THREADS;
+                treg[x] = piece < (int)(TCP_A_IMAGE / 16) ? __ldcs(src + piece) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (PREMAT) {
+            const int job = t;
+            const int jj = job / (TC_ROWS * 8), rem = job % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
+            const bool on = job < JOBS && js + jj < j1;
+            const ulonglong2* src = reinterpret_cast<const ulonglong2*>(
+                d_M + ((js + jj) * (uint64_t)KAPPA + (uint64_t)(group * TC_ROWS + il)) * D + 8 * blk);
+#pragma unroll
+            for (int x = 0; x < 4; x++) creg[x] = on ? __ldcs(src + x) : make_ulonglong2(0, 0);
+        }
+    };
+    const int n_stages = (int)((j1 - j0 + TC_STAGE_COLS - 1) / TC_STAGE_COLS);
+    if (n_stages > 0) fetch(j0);
+
+    for (int sidx = 0; sidx < n_stages && !failed; sidx++) {
+        const uint64_t js = j0 + (uint64_t)sidx * TC_STAGE_COLS;
+        const int buf = sidx & 1;
+        uint8_t* A_sh = smem + buf * buf_bytes;
+        uint8_t* B_sh = A_sh + TC_A_BYTES;
+        // ---- reversed, sign-wrapped digit windows straight from the prefetched digits: the z word zi of a
+        // (column, plane) is window word 15 - zi reversed, and word 31 - zi reversed and negated ----
+        if (4 * t < TC_STAGE_COLS * np * D) {
+            if (((zreg & 0xffu) == 0x80u) | ((zreg & 0xff00u) == 0x8000u) | ((zreg & 0xff0000u) == 0x800000u) | ((zreg >> 24) == 0x80u))
+                bad_digit = 1;
+            uint32_t* win = reinterpret_cast<uint32_t*>(V_sh + (t >> 4) * TC_V_STRIDE);
+            const uint32_t rev = __byte_perm(zreg, 0, 0x0123);
+            win[15 - (t & 15)] = rev;
+            win[31 - (t & 15)] = __vneg4(rev);
+        }
+        // the MMAs that last read this buffer must be done before it is rewritten
+        if (sidx >= 2 && !materialize) {
+            if (!mbar_wait(smem_u32(&mbar[buf]), (uint32_t)(((sidx >> 1) - 1) & 1))) failed = true;
+        }
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        // ---- A: byte planes of the matrix coefficients ----
+        if (SRC == TC_SRC_TILED) {
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int piece = t + x * TCP_THREADS;
+                if (piece < (int)(TCP_A_IMAGE / 16)) reinterpret_cast<uint4*>(A_sh)[piece] = treg[x];
+            }
+        } else {
+            const int job = t;   // 448 jobs, one per thread
+            if (job < JOBS) {
+                const int jj = job / (TC_ROWS * 8), rem = job % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
+                uint64_t c[8];
+                if (PREMAT) {
+#pragma unroll
+                    for (int x = 0; x < 4; x++) {
+                        c[2 * x] = creg[x].x;
+                        c[2 * x + 1] = creg[x].y;
+                    }
+                } else {
+                    prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
+                }
+                const uint32_t kk = (uint32_t)(jj * D + 8 * blk);
+                uint8_t* dst = A_sh + il * TC_SBO + (kk >> 4) * TC_CORE + (kk & 15);
+                const int rot = (t >> 1) & 3;
+#pragma unroll
+                for (int b = 0; b < 8; b++) {
+                    const int bp = (b & 4) | ((b + rot) & 3);
+                    uint32_t w[8];
+#pragma unroll
+                    for (int x = 0; x < 8; x++) w[x] = b < 4 ? (uint32_t)c[x] : (uint32_t)(c[x] >> 32);
+                    const uint32_t sel = (uint32_t)(bp & 3) | ((4u + (uint32_t)(bp & 3)) << 4);
+                    const uint32_t lo = __byte_perm(__byte_perm(w[0], w[1], sel), __byte_perm(w[2], w[3], sel), 0x5410);
+                    const uint32_t hi = __byte_perm(__byte_perm(w[4], w[5], sel), __byte_perm(w[6], w[7], sel), 0x5410);
+                    *reinterpret_cast<uint2*>(dst + bp * 16) = make_uint2(lo, hi);
+                }
+            }
+        }
+        if (materialize) {
+            __syncthreads();
+            uint4* out = reinterpret_cast<uint4*>(materialize + ((js / TC_STAGE_COLS) * 3 + (uint64_t)group) * TCP_A_IMAGE);
+            for (int piece = t; piece < (int)(TCP_A_IMAGE / 16); piece += TCP_THREADS) out[piece] = reinterpret_cast<const uint4*>(A_sh)[piece];
+            __syncthreads();
+            continue;
+        }
+        // ---- the next stage's global reads are in flight while this one is built ----
+        if (sidx + 1 < n_stages) fetch(js + TC_STAGE_COLS);
+        // ---- B in full: task = (column-plane, two rows i = ipar + 2 (2 mr + d), byte class c); row r = 63 - c - 4 i,
+        // K block cq takes the window at word offset i + 4 cq of class c. The eight lanes of a quarter warp
+        // (c, ipar) write the eight rows of one core matrix: 128 contiguous bytes per store instruction ----
+        if (WIDE) {
+            for (int x = t; x < TC_STAGE_COLS * np * 32; x += TCP_THREADS) {
+                const int cls = x & 3, ipar = (x >> 2) & 1, mr = (x >> 3) & 3, cp = x >> 5, sh = 8 * cls;
+                const int jj = cp / np, p = cp % np, a0 = ipar + 4 * mr;
+                const uint32_t* W = reinterpret_cast<const uint32_t*>(V_sh + cp * TC_V_STRIDE) + a0;
+                uint32_t F[18];   // funnel-shifted words a0 .. a0 + 17 of the class
+                uint32_t wl = W[0];
+#pragma unroll
+                for (int q = 0; q < 18; q++) {
+                    const uint32_t wn = W[q + 1];
+                    F[q] = __funnelshift_r(wl, wn, sh);
+                    wl = wn;
+                }
+#pragma unroll
+                for (int d = 0; d < 2; d++) {
+                    const int r = 63 - cls - 4 * (a0 + 2 * d), n = 64 * p + r;
+                    uint8_t* row = B_sh + (n >> 3) * TC_SBO + (4 * jj) * TC_CORE + (n & 7) * 16;
+#pragma unroll
+                    for (int cq = 0; cq < 4; cq++)
+                        *reinterpret_cast<uint4*>(row + cq * TC_CORE) =
+                            make_uint4(F[2 * d + 4 * cq], F[2 * d + 4 * cq + 1], F[2 * d + 4 * cq + 2], F[2 * d + 4 * cq + 3]);
+                }
+            }
+        }
+        // ---- B: the 16-byte window of w at every byte offset; task = (column-plane, range of 7 word offsets, byte class) ----
+        for (int x = t; !WIDE && x < TC_STAGE_COLS * np * 16; x += TCP_THREADS) {
+            const int cp = x >> 4, cls = x & 3, a0 = 7 * ((x >> 2) & 3), sh = 8 * cls;
+            const uint32_t* W = reinterpret_cast<const uint32_t*>(V_sh + cp * TC_V_STRIDE) + a0;
+            uint8_t* dst = B_sh + cp * TC_BCP_BYTES + (4 * a0 + cls) * 16;
+            uint32_t wl = W[0], wn = W[1];
+            uint32_t f0 = __funnelshift_r(wl, wn, sh);
+            wl = wn; wn = W[2];
+            uint32_t f1 = __funnelshift_r(wl, wn, sh);
+            wl = wn; wn = W[3];
+            uint32_t f2 = __funnelshift_r(wl, wn, sh);
+            wl = wn; wn = W[4];
+            uint32_t f3 = __funnelshift_r(wl, wn, sh);
+#pragma unroll
+            for (int q = 0; q < 7; q++) {
+                *reinterpret_cast<uint4*>(dst + 64 * q) = make_uint4(f0, f1, f2, f3);
+                f0 = f1; f1 = f2; f2 = f3;
+                wl = wn; wn = W[q + 5];      // W[11] of the last range is word 32 of the window: padding
+                f3 = __funnelshift_r(wl, wn, sh);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (t == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;");
+            const uint32_t a_addr = smem_u32(A_sh), b_addr = smem_u32(B_sh);
+            // One thread issues 8 x np instructions per stage, so the loop body is kept to a few integer operations:
+            // the descriptors advance by adding to their address field (bytes / 16, no carry out of its 14 bits).
+            const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO), db0 = WIDE ? umma_desc(b_addr, TC_CORE, TC_SBO) : umma_desc(b_addr, 256, 128);
+            if (WIDE) {
+#pragma unroll
+                for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
+                    const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16), db = db0 + (uint64_t)(ks * 2 * TC_CORE / 16);
+                    const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                                 ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+                }
+            }
+#pragma unroll
+            for (int ks = 0; !WIDE && ks < TC_STAGE_K / 32; ks++) {
+                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16);
+                uint64_t db = db0 + (uint64_t)(((ks >> 1) * np * TC_BCP_BYTES + 256 * 2 * (ks & 1)) / 16);
+                uint32_t dcol = tmem;
+                if (sidx == 0 && ks == 0) {
+                    for (int p = 0; p < np; p++, db += TC_BCP_BYTES / 16, dcol += 64)
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                                     ::"r"(dcol), "l"(da), "l"(db), "r"(idesc) : "memory");
+                } else {
+                    for (int p = 0; p < np; p++, db += TC_BCP_BYTES / 16, dcol += 64)
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 1, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                                     ::"r"(dcol), "l"(da), "l"(db), "r"(idesc) : "memory");
+                }
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mbar[buf])) : "memory");
+        }
+    }
+    // ---- the last commit covers every MMA issued before it ----
+    if (!failed && n_stages > 0 && !materialize) {
+        const int last = n_stages - 1;
+        if (!mbar_wait(smem_u32(&mbar[last & 1]), (uint32_t)((last >> 1) & 1))) failed = true;
+    }
+    if (__syncthreads_or(failed)) failed = true;
+    asm volatile("tcgen05.fence::after_thread_sync;");
+
+    if (!failed && n_stages > 0 && !materialize) {
+        const int q = warp & 3, part = warp >> 2;   // four warps per quarter of the columns
+        const int m = 32 * q + lane, b = m & 7, il = m >> 3;
+        const uint64_t scale = 1ULL << (8 * b);
+        const int c_lo = part * (n_cols / 4), c_hi = c_lo + n_cols / 4;
+        for (int c0 = c_lo; c0 < c_hi; c0 += 8) {
+            uint32_t v[8];
+            const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)c0;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                         : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int32_t sv = (int32_t)v[e];
+                uint64_t f = sv >= 0 ? (uint64_t)sv : agl::P - (uint64_t)(-(int64_t)sv);
+                f = agl::mul(f, scale);
+#pragma unroll
+                for (int off = 1; off < 8; off <<= 1) f = agl::add(f, __shfl_xor_sync(0xffffffffu, f, off));
+                if (b == 0 && il < TC_ROWS) {
+                    const int n = c0 + e, p = n >> 6, r = WIDE ? (n & 63) : 63 - (n & 63);   // compact form: rows stored reversed
+                    partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols));
+    if (failed && t == 0) atomicMax(d_error, (int)TC_ERR_TIMEOUT);
+    if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
+}
+
+inline size_t tc_pipe_smem_bytes(int np, bool wide) {
+    return 2 * (TC_A_BYTES + (wide ? (size_t)(64 * np / 8) * TC_SBO : (size_t)TC_STAGE_COLS * np * TC_BCP_BYTES)) + TC_STAGE_COLS * TCP_MAX_PLANES * TC_V_STRIDE +
+           TC_STAGE_COLS * TCP_MAX_PLANES * D;
 }
 
 // out[p][i][r] = sum over chunks of partial[chunk][group = i / 14][p][i % 14][r]

@@ -215,6 +215,10 @@ _AGL_SIGNATURES = {
     "ajtai_commit_wide_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_int, c_void_p]),
     "ajtai_materialize_m_ffi": (c_int, [c_void_p, c_void_p, c_u64]),
     "ajtai_commit_s8_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
+    "ajtai_commit_s8_premat_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_void_p]),
+    "ajtai_tc_matrix_bytes": (c_u64, [c_u64]),
+    "ajtai_materialize_tc_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64]),
+    "ajtai_commit_s8_tiled_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_void_p]),
     "ajtai_commit_s8_scalar_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_u64, c_void_p]),
     "ajtai_fold_witness_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_int, c_void_p]),
     "ajtai_fold_commitment_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -151,6 +151,31 @@ def test_ternary_commit_matches_oracle(lib, n_ring):
     assert not d_o.to_numpy().any()
 
 
+@pytest.mark.parametrize("n_ring,planes", [(1, 1), (5, 3), (513, 4), (1100, 6), (700, 8), (130, 13)])
+def test_signed_digits_against_a_materialised_matrix(lib, n_ring, planes):
+    """The tensor-core kernel streaming the materialised matrix equals the one regenerating it (and the oracle)."""
+    from oracle import pyoracle
+    rng = np.random.default_rng(70 + n_ring)
+    digits = rng.integers(-127, 128, size=planes * n_ring * 64, dtype=np.int8)
+    d_k, d_z = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, digits)
+    d_m = DeviceBuffer(lib, 8 * 42 * 64 * n_ring)
+    assert lib.ajtai_materialize_m_ffi(d_k.ptr, d_m.ptr, n_ring) == 0
+    d_a, d_b = DeviceBuffer(lib, planes * 42 * 64 * 8), DeviceBuffer(lib, planes * 42 * 64 * 8)
+    assert lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n_ring, planes, 0, d_a.ptr) == 0
+    assert lib.ajtai_commit_s8_premat_ffi(d_m.ptr, d_z.ptr, n_ring, planes, d_b.ptr) == 0
+    assert np.array_equal(d_a.to_numpy(), d_b.to_numpy())
+    if n_ring <= 16:
+        assert np.array_equal(d_b.to_numpy(), pyoracle.ajtai_commit(KEY, digits, 1, n_ring, planes))
+    assert lib.ajtai_commit_s8_premat_ffi(None, d_z.ptr, n_ring, planes, d_b.ptr) == -2
+    # byte planes in operand order
+    d_t = DeviceBuffer(lib, lib.ajtai_tc_matrix_bytes(n_ring))
+    assert lib.ajtai_tc_matrix_bytes(n_ring) == ((n_ring + 3) // 4) * 3 * 28672
+    assert lib.ajtai_materialize_tc_ffi(d_k.ptr, d_t.ptr, n_ring, 0) == 0
+    d_c = DeviceBuffer(lib, planes * 42 * 64 * 8)
+    assert lib.ajtai_commit_s8_tiled_ffi(d_t.ptr, d_z.ptr, n_ring, planes, d_c.ptr) == 0
+    assert np.array_equal(d_a.to_numpy(), d_c.to_numpy())
+
+
 @pytest.mark.parametrize("n_ring,k_chunks", [(1, 13), (50, 13), (300, 8), (64, 16)])
 def test_wide_to_ternary_and_back(lib, n_ring, k_chunks):
     """Planes recombine to the coefficients (sum_i 2^i (pos_i - neg_i)); a coefficient that needs more bits
