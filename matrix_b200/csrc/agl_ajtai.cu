@@ -94,20 +94,19 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
 }  // extern "C"
 
 namespace {
-constexpr bool TC_WIDE = true;   // one MMA over all planes of a pass (N = 64 np, four planes) rather than one per plane
-constexpr int TC_PASS_PLANES = TC_WIDE ? TC_MAX_PLANES : TCP_MAX_PLANES;
+constexpr int TC_PASS_PLANES = TC_MAX_PLANES;   // one MMA covers all planes of a pass: N = 64 np <= 256
 
 template <int SRC>
 int launch_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0, int np,
               uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks) {
-    const size_t smem = tc_pipe_smem_bytes(np, TC_WIDE);
-    if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC, TC_WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
+    const size_t smem = tc_pipe_smem_bytes(np);
+    if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
     dim3 grid((unsigned)chunks, 3);
-    commit_tc_pipe_kernel<SRC, TC_WIDE><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, np, col_offset, partial, d_err, materialize);
+    commit_tc_pipe_kernel<SRC><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, np, col_offset, partial, d_err, materialize);
     return MB_OK;
 }
 
-// Signed 8-bit digit planes on the tensor cores, eight planes per pass; the matrix comes from the key stream
+// Signed 8-bit digit planes on the tensor cores, four planes per pass; the matrix comes from the key stream
 // (d_key), from 64-bit coefficients (d_M) or from byte planes in operand order (d_T).
 int commit_s8_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int planes,
                  uint64_t col_offset, uint64_t* d_out) {
@@ -120,7 +119,7 @@ int commit_s8_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T,
     const size_t chunks = (N + TC_CHUNK_COLS - 1) / TC_CHUNK_COLS;
     uint64_t* partial = nullptr;
     int* d_err = nullptr;
-    MB_CUDA(pool_alloc((void**)&partial, chunks * 3 * TCP_MAX_PLANES * TC_ROWS * D * sizeof(uint64_t)));
+    MB_CUDA(pool_alloc((void**)&partial, chunks * 3 * TC_MAX_PLANES * TC_ROWS * D * sizeof(uint64_t)));
     if (pool_alloc((void**)&d_err, sizeof(int)) != cudaSuccess) { pool_free(partial); return MB_ERR_CUDA; }
     int rc = MB_OK;
     if (cudaMemsetAsync(d_err, 0, sizeof(int), MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
@@ -158,7 +157,7 @@ extern "C" {
 // Addition: the same signed-digit commit on the tensor cores (tcgen05 kind::i8).
 // Digits must lie in [-127, 127] (-3 if a -128 is met: its negation, needed by
 // the negacyclic wrap, is not an s8; use the scalar entry point then). Planes
-// are processed eight at a time.
+// are processed four at a time.
 int ajtai_commit_s8_ffi(const uint32_t* d_key, const int8_t* d_digits, uint64_t N, int planes, uint64_t col_offset,
                         uint64_t* d_out) {
     if (!d_key) return MB_ERR_ARG;

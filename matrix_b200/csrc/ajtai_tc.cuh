@@ -12,14 +12,25 @@
 // columns (K = 32768) stays below 255 * 127 * 32768 < 2^31, so the accumulators
 // are drained every 512 columns.
 //
-// One CTA owns a chunk of columns and one of three groups of 14 matrix rows, so
-// no ChaCha8 block is generated twice. Per stage of four columns its 256 threads
-// generate the A bytes (the dominant cost: 112 ChaCha8 blocks per column) and
-// expand the digits into B, both in the no-swizzle K-major core-matrix layout
-// (8 rows x 16 bytes, cores contiguous along K), then one thread issues eight
-// K = 32 MMAs and commits them to an mbarrier that gates the reuse of the
-// buffers. Every wait is bounded and reports through an error word instead of
-// spinning forever.
+// One CTA (512 threads) owns a chunk of 512 columns and one of three groups of 14 matrix rows, so no ChaCha8
+// block is generated twice. It works in stages of four columns (K = 256) with two operand buffers: while one
+// thread's eight K = 32 MMAs of stage s run (committed to the buffer's mbarrier), all threads build stage s + 1,
+// and what a stage reads from global memory is loaded into registers one stage ahead. Operands use the
+// no-swizzle K-major core-matrix layout (8 rows x 16 bytes, cores contiguous along K). Barrier b = s & 1 is
+// committed by stage s; a buffer is rewritten at stage s only after the commit of stage s - 2 has completed
+// (its (s >> 1)-th completion, parity ((s >> 1) - 1) & 1). Every wait is bounded and reports through an error
+// word instead of spinning forever.
+//
+// B (the Toeplitz expansion) is built from the reversed, sign-wrapped digit window w of a (column, plane):
+// row r, K block cq is the 16 bytes of w at byte offset 63 - r + 16 cq. A thread takes one alignment class
+// (offset mod 4) and a run of word offsets, forms each window word with one funnel shift and stores every window
+// to the (row, K block) places that use it; the eight lanes of a quarter warp write the eight rows of one core
+// matrix (128 contiguous bytes per store instruction).
+//
+// Where the matrix comes from (TcSource): the ChaCha8 stream; d_M[j][i][k] as 64-bit coefficients (split into
+// byte planes here); or d_T, the byte planes already in operand order: per stage of four columns and row group
+// the 28 KB image of the A buffer, [stage][group][14 x 2048] (written by this kernel in its materialise mode),
+// which is copied as is.
 #pragma once
 #include "ajtai_kernels.cuh"
 
@@ -31,7 +42,6 @@ constexpr int TC_STAGE_COLS = 4;        // columns per MMA stage
 constexpr int TC_STAGE_K = TC_STAGE_COLS * D;   // 256 bytes of K per stage
 constexpr int TC_CHUNK_COLS = 512;      // columns per accumulation (s32 exactness)
 constexpr int TC_MAX_PLANES = 4;        // digit planes per CTA: N = 64 * planes <= 256
-constexpr int TC_THREADS = 256;
 constexpr uint32_t TC_CORE = 128;       // bytes of one 8 x 16 core matrix
 constexpr uint32_t TC_SBO = (TC_STAGE_K / 16) * TC_CORE;  // 2048: next 8-row group
 constexpr uint32_t TC_A_BYTES = 16 * TC_SBO;              // 128 rows
@@ -65,228 +75,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-// grid = (column chunks, 3 row groups); block = 256 threads; dynamic shared memory.
-// d_digits: [planes][N][64] s8 (this CTA uses planes p0 .. p0 + np - 1).
-// partial[((chunk * 3 + group) * np + p) * 14 * 64 + i_local * 64 + r] = canonical chunk sum.
-// PREMAT: the coefficients come from d_M[j][i][k] (the layout of ajtai_materialize_m_ffi, column j relative to
-// the first column of this call) instead of the ChaCha8 stream: the kernel then streams 28 KB of the matrix per
-// stage and its cost is the operand build and the reads of d_M, not the generation.
-template <bool PREMAT>
-static __global__ void __launch_bounds__(TC_THREADS)
-commit_tc_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const int8_t* __restrict__ d_digits, uint64_t N,
-                 int p0, int np, uint64_t col_offset, uint64_t* __restrict__ partial, int* __restrict__ d_error) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    const int n_cols = 64 * np;                       // UMMA N
-    uint8_t* A_sh = smem;                             // 32 KB
-    uint8_t* B_sh = smem + TC_A_BYTES;                // (n_cols / 8) * 2048
-    uint8_t* V_sh = B_sh + (size_t)(n_cols / 8) * TC_SBO;  // [4 cols][np][144]
-    int8_t* Z_sh = reinterpret_cast<int8_t*>(V_sh + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE);  // [4][np][64]
-    __shared__ __align__(8) uint64_t mbar;
-    __shared__ uint32_t tmem_base_sh;
-
-    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-    const int group = blockIdx.y;
-    const uint64_t j0 = (uint64_t)blockIdx.x * TC_CHUNK_COLS;
-    const uint64_t j1 = j0 + TC_CHUNK_COLS < N ? j0 + TC_CHUNK_COLS : N;
-    uint32_t key[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) key[k] = PREMAT ? 0u : d_key[k];
-
-    // zero the padding rows 112..127 of A (row groups 14, 15) once
-    for (int x = t; x < (int)(2 * TC_SBO / 16); x += TC_THREADS)
-        reinterpret_cast<uint4*>(A_sh + 14 * TC_SBO)[x] = make_uint4(0, 0, 0, 0);
-    if (t == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar)));
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(256u));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;");
-    const uint32_t tmem = tmem_base_sh;
-    const uint32_t bar = smem_u32(&mbar);
-    const uint32_t idesc = umma_idesc_i8(n_cols);
-    uint32_t phase = 0;
-    bool first = true, failed = false;
-    int bad_digit = 0;
-
-    for (uint64_t js = j0; js < j1 && !failed; js += TC_STAGE_COLS) {
-        // the previous stage's MMAs must have read A and B before they are overwritten
-        if (!first) {
-            if (!mbar_wait(bar, phase)) failed = true;
-            phase ^= 1;
-            if (__syncthreads_or(failed)) { failed = true; break; }
-        }
-        // ---- digits of this stage (zero beyond the last column) ----
-        for (int x = t; x < TC_STAGE_COLS * np * D; x += TC_THREADS) {
-            int jj = x / (np * D), rem = x % (np * D), p = rem / D, l = rem % D;
-            int8_t dgt = 0;
-            if (js + jj < j1) dgt = d_digits[((size_t)(p0 + p) * N + js + jj) * D + l];
-            if (dgt == -128) bad_digit = 1;
-            Z_sh[x] = dgt;
-        }
-        // ---- A: byte planes of the generated matrix coefficients ----
-        for (int job = t; job < TC_STAGE_COLS * TC_ROWS * 8; job += TC_THREADS) {
-            int jj = job / (TC_ROWS * 8), rem = job % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
-            uint64_t c[8];
-            if (PREMAT) {
-                if (js + jj < j1) {
-                    const ulonglong2* src = reinterpret_cast<const ulonglong2*>(
-                        d_M + ((js + jj) * (uint64_t)KAPPA + (uint64_t)(group * TC_ROWS + il)) * D + 8 * blk);
-#pragma unroll
-                    for (int x = 0; x < 4; x++) {
-                        const ulonglong2 v = __ldcs(src + x);
-                        c[2 * x] = v.x;
-                        c[2 * x + 1] = v.y;
-                    }
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 8; x++) c[x] = 0;
-                }
-            } else {
-                prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
-            }
-            uint32_t kk = (uint32_t)(jj * D + 8 * blk);
-            uint8_t* dst = A_sh + il * TC_SBO + (kk >> 4) * TC_CORE + (kk & 15);
-            // Two lanes fill one 128-byte core (8 plane rows x 16 bytes). The plane order is rotated by the
-            // lane pair so that the lanes of a store instruction spread over the rows (banks) instead of
-            // all writing the same row of different cores.
-            const int rot = (t >> 1) & 3;
-#pragma unroll
-            for (int b = 0; b < 8; b++) {
-                const int bp = (b & 4) | ((b + rot) & 3);
-                uint32_t w[8];
-#pragma unroll
-                for (int x = 0; x < 8; x++) w[x] = b < 4 ? (uint32_t)c[x] : (uint32_t)(c[x] >> 32);
-                const uint32_t sel = (uint32_t)(bp & 3) | ((4u + (uint32_t)(bp & 3)) << 4);
-                uint32_t lo = __byte_perm(__byte_perm(w[0], w[1], sel), __byte_perm(w[2], w[3], sel), 0x5410);
-                uint32_t hi = __byte_perm(__byte_perm(w[4], w[5], sel), __byte_perm(w[6], w[7], sel), 0x5410);
-                *reinterpret_cast<uint2*>(dst + bp * 16) = make_uint2(lo, hi);
-            }
-        }
-        __syncthreads();
-        // ---- w: the reversed, sign-wrapped digit window of every (column, plane): w[i] = z[63 - i] for i < 64,
-        // -z[127 - i] for 64 <= i < 128, one word (four digits) per thread and step; word 32 is padding ----
-        for (int x = t; x < TC_STAGE_COLS * np * 33; x += TC_THREADS) {
-            const int cp = x / 33, q = x % 33;  // cp = jj * np + p
-            const uint32_t* zw = reinterpret_cast<const uint32_t*>(Z_sh + cp * D);
-            uint32_t v = 0;
-            if (q < 16) v = __byte_perm(zw[15 - q], 0, 0x0123);
-            else if (q < 32) v = __vneg4(__byte_perm(zw[31 - q], 0, 0x0123));
-            reinterpret_cast<uint32_t*>(V_sh + cp * TC_V_STRIDE)[q] = v;
-        }
-        __syncthreads();
-        // ---- B[(p, r)][(jj, k)] = w[63 - r + k], 16-byte chunks along k cut out of w at any byte offset
-        // (five aligned words, funnel shifts). Consecutive lanes take consecutive rows of one core (16 bytes
-        // apart): a store instruction covers whole 128-byte cores. ----
-        for (int x = t; x < n_cols * 16; x += TC_THREADS) {
-            int n = ((x >> 7) << 3) | (x & 7), kc = (x >> 3) & 15, p = n >> 6, r = n & 63, jj = kc >> 2, cq = kc & 3;
-            const int s0 = 63 - r + 16 * cq, sh = 8 * (s0 & 3);
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(V_sh + (jj * np + p) * TC_V_STRIDE) + (s0 >> 2);
-            const uint32_t w0 = src[0], w1 = src[1], w2 = src[2], w3 = src[3], w4 = src[4];
-            uint4 v = make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
-                                 __funnelshift_r(w3, w4, sh));
-            *reinterpret_cast<uint4*>(B_sh + (n >> 3) * TC_SBO + kc * TC_CORE + (n & 7) * 16) = v;
-        }
-        // generic-proxy writes -> visible to the tensor core (async proxy)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (t == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;");
-            const uint32_t a_addr = smem_u32(A_sh), b_addr = smem_u32(B_sh);
-#pragma unroll 1
-            for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
-                uint64_t da = umma_desc(a_addr + ks * 2 * TC_CORE, TC_CORE, TC_SBO);
-                uint64_t db = umma_desc(b_addr + ks * 2 * TC_CORE, TC_CORE, TC_SBO);
-                uint32_t acc = (first && ks == 0) ? 0u : 1u;
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                    ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
-            }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-        }
-        first = false;
-    }
-    // ---- all MMAs of the chunk done ----
-    if (!first && !failed) {
-        if (!mbar_wait(bar, phase)) failed = true;
-    }
-    if (__syncthreads_or(failed)) failed = true;
-    asm volatile("tcgen05.fence::after_thread_sync;");
-
-    if (!failed && !first) {
-        // Drain: warp w reads TMEM lanes 32 (w & 3) ..+31 (row m = lane), warps 0-3 the first
-        // half of the columns, warps 4-7 the second. Row m = 8 i_local + b: the eight byte
-        // planes of one matrix row sit in eight consecutive lanes and are combined with a
-        // three-step butterfly of field additions after scaling by 2^(8b).
-        const int q = warp & 3, half = warp >> 2;
-        const int m = 32 * q + lane, b = m & 7, il = m >> 3;
-        const uint64_t scale = 1ULL << (8 * b);  // < 2^56, canonical
-        const int c_lo = half * (n_cols / 2), c_hi = c_lo + n_cols / 2;
-        for (int c0 = c_lo; c0 < c_hi; c0 += 8) {
-            uint32_t v[8];
-            uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)c0;
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                         : "r"(taddr));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                int32_t sv = (int32_t)v[e];
-                uint64_t f = sv >= 0 ? (uint64_t)sv : agl::P - (uint64_t)(-(int64_t)sv);
-                f = agl::mul(f, scale);
-#pragma unroll
-                for (int off = 1; off < 8; off <<= 1) f = agl::add(f, __shfl_xor_sync(0xffffffffu, f, off));
-                if (b == 0 && il < TC_ROWS) {
-                    int n = c0 + e, p = n >> 6, r = n & 63;
-                    partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
-                }
-            }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;");
-    __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u));
-    if (failed && t == 0) atomicMax(d_error, (int)TC_ERR_TIMEOUT);
-    if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
-}
-
-// ---------------------------------------------------------------------------------------------------
-// Pipelined form of the kernel above with a compact B operand: two operand buffers, so the MMAs of stage s run while the threads
-// build stage s + 1, and what a stage reads from global memory (digits; matrix coefficients when PREMAT) is
-// loaded into registers one stage ahead. One CTA per SM (2 x 96 KB of operands), 256 TMEM columns.
-// Barrier b = s & 1 is committed by stage s; a buffer is rewritten at stage s only after the commit of
-// stage s - 2 has completed (its (s >> 1)-th completion, parity ((s >> 1) - 1) & 1).
-//
-// B without the Toeplitz blow-up. With the output rows reversed (n = 63 - r) the operand of one (column, plane)
-// is B[n][k] = w[n + k], so the 8 x 16 core matrix at (row group nb, K block kq) depends on nb + 2 kq only. Stored
-// once per value d = nb + 2 kq (14 cores instead of 32), core d at byte 128 d, the matrix is exactly "the 16-byte
-// window of w at every byte offset o = 0..111, at address 16 o"; a K = 32 MMA over K blocks kq0, kq0 + 1 reads it
-// through a descriptor with start = base + 256 kq0, stride 128 between row groups and 256 between K blocks, one
-// MMA (N = 64) per plane. A thread produces seven consecutive windows of one alignment class with one funnel
-// shift per window.
-constexpr int TCP_THREADS = 512;                   // sixteen warps hide the latencies of the build
-constexpr int TC_BWIN = 112;                       // windows per (column, plane)
-constexpr uint32_t TC_BCP_BYTES = TC_BWIN * 16;    // 1792
-//
-// Where the matrix comes from (SRC): the ChaCha8 stream; d_M[j][i][k] as 64-bit coefficients (split into byte
-// planes here); or d_T, the byte planes already in operand order: for every stage of four columns and row group
-// the 28 KB image of the A buffer, [stage][group][14 x 2048] (ajtai_materialize_tc_ffi), which is copied as is.
-// With the last source and up to eight planes per pass (512 TMEM columns) the kernel's work is the B windows,
-// the copies and the MMAs.
-// materialize != nullptr: no digits, no MMAs; the A images of this CTA's stages are written there instead.
+constexpr int TCP_THREADS = 512;                    // sixteen warps hide the latencies of the build
 enum TcSource { TC_SRC_CHACHA = 0, TC_SRC_COEFFS = 1, TC_SRC_TILED = 2 };
-constexpr int TCP_MAX_PLANES = 8;
-constexpr uint32_t TCP_A_IMAGE = 14 * TC_SBO;       // 28672 bytes: the rows that hold data
+constexpr uint32_t TCP_A_IMAGE = 14 * TC_SBO;       // 28672 bytes: the rows of the A buffer that hold data
 
-// WIDE: the B operand is stored in full (every core matrix of the Toeplitz expansion, rows in natural order), so
-// that one MMA covers all planes of the pass (N = 64 np <= 256) instead of one MMA per plane: instructions of
-// N = 64 run far below the rate of the tensor pipe. The windows are still produced once per byte offset and
-// alignment class; each is stored to every (row, K block) that uses it.
-template <int SRC, bool WIDE>
+// grid = (column chunks, 3 row groups); dynamic shared memory tc_pipe_smem_bytes(np).
+// d_digits: [planes][N][64] s8 (this CTA uses planes p0 .. p0 + np - 1, np <= 4: N = 64 np columns of one MMA).
+// partial[((chunk * 3 + group) * np + p) * 14 * 64 + i_local * 64 + r] = canonical chunk sum.
+// materialize != nullptr: no digits, no MMAs; the A images of this CTA's stages are written there instead.
+template <int SRC>
 static __global__ void __launch_bounds__(TCP_THREADS, 1)
 commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const uint8_t* __restrict__ d_T,
                       const int8_t* __restrict__ d_digits, uint64_t N, int p0, int np, uint64_t col_offset, uint64_t* __restrict__ partial,
@@ -294,7 +91,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     constexpr bool PREMAT = SRC == TC_SRC_COEFFS;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int n_cols = 64 * np;
-    const size_t b_bytes = WIDE ? (size_t)(n_cols / 8) * TC_SBO : (size_t)TC_STAGE_COLS * np * TC_BCP_BYTES, buf_bytes = TC_A_BYTES + b_bytes;
+    const size_t b_bytes = (size_t)(n_cols / 8) * TC_SBO, buf_bytes = TC_A_BYTES + b_bytes;
     uint8_t* V_sh = smem + 2 * buf_bytes;
     __shared__ __align__(8) uint64_t mbar[2];
     __shared__ uint32_t tmem_base_sh;
@@ -306,9 +103,9 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     uint32_t key[8];
 #pragma unroll
     for (int k = 0; k < 8; k++) key[k] = SRC == TC_SRC_CHACHA ? d_key[k] : 0u;
-    const uint32_t tmem_cols = np > 4 ? 512u : 256u;
+    const uint32_t tmem_cols = 256u;
 
-    for (int x = t; x < TC_STAGE_COLS * TCP_MAX_PLANES * TC_V_STRIDE / 4; x += TCP_THREADS) reinterpret_cast<uint32_t*>(V_sh)[x] = 0;
+    for (int x = t; x < TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE / 4; x += TCP_THREADS) reinterpret_cast<uint32_t*>(V_sh)[x] = 0;
     for (int b = 0; b < 2; b++)   // zero padding rows 112..127 of both A buffers
         for (int x = t; x < (int)(2 * TC_SBO / 16); x += TCP_THREADS)
             reinterpret_cast<uint4*>(smem + b * buf_bytes + 14 * TC_SBO)[x] = make_uint4(0, 0, 0, 0);
@@ -325,7 +122,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;");
     const uint32_t tmem = tmem_base_sh;
-    const uint32_t idesc = umma_idesc_i8(WIDE ? n_cols : 64);
+    const uint32_t idesc = umma_idesc_i8(n_cols);
     bool failed = false;
     int bad_digit = 0;
 
@@ -431,49 +228,26 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
         // ---- B in full: task = (column-plane, two rows i = ipar + 2 (2 mr + d), byte class c); row r = 63 - c - 4 i,
         // K block cq takes the window at word offset i + 4 cq of class c. The eight lanes of a quarter warp
         // (c, ipar) write the eight rows of one core matrix: 128 contiguous bytes per store instruction ----
-        if (WIDE) {
-            for (int x = t; x < TC_STAGE_COLS * np * 32; x += TCP_THREADS) {
-                const int cls = x & 3, ipar = (x >> 2) & 1, mr = (x >> 3) & 3, cp = x >> 5, sh = 8 * cls;
-                const int jj = cp / np, p = cp % np, a0 = ipar + 4 * mr;
-                const uint32_t* W = reinterpret_cast<const uint32_t*>(V_sh + cp * TC_V_STRIDE) + a0;
-                uint32_t F[18];   // funnel-shifted words a0 .. a0 + 17 of the class
-                uint32_t wl = W[0];
-#pragma unroll
-                for (int q = 0; q < 18; q++) {
-                    const uint32_t wn = W[q + 1];
-                    F[q] = __funnelshift_r(wl, wn, sh);
-                    wl = wn;
-                }
-#pragma unroll
-                for (int d = 0; d < 2; d++) {
-                    const int r = 63 - cls - 4 * (a0 + 2 * d), n = 64 * p + r;
-                    uint8_t* row = B_sh + (n >> 3) * TC_SBO + (4 * jj) * TC_CORE + (n & 7) * 16;
-#pragma unroll
-                    for (int cq = 0; cq < 4; cq++)
-                        *reinterpret_cast<uint4*>(row + cq * TC_CORE) =
-                            make_uint4(F[2 * d + 4 * cq], F[2 * d + 4 * cq + 1], F[2 * d + 4 * cq + 2], F[2 * d + 4 * cq + 3]);
-                }
-            }
-        }
-        // ---- B: the 16-byte window of w at every byte offset; task = (column-plane, range of 7 word offsets, byte class) ----
-        for (int x = t; !WIDE && x < TC_STAGE_COLS * np * 16; x += TCP_THREADS) {
-            const int cp = x >> 4, cls = x & 3, a0 = 7 * ((x >> 2) & 3), sh = 8 * cls;
+        for (int x = t; x < TC_STAGE_COLS * np * 32; x += TCP_THREADS) {
+            const int cls = x & 3, ipar = (x >> 2) & 1, mr = (x >> 3) & 3, cp = x >> 5, sh = 8 * cls;
+            const int jj = cp / np, p = cp % np, a0 = ipar + 4 * mr;
             const uint32_t* W = reinterpret_cast<const uint32_t*>(V_sh + cp * TC_V_STRIDE) + a0;
-            uint8_t* dst = B_sh + cp * TC_BCP_BYTES + (4 * a0 + cls) * 16;
-            uint32_t wl = W[0], wn = W[1];
-            uint32_t f0 = __funnelshift_r(wl, wn, sh);
-            wl = wn; wn = W[2];
-            uint32_t f1 = __funnelshift_r(wl, wn, sh);
-            wl = wn; wn = W[3];
-            uint32_t f2 = __funnelshift_r(wl, wn, sh);
-            wl = wn; wn = W[4];
-            uint32_t f3 = __funnelshift_r(wl, wn, sh);
+            uint32_t F[18];   // funnel-shifted words a0 .. a0 + 17 of the class
+            uint32_t wl = W[0];
 #pragma unroll
-            for (int q = 0; q < 7; q++) {
-                *reinterpret_cast<uint4*>(dst + 64 * q) = make_uint4(f0, f1, f2, f3);
-                f0 = f1; f1 = f2; f2 = f3;
-                wl = wn; wn = W[q + 5];      // W[11] of the last range is word 32 of the window: padding
-                f3 = __funnelshift_r(wl, wn, sh);
+            for (int q = 0; q < 18; q++) {
+                const uint32_t wn = W[q + 1];
+                F[q] = __funnelshift_r(wl, wn, sh);
+                wl = wn;
+            }
+#pragma unroll
+            for (int d = 0; d < 2; d++) {
+                const int r = 63 - cls - 4 * (a0 + 2 * d), n = 64 * p + r;
+                uint8_t* row = B_sh + (n >> 3) * TC_SBO + (4 * jj) * TC_CORE + (n & 7) * 16;
+#pragma unroll
+                for (int cq = 0; cq < 4; cq++)
+                    *reinterpret_cast<uint4*>(row + cq * TC_CORE) =
+                        make_uint4(F[2 * d + 4 * cq], F[2 * d + 4 * cq + 1], F[2 * d + 4 * cq + 2], F[2 * d + 4 * cq + 3]);
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -481,32 +255,14 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
         if (t == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;");
             const uint32_t a_addr = smem_u32(A_sh), b_addr = smem_u32(B_sh);
-            // One thread issues 8 x np instructions per stage, so the loop body is kept to a few integer operations:
-            // the descriptors advance by adding to their address field (bytes / 16, no carry out of its 14 bits).
-            const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO), db0 = WIDE ? umma_desc(b_addr, TC_CORE, TC_SBO) : umma_desc(b_addr, 256, 128);
-            if (WIDE) {
+            // the descriptors advance by adding to their address field (bytes / 16, no carry out of its 14 bits)
+            const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO), db0 = umma_desc(b_addr, TC_CORE, TC_SBO);
 #pragma unroll
-                for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
-                    const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16), db = db0 + (uint64_t)(ks * 2 * TC_CORE / 16);
-                    const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
-                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                                 ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
-                }
-            }
-#pragma unroll
-            for (int ks = 0; !WIDE && ks < TC_STAGE_K / 32; ks++) {
-                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16);
-                uint64_t db = db0 + (uint64_t)(((ks >> 1) * np * TC_BCP_BYTES + 256 * 2 * (ks & 1)) / 16);
-                uint32_t dcol = tmem;
-                if (sidx == 0 && ks == 0) {
-                    for (int p = 0; p < np; p++, db += TC_BCP_BYTES / 16, dcol += 64)
-                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                                     ::"r"(dcol), "l"(da), "l"(db), "r"(idesc) : "memory");
-                } else {
-                    for (int p = 0; p < np; p++, db += TC_BCP_BYTES / 16, dcol += 64)
-                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 1, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                                     ::"r"(dcol), "l"(da), "l"(db), "r"(idesc) : "memory");
-                }
+            for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
+                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16), db = db0 + (uint64_t)(ks * 2 * TC_CORE / 16);
+                const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                             ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mbar[buf])) : "memory");
         }
@@ -539,7 +295,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
 #pragma unroll
                 for (int off = 1; off < 8; off <<= 1) f = agl::add(f, __shfl_xor_sync(0xffffffffu, f, off));
                 if (b == 0 && il < TC_ROWS) {
-                    const int n = c0 + e, p = n >> 6, r = WIDE ? (n & 63) : 63 - (n & 63);   // compact form: rows stored reversed
+                    const int n = c0 + e, p = n >> 6, r = n & 63;
                     partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
                 }
             }
@@ -552,9 +308,8 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
 }
 
-inline size_t tc_pipe_smem_bytes(int np, bool wide) {
-    return 2 * (TC_A_BYTES + (wide ? (size_t)(64 * np / 8) * TC_SBO : (size_t)TC_STAGE_COLS * np * TC_BCP_BYTES)) + TC_STAGE_COLS * TCP_MAX_PLANES * TC_V_STRIDE +
-           TC_STAGE_COLS * TCP_MAX_PLANES * D;
+inline size_t tc_pipe_smem_bytes(int np) {
+    return 2 * (TC_A_BYTES + (size_t)(64 * np / 8) * TC_SBO) + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE;
 }
 
 // out[p][i][r] = sum over chunks of partial[chunk][group = i / 14][p][i % 14][r]
@@ -572,10 +327,6 @@ static __global__ void reduce_tc_partials_kernel(const uint64_t* __restrict__ pa
     }
 }
 
-inline size_t tc_smem_bytes(int np) {
-    return TC_A_BYTES + (size_t)(64 * np / 8) * TC_SBO + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE +
-           TC_STAGE_COLS * TC_MAX_PLANES * D;
-}
 
 }  // namespace aj
 }  // namespace mb
