@@ -313,6 +313,15 @@ def column_range(n_ring, world, rank):
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+def _add_mod_q(a, b):
+    """(a + b) mod q on uint64 arrays of canonical residues, without leaving 64-bit arithmetic."""
+    q = np.uint64(AGL_Q)
+    b = np.where(b >= q, b - q, b)
+    s = a + b                      # wraps mod 2^64
+    wrapped = s < a
+    return np.where(wrapped | (s >= q), s - q, s)   # after a wrap s - q wraps back to the true a + b - q
+
+
 def _sum_column_shards(commit_columns, comm, ncols, words):
     """All-gathers the ranks' partial results over their column ranges and adds them mod q."""
     parts = []
@@ -322,10 +331,10 @@ def _sum_column_shards(commit_columns, comm, ncols, words):
         assert part.size == words
         parts.append(part)
     gathered = comm.allgather(parts)
-    total = np.zeros(words, dtype=object)
+    total = np.zeros(words, dtype=np.uint64)
     for p in gathered:
-        total = (total + p.astype(object)) % AGL_Q
-    return np.array(total, dtype=np.uint64)
+        total = _add_mod_q(total, np.asarray(p, dtype=np.uint64).reshape(-1))
+    return total
 
 
 def link_round_sharded(round_commitments, comm, n_commit):
