@@ -96,14 +96,24 @@ int ajtai_commit_s8_scalar_ffi(const uint32_t* d_key, const int8_t* d_digits, ui
 namespace {
 constexpr int TC_PASS_PLANES = TC_MAX_PLANES;   // one MMA covers all planes of a pass: N = 64 np <= 256
 
+template <int SRC, int NP>
+int launch_tc_np(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0,
+                 uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks) {
+    const size_t smem = tc_pipe_smem_bytes(NP);
+    if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
+    dim3 grid((unsigned)chunks, 3);
+    commit_tc_pipe_kernel<SRC, NP><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize);
+    return MB_OK;
+}
 template <int SRC>
 int launch_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0, int np,
               uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks) {
-    const size_t smem = tc_pipe_smem_bytes(np);
-    if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
-    dim3 grid((unsigned)chunks, 3);
-    commit_tc_pipe_kernel<SRC><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, np, col_offset, partial, d_err, materialize);
-    return MB_OK;
+    switch (np) {
+        case 1: return launch_tc_np<SRC, 1>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
+        case 2: return launch_tc_np<SRC, 2>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
+        case 3: return launch_tc_np<SRC, 3>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
+        default: return launch_tc_np<SRC, 4>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
+    }
 }
 
 // Signed 8-bit digit planes on the tensor cores, four planes per pass; the matrix comes from the key stream

@@ -83,11 +83,14 @@ constexpr uint32_t TCP_A_IMAGE = 14 * TC_SBO;       // 28672 bytes: the rows of 
 // d_digits: [planes][N][64] s8 (this CTA uses planes p0 .. p0 + np - 1, np <= 4: N = 64 np columns of one MMA).
 // partial[((chunk * 3 + group) * np + p) * 14 * 64 + i_local * 64 + r] = canonical chunk sum.
 // materialize != nullptr: no digits, no MMAs; the A images of this CTA's stages are written there instead.
-template <int SRC>
+// The number of planes of the pass is a template parameter: the index arithmetic of the build (which column,
+// plane, row a task works on) folds to shifts and constants.
+template <int SRC, int NP>
 static __global__ void __launch_bounds__(TCP_THREADS, 1)
 commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const uint8_t* __restrict__ d_T,
-                      const int8_t* __restrict__ d_digits, uint64_t N, int p0, int np, uint64_t col_offset, uint64_t* __restrict__ partial,
+                      const int8_t* __restrict__ d_digits, uint64_t N, int p0, uint64_t col_offset, uint64_t* __restrict__ partial,
                       int* __restrict__ d_error, uint8_t* __restrict__ materialize) {
+    constexpr int np = NP;
     constexpr bool PREMAT = SRC == TC_SRC_COEFFS;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int n_cols = 64 * np;
