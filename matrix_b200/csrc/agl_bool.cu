@@ -32,6 +32,21 @@ __device__ __forceinline__ E2 ld(const uint64_t* p, uint64_t i) { return agl::e2
 __device__ __forceinline__ void st(uint64_t* p, uint64_t i, E2 v) { agl::e2_store(p + 2 * i, agl::e2_canon(v)); }
 __device__ __forceinline__ E2 zero() { return E2{0, 0}; }
 
+// Exact sums of extension products a b (three 160-bit integer sums), reduced once: at most 64 products.
+struct LazyE2 {
+    gl::Acc s00, s11, s01;
+};
+__device__ __forceinline__ LazyE2 lazy_zero() { return LazyE2{gl::acc_zero(), gl::acc_zero(), gl::acc_zero()}; }
+__device__ __forceinline__ void lazy_mul(LazyE2& q, E2 a, E2 b) {
+    gl::acc_mul(q.s00, a.c0, b.c0);
+    gl::acc_mul(q.s11, a.c1, b.c1);
+    gl::acc_mul(q.s01, a.c0, b.c1);
+    gl::acc_mul(q.s01, a.c1, b.c0);
+}
+__device__ __forceinline__ E2 lazy_reduce(const LazyE2& q) {
+    return E2{agl::add(agl::acc_reduce(q.s00), agl::mul_small(agl::acc_reduce(q.s11), 3)), agl::acc_reduce(q.s01)};
+}
+
 // Largest t in [0, n_terms) with off[t] <= i (the term whose slice holds entry i; empty terms are skipped).
 __device__ __forceinline__ int find_term(const uint32_t* off, int n_terms, uint32_t i) {
     int lo = 0, hi = n_terms - 1;
@@ -53,7 +68,7 @@ __device__ __forceinline__ E2 warp_sum(E2 v) {
 }
 
 // One tile per block: flags, the tile's group count and its share of the message.
-__global__ void __launch_bounds__(THREADS) bool_mark_msg_kernel(const uint32_t* __restrict__ idx, const uint64_t* __restrict__ val,
+__global__ void __launch_bounds__(THREADS, 2) bool_mark_msg_kernel(const uint32_t* __restrict__ idx, const uint64_t* __restrict__ val,
                                                                 const uint32_t* __restrict__ term_off, const uint64_t* __restrict__ w,
                                                                 const uint64_t* __restrict__ eq, int n_terms, uint32_t n,
                                                                 uint32_t* __restrict__ flags, uint32_t* __restrict__ tile_count,
@@ -69,9 +84,25 @@ __global__ void __launch_bounds__(THREADS) bool_mark_msg_kernel(const uint32_t* 
     const uint32_t* off = cached ? soff : term_off;
     const uint32_t covered = off[n_terms];   // entries past the last term belong to no group
 
+    // The weight of a term is applied once per run of entries of that term: S[c] collects a_c (a_c - 1) e_c as exact
+    // sums (a thread has at most eight entries), acc[c] += w_t S[c] when the term changes and at the end.
     E2 acc[4];
+    LazyE2 S[4];
 #pragma unroll
-    for (int k = 0; k < 4; k++) acc[k] = zero();
+    for (int k = 0; k < 4; k++) {
+        acc[k] = zero();
+        S[k] = lazy_zero();
+    }
+    int cur_t = -1;
+    auto flush = [&]() {
+        if (cur_t < 0) return;
+        const E2 wt = ld(w, cur_t);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            acc[k] = agl::e2_add(acc[k], agl::e2_mul_lazy(wt, lazy_reduce(S[k])));
+            S[k] = lazy_zero();
+        }
+    };
     uint32_t count = 0;
     const uint32_t base = blockIdx.x * (uint32_t)TILE;
 #pragma unroll 1
@@ -98,17 +129,21 @@ __global__ void __launch_bounds__(THREADS) bool_mark_msg_kernel(const uint32_t* 
             v1 = ld(val, i);
         }
         const E2 e0 = ld(eq, 2 * (uint64_t)rest), e1 = ld(eq, 2 * (uint64_t)rest + 1);
-        const E2 wt = ld(w, t), one{1, 0};
+        if (t != cur_t) {
+            flush();
+            cur_t = t;
+        }
+        const E2 one{1, 0};
         const E2 vd = agl::e2_sub(v1, v0), ed = agl::e2_sub(e1, e0);
         E2 a = v0, ec = e0;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const E2 q = agl::e2_mul_lazy(a, agl::e2_sub(a, one));
-            acc[c] = agl::e2_add(acc[c], agl::e2_mul_lazy(agl::e2_mul_lazy(wt, q), ec));
+            lazy_mul(S[c], agl::e2_mul_lazy(a, agl::e2_sub(a, one)), ec);
             a = agl::e2_add(a, vd);
             ec = agl::e2_add(ec, ed);
         }
     }
+    flush();
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         const E2 v = warp_sum(acc[k]);
