@@ -56,6 +56,20 @@ int ext2_batch_exp_ffi(const uint64_t* d_a, uint64_t exp, uint64_t* d_result, in
 int ext2_scale_accumulate_ffi(uint64_t scalar_c0, uint64_t scalar_c1, const uint64_t* d_src, uint64_t* d_acc, int n);
 int gl_to_ext2_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
 int ext2_to_gl_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+/* Degree-5 extension F_p[X]/(X^5 - 3), five consecutive words per element
+ * (goldilocks-cuda-rs/src/ffi.rs:229-281; arithmetic cuda/extension.cuh:299-700).
+ * The inverse of zero is zero; the Frobenius map is x -> x^p. */
+int ext5_batch_add_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int ext5_batch_sub_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int ext5_batch_mul_ffi(const uint64_t* d_a, const uint64_t* d_b, uint64_t* d_result, int n);
+int ext5_batch_inverse_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext5_batch_mul_scalar_ffi(uint64_t scalar, const uint64_t* d_a, uint64_t* d_result, int n);
+int ext5_batch_neg_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext5_batch_square_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext5_batch_frobenius_ffi(const uint64_t* d_a, uint64_t* d_result, int n);
+int ext5_batch_exp_ffi(const uint64_t* d_a, uint64_t exp, uint64_t* d_result, int n);
+int gl_to_ext5_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
+int ext5_to_gl_batch_ffi(const uint64_t* d_input, uint64_t* d_output, int n);
 int gl_zero_buffer(uint64_t* d_buf, int n);
 /* out[new] = in[old] where bit b of new is bit d_perm_map[b] of old (wrapper.cu:1843-1860) */
 int bit_permute_gl_ffi(const uint64_t* d_input, uint64_t* d_output, const int* d_perm_map, int n_bits, int total);

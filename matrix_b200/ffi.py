@@ -96,6 +96,17 @@ _GL_SIGNATURES = {
     "gl_batch_exp": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
     "ext2_batch_exp_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
     "ext2_scale_accumulate_ffi": (c_int, [c_u64, c_u64, c_void_p, c_void_p, c_int]),
+    "ext5_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "ext5_batch_sub_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "ext5_batch_mul_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "ext5_batch_inverse_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext5_batch_neg_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext5_batch_square_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext5_batch_frobenius_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext5_batch_mul_scalar_ffi": (c_int, [c_u64, c_void_p, c_void_p, c_int]),
+    "ext5_batch_exp_ffi": (c_int, [c_void_p, c_u64, c_void_p, c_int]),
+    "gl_to_ext5_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
+    "ext5_to_gl_batch_ffi": (c_int, [c_void_p, c_void_p, c_int]),
     "gl_zero_buffer": (c_int, [c_void_p, c_int]),
     "bit_permute_gl_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "monolith_merkle_tree_gl_ffi": (c_int, [c_void_p, c_void_p, c_int]),

@@ -213,3 +213,54 @@ void gl_compress(const uint64_t l[4], const uint64_t r[4], uint64_t out[4]) {
 
 /* flat wrappers for tests */
 void oracle_gl_e2_inv(const uint64_t *a, uint64_t *out) { ext2_t r = e2_inv(e2(a[0], a[1])); out[0] = r.c0; out[1] = r.c1; }
+
+/* ---- Degree-5 extension F_p[X]/(X^5 - 3): cuda/extension.cuh:27-28 (W = 3,
+ * DTH_ROOT = W^((p-1)/5)), :388-456 (product, wrapped terms times W), :516-530
+ * (Frobenius: coefficient i times DTH_ROOT^i), :574-611 (inverse through the four
+ * conjugates and the norm), :625-638 (square-and-multiply, low bit first).
+ * Elements are five canonical words; inputs are canonicalised first. ---- */
+#define E5_DTH 1041288259238279555ULL
+
+static void e5_mul_o(const uint64_t *a, const uint64_t *b, uint64_t *r) {
+    uint64_t t[9] = {0};
+    for (int i = 0; i < 5; i++)
+        for (int j = 0; j < 5; j++) t[i + j] = gl_add(t[i + j], gl_mul(a[i], b[j]));
+    for (int k = 0; k < 5; k++) r[k] = k < 4 ? gl_add(t[k], gl_mul(3, t[k + 5])) : t[k];
+}
+static void e5_frob_o(const uint64_t *a, uint64_t *r) {
+    uint64_t d = 1;
+    for (int i = 0; i < 5; i++) { r[i] = gl_mul(a[i], d); d = gl_mul(d, E5_DTH); }
+}
+void oracle_gl_e5_mul(const uint64_t *a, const uint64_t *b, uint64_t *out) {
+    uint64_t x[5], y[5];
+    for (int i = 0; i < 5; i++) { x[i] = a[i] % GL_P; y[i] = b[i] % GL_P; }
+    e5_mul_o(x, y, out);
+}
+void oracle_gl_e5_frobenius(const uint64_t *a, uint64_t *out) {
+    uint64_t x[5];
+    for (int i = 0; i < 5; i++) x[i] = a[i] % GL_P;
+    e5_frob_o(x, out);
+}
+void oracle_gl_e5_inv(const uint64_t *a, uint64_t *out) {
+    uint64_t x[5], f[5], conj[5], t[5], norm[5];
+    for (int i = 0; i < 5; i++) x[i] = a[i] % GL_P;
+    e5_frob_o(x, f);                 /* a^p */
+    memcpy(conj, f, sizeof conj);
+    for (int k = 0; k < 3; k++) {    /* times a^(p^2), a^(p^3), a^(p^4) */
+        e5_frob_o(f, t); memcpy(f, t, sizeof f);
+        e5_mul_o(conj, f, t); memcpy(conj, t, sizeof conj);
+    }
+    e5_mul_o(x, conj, norm);         /* in the base field */
+    uint64_t ni = gl_inv(norm[0]);
+    for (int i = 0; i < 5; i++) out[i] = gl_mul(conj[i], ni);
+}
+void oracle_gl_e5_pow(const uint64_t *a, uint64_t e, uint64_t *out) {
+    uint64_t r[5] = {1, 0, 0, 0, 0}, b[5], t[5];
+    for (int i = 0; i < 5; i++) b[i] = a[i] % GL_P;
+    while (e) {
+        if (e & 1) { e5_mul_o(r, b, t); memcpy(r, t, sizeof r); }
+        e5_mul_o(b, b, t); memcpy(b, t, sizeof b);
+        e >>= 1;
+    }
+    memcpy(out, r, sizeof r);
+}

@@ -200,7 +200,24 @@ _SIGS.update({
     "oracle_gl_batched_claims": (None, [vp, vp, ci, sz, sz, vp]),
     "oracle_gl_batched_prove": (ci, [vp, vp, vp, ci, ci, ctypes.c_char_p, sz, vp, vp, vp, vp, vp, vp, vp]),
     "oracle_gl_e2_inv": (None, [vp, vp]),
+    "oracle_gl_e5_mul": (None, [vp, vp, vp]),
+    "oracle_gl_e5_frobenius": (None, [vp, vp]),
+    "oracle_gl_e5_inv": (None, [vp, vp]),
+    "oracle_gl_e5_pow": (None, [vp, u64, vp]),
 })
+
+
+def e5_op(name, a, b=None, e=None):
+    """One Ext5 operation of the oracle on lists of five words: name in mul / frobenius / inv / pow."""
+    lib = load()
+    A, O = (u64 * 5)(*a), (u64 * 5)()
+    if name == "mul":
+        lib.oracle_gl_e5_mul(A, (u64 * 5)(*b), O)
+    elif name == "pow":
+        lib.oracle_gl_e5_pow(A, e, O)
+    else:
+        getattr(lib, "oracle_gl_e5_" + name)(A, O)
+    return [int(x) for x in O]
 
 
 def batched_prove(a, b, point, K, nv, label=b"bench"):

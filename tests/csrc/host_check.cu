@@ -2,6 +2,7 @@
 // field, Poseidon2 and transcript code so they can be compared with the CPU
 // oracle on a machine without a GPU. Not part of the product libraries.
 #include "gl_field.cuh"
+#include "gl_ext5.cuh"
 #include "gl_poseidon2.cuh"
 #include "agl_field.cuh"
 #include "host/gl_transcript.hpp"
@@ -23,6 +24,10 @@ void hc_e2_inv(const uint64_t* a, uint64_t* o) {
     gl::E2 r = gl::e2_inv(gl::E2{a[0], a[1]});
     o[0] = r.c0; o[1] = r.c1;
 }
+void hc_e5_mul(const uint64_t* a, const uint64_t* b, uint64_t* o) { gl::e5_store(o, gl::e5_mul(gl::e5_load(a), gl::e5_load(b))); }
+void hc_e5_inv(const uint64_t* a, uint64_t* o) { gl::e5_store(o, gl::e5_inv(gl::e5_load(a))); }
+void hc_e5_pow(const uint64_t* a, uint64_t e, uint64_t* o) { gl::e5_store(o, gl::e5_pow(gl::e5_load(a), e)); }
+void hc_e5_frobenius(const uint64_t* a, uint64_t* o) { gl::e5_store(o, gl::e5_frobenius<1>(gl::e5_load(a))); }
 uint64_t hc_gl_mul_add(uint64_t a, uint64_t b, uint64_t c) { return gl::mul_add(a, b, c); }
 uint64_t hc_gl_reduce_limb_sums(uint64_t L, uint64_t H) { return gl::reduce_limb_sums(L, H); }
 uint64_t hc_gl_reduce_limbs(uint32_t z0, uint32_t z1, uint32_t z2, uint32_t z3) { return gl::reduce_limbs(z0, z1, z2, z3); }

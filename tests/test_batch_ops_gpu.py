@@ -193,3 +193,52 @@ def test_streams_copies_and_pool():
     assert lib.agl_cached_bytes() >= 0
     assert lib.cuda_pool_trim(0) == 0
     assert b"no error" in lib.agl_cuda_error_string(0)
+
+
+def test_ext5_ops():
+    """Degree-5 extension of Goldilocks (five words per element): products, inverses, powers and the
+    Frobenius map against the CPU oracle; coefficient-wise operations against Python integers."""
+    from oracle import pyoracle
+    lib, p, n = load_gl(), GL_P, 300
+    a, b = _inputs(11, 5 * n, p), _inputs(12, 5 * n, p)
+    a[10:15] = 0            # a zero element
+    a[15:20] = p            # zero as a non-canonical representative
+    a[20:25] = [9, 0, 0, 0, 0]
+    da, db, dr = DeviceBuffer.from_numpy(lib, a), DeviceBuffer.from_numpy(lib, b), DeviceBuffer(lib, 40 * n)
+    A = [[int(x) for x in a[5 * i:5 * i + 5]] for i in range(n)]
+    B = [[int(x) for x in b[5 * i:5 * i + 5]] for i in range(n)]
+    elems = lambda arr: [[int(x) for x in arr[5 * i:5 * i + 5]] for i in range(n)]
+
+    def run(f, *args):
+        assert getattr(lib, f)(*args) == 0
+        lib.cuda_device_synchronize()
+        return elems(dr.to_numpy())
+
+    assert run("ext5_batch_add_ffi", da.ptr, db.ptr, dr.ptr, n) == [[(x + y) % p for x, y in zip(u, v)] for u, v in zip(A, B)]
+    assert run("ext5_batch_sub_ffi", da.ptr, db.ptr, dr.ptr, n) == [[(x - y) % p for x, y in zip(u, v)] for u, v in zip(A, B)]
+    assert run("ext5_batch_neg_ffi", da.ptr, dr.ptr, n) == [[(-x) % p for x in u] for u in A]
+    for s in (0, 3, p - 1, 2**64 - 1):
+        assert run("ext5_batch_mul_scalar_ffi", s, da.ptr, dr.ptr, n) == [[(s * x) % p for x in u] for u in A]
+    assert run("ext5_batch_mul_ffi", da.ptr, db.ptr, dr.ptr, n) == [pyoracle.e5_op("mul", u, v) for u, v in zip(A, B)]
+    assert run("ext5_batch_square_ffi", da.ptr, dr.ptr, n) == [pyoracle.e5_op("mul", u, u) for u in A]
+    assert run("ext5_batch_frobenius_ffi", da.ptr, dr.ptr, n) == [pyoracle.e5_op("frobenius", u) for u in A]
+    inv = run("ext5_batch_inverse_ffi", da.ptr, dr.ptr, n)
+    assert inv == [pyoracle.e5_op("inv", u) for u in A]
+    assert inv[2] == inv[3] == [0] * 5 and inv[4] == [pow(9, p - 2, p), 0, 0, 0, 0]
+    for e in (0, 1, 5, 2**40 + 3, 2**64 - 1):
+        assert run("ext5_batch_exp_ffi", da.ptr, e, dr.ptr, n) == [pyoracle.e5_op("pow", u, e=e) for u in A]
+    # in place: result over the first operand
+    dc = DeviceBuffer.from_numpy(lib, a)
+    assert lib.ext5_batch_mul_ffi(dc.ptr, db.ptr, dc.ptr, n) == 0
+    lib.cuda_device_synchronize()
+    assert elems(dc.to_numpy()) == [pyoracle.e5_op("mul", u, v) for u, v in zip(A, B)]
+    # lift and projection
+    assert run("gl_to_ext5_batch_ffi", da.ptr, dr.ptr, n) == [[int(a[i]) % p, 0, 0, 0, 0] for i in range(n)]
+    d1 = DeviceBuffer(lib, 8 * n)
+    assert lib.ext5_to_gl_batch_ffi(da.ptr, d1.ptr, n) == 0
+    lib.cuda_device_synchronize()
+    assert [int(x) for x in d1.to_numpy()] == [u[0] % p for u in A]
+    # empty batch and bad arguments
+    assert lib.ext5_batch_mul_ffi(da.ptr, db.ptr, dr.ptr, 0) == 0
+    assert lib.ext5_batch_mul_ffi(da.ptr, None, dr.ptr, 4) != 0
+    assert lib.ext5_batch_inverse_ffi(da.ptr, dr.ptr, -1) != 0

@@ -202,3 +202,54 @@ def test_almost_goldilocks_extension_lazy_forms(hostcheck):
         assert (O[0], O[1]) == ((a[0] + r[0] * d[0] + 3 * r[1] * d[1]) % Q, (a[1] + r[0] * d[1] + r[1] * d[0]) % Q)
         hc.hc_aext2_fma_pre_base(R, d[0], a[0], O)
         assert (O[0], O[1]) == ((a[0] + r[0] * d[0]) % Q, (r[1] * d[0]) % Q)
+
+
+def _e5_mul_int(a, b):
+    """Schoolbook product in F_p[X]/(X^5 - 3) with Python integers."""
+    t = [0] * 9
+    for i in range(5):
+        for j in range(5):
+            t[i + j] += a[i] * b[j]
+    return [(t[k] + (3 * t[k + 5] if k < 4 else 0)) % P for k in range(5)]
+
+
+def _e5_pow_int(a, e):
+    r, b = [1, 0, 0, 0, 0], [x % P for x in a]
+    while e:
+        if e & 1:
+            r = _e5_mul_int(r, b)
+        b = _e5_mul_int(b, b)
+        e >>= 1
+    return r
+
+
+def test_ext5_oracle_and_host_forms(hostcheck, oracle):
+    """Degree-5 extension: the oracle against Python integers (the Frobenius map is x -> x^p, the
+    inverse multiplies back to one), and the library's lazy-sum forms against the oracle."""
+    from oracle import pyoracle
+    rnd = random.Random(21)
+    edge = [0, 1, P - 1, P, 2**64 - 1]
+    u5 = u64 * 5
+    elems = [[rnd.choice(edge) for _ in range(5)] for _ in range(20)] + [[rnd.randrange(2**64) for _ in range(5)] for _ in range(200)]
+    for k, a in enumerate(elems):
+        b = elems[(k * 7 + 3) % len(elems)]
+        want = _e5_mul_int(a, b)
+        assert pyoracle.e5_op("mul", a, b) == want
+        O = u5()
+        hostcheck.hc_e5_mul(u5(*a), u5(*b), O)
+        assert list(O) == want
+        hostcheck.hc_e5_frobenius(u5(*a), O)
+        assert list(O) == pyoracle.e5_op("frobenius", a)
+    for a in elems[:4] + elems[20:26]:
+        assert pyoracle.e5_op("frobenius", a) == _e5_pow_int(a, P)
+    for a in elems[:30] + [[0] * 5, [P] * 5, [5, 0, 0, 0, 0]]:
+        inv = pyoracle.e5_op("inv", a)
+        O = u5()
+        hostcheck.hc_e5_inv(u5(*a), O)
+        assert list(O) == inv
+        assert _e5_mul_int(a, inv) == ([1, 0, 0, 0, 0] if any(x % P for x in a) else [0] * 5)
+        for e in (0, 1, 2, 5, 2**40 + 3, 2**64 - 1):
+            want = _e5_pow_int(a, e)
+            assert pyoracle.e5_op("pow", a, e=e) == want
+            hostcheck.hc_e5_pow(u5(*a), u64(e), O)
+            assert list(O) == want
