@@ -357,6 +357,25 @@ int agl_transcript_challenge_scalar(void* transcript, const uint8_t* label, size
 int agl_transcript_challenge_vector(void* transcript, const uint8_t* label, size_t label_len, uint64_t* out, size_t n);
 int agl_transcript_state(const void* transcript, uint64_t* out12);
 
+/* ---- host layer: the whole linear sumcheck (the reference keeps these loops in Rust) ----
+ * GpuLinearSumcheckProver::new + prove / prove_ext2 / prove_gpu_resident
+ * (zk-torch-4/src/sumcheck/gpu_prover.rs:26-112), interoperable with CpuLinearSumcheckProverExt2
+ * (zk-torch-4/src/sumcheck/cpu_ext2_prover.rs:21-100). d tables of 2^num_var elements, poly-major;
+ * base_field != 0: one word per element, else (c0, c1). `transcript` is a handle from
+ * agl_transcript_create and is advanced by the proof (append num_var, num_poly; per round the d+1
+ * values under "round_message", then challenge_ext2("challenge")). Host outputs:
+ * round_msgs[num_var][d+1][2], challenges[num_var][2] (may be NULL), final_evals[d][2] (may be
+ * NULL), final_eval[2] = product of the final evaluations (SumcheckProof, sumcheck/mod.rs:32-36). */
+int agl_sumcheck_prove_device_ffi(const uint64_t* d_tables, int d, int num_var, int base_field, void* transcript,
+                                  uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_evals,
+                                  uint64_t* final_eval);
+int agl_sumcheck_prove_host_ffi(const uint64_t* h_tables, int d, int num_var, int base_field, void* transcript,
+                                uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_evals, uint64_t* final_eval);
+/* SumcheckVerifier::verify (zk-torch-4/src/sumcheck/verifier.rs:14-113), on the host: *ok = 1 when the
+ * proof is accepted against claimed_sum[2]; challenges[num_var][2] may be NULL. */
+int agl_sumcheck_verify_ffi(const uint64_t* round_msgs, const uint64_t* final_eval, const uint64_t* claimed_sum, int d,
+                            int num_var, void* transcript, uint64_t* challenges, int* ok);
+
 /* ---- additions shared with the Goldilocks library ---- */
 /* d_out[i] = splitmix64(seed) output i + 1 mod modulus: seeded synthetic inputs made on the device */
 int mb_fill_splitmix(uint64_t* d_out, size_t n, uint64_t seed, uint64_t modulus);

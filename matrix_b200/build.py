@@ -51,6 +51,7 @@ LIBRARIES = {
         "agl_batched.cu",
         "agl_ajtai_fold.cu",
         "host/agl_transcript.cu",
+        "host/agl_sumcheck_prover.cu",
     ],
 }
 

@@ -11,7 +11,7 @@ struct AglAdd {
     __device__ __forceinline__ uint64_t operator()(uint64_t a, uint64_t b) const { return agl::add(a, b); }
 };
 struct AglCanon {
-    __device__ __forceinline__ uint64_t operator()(uint64_t a) const { return agl::canon(a); }
+    __host__ __device__ __forceinline__ uint64_t operator()(uint64_t a) const { return agl::canon(a); }
 };
 
 struct AglBase {

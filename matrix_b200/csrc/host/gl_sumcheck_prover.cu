@@ -1,20 +1,15 @@
-// Host layer above the C-ABI for the Goldilocks sumcheck: the state object and
-// the prover loop the reference keeps in Rust, written in C++ because no Rust
-// toolchain exists on the build machine.
+// Host layer above the C-ABI for the Goldilocks sumcheck: the prover loop the
+// reference keeps in Rust, written in C++ because no Rust toolchain exists on
+// the build machine.
 //
 //   GpuSumcheckStateExt2      goldilocks-cuda-rs/src/sumcheck_prover.rs:206-436
+//                             (linear_sumcheck_state.cuh, shared with almost-Goldilocks)
 //   GpuLinearSumcheckProver   zk-torch-3/src/sumcheck/gpu_prover.rs:13-150
 //
-// Method names and protocol order follow the reference. Two things differ in
-// how the work is done, not in what comes out:
-//  * base-field tables are not widened on upload; round 0 runs on the 8-byte
-//    tables and the first fold lifts them with the extension challenge;
-//  * fold(r) also accumulates the next round's message in the same pass, and
-//    the block partials are summed on the device, so compute_round_message()
-//    after a fold only reads (d+1) extension elements back.
+// Method names and protocol order follow the reference.
 #include <vector>
 #include <memory>
-#include "../gl_sumcheck_launch.cuh"
+#include "linear_sumcheck_state.cuh"
 #include "gl_transcript.hpp"
 
 using namespace mb;
@@ -22,151 +17,7 @@ using namespace mb::sc;
 
 namespace mbhost {
 
-class GpuSumcheckStateExt2 {
-public:
-    ~GpuSumcheckStateExt2() { release(); }
-
-    // d tables of 2^num_vars elements, poly-major, already on the device
-    // (base field: u64 each; extension: (c0, c1) each). The tables are read in
-    // place and never written.
-    int init_device(const uint64_t* d_tables, int d, int num_vars, bool base_field) {
-        if (d < 1 || d > MAX_D || num_vars < 0 || num_vars > 40 || !d_tables) return MB_ERR_ARG;
-        d_ = d;
-        num_vars_ = num_vars;
-        n_ = (size_t)1 << num_vars;
-        base_ = base_field;
-        src_ = d_tables;
-        round_ = 0;
-        cur_ = nullptr;
-        size_t cap_a = n_ >= 2 ? n_ / 2 : 1, cap_b = n_ >= 4 ? n_ / 4 : 1;
-        stride_a_ = cap_a;
-        stride_b_ = cap_b;
-        MB_CUDA(pool_alloc((void**)&buf_a_, sizeof(uint64_t) * 2 * cap_a * d));
-        MB_CUDA(pool_alloc((void**)&buf_b_, sizeof(uint64_t) * 2 * cap_b * d));
-        max_blocks_ = prover_grid(n_ / 2 > 0 ? n_ / 2 : 1);
-        MB_CUDA(pool_alloc((void**)&partial_, sizeof(uint64_t) * 2 * (d + 1) * (size_t)max_blocks_));
-        MB_CUDA(pool_alloc((void**)&msg_dev_, sizeof(uint64_t) * 2 * (MAX_D + 1)));
-        MB_CUDA(pool_alloc((void**)&counter_, sizeof(unsigned int)));
-        MB_CUDA(cudaMemsetAsync(counter_, 0, sizeof(unsigned int), MB_STREAM));
-        msg_host_ = pinned_scratch();
-        if (!msg_host_) return MB_ERR_CUDA;
-        have_msg_ = false;
-        return MB_OK;
-    }
-
-    // Evaluations P(0..d) of the current round polynomial, canonical.
-    int compute_round_message(std::vector<Ext2>& out) {
-        if (round_ >= num_vars_) return MB_ERR_ARG;
-        size_t live = n_ >> round_, half = live / 2;
-        if (!have_msg_) {
-            // Only round 0 gets here: every fold leaves the next message behind.
-            int grid = prover_grid(half);
-            int rc;
-            if (base_) {
-                rc = launch_round_message<GlBase>(src_, partial_, d_, n_, half, grid, MB_STREAM, counter_, msg_dev_);
-            } else {
-                rc = launch_round_message<GlExt2>(src_, partial_, d_, n_, half, grid, MB_STREAM, counter_, msg_dev_);
-            }
-            if (rc != MB_OK) return rc;
-            msg_words_ = base_ ? 1 : 2;
-        }
-        MB_CUDA(cudaMemcpyAsync(msg_host_, msg_dev_, sizeof(uint64_t) * msg_words_ * (d_ + 1),
-                                cudaMemcpyDeviceToHost, MB_STREAM));
-        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
-        out.resize(d_ + 1);
-        for (int c = 0; c <= d_; c++) {
-            if (msg_words_ == 1) {
-                out[c].c0 = msg_host_[c];
-                out[c].c1 = 0;
-            } else {
-                out[c].c0 = msg_host_[2 * c];
-                out[c].c1 = msg_host_[2 * c + 1];
-            }
-        }
-        return MB_OK;
-    }
-
-    // Fold every table on `challenge`; leaves the next round's message ready.
-    int fold(Ext2 challenge) {
-        if (round_ >= num_vars_) return MB_ERR_ARG;
-        size_t live = n_ >> round_, half = live / 2, quarter = live / 4;
-        gl::E2 r{gl::canon(challenge.c0), gl::canon(challenge.c1)};
-        const uint64_t* in = round_ == 0 ? src_ : cur_;
-        size_t stride_in = round_ == 0 ? n_ : cur_stride_;
-        bool to_a = (round_ == 0) || (cur_ == buf_b_);
-        uint64_t* out = to_a ? buf_a_ : buf_b_;
-        size_t stride_out = to_a ? stride_a_ : stride_b_;
-        bool in_base = base_ && round_ == 0;
-        int rc;
-        if (quarter >= 1) {
-            int grid = prover_grid(quarter);
-            if (in_base) {
-                rc = launch_fold_message<GlBase, GlExt2>(in, out, r, nullptr, d_, stride_in, stride_out, quarter,
-                                                         partial_, grid, MB_STREAM, counter_, msg_dev_);
-            } else {
-                rc = launch_fold_message<GlExt2, GlExt2>(in, out, r, nullptr, d_, stride_in, stride_out, quarter,
-                                                         partial_, grid, MB_STREAM, counter_, msg_dev_);
-            }
-            have_msg_ = true;
-            msg_words_ = 2;
-        } else {
-            if (in_base) {
-                rc = launch_fold_lift<GlBase, GlExt2>(in, out, r, nullptr, d_, stride_in, stride_out, half, MB_STREAM);
-            } else {
-                rc = launch_fold_lift<GlExt2, GlExt2>(in, out, r, nullptr, d_, stride_in, stride_out, half, MB_STREAM);
-            }
-            have_msg_ = false;
-        }
-        if (rc != MB_OK) return rc;
-        cur_ = out;
-        cur_stride_ = stride_out;
-        round_++;
-        return MB_OK;
-    }
-
-    // One value per table once every variable is bound.
-    int final_evaluations(std::vector<Ext2>& out) {
-        if (round_ != num_vars_) return MB_ERR_ARG;
-        out.resize(d_);
-        for (int i = 0; i < d_; i++) {
-            uint64_t w[2] = {0, 0};
-            if (num_vars_ == 0) {
-                const uint64_t* p = base_ ? src_ + i : src_ + 2 * (size_t)i;
-                MB_CUDA(cudaMemcpyAsync(w, p, base_ ? 8 : 16, cudaMemcpyDeviceToHost, MB_STREAM));
-            } else {
-                MB_CUDA(cudaMemcpyAsync(w, cur_ + 2 * (size_t)i * cur_stride_, 16, cudaMemcpyDeviceToHost, MB_STREAM));
-            }
-            MB_CUDA(cudaStreamSynchronize(MB_STREAM));
-            out[i].c0 = gl::canon(w[0]);
-            out[i].c1 = gl::canon(w[1]);
-        }
-        return MB_OK;
-    }
-
-    int num_vars() const { return num_vars_; }
-    int num_polys() const { return d_; }
-    int current_round() const { return round_; }
-
-private:
-    void release() {
-        pool_free(buf_a_);
-        pool_free(buf_b_);
-        pool_free(partial_);
-        pool_free(msg_dev_);
-        pool_free(counter_);
-        buf_a_ = buf_b_ = partial_ = msg_dev_ = nullptr;
-        counter_ = nullptr;
-        msg_host_ = nullptr;
-    }
-
-    int d_ = 0, num_vars_ = 0, round_ = 0, max_blocks_ = 0, msg_words_ = 2;
-    size_t n_ = 0, stride_a_ = 0, stride_b_ = 0, cur_stride_ = 0;
-    bool base_ = false, have_msg_ = false;
-    const uint64_t* src_ = nullptr;
-    uint64_t *buf_a_ = nullptr, *buf_b_ = nullptr, *cur_ = nullptr, *partial_ = nullptr, *msg_dev_ = nullptr;
-    unsigned int* counter_ = nullptr;
-    uint64_t* msg_host_ = nullptr;
-};
+using GpuSumcheckStateExt2 = LinearSumcheckState<GlBase, GlExt2>;
 
 static Ext2 ext2_mul_host(Ext2 a, Ext2 b) {
     gl::E2 r = gl::e2_canon(gl::e2_mul(gl::E2{a.c0, a.c1}, gl::E2{b.c0, b.c1}));

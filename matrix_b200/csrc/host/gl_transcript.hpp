@@ -11,12 +11,9 @@
 #include <cstring>
 #include <string>
 #include "../gl_poseidon2.cuh"
+#include "ext2_words.hpp"
 
 namespace mbhost {
-
-struct Ext2 {
-    uint64_t c0 = 0, c1 = 0;
-};
 
 class Transcript {
 public:

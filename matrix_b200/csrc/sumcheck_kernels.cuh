@@ -32,7 +32,7 @@ struct GlAdd {
     __device__ __forceinline__ uint64_t operator()(uint64_t a, uint64_t b) const { return gl::add(a, b); }
 };
 struct GlCanon {
-    __device__ __forceinline__ uint64_t operator()(uint64_t a) const { return gl::canon(a); }
+    __host__ __device__ __forceinline__ uint64_t operator()(uint64_t a) const { return gl::canon(a); }
 };
 
 struct GlBase {

@@ -343,6 +343,9 @@ _AGL_SIGNATURES = {
     "agl_transcript_challenge_scalar": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, ctypes.POINTER(ctypes.c_uint64)]),
     "agl_transcript_challenge_vector": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_void_p, c_size_t]),
     "agl_transcript_state": (c_int, [c_void_p, c_void_p]),
+    "agl_sumcheck_prove_device_ffi": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "agl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "agl_sumcheck_verify_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(c_int)]),
     "agl_fused_permute_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "agl_partial_eval_ffi": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "agl_partial_eval_ext2_from_base_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int]),

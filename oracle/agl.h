@@ -26,4 +26,10 @@ static inline aext2_t ae2_mul(aext2_t a, aext2_t b) {
     uint64_t m0 = agl_mul(a.c0, b.c0), m1 = agl_mul(a.c1, b.c1);
     return ae2(agl_add(m0, agl_mul(3, m1)), agl_add(agl_mul(a.c0, b.c1), agl_mul(a.c1, b.c0)));
 }
+/* 1 / (c0 + c1 X) = (c0 - c1 X) / (c0^2 - 3 c1^2); the inverse of zero is zero */
+static inline aext2_t ae2_inv(aext2_t a) {
+    uint64_t n = agl_sub(agl_mul(a.c0, a.c0), agl_mul(3, agl_mul(a.c1, a.c1)));
+    uint64_t ni = agl_inv(n);
+    return ae2(agl_mul(a.c0, ni), agl_mul(agl_sub(0, a.c1), ni));
+}
 #endif

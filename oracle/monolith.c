@@ -19,6 +19,7 @@
 #include "gl.h"
 #include "agl.h"
 #include <string.h>
+#include <stdlib.h>
 
 #define MW 12
 #define MROUNDS 6
@@ -273,4 +274,128 @@ size_t oracle_agl_transcript_run(const uint8_t *init_label, size_t init_len, siz
     }
     if (state_out) memcpy(state_out, t.sponge, sizeof(t.sponge));
     return n_out;
+}
+
+/* ------------------------------------------------------------------ */
+/* Linear sumcheck over the almost-Goldilocks extension with this       */
+/* transcript (zk-torch-4)                                              */
+/* ------------------------------------------------------------------ */
+static void agl_append_u64(agl_transcript_t *t, const char *label, uint64_t v) { /* transcript.rs:83-88 */
+    agl_absorb_label(t, (const uint8_t *)label, strlen(label));
+    agl_absorb(t, v % AGL_Q);
+}
+static void agl_append_ext2(agl_transcript_t *t, const char *label, aext2_t v) { /* transcript.rs:102-106 */
+    agl_absorb_label(t, (const uint8_t *)label, strlen(label));
+    agl_absorb(t, v.c0 % AGL_Q);
+    agl_absorb(t, v.c1 % AGL_Q);
+}
+static aext2_t agl_challenge_ext2(agl_transcript_t *t, const char *label) { /* transcript.rs:120-125 */
+    agl_absorb_label(t, (const uint8_t *)label, strlen(label));
+    uint64_t c0 = agl_squeeze(t), c1 = agl_squeeze(t);
+    return ae2(c0, c1);
+}
+static void agl_transcript_init(agl_transcript_t *t, const uint8_t *label, size_t n) { /* transcript.rs:34-47 */
+    memset(t, 0, sizeof(*t));
+    for (size_t i = 0; i < n; i++) agl_absorb(t, label[i]);
+}
+
+/* CpuLinearSumcheckProverExt2::new + prove (zk-torch-4/src/sumcheck/cpu_ext2_prover.rs:23-100),
+ * the loop GpuLinearSumcheckProver runs with the same labels (gpu_prover.rs:26-112).
+ * polys: d tables of 2^num_var extension elements, poly-major, (c0, c1) words (a base-field
+ * table is lifted first: from_base). The transcript starts as Transcript::new(label).
+ * Outputs: round_msgs[num_var][d+1][2], challenges[num_var][2], final_evals[d][2],
+ * final_eval[2], state12 (sponge words after the proof; may be NULL). */
+int oracle_agl_sumcheck_prove(const uint64_t *polys_in, int d, int num_var, int base_field, const uint8_t *label,
+                              size_t label_len, uint64_t *round_msgs, uint64_t *challenges, uint64_t *final_evals,
+                              uint64_t *final_eval, uint64_t *state12) {
+    size_t n = (size_t)1 << num_var;
+    aext2_t *p = malloc(sizeof(aext2_t) * n * (size_t)d);
+    if (!p) return -1;
+    for (size_t i = 0; i < n * (size_t)d; i++)
+        p[i] = base_field ? ae2(polys_in[i] % AGL_Q, 0) : ae2(polys_in[2 * i] % AGL_Q, polys_in[2 * i + 1] % AGL_Q);
+    agl_transcript_t t;
+    agl_transcript_init(&t, label, label_len);
+    agl_append_u64(&t, "num_var", (uint64_t)num_var);
+    agl_append_u64(&t, "num_poly", (uint64_t)d);
+    size_t len = n;
+    for (int round = 0; round < num_var; round++) {
+        size_t half = len / 2;
+        for (int e = 0; e <= d; e++) {
+            aext2_t c = ae2((uint64_t)e, 0), sum = ae2(0, 0);
+            for (size_t j = 0; j < half; j++) {
+                aext2_t prod = ae2(1, 0);
+                for (int i = 0; i < d; i++) {
+                    aext2_t a = p[(size_t)i * n + 2 * j], b = p[(size_t)i * n + 2 * j + 1];
+                    prod = ae2_mul(prod, ae2_add(a, ae2_mul(c, ae2_sub(b, a))));
+                }
+                sum = ae2_add(sum, prod);
+            }
+            round_msgs[((size_t)round * (d + 1) + e) * 2] = sum.c0;
+            round_msgs[((size_t)round * (d + 1) + e) * 2 + 1] = sum.c1;
+        }
+        for (int e = 0; e <= d; e++) {
+            const uint64_t *w = round_msgs + ((size_t)round * (d + 1) + e) * 2;
+            agl_append_ext2(&t, "round_message", ae2(w[0], w[1]));
+        }
+        aext2_t r = agl_challenge_ext2(&t, "challenge");
+        challenges[2 * round] = r.c0;
+        challenges[2 * round + 1] = r.c1;
+        r = ae2(r.c0 % AGL_Q, r.c1 % AGL_Q);
+        for (int i = 0; i < d; i++)
+            for (size_t j = 0; j < half; j++) {
+                aext2_t a = p[(size_t)i * n + 2 * j], b = p[(size_t)i * n + 2 * j + 1];
+                p[(size_t)i * n + j] = ae2_add(a, ae2_mul(r, ae2_sub(b, a)));
+            }
+        len = half;
+    }
+    aext2_t prod = ae2(1, 0);
+    for (int i = 0; i < d; i++) {
+        final_evals[2 * i] = p[(size_t)i * n].c0;
+        final_evals[2 * i + 1] = p[(size_t)i * n].c1;
+        prod = ae2_mul(prod, p[(size_t)i * n]);
+    }
+    final_eval[0] = prod.c0;
+    final_eval[1] = prod.c1;
+    if (state12) memcpy(state12, t.sponge, sizeof(t.sponge));
+    free(p);
+    return 0;
+}
+
+/* verifier.rs:91-113 */
+static aext2_t agl_interpolate(const aext2_t *evals, int n, aext2_t x) {
+    aext2_t result = ae2(0, 0);
+    for (int i = 0; i < n; i++) {
+        aext2_t basis = ae2(1, 0);
+        for (int j = 0; j < n; j++) {
+            if (j == i) continue;
+            aext2_t num = ae2_sub(x, ae2((uint64_t)j, 0)), den = ae2_sub(ae2((uint64_t)i, 0), ae2((uint64_t)j, 0));
+            basis = ae2_mul(basis, ae2_mul(num, ae2_inv(den)));
+        }
+        result = ae2_add(result, ae2_mul(basis, evals[i]));
+    }
+    return result;
+}
+/* SumcheckVerifier::verify (verifier.rs:14-88): 1 = accepted; challenges written as far as checked. */
+int oracle_agl_sumcheck_verify(const uint64_t *round_msgs, const uint64_t *final_eval, const uint64_t *claimed_sum, int d,
+                               int num_var, const uint8_t *label, size_t label_len, uint64_t *challenges) {
+    agl_transcript_t t;
+    agl_transcript_init(&t, label, label_len);
+    agl_append_u64(&t, "num_var", (uint64_t)num_var);
+    agl_append_u64(&t, "num_poly", (uint64_t)d);
+    aext2_t current = ae2(claimed_sum[0] % AGL_Q, claimed_sum[1] % AGL_Q);
+    for (int round = 0; round < num_var; round++) {
+        aext2_t msg[16];
+        for (int e = 0; e <= d; e++) {
+            const uint64_t *w = round_msgs + ((size_t)round * (d + 1) + e) * 2;
+            msg[e] = ae2(w[0] % AGL_Q, w[1] % AGL_Q);
+        }
+        aext2_t s = ae2_add(msg[0], msg[1]);
+        if (s.c0 != current.c0 || s.c1 != current.c1) return 0;
+        for (int e = 0; e <= d; e++) agl_append_ext2(&t, "round_message", msg[e]);
+        aext2_t r = agl_challenge_ext2(&t, "challenge");
+        challenges[2 * round] = r.c0;
+        challenges[2 * round + 1] = r.c1;
+        current = agl_interpolate(msg, d + 1, ae2(r.c0 % AGL_Q, r.c1 % AGL_Q));
+    }
+    return current.c0 == final_eval[0] % AGL_Q && current.c1 == final_eval[1] % AGL_Q;
 }

@@ -207,6 +207,42 @@ _SIGS.update({
 })
 
 
+_SIGS.update({
+    "oracle_agl_sumcheck_prove": (ci, [vp, ci, ci, ci, ctypes.c_char_p, sz, vp, vp, vp, vp, vp]),
+    "oracle_agl_sumcheck_verify": (ci, [vp, vp, vp, ci, ci, ctypes.c_char_p, sz, vp]),
+})
+
+
+def agl_sumcheck_prove(polys, d, num_var, base_field, label=b"bench"):
+    """zk-torch-4's linear sumcheck prover (Monolith transcript) on a numpy array of d poly-major tables.
+    Returns (round_msgs, challenges, final_evals, final_eval, sponge_state) as numpy arrays."""
+    import numpy as np
+    lib = load()
+    polys = np.ascontiguousarray(polys, dtype=np.uint64)
+    msgs = np.zeros(max(num_var, 1) * (d + 1) * 2, dtype=np.uint64)
+    ch = np.zeros(max(num_var, 1) * 2, dtype=np.uint64)
+    fe = np.zeros(2 * d, dtype=np.uint64)
+    fin = np.zeros(2, dtype=np.uint64)
+    st = np.zeros(12, dtype=np.uint64)
+    rc = lib.oracle_agl_sumcheck_prove(polys.ctypes.data, d, num_var, int(base_field), label, len(label), msgs.ctypes.data,
+                                       ch.ctypes.data, fe.ctypes.data, fin.ctypes.data, st.ctypes.data)
+    assert rc == 0
+    return msgs[:num_var * (d + 1) * 2], ch[:2 * num_var], fe, fin, st
+
+
+def agl_sumcheck_verify(msgs, final_eval, claimed, d, num_var, label=b"bench"):
+    """zk-torch-4's SumcheckVerifier::verify; returns (accepted, challenges)."""
+    import numpy as np
+    lib = load()
+    msgs = np.ascontiguousarray(msgs, dtype=np.uint64)
+    fin = np.ascontiguousarray(final_eval, dtype=np.uint64)
+    cl = np.ascontiguousarray(claimed, dtype=np.uint64)
+    ch = np.zeros(max(num_var, 1) * 2, dtype=np.uint64)
+    ok = lib.oracle_agl_sumcheck_verify(msgs.ctypes.data, fin.ctypes.data, cl.ctypes.data, d, num_var, label, len(label),
+                                        ch.ctypes.data)
+    return bool(ok), ch[:2 * num_var]
+
+
 def e5_op(name, a, b=None, e=None):
     """One Ext5 operation of the oracle on lists of five words: name in mul / frobenius / inv / pow."""
     lib = load()
