@@ -21,8 +21,13 @@ extern "C" {
 
 /* ---- init, memory, device: ffi.rs:77-100 (wrapper.cu:111-116, 205-330) ---- */
 int almost_goldilocks_cuda_init(void);
+/* Freed blocks are cached per device and reused (best fit, at most 25 % + 2 MiB larger; released and retried
+ * when the driver is out of memory; AGL_ALLOC_CACHE=0 disables): almost-goldilocks-cuda-rs/cuda/wrapper.cu:118-235 */
 int cuda_malloc(void** ptr, size_t size);
 int cuda_free(void* ptr);
+/* additions: release the current device's cached blocks; bytes they hold */
+int mb_alloc_cache_flush(void);
+size_t mb_alloc_cache_bytes(void);
 int cuda_memcpy_htod(void* dst, const void* src, size_t size);
 int cuda_memcpy_dtoh(void* dst, const void* src, size_t size);
 int cuda_memcpy_dtod(void* dst, const void* src, size_t size);

@@ -79,8 +79,10 @@ int cuda_enable_peer_access(int peer) {
     if (err != cudaSuccess) { cudaGetLastError(); return MB_ERR_CUDA; }
     return MB_OK;
 }
-// Hands memory cached by the stream-ordered pool back to the driver.
+// Hands memory cached by the stream-ordered pool and by cuda_malloc's block cache back to the driver.
+int mb_alloc_cache_flush();
 int cuda_pool_trim(size_t min_bytes_to_keep) {
+    mb_alloc_cache_flush();
     int dev = 0;
     cudaMemPool_t pool;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetDefaultMemPool(&pool, dev) != cudaSuccess) return MB_ERR_CUDA;

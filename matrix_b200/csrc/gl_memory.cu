@@ -8,6 +8,154 @@
 #include "common.cuh"
 #include <cstring>
 
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace mb {
+
+class AllocCache {
+public:
+    static constexpr int MAX_DEV = 64;
+    AllocCache() {
+        const char* e = std::getenv("AGL_ALLOC_CACHE");
+        on_ = !(e && e[0] == '0' && e[1] == 0);
+    }
+    int allocate(void** out, size_t size) {
+        int dev = 0;
+        if (!on_ || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV)
+            return cudaMalloc(out, size) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+        const size_t want = ((size ? size : 1) + 511) & ~(size_t)511;
+        Block hit{};
+        bool found = false;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            auto& fl = free_[dev];
+            auto it = fl.lower_bound(want);
+            if (it != fl.end() && it->first <= want + want / 4 + ((size_t)2 << 20)) {
+                hit = it->second;
+                fl.erase(it);
+                cached_[dev] -= hit.size;
+                found = true;
+            }
+        }
+        if (found) {
+            // the previous owner's work on the block must be over before anyone touches it again
+            if (cudaEventQuery(hit.ev) != cudaSuccess) {
+                cudaGetLastError();
+                cudaEventSynchronize(hit.ev);
+            }
+            std::lock_guard<std::mutex> lk(mu_);
+            events_[dev].push_back(hit.ev);
+            live_[hit.p] = Live{dev, hit.size};
+            *out = hit.p;
+            return MB_OK;
+        }
+        void* p = nullptr;
+        if (cudaMalloc(&p, want) != cudaSuccess) {
+            cudaGetLastError();  // clear the error, release what the cache holds, try once more
+            flush(dev);
+            if (cudaMalloc(&p, want) != cudaSuccess) {
+                cudaGetLastError();
+                return MB_ERR_CUDA;
+            }
+        }
+        std::lock_guard<std::mutex> lk(mu_);
+        live_[p] = Live{dev, want};
+        *out = p;
+        return MB_OK;
+    }
+    int release(void* p) {
+        if (!p) return MB_OK;
+        Live info{};
+        cudaEvent_t ev = nullptr;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            auto it = live_.find(p);
+            if (!on_ || it == live_.end())  // not handed out by this cache
+                return cudaFree(p) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+            info = it->second;
+            live_.erase(it);
+            auto& pool = events_[info.dev];
+            if (!pool.empty()) {
+                ev = pool.back();
+                pool.pop_back();
+            }
+        }
+        int cur = info.dev;
+        cudaGetDevice(&cur);
+        // The event has to be recorded on the block's device; a buffer dropped while another device is
+        // current (or when no event can be had) goes straight back to the driver.
+        if (cur != info.dev || (!ev && cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess)) {
+            if (ev) {
+                std::lock_guard<std::mutex> lk(mu_);
+                events_[info.dev].push_back(ev);
+            }
+            return cudaFree(p) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+        }
+        cudaEventRecord(ev, MB_STREAM);
+        std::lock_guard<std::mutex> lk(mu_);
+        free_[info.dev].emplace(info.size, Block{p, info.size, ev});
+        cached_[info.dev] += info.size;
+        return MB_OK;
+    }
+    int flush_current() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return MB_ERR_CUDA;
+        flush(dev);
+        return MB_OK;
+    }
+    size_t cached_bytes_current() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 0;
+        std::lock_guard<std::mutex> lk(mu_);
+        return cached_[dev];
+    }
+
+private:
+    struct Block {
+        void* p;
+        size_t size;
+        cudaEvent_t ev;
+    };
+    struct Live {
+        int dev;
+        size_t size;
+    };
+    // Called with `dev` current (allocate) or made current by the caller (flush_current).
+    void flush(int dev) {
+        std::vector<Block> drop;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            for (auto& kv : free_[dev]) drop.push_back(kv.second);
+            free_[dev].clear();
+            cached_[dev] = 0;
+        }
+        for (auto& b : drop) {
+            cudaEventSynchronize(b.ev);
+            cudaFree(b.p);
+            std::lock_guard<std::mutex> lk(mu_);
+            events_[dev].push_back(b.ev);
+        }
+    }
+    bool on_ = true;
+    std::mutex mu_;
+    std::multimap<size_t, Block> free_[MAX_DEV];
+    std::vector<cudaEvent_t> events_[MAX_DEV];
+    size_t cached_[MAX_DEV] = {};
+    std::unordered_map<void*, Live> live_;
+};
+
+// One cache per library image, never destroyed (buffers may be dropped during process exit).
+inline AllocCache& alloc_cache() {
+    static AllocCache* c = new AllocCache();
+    return *c;
+}
+
+}  // namespace mb
+
 namespace {
 // out[i] = splitmix64 output number i + 1 started at `seed`, reduced mod `modulus`
 // (the generator of matrix_b200/inputs.py, so device-made inputs equal host-made ones).
@@ -52,11 +200,23 @@ int monolith_cuda_init() {
     return (cudaGetDeviceCount(&n) == cudaSuccess && n > 0) ? MB_OK : MB_ERR_CUDA;
 }
 
+// cuda_malloc / cuda_free keep freed blocks for reuse, the role of the caching allocator in
+// almost-goldilocks-cuda-rs/cuda/wrapper.cu:118-235: the Rust callers create and drop a DeviceBuffer around
+// almost every call, and cudaMalloc / cudaFree serialise on a driver lock (cudaFree also waits for the
+// device). Same contract: a request takes the smallest cached block of its device that fits and is at most
+// 25 % + 2 MiB larger; when the driver is out of memory the device's cache is released and the request
+// retried; AGL_ALLOC_CACHE=0 restores plain cudaMalloc / cudaFree. A freed block remembers an event
+// recorded on the freeing thread's stream; it is handed out again only once that event has completed
+// (checked without blocking first; the wait is rare because entry points return after their work is done).
 int cuda_malloc(void** ptr, size_t size) {
     if (!ptr) return MB_ERR_ARG;
-    return cudaMalloc(ptr, size) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+    return mb::alloc_cache().allocate(ptr, size);
 }
-int cuda_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? MB_OK : MB_ERR_CUDA; }
+int cuda_free(void* ptr) { return mb::alloc_cache().release(ptr); }
+// Gives the current device's cached blocks back to the driver (cuda_pool_trim does this too).
+int mb_alloc_cache_flush() { return mb::alloc_cache().flush_current(); }
+// Bytes held in cached (free) blocks of the current device.
+size_t mb_alloc_cache_bytes() { return mb::alloc_cache().cached_bytes_current(); }
 
 static int copy_sync(void* dst, const void* src, size_t size, cudaMemcpyKind kind) {
     if (size == 0) return MB_OK;

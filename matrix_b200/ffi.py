@@ -34,6 +34,8 @@ _GL_SIGNATURES = {
     "monolith_cuda_init": (c_int, []),
     "cuda_malloc": (c_int, [ctypes.POINTER(c_void_p), c_size_t]),
     "cuda_free": (c_int, [c_void_p]),
+    "mb_alloc_cache_flush": (c_int, []),
+    "mb_alloc_cache_bytes": (c_size_t, []),
     "cuda_memcpy_htod": (c_int, [c_void_p, c_void_p, c_size_t]),
     "cuda_memcpy_dtoh": (c_int, [c_void_p, c_void_p, c_size_t]),
     "cuda_memcpy_dtod": (c_int, [c_void_p, c_void_p, c_size_t]),
@@ -201,7 +203,7 @@ def load_gl():
 
 
 _AGL = None
-_MEM = ["cuda_malloc", "cuda_free", "cuda_memcpy_htod", "cuda_memcpy_dtoh", "cuda_memcpy_dtod", "cuda_device_synchronize",
+_MEM = ["cuda_malloc", "cuda_free", "mb_alloc_cache_flush", "mb_alloc_cache_bytes", "cuda_memcpy_htod", "cuda_memcpy_dtoh", "cuda_memcpy_dtod", "cuda_device_synchronize",
         "cuda_get_last_error", "cuda_peek_at_last_error", "cuda_mem_get_info", "cuda_set_device", "cuda_get_device",
         "cuda_get_device_count", "mb_event_create", "mb_event_record", "mb_event_sync", "mb_event_elapsed_ms",
         "mb_event_destroy", "mb_stream_sync", "mb_launch_count", "mb_fill_splitmix"]
