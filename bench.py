@@ -700,6 +700,64 @@ def run_llama_layer(args):
     print(json.dumps(line))
 
 
+def run_peval(args):
+    """Table preparation kernels of the sumcheck callers on one GPU, almost-Goldilocks: partial evaluation of the 12
+    low variables of a 2^n base-field table (extension challenges), the fused bit-permutation + partial evaluation
+    with the 12 high variables fixed, and the eq table of n variables. Event-timed per call; the partial evaluation
+    is the headline of the line."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    from matrix_b200 import load_agl
+    from matrix_b200.ffi import DeviceBuffer
+    from matrix_b200.inputs import AGL_Q, field_elems
+    from matrix_b200.layer_trace import split_luts
+    lib = load_agl()
+    assert lib.cuda_set_device(local) == 0
+    peak, peak_kind = measured_peaks()
+    log_n, m = (args.num_vars if args.num_vars != 24 else 26), 12
+    n = 1 << log_n
+    src = DeviceBuffer(lib, 8 * n)
+    assert lib.mb_fill_splitmix(src.ptr, n, 1, AGL_Q) == 0
+    out, o2 = DeviceBuffer(lib, 16 * (n >> 1)), DeviceBuffer(lib, 16 * (n >> m))
+    r = DeviceBuffer.from_numpy(lib, field_elems(3, 2 * log_n, AGL_Q))
+    order = list(range(log_n - m, log_n)) + list(range(log_n - m))
+    lo, hi = split_luts(log_n, order, log_n // 2)
+    dlo, dhi = DeviceBuffer.from_numpy(lib, lo), DeviceBuffer.from_numpy(lib, hi)
+    eq_a, eq_b, res = DeviceBuffer(lib, 16 * n), DeviceBuffer(lib, 16 * n), ctypes.c_void_p()
+    eq_m = DeviceBuffer.from_numpy(lib, field_elems(4, 2 << m, AGL_Q))
+    timed = _event_timer(lib)
+    calls = {"partial_eval": lambda: lib.agl_partial_eval_ext2_from_base_ffi(src.ptr, out.ptr, r.ptr, log_n, m),
+             "fused_permute_partial_eval": lambda: lib.agl_fused_permute_partial_eval_ffi(
+                 src.ptr, o2.ptr, eq_m.ptr, dlo.ptr, dhi.ptr, log_n, m, log_n // 2, n >> m, 0),
+             "eq_table": lambda: lib.aext2_eq_dp_all_ffi(r.ptr, eq_a.ptr, eq_b.ptr, log_n, ctypes.byref(res))}
+    for fn in calls.values():
+        for _ in range(max(args.warmup, 3)):
+            assert fn() == 0
+    sampler = ClockSampler(local)
+    launches0 = lib.mb_launch_count()
+    sampler.start()
+    ms = {k: timed(fn, args.steps) / args.steps for k, fn in calls.items()}
+    launches = lib.mb_launch_count() - launches0
+    t_end = time.perf_counter() + 2.0
+    while not sampler.lines and time.perf_counter() < t_end:
+        calls["partial_eval"]()
+    clocks = sampler.stop()
+    alg = 8.0 * n + 16.0 * (n >> m)
+    ach = alg / (ms["partial_eval"] * 1e-3) / 1e9
+    line = {"metric": "field-elems/s: partial evaluation of %d variables of a 2^%d base-field table, almost-Goldilocks" % (m, log_n),
+            "value": n / (ms["partial_eval"] * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms["partial_eval"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
+            "data": "synthetic", "config": {"workload": "peval n=%d m=%d" % (log_n, m), "l2": "table of %d MB, larger than L2" % (8 * n >> 20)},
+            "ms_per_call": ms,
+            "gbs": {"partial_eval": ach, "fused_permute_partial_eval": alg / (ms["fused_permute_partial_eval"] * 1e-3) / 1e9,
+                    "eq_table": 16.0 * n / (ms["eq_table"] * 1e-3) / 1e9},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "peak_kind": peak_kind, "note": "whole call (three passes, the first reads the table once: 8 B per element)"}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -709,7 +767,7 @@ def main():
     ap.add_argument("--num-vars", type=int, default=24)
     ap.add_argument("--ref-num-vars", type=int, default=20, help="sample size of the CPU arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit", "link", "llama_layer"],
+    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit", "link", "llama_layer", "peval"],
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
@@ -734,6 +792,9 @@ def main():
         return
     if args.workload == "llama_layer":
         run_llama_layer(args)
+        return
+    if args.workload == "peval":
+        run_peval(args)
         return
 
     if args.impl == "reference":

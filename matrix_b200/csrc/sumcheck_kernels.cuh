@@ -54,6 +54,7 @@ struct GlBase {
     static __device__ __forceinline__ T mul(T a, T b) { return gl::mul(a, b); }
     static __device__ __forceinline__ T zero() { return 0; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v; }
+    static __device__ __forceinline__ T from_words(const uint64_t* w) { return w[0]; }
 };
 
 struct GlExt2 {
@@ -78,6 +79,9 @@ struct GlExt2 {
     static __device__ __forceinline__ T mul(T a, T b) { return gl::e2_mul_lazy(a, b); }
     static __device__ __forceinline__ T zero() { return gl::E2{0, 0}; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
+    static __device__ __forceinline__ T from_words(const uint64_t* w) { return T{w[0], w[1]}; }
+    // an exact sum of at most 64 products of 64-bit words, reduced to a loose residue
+    static __device__ __forceinline__ uint64_t reduce_acc(const gl::Acc& s) { return gl::acc_reduce(s); }
 };
 
 // ---- block-wide sum of NV residues per thread -------------------------------

@@ -217,3 +217,40 @@ def test_fused_permute_partial_eval_both_fields(lib, oracle, n, m, half):
         else:
             pex(permuted.ctypes.data, exp.ctypes.data, r.ctypes.data, n, m)
         assert np.array_equal(d_o.to_numpy(), exp)
+
+
+def test_fused_permute_partial_eval_tables_of_exactly_48k(lib, oracle):
+    """n = 25, half = 12: the two index tables take exactly 48 KB of dynamic shared memory, which together with
+    the kernel's static shared memory is above the default limit (the launch has to opt in)."""
+    n, m, half = 25, 12, 12
+    order = list(range(n - m, n)) + list(range(n - m))   # the m high variables become the low ones
+    lo, hi = _split_luts(n, order, half)
+    x = np.arange(1 << n, dtype=np.int64)
+    perm = lo[x & ((1 << half) - 1)].astype(np.int64) | hi[x >> half].astype(np.int64)
+    evals = field_elems(925, 1 << n, Q)
+    r = field_elems(926, 2 * m, Q)
+    eq = np.zeros(2 << m, dtype=np.uint64)
+    oracle.oracle_agl_eq_ext2(r.ctypes.data, m, eq.ctypes.data)
+    out_size = 1 << (n - m)
+    d_e, d_q = DeviceBuffer.from_numpy(lib, evals), DeviceBuffer.from_numpy(lib, eq)
+    d_lo, d_hi = DeviceBuffer.from_numpy(lib, lo), DeviceBuffer.from_numpy(lib, hi)
+    d_o = DeviceBuffer(lib, 16 * out_size)
+    assert lib.agl_fused_permute_partial_eval_ffi(d_e.ptr, d_o.ptr, d_q.ptr, d_lo.ptr, d_hi.ptr, n, m, half, out_size, 0) == 0
+    permuted = np.ascontiguousarray(evals[perm])
+    exp = np.zeros(2 * out_size, dtype=np.uint64)
+    oracle.oracle_agl_partial_eval_ext2_from_base(permuted.ctypes.data, exp.ctypes.data, r.ctypes.data, n, m)
+    assert np.array_equal(d_o.to_numpy(), exp)
+    # a few fixed variables on the same table: groups of lanes instead of a block per output
+    for m2 in (1, 3, 6):
+        order2 = list(range(n - m2, n)) + list(range(n - m2))
+        lo2, hi2 = _split_luts(n, order2, half)
+        perm2 = lo2[x & ((1 << half) - 1)].astype(np.int64) | hi2[x >> half].astype(np.int64)
+        oracle.oracle_agl_eq_ext2(r.ctypes.data, m2, eq.ctypes.data)
+        d_q2 = DeviceBuffer.from_numpy(lib, eq[:2 << m2])
+        d_l2, d_h2 = DeviceBuffer.from_numpy(lib, lo2), DeviceBuffer.from_numpy(lib, hi2)
+        d_o2 = DeviceBuffer(lib, 16 << (n - m2))
+        assert lib.agl_fused_permute_partial_eval_ffi(d_e.ptr, d_o2.ptr, d_q2.ptr, d_l2.ptr, d_h2.ptr, n, m2, half, 1 << (n - m2), 0) == 0
+        permuted = np.ascontiguousarray(evals[perm2])
+        exp2 = np.zeros(2 << (n - m2), dtype=np.uint64)
+        oracle.oracle_agl_partial_eval_ext2_from_base(permuted.ctypes.data, exp2.ctypes.data, r.ctypes.data, n, m2)
+        assert np.array_equal(d_o2.to_numpy(), exp2)
