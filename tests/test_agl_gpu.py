@@ -254,3 +254,29 @@ def test_fused_permute_partial_eval_tables_of_exactly_48k(lib, oracle):
         exp2 = np.zeros(2 << (n - m2), dtype=np.uint64)
         oracle.oracle_agl_partial_eval_ext2_from_base(permuted.ctypes.data, exp2.ctypes.data, r.ctypes.data, n, m2)
         assert np.array_equal(d_o2.to_numpy(), exp2)
+
+
+def test_fused_permute_partial_eval_sector_loads_and_unaligned_table(lib, oracle):
+    """Fixed variables moved down, the rest in order: four consecutive outputs read one 32-byte sector. The same
+    call on a table that starts 8 bytes into its allocation must not use 16-byte loads; one and two outputs
+    (no group of four) take the per-output kernels."""
+    for n, m, half in ((12, 5, 6), (14, 9, 7), (9, 2, 4), (6, 5, 3), (5, 5, 2)):
+        order = list(range(n - m, n)) + list(range(n - m))
+        lo, hi = _split_luts(n, order, half)
+        x = np.arange(1 << n, dtype=np.int64)
+        perm = lo[x & ((1 << half) - 1)].astype(np.int64) | hi[x >> half].astype(np.int64)
+        evals = field_elems(930 + n, (1 << n) + 1, Q)
+        r = field_elems(931 + n, 2 * m, Q)
+        eq = np.zeros(2 << m, dtype=np.uint64)
+        oracle.oracle_agl_eq_ext2(r.ctypes.data, m, eq.ctypes.data)
+        out_size = 1 << (n - m)
+        d_e, d_q = DeviceBuffer.from_numpy(lib, evals), DeviceBuffer.from_numpy(lib, eq)
+        d_lo, d_hi = DeviceBuffer.from_numpy(lib, lo), DeviceBuffer.from_numpy(lib, hi)
+        d_o = DeviceBuffer(lib, 16 * out_size)
+        for shift in (0, 1):
+            assert lib.agl_fused_permute_partial_eval_ffi(d_e.ptr + 8 * shift, d_o.ptr, d_q.ptr, d_lo.ptr, d_hi.ptr, n, m, half,
+                                                          out_size, 0) == 0
+            permuted = np.ascontiguousarray(evals[shift:shift + (1 << n)][perm])
+            exp = np.zeros(2 * out_size, dtype=np.uint64)
+            oracle.oracle_agl_partial_eval_ext2_from_base(permuted.ctypes.data, exp.ctypes.data, r.ctypes.data, n, m)
+            assert np.array_equal(d_o.to_numpy(), exp), (n, m, shift)
