@@ -98,21 +98,32 @@ constexpr int TC_PASS_PLANES = TC_MAX_PLANES;   // one MMA covers all planes of 
 
 template <int SRC, int NP>
 int launch_tc_np(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0,
-                 uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks) {
+                 uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks, int chunk_cols) {
     const size_t smem = tc_pipe_smem_bytes(NP);
     if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
     dim3 grid((unsigned)chunks, 3);
-    commit_tc_pipe_kernel<SRC, NP><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize);
+    commit_tc_pipe_kernel<SRC, NP><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize,
+                                                                             chunk_cols);
     return MB_OK;
+}
+// Columns per CTA: the full 512 when that already gives every SM work, otherwise narrower chunks (a multiple
+// of the four columns of an MMA stage) so that a short witness is spread over about two CTAs per SM.
+inline int tc_chunk_cols(uint64_t N) {
+    const uint64_t want_chunks = ((uint64_t)sm_count() * 2 + 2) / 3;
+    uint64_t cols = (N + want_chunks - 1) / want_chunks;
+    cols = (cols + TC_STAGE_COLS - 1) / TC_STAGE_COLS * TC_STAGE_COLS;
+    if (cols < TC_CHUNK_MIN) cols = TC_CHUNK_MIN;
+    if (cols > TC_CHUNK_COLS) cols = TC_CHUNK_COLS;
+    return (int)cols;
 }
 template <int SRC>
 int launch_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0, int np,
-              uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks) {
+              uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks, int chunk_cols) {
     switch (np) {
-        case 1: return launch_tc_np<SRC, 1>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
-        case 2: return launch_tc_np<SRC, 2>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
-        case 3: return launch_tc_np<SRC, 3>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
-        default: return launch_tc_np<SRC, 4>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks);
+        case 1: return launch_tc_np<SRC, 1>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks, chunk_cols);
+        case 2: return launch_tc_np<SRC, 2>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks, chunk_cols);
+        case 3: return launch_tc_np<SRC, 3>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks, chunk_cols);
+        default: return launch_tc_np<SRC, 4>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize, chunks, chunk_cols);
     }
 }
 
@@ -126,7 +137,8 @@ int commit_s8_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T,
         MB_CUDA(cudaMemsetAsync(d_out, 0, planes * plane_words * sizeof(uint64_t), MB_STREAM));
         return finish_sync();
     }
-    const size_t chunks = (N + TC_CHUNK_COLS - 1) / TC_CHUNK_COLS;
+    const int chunk_cols = tc_chunk_cols(N);
+    const size_t chunks = (N + chunk_cols - 1) / chunk_cols;
     uint64_t* partial = nullptr;
     int* d_err = nullptr;
     MB_CUDA(pool_alloc((void**)&partial, chunks * 3 * TC_MAX_PLANES * TC_ROWS * D * sizeof(uint64_t)));
@@ -137,9 +149,9 @@ int commit_s8_tc(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T,
         const int np = planes - p0 < TC_PASS_PLANES ? planes - p0 : TC_PASS_PLANES;
         {
             MB_KERNEL(d_T ? "ajtai_commit_tc_tiled" : d_M ? "ajtai_commit_tc_premat" : "ajtai_commit_tc");
-            if (d_T) rc = launch_tc<TC_SRC_TILED>(nullptr, nullptr, d_T, d_digits, N, p0, np, 0, partial, d_err, nullptr, chunks);
-            else if (d_M) rc = launch_tc<TC_SRC_COEFFS>(nullptr, d_M, nullptr, d_digits, N, p0, np, 0, partial, d_err, nullptr, chunks);
-            else rc = launch_tc<TC_SRC_CHACHA>(d_key, nullptr, nullptr, d_digits, N, p0, np, col_offset, partial, d_err, nullptr, chunks);
+            if (d_T) rc = launch_tc<TC_SRC_TILED>(nullptr, nullptr, d_T, d_digits, N, p0, np, 0, partial, d_err, nullptr, chunks, chunk_cols);
+            else if (d_M) rc = launch_tc<TC_SRC_COEFFS>(nullptr, d_M, nullptr, d_digits, N, p0, np, 0, partial, d_err, nullptr, chunks, chunk_cols);
+            else rc = launch_tc<TC_SRC_CHACHA>(d_key, nullptr, nullptr, d_digits, N, p0, np, col_offset, partial, d_err, nullptr, chunks, chunk_cols);
         }
         if (rc != MB_OK) break;
         {
@@ -191,13 +203,14 @@ uint64_t ajtai_tc_matrix_bytes(uint64_t N) { return ((N + TC_STAGE_COLS - 1) / T
 int ajtai_materialize_tc_ffi(const uint32_t* d_key, uint8_t* d_T, uint64_t N, uint64_t col_offset) {
     if (!d_key || (!d_T && N)) return MB_ERR_ARG;
     if (N == 0) return MB_OK;
-    const size_t chunks = (N + TC_CHUNK_COLS - 1) / TC_CHUNK_COLS;
+    const int chunk_cols = tc_chunk_cols(N);
+    const size_t chunks = (N + chunk_cols - 1) / chunk_cols;
     int* d_err = nullptr;
     MB_CUDA(pool_alloc((void**)&d_err, sizeof(int)));
     int rc = cudaMemsetAsync(d_err, 0, sizeof(int), MB_STREAM) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
     if (rc == MB_OK) {
         MB_KERNEL("ajtai_materialize_tc");
-        rc = launch_tc<TC_SRC_CHACHA>(d_key, nullptr, nullptr, nullptr, N, 0, 1, col_offset, nullptr, d_err, d_T, chunks);
+        rc = launch_tc<TC_SRC_CHACHA>(d_key, nullptr, nullptr, nullptr, N, 0, 1, col_offset, nullptr, d_err, d_T, chunks, chunk_cols);
     }
     if (rc == MB_OK) rc = finish_sync();
     pool_free(d_err);

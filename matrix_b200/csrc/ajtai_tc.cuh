@@ -40,7 +40,8 @@ namespace aj {
 constexpr int TC_ROWS = 14;             // matrix rows per CTA (3 groups cover 42)
 constexpr int TC_STAGE_COLS = 4;        // columns per MMA stage
 constexpr int TC_STAGE_K = TC_STAGE_COLS * D;   // 256 bytes of K per stage
-constexpr int TC_CHUNK_COLS = 512;      // columns per accumulation (s32 exactness)
+constexpr int TC_CHUNK_COLS = 512;      // most columns per accumulation (s32 exactness)
+constexpr int TC_CHUNK_MIN = 32;        // fewest columns per CTA: below that the set-up and the epilogue dominate
 constexpr int TC_MAX_PLANES = 4;        // digit planes per CTA: N = 64 * planes <= 256
 constexpr uint32_t TC_CORE = 128;       // bytes of one 8 x 16 core matrix
 constexpr uint32_t TC_SBO = (TC_STAGE_K / 16) * TC_CORE;  // 2048: next 8-row group
@@ -79,7 +80,7 @@ constexpr int TCP_THREADS = 512;                    // sixteen warps hide the la
 enum TcSource { TC_SRC_CHACHA = 0, TC_SRC_COEFFS = 1, TC_SRC_TILED = 2 };
 constexpr uint32_t TCP_A_IMAGE = 14 * TC_SBO;       // 28672 bytes: the rows of the A buffer that hold data
 
-// grid = (column chunks, 3 row groups); dynamic shared memory tc_pipe_smem_bytes(np).
+// grid = (column chunks of chunk_cols columns, a multiple of 4 and at most 512; 3 row groups); dynamic shared memory tc_pipe_smem_bytes(np).
 // d_digits: [planes][N][64] s8 (this CTA uses planes p0 .. p0 + np - 1, np <= 4: N = 64 np columns of one MMA).
 // partial[((chunk * 3 + group) * np + p) * 14 * 64 + i_local * 64 + r] = canonical chunk sum.
 // materialize != nullptr: no digits, no MMAs; the A images of this CTA's stages are written there instead.
@@ -89,7 +90,7 @@ template <int SRC, int NP>
 static __global__ void __launch_bounds__(TCP_THREADS, 1)
 commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const uint8_t* __restrict__ d_T,
                       const int8_t* __restrict__ d_digits, uint64_t N, int p0, uint64_t col_offset, uint64_t* __restrict__ partial,
-                      int* __restrict__ d_error, uint8_t* __restrict__ materialize) {
+                      int* __restrict__ d_error, uint8_t* __restrict__ materialize, int chunk_cols) {
     constexpr int np = NP;
     constexpr bool PREMAT = SRC == TC_SRC_COEFFS;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -101,8 +102,8 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int group = blockIdx.y;
-    const uint64_t j0 = (uint64_t)blockIdx.x * TC_CHUNK_COLS;
-    const uint64_t j1 = j0 + TC_CHUNK_COLS < N ? j0 + TC_CHUNK_COLS : N;
+    const uint64_t j0 = (uint64_t)blockIdx.x * (uint64_t)chunk_cols;
+    const uint64_t j1 = j0 + (uint64_t)chunk_cols < N ? j0 + (uint64_t)chunk_cols : N;
     uint32_t key[8];
 #pragma unroll
     for (int k = 0; k < 8; k++) key[k] = SRC == TC_SRC_CHACHA ? d_key[k] : 0u;
