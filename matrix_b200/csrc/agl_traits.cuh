@@ -62,6 +62,32 @@ struct AglExt2 {
 };
 
 template <>
+struct Lazy<AglBase> {
+    using A = gl::Acc;
+    static __device__ __forceinline__ A zero() { return gl::acc_zero(); }
+    static __device__ __forceinline__ void mul(A& s, uint64_t x, uint64_t y) { gl::acc_mul(s, x, y); }
+    static __device__ __forceinline__ uint64_t reduce(const A& s) { return agl::acc_reduce(s); }
+};
+// sum x_k y_k over the extension X^2 = 3 as three exact sums (c0 c0, c1 c1, cross terms)
+struct AglE2Acc {
+    gl::Acc s00, s11, s01;
+};
+template <>
+struct Lazy<AglExt2> {
+    using A = AglE2Acc;
+    static __device__ __forceinline__ A zero() { return A{gl::acc_zero(), gl::acc_zero(), gl::acc_zero()}; }
+    static __device__ __forceinline__ void mul(A& q, agl::E2 x, agl::E2 y) {
+        gl::acc_mul(q.s00, x.c0, y.c0);
+        gl::acc_mul(q.s11, x.c1, y.c1);
+        gl::acc_mul(q.s01, x.c0, y.c1);
+        gl::acc_mul(q.s01, x.c1, y.c0);
+    }
+    static __device__ __forceinline__ agl::E2 reduce(const A& q) {
+        return agl::E2{agl::add(agl::acc_reduce(q.s00), agl::mul_small(agl::acc_reduce(q.s11), 3)), agl::acc_reduce(q.s01)};
+    }
+};
+
+template <>
 struct FoldOp<AglBase, AglExt2> {
     static __device__ __forceinline__ agl::E2 apply(uint64_t a, uint64_t b, agl::E2 r) {
         return agl::e2_fma_pre_base(agl::e2_pre(r), agl::sub(b, a), a);

@@ -84,6 +84,66 @@ struct GlExt2 {
     static __device__ __forceinline__ uint64_t reduce_acc(const gl::Acc& s) { return gl::acc_reduce(s); }
 };
 
+// Exact sums of products for a field: A holds sum x_k y_k without any reduction; at most LAZY_MAX products
+// may be added before reduce(). Specialised per field (almost-Goldilocks in agl_traits.cuh).
+template <class F>
+struct Lazy;
+constexpr int LAZY_MAX = 64;
+template <>
+struct Lazy<GlBase> {
+    using A = gl::Acc;
+    static __device__ __forceinline__ A zero() { return gl::acc_zero(); }
+    static __device__ __forceinline__ void mul(A& s, uint64_t x, uint64_t y) { gl::acc_mul(s, x, y); }
+    static __device__ __forceinline__ uint64_t reduce(const A& s) { return gl::acc_reduce(s); }
+};
+template <>
+struct Lazy<GlExt2> {
+    using A = gl::E2Acc;
+    static __device__ __forceinline__ A zero() { return gl::e2acc_zero(); }
+    static __device__ __forceinline__ void mul(A& s, gl::E2 x, gl::E2 y) { gl::e2acc_mul(s, x, y); }
+    static __device__ __forceinline__ gl::E2 reduce(const A& s) { return gl::e2acc_reduce(s); }
+};
+
+// Round polynomial of a product of two tables from three exact sums. With a = value at 0, b = value at 1 and
+// d = b - a per table, P(c) = S0 + c S1 + c^2 S2 where S0 = sum a0 a1 = P(0), S2 = sum d0 d1 and
+// P(1) = sum b0 b1, hence P(2) = 2 P(1) - S0 + 2 S2. The three sums take one multiply-accumulate chain each per
+// pair and are reduced once per LAZY_MAX pairs, instead of three reduced products, three modular additions and
+// two rounds of value updates per pair.
+template <class F>
+struct PairSums {
+    using T = typename F::T;
+    typename Lazy<F>::A s0, s1, s2;
+    T t0, t1, t2;
+    int pending;
+    __device__ __forceinline__ void init() {
+        s0 = Lazy<F>::zero(); s1 = Lazy<F>::zero(); s2 = Lazy<F>::zero();
+        t0 = F::zero(); t1 = F::zero(); t2 = F::zero();
+        pending = 0;
+    }
+    __device__ __forceinline__ void flush() {
+        t0 = F::add(t0, Lazy<F>::reduce(s0));
+        t1 = F::add(t1, Lazy<F>::reduce(s1));
+        t2 = F::add(t2, Lazy<F>::reduce(s2));
+        s0 = Lazy<F>::zero(); s1 = Lazy<F>::zero(); s2 = Lazy<F>::zero();
+        pending = 0;
+    }
+    // a_i, b_i: the two tables' values at 0 and 1
+    __device__ __forceinline__ void add_pair(T a0, T b0, T a1, T b1) {
+        Lazy<F>::mul(s0, a0, a1);
+        Lazy<F>::mul(s1, b0, b1);
+        Lazy<F>::mul(s2, F::sub(b0, a0), F::sub(b1, a1));
+        if (++pending == LAZY_MAX) flush();
+    }
+    // acc[0..2] = this thread's share of P(0), P(1), P(2)
+    __device__ __forceinline__ void finish(T (&acc)[3]) {
+        flush();
+        acc[0] = t0;
+        acc[1] = t1;
+        T twice = F::add(F::add(t1, t1), F::add(t2, t2));
+        acc[2] = F::sub(twice, t0);
+    }
+};
+
 // ---- block-wide sum of NV residues per thread -------------------------------
 // Warp shuffles, then one shared-memory hop across warps. Thread 0 writes the
 // canonical totals to out[0..NV). blockDim.x must be a multiple of 32.
@@ -171,24 +231,36 @@ __device__ __forceinline__ void store_partials(typename F::T (&acc)[D + 1], uint
 // ---- round message ----------------------------------------------------------
 // partial[(blockIdx.x * (D+1) + c) * NW ...] = this block's share of P(c).
 template <class F, int D>
-__global__ void __launch_bounds__(D <= 3 ? 1024 : 256)
+__global__ void __launch_bounds__(D == 2 ? 512 : D == 3 ? 1024 : 256)   // D = 2 keeps exact sums in registers
 round_message_kernel(const uint64_t* __restrict__ polys, size_t stride, size_t half, uint64_t* __restrict__ partial,
                      unsigned int* counter, uint64_t* final_out) {
     using T = typename F::T;
     T acc[D + 1];
-#pragma unroll
-    for (int c = 0; c <= D; c++) acc[c] = F::zero();
     const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
-        T val[D], diff[D];
-#pragma unroll
-        for (int i = 0; i < D; i++) {
-            T a, b;
-            F::load2(polys + (size_t)i * stride * F::NW, 2 * y, a, b);
-            val[i] = a;
-            diff[i] = F::sub(b, a);
+    if constexpr (D == 2) {
+        PairSums<F> ps;
+        ps.init();
+        for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
+            T a0, b0, a1, b1;
+            F::load2(polys, 2 * y, a0, b0);
+            F::load2(polys + stride * F::NW, 2 * y, a1, b1);
+            ps.add_pair(a0, b0, a1, b1);
         }
-        accumulate_pair<F, D>(val, diff, acc);
+        ps.finish(acc);
+    } else {
+#pragma unroll
+        for (int c = 0; c <= D; c++) acc[c] = F::zero();
+        for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
+            T val[D], diff[D];
+#pragma unroll
+            for (int i = 0; i < D; i++) {
+                T a, b;
+                F::load2(polys + (size_t)i * stride * F::NW, 2 * y, a, b);
+                val[i] = a;
+                diff[i] = F::sub(b, a);
+            }
+            accumulate_pair<F, D>(val, diff, acc);
+        }
     }
     store_partials<F, D>(acc, partial, counter, final_out);
 }
@@ -248,24 +320,44 @@ fold_message_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out,
     TO r = r_val;
     if (r_ptr != nullptr) r = FOut::load(r_ptr, 0);
     TO acc[D + 1];
-#pragma unroll
-    for (int c = 0; c <= D; c++) acc[c] = FOut::zero();
     const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < quarter; y += step) {
-        TO val[D], diff[D];
+    if constexpr (D == 2) {
+        PairSums<FOut> ps;
+        ps.init();
+        for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < quarter; y += step) {
+            TO f[2][2];
 #pragma unroll
-        for (int i = 0; i < D; i++) {
-            TI e0, e1, e2, e3;
-            const uint64_t* pin = in + (size_t)i * stride_in * FIn::NW;
-            FIn::load2(pin, 4 * y, e0, e1);
-            FIn::load2(pin, 4 * y + 2, e2, e3);
-            TO f0 = FoldOp<FIn, FOut>::apply(e0, e1, r);
-            TO f1 = FoldOp<FIn, FOut>::apply(e2, e3, r);
-            FOut::store2(out + (size_t)i * stride_out * FOut::NW, 2 * y, f0, f1);
-            val[i] = f0;
-            diff[i] = FOut::sub(f1, f0);
+            for (int i = 0; i < 2; i++) {
+                TI e0, e1, e2, e3;
+                const uint64_t* pin = in + (size_t)i * stride_in * FIn::NW;
+                FIn::load2(pin, 4 * y, e0, e1);
+                FIn::load2(pin, 4 * y + 2, e2, e3);
+                f[i][0] = FoldOp<FIn, FOut>::apply(e0, e1, r);
+                f[i][1] = FoldOp<FIn, FOut>::apply(e2, e3, r);
+                FOut::store2(out + (size_t)i * stride_out * FOut::NW, 2 * y, f[i][0], f[i][1]);
+            }
+            ps.add_pair(f[0][0], f[0][1], f[1][0], f[1][1]);
         }
-        accumulate_pair<FOut, D>(val, diff, acc);
+        ps.finish(acc);
+    } else {
+#pragma unroll
+        for (int c = 0; c <= D; c++) acc[c] = FOut::zero();
+        for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < quarter; y += step) {
+            TO val[D], diff[D];
+#pragma unroll
+            for (int i = 0; i < D; i++) {
+                TI e0, e1, e2, e3;
+                const uint64_t* pin = in + (size_t)i * stride_in * FIn::NW;
+                FIn::load2(pin, 4 * y, e0, e1);
+                FIn::load2(pin, 4 * y + 2, e2, e3);
+                TO f0 = FoldOp<FIn, FOut>::apply(e0, e1, r);
+                TO f1 = FoldOp<FIn, FOut>::apply(e2, e3, r);
+                FOut::store2(out + (size_t)i * stride_out * FOut::NW, 2 * y, f0, f1);
+                val[i] = f0;
+                diff[i] = FOut::sub(f1, f0);
+            }
+            accumulate_pair<FOut, D>(val, diff, acc);
+        }
     }
     store_partials<FOut, D>(acc, partial, counter, final_out);
 }
