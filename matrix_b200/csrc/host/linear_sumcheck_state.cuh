@@ -48,11 +48,14 @@ public:
         MB_CUDA(pool_alloc((void**)&buf_b_, sizeof(uint64_t) * 2 * cap_b * d));
         max_blocks_ = prover_grid(n_ / 2 > 0 ? n_ / 2 : 1);
         MB_CUDA(pool_alloc((void**)&partial_, sizeof(uint64_t) * 2 * (d + 1) * (size_t)max_blocks_));
-        MB_CUDA(pool_alloc((void**)&msg_dev_, sizeof(uint64_t) * 2 * (MAX_D + 1)));
         MB_CUDA(pool_alloc((void**)&counter_, sizeof(unsigned int)));
         MB_CUDA(cudaMemsetAsync(counter_, 0, sizeof(unsigned int), MB_STREAM));
+        // The finished message is written by the last block of a kernel straight into pinned host memory
+        // (device-addressable under unified addressing), so a round costs one stream synchronisation and no
+        // copy call.
         msg_host_ = pinned_scratch();
         if (!msg_host_) return MB_ERR_CUDA;
+        msg_dev_ = msg_host_;
         have_msg_ = false;
         return MB_OK;
     }
@@ -73,8 +76,6 @@ public:
             if (rc != MB_OK) return rc;
             msg_words_ = base_ ? 1 : 2;
         }
-        MB_CUDA(cudaMemcpyAsync(msg_host_, msg_dev_, sizeof(uint64_t) * msg_words_ * (d_ + 1),
-                                cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         out.resize(d_ + 1);
         for (int c = 0; c <= d_; c++) {
@@ -157,7 +158,6 @@ private:
         pool_free(buf_a_);
         pool_free(buf_b_);
         pool_free(partial_);
-        pool_free(msg_dev_);
         pool_free(counter_);
         buf_a_ = buf_b_ = partial_ = msg_dev_ = nullptr;
         counter_ = nullptr;
