@@ -34,6 +34,10 @@ struct AglBase {
     static __device__ __forceinline__ T zero() { return 0; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v; }
     static __device__ __forceinline__ T from_words(const uint64_t* w) { return w[0]; }
+    // a factor used many times (nothing to prepare in the base field)
+    using Pre = uint64_t;
+    static __device__ __forceinline__ Pre pre(T x) { return x; }
+    static __device__ __forceinline__ T mul_pre(Pre p, T x) { return agl::mul(p, x); }
 };
 
 struct AglExt2 {
@@ -57,6 +61,10 @@ struct AglExt2 {
     static __device__ __forceinline__ T zero() { return agl::E2{0, 0}; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
     static __device__ __forceinline__ T from_words(const uint64_t* w) { return T{w[0], w[1]}; }
+    // a factor used many times, with its c1 times the non-residue prepared: four products, two reductions
+    using Pre = agl::E2Pre;
+    static __device__ __forceinline__ Pre pre(T x) { return agl::e2_pre(x); }
+    static __device__ __forceinline__ T mul_pre(Pre p, T x) { return agl::e2_fma_pre(p, x, agl::E2{0, 0}); }
     // an exact sum of at most 64 products of 64-bit words, reduced to a loose residue
     static __device__ __forceinline__ uint64_t reduce_acc(const gl::Acc& s) { return agl::acc_reduce(s); }
 };

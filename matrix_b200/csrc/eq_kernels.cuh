@@ -43,13 +43,17 @@ __global__ void small_tables_kernel(const uint64_t* __restrict__ r, int nbits0, 
     }
 }
 
+// out[row 2^n_lo + j] = lo[j] * hi[row]: a block keeps one hi entry (prepared once) per row of 2^n_lo outputs.
 template <class F>
-__global__ void outer_product_kernel(const uint64_t* __restrict__ lo, const uint64_t* __restrict__ hi, int n_lo,
-                                     uint64_t* __restrict__ out, size_t n) {
-    const size_t mask = ((size_t)1 << n_lo) - 1;
-    const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (size_t x = (size_t)blockIdx.x * blockDim.x + threadIdx.x; x < n; x += step)
-        F::store(out, x, F::mul(F::load(lo, x & mask), F::load(hi, x >> n_lo)));
+__global__ void __launch_bounds__(256)
+outer_product_kernel(const uint64_t* __restrict__ lo, const uint64_t* __restrict__ hi, int n_lo,
+                     uint64_t* __restrict__ out, size_t n) {
+    const size_t lo_size = (size_t)1 << n_lo, rows = n >> n_lo;
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const typename F::Pre h = F::pre(F::load(hi, row));
+        for (size_t j = threadIdx.x; j < lo_size; j += blockDim.x)
+            F::store(out, row * lo_size + j, F::mul_pre(h, F::load(lo, j)));
+    }
 }
 
 // Builds the table in d_out (2^log_n elements). d_scratch needs room for
@@ -76,7 +80,7 @@ inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int 
     size_t n = (size_t)1 << log_n;
     {
         MB_KERNEL_ON("outer_product", st);
-        outer_product_kernel<F><<<grid_for(n, 256, 8), 256, 0, st>>>(lo, hi, n_lo, d_out, n);
+        outer_product_kernel<F><<<grid_for((n >> n_lo) * 256, 256, 8), 256, 0, st>>>(lo, hi, n_lo, d_out, n);
     }
     return finish_async();
 }

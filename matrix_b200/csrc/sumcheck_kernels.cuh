@@ -55,6 +55,10 @@ struct GlBase {
     static __device__ __forceinline__ T zero() { return 0; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v; }
     static __device__ __forceinline__ T from_words(const uint64_t* w) { return w[0]; }
+    // a factor used many times (nothing to prepare in the base field)
+    using Pre = uint64_t;
+    static __device__ __forceinline__ Pre pre(T x) { return x; }
+    static __device__ __forceinline__ T mul_pre(Pre p, T x) { return gl::mul(p, x); }
 };
 
 struct GlExt2 {
@@ -80,6 +84,10 @@ struct GlExt2 {
     static __device__ __forceinline__ T zero() { return gl::E2{0, 0}; }
     static __device__ __forceinline__ void to_words(T v, uint64_t* w) { w[0] = v.c0; w[1] = v.c1; }
     static __device__ __forceinline__ T from_words(const uint64_t* w) { return T{w[0], w[1]}; }
+    // a factor used many times, with its c1 times the non-residue prepared: four products, two reductions
+    using Pre = gl::E2Pre;
+    static __device__ __forceinline__ Pre pre(T x) { return gl::e2_pre(x); }
+    static __device__ __forceinline__ T mul_pre(Pre p, T x) { return gl::e2_mul_pre(p, x); }
     // an exact sum of at most 64 products of 64-bit words, reduced to a loose residue
     static __device__ __forceinline__ uint64_t reduce_acc(const gl::Acc& s) { return gl::acc_reduce(s); }
 };
