@@ -56,7 +56,7 @@ fold_levels_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, 
 // First pass over a base-field table: K variables at once as an inner product with
 // eq weights. One tile = 256 outputs = 256 * 2^K inputs; n_out is a multiple of 256.
 template <class FIn, class FOut, int K>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 4)
 dot_levels_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, const uint64_t* __restrict__ r, int lvl,
                   size_t n_out) {
     using TO = typename FOut::T;
@@ -108,7 +108,7 @@ dot_levels_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, c
 
 template <class FIn, class FOut>
 inline void launch_dot(const uint64_t* in, uint64_t* out, const uint64_t* r, int lvl, int k, size_t n_out, cudaStream_t st) {
-    int grid = grid_for(n_out, 256, 3);
+    int grid = grid_for(n_out, 256, 4);
     MB_KERNEL_ON("partial_eval_dot", st);
     switch (k) {
         case 1: dot_levels_kernel<FIn, FOut, 1><<<grid, 256, 0, st>>>(in, out, r, lvl, n_out); break;
