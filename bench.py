@@ -115,8 +115,8 @@ def cpu_oracle_sample(num_vars, threads=None, merkle_hash="poseidon2"):
     """One commit + open of the CPU oracle at 2^num_vars; returns seconds and thread count."""
     from matrix_b200.inputs import field_elems
     from oracle import pyoracle
-    if threads:
-        os.environ["OMP_NUM_THREADS"] = str(threads)
+    # every host core, whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1 for N > 1)
+    pyoracle.load().oracle_set_threads(threads or os.cpu_count() or 1)
     pyoracle.load().oracle_set_merkle_hash(1 if merkle_hash == "monolith" else 0)
     evals = field_elems(3, 1 << num_vars)
     point = field_elems(4, 2 * num_vars)
@@ -277,6 +277,7 @@ def run_reference_batched(args):
         return
     from matrix_b200.inputs import field_elems
     from oracle import pyoracle
+    pyoracle.load().oracle_set_threads(os.cpu_count() or 1)   # the launcher may have exported OMP_NUM_THREADS=1
     nv, K = args.ref_num_vars, args.instances
     n = 1 << nv
     a = np.concatenate([field_elems(100 + k, n) for k in range(K)])

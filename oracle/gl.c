@@ -264,3 +264,9 @@ void oracle_gl_e5_pow(const uint64_t *a, uint64_t e, uint64_t *out) {
     }
     memcpy(out, r, sizeof r);
 }
+
+/* Thread count of the OpenMP regions of this library (a launcher may have set OMP_NUM_THREADS=1 in the
+ * environment; the timed CPU arm wants every host core). */
+#include <omp.h>
+void oracle_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int oracle_max_threads(void) { return omp_get_max_threads(); }

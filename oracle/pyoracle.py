@@ -208,6 +208,8 @@ _SIGS.update({
 
 
 _SIGS.update({
+    "oracle_set_threads": (None, [ci]),
+    "oracle_max_threads": (ci, []),
     "oracle_agl_sumcheck_prove": (ci, [vp, ci, ci, ci, ctypes.c_char_p, sz, vp, vp, vp, vp, vp]),
     "oracle_agl_sumcheck_verify": (ci, [vp, vp, vp, ci, ci, ctypes.c_char_p, sz, vp]),
 })
