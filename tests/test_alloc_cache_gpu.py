@@ -79,3 +79,40 @@ def test_switch_restores_plain_allocation():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "plain" in out.stdout, out.stderr
+
+
+def test_concurrent_threads_never_share_a_block():
+    """The reference's callers are rayon workers: several host threads allocate and drop buffers at once. Each
+    thread writes its own pattern into every buffer it holds and reads it back after the others had time to
+    allocate: a block handed to two owners would show the wrong pattern."""
+    import threading
+    lib = load_agl()
+    errors = []
+
+    def worker(tid):
+        try:
+            lib.cuda_set_device(0)
+            rng = np.random.default_rng(tid)
+            for it in range(60):
+                sizes = [int(rng.integers(1, 64)) * 4096 for _ in range(3)]
+                held = []
+                for k, n in enumerate(sizes):
+                    p = _malloc(lib, n)
+                    pat = np.full(n // 8, (tid << 32) | (it << 8) | k, dtype=np.uint64)
+                    assert lib.cuda_memcpy_htod(p, pat.ctypes.data, pat.nbytes) == 0
+                    held.append((p, pat))
+                for p, pat in held:
+                    back = np.empty_like(pat)
+                    assert lib.cuda_memcpy_dtoh(back.ctypes.data, p, back.nbytes) == 0
+                    assert np.array_equal(back, pat)
+                    assert lib.cuda_free(p) == 0
+        except Exception as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(t + 1,)) for t in range(6)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert lib.mb_alloc_cache_flush() == 0
