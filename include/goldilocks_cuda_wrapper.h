@@ -136,7 +136,10 @@ int sumcheck_fold_mixed_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_
  * d_message receives the d + 1 evaluations P(0..d), canonical. Limits: d <= 8,
  * half <= 2^30 (-3 beyond). First call per device resolves the array's address
  * (do it before any stream capture). Calls on one device share the array and
- * must not overlap. */
+ * must not overlap. "Allocates nothing" holds with the library's per-kernel
+ * timing off (mb_prof_enable(0), the default): with it on, every launch creates
+ * two CUDA events. The resolved address is cached for the life of the process
+ * and is not valid after a cudaDeviceReset of that device. */
 int sumcheck_round_message_ext2_noalloc_ffi(const uint64_t* d_polys, uint64_t* d_message, int d,
                                             size_t original_size, size_t half);
 

@@ -13,6 +13,12 @@
 // call on a device uses the same array, and two calls that overlap on the GPU
 // (different streams or host threads) would overwrite each other's partial
 // sums. Callers must serialise calls per device.
+//
+// Two conditions on "allocates nothing": the library's per-kernel timing must
+// be off (mb_prof_enable(0), the default), because with it on every launch
+// creates two CUDA events; and the array's address, looked up once per device
+// and cached for the life of the process, does not survive a cudaDeviceReset
+// of that device.
 #include "gl_sumcheck_launch.cuh"
 #include <mutex>
 

@@ -41,8 +41,11 @@ int launch_round_message(const uint64_t* d_polys, uint64_t* d_partial, int d, si
     if (half < 1 || 2 * half > stride) return MB_ERR_ARG;
     if (!aligned16(d_polys) || ((stride * F::NW) & 1)) return MB_ERR_ARG;
     int threads = threads_for(half, num_blocks);
-    if (d > 3 && threads > 256) threads = 256;
-    if (d == 2 && threads > 512) threads = 512;   // launch bounds of the kernels (register budget of the exact sums)
+    // launch bounds of round_message_kernel: 512 threads for two tables (register budget of the exact
+    // sums), 1024 for three, 256 for every other count (one table included); the kernels are
+    // grid-stride loops, so a smaller block only means more sweeps
+    const int bound = d == 2 ? 512 : d == 3 ? 1024 : 256;
+    if (threads > bound) threads = bound;
     MB_KERNEL_ON("sumcheck_round_message", st);
     MB_DISPATCH_D(d, (round_message_kernel<F, D><<<num_blocks, threads, 0, st>>>(d_polys, stride, half, d_partial,
                                                                                      d_counter, d_final)));

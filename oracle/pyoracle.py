@@ -17,10 +17,11 @@ sz = ctypes.c_size_t
 
 
 def build(ref=True):
-    """Compile the oracle (and, if the reference tree is present, oracle/_ref)."""
+    """Compile the oracle and, when the reference tree is where the Makefile's REF points, oracle/_ref:
+    the reference's host-only code (target ref) and its CUDA wrappers for sm_100a (target refcuda)."""
     subprocess.check_call(["make", "-s", "-C", HERE])
-    if ref:
-        subprocess.call(["make", "-s", "-C", HERE, "ref"])
+    if ref and subprocess.call(["make", "-s", "-C", HERE, "have-ref"]) == 0:
+        subprocess.call(["make", "-s", "-C", HERE, "ref", "refcuda"])
 
 
 _SIGS = {

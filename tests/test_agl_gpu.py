@@ -54,7 +54,7 @@ def _sum_rows(buf, rows, width):
     return [sum(int(x) for x in part[:, k]) % Q for k in range(width)]
 
 
-@pytest.mark.parametrize("nv,d", [(1, 1), (4, 2), (9, 3), (12, 3), (14, 8), (16, 2)])
+@pytest.mark.parametrize("nv,d", [(1, 1), (4, 2), (9, 3), (12, 3), (14, 8), (16, 2), (18, 1)])
 def test_base_sumcheck_dropin(lib, oracle, nv, d):
     n = 1 << nv
     cur = aelems(100 + nv + d, n * d)
@@ -79,7 +79,7 @@ def test_base_sumcheck_dropin(lib, oracle, nv, d):
         d_a, d_b = d_b, d_a
 
 
-@pytest.mark.parametrize("nv,d", [(1, 1), (5, 2), (11, 3), (13, 5), (16, 3)])
+@pytest.mark.parametrize("nv,d", [(1, 1), (5, 2), (11, 3), (13, 5), (16, 3), (18, 1)])
 def test_ext2_sumcheck_dropin_and_fused(lib, oracle, nv, d):
     n = 1 << nv
     cur = aelems(200 + nv + d, n * d * 2)

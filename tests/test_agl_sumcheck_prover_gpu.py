@@ -84,7 +84,7 @@ def test_reference_cases():
 
 
 @pytest.mark.parametrize("d,nv,base", [(1, 9, True), (2, 12, True), (3, 11, False), (4, 8, False), (5, 7, True),
-                                        (2, 1, False), (3, 0, False), (2, 14, False)])
+                                        (2, 1, False), (3, 0, False), (2, 14, False), (1, 19, True)])
 def test_random_tables_match_oracle(d, nv, base):
     lib = load_agl()
     n = 1 << nv

@@ -71,7 +71,8 @@ def test_signed_digits_match_oracle(lib, n, planes, off):
 @pytest.mark.parametrize("n,planes,off", [(1, 1, 0), (4, 1, 0), (5, 3, 9), (70, 4, 0), (130, 8, 3), (600, 3, 1 << 20)])
 def test_tensor_core_digits_match_oracle(lib, n, planes, off):
     # tcgen05 path: exact integer accumulation, so the result must equal the CPU oracle bit for bit;
-    # n = 600 crosses the 512-column drain boundary, planes = 8 runs two plane groups
+    # planes = 8 runs two plane groups. Witnesses this short are cut into narrow column chunks (a CTA gets
+    # 32 columns); the full 512-column chunk has its own test below.
     from oracle import pyoracle
     rng = np.random.default_rng(n * 5 + planes)
     dig = rng.integers(-127, 128, size=planes * n * 64, dtype=np.int8)
@@ -84,6 +85,47 @@ def test_tensor_core_digits_match_oracle(lib, n, planes, off):
     exp = pyoracle.ajtai_commit(KEY, dig, 1, n, planes, off)
     bad = np.nonzero(got != exp)[0]
     assert len(bad) == 0, "%d of %d words differ, first at %d" % (len(bad), len(exp), bad[0])
+
+
+def test_tensor_core_full_width_chunks_with_worst_case_sums(lib):
+    """50 688 ring columns: the smallest witness whose column chunks are the full 512 columns wide, the width the
+    2^18-column configuration runs at. Every digit of chunk 0 is +127 and every digit of chunk 1 is -127, the
+    largest magnitude a 32-bit accumulator sees before it is drained (255 * 127 * 64 * 512 < 2^31); the rest is
+    random. All 42 x 64 output words against the scalar kernel (itself pinned to the CPU oracle), and rows 0 and
+    41 against the reference's own host code (ring elements from its ChaCha8 expansion, products by its
+    cpu_ring_mul), summed here."""
+    from oracle import pyoracle
+    n, planes = 50688, 2
+    rng = np.random.default_rng(99)
+    dig = rng.integers(-127, 128, size=planes * n * 64, dtype=np.int8)
+    dig[:512 * 64] = 127
+    dig[512 * 64:1024 * 64] = -127
+    dig[n * 64 + 1024 * 64:n * 64 + 1536 * 64] = 127          # plane 1: a different chunk
+    d_k, d_z = DeviceBuffer.from_numpy(lib, KEY), DeviceBuffer.from_numpy(lib, dig)
+    d_a, d_b = DeviceBuffer(lib, planes * 42 * 64 * 8), DeviceBuffer(lib, planes * 42 * 64 * 8)
+    assert lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n, planes, 0, d_a.ptr) == 0
+    assert lib.ajtai_commit_s8_scalar_ffi(d_k.ptr, d_z.ptr, n, planes, 0, d_b.ptr) == 0
+    got = d_a.to_numpy()
+    assert np.array_equal(got, d_b.to_numpy())
+    ref = pyoracle.load_ref("libajtai_ref.so")
+    if ref is None:
+        pytest.skip("oracle/_ref/libajtai_ref.so not built")
+    z = np.where(dig[:n * 64] < 0, np.uint64(Q) - (-dig[:n * 64].astype(np.int64)).astype(np.uint64),
+                 dig[:n * 64].astype(np.int64).astype(np.uint64)).reshape(n, 64)
+    z = np.ascontiguousarray(z)
+    for row in (0, 41):
+        acc = np.zeros(64, dtype=object)
+        m, prod = np.zeros(64, dtype=np.uint64), np.zeros(64, dtype=np.uint64)
+        part = np.zeros(64, dtype=object)
+        for j in range(n):
+            ref.ref_ajtai_ring_elem(KEY.ctypes.data, row, j, m.ctypes.data)
+            ref.ref_ring_mul(m.ctypes.data, z[j].ctypes.data, prod.ctypes.data)
+            part += prod.astype(object)
+            if j % 4096 == 4095:
+                acc = (acc + part) % Q
+                part = np.zeros(64, dtype=object)
+        acc = (acc + part) % Q
+        assert [int(x) for x in got[row * 64:(row + 1) * 64]] == [int(x) for x in acc], "row %d" % row
 
 
 def test_tensor_core_rejects_minus_128(lib):

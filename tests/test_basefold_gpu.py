@@ -212,6 +212,38 @@ def test_commit_open_matches_oracle(lib, nv, lr, nq):
     lib.basefold_table_destroy(h)
 
 
+def test_full_size_commit_and_opening_2_24(lib):
+    """The benchmarked configuration at its own size: 2^24 evaluations (seed 3), rate 1/2, 100 queries, point
+    seed 4, table seed 42, label "bench". The commitment root must equal the root of one full-size commit by the
+    CPU oracle, the folding table must equal the oracle's, and the proof must pass the oracle's restatement of
+    the reference verifier (goldilocks-cuda-rs/src/basefold.rs:1759-1925). About a minute of CPU work."""
+    from oracle import pyoracle
+    nv, lr, nq = 24, 1, 100
+    evals = field_elems(3, 1 << nv)
+    point = field_elems(4, 2 * nv)
+    h = _table(lib, nv, lr)
+    words = lib.basefold_proof_words(nv, lr, nq)
+    proof = np.zeros(words, dtype=np.uint64)
+    root = np.zeros(4, dtype=np.uint64)
+    assert lib.basefold_prove_host(evals.ctypes.data, nv, lr, point.ctypes.data, h, b"bench", 5, nq,
+                                   root.ctypes.data, proof.ctypes.data) == 0
+    table = pyoracle.bf_table(nv, lr)
+    got_table = np.zeros(2 * lib.basefold_table_entries(h), dtype=np.uint64)
+    assert lib.basefold_table_download(h, got_table.ctypes.data) == 0
+    assert np.array_equal(got_table, table)
+    del got_table
+    lib.basefold_table_destroy(h)
+    _, _, tree = pyoracle.bf_commit(evals, nv, lr)
+    assert np.array_equal(root, tree[-4:]), "commitment root of the 2^24 polynomial"
+    del tree
+    assert pyoracle.bf_verify(root, nv, lr, point, table, nq, proof) == 0
+    # a flipped word of the first oracle, of a folded root and of a query value must all be caught
+    for pos in (2, 2 + 6 * nv + 1, words - 1 - 4 * (nv + lr)):
+        bad = proof.copy()
+        bad[pos] ^= np.uint64(1)
+        assert pyoracle.bf_verify(root, nv, lr, point, table, nq, bad) != 0, "tampered word %d accepted" % pos
+
+
 def test_reference_call_sequence_through_dropin_entry_points(lib, oracle):
     # Replays open_ext2's own kernel sequence (goldilocks-cuda-rs/src/basefold.rs:578-863:
     # interp / product / eval / fused round / fold / tree, partial sums added on

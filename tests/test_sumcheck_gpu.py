@@ -28,7 +28,8 @@ def _sum_partials(partials, rows, width):
     return out
 
 
-@pytest.mark.parametrize("nv,d", [(1, 1), (1, 2), (2, 2), (4, 2), (3, 3), (9, 1), (10, 4), (12, 3), (13, 8), (16, 2)])
+@pytest.mark.parametrize("nv,d", [(1, 1), (1, 2), (2, 2), (4, 2), (3, 3), (9, 1), (10, 4), (12, 3), (13, 8), (16, 2),
+                                  (18, 1), (19, 4)])   # one table, and five or more, beyond 2^16 pairs: 256-thread blocks
 def test_base_round_and_fold_dropin(lib, oracle, nv, d):
     n = 1 << nv
     polys = field_elems(1000 + nv * 10 + d, n * d)
@@ -60,7 +61,7 @@ def test_base_round_and_fold_dropin(lib, oracle, nv, d):
         size = half
 
 
-@pytest.mark.parametrize("nv,d", [(1, 1), (2, 2), (5, 3), (11, 2), (12, 5), (14, 8), (16, 3)])
+@pytest.mark.parametrize("nv,d", [(1, 1), (2, 2), (5, 3), (11, 2), (12, 5), (14, 8), (16, 3), (18, 1)])
 def test_ext2_round_and_fold_dropin(lib, oracle, nv, d):
     n = 1 << nv
     cur = field_elems(2000 + nv * 10 + d, n * d * 2)
@@ -107,7 +108,8 @@ def test_noncanonical_inputs_give_canonical_outputs(lib, oracle):
 
 
 @pytest.mark.parametrize("nv,d,base", [(1, 1, True), (1, 2, False), (2, 2, True), (3, 3, False), (6, 2, True),
-                                       (10, 3, True), (12, 2, False), (15, 4, True), (18, 2, True), (20, 2, True)])
+                                       (10, 3, True), (12, 2, False), (15, 4, True), (18, 2, True), (20, 2, True),
+                                       (19, 1, True), (19, 1, False)])
 def test_whole_proof_matches_oracle(lib, nv, d, base):
     # (20, 2, True) is the 2^20 configuration: f, g uniform with seeds 1 and 2,
     # transcript label "bench"; every round polynomial, challenge and the final
