@@ -281,6 +281,39 @@ int basefold_prove_host(const uint64_t* h_evals, int num_vars, int log_rate, con
                         const void* table, const uint8_t* label, size_t label_len, int num_queries, uint64_t* h_root,
                         uint64_t* h_proof);
 
+/* ---- additions: one commitment + opening shared by several GPUs ----
+ * No counterpart in the reference, which runs one whole prover per device
+ * (zk-torch-3/src/commit/basefold.rs:119-146). The ranks (one host thread or
+ * process per GPU) talk through an mb_exchange: a gather of a few host words per
+ * round and one device all-to-all per proof. Exchange objects: threads of one
+ * process (local), or processes on one machine with a mailbox in POSIX shared
+ * memory for the host words and a caller-supplied device all-to-all (shm). Every
+ * wait is a bounded host wait (-4 = MB_ERR_EXCHANGE when it runs out). */
+typedef struct mb_exchange {
+    void* ctx;
+    int rank;
+    int world;
+    int (*all_gather_host)(void* ctx, const uint64_t* mine, size_t words, uint64_t* all);
+    int (*all_to_all_device)(void* ctx, const uint64_t* d_send, uint64_t* d_recv, size_t words_per_rank);
+} mb_exchange;
+typedef int (*mb_all_to_all_fn)(void* ctx, const uint64_t* d_send, uint64_t* d_recv, size_t words_per_rank);
+int mb_exchange_local_create(int world, mb_exchange** out /* world pointers */);
+int mb_exchange_shm_create(const char* name, int rank, int world, size_t slot_words, mb_all_to_all_fn a2a, void* a2a_ctx,
+                           mb_exchange** out);
+int mb_exchange_destroy(mb_exchange* ex);
+int mb_exchange_all_gather_host(mb_exchange* ex, const uint64_t* mine, size_t words, uint64_t* all);
+int mb_exchange_all_to_all_device(mb_exchange* ex, const uint64_t* d_send, uint64_t* d_recv, size_t words_per_rank);
+/* Rank r passes evaluations [r n / world, (r + 1) n / world) of the polynomial; point, table, label and query count
+ * are the same on every rank. h_root and h_proof receive, on every rank, exactly the words basefold_prove_host
+ * writes for the whole polynomial. world: a power of two, 2^log_rate <= world <= 16 * 2^log_rate;
+ * num_vars >= log2(world) + 9 (-3 otherwise). */
+int basefold_prove_sharded_device(const uint64_t* d_evals_shard, int num_vars, int log_rate, const uint64_t* h_point,
+                                  const void* table, const uint8_t* label, size_t label_len, int num_queries,
+                                  const mb_exchange* ex, uint64_t* h_root, uint64_t* h_proof);
+int basefold_prove_sharded_host(const uint64_t* h_evals_shard, int num_vars, int log_rate, const uint64_t* h_point,
+                                const void* table, const uint8_t* label, size_t label_len, int num_queries,
+                                const mb_exchange* ex, uint64_t* h_root, uint64_t* h_proof);
+
 /* ---- additions: batched degree-3 sumcheck with a shared eq table, one shard ----
  * S = sum_k alpha^k sum_x eq(t, x) a_k(x) b_k(x). d_a, d_b: [K][2^n_loc] base-field
  * slices of this shard; h_point_low: n_loc (c0, c1) pairs; h_eq_scale: eq of the

@@ -36,6 +36,8 @@ LIBRARIES = {
         "gl_challenger.cu",
         "host/gl_sumcheck_prover.cu",
         "host/gl_basefold_prover.cu",
+        "host/gl_basefold_sharded.cu",
+        "host/exchange.cu",
         "host/gl_batched_prover.cu",
     ],
     "libalmost_goldilocks_cuda_wrapper.so": [
