@@ -20,9 +20,16 @@ Printed on one JSON line:
            of the timed region) against the measured HBM peak;
   cpu_baseline  the CPU oracle (a C restatement of the reference's CPU
            prover) on a bounded sample, all host cores.
-With N > 1 (launched by torch.distributed.run) every rank proves its own
-polynomial: independent objects, no data-path collective, weak scaling.
-`--impl reference` times the CPU oracle alone on the host cores.
+The N = 1 line also carries `parts`: the linear sumcheck of f * g at 2^24 and
+the Ajtai ring commit at 2^18 ring columns, each with its own roofline, e2e and
+CPU figure (the metric names all three paths).
+With N > 1 (launched by torch.distributed.run) the SAME single polynomial is
+partitioned over the N GPUs (strong scaling: contiguous ranges of the
+evaluations and of every codeword, one device all-to-all per proof, one gather
+of 10 words per rank and round); `replicas` beside it is N independent provers.
+Timed regions run without per-kernel events; kernel times come from a separate
+pass. `--impl reference` times the CPU oracle alone on the host cores, at the
+full size.
 """
 import argparse
 import ctypes
@@ -54,9 +61,12 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi. It is started before the warm-up (nvidia-smi takes
+    a while to print its first line) and asked for the samples that fall inside the timed region; when the region
+    was shorter than the sampling period, the samples taken under the same load just before it are used and the
+    answer says so."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -64,44 +74,63 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.lines = []
+        self.t_load = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
+        self.t_load = time.time()
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.06)   # let the sample that covers the end of the region arrive
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        for line in self.lines:
+        rows = []
+        for t, line in self.lines:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
+                rows.append((t, float(parts[2]), float(parts[3]), parts[6:10]))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+        t0 = self.t0 if self.t0 is not None else self.t_load
+        t1 = (self.t1 if self.t1 is not None else time.time()) + 0.06
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        window = "timed region"
+        if not inside:
+            inside = [r for r in rows if r[0] >= (self.t_load or 0)]
+            window = "warm-up and timed region (the timed region is shorter than the sampling period)"
+        reasons = set()
+        for r in inside:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median([r[1] for r in inside])) if inside else None,
+                "sm_max_mhz": max(r[2] for r in inside) if inside else None,
+                "reasons": sorted(reasons), "samples": len(inside), "window": window}
 
 
 def dist_env():
@@ -129,32 +158,40 @@ def cpu_oracle_sample(num_vars, threads=None, merkle_hash="poseidon2"):
 
 
 def run_reference(args):
-    """The reference arm: the CPU prover (oracle port) on the host cores, rank 0 only."""
+    """The reference arm: the CPU prover (oracle port) on the host cores, rank 0 only. Steps run at the full size
+    (2^num_vars) while a time budget lasts, at least one; a small sample is reported beside them."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    nv = args.ref_num_vars
-    for _ in range(args.warmup):
-        cpu_oracle_sample(min(nv, 16), merkle_hash=args.hash)
+    nv, snv = args.num_vars, min(args.ref_num_vars, args.num_vars)
+    for _ in range(min(args.warmup, 1)):
+        cpu_oracle_sample(min(snv, 16), merkle_hash=args.hash)
+    dt_small, _ = cpu_oracle_sample(snv, merkle_hash=args.hash)
+    budget = float(os.environ.get("MB_REFERENCE_BUDGET_S", "150"))
     times = []
-    for _ in range(args.steps):
+    t_begin = time.perf_counter()
+    while len(times) < args.steps:
         dt, _ = cpu_oracle_sample(nv, merkle_hash=args.hash)
         times.append(dt)
+        if time.perf_counter() - t_begin + dt > budget:
+            break
     total = sum(times)
-    value = (1 << nv) * args.steps / total
+    value = (1 << nv) * len(times) / total
     line = {
         "impl": "reference",
         "metric": METRIC if args.hash == "poseidon2" else METRIC.replace("Poseidon2 Merkle", "Monolith Merkle"),
         "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-        "config": {"workload": "basefold_commit_open nv=24 lr=1 queries=100 %s (sampled at nv=%d)" % (args.hash, nv),
-                   "num_vars": 24, "log_rate": LOG_RATE, "num_queries": NUM_QUERIES},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "steps_run_at_full_size": len(times),
+        "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "u64",
+        "data": "synthetic",
+        "config": basefold_config(nv, args.hash, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "CPU oracle (C restatement of the reference's CPU prover, OpenMP) commit+open at "
-                                   "2^%d evaluations per step; throughput in elements/s carries over to 2^24 "
-                                   "because every phase is linear in the size" % nv},
+                         "sample": "CPU oracle (C restatement of the reference's CPU prover, OpenMP on %d cores) commit+open at the "
+                                   "full 2^%d evaluations, %d step(s) of %.1f s each inside a %.0f s budget; table generation "
+                                   "excluded; a 2^%d sample ran at %.3e elements/s" %
+                                   (cores, nv, len(times), total / len(times), budget, snv, (1 << snv) / dt_small)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -759,6 +796,402 @@ def run_peval(args):
     print(json.dumps(line))
 
 
+def basefold_config(nv, hash_name, world):
+    """The `config` object of the headline line; the same for both arms so that the two lines describe one workload."""
+    cfg = {"workload": "basefold_commit_open nv=%d lr=%d queries=%d %s" % (nv, LOG_RATE, NUM_QUERIES, hash_name),
+           "num_vars": nv, "log_rate": LOG_RATE, "num_queries": NUM_QUERIES,
+           "l2": "inputs larger than L2 (codeword 256 MiB, trees > 1 GiB per step)"}
+    if world > 1:
+        cfg["partition"] = ("one polynomial over %d GPUs: contiguous ranges of the evaluations and of every codeword; one "
+                            "device all-to-all per proof, one gather of 10 words per rank and round" % world)
+    return cfg
+
+
+def prof_report(lib):
+    need = lib.mb_prof_report(None, 0)
+    buf = ctypes.create_string_buffer(need + 16)
+    lib.mb_prof_report(buf, need + 16)
+    kernels = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.split()
+        name = name[len("monolith_"):] if name.startswith("monolith_") else name
+        kernels[name] = (int(cnt), float(ms))
+    return kernels
+
+
+def part_sumcheck(lib, args, peak, peak_kind):
+    """The linear sumcheck of f * g over 2^24 points (base-field tables, extension challenges): whole proof through
+    gl_sumcheck_prove_device_ffi (tables resident) and gl_sumcheck_prove_host_ffi (host tables, copy inside)."""
+    from matrix_b200.ffi import DeviceBuffer
+    from matrix_b200.inputs import field_elems
+    nv, d = min(args.num_vars, 24), 2
+    n = 1 << nv
+    polys = np.concatenate([field_elems(1, n), field_elems(2, n)])
+    d_t = DeviceBuffer.from_numpy(lib, polys)
+    h_p = ctypes.c_void_p()
+    assert lib.mb_host_alloc(ctypes.byref(h_p), polys.nbytes) == 0
+    ctypes.memmove(h_p.value, polys.ctypes.data, polys.nbytes)
+    rm, ch = np.zeros((nv, d + 1, 2), dtype=np.uint64), np.zeros((nv, 2), dtype=np.uint64)
+    fes, fe = np.zeros((d, 2), dtype=np.uint64), np.zeros(2, dtype=np.uint64)
+
+    def step():
+        assert lib.gl_sumcheck_prove_device_ffi(d_t.ptr, d, nv, 1, LABEL, len(LABEL), rm.ctypes.data, ch.ctypes.data,
+                                                fes.ctypes.data, fe.ctypes.data, None) == 0
+
+    def step_e2e():
+        assert lib.gl_sumcheck_prove_host_ffi(h_p, d, nv, 1, LABEL, len(LABEL), rm.ctypes.data, ch.ctypes.data,
+                                              fes.ctypes.data, fe.ctypes.data, None) == 0
+
+    timed = _event_timer(lib)
+    reps = max(args.steps, 5)
+    for _ in range(3):
+        step()
+    lib.mb_prof_enable(0)
+    ms = timed(step, reps) / reps
+    step_e2e()
+    ms_e2e = timed(step_e2e, reps) / reps
+    lib.mb_prof_reset(); lib.mb_prof_enable(1)
+    step()
+    lib.mb_prof_enable(0)
+    kernels = prof_report(lib)
+    alg_bytes = d * n * 48.0   # round 0 reads 8 B per element, the first fold reads 8 and writes 8, later rounds halve
+    ach = alg_bytes / (ms * 1e-3) / 1e9
+    # the largest launch: fold of round 0 fused with the message of round 1 (read 8 B, write 8 B per element)
+    big = kernels.get("sumcheck_fold_message", (0, 0.0))
+    out = {"metric": "field-elems/s: sumcheck of f*g over 2^%d points, Goldilocks" % nv, "value": d * n / (ms * 1e-3), "unit": UNIT,
+           "ms": ms, "config": {"workload": "sumcheck nv=%d d=2" % nv},
+           "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                        "peak_kind": peak_kind,
+                        "note": "whole proof (%d rounds, host transcript between them) against the %.2f GB its passes must "
+                                "move; the first rounds run at 63-78 %% of the copy peak per launch, the last ones are "
+                                "latency bound" % (nv, alg_bytes / 1e9)},
+           "e2e": {"value": d * n / (ms_e2e * 1e-3), "unit": UNIT, "ms": ms_e2e, "h2d_bytes_per_step": int(polys.nbytes),
+                   "d2h_bytes_per_step": int(rm.nbytes + fe.nbytes)},
+           "kernel_times_ms": {k: {"launches": c, "ms": round(x, 4)} for k, (c, x) in sorted(kernels.items())},
+           "fold_message_launches_ms": big[1]}
+    if not args.no_cpu_baseline:
+        from oracle import pyoracle
+        snv = min(nv, 22)
+        sp = np.concatenate([field_elems(1, 1 << snv), field_elems(2, 1 << snv)])
+        pyoracle.load().oracle_set_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        pyoracle.sumcheck_prove(sp, d, snv, True, LABEL)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": d * (1 << snv) / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                               "sample": "CPU oracle prover (restating cpu_ext2_prover.rs) at 2^%d points, %.2f s" % (snv, dt)}
+    lib.mb_host_free(h_p)
+    return out
+
+
+def int8_peak(agl):
+    """Sustained int8 multiply-accumulate rate of the tensor pipe as this library's own tcgen05 kind::i8 issue loop
+    measures it (resident operands, no operand build); None when the library has no such probe."""
+    fn = getattr(agl, "ajtai_tc_int8_peak_ffi", None)
+    if fn is None:
+        return None
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+    best = 0.0
+    for _ in range(3):
+        v = ctypes.c_double()
+        if fn(4096, ctypes.byref(v)) != 0:
+            return None
+        best = max(best, v.value)
+    return best
+
+
+def part_ajtai(args, local):
+    """The Ajtai ring commit (42 x 64 rows) of 2^18 ring columns = 2^24 coefficients in three signed 8-bit digit
+    planes on the tensor cores, matrix regenerated from the ChaCha8 stream."""
+    from matrix_b200 import load_agl
+    from matrix_b200.ffi import DeviceBuffer
+    agl = load_agl()
+    assert agl.cuda_set_device(local) == 0 and agl.almost_goldilocks_cuda_init() == 0
+    logn, L = min(args.num_vars, 24) - 6, 3
+    n_ring = 1 << logn
+    key = np.arange(1, 9, dtype=np.uint32)
+    dig = np.random.default_rng(5).integers(-127, 128, size=L * n_ring * 64, dtype=np.int8)
+    d_k, d_z = DeviceBuffer.from_numpy(agl, key), DeviceBuffer.from_numpy(agl, dig)
+    d_o = DeviceBuffer(agl, L * 42 * 64 * 8)
+    out = np.zeros(L * 42 * 64, dtype=np.uint64)
+
+    def step():
+        assert agl.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n_ring, L, 0, d_o.ptr) == 0
+
+    def step_e2e():
+        agl.cuda_memcpy_htod(d_z.ptr, dig.ctypes.data, dig.nbytes)
+        step()
+        agl.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
+
+    timed = _event_timer(agl)
+    reps = max(args.steps, 5)
+    for _ in range(3):
+        step()
+    ms = timed(step, reps) / reps
+    step_e2e()
+    ms_e2e = timed(step_e2e, reps) / reps
+    macs = 2688.0 * n_ring * 64 * 8 * L      # 42 x 64 rows, 64 coefficients per column, 8 byte planes of the matrix, L digit planes
+    mac_rate = macs / (ms * 1e-3)
+    peak = int8_peak(agl)
+    res = {"metric": "field-elems/s: Ajtai ring commit (42 x 64 rows), %d signed 8-bit digit planes, almost-Goldilocks" % L,
+           "value": n_ring * 64 / (ms * 1e-3), "unit": UNIT, "ms": ms,
+           "config": {"workload": "ajtai_commit_s8 n_ring=2^%d planes=%d" % (logn, L)},
+           "roofline": {"bound": "tensor", "achieved": mac_rate / 1e12, "peak": peak / 1e12 if peak else None,
+                        "unit": "int8 TMAC/s", "frac": mac_rate / peak if peak else None, "traffic": None,
+                        "peak_kind": "measured in this run by the library's tcgen05 kind::i8 issue loop on resident operands"
+                        if peak else "unmeasured",
+                        "note": "the matrix is regenerated from the ChaCha8 stream in every pass; generation and the "
+                                "operand build bound the kernel before the tensor pipe does"},
+           "e2e": {"value": n_ring * 64 / (ms_e2e * 1e-3), "unit": UNIT, "ms": ms_e2e, "h2d_bytes_per_step": int(dig.nbytes),
+                   "d2h_bytes_per_step": int(out.nbytes)}}
+    if not args.no_cpu_baseline:
+        from oracle import pyoracle
+        cols = 256
+        pyoracle.load().oracle_set_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        pyoracle.ajtai_commit(key, dig[:L * cols * 64], 1, cols, L)
+        dt = time.perf_counter() - t0
+        res["cpu_baseline"] = {"value": cols * 64 / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                               "sample": "CPU oracle (pinned to the reference's cpu_ajtai_commit) on %d ring columns x %d planes, "
+                                         "%.2f s; the cost is linear in the columns" % (cols, L, dt)}
+    return res
+
+
+def run_basefold(args):
+    """The headline. N = 1: one polynomial on one GPU. N > 1: the same single polynomial partitioned over the N
+    GPUs (strong scaling); the figure for N independent provers is reported beside it as `replicas`."""
+    rank, world, local = dist_env()
+    from matrix_b200 import load_gl
+    from matrix_b200.ffi import DeviceBuffer
+    from matrix_b200.inputs import field_elems
+
+    lib = load_gl()  # raises when the CUDA library is missing: there is no CPU path
+    assert lib.basefold_set_merkle_hash(1 if args.hash == "monolith" else 0) == 0
+    if lib.cuda_set_device(local) != 0:
+        raise SystemExit("cuda_set_device(%d) failed" % local)
+
+    dist, exch = None, None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        from matrix_b200.sharded import ProcessExchange
+        torch.cuda.set_device(local)
+        lib.cuda_set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        token = [os.urandom(6).hex() if rank == 0 else None]
+        dist.broadcast_object_list(token, src=0)
+        exch = ProcessExchange(lib, "/mb_basefold_%s" % token[0], rank, world, torch.device("cuda", local))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        lib.cuda_device_synchronize()
+
+    nv, lr, nq = args.num_vars, LOG_RATE, NUM_QUERIES
+    n = 1 << nv
+    evals = field_elems(3, n)            # one polynomial, the same on every rank
+    point = field_elems(4, 2 * nv)
+    table = ctypes.c_void_p()
+    rc = lib.basefold_table_create(nv, lr, nv, 42, ctypes.byref(table))   # key material, untimed
+    assert rc == 0, "basefold_table_create: %d" % rc
+    words = lib.basefold_proof_words(nv, lr, nq)
+    n_loc = n // world
+    shard = np.ascontiguousarray(evals[rank * n_loc:(rank + 1) * n_loc])
+
+    # pinned host staging for the e2e path
+    h_evals_p, h_proof_p = ctypes.c_void_p(), ctypes.c_void_p()
+    assert lib.mb_host_alloc(ctypes.byref(h_evals_p), 8 * n_loc) == 0
+    assert lib.mb_host_alloc(ctypes.byref(h_proof_p), 8 * words) == 0
+    ctypes.memmove(h_evals_p.value, shard.ctypes.data, 8 * n_loc)
+    h_proof = np.ctypeslib.as_array(ctypes.cast(h_proof_p.value, ctypes.POINTER(ctypes.c_uint64)), shape=(words,))
+    root = np.zeros(4, dtype=np.uint64)
+    d_evals = DeviceBuffer.from_numpy(lib, shard)
+
+    if world == 1:
+        def step_resident():
+            c = ctypes.c_void_p()
+            rc = lib.basefold_commit_device(d_evals.ptr, nv, lr, ctypes.byref(c), root.ctypes.data)
+            assert rc == 0, "basefold_commit_device: %d" % rc
+            rc = lib.basefold_open_ext2(c, point.ctypes.data, table, LABEL, len(LABEL), nq, h_proof_p, None)
+            assert rc == 0, "basefold_open_ext2: %d" % rc
+            lib.basefold_commitment_destroy(c)
+
+        def step_e2e():
+            rc = lib.basefold_prove_host(h_evals_p, nv, lr, point.ctypes.data, table, LABEL, len(LABEL), nq,
+                                         root.ctypes.data, h_proof_p)
+            assert rc == 0, "basefold_prove_host: %d" % rc
+    else:
+        def step_resident():
+            rc = lib.basefold_prove_sharded_device(d_evals.ptr, nv, lr, point.ctypes.data, table, LABEL, len(LABEL), nq,
+                                                   exch.handle, root.ctypes.data, h_proof_p)
+            assert rc == 0, "basefold_prove_sharded_device: %d" % rc
+
+        def step_e2e():
+            rc = lib.basefold_prove_sharded_host(h_evals_p, nv, lr, point.ctypes.data, table, LABEL, len(LABEL), nq,
+                                                 exch.handle, root.ctypes.data, h_proof_p)
+            assert rc == 0, "basefold_prove_sharded_host: %d" % rc
+
+    def ev():
+        e = ctypes.c_void_p()
+        assert lib.mb_event_create(ctypes.byref(e)) == 0
+        return e
+
+    def timed(fn, steps, sampler=None):
+        """CUDA events on the library's stream around `steps` calls; returns max-over-ranks ms."""
+        a, b = ev(), ev()
+        barrier()
+        if sampler:
+            sampler.mark_begin()
+        lib.mb_event_record(a)
+        for _ in range(steps):
+            fn()
+        lib.mb_event_record(b)
+        lib.mb_event_sync(b)
+        if sampler:
+            sampler.mark_end()
+        barrier()
+        ms = ctypes.c_float()
+        lib.mb_event_elapsed_ms(a, b, ctypes.byref(ms))
+        val = ms.value
+        if dist is not None:
+            import torch
+            t = torch.tensor([val], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            val = float(t.item())
+        return val
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    lib.mb_prof_enable(0)
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    launches0 = lib.mb_launch_count()
+    ms_total = timed(step_resident, args.steps, sampler)      # clean: no per-kernel events in the timed region
+    launches = lib.mb_launch_count() - launches0
+    clocks = sampler.stop()
+    proof_words_sum = int(h_proof.sum(dtype=np.uint64))     # a checksum of the proof, equal on every N
+
+    # e2e: host buffers in, proof out
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+
+    # per-kernel times: a separate, untimed pass with CUDA events around every launch
+    prof_steps = min(args.steps, 3)
+    lib.mb_prof_reset()
+    lib.mb_prof_enable(1)
+    for _ in range(prof_steps):
+        step_resident()
+    lib.cuda_device_synchronize()
+    lib.mb_prof_enable(0)
+    kernels = prof_report(lib)
+
+    ms_step = ms_total / args.steps
+    value = n * args.steps / (ms_total * 1e-3)
+    e2e_value = n * args.steps / (ms_e2e * 1e-3)
+
+    # Roofline of the dominant kernel by device time. Algorithmic bytes per unit:
+    #   hash_leaves     base pair 16 B in + 32 B digest out (commit tree); extension pair 32 B + 32 B (folded trees)
+    #   compress_layer  64 B in + 32 B out per node
+    # Units per launch come from this rank's share of the work (1 / world of every tree before the gather).
+    peak, peak_kind = measured_peaks()
+    total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
+    dom = max(kernels, key=lambda k: kernels[k][1]) if kernels else None
+    cw_len = 1 << (nv + lr)
+    leaves_commit = ((cw_len // 2) >> lr) // world
+    leaves_folded = sum((cw_len >> (i + 2)) for i in range(nv - 1)) // world
+    nodes_per_step = leaves_commit + sum(max((cw_len >> (i + 2)) - 1, 0) for i in range(nv - 1)) // world
+    roofline = None
+    hash_ms = sum(kernels.get(k, (0, 0))[1] for k in ("hash_leaves", "compress_layer", "tree_tail", "compress_layer_coop",
+                                                       "hash_leaves_coop"))
+    perms_per_s = (leaves_commit + leaves_folded + nodes_per_step) * prof_steps / (hash_ms * 1e-3) if hash_ms else 0.0
+    inst_per_perm = 15550.0 if args.hash == "poseidon2" else 6900.0  # thread instructions per permutation (ncu)
+    sm_hz = 1e6 * (clocks.get("sm_mhz") or 1965.0)
+    if dom is not None:
+        cnt, ms = kernels[dom]
+        if dom == "hash_leaves":
+            total_bytes = (leaves_commit * 48 + leaves_folded * 64) * prof_steps
+        elif dom == "compress_layer":
+            total_bytes = 96 * nodes_per_step * prof_steps
+        else:
+            total_bytes = None
+        if total_bytes is not None:
+            achieved = total_bytes / (ms * 1e-3) / 1e9
+            # DRAM bytes per launch, scaled from an ncu capture of the 2^22 case by the units hashed (reads equal the
+            # algorithmic reads; most digest writes are still in L2 when a kernel ends): 65.06 B per node,
+            # 20.44 B per base leaf pair, extension leaf pairs taken as 32 B read + the same write share.
+            if dom == "compress_layer":
+                traffic = 65.06 * nodes_per_step * prof_steps / cnt
+            else:
+                traffic = (20.44 * leaves_commit + 36.4 * leaves_folded) * prof_steps / cnt
+            roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                        "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                        "traffic_note": "bytes per launch (average), scaled from the ncu capture in profiles/",
+                        "launches": cnt, "avg_launch_ms": ms / cnt, "share_of_kernel_time": ms / total_kernel_ms,
+                        "timed_in": "a separate pass of %d steps with CUDA events around every launch (not the timed region)" % prof_steps,
+                        "note": ("Poseidon2 hashing: ~520 modular multiplications per 32-byte digest, bound by the "
+                                 "integer pipes, not HBM; permutations/s is the meaningful rate") if args.hash == "poseidon2"
+                        else "Monolith hashing: bound by the integer pipes, not HBM; permutations/s is the meaningful rate",
+                        "permutations_per_s": perms_per_s,
+                        # the bound that applies: warp instructions issued against the issue slots of the machine
+                        # (instructions per permutation from the ncu capture in profiles/; 148 SMs x 4 schedulers)
+                        "issue": {"warp_inst_per_permutation": inst_per_perm / 32.0,
+                                  "achieved_warp_inst_per_s": perms_per_s * inst_per_perm / 32.0,
+                                  "peak_warp_inst_per_s": 148 * 4 * sm_hz,
+                                  "frac": perms_per_s * inst_per_perm / 32.0 / (148 * 4 * sm_hz),
+                                  "note": "integer additions, logic and multiply-adds share one 16-lane datapath per "
+                                          "scheduler: 0.57 of the issue slots is the measured ceiling for this mix"}}
+    line = {
+        "metric": METRIC if args.hash == "poseidon2" else METRIC.replace("Poseidon2 Merkle", "Monolith Merkle"),
+        "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
+        "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": basefold_config(nv, args.hash, world),
+        "roofline": roofline,
+        "kernel_times_ms": {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in sorted(kernels.items())},
+        "kernel_times_steps": prof_steps,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": 8 * n_loc + 16 * nv, "d2h_bytes_per_step": 8 * words + 32},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "proof_checksum": proof_words_sum,
+    }
+    if world > 1:
+        line["bounded_by"] = ("per-round fixed cost: %d rounds x (kernel launches, one stream synchronisation, one host gather of 10 "
+                              "words per rank); the hashing itself splits evenly" % (nv - 1))
+        line["exchange"] = {"device_all_to_all_calls": exch.calls, "host_gather": "POSIX shared-memory mailbox"}
+        # N independent provers (what the reference does across devices): every rank proves its own polynomial
+        own = DeviceBuffer.from_numpy(lib, field_elems(3 + rank, n))
+
+        def step_replica():
+            c = ctypes.c_void_p()
+            assert lib.basefold_commit_device(own.ptr, nv, lr, ctypes.byref(c), root.ctypes.data) == 0
+            assert lib.basefold_open_ext2(c, point.ctypes.data, table, LABEL, len(LABEL), nq, h_proof_p, None) == 0
+            lib.basefold_commitment_destroy(c)
+        step_replica()
+        rsteps = min(args.steps, 5)
+        ms_rep = timed(step_replica, rsteps)
+        line["replicas"] = {"value": world * n * rsteps / (ms_rep * 1e-3), "unit": UNIT, "ms_per_step": ms_rep / rsteps,
+                            "scaling": "weak", "note": "one polynomial per rank, no exchange"}
+    if rank == 0 and world == 1:
+        line["parts"] = {"sumcheck": part_sumcheck(lib, args, peak, peak_kind), "ajtai": part_ajtai(args, local)}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        snv = min(args.ref_num_vars, nv)
+        dt, _ = cpu_oracle_sample(snv, merkle_hash=args.hash)
+        line["cpu_baseline"] = {"value": (1 << snv) / dt, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": "CPU oracle commit+open at 2^%d evaluations (%.2f s), OpenMP on all cores; "
+                                          "table generation excluded on both sides; the reference arm (--impl reference) "
+                                          "times the full size" % (snv, dt)}
+    if rank == 0:
+        print(json.dumps(line))
+    lib.basefold_table_destroy(table)
+    if exch is not None:
+        dist.barrier()
+        exch.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -802,190 +1235,7 @@ def main():
         run_reference(args)
         return
 
-    rank, world, local = dist_env()
-    from matrix_b200 import load_gl
-    from matrix_b200.ffi import DeviceBuffer
-    from matrix_b200.inputs import field_elems
-
-    lib = load_gl()  # raises when the CUDA library is missing: there is no CPU path
-    assert lib.basefold_set_merkle_hash(1 if args.hash == "monolith" else 0) == 0
-    if lib.cuda_set_device(local) != 0:
-        raise SystemExit("cuda_set_device(%d) failed" % local)
-
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        lib.cuda_device_synchronize()
-
-    nv, lr, nq = args.num_vars, LOG_RATE, NUM_QUERIES
-    n = 1 << nv
-    evals = field_elems(3 + rank, n)
-    point = field_elems(4, 2 * nv)
-    table = ctypes.c_void_p()
-    rc = lib.basefold_table_create(nv, lr, nv, 42, ctypes.byref(table))
-    assert rc == 0, "basefold_table_create: %d" % rc
-    words = lib.basefold_proof_words(nv, lr, nq)
-
-    # pinned host staging for the e2e path
-    h_evals_p, h_proof_p = ctypes.c_void_p(), ctypes.c_void_p()
-    assert lib.mb_host_alloc(ctypes.byref(h_evals_p), 8 * n) == 0
-    assert lib.mb_host_alloc(ctypes.byref(h_proof_p), 8 * words) == 0
-    ctypes.memmove(h_evals_p.value, evals.ctypes.data, 8 * n)
-    h_proof = np.ctypeslib.as_array(ctypes.cast(h_proof_p.value, ctypes.POINTER(ctypes.c_uint64)), shape=(words,))
-    root = np.zeros(4, dtype=np.uint64)
-    d_evals = DeviceBuffer.from_numpy(lib, evals)
-
-    def step_resident():
-        c = ctypes.c_void_p()
-        rc = lib.basefold_commit_device(d_evals.ptr, nv, lr, ctypes.byref(c), root.ctypes.data)
-        assert rc == 0, "basefold_commit_device: %d" % rc
-        rc = lib.basefold_open_ext2(c, point.ctypes.data, table, LABEL, len(LABEL), nq, h_proof_p, None)
-        assert rc == 0, "basefold_open_ext2: %d" % rc
-        lib.basefold_commitment_destroy(c)
-
-    def step_e2e():
-        rc = lib.basefold_prove_host(h_evals_p, nv, lr, point.ctypes.data, table, LABEL, len(LABEL), nq,
-                                     root.ctypes.data, h_proof_p)
-        assert rc == 0, "basefold_prove_host: %d" % rc
-
-    def ev():
-        e = ctypes.c_void_p()
-        assert lib.mb_event_create(ctypes.byref(e)) == 0
-        return e
-
-    def timed(fn, steps):
-        """CUDA events on the library's stream around `steps` calls; returns max-over-ranks ms."""
-        a, b = ev(), ev()
-        barrier()
-        lib.mb_event_record(a)
-        for _ in range(steps):
-            fn()
-        lib.mb_event_record(b)
-        lib.mb_event_sync(b)
-        barrier()
-        ms = ctypes.c_float()
-        lib.mb_event_elapsed_ms(a, b, ctypes.byref(ms))
-        val = ms.value
-        if dist is not None:
-            import torch
-            t = torch.tensor([val], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            val = float(t.item())
-        return val
-
-    for _ in range(args.warmup):
-        step_resident()
-    sampler = ClockSampler(local)
-    lib.mb_prof_reset()
-    lib.mb_prof_enable(1)
-    launches0 = lib.mb_launch_count()
-    sampler.start()
-    ms_total = timed(step_resident, args.steps)
-    clocks = sampler.stop()
-    launches = lib.mb_launch_count() - launches0
-    lib.mb_prof_enable(0)
-    need = lib.mb_prof_report(None, 0)
-    buf = ctypes.create_string_buffer(need + 16)
-    lib.mb_prof_report(buf, need + 16)
-    kernels = {}
-    for line in buf.value.decode().splitlines():
-        name, cnt, ms = line.split()
-        name = name[len("monolith_"):] if name.startswith("monolith_") else name
-        kernels[name] = (int(cnt), float(ms))
-
-    # e2e: host buffers in, proof out
-    step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
-
-    ms_step = ms_total / args.steps
-    value = world * n * args.steps / (ms_total * 1e-3)
-    e2e_value = world * n * args.steps / (ms_e2e * 1e-3)
-
-    # Roofline of the dominant kernel by device time. Algorithmic bytes per unit:
-    #   hash_leaves     base pair 16 B in + 32 B digest out (commit tree); extension pair 32 B + 32 B (folded trees)
-    #   compress_layer  64 B in + 32 B out per node
-    peak, peak_kind = measured_peaks()
-    total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
-    dom = max(kernels, key=lambda k: kernels[k][1]) if kernels else None
-    cw_len = 1 << (nv + lr)
-    # The commitment tree is periodic (2^lr equal blocks): one block is hashed, the rest is copied.
-    leaves_commit = (cw_len // 2) >> lr
-    leaves_folded = sum((cw_len >> (i + 2)) for i in range(nv - 1))
-    nodes_per_step = leaves_commit + sum(max((cw_len >> (i + 2)) - 1, 0) for i in range(nv - 1))
-    alg_bytes = {"hash_leaves": (leaves_commit * 48 + leaves_folded * 64) * args.steps}
-    roofline = None
-    hash_ms = sum(kernels.get(k, (0, 0))[1] for k in ("hash_leaves", "compress_layer", "tree_tail", "compress_layer_coop",
-                                                       "hash_leaves_coop"))
-    perms_per_s = (leaves_commit + leaves_folded + nodes_per_step) * args.steps / (hash_ms * 1e-3) if hash_ms else 0.0
-    inst_per_perm = 15550.0 if args.hash == "poseidon2" else 6900.0  # thread instructions per permutation (ncu)
-    sm_hz = 1e6 * (clocks.get("sm_mhz") or 1965.0)
-    if dom is not None:
-        cnt, ms = kernels[dom]
-        if dom == "hash_leaves":
-            total_bytes = alg_bytes["hash_leaves"]
-        elif dom == "compress_layer":
-            total_bytes = 96 * nodes_per_step * args.steps
-        else:
-            total_bytes = None
-        if total_bytes is not None:
-            achieved = total_bytes / (ms * 1e-3) / 1e9
-            # DRAM bytes per launch, scaled from an ncu capture of the 2^22 case by the units hashed (reads equal the
-            # algorithmic reads; most digest writes are still in L2 when a kernel ends): 65.06 B per node,
-            # 20.44 B per base leaf pair, extension leaf pairs taken as 32 B read + the same write share.
-            if dom == "compress_layer":
-                traffic = 65.06 * nodes_per_step * args.steps / cnt
-            else:
-                traffic = (20.44 * leaves_commit + 36.4 * leaves_folded) * args.steps / cnt
-            roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                        "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                        "traffic_note": "bytes per launch (average), scaled from the ncu capture in profiles/",
-                        "launches": cnt, "avg_launch_ms": ms / cnt, "share_of_kernel_time": ms / total_kernel_ms,
-                        "note": ("Poseidon2 hashing: ~520 modular multiplications per 32-byte digest, bound by the "
-                                 "integer pipes, not HBM; permutations/s is the meaningful rate") if args.hash == "poseidon2"
-                        else "Monolith hashing: bound by the integer pipes, not HBM; permutations/s is the meaningful rate",
-                        "permutations_per_s": perms_per_s,
-                        # the bound that applies: warp instructions issued against the issue slots of the machine
-                        # (instructions per permutation from the ncu capture in profiles/; 148 SMs x 4 schedulers)
-                        "issue": {"warp_inst_per_permutation": inst_per_perm / 32.0,
-                                  "achieved_warp_inst_per_s": perms_per_s * inst_per_perm / 32.0,
-                                  "peak_warp_inst_per_s": 148 * 4 * sm_hz,
-                                  "frac": perms_per_s * inst_per_perm / 32.0 / (148 * 4 * sm_hz),
-                                  "note": "integer additions, logic and multiply-adds share one 16-lane datapath per "
-                                          "scheduler: 0.57 of the issue slots is the measured ceiling for this mix"}}
-    line = {
-        "metric": METRIC if args.hash == "poseidon2" else METRIC.replace("Poseidon2 Merkle", "Monolith Merkle"),
-        "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
-        "data": "synthetic",
-        "config": {"workload": "basefold_commit_open nv=%d lr=%d queries=%d %s" % (nv, lr, nq, args.hash),
-                   "num_vars": nv, "log_rate": lr, "num_queries": nq, "per_gpu": "one polynomial per rank",
-                   "l2": "inputs larger than L2 (codeword 256 MiB, trees > 1 GiB per step)"},
-        "roofline": roofline,
-        "kernel_times_ms": {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in sorted(kernels.items())},
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": 8 * n + 16 * nv, "d2h_bytes_per_step": 8 * words + 32},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
-    }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cores = os.cpu_count() or 1
-        snv = args.ref_num_vars
-        dt, _ = cpu_oracle_sample(snv, merkle_hash=args.hash)
-        line["cpu_baseline"] = {"value": (1 << snv) / dt, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": "CPU oracle commit+open at 2^%d evaluations (%.2f s), OpenMP on all cores; "
-                                          "table generation excluded on both sides" % (snv, dt)}
-    if rank == 0:
-        print(json.dumps(line))
-    lib.basefold_table_destroy(table)
-    if dist is not None:
-        dist.destroy_process_group()
+    run_basefold(args)
 
 
 if __name__ == "__main__":

@@ -364,3 +364,55 @@ def commit_sharded(commit_columns, comm, n_ring, planes):
     mod q. `commit_columns(lo, hi)` returns this rank's partial commitment as a uint64 array (zeros for an
     empty range). Returns the same array on every process."""
     return _sum_column_shards(commit_columns, comm, n_ring, planes * 42 * 64)
+
+
+# ---- one Basefold proof over several processes ------------------------------------------------------
+class _RawDeviceWords:
+    """A view of `words` 64-bit words of device memory for torch.as_tensor (CUDA array interface, no copy)."""
+
+    def __init__(self, ptr, words):
+        self.__cuda_array_interface__ = {"shape": (int(words),), "typestr": "<i8", "data": (int(ptr), False), "version": 2}
+
+
+class ProcessExchange:
+    """The exchange object of the sharded Basefold prover for one process per GPU on one machine: the host words of
+    every round go through the library's mailbox in POSIX shared memory, the device all-to-all of the commit phase
+    is one torch.distributed all_to_all_single (NCCL) on the caller's process group.
+
+    `name` must be the same on every rank and unused by any other run (e.g. derived from MASTER_PORT); `device` is
+    this rank's torch device. Keep the object alive while the exchange is in use: it owns the callback."""
+
+    A2A = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t)
+
+    def __init__(self, lib, name, rank, world, device, slot_words=1 << 17):
+        import torch
+        import torch.distributed as dist
+        self.lib, self.rank, self.world = lib, rank, world
+        self.calls = 0
+
+        def all_to_all(_ctx, d_send, d_recv, words_per_rank):
+            try:
+                total = words_per_rank * world
+                send = torch.as_tensor(_RawDeviceWords(d_send, total), device=device)
+                recv = torch.as_tensor(_RawDeviceWords(d_recv, total), device=device)
+                dist.all_to_all_single(recv, send)
+                torch.cuda.synchronize(device)
+                self.calls += 1
+                return 0
+            except Exception as exc:  # an exception must not cross the C boundary
+                import sys
+                sys.stderr.write("ProcessExchange.all_to_all failed: %r\n" % (exc,))
+                return -4
+
+        self._cb = self.A2A(all_to_all)
+        h = ctypes.c_void_p()
+        rc = lib.mb_exchange_shm_create(name.encode(), rank, world, slot_words, ctypes.cast(self._cb, ctypes.c_void_p), None,
+                                        ctypes.byref(h))
+        if rc != 0:
+            raise RuntimeError("mb_exchange_shm_create: %d" % rc)
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            self.lib.mb_exchange_destroy(self.handle)
+            self.handle = None
