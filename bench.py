@@ -871,7 +871,7 @@ def part_sumcheck(lib, args, peak, peak_kind):
            "fold_message_launches_ms": big[1]}
     if not args.no_cpu_baseline:
         from oracle import pyoracle
-        snv = min(nv, 22)
+        snv = nv
         sp = np.concatenate([field_elems(1, 1 << snv), field_elems(2, 1 << snv)])
         pyoracle.load().oracle_set_threads(os.cpu_count() or 1)
         t0 = time.perf_counter()
@@ -946,7 +946,7 @@ def part_ajtai(args, local):
                    "d2h_bytes_per_step": int(out.nbytes)}}
     if not args.no_cpu_baseline:
         from oracle import pyoracle
-        cols = 256
+        cols = 8192
         pyoracle.load().oracle_set_threads(os.cpu_count() or 1)
         t0 = time.perf_counter()
         pyoracle.ajtai_commit(key, dig[:L * cols * 64], 1, cols, L)

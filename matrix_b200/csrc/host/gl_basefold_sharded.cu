@@ -31,11 +31,16 @@
 //            When a rank's sumcheck piece is down to 2^TAIL_LOG elements the
 //            pieces are gathered and every rank finishes the remaining rounds on
 //            the whole (small) tables, replicated.
-//   queries  Every rank writes the values and the lower path levels of the
-//            (query, level) pairs whose leaves it hashed, the upper levels come
-//            from the gathered roots, and the buffers are OR-ed together.
+//   queries  Every rank packs the values and the lower path levels of the
+//            (query, level) pairs whose leaves it hashed; one gather moves the
+//            packed pieces (about 1 / G of the query section per rank); the upper
+//            levels come from the gathered roots, the levels after the gather from
+//            the rank's own copies.
 //
 // Exchanges go through mb_exchange (exchange.hpp); no kernel waits on another rank.
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include "gl_basefold_common.cuh"
 #include "exchange.hpp"
 
@@ -93,41 +98,48 @@ struct ShardQuery {
     const uint64_t* ftree[40];
 };
 
-// Block q writes this rank's share of query q into a zeroed buffer.
-__global__ void query_gather_sharded_kernel(ShardQuery sq, const uint64_t* __restrict__ leaf_idx, uint64_t* __restrict__ out,
-                                            size_t qwords) {
+// Block q writes this rank's share of query q. Levels hashed before the gather belong to one rank each: their
+// values and lower path levels (an "item": 4 + 4 * depth words) go to `packed` at the offset the host computed
+// for (query, level) in item_off (entries of other ranks' items are not read). Levels after the gather are held
+// by every rank: they go straight to their place in `out`, laid out like the proof's query section.
+__global__ void query_gather_sharded_kernel(ShardQuery sq, const uint64_t* __restrict__ leaf_idx,
+                                            const uint32_t* __restrict__ item_off, uint64_t* __restrict__ packed,
+                                            uint64_t* __restrict__ out, size_t qwords) {
     const int nv = sq.nv, lr = sq.lr;
+    const int items = sq.switch_round + 1;
     uint64_t* pq = out + (size_t)blockIdx.x * qwords;
     const size_t leaf = (size_t)leaf_idx[blockIdx.x];
-    uint64_t* vals = pq + 1;
-    uint64_t* pp = vals + 4 * nv;
+    const uint32_t* off = item_off + (size_t)blockIdx.x * items;
     if (threadIdx.x == 0) pq[0] = leaf;
     // commitment tree: the block repeats, a leaf belongs to the part that hashed its image in the first block
     {
         const size_t bl = leaf & (((size_t)1 << (nv - 1)) - 1);
         if ((int)(bl / sq.part_leaves) == sq.part) {
+            uint64_t* dst = packed + off[0];
             const size_t in_slice = bl - sq.slice_first_leaf;
             if (threadIdx.x == 0) {
-                vals[0] = sq.slice[2 * in_slice];
-                vals[1] = 0;
-                vals[2] = sq.slice[2 * in_slice + 1];
-                vals[3] = 0;
+                dst[0] = sq.slice[2 * in_slice];
+                dst[1] = 0;
+                dst[2] = sq.slice[2 * in_slice + 1];
+                dst[3] = 0;
             }
-            copy_path(sq.part_tree, sq.part_leaves, bl - (size_t)sq.part * sq.part_leaves, pp);
+            copy_path(sq.part_tree, sq.part_leaves, bl - (size_t)sq.part * sq.part_leaves, dst + 4);
         }
     }
-    pp += 4 * (nv + lr - 1);
+    uint64_t* vals = pq + 1;
+    uint64_t* pp = vals + 4 * nv + 4 * (nv + lr - 1);
     for (int i = 0; i <= nv - 2; i++) {
         const size_t tree_leaves = (size_t)1 << (nv + lr - 2 - i);
         const size_t idx = leaf >> (i + 1);
         if (i < sq.switch_round) {
             const size_t local = tree_leaves >> sq.gamma;
             if ((int)(idx / local) == sq.rank) {
+                uint64_t* dst = packed + off[i + 1];
                 const size_t li = idx - (size_t)sq.rank * local;
-                if (threadIdx.x < 4) vals[4 * (i + 1) + threadIdx.x] = sq.fcw[i][4 * li + threadIdx.x];
-                copy_path(sq.ftree[i], local, li, pp);
+                if (threadIdx.x < 4) dst[threadIdx.x] = sq.fcw[i][4 * li + threadIdx.x];
+                copy_path(sq.ftree[i], local, li, dst + 4);
             }
-        } else if (sq.rank == 0) {
+        } else {
             if (threadIdx.x < 4) vals[4 * (i + 1) + threadIdx.x] = sq.fcw[i][4 * idx + threadIdx.x];
             copy_path(sq.ftree[i], tree_leaves, idx, pp);
         }
@@ -136,6 +148,26 @@ __global__ void query_gather_sharded_kernel(ShardQuery sq, const uint64_t* __res
 }
 
 namespace {
+
+// Host-side stopwatch of the phases of one proof, printed by rank 0 when MB_SHARD_TIMING is set
+// (a line per proof on stderr: milliseconds per phase). Costs a few clock reads otherwise.
+struct PhaseClock {
+    using clk = std::chrono::steady_clock;
+    clk::time_point last = clk::now();
+    double ms[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    void lap(int phase) {
+        auto now = clk::now();
+        ms[phase] += std::chrono::duration<double, std::milli>(now - last).count();
+        last = now;
+    }
+    void report(int rank) const {
+        static const bool on = std::getenv("MB_SHARD_TIMING") != nullptr;
+        if (!on || rank != 0) return;
+        std::fprintf(stderr, "[sharded basefold] pack+all-to-all %.3f  slice transform+part tree %.3f  eq+oracle0 %.3f  "
+                             "rounds before the gather %.3f  gather %.3f  rounds after %.3f  queries %.3f ms\n",
+                     ms[0], ms[1], ms[2], ms[3], ms[4], ms[5], ms[6]);
+    }
+};
 
 struct Digest {
     uint64_t w[4];
@@ -167,20 +199,6 @@ int ilog2(size_t x) {
     int l = 0;
     while (((size_t)1 << l) < x) l++;
     return l;
-}
-
-// D2H of `words`, gather over the ranks, H2D of world * words into d_all (rank-major).
-int gather_device_words(const mb_exchange* ex, const uint64_t* d_piece, size_t words, uint64_t* d_all,
-                        std::vector<uint64_t>& h_mine, std::vector<uint64_t>& h_all) {
-    h_mine.resize(words);
-    h_all.resize(words * (size_t)ex->world);
-    MB_CUDA(cudaMemcpyAsync(h_mine.data(), d_piece, words * sizeof(uint64_t), cudaMemcpyDeviceToHost, MB_STREAM));
-    MB_CUDA(cudaStreamSynchronize(MB_STREAM));
-    int rc = ex->all_gather_host(ex->ctx, h_mine.data(), words, h_all.data());
-    if (rc != MB_OK) return rc;
-    MB_CUDA(cudaMemcpyAsync(d_all, h_all.data(), h_all.size() * sizeof(uint64_t), cudaMemcpyHostToDevice, MB_STREAM));
-    MB_CUDA(cudaStreamSynchronize(MB_STREAM));   // h_all is pageable and reused
-    return MB_OK;
 }
 
 }  // namespace
@@ -216,6 +234,7 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
     uint64_t* h_small = pinned_scratch();
     if (!h_small) return MB_ERR_CUDA;
 
+    PhaseClock pc;
     // ---- commit ---------------------------------------------------------------------------------
     DevBuf send, slice, part_tree;
     int rc = send.alloc(C);
@@ -230,6 +249,7 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
     MB_CUDA(cudaStreamSynchronize(MB_STREAM));
     rc = ex->all_to_all_device(ex->ctx, send.p, slice.p, piece);
     if (rc != MB_OK) return rc;
+    pc.lap(0);
     // the remaining nv - m bits: coefficients in `send`, butterflies in place, reversal into `slice`
     rc = bf::interpolate_async(slice.p, send.p, nullptr, nv - m, MB_STREAM);
     if (rc == MB_OK) rc = bf::encode_async(send.p, send.p, slice.p, nv - m, 0, MB_STREAM);
@@ -263,6 +283,7 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
     uint64_t root[4];
     std::memcpy(root, commit_top.back()[0].w, 32);
     if (h_root) std::memcpy(h_root, root, 32);
+    pc.lap(1);
 
     // ---- open ------------------------------------------------------------------------------------
     t.observe_hash(root);
@@ -326,6 +347,7 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
         p_eval[1] = ev.c1;
     }
     for (int k = 0; k < 3; k++) t.observe_ext2(Ext2{p_oracles[2 * k], p_oracles[2 * k + 1]});
+    pc.lap(2);
 
     // folded codewords and trees: the rank's piece before the switch, whole from the switch on
     std::vector<std::unique_ptr<DevBuf>> fcw(nv), ftree(nv - 1);
@@ -362,17 +384,32 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
     bool distributed = true;
     for (int round = 0; round < nv - 1; round++) {
         if (round == switch_round) {
+            pc.lap(3);
             // gather the sumcheck pieces and the last folded codeword; from here on every rank holds everything
-            rc = gather_device_words(ex, eq_cur, 2 * live, tail_eq[0].p, h_mine, h_all);
-            if (rc == MB_OK) rc = gather_device_words(ex, bh_cur, 2 * live, tail_bh[0].p, h_mine, h_all);
-            if (rc == MB_OK) rc = gather_device_words(ex, fcw[round - 1]->p, 4 * cw_pairs, tail_cw.p, h_mine, h_all);
+            // one message per rank: its eq piece, its bh piece, its piece of the last folded codeword
+            const size_t w_sc = 2 * live, w_cw = 4 * cw_pairs, w_all = 2 * w_sc + w_cw;
+            h_mine.resize(w_all);
+            MB_CUDA(cudaMemcpyAsync(h_mine.data(), eq_cur, w_sc * sizeof(uint64_t), cudaMemcpyDeviceToHost, MB_STREAM));
+            MB_CUDA(cudaMemcpyAsync(h_mine.data() + w_sc, bh_cur, w_sc * sizeof(uint64_t), cudaMemcpyDeviceToHost, MB_STREAM));
+            MB_CUDA(cudaMemcpyAsync(h_mine.data() + 2 * w_sc, fcw[round - 1]->p, w_cw * sizeof(uint64_t), cudaMemcpyDeviceToHost, MB_STREAM));
+            MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+            h_all.resize(w_all * (size_t)G);
+            rc = ex->all_gather_host(ex->ctx, h_mine.data(), w_all, h_all.data());
             if (rc != MB_OK) return rc;
+            for (int q = 0; q < G; q++) {
+                const uint64_t* src = h_all.data() + (size_t)q * w_all;
+                MB_CUDA(cudaMemcpyAsync(tail_eq[0].p + (size_t)q * w_sc, src, w_sc * sizeof(uint64_t), cudaMemcpyHostToDevice, MB_STREAM));
+                MB_CUDA(cudaMemcpyAsync(tail_bh[0].p + (size_t)q * w_sc, src + w_sc, w_sc * sizeof(uint64_t), cudaMemcpyHostToDevice, MB_STREAM));
+                MB_CUDA(cudaMemcpyAsync(tail_cw.p + (size_t)q * w_cw, src + 2 * w_sc, w_cw * sizeof(uint64_t), cudaMemcpyHostToDevice, MB_STREAM));
+            }
+            MB_CUDA(cudaStreamSynchronize(MB_STREAM));   // h_all is pageable and reused later
             eq_cur = tail_eq[0].p; bh_cur = tail_bh[0].p;
             eq_nxt = tail_eq[1].p; bh_nxt = tail_bh[1].p;
             cw_prev = tail_cw.p;
             live <<= gamma;
             cw_pairs <<= gamma;
             distributed = false;
+            pc.lap(4);
         }
         Ext2 ch = t.sample_challenge_ext2();
         gl::E2 r{ch.c0, ch.c1};
@@ -448,18 +485,50 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
         MB_CUDA(cudaMemcpyAsync(p_final, fcw[nv - 1]->p, sizeof(uint64_t) * ((size_t)2 << lr), cudaMemcpyDeviceToHost, MB_STREAM));
     }
 
+    pc.lap(5);
     // ---- queries ------------------------------------------------------------------------------------
     if (num_queries > 0) {
         std::vector<uint64_t> idx(num_queries);
         for (int q = 0; q < num_queries; q++) idx[q] = t.sample_challenge() % (uint64_t)(cw_len / 2);
         const size_t qw = query_words(nv, lr);
         const size_t total = qw * (size_t)num_queries;
-        DevBuf d_idx, d_q;
+        const int items = switch_round + 1;      // per query: the commitment tree and the trees hashed before the gather
+        const int part_depth = ilog2(part_leaves);
+        // every rank lays out every rank's packed buffer the same way: item (q, level) of owner r at offset[r]
+        std::vector<uint32_t> item_off((size_t)num_queries * items), item_owner((size_t)num_queries * items);
+        std::vector<uint32_t> fill(G, 0);
+        auto item_words = [&](int level) {   // level 0: commitment tree; level i + 1: folded tree i
+            if (level == 0) return (uint32_t)(4 + 4 * part_depth);
+            return (uint32_t)(4 + 4 * (nv + lr - 2 - (level - 1) - gamma));
+        };
+        for (int q = 0; q < num_queries; q++) {
+            const size_t leaf = (size_t)idx[q];
+            for (int level = 0; level < items; level++) {
+                int owner;
+                if (level == 0) {
+                    const int pr = (int)((leaf & (((size_t)1 << (nv - 1)) - 1)) / part_leaves);
+                    owner = ((pr & ((1 << lr) - 1)) << m) | (pr >> lr);   // the rank whose part index is pr
+                } else {
+                    const size_t local = ((size_t)1 << (nv + lr - 2 - (level - 1))) >> gamma;
+                    owner = (int)((leaf >> level) / local);
+                }
+                item_owner[(size_t)q * items + level] = (uint32_t)owner;
+                item_off[(size_t)q * items + level] = fill[owner];
+                fill[owner] += item_words(level);
+            }
+        }
+        uint32_t packed_words = 16;
+        for (int r = 0; r < G; r++) packed_words = fill[r] > packed_words ? fill[r] : packed_words;
+        DevBuf d_idx, d_q, d_off, d_packed;
         rc = d_idx.alloc(num_queries);
         if (rc == MB_OK) rc = d_q.alloc(total);
+        if (rc == MB_OK) rc = d_off.alloc((item_off.size() + 1) / 2);
+        if (rc == MB_OK) rc = d_packed.alloc(packed_words);
         if (rc != MB_OK) return rc;
         MB_CUDA(cudaMemcpyAsync(d_idx.p, idx.data(), sizeof(uint64_t) * num_queries, cudaMemcpyHostToDevice, MB_STREAM));
+        MB_CUDA(cudaMemcpyAsync(d_off.p, item_off.data(), sizeof(uint32_t) * item_off.size(), cudaMemcpyHostToDevice, MB_STREAM));
         MB_CUDA(cudaMemsetAsync(d_q.p, 0, sizeof(uint64_t) * total, MB_STREAM));
+        MB_CUDA(cudaMemsetAsync(d_packed.p, 0, sizeof(uint64_t) * packed_words, MB_STREAM));
         ShardQuery sq;
         sq.nv = nv; sq.lr = lr; sq.gamma = gamma; sq.rank = g; sq.world = G; sq.switch_round = switch_round;
         sq.part = part;
@@ -470,51 +539,54 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
         for (int i = 0; i <= nv - 2; i++) { sq.fcw[i] = fcw[i]->p; sq.ftree[i] = ftree[i]->p; }
         {
             MB_KERNEL_ON("query_gather", MB_STREAM);
-            query_gather_sharded_kernel<<<num_queries, 128, 0, MB_STREAM>>>(sq, d_idx.p, d_q.p, qw);
+            query_gather_sharded_kernel<<<num_queries, 128, 0, MB_STREAM>>>(sq, d_idx.p, reinterpret_cast<const uint32_t*>(d_off.p),
+                                                                              d_packed.p, d_q.p, qw);
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        h_mine.resize(total);
-        MB_CUDA(cudaMemcpyAsync(h_mine.data(), d_q.p, sizeof(uint64_t) * total, cudaMemcpyDeviceToHost, MB_STREAM));
+        h_mine.resize(packed_words);
+        MB_CUDA(cudaMemcpyAsync(p_queries, d_q.p, sizeof(uint64_t) * total, cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaMemcpyAsync(h_mine.data(), d_packed.p, sizeof(uint64_t) * packed_words, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
-        // upper path levels from the gathered roots (rank 0 adds them; the OR below spreads them)
-        if (g == 0) {
-            const int part_depth = ilog2(part_leaves);
-            for (int q = 0; q < num_queries; q++) {
-                uint64_t* pq = h_mine.data() + (size_t)q * qw;
-                const size_t leaf = (size_t)idx[q];
-                uint64_t* pp = pq + 1 + 4 * (size_t)nv;
-                const size_t bl = leaf & (((size_t)1 << (nv - 1)) - 1);
-                const size_t pidx = bl / part_leaves;
+        h_all.resize((size_t)packed_words * G);
+        rc = ex->all_gather_host(ex->ctx, h_mine.data(), packed_words, h_all.data());
+        if (rc != MB_OK) return rc;
+        // items from their owners, then the upper path levels from the gathered roots
+        for (int q = 0; q < num_queries; q++) {
+            uint64_t* pq = p_queries + (size_t)q * qw;
+            const size_t leaf = (size_t)idx[q];
+            uint64_t* vals = pq + 1;
+            uint64_t* pp = vals + 4 * (size_t)nv;
+            {
+                const uint64_t* src = h_all.data() + (size_t)item_owner[(size_t)q * items] * packed_words + item_off[(size_t)q * items];
+                std::memcpy(vals, src, 32);
+                std::memcpy(pp, src + 4, 32 * (size_t)part_depth);
+                const size_t pidx = (leaf & (((size_t)1 << (nv - 1)) - 1)) / part_leaves;
                 for (int l = part_depth; l < nv + lr - 1; l++) {
                     const int k = l - part_depth;   // level above the parts
                     const Digest& sib = k < gamma ? commit_top[k][(pidx >> k) ^ 1] : commit_top[k][0];
                     std::memcpy(pp + 4 * (size_t)l, sib.w, 32);
                 }
-                pp += 4 * (size_t)(nv + lr - 1);
-                for (int i = 0; i <= nv - 2; i++) {
-                    const size_t tree_leaves = (size_t)1 << (nv + lr - 2 - i);
-                    if (i < switch_round) {
-                        const size_t local = tree_leaves >> gamma;
-                        const int local_depth = ilog2(local);
-                        const size_t owner = (leaf >> (i + 1)) / local;
-                        for (int k = 0; k < gamma; k++)
-                            std::memcpy(pp + 4 * (size_t)(local_depth + k), ftop[i][k][(owner >> k) ^ 1].w, 32);
-                    }
-                    pp += 4 * (size_t)(nv + lr - 2 - i);
-                }
             }
-        }
-        h_all.resize(total * (size_t)G);
-        rc = ex->all_gather_host(ex->ctx, h_mine.data(), total, h_all.data());
-        if (rc != MB_OK) return rc;
-        for (size_t w = 0; w < total; w++) {
-            uint64_t v = 0;
-            for (int r = 0; r < G; r++) v |= h_all[(size_t)r * total + w];
-            p_queries[w] = v;
+            pp += 4 * (size_t)(nv + lr - 1);
+            for (int i = 0; i <= nv - 2; i++) {
+                if (i < switch_round) {
+                    const size_t it = (size_t)q * items + i + 1;
+                    const uint64_t* src = h_all.data() + (size_t)item_owner[it] * packed_words + item_off[it];
+                    const int local_depth = nv + lr - 2 - i - gamma;
+                    std::memcpy(vals + 4 * (size_t)(i + 1), src, 32);
+                    std::memcpy(pp, src + 4, 32 * (size_t)local_depth);
+                    const size_t owner = item_owner[it];
+                    for (int k = 0; k < gamma; k++)
+                        std::memcpy(pp + 4 * (size_t)(local_depth + k), ftop[i][k][(owner >> k) ^ 1].w, 32);
+                }
+                pp += 4 * (size_t)(nv + lr - 2 - i);
+            }
         }
     } else {
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
     }
+    pc.lap(6);
+    pc.report(g);
     return MB_OK;
 }
 

@@ -194,6 +194,34 @@ tree_tail_coop_kernel(uint64_t* layer, size_t size) {
     }
 }
 
+// Six levels in one launch: block b takes nodes [64 b, 64 b + 64) of `layer` (size nodes, a multiple of 64, at
+// most 4096) and writes its 32, 16, 8, 4, 2, 1 nodes of the six layers above, so that the layer six levels up
+// (size / 64 nodes) is complete when the grid ends. Replaces six launches of the per-layer kernel, each of which
+// costs a launch on top of the latency of one permutation.
+static __global__ void __launch_bounds__(256)
+tree_mid_coop_kernel(uint64_t* layer, size_t size) {
+    const int l = threadIdx.x & 7;
+    const size_t g = threadIdx.x >> 3;   // 32 groups of 8 lanes
+    size_t in_nodes = 64;                // nodes of this block in the current layer
+    size_t layer_size = size;
+    uint64_t* cur = layer;
+#pragma unroll 1
+    for (int t = 0; t < 6; t++) {
+        uint64_t* next = cur + 4 * layer_size;
+        const size_t half = in_nodes / 2;
+        const uint64_t* src = cur + 4 * ((size_t)blockIdx.x * in_nodes);
+        uint64_t* dst = next + 4 * ((size_t)blockIdx.x * half);
+        const bool live = g < half;
+        uint64_t x = live ? src[8 * g + l] : 0;
+        x = gl::poseidon2_permute_coop8(x, l);
+        if (live && l < 4) dst[4 * g + l] = gl::canon(x);
+        __syncthreads();
+        cur = next;
+        layer_size /= 2;
+        in_nodes = half;
+    }
+}
+
 // Full permutation of n width-8 states (poseidon2_hash_batch_ffi).
 static __global__ void __launch_bounds__(BLOCK)
 permute_batch_kernel(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
@@ -248,18 +276,40 @@ inline void launch_tree_tail(uint64_t* layer, size_t size, cudaStream_t st) {
     else tree_tail_kernel<H><<<1, TAIL_NODES / 2, 0, st>>>(layer, size);
 }
 
+// Every layer above `layer` (`size` nodes) up to the root. Layers of more than COOP_NODES nodes take one launch
+// each; with an 8-lane permutation the rest is two launches (six levels per block, then one block to the root).
+template <class H>
+inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st) {
+    if constexpr (H::COOP) {
+        while (size > COOP_NODES) {
+            size_t half = size / 2;
+            launch_compress_layer<H>(layer, layer + 4 * size, half, st);
+            layer += 4 * size;
+            size = half;
+        }
+        if (size > (size_t)TAIL_NODES) {
+            {
+                MB_KERNEL_ON("tree_mid", st);
+                tree_mid_coop_kernel<<<(unsigned)(size / 64), 256, 0, st>>>(layer, size);
+            }
+            layer += 4 * (2 * size - size / 32);   // size + size/2 + ... + size/32 nodes
+            size /= 64;
+        }
+    } else {
+        while (size > (size_t)TAIL_NODES) {
+            size_t half = size / 2;
+            launch_compress_layer<H>(layer, layer + 4 * size, half, st);
+            layer += 4 * size;
+            size = half;
+        }
+    }
+    if (size > 1) launch_tree_tail<H>(layer, size, st);
+}
+
 // Layers above the digests already present in tree[0 .. 4*num_leaves).
 template <class H>
 inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
-    uint64_t* layer = d_tree;
-    size_t size = num_leaves;
-    while (size > TAIL_NODES) {
-        size_t half = size / 2;
-        launch_compress_layer<H>(layer, layer + 4 * size, half, st);
-        layer += 4 * size;
-        size = half;
-    }
-    if (size > 1) launch_tree_tail<H>(layer, size, st);
+    finish_layers<H>(d_tree, num_leaves, st);
     return finish_async();
 }
 
@@ -315,13 +365,7 @@ inline int build_tree_periodic(const uint64_t* d_codeword, uint64_t* d_tree, siz
         size = half;
     }
     // the remaining layers are small: ordinary path on the fully populated layer
-    while (size > TAIL_NODES) {
-        size_t half = size / 2;
-        launch_compress_layer<H>(layer, layer + 4 * size, half, st);
-        layer += 4 * size;
-        size = half;
-    }
-    if (size > 1) launch_tree_tail<H>(layer, size, st);
+    finish_layers<H>(layer, size, st);
     return finish_async();
 }
 
