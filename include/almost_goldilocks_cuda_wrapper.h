@@ -193,6 +193,10 @@ int ajtai_commit_s8_premat_ffi(const uint64_t* d_M, const int8_t* d_digits, uint
 uint64_t ajtai_tc_matrix_bytes(uint64_t N);
 int ajtai_materialize_tc_ffi(const uint32_t* d_key, uint8_t* d_T, uint64_t N, uint64_t col_offset);
 int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int planes, uint64_t* d_out);
+/* Addition (measurement helper, no reference counterpart): sustained int8 multiply-accumulates per second of the
+ * tensor pipes of the current device, from the commit kernel's own tcgen05 kind::i8 issue loop on operands that
+ * stay in shared memory (one CTA per SM, `groups` groups of eight M = 128, N = 256, K = 32 MMAs). */
+int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second);
 
 /* ---- batched same-point sumcheck family (sum_x eq(x) f(x) per leaf, messages at c = 0, 1, 2): ffi.rs:177-195,265-423
  * (wrapper.cu:674-707,851-1060; kernels cuda_almost_goldilocks/almost_sumcheck_prover.cuh:233-1007). Tables are Ext2
@@ -391,6 +395,69 @@ int mb_event_elapsed_ms(void* start, void* stop, float* ms);
 int mb_event_destroy(void* ev);
 int mb_stream_sync(void);
 uint64_t mb_launch_count(void);
+
+
+/* ---- out of scope: stubs ----
+ * Declared by the reference's ffi.rs but outside the prover's field-arithmetic path. Exported so that the
+ * crates link unchanged: every one returns -3 (unsupported) and touches nothing (the two profiler range
+ * markers are no-ops). Parameter lists are those of ffi.rs and are not repeated here. */
+#ifdef __cplusplus
+#define MB_STUB_ARGS ...
+#else
+#define MB_STUB_ARGS
+#endif
+int agl_morpheus_gauss_words(MB_STUB_ARGS);
+int agl_morpheus_gauss_dev(MB_STUB_ARGS);
+int agl_mauth_wtable(MB_STUB_ARGS);
+int agl_mauth_ev(MB_STUB_ARGS);
+int agl_mauth_decode(MB_STUB_ARGS);
+int agl_mauth_combine_multi(MB_STUB_ARGS);
+int agl_mauth_combine(MB_STUB_ARGS);
+int agl_mauth_norm(MB_STUB_ARGS);
+int agl_mauth_pack37(MB_STUB_ARGS);
+int agl_mauth_unpack37(MB_STUB_ARGS);
+int agl_mlink_phase1(MB_STUB_ARGS);
+int agl_mlink_fold(MB_STUB_ARGS);
+int agl_morpheus_coins(MB_STUB_ARGS);
+int agl_mlink2_consts(MB_STUB_ARGS);
+int agl_mlink2_round(MB_STUB_ARGS);
+int agl_mlink2_range_bin1(MB_STUB_ARGS);
+int agl_mlink2_coarse_init(MB_STUB_ARGS);
+int agl_i64_to_i32(MB_STUB_ARGS);
+int agl_add_i32_i64(MB_STUB_ARGS);
+int agl_mlink2_coarse_init2(MB_STUB_ARGS);
+int agl_mlink2_b_build(MB_STUB_ARGS);
+int agl_mlink2_b_halve(MB_STUB_ARGS);
+int agl_mlink2_dense_expand(MB_STUB_ARGS);
+int agl_mlink2_coarse_round(MB_STUB_ARGS);
+int agl_mlink2_coarse_fold(MB_STUB_ARGS);
+int agl_mlink2_onehot3(MB_STUB_ARGS);
+int agl_mlink2_onehot_pre(MB_STUB_ARGS);
+int agl_mlink2_onehot_bin(MB_STUB_ARGS);
+int agl_mlink2_rep_reduce(MB_STUB_ARGS);
+int agl_morpheus_permute(MB_STUB_ARGS);
+int agl_morpheus_unpack2(MB_STUB_ARGS);
+int agl_morpheus_permute2(MB_STUB_ARGS);
+int agl_mauth_ev_packed_batch(MB_STUB_ARGS);
+int agl_mauth_combine_tc(MB_STUB_ARGS);
+int agl_mauth_combine_packed(MB_STUB_ARGS);
+int agl_gauss_low_priority(MB_STUB_ARGS);
+int agl_mlink2_index(MB_STUB_ARGS);
+int agl_morpheus_gauss_scatter(MB_STUB_ARGS);
+void agl_nvtx_push(MB_STUB_ARGS);
+void agl_nvtx_pop(MB_STUB_ARGS);
+int ajtai_tc_commit_probe_ffi(MB_STUB_ARGS);
+int agl_einsum2_ffi(MB_STUB_ARGS);
+int agl_einsum1_ffi(MB_STUB_ARGS);
+int agl_relu_helper_ffi(MB_STUB_ARGS);
+int agl_conv2d_ffi(MB_STUB_ARGS);
+int agl_flatten_kernel2d_ffi(MB_STUB_ARGS);
+int agl_conv3d_ffi(MB_STUB_ARGS);
+int agl_flatten_kernel3d_ffi(MB_STUB_ARGS);
+int agl_depthwise_conv2d_ffi(MB_STUB_ARGS);
+int agl_conv_transpose2d_ffi(MB_STUB_ARGS);
+int agl_conv_transpose3d_ffi(MB_STUB_ARGS);
+int agl_conv_full_ffi(MB_STUB_ARGS);
 
 #ifdef __cplusplus
 }

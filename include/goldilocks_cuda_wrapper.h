@@ -101,7 +101,13 @@ int cuda_get_device_name(int device, char* name, int max_len);
 /* ---- sumcheck, base field: ffi.rs:588-604 (wrapper.cu:1716-1749) ----
  * d tables of `original_size` u64 each, poly-major; `half` = live length / 2.
  * round_message writes num_blocks*(d+1) partial sums, d_partial[block*(d+1)+c];
- * the caller adds the rows. fold writes d_output[i*original_size + y]. */
+ * the caller adds the rows. fold writes d_output[i*original_size + y].
+ * Stricter than the reference in one respect: the tables are read with 128-bit
+ * loads, so d_polys / d_input must be 16-byte aligned and original_size even for
+ * base-field tables (-2 otherwise; the reference accepts any 8-byte-aligned
+ * pointer). Buffers from cuda_malloc are 256-byte aligned; only a sub-slice that
+ * starts at an odd u64 offset is refused. The same holds for the extension-field
+ * and almost-Goldilocks forms below. */
 int sumcheck_round_message_ffi(const uint64_t* d_polys, uint64_t* d_partial, int d, size_t original_size,
                                size_t half, int num_blocks);
 int sumcheck_fold_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge, int d,
@@ -321,7 +327,11 @@ int basefold_prove_sharded_host(const uint64_t* h_evals_shard, int num_vars, int
  * claims: K local shares of the per-instance sums; round_message: local share of
  * m(0..3) (4 extension elements); fold binds the low variable on the challenge;
  * finals (after n_loc folds): eq, alpha^k a_k (K), b_k (K). The caller adds the
- * shards' shares and runs the transcript (matrix_b200/sharded.py). */
+ * shards' shares and runs the transcript (matrix_b200/sharded.py).
+ * Threads: create returns with the handle's tables complete, and a handle may then
+ * be used from any host thread, one call at a time. Work is queued on the calling
+ * thread's stream; claims, round_message and finals wait for it, fold does not, so
+ * pass a handle to another thread only after one of the waiting calls. */
 int gl_batched_state_create(const uint64_t* d_a, const uint64_t* d_b, const uint64_t* h_point_low,
                             const uint64_t* h_eq_scale, int K, int n_loc, void** state);
 int gl_batched_state_destroy(void* state);
@@ -361,6 +371,28 @@ uint64_t mb_launch_count(void);
 int mb_prof_enable(int on);
 int mb_prof_reset(void);
 size_t mb_prof_report(char* buf, size_t cap);
+
+
+/* ---- out of scope: stubs ----
+ * Declared by the reference's ffi.rs but outside the prover's field-arithmetic path. Exported so that the
+ * crates link unchanged: every one returns -3 (unsupported) and touches nothing (the two profiler range
+ * markers are no-ops). Parameter lists are those of ffi.rs and are not repeated here. */
+#ifdef __cplusplus
+#define MB_STUB_ARGS ...
+#else
+#define MB_STUB_ARGS
+#endif
+int gl_einsum2(MB_STUB_ARGS);
+int gl_einsum1(MB_STUB_ARGS);
+int gl_scale_down(MB_STUB_ARGS);
+int gl_scale_up(MB_STUB_ARGS);
+int gl_decompose_bits32(MB_STUB_ARGS);
+int gl_conv2d(MB_STUB_ARGS);
+int gl_flatten_kernel2d(MB_STUB_ARGS);
+int gl_relu_helper(MB_STUB_ARGS);
+int gl_conv3d(MB_STUB_ARGS);
+int gl_flatten_kernel3d(MB_STUB_ARGS);
+int gl_depthwise_conv2d(MB_STUB_ARGS);
 
 #ifdef __cplusplus
 }

@@ -34,6 +34,7 @@ LIBRARIES = {
         "gl_batch.cu",
         "gl_basefold.cu",
         "gl_challenger.cu",
+        "gl_stubs.cu",
         "host/gl_sumcheck_prover.cu",
         "host/gl_basefold_prover.cu",
         "host/gl_basefold_sharded.cu",
@@ -52,6 +53,7 @@ LIBRARIES = {
         "agl_bool.cu",
         "agl_batched.cu",
         "agl_ajtai_fold.cu",
+        "agl_stubs.cu",
         "host/agl_transcript.cu",
         "host/agl_sumcheck_prover.cu",
     ],

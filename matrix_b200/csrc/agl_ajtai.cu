@@ -222,6 +222,43 @@ int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64
     return commit_s8_tc(nullptr, nullptr, d_T, d_digits, N, planes, 0, d_out);
 }
 
+// Addition (measurement helper, no reference counterpart): the sustained int8 multiply-accumulate rate of the
+// tensor pipes of the current device, from the commit kernel's own tcgen05 kind::i8 issue loop on operands that
+// stay in shared memory (one CTA per SM, `groups` groups of eight M = 128, N = 256, K = 32 MMAs each). Writes
+// multiply-accumulates per second. The roofline denominator of the tensor-core commit.
+int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) {
+    if (groups < 1 || groups > (1 << 20) || !mac_per_second) return MB_ERR_ARG;
+    const size_t smem = TC_A_BYTES + 32 * (size_t)TC_SBO;
+    if (cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
+    int* d_err = nullptr;
+    MB_CUDA(pool_alloc((void**)&d_err, sizeof(int)));
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { pool_free(d_err); return MB_ERR_CUDA; }
+    int rc = cudaMemsetAsync(d_err, 0, sizeof(int), MB_STREAM) == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+    const int grid = sm_count();
+    float ms = 0.f;
+    int h_err = 0;
+    if (rc == MB_OK) {
+        int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups / 8 > 0 ? groups / 8 : 1, d_err);   // warm-up
+        cudaEventRecord(a, MB_STREAM);
+        {
+            MB_KERNEL("int8_peak");
+            int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups, d_err);
+        }
+        cudaEventRecord(b, MB_STREAM);
+        if (cudaMemcpyAsync(&h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
+        if (rc == MB_OK) rc = finish_sync();
+        if (rc == MB_OK && cudaEventElapsedTime(&ms, a, b) != cudaSuccess) rc = MB_ERR_CUDA;
+    }
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    pool_free(d_err);
+    if (rc != MB_OK) return rc;
+    if (h_err != 0 || ms <= 0.f) return MB_ERR_CUDA;
+    *mac_per_second = (double)grid * (double)groups * 8.0 * 128.0 * 256.0 * 32.0 / ((double)ms * 1e-3);
+    return MB_OK;
+}
+
 // ---- ternary planes, sparse positions (ffi.rs:352-359,603-625,649-655; wrapper.cu:959-969,1642-1699,1741-1758) ----
 namespace {
 constexpr int SPLIT_K = 13;  // ternary planes per witness (cuda_almost_goldilocks/ajtai.cuh commit_ternary_kernel)

@@ -28,14 +28,27 @@ int scratch_for(int grid, Scratch** out) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MB_ERR_CUDA;
     Scratch& sc = s[dev];
     if (grid > sc.grid_cap) {
-        if (sc.partial) { pool_free(sc.partial); pool_free(sc.sums); }
+        // allocate into temporaries: the thread's scratch changes only when everything succeeded, so a failed
+        // allocation leaves the old (smaller, still valid) buffers or none, never a dangling pointer
         const int cap = sm_count() * 8;
-        sc.grid_cap = grid > cap ? grid : cap;
+        const int want = grid > cap ? grid : cap;
         const size_t row = (size_t)(MAXTAB + 1) * 8;
-        if (pool_alloc((void**)&sc.partial, sizeof(uint64_t) * row * sc.grid_cap) != cudaSuccess) return MB_ERR_CUDA;
-        if (pool_alloc((void**)&sc.sums, sizeof(uint64_t) * (row + 2)) != cudaSuccess) return MB_ERR_CUDA;
-        sc.counter = reinterpret_cast<unsigned int*>(sc.sums + row);
-        if (cudaMemsetAsync(sc.counter, 0, 2 * sizeof(uint64_t), MB_STREAM) != cudaSuccess) return MB_ERR_CUDA;
+        uint64_t *partial = nullptr, *sums = nullptr;
+        if (pool_alloc((void**)&partial, sizeof(uint64_t) * row * want) != cudaSuccess) return MB_ERR_CUDA;
+        if (pool_alloc((void**)&sums, sizeof(uint64_t) * (row + 2)) != cudaSuccess) {
+            pool_free(partial);
+            return MB_ERR_CUDA;
+        }
+        if (cudaMemsetAsync(sums + row, 0, 2 * sizeof(uint64_t), MB_STREAM) != cudaSuccess) {
+            pool_free(partial);
+            pool_free(sums);
+            return MB_ERR_CUDA;
+        }
+        if (sc.partial) { pool_free(sc.partial); pool_free(sc.sums); }
+        sc.partial = partial;
+        sc.sums = sums;
+        sc.counter = reinterpret_cast<unsigned int*>(sums + row);
+        sc.grid_cap = want;
     }
     *out = &sc;
     return MB_OK;

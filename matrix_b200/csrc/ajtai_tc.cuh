@@ -21,11 +21,15 @@
 // (its (s >> 1)-th completion, parity ((s >> 1) - 1) & 1). Every wait is bounded and reports through an error
 // word instead of spinning forever.
 //
-// B (the Toeplitz expansion) is built from the reversed, sign-wrapped digit window w of a (column, plane):
-// row r, K block cq is the 16 bytes of w at byte offset 63 - r + 16 cq. A thread takes one alignment class
-// (offset mod 4) and a run of word offsets, forms each window word with one funnel shift and stores every window
-// to the (row, K block) places that use it; the eight lanes of a quarter warp write the eight rows of one core
-// matrix (128 contiguous bytes per store instruction).
+// B (the Toeplitz expansion) is never written out as 64 x 64 bytes per (column, plane). With the rows taken in
+// reverse (MMA column n = 63 - r) entry (n, k) is w[n + k], w the reversed, sign-wrapped digit window of the
+// (column, plane) (128 bytes), so the 8 x 16 core matrix at row group g and K block c holds rows
+// w[8 (g + 2 c) + i .. + 15], i = 0..7: it depends on g + 2 c only. The operand is therefore stored as 112
+// consecutive 16-byte rows, row o = w[o .. o + 15] (1792 bytes instead of 4096), and addressed with a stride of
+// 128 bytes between row groups and 256 bytes between K blocks, so that the core matrices of the descriptor
+// overlap in shared memory. A thread forms one row with four funnel shifts and one 16-byte store. Planes cannot
+// share one descriptor (their row groups would overlap each other), so every plane is an MMA of N = 64 with its
+// own 64 columns of tensor memory.
 //
 // Where the matrix comes from (TcSource): the ChaCha8 stream; d_M[j][i][k] as 64-bit coefficients (split into
 // byte planes here); or d_T, the byte planes already in operand order: per stage of four columns and row group
@@ -47,6 +51,8 @@ constexpr uint32_t TC_CORE = 128;       // bytes of one 8 x 16 core matrix
 constexpr uint32_t TC_SBO = (TC_STAGE_K / 16) * TC_CORE;  // 2048: next 8-row group
 constexpr uint32_t TC_A_BYTES = 16 * TC_SBO;              // 128 rows
 constexpr int TC_V_STRIDE = 144;        // bytes per reversed digit window (128 + padding, 16-byte multiple)
+constexpr int TC_B_ROWS = 112;          // sliding 16-byte rows of one (column, plane): offsets 0 .. 111
+constexpr uint32_t TC_B_IMAGE = TC_B_ROWS * 16;   // 1792 bytes per (column, plane)
 
 enum TcError { TC_OK = 0, TC_ERR_DIGIT_RANGE = 1, TC_ERR_TIMEOUT = 2 };
 
@@ -95,7 +101,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     constexpr bool PREMAT = SRC == TC_SRC_COEFFS;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int n_cols = 64 * np;
-    const size_t b_bytes = (size_t)(n_cols / 8) * TC_SBO, buf_bytes = TC_A_BYTES + b_bytes;
+    const size_t b_bytes = (size_t)TC_STAGE_COLS * np * TC_B_IMAGE, buf_bytes = TC_A_BYTES + b_bytes;
     uint8_t* V_sh = smem + 2 * buf_bytes;
     __shared__ __align__(8) uint64_t mbar[2];
     __shared__ uint32_t tmem_base_sh;
@@ -126,7 +132,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;");
     const uint32_t tmem = tmem_base_sh;
-    const uint32_t idesc = umma_idesc_i8(n_cols);
+    const uint32_t idesc = umma_idesc_i8(64);   // one plane per MMA
     bool failed = false;
     int bad_digit = 0;
 
@@ -229,30 +235,15 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
         }
         // ---- the next stage's global reads are in flight while this one is built ----
         if (sidx + 1 < n_stages) fetch(js + TC_STAGE_COLS);
-        // ---- B in full: task = (column-plane, two rows i = ipar + 2 (2 mr + d), byte class c); row r = 63 - c - 4 i,
-        // K block cq takes the window at word offset i + 4 cq of class c. The eight lanes of a quarter warp
-        // (c, ipar) write the eight rows of one core matrix: 128 contiguous bytes per store instruction ----
-        for (int x = t; x < TC_STAGE_COLS * np * 32; x += TCP_THREADS) {
-            const int cls = x & 3, ipar = (x >> 2) & 1, mr = (x >> 3) & 3, cp = x >> 5, sh = 8 * cls;
-            const int jj = cp / np, p = cp % np, a0 = ipar + 4 * mr;
-            const uint32_t* W = reinterpret_cast<const uint32_t*>(V_sh + cp * TC_V_STRIDE) + a0;
-            uint32_t F[18];   // funnel-shifted words a0 .. a0 + 17 of the class
-            uint32_t wl = W[0];
-#pragma unroll
-            for (int q = 0; q < 18; q++) {
-                const uint32_t wn = W[q + 1];
-                F[q] = __funnelshift_r(wl, wn, sh);
-                wl = wn;
-            }
-#pragma unroll
-            for (int d = 0; d < 2; d++) {
-                const int r = 63 - cls - 4 * (a0 + 2 * d), n = 64 * p + r;
-                uint8_t* row = B_sh + (n >> 3) * TC_SBO + (4 * jj) * TC_CORE + (n & 7) * 16;
-#pragma unroll
-                for (int cq = 0; cq < 4; cq++)
-                    *reinterpret_cast<uint4*>(row + cq * TC_CORE) =
-                        make_uint4(F[2 * d + 4 * cq], F[2 * d + 4 * cq + 1], F[2 * d + 4 * cq + 2], F[2 * d + 4 * cq + 3]);
-            }
+        // ---- B: the 112 sliding rows of every (column, plane) of the stage; row o = window bytes o .. o + 15 ----
+        for (int x = t; x < TC_STAGE_COLS * np * TC_B_ROWS; x += TCP_THREADS) {
+            const int cp = x / TC_B_ROWS, o = x - cp * TC_B_ROWS;
+            const uint32_t* W = reinterpret_cast<const uint32_t*>(V_sh + cp * TC_V_STRIDE) + (o >> 2);
+            const int sh = 8 * (o & 3);
+            const uint32_t w0 = W[0], w1 = W[1], w2 = W[2], w3 = W[3], w4 = W[4];
+            *reinterpret_cast<uint4*>(B_sh + (size_t)cp * TC_B_IMAGE + 16 * o) =
+                make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                           __funnelshift_r(w3, w4, sh));
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
@@ -260,13 +251,20 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
             asm volatile("tcgen05.fence::after_thread_sync;");
             const uint32_t a_addr = smem_u32(A_sh), b_addr = smem_u32(B_sh);
             // the descriptors advance by adding to their address field (bytes / 16, no carry out of its 14 bits)
-            const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO), db0 = umma_desc(b_addr, TC_CORE, TC_SBO);
+            const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO);
+            // B: K blocks 256 bytes apart, row groups 128 bytes apart (overlapping core matrices, see the header)
+            const uint64_t db0 = umma_desc(b_addr, 2 * TC_CORE, TC_CORE);
 #pragma unroll
             for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
-                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16), db = db0 + (uint64_t)(ks * 2 * TC_CORE / 16);
-                const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
-                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                             ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16);
+                const int jj = ks >> 1, h = ks & 1;   // column of the stage, half of its 64 coefficients
+#pragma unroll
+                for (int p = 0; p < np; p++) {
+                    const uint64_t db = db0 + (uint64_t)(((jj * np + p) * TC_B_IMAGE + h * 4 * TC_CORE) / 16);
+                    const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                                 ::"r"(tmem + (uint32_t)(64 * p)), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+                }
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mbar[buf])) : "memory");
         }
@@ -299,7 +297,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
 #pragma unroll
                 for (int off = 1; off < 8; off <<= 1) f = agl::add(f, __shfl_xor_sync(0xffffffffu, f, off));
                 if (b == 0 && il < TC_ROWS) {
-                    const int n = c0 + e, p = n >> 6, r = n & 63;
+                    const int n = c0 + e, p = n >> 6, r = 63 - (n & 63);   // the rows of B run in reverse
                     partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
                 }
             }
@@ -312,8 +310,70 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
 }
 
+// ---- sustained int8 rate of the tensor pipe, measured with this file's own issue loop -------------------
+// One CTA per SM; the operands (A: 128 rows, B: 256 columns, K = 256 bytes, pseudo-random bytes, ordinary
+// non-overlapping core-matrix layout) stay in shared memory; one thread issues `groups` times eight K = 32 MMAs
+// of M = 128, N = 256 into the same accumulators, committing every group to one of two mbarriers and waiting
+// (bounded) for the group before the last one, so that the pipe always has work queued. No operand is built
+// and nothing is read back: this is the ceiling the commit kernel is compared with.
+static __global__ void __launch_bounds__(128, 1)
+int8_peak_kernel(int groups, int* __restrict__ d_error) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t mbar[2];
+    __shared__ uint32_t tmem_base_sh;
+    const int t = threadIdx.x, warp = t >> 5;
+    const uint32_t b_bytes = 32 * TC_SBO;   // 256 columns
+    for (uint32_t x = t; x < (TC_A_BYTES + b_bytes) / 4; x += blockDim.x) {
+        uint32_t h = x * 2654435761u + blockIdx.x * 40503u;
+        h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+        reinterpret_cast<uint32_t*>(smem)[x] = h;
+    }
+    if (t == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[1])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const uint32_t tmem_cols = 256u;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;");
+    const uint32_t tmem = tmem_base_sh;
+    bool failed = false;
+    if (t == 0) {
+        const uint32_t idesc = umma_idesc_i8(256);
+        const uint64_t da0 = umma_desc(smem_u32(smem), TC_CORE, TC_SBO), db0 = umma_desc(smem_u32(smem + TC_A_BYTES), TC_CORE, TC_SBO);
+        for (int gidx = 0; gidx < groups && !failed; gidx++) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16), db = db0 + (uint64_t)(ks * 2 * TC_CORE / 16);
+                const uint32_t acc = (gidx == 0 && ks == 0) ? 0u : 1u;
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                             ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mbar[gidx & 1])) : "memory");
+            if (gidx >= 1) {
+                const int prev = gidx - 1;
+                if (!mbar_wait(smem_u32(&mbar[prev & 1]), (uint32_t)((prev >> 1) & 1))) failed = true;
+            }
+        }
+        if (!failed && groups > 0) {
+            const int last = groups - 1;
+            if (!mbar_wait(smem_u32(&mbar[last & 1]), (uint32_t)((last >> 1) & 1))) failed = true;
+        }
+        if (failed) atomicMax(d_error, (int)TC_ERR_TIMEOUT);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols));
+}
+
 inline size_t tc_pipe_smem_bytes(int np) {
-    return 2 * (TC_A_BYTES + (size_t)(64 * np / 8) * TC_SBO) + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE;
+    return 2 * (TC_A_BYTES + (size_t)TC_STAGE_COLS * np * TC_B_IMAGE) + TC_STAGE_COLS * TC_MAX_PLANES * TC_V_STRIDE;
 }
 
 // out[p][i][r] = sum over chunks of partial[chunk][group = i / 14][p][i % 14][r]

@@ -62,8 +62,10 @@ public:
         // eq slice scaled by eq(t_top, shard); ab_a_ is free until the first fold and serves as scratch
         int rc = eq::build<GlExt2>(point_dev, eq0_, ab_a_, n_loc, MB_STREAM, scale_dev);
         if (rc != MB_OK) return rc;
-        h_ = pinned_scratch();
-        return h_ ? MB_OK : MB_ERR_CUDA;
+        // the table build and the copies above are complete before the handle is handed out, so that the
+        // first call on it may come from another host thread (whose stream knows nothing of this one)
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        return MB_OK;
     }
 
     // Per-instance round-0 messages m_k(0..3) of this shard, one pass over the caller's tables.
@@ -157,10 +159,12 @@ public:
             return MB_OK;
         }
         if (!have_msg_) return MB_ERR_ARG;
-        MB_CUDA(cudaMemcpyAsync(h_, msg_dev_, 16 * bt::NC, cudaMemcpyDeviceToHost, MB_STREAM));
+        uint64_t* h = pinned_scratch();   // the calling thread's landing zone, not the creating thread's
+        if (!h) return MB_ERR_CUDA;
+        MB_CUDA(cudaMemcpyAsync(h, msg_dev_, 16 * bt::NC, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         gl::E2 m[4];
-        expand_message(h_, round_, m);
+        expand_message(h, round_, m);
         for (int c = 0; c < 4; c++) {
             h_msg[2 * c] = m[c].c0;
             h_msg[2 * c + 1] = m[c].c1;
@@ -248,7 +252,6 @@ private:
     uint64_t *eq0_ = nullptr, *eq_a_ = nullptr, *eq_b_ = nullptr, *ab_a_ = nullptr, *ab_b_ = nullptr;
     uint64_t *partial_ = nullptr, *small_ = nullptr, *msg_dev_ = nullptr, *alpha_dev_ = nullptr, *eq_cur_ = nullptr, *ab_cur_ = nullptr;
     unsigned int* counter_ = nullptr;
-    uint64_t* h_ = nullptr;
 };
 
 }  // namespace mbhost
