@@ -99,11 +99,17 @@ constexpr int TC_PASS_PLANES = TC_MAX_PLANES;   // one MMA covers all planes of 
 template <int SRC, int NP>
 int launch_tc_np(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T, const int8_t* d_digits, uint64_t N, int p0,
                  uint64_t col_offset, uint64_t* partial, int* d_err, uint8_t* materialize, size_t chunks, int chunk_cols) {
-    const size_t smem = tc_pipe_smem_bytes(NP);
-    if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
     dim3 grid((unsigned)chunks, 3);
-    commit_tc_pipe_kernel<SRC, NP><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, materialize,
-                                                                             chunk_cols);
+    if (materialize) {   // the matrix as byte planes in operand order: the builder of the single-phase kernel, no MMAs
+        const size_t smem = tc_pipe_smem_bytes(NP);
+        if (cudaFuncSetAttribute(commit_tc_pipe_kernel<SRC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
+        commit_tc_pipe_kernel<SRC, NP><<<grid, TCP_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err,
+                                                                                 materialize, chunk_cols);
+        return MB_OK;
+    }
+    const size_t smem = tc_ws_smem_bytes(SRC, NP);
+    if (cudaFuncSetAttribute(commit_tc_ws_kernel<SRC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
+    commit_tc_ws_kernel<SRC, NP><<<grid, WS_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, chunk_cols);
     return MB_OK;
 }
 // Columns per CTA: the full 512 when that already gives every SM work, otherwise narrower chunks (a multiple
@@ -224,10 +230,11 @@ int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64
 
 // Addition (measurement helper, no reference counterpart): the sustained int8 multiply-accumulate rate of the
 // tensor pipes of the current device, from the commit kernel's own tcgen05 kind::i8 issue loop on operands that
-// stay in shared memory (one CTA per SM, `groups` groups of eight M = 128, N = 256, K = 32 MMAs each). Writes
-// multiply-accumulates per second. The roofline denominator of the tensor-core commit.
-int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) {
-    if (groups < 1 || groups > (1 << 20) || !mac_per_second) return MB_ERR_ARG;
+// stay in shared memory (one CTA per SM, `groups` groups of eight M = 128, N = n_cols, K = 32 MMAs each). Writes
+// multiply-accumulates per second. N = 256 (ajtai_tc_int8_peak_ffi) is the roofline denominator of the
+// tensor-core commit; smaller N shows what the shape of an MMA costs.
+int ajtai_tc_int8_peak_n_ffi(int groups, int n_cols, double* mac_per_second) {
+    if (groups < 1 || groups > (1 << 20) || !mac_per_second || n_cols < 16 || n_cols > 256 || (n_cols & 15)) return MB_ERR_ARG;
     const size_t smem = TC_A_BYTES + 32 * (size_t)TC_SBO;
     if (cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
     int* d_err = nullptr;
@@ -239,11 +246,11 @@ int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) {
     float ms = 0.f;
     int h_err = 0;
     if (rc == MB_OK) {
-        int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups / 8 > 0 ? groups / 8 : 1, d_err);   // warm-up
+        int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups / 8 > 0 ? groups / 8 : 1, n_cols, d_err);   // warm-up
         cudaEventRecord(a, MB_STREAM);
         {
             MB_KERNEL("int8_peak");
-            int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups, d_err);
+            int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups, n_cols, d_err);
         }
         cudaEventRecord(b, MB_STREAM);
         if (cudaMemcpyAsync(&h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
@@ -255,9 +262,10 @@ int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) {
     pool_free(d_err);
     if (rc != MB_OK) return rc;
     if (h_err != 0 || ms <= 0.f) return MB_ERR_CUDA;
-    *mac_per_second = (double)grid * (double)groups * 8.0 * 128.0 * 256.0 * 32.0 / ((double)ms * 1e-3);
+    *mac_per_second = (double)grid * (double)groups * 8.0 * 128.0 * (double)n_cols * 32.0 / ((double)ms * 1e-3);
     return MB_OK;
 }
+int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) { return ajtai_tc_int8_peak_n_ffi(groups, 256, mac_per_second); }
 
 // ---- ternary planes, sparse positions (ffi.rs:352-359,603-625,649-655; wrapper.cu:959-969,1642-1699,1741-1758) ----
 namespace {

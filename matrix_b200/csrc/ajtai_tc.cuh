@@ -310,6 +310,289 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
     if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
 }
 
+// ---- the commit kernel: builder warps and an issuing warp ------------------------------------------------
+// Fifteen warps build operands, the sixteenth issues MMAs; they meet only at mbarriers, so a builder never
+// waits for the issue of a stage and the issuer never waits for a block-wide barrier.
+// A stage uses buffer b = s mod WS_NB (three buffers: the round trip builder -> issuer -> tensor pipe -> builder
+// is longer than a stage, two buffers left the pipe waiting).
+//   full[b]   (count 15)  every builder warp has finished buffer b of this stage (lane 0 arrives after a
+//                         proxy fence and a warp barrier)
+//   empty[b]  (count 1)   the MMAs that read buffer b have completed (tcgen05.commit)
+//   tma[q]    (tiled)     the 28 KB image of stage s has landed in slot q = s mod WS_A_SLOTS of the A ring
+// Work needs no other synchronisation: a (column, plane) pair's digit window is loaded, reversed and expanded
+// into its rows of B by one warp (pairs w, w + 15 of the stage go to warp w), and every matrix job (one
+// ChaCha8 block or eight coefficients -> one 8 x 8 byte tile of A) belongs to one thread.
+// B is the overlapping sliding-row image described at the top of this file (1792 bytes per pair, one MMA of
+// N = 64 per plane). The other way to lay B out, one MMA over all planes with the two K blocks of an MMA in
+// separate images so that planes can sit 1024 bytes apart, was measured too: it needs 4096 bytes of stores
+// per pair and came out 5 to 10 % slower (2.16 against 1.96 ms for four planes from byte planes in operand
+// order), so what a stage costs is the operand traffic through shared memory, not the number of MMAs issued.
+// The small B leaves room for a deeper ring of A images, which is what the copies from HBM need.
+// TILED: the A image is not touched by threads at all: thread 0 issues one bulk copy per stage into a ring of
+// WS_NB + 1 slots, one stage ahead of the builders (the copy issued at stage s reuses the slot of stage
+// s - WS_NB, whose MMAs the thread has just seen complete); rows 112..127 of the M = 128 operand are whatever follows the slot in shared
+// memory: they only feed accumulator rows that nobody reads.
+// Every wait is bounded; a warp that gives up records TC_ERR_TIMEOUT and leaves the loop, the others then run
+// out of their own waits, and all threads meet at the barrier before the epilogue.
+constexpr int WS_BUILD_WARPS = 15;
+constexpr int WS_THREADS = 512;
+constexpr int WS_NB = 3;                             // operand buffers in flight (a round trip builder -> issuer ->
+                                                     // tensor pipe -> builder takes about two stage times)
+constexpr int WS_A_SLOTS = WS_NB + 1;                // tiled: ring of A images, one more than the buffers
+__host__ __device__ constexpr int ws_a_slots(int) { return WS_A_SLOTS; }
+
+template <int SRC, int NP>
+static __global__ void __launch_bounds__(WS_THREADS, 1)
+commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const uint8_t* __restrict__ d_T,
+                    const int8_t* __restrict__ d_digits, uint64_t N, int p0, uint64_t col_offset, uint64_t* __restrict__ partial,
+                    int* __restrict__ d_error, int chunk_cols) {
+    constexpr int np = NP;
+    constexpr bool TILED = SRC == TC_SRC_TILED, PREMAT = SRC == TC_SRC_COEFFS;
+    constexpr int PAIRS = TC_STAGE_COLS * np;                       // (column, plane) pairs per stage
+    constexpr int PAIRS_PER_WARP = (PAIRS + WS_BUILD_WARPS - 1) / WS_BUILD_WARPS;
+    constexpr uint32_t A_SLOT = TILED ? TCP_A_IMAGE : TC_A_BYTES;
+    constexpr int NB = WS_NB;
+    constexpr int A_SLOTS = TILED ? ws_a_slots(NP) : NB;
+    constexpr int TMA_AHEAD = A_SLOTS - NB;                         // builder stages between a bulk copy and its stage
+    constexpr uint32_t B_BYTES = PAIRS * TC_B_IMAGE;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* A_base = smem;
+    uint8_t* B_base = smem + A_SLOTS * A_SLOT;
+    uint8_t* V_base = B_base + NB * B_BYTES;                         // per builder warp: PAIRS_PER_WARP windows
+    __shared__ __align__(8) uint64_t bar_full[WS_NB], bar_empty[WS_NB], bar_tma[WS_A_SLOTS];
+    __shared__ uint32_t tmem_base_sh;
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int group = blockIdx.y;
+    const int n_cols = 64 * np;
+    const uint64_t j0 = (uint64_t)blockIdx.x * (uint64_t)chunk_cols;
+    const uint64_t j1 = j0 + (uint64_t)chunk_cols < N ? j0 + (uint64_t)chunk_cols : N;
+    const int n_stages = (int)((j1 - j0 + TC_STAGE_COLS - 1) / TC_STAGE_COLS);
+    const uint32_t tmem_cols = 256u;
+
+    if (!TILED) {   // rows 112..127 of the A buffers stay zero
+        for (int b = 0; b < NB; b++)
+            for (int x = t; x < (int)(2 * TC_SBO / 16); x += WS_THREADS)
+                reinterpret_cast<uint4*>(A_base + b * A_SLOT + 14 * TC_SBO)[x] = make_uint4(0, 0, 0, 0);
+    }
+    if (t == 0) {
+        for (int b = 0; b < NB; b++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&bar_full[b])), "r"(WS_BUILD_WARPS));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_empty[b])));
+        }
+        for (int q = 0; q < WS_A_SLOTS; q++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_tma[q])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;");
+    const uint32_t tmem = tmem_base_sh;
+    bool failed = false;
+    int bad_digit = 0;
+
+    auto tma_issue = [&](int stage) {   // one thread: the A image of `stage` into its ring slot
+        const uint32_t bar = smem_u32(&bar_tma[stage % A_SLOTS]);
+        const uint32_t dst = smem_u32(A_base + (stage % A_SLOTS) * A_SLOT);
+        const uint8_t* src = d_T + (((j0 / TC_STAGE_COLS) + (uint64_t)stage) * 3 + (uint64_t)group) * TCP_A_IMAGE;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)TCP_A_IMAGE) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst), "l"(src), "r"((uint32_t)TCP_A_IMAGE), "r"(bar) : "memory");
+    };
+
+    if (warp < WS_BUILD_WARPS) {
+        // ================= builders =================
+        uint32_t key[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) key[k] = SRC == TC_SRC_CHACHA ? d_key[k] : 0u;
+        constexpr int JOBS = TC_STAGE_COLS * TC_ROWS * 8;   // 448 matrix jobs per stage, one per thread
+        uint32_t zreg[PAIRS_PER_WARP];
+        ulonglong2 creg[4];
+        auto fetch = [&](uint64_t js) {
+#pragma unroll
+            for (int q = 0; q < PAIRS_PER_WARP; q++) {
+                const int cp = warp + WS_BUILD_WARPS * q;
+                zreg[q] = 0;
+                if (cp < PAIRS && lane < 16) {
+                    const int jj = cp / np, p = cp % np;
+                    if (js + jj < j1) zreg[q] = *reinterpret_cast<const uint32_t*>(d_digits + ((size_t)(p0 + p) * N + js + jj) * D + 4 * lane);
+                }
+            }
+            if (PREMAT) {
+                const int jj = t / (TC_ROWS * 8), rem = t % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
+                const bool on = t < JOBS && js + jj < j1;
+                const ulonglong2* src = reinterpret_cast<const ulonglong2*>(
+                    d_M + ((js + jj) * (uint64_t)KAPPA + (uint64_t)(group * TC_ROWS + il)) * D + 8 * blk);
+#pragma unroll
+                for (int x = 0; x < 4; x++) creg[x] = on ? __ldcs(src + x) : make_ulonglong2(0, 0);
+            }
+        };
+        if (TILED && t == 0) {
+            for (int st = 0; st < TMA_AHEAD && st < n_stages; st++) tma_issue(st);
+        }
+        if (n_stages > 0) fetch(j0);
+        uint32_t* V_w = reinterpret_cast<uint32_t*>(V_base + warp * (PAIRS_PER_WARP * TC_V_STRIDE));
+        for (int sidx = 0; sidx < n_stages; sidx++) {
+            const uint64_t js = j0 + (uint64_t)sidx * TC_STAGE_COLS;
+            const int buf = sidx % NB, use = sidx / NB;   // buffer and how many times it has been used before
+            uint8_t* A_sh = A_base + buf * A_SLOT;     // not used when TILED
+            uint8_t* B_sh = B_base + buf * B_BYTES;
+            // the MMAs that last read this buffer (stage sidx - NB) must be done before it is rewritten
+            if (sidx >= NB) {
+                uint32_t ok = 1;
+                if (lane == 0) ok = mbar_wait(smem_u32(&bar_empty[buf]), (uint32_t)((use - 1) & 1)) ? 1u : 0u;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { failed = true; break; }
+            }
+            // the copy for stage sidx + TMA_AHEAD reuses the slot of stage sidx - NB, whose MMAs are done
+            if (TILED && t == 0 && sidx + TMA_AHEAD < n_stages) tma_issue(sidx + TMA_AHEAD);
+            // windows of this warp's pairs: word zi of the digits is window word 15 - zi reversed, and word
+            // 31 - zi reversed and negated
+#pragma unroll
+            for (int q = 0; q < PAIRS_PER_WARP; q++) {
+                if (warp + WS_BUILD_WARPS * q < PAIRS && lane < 16) {
+                    const uint32_t z = zreg[q];
+                    if (((z & 0xffu) == 0x80u) | ((z & 0xff00u) == 0x8000u) | ((z & 0xff0000u) == 0x800000u) | ((z >> 24) == 0x80u))
+                        bad_digit = 1;
+                    uint32_t* win = V_w + q * (TC_V_STRIDE / 4);
+                    const uint32_t rev = __byte_perm(z, 0, 0x0123);
+                    win[15 - lane] = rev;
+                    win[31 - lane] = __vneg4(rev);
+                }
+            }
+            __syncwarp();
+            // A: byte planes of this thread's eight coefficients
+            if (!TILED && t < JOBS) {
+                const int jj = t / (TC_ROWS * 8), rem = t % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
+                uint64_t c[8];
+                if (PREMAT) {
+#pragma unroll
+                    for (int x = 0; x < 4; x++) {
+                        c[2 * x] = creg[x].x;
+                        c[2 * x + 1] = creg[x].y;
+                    }
+                } else {
+                    prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
+                }
+                const uint32_t kk = (uint32_t)(jj * D + 8 * blk);
+                uint8_t* dst = A_sh + il * TC_SBO + (kk >> 4) * TC_CORE + (kk & 15);
+                const int rot = (t >> 1) & 3;
+#pragma unroll
+                for (int b = 0; b < 8; b++) {
+                    const int bp = (b & 4) | ((b + rot) & 3);
+                    uint32_t w[8];
+#pragma unroll
+                    for (int x = 0; x < 8; x++) w[x] = b < 4 ? (uint32_t)c[x] : (uint32_t)(c[x] >> 32);
+                    const uint32_t sel = (uint32_t)(bp & 3) | ((4u + (uint32_t)(bp & 3)) << 4);
+                    const uint32_t lo = __byte_perm(__byte_perm(w[0], w[1], sel), __byte_perm(w[2], w[3], sel), 0x5410);
+                    const uint32_t hi = __byte_perm(__byte_perm(w[4], w[5], sel), __byte_perm(w[6], w[7], sel), 0x5410);
+                    *reinterpret_cast<uint2*>(dst + bp * 16) = make_uint2(lo, hi);
+                }
+            }
+            // B: the 112 sliding rows of this warp's pairs (the windows above were written by this warp)
+#pragma unroll
+            for (int q = 0; q < PAIRS_PER_WARP; q++) {
+                const int cp = warp + WS_BUILD_WARPS * q;
+                if (cp < PAIRS) {
+                    const uint32_t* win = V_w + q * (TC_V_STRIDE / 4);
+                    for (int o = lane; o < TC_B_ROWS; o += 32) {
+                        const uint32_t* W = win + (o >> 2);
+                        const int sh = 8 * (o & 3);
+                        const uint32_t w0 = W[0], w1 = W[1], w2 = W[2], w3 = W[3], w4 = W[4];
+                        *reinterpret_cast<uint4*>(B_sh + (size_t)cp * TC_B_IMAGE + 16 * o) =
+                            make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                                       __funnelshift_r(w3, w4, sh));
+                    }
+                }
+            }
+            // next stage's global reads go out before this warp reports the stage
+            if (sidx + 1 < n_stages) fetch(js + TC_STAGE_COLS);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_full[buf])) : "memory");
+        }
+    } else if (lane == 0) {
+        // ================= issuer =================
+        const uint32_t idesc = umma_idesc_i8(64);   // one plane per MMA
+        for (int sidx = 0; sidx < n_stages; sidx++) {
+            const int buf = sidx % NB;
+            if (!mbar_wait(smem_u32(&bar_full[buf]), (uint32_t)((sidx / NB) & 1))) { failed = true; break; }
+            if (TILED && !mbar_wait(smem_u32(&bar_tma[sidx % A_SLOTS]), (uint32_t)((sidx / A_SLOTS) & 1))) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;");
+            const uint32_t a_addr = smem_u32(A_base + (TILED ? (sidx % A_SLOTS) : buf) * A_SLOT);
+            const uint32_t b_addr = smem_u32(B_base + buf * B_BYTES);
+            // the descriptors advance by adding to their address field (bytes / 16, no carry out of its 14 bits)
+            const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO);
+            // B: K blocks 256 bytes apart, row groups 128 bytes apart (overlapping core matrices, see the header)
+            const uint64_t db0 = umma_desc(b_addr, 2 * TC_CORE, TC_CORE);
+#pragma unroll
+            for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
+                const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16);
+                const int jj = ks >> 1, h = ks & 1;   // column of the stage, half of its 64 coefficients
+#pragma unroll
+                for (int p = 0; p < np; p++) {
+                    const uint64_t db = db0 + (uint64_t)(((jj * np + p) * TC_B_IMAGE + h * 4 * TC_CORE) / 16);
+                    const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                                 ::"r"(tmem + (uint32_t)(64 * p)), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+                }
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bar_empty[buf])) : "memory");
+        }
+        // the last commit covers every MMA issued before it
+        if (!failed && n_stages > 0) {
+            const int last = n_stages - 1;
+            if (!mbar_wait(smem_u32(&bar_empty[last % NB]), (uint32_t)((last / NB) & 1))) failed = true;
+        }
+    }
+    if (__syncthreads_or(failed)) failed = true;
+    asm volatile("tcgen05.fence::after_thread_sync;");
+
+    if (!failed && n_stages > 0) {
+        const int q = warp & 3, part = warp >> 2;   // four warps per quarter of the columns
+        const int m = 32 * q + lane, b = m & 7, il = m >> 3;
+        const uint64_t scale = 1ULL << (8 * b);
+        const int c_lo = part * (n_cols / 4), c_hi = c_lo + n_cols / 4;
+        for (int c0 = c_lo; c0 < c_hi; c0 += 8) {
+            uint32_t v[8];
+            const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)c0;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                         : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int32_t sv = (int32_t)v[e];
+                uint64_t f = sv >= 0 ? (uint64_t)sv : agl::P - (uint64_t)(-(int64_t)sv);
+                f = agl::mul(f, scale);
+#pragma unroll
+                for (int off = 1; off < 8; off <<= 1) f = agl::add(f, __shfl_xor_sync(0xffffffffu, f, off));
+                if (b == 0 && il < TC_ROWS) {
+                    const int n = c0 + e, p = n >> 6, r = 63 - (n & 63);   // the rows of B run in reverse
+                    partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols));
+    if (failed && lane == 0) atomicMax(d_error, (int)TC_ERR_TIMEOUT);
+    if (bad_digit) atomicMax(d_error, (int)TC_ERR_DIGIT_RANGE);
+}
+
+inline size_t tc_ws_smem_bytes(int src, int np) {
+    const size_t pairs = (size_t)TC_STAGE_COLS * np;
+    const size_t a = src == TC_SRC_TILED ? (size_t)ws_a_slots(np) * TCP_A_IMAGE : (size_t)WS_NB * TC_A_BYTES;
+    const size_t per_warp = (pairs + WS_BUILD_WARPS - 1) / WS_BUILD_WARPS;
+    // the tiled ring's last slot is read 4 KB past its image (rows 112..127 of the operand): B follows it
+    return a + (size_t)WS_NB * pairs * TC_B_IMAGE + (size_t)WS_BUILD_WARPS * per_warp * TC_V_STRIDE + 4096;
+}
+
 // ---- sustained int8 rate of the tensor pipe, measured with this file's own issue loop -------------------
 // One CTA per SM; the operands (A: 128 rows, B: 256 columns, K = 256 bytes, pseudo-random bytes, ordinary
 // non-overlapping core-matrix layout) stay in shared memory; one thread issues `groups` times eight K = 32 MMAs
@@ -317,7 +600,7 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
 // (bounded) for the group before the last one, so that the pipe always has work queued. No operand is built
 // and nothing is read back: this is the ceiling the commit kernel is compared with.
 static __global__ void __launch_bounds__(128, 1)
-int8_peak_kernel(int groups, int* __restrict__ d_error) {
+int8_peak_kernel(int groups, int n_cols, int* __restrict__ d_error) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t mbar[2];
     __shared__ uint32_t tmem_base_sh;
@@ -345,7 +628,7 @@ int8_peak_kernel(int groups, int* __restrict__ d_error) {
     const uint32_t tmem = tmem_base_sh;
     bool failed = false;
     if (t == 0) {
-        const uint32_t idesc = umma_idesc_i8(256);
+        const uint32_t idesc = umma_idesc_i8(n_cols);
         const uint64_t da0 = umma_desc(smem_u32(smem), TC_CORE, TC_SBO), db0 = umma_desc(smem_u32(smem + TC_A_BYTES), TC_CORE, TC_SBO);
         for (int gidx = 0; gidx < groups && !failed; gidx++) {
 #pragma unroll

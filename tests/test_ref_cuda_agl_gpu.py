@@ -346,9 +346,9 @@ def _link_dense_and_listed(lib, log_half, nc, density, first, chunks):
                         nc, first)]
     wz = np.stack([(w[2 * e * stride:2 * (e * stride + 2 * half)].reshape(2, half, 2) != 0).any(axis=(0, 2)) for e in range(nc)])
     lists = support_lists(wz, extra_seed=2)
-    eq_g = ext(53, max(int(lists[2].sum()), 1))
+    d_eq_g = Buf.of(lib, ext(53, max(int(lists[2].sum()), 1)))     # named: a buffer lives as long as its Python object
     d_l = [Buf.of(lib, a) for a in lists]
-    outs.append(_link_round(lib, lib.link_round_message_sparse_ffi, chunks, nc, d_w.ptr, d_om.ptr, Buf.of(lib, eq_g).ptr, d_tags.ptr,
+    outs.append(_link_round(lib, lib.link_round_message_sparse_ffi, chunks, nc, d_w.ptr, d_om.ptr, d_eq_g.ptr, d_tags.ptr,
                             d_l[0].ptr, d_l[1].ptr, d_l[2].ptr, stride, ostride, half, nc, first))
     r = ext(82, 1)
     assert lib.link_fold_ffi(d_w.ptr, d_om.ptr, stride, ostride, half, nc, int(r[0]), int(r[1])) == 0
@@ -378,7 +378,8 @@ def _link_bits(lib, log_half, nc, density):
     eq_g = np.concatenate([eq.reshape(half, 2)[lists[0][int(o):int(o) + int(n)]] for o, n in zip(lists[1], lists[2])]
                           + [np.zeros((1, 2), dtype=np.uint64)]).reshape(-1)
     d_l = [Buf.of(lib, a) for a in lists]
-    outs.append(_link_round(lib, lib.link_round0_bits_sparse_ffi, 4, nc, d_bits.ptr, d_om.ptr, Buf.of(lib, eq_g).ptr, d_tags.ptr,
+    d_eq_g = Buf.of(lib, eq_g)
+    outs.append(_link_round(lib, lib.link_round0_bits_sparse_ffi, 4, nc, d_bits.ptr, d_om.ptr, d_eq_g.ptr, d_tags.ptr,
                             d_l[0].ptr, d_l[1].ptr, d_l[2].ptr, stride, half, nc))
     r = ext(82, 1)
     d_out = Buf(lib, nc * half * 16)
@@ -436,8 +437,9 @@ def _link_interleaved(lib, first, rnd):
     eq_g = ext(75, max(int(lists[2].sum()), 1))
     d_l = [Buf.of(lib, a) for a in lists]
     d_bits, d_w = Buf.of(lib, words), Buf.of(lib, w)
-    return [_link_round(lib, lib.link_round_interleaved_ffi, 3, nc, d_bits.ptr, d_w.ptr, Buf.of(lib, pts).ptr, Buf.of(lib, scale).ptr,
-                        Buf.of(lib, eq_g).ptr, Buf.of(lib, tags).ptr, d_l[0].ptr, d_l[1].ptr, d_l[2].ptr, w_stride, bits_stride_words,
+    d_pts, d_scale, d_eq_g, d_tags = Buf.of(lib, pts), Buf.of(lib, scale), Buf.of(lib, eq_g), Buf.of(lib, tags)
+    return [_link_round(lib, lib.link_round_interleaved_ffi, 3, nc, d_bits.ptr, d_w.ptr, d_pts.ptr, d_scale.ptr,
+                        d_eq_g.ptr, d_tags.ptr, d_l[0].ptr, d_l[1].ptr, d_l[2].ptr, w_stride, bits_stride_words,
                         half, nc, blocks - 1, block_bits, leaf_arity, rnd, first)]
 
 
@@ -458,12 +460,12 @@ def _link_expansions(lib):
         span *= 2
     outs = [d_t.get(count=2 << nv)]
     lst = np.random.default_rng(1).integers(0, 1 << nv, size=777, dtype=np.uint32)
-    d_o = Buf(lib, len(lst) * 16)
-    assert lib.link_eq_gather_ffi(Buf.of(lib, pt).ptr, nv, Buf.of(lib, lst).ptr, d_o.ptr, len(lst)) == 0
+    d_o, d_pt, d_lst = Buf(lib, len(lst) * 16), Buf.of(lib, pt), Buf.of(lib, lst)
+    assert lib.link_eq_gather_ffi(d_pt.ptr, nv, d_lst.ptr, d_o.ptr, len(lst)) == 0
     outs.append(d_o.get(count=2 * len(lst)))
     span, bases = 300, np.array([0, 1000, 5000], dtype=np.uint64)
-    d_om = Buf.of(lib, ext(91, 6000))
-    assert lib.link_omega_expand_ffi(d_om.ptr, Buf.of(lib, bases).ptr, Buf.of(lib, ext(92, 3)).ptr, span, 3) == 0
+    d_om, d_bases, d_rs = Buf.of(lib, ext(91, 6000)), Buf.of(lib, bases), Buf.of(lib, ext(92, 3))
+    assert lib.link_omega_expand_ffi(d_om.ptr, d_bases.ptr, d_rs.ptr, span, 3) == 0
     outs.append(d_om.get(count=12000))
     return outs
 
