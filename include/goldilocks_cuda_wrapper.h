@@ -312,7 +312,7 @@ int mb_exchange_all_to_all_device(mb_exchange* ex, const uint64_t* d_send, uint6
 /* Rank r passes evaluations [r n / world, (r + 1) n / world) of the polynomial; point, table, label and query count
  * are the same on every rank. h_root and h_proof receive, on every rank, exactly the words basefold_prove_host
  * writes for the whole polynomial. world: a power of two, 2^log_rate <= world <= 16 * 2^log_rate;
- * num_vars >= log2(world) + 9 (-3 otherwise). */
+ * num_vars >= log2(world) + 3 (-3 otherwise). */
 int basefold_prove_sharded_device(const uint64_t* d_evals_shard, int num_vars, int log_rate, const uint64_t* h_point,
                                   const void* table, const uint8_t* label, size_t label_len, int num_queries,
                                   const mb_exchange* ex, uint64_t* h_root, uint64_t* h_proof);

@@ -28,7 +28,7 @@
 //            piece, then one gather of ten words per rank (three partial oracle
 //            coefficients, the root of the rank's subtree of the folded
 //            codeword); the top gamma levels of each tree are hashed on the host.
-//            When a rank's sumcheck piece is down to 2^TAIL_LOG elements the
+//            When a rank's sumcheck piece is down to 2^TAIL_LOG = 4 elements the
 //            pieces are gathered and every rank finishes the remaining rounds on
 //            the whole (small) tables, replicated.
 //   queries  Every rank packs the values and the lower path levels of the
@@ -46,7 +46,11 @@
 
 namespace mbhost {
 
-constexpr int TAIL_LOG = 8;        // sumcheck piece length at which the ranks gather and finish together
+// Sumcheck piece length (log2) at which the ranks gather and finish together. Small on purpose: a round on a
+// rank's piece hashes a subtree that is log2(world) levels shallower than the whole tree (those levels are seven
+// host permutations), and a tree level costs the latency of one permutation on the device whatever its width, so
+// rounds are cheaper before the gather than after it.
+constexpr int TAIL_LOG = 2;
 constexpr int MAX_SLICE_BITS = 4;  // low index bits transformed before the exchange (G <= 16 * 2^lr)
 
 // Low-`m`-bit part of the commitment transform and packing for the all-to-all:
@@ -598,7 +602,7 @@ extern "C" {
 // rank calls this with its own contiguous 1 / world range of the evaluations in device memory (rank r: elements
 // [r n / world, (r + 1) n / world)) and the same point, table, label and query count. h_root and h_proof receive
 // the same words on every rank: exactly those of basefold_prove_host on the whole polynomial. -3 when the shape is
-// not supported (num_vars < log2(world) + 9, or world > 16 * 2^log_rate).
+// not supported (num_vars < log2(world) + 3, or world > 16 * 2^log_rate).
 int basefold_prove_sharded_device(const uint64_t* d_evals_shard, int num_vars, int log_rate, const uint64_t* h_point,
                                   const void* table, const uint8_t* label, size_t label_len, int num_queries,
                                   const mb_exchange* ex, uint64_t* h_root, uint64_t* h_proof) {

@@ -56,7 +56,7 @@ def prove_with_threads(lib, evals, point, nv, lr, nq, h, world):
     return rcs, roots, proofs
 
 
-@pytest.mark.parametrize("nv,lr,nq,world", [(10, 1, 5, 2), (12, 1, 9, 2), (12, 1, 9, 4), (13, 2, 16, 4), (14, 1, 34, 8),
+@pytest.mark.parametrize("nv,lr,nq,world", [(4, 1, 3, 2), (6, 0, 4, 4), (7, 2, 5, 8), (10, 1, 5, 2), (12, 1, 9, 2), (12, 1, 9, 4), (13, 2, 16, 4), (14, 1, 34, 8),
                                             (13, 0, 7, 2), (14, 0, 7, 4), (16, 3, 20, 8), (18, 1, 100, 8), (20, 1, 100, 4)])
 def test_sharded_proof_equals_single_gpu_proof(lib, nv, lr, nq, world):
     evals = field_elems(3, 1 << nv)
@@ -91,12 +91,12 @@ def test_sharded_proof_verifies_under_the_oracle(lib):
 
 
 def test_unsupported_shapes_are_refused(lib):
-    nv, lr = 9, 1
+    nv, lr = 4, 1
     evals, point = field_elems(3, 1 << nv), field_elems(4, 2 * nv)
     h = ctypes.c_void_p()
     assert lib.basefold_table_create(nv, lr, nv, 42, ctypes.byref(h)) == 0
-    rcs, _, _ = prove_with_threads(lib, evals, point, nv, lr, 2, h, 2)     # too few variables for two ranks
-    assert rcs == [-3, -3]
+    rcs, _, _ = prove_with_threads(lib, evals, point, nv, lr, 2, h, 4)     # too few variables for four ranks
+    assert rcs == [-3] * 4
     lib.basefold_table_destroy(h)
     nv, lr = 12, 2
     evals, point = field_elems(3, 1 << nv), field_elems(4, 2 * nv)
