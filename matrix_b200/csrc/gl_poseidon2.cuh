@@ -202,18 +202,35 @@ __device__ __forceinline__ uint64_t poseidon2_permute_coop8(uint64_t x, int lane
         x = sbox7(x);
         x = p2_coop_external(x, w, r < 3 ? g_p2_rc_ext[r + 1][lane8] : (lane8 == 0 ? p2_rc_int(0) : 0));
     }
+    // Internal rounds: x_0 <- sbox(x_0), then x_i <- diag_i x_i + sum_j x_j. What matters here is the length of
+    // the dependent chain, so everything that does not need the S-box output runs beside it: the products
+    // diag_i x_i of the other lanes and the sum of their x_i (a three-step butterfly) are formed from the round's
+    // inputs while the S-box chain (three multiplications deep) is in flight; afterwards lane 0's value is
+    // broadcast, added to the partial sum, and one 128-bit add and reduction finish every lane. All lanes execute
+    // the S-box arithmetic (only lane 0 keeps it), which keeps the warp converged so that the two chains interleave.
+    const bool lane0 = lane8 == 0;
 #pragma unroll 1
     for (int r = 0; r < 22; r++) {
-        if (lane8 == 0) x = sbox7(x);
-        uint64_t SL = lo32(x), SH = hi32(x);
+        const uint64_t t = sbox7(x);
+        // beside the S-box: the other lanes' products and their partial sum
+        uint64_t ylo = x * diag, yhi = umulhi(x, diag);
+        uint64_t UL = lane0 ? 0 : lo32(x), UH = lane0 ? 0 : hi32(x);
 #pragma unroll
         for (int off = 1; off < 8; off <<= 1) {
-            SL += __shfl_xor_sync(0xffffffffu, SL, off, 8);
-            SH += __shfl_xor_sync(0xffffffffu, SH, off, 8);
+            UL += __shfl_xor_sync(0xffffffffu, UL, off, 8);
+            UH += __shfl_xor_sync(0xffffffffu, UH, off, 8);
         }
-        uint64_t sum = reduce_limb_sums(SL, SH);
-        if (lane8 == 0 && r < 21) sum = add_c(sum, p2_rc_int(r + 1));
-        x = mul_add(x, diag, sum);
+        // after the S-box: its output to every lane, the full sum, lane 0's own product
+        const uint32_t tl = __shfl_sync(0xffffffffu, lo32(t), 0, 8), th = __shfl_sync(0xffffffffu, hi32(t), 0, 8);
+        // lane 0's own product needs the S-box output; formed on every lane (no branch) beside the sum
+        const uint64_t zlo = t * diag, zhi = umulhi(t, diag);
+        uint64_t sum = reduce_limb_sums(UL + tl, UH + th);
+        sum = add_c(sum, (lane0 && r < 21) ? p2_rc_int(r + 1) : 0);
+        ylo = lane0 ? zlo : ylo;
+        yhi = lane0 ? zhi : yhi;
+        uint32_t carry;
+        const uint64_t l2 = add_carry(ylo, sum, carry);
+        x = reduce128(l2, yhi + carry);
     }
     x = add_c(x, g_p2_rc_ext[4][lane8]);
 #pragma unroll 1

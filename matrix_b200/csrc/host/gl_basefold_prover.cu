@@ -117,21 +117,22 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
         gl::E2 r{ch.c0, ch.c1};
         size_t quarter = live / 4;
         int g = grid_for(quarter, 256, 4);
+        // the last block of the round kernel writes the finished oracle straight into pinned host memory, the last
+        // block of the tree its root: a round is its launches and one stream synchronisation, no copy command
         if (round == 0) {
             {
                 MB_KERNEL_ON("open_round", MB_STREAM);
                 open_round_kernel<true><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
-                                                                  counter, small.p);
+                                                                  counter, h_small);
             }
         } else {
             {
                 MB_KERNEL_ON("open_round", MB_STREAM);
                 open_round_kernel<false><<<g, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p,
-                                                                   counter, small.p);
+                                                                   counter, h_small);
             }
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        MB_CUDA(cudaMemcpyAsync(h_small, small.p, 48, cudaMemcpyDeviceToHost, MB_STREAM));
         // codeword fold with this round's table level, then its tree
         const uint64_t* level = table.device_level_ptr(round);
         int gf = grid_for(cw_pairs, 256, 8);
@@ -147,10 +148,9 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
             }
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        rc = cm.hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM)
-                     : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM);
+        rc = cm.hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 8)
+                     : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 8);
         if (rc != MB_OK) return rc;
-        MB_CUDA(cudaMemcpyAsync(h_small + 8, ftree[round]->p + 4 * (cw_pairs - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         uint64_t* po = p_oracles + 6 * (size_t)(round + 1);
         std::memcpy(po, h_small, 48);

@@ -422,12 +422,12 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
         {
             MB_KERNEL_ON("open_round", MB_STREAM);
             if (round == 0)
-                open_round_kernel<true><<<gq, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p, counter, small.p);
+                open_round_kernel<true><<<gq, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p, counter, h_small);
             else
-                open_round_kernel<false><<<gq, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p, counter, small.p);
+                open_round_kernel<false><<<gq, 256, 0, MB_STREAM>>>(eq_cur, bh_cur, r, eq_nxt, bh_nxt, quarter, partial.p, counter, h_small);
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        MB_CUDA(cudaMemcpyAsync(h_small, small.p, 48, cudaMemcpyDeviceToHost, MB_STREAM));
+        // (the kernel's last block and the tree's last block write into the pinned landing zone themselves)
         // codeword fold on this rank's pairs with its entries of the round's table level, then the tree
         const uint64_t* level = table.device_level_ptr(round) + (distributed ? 2 * (size_t)g * cw_pairs : 0);
         const int gf = grid_for(cw_pairs, 256, 8);
@@ -439,10 +439,9 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
             bf::fold_ext2_kernel<<<gf, 256, 0, MB_STREAM>>>(cw_prev, level, r, fcw[round]->p, cw_pairs);
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        rc = hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM)
-                  : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM);
+        rc = hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 6)
+                  : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 6);
         if (rc != MB_OK) return rc;
-        MB_CUDA(cudaMemcpyAsync(h_small + 6, ftree[round]->p + 4 * (cw_pairs - 2), 32, cudaMemcpyDeviceToHost, MB_STREAM));
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         uint64_t* po = p_oracles + 6 * (size_t)(round + 1);
         uint64_t* pr = p_roots + 4 * (size_t)round;

@@ -113,7 +113,7 @@ compress_pairs_kernel(const uint64_t* __restrict__ left, const uint64_t* __restr
 // one permutation per thread (hashes without an 8-lane variant).
 template <class H>
 __global__ void __launch_bounds__(TAIL_NODES / 2)
-tree_tail_kernel(uint64_t* layer, size_t size) {
+tree_tail_kernel(uint64_t* layer, size_t size, uint64_t* root_out) {
     while (size > 1) {
         uint64_t* next = layer + 4 * size;
         const size_t half = size / 2;
@@ -122,6 +122,7 @@ tree_tail_kernel(uint64_t* layer, size_t size) {
         layer = next;
         size = half;
     }
+    if (root_out != nullptr && threadIdx.x < 4) root_out[threadIdx.x] = layer[threadIdx.x];
 }
 
 // Full Monolith permutation of n width-12 states, canonical outputs.
@@ -172,49 +173,69 @@ hash_leaves_coop_kernel(const uint64_t* __restrict__ cw, uint64_t* __restrict__ 
 }
 
 // One block (256 threads = 32 permutations at a time) walks every remaining
-// layer above `layer` (of `size` <= 64 nodes) up to the root.
+// layer above `layer` (of `size` <= 64 nodes) up to the root. root_out (may be null) receives a copy of the
+// root: pinned host memory there saves the caller a copy command per tree.
 static __global__ void __launch_bounds__(256)
-tree_tail_coop_kernel(uint64_t* layer, size_t size) {
+tree_tail_coop_kernel(uint64_t* layer, size_t size, uint64_t* root_out) {
+    __shared__ uint64_t node[64 * 4];    // the current layer, kept on chip between levels (also written to the tree)
     const int l = threadIdx.x & 7;
-    const size_t groups = blockDim.x >> 3;
+    const size_t g = threadIdx.x >> 3;   // 32 groups: a layer of at most 64 nodes is one pass
+    if (threadIdx.x < 4 * size) node[threadIdx.x] = layer[threadIdx.x];
+    __syncthreads();
     while (size > 1) {
         uint64_t* next = layer + 4 * size;
         const size_t half = size / 2;
-        const size_t rounds = (half + groups - 1) / groups;
-        size_t k = threadIdx.x >> 3;
-        for (size_t it = 0; it < rounds; it++, k += groups) {
-            const bool live = k < half;
-            uint64_t x = live ? layer[8 * k + l] : 0;
+        const bool live = g < half;
+        uint64_t x = live ? node[8 * g + l] : 0;
+        if (g < ((half + 3) & ~(size_t)3)) {   // only warps with a live group spend issue slots (four groups per warp)
             x = gl::poseidon2_permute_coop8(x, l);
-            if (live && l < 4) next[4 * k + l] = gl::canon(x);
+            x = gl::canon(x);
+        }
+        __syncthreads();
+        if (live && l < 4) {
+            node[4 * g + l] = x;
+            next[4 * g + l] = x;
         }
         __syncthreads();
         layer = next;
         size = half;
     }
+    if (root_out != nullptr && threadIdx.x < 4) root_out[threadIdx.x] = node[threadIdx.x];
 }
 
-// Six levels in one launch: block b takes nodes [64 b, 64 b + 64) of `layer` (size nodes, a multiple of 64, at
-// most 4096) and writes its 32, 16, 8, 4, 2, 1 nodes of the six layers above, so that the layer six levels up
-// (size / 64 nodes) is complete when the grid ends. Replaces six launches of the per-layer kernel, each of which
-// costs a launch on top of the latency of one permutation.
-static __global__ void __launch_bounds__(256)
-tree_mid_coop_kernel(uint64_t* layer, size_t size) {
+// Five levels in one launch: block b (four warps) takes nodes [32 b, 32 b + 32) of `layer` (size nodes, a
+// multiple of 32) and writes its 16, 8, 4, 2, 1 nodes of the five layers above, so that the layer five levels up
+// (size / 32 nodes) is complete when the grid ends. What a small layer costs is not the dependent chain of a
+// permutation but issue slots: eight warps of 8-lane permutations on one SM take about 8 us per level, one warp
+// per scheduler about half of that. So a block holds only 16 permutations (one warp per scheduler) and a layer of
+// 4096 nodes is spread over 128 SMs; the old form (one launch per layer of 256-thread blocks, then one block for
+// the last six levels) cost 136 us for the twelve top levels of every tree, this one about half.
+static __global__ void __launch_bounds__(128)
+tree_up5_coop_kernel(uint64_t* layer, size_t size) {
+    __shared__ uint64_t node[32 * 4];    // this block's nodes of the current layer (also written to the tree)
     const int l = threadIdx.x & 7;
-    const size_t g = threadIdx.x >> 3;   // 32 groups of 8 lanes
-    size_t in_nodes = 64;                // nodes of this block in the current layer
+    const size_t g = threadIdx.x >> 3;   // 16 groups of 8 lanes
+    node[threadIdx.x] = layer[4 * ((size_t)blockIdx.x * 32) + threadIdx.x];
+    __syncthreads();
+    size_t in_nodes = 32;                // nodes of this block in the current layer
     size_t layer_size = size;
     uint64_t* cur = layer;
 #pragma unroll 1
-    for (int t = 0; t < 6; t++) {
+    for (int t = 0; t < 5; t++) {
         uint64_t* next = cur + 4 * layer_size;
         const size_t half = in_nodes / 2;
-        const uint64_t* src = cur + 4 * ((size_t)blockIdx.x * in_nodes);
         uint64_t* dst = next + 4 * ((size_t)blockIdx.x * half);
-        const bool live = g < half;
-        uint64_t x = live ? src[8 * g + l] : 0;
-        x = gl::poseidon2_permute_coop8(x, l);
-        if (live && l < 4) dst[4 * g + l] = gl::canon(x);
+        const bool live = g < half;      // whole warps drop out as the layers shrink
+        uint64_t x = live ? node[8 * g + l] : 0;
+        if (g < ((half + 3) & ~(size_t)3)) {   // warps with a live group (warp-uniform: four groups per warp)
+            x = gl::poseidon2_permute_coop8(x, l);
+            x = gl::canon(x);
+        }
+        __syncthreads();                 // every group has read its pair before the nodes are overwritten
+        if (live && l < 4) {
+            node[4 * g + l] = x;
+            dst[4 * g + l] = x;
+        }
         __syncthreads();
         cur = next;
         layer_size /= 2;
@@ -270,16 +291,17 @@ inline void launch_hash_leaves(const uint64_t* cw, uint64_t* digests, size_t n, 
 }
 
 template <class H>
-inline void launch_tree_tail(uint64_t* layer, size_t size, cudaStream_t st) {
+inline void launch_tree_tail(uint64_t* layer, size_t size, cudaStream_t st, uint64_t* root_out = nullptr) {
     MB_KERNEL_ON("tree_tail", st);
-    if constexpr (H::COOP) tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size);
-    else tree_tail_kernel<H><<<1, TAIL_NODES / 2, 0, st>>>(layer, size);
+    if constexpr (H::COOP) tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size, root_out);
+    else tree_tail_kernel<H><<<1, TAIL_NODES / 2, 0, st>>>(layer, size, root_out);
 }
 
 // Every layer above `layer` (`size` nodes) up to the root. Layers of more than COOP_NODES nodes take one launch
-// each; with an 8-lane permutation the rest is two launches (six levels per block, then one block to the root).
+// each; with an 8-lane permutation the rest goes five levels per launch, then one block for what is left
+// (at most 16 nodes).
 template <class H>
-inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st) {
+inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st, uint64_t* root_out = nullptr) {
     if constexpr (H::COOP) {
         while (size > COOP_NODES) {
             size_t half = size / 2;
@@ -287,13 +309,13 @@ inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st) {
             layer += 4 * size;
             size = half;
         }
-        if (size > (size_t)TAIL_NODES) {
+        while (size >= 64) {   // leaves 2 .. 32 nodes for the last block, which also hands out the root
             {
-                MB_KERNEL_ON("tree_mid", st);
-                tree_mid_coop_kernel<<<(unsigned)(size / 64), 256, 0, st>>>(layer, size);
+                MB_KERNEL_ON("tree_up5", st);
+                tree_up5_coop_kernel<<<(unsigned)(size / 32), 128, 0, st>>>(layer, size);
             }
-            layer += 4 * (2 * size - size / 32);   // size + size/2 + ... + size/32 nodes
-            size /= 64;
+            layer += 4 * (2 * size - size / 16);   // size + size/2 + size/4 + size/8 + size/16 nodes
+            size /= 32;
         }
     } else {
         while (size > (size_t)TAIL_NODES) {
@@ -303,21 +325,24 @@ inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st) {
             size = half;
         }
     }
-    if (size > 1) launch_tree_tail<H>(layer, size, st);
+    if (size > 1) launch_tree_tail<H>(layer, size, st, root_out);
+    else if (root_out != nullptr) cudaMemcpyAsync(root_out, layer, 32, cudaMemcpyDefault, st);   // a single leaf
 }
 
-// Layers above the digests already present in tree[0 .. 4*num_leaves).
+// Layers above the digests already present in tree[0 .. 4*num_leaves). root_out (may be null; device or pinned
+// host memory) receives a copy of the root.
 template <class H>
-inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
-    finish_layers<H>(d_tree, num_leaves, st);
+inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st, uint64_t* root_out = nullptr) {
+    finish_layers<H>(d_tree, num_leaves, st, root_out);
     return finish_async();
 }
 
 template <class H, bool EXT2>
-inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st) {
+inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st,
+                      uint64_t* root_out = nullptr) {
     if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
     launch_hash_leaves<H, EXT2>(d_codeword, d_tree, num_leaves, st);
-    return build_layers<H>(d_tree, num_leaves, st);
+    return build_layers<H>(d_tree, num_leaves, st, root_out);
 }
 
 // dst[c * words + i] = src[i] for c = 1 .. copies-1 (dst = src: in-place replication of a prefix).
