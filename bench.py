@@ -454,7 +454,7 @@ def run_simple(args):
             dist.init_process_group("nccl", device_id=torch.device("cuda", local))
             comm = TorchComm(device=torch.device("cuda", local))
         logn = args.num_vars if args.num_vars != 24 else 18
-        n_ring, L = 1 << logn, 3
+        n_ring, L = 1 << logn, args.planes
         lo, hi = column_range(n_ring, world, rank)
         cols = hi - lo
         key = np.arange(1, 9, dtype=np.uint32)
@@ -468,22 +468,34 @@ def run_simple(args):
             lib.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
             return out
 
+        d_tiled = None
+        if args.matrix == "tiled":
+            # the matrix as byte planes in operand order, built once (key material, untimed); one GPU only
+            assert world == 1, "--matrix tiled runs on one GPU"
+            d_tiled = DeviceBuffer(lib, lib.ajtai_tc_matrix_bytes(n_ring))
+            assert lib.ajtai_materialize_tc_ffi(d_k.ptr, d_tiled.ptr, n_ring, 0) == 0
+
+        def commit_all():
+            if d_tiled is not None:
+                return lib.ajtai_commit_s8_tiled_ffi(d_tiled.ptr, d_z.ptr, n_ring, L, d_o.ptr)
+            return lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n_ring, L, 0, d_o.ptr)
+
         def step():
             if world == 1:
-                return lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n_ring, L, 0, d_o.ptr)
+                return commit_all()
             commit_sharded(local_commit, comm, n_ring, L)
             return 0
 
         def step_e2e():
             lib.cuda_memcpy_htod(d_z.ptr, dig.ctypes.data, dig.nbytes)
             if world == 1:
-                lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n_ring, L, 0, d_o.ptr)
+                commit_all()
                 lib.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
             else:
                 commit_sharded(local_commit, comm, n_ring, L)
         units = n_ring * 64
         metric = "field-elems/s: Ajtai ring commit (42 x 64 rows), %d signed 8-bit digit planes, almost-Goldilocks" % L
-        workload = "ajtai_commit_s8 n_ring=2^%d planes=%d" % (logn, L)
+        workload = "ajtai_commit_s8 n_ring=2^%d planes=%d matrix=%s" % (logn, L, args.matrix)
         alg_bytes = None
         h2d, d2h = dig.nbytes, out.nbytes
         scaling = "strong"
@@ -543,11 +555,16 @@ def run_simple(args):
                             "whole proof (all rounds, host transcript between them) against the bytes its passes must move; "
                             "small tables are latency bound"}
     else:
-        macs = 2688.0 * units * 8 * 3
-        line["roofline"] = {"bound": "tensor", "achieved": 2 * macs * args.steps / (ms * 1e-3) / 1e12, "peak": None,
-                            "unit": "int8 TOP/s", "frac": None, "traffic": None,
-                            "note": "the matrix is regenerated from the ChaCha8 stream in every pass; generation and the "
-                                    "operand build bound the kernel, not the tensor pipe"}
+        macs = 2688.0 * units * 8 * args.planes   # 42 x 64 rows, 8 byte planes of the matrix, digit planes of the witness
+        mac_rate = macs * args.steps / (ms * 1e-3)
+        ipeak = int8_peak(lib) if rank == 0 else None
+        line["roofline"] = {"bound": "tensor", "achieved": mac_rate / 1e12, "peak": ipeak / 1e12 if ipeak else None,
+                            "unit": "int8 TMAC/s", "frac": mac_rate / (ipeak * world) if ipeak else None, "traffic": None,
+                            "peak_kind": "measured in this run by the library's tcgen05 kind::i8 issue loop on resident "
+                                         "operands (per GPU)" if ipeak else "unmeasured",
+                            "note": "matrix byte planes read in operand order from HBM" if args.matrix == "tiled" else
+                                    "the matrix is regenerated from the ChaCha8 stream in every pass; generation and the "
+                                    "operand build bound the kernel before the tensor pipe does"}
     if args.workload == "mcommit" and rank == 0 and not args.no_cpu_baseline:
         # the oracle's schoolbook products (what the reference's CPU test compares with, commit.rs:92-131) on two columns
         from oracle import pyoracle
@@ -1205,6 +1222,10 @@ def main():
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
+    ap.add_argument("--planes", type=int, default=3, help="ajtai workload: signed 8-bit digit planes of the witness")
+    ap.add_argument("--matrix", default="stream", choices=["stream", "tiled"],
+                    help="ajtai workload: regenerate the matrix from the ChaCha8 stream in every pass, or read byte planes "
+                         "in operand order built once")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "shm"],
                     help="batched_sumcheck at N > 1: how the ranks exchange their round messages (48 bytes per rank and "
                          "round): an NCCL all-gather, or a mailbox file in host shared memory (one node)")
