@@ -199,34 +199,48 @@ def run_reference(args):
 
 
 def run_batched(args):
-    """Config 4: K instances of eq*a*b over 2^nv points, combined with powers of alpha, sharded over
-    the top log2(N) variables; one all-gather of 64 bytes per rank and round."""
+    """Config 4: K instances of eq*a*b over 2^nv points, combined with powers of alpha, one proof sharded over
+    the top log2(N) variables (strong scaling). Default driver: the whole round loop inside the library
+    (gl_batched_prove_sharded), the ranks' 64-byte shares of every round polynomial exchanged through the
+    library's mailbox in POSIX shared memory. --exchange nccl / shm keep the Python round loop over an NCCL
+    all-gather or a mailbox file."""
     rank, world, local = dist_env()
     from matrix_b200 import load_gl
     from matrix_b200.ffi import DeviceBuffer
     from matrix_b200.inputs import GL_P, field_elems
-    from matrix_b200.sharded import GpuShard, LibTranscript, SingleComm, TorchComm, prove_sharded
+    from matrix_b200.sharded import (GpuShard, LibTranscript, MailboxExchange, SingleComm, TorchComm, prove_batched_native,
+                                     prove_sharded)
     lib = load_gl()
     assert lib.cuda_set_device(local) == 0
     nv = args.num_vars if args.num_vars != 24 else 26
     K = args.instances
     g_bits = world.bit_length() - 1
     assert world == 1 << g_bits, "the number of ranks must be a power of two"
+    native = args.exchange == "mailbox"
     comm = SingleComm(1)
-    dist = None
+    dist, exch, handle = None, None, None
     if world > 1:
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        comm = TorchComm(device=torch.device("cuda", local))
-        if args.exchange == "shm":
-            from matrix_b200.sharded import ShmComm
-            path = "/dev/shm/matrix_b200_mailbox_%s" % os.environ.get("MASTER_PORT", "0")
-            if rank == 0 and os.path.exists(path):
-                os.remove(path)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))   # timing barrier and max over ranks
+        if native:
+            exch = MailboxExchange(lib, "/mb_batched_%s" % os.environ.get("MASTER_PORT", "0"), rank, world)
+            handle = exch.handle
             dist.barrier()
-            comm = ShmComm(path, rank, world)
+        else:
+            comm = TorchComm(device=torch.device("cuda", local))
+            if args.exchange == "shm":
+                from matrix_b200.sharded import ShmComm
+                path = "/dev/shm/matrix_b200_mailbox_%s" % os.environ.get("MASTER_PORT", "0")
+                if rank == 0 and os.path.exists(path):
+                    os.remove(path)
+                dist.barrier()
+                comm = ShmComm(path, rank, world)
+    elif native:
+        exs = (ctypes.c_void_p * 1)()
+        assert lib.mb_exchange_local_create(1, exs) == 0
+        handle = exs[0]
     n_loc = nv - g_bits
     m = 1 << n_loc
     # this rank's slices, made on the device: instance k, table a / b, entries [rank * m, (rank + 1) * m)
@@ -239,7 +253,9 @@ def run_batched(args):
     pt = field_elems(6, 2 * nv)
     point = [(int(pt[2 * i]), int(pt[2 * i + 1])) for i in range(nv)]
 
-    def step():
+    def step(timing=False):
+        if native:
+            return prove_batched_native(lib, handle, d_a.ptr, d_b.ptr, K, nv, point, LABEL, timing=timing)
         return prove_sharded(lambda g, pl, sc: GpuShard(lib, d_a.ptr, d_b.ptr, pl, sc, K, n_loc),
                              LibTranscript(lib, LABEL), comm, point, K, nv, g_bits)
 
@@ -248,34 +264,42 @@ def run_batched(args):
             dist.barrier()
         lib.cuda_device_synchronize()
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     a, b = ctypes.c_void_p(), ctypes.c_void_p()
     lib.mb_event_create(ctypes.byref(a)); lib.mb_event_create(ctypes.byref(b))
-    sampler = ClockSampler(local)
-    lib.mb_prof_reset(); lib.mb_prof_enable(1)
+    lib.mb_prof_enable(0)
     launches0 = lib.mb_launch_count()
-    sampler.start()
     barrier()
+    sampler.mark_begin()
     lib.mb_event_record(a)
     for _ in range(args.steps):
         proof = step()
     lib.mb_event_record(b); lib.mb_event_sync(b)
+    sampler.mark_end()
     barrier()
-    clocks = sampler.stop()
     ms = ctypes.c_float(); lib.mb_event_elapsed_ms(a, b, ctypes.byref(ms))
     val = ms.value
+    launches = lib.mb_launch_count() - launches0
     if dist is not None:
         import torch
         t = torch.tensor([val], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         val = float(t.item())
-    launches = lib.mb_launch_count() - launches0
+    # per-kernel times and per-round costs: a separate pass, outside the timed region
+    psteps = min(args.steps, 3)
+    os.environ["MB_SHARD_TIMING"] = "1"
+    lib.mb_prof_reset(); lib.mb_prof_enable(1)
+    barrier()
+    for _ in range(psteps):
+        timed_proof = step(timing=True)
+    barrier()
     lib.mb_prof_enable(0)
-    need = lib.mb_prof_report(None, 0)
-    buf = ctypes.create_string_buffer(need + 16)
-    lib.mb_prof_report(buf, need + 16)
-    kernels = {l.split()[0]: (int(l.split()[1]), float(l.split()[2])) for l in buf.value.decode().splitlines()}
+    os.environ.pop("MB_SHARD_TIMING", None)
+    clocks = sampler.stop()
+    kernels = prof_report(lib)
     elems = 2 * K * (1 << nv)  # field elements of the 2K witness tables (eq is derived, not counted)
     peak, peak_kind = measured_peaks()
     # algorithmic bytes of the dominant pass (fold of round 0 fused with message 1): read 8 B, write 8 B per element
@@ -285,24 +309,41 @@ def run_batched(args):
         # per step and rank: round 0 fold reads 2K*m*8 + eq m*16, writes (2K+1)*m/2*16; later rounds halve: read S, write S/2
         first = 2 * K * m * 8 + m * 16 + (2 * K + 1) * (m // 2) * 16
         later = sum((2 * K + 1) * (m >> r) * 16 * 1.5 for r in range(1, n_loc - 1))
-        total_bytes = (first + later) * args.steps
+        total_bytes = (first + later) * psteps
         ach = total_bytes / (kms * 1e-3) / 1e9
         roofline = {"kernel": "batched_fold_message", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
                     "frac": ach / peak, "traffic": None, "peak_kind": peak_kind, "launches": cnt,
-                    "avg_launch_ms": kms / cnt, "note": "per rank; all rounds' fold+message launches together"}
+                    "avg_launch_ms": kms / cnt,
+                    "timed_in": "a separate pass of %d steps with CUDA events around every launch (not the timed region)" % psteps,
+                    "note": "per rank; all rounds' fold+message launches together"}
+    kernel_ms = sum(x for _, x in kernels.values()) / psteps
+    how = {"mailbox": "round loop inside the library; host mailbox in POSIX shared memory",
+           "nccl": "Python round loop; NCCL all-gather", "shm": "Python round loop; mailbox file in /dev/shm"}[args.exchange]
     line = {"metric": "field-elems/s: batched degree-3 sumcheck eq*a*b, %d instances, 2^%d points" % (K, nv),
             "value": elems * args.steps / (val * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": val / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": "batched_sumcheck nv=%d instances=%d" % (nv, K), "sharding": "top %d variables" % g_bits,
-                       "collective": "one all-gather of 48 B per rank and round (%s)" % ("NCCL" if args.exchange == "nccl" else "host shared memory"),
+                       "collective": "one all-gather of 64 B per rank and round (%s)" % how,
                        "l2": "tables larger than L2"},
             "roofline": roofline,
             "kernel_times_ms": {k: {"launches": c, "ms": round(x, 4)} for k, (c, x) in sorted(kernels.items())},
+            "kernel_times_steps": psteps,
+            "per_step": {"kernel_ms": kernel_ms, "other_ms": val / args.steps - kernel_ms,
+                         "note": "other = launches, read-backs, exchange, transcript and the host rounds (rank 0's kernels)"},
             "gpu_launches": int(launches), "clocks": clocks,
             "final_eval": [int(x) for x in proof["final_eval"]]}
+    if native and "round_us" in timed_proof:
+        us = [float(x) for x in timed_proof["round_us"]]
+        line["round_fixed_cost_us"] = {"kernel_wait": us[0], "exchange": us[1], "recombination_and_transcript": us[2],
+                                       "note": "rank 0, microseconds per local round in the per-kernel pass (launch events on)"}
     if rank == 0:
         print(json.dumps(line))
+    if exch is not None:
+        dist.barrier()
+        exch.close()
+    elif native and handle is not None:
+        lib.mb_exchange_destroy(handle)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -1226,9 +1267,10 @@ def main():
     ap.add_argument("--matrix", default="stream", choices=["stream", "tiled"],
                     help="ajtai workload: regenerate the matrix from the ChaCha8 stream in every pass, or read byte planes "
                          "in operand order built once")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "shm"],
-                    help="batched_sumcheck at N > 1: how the ranks exchange their round messages (48 bytes per rank and "
-                         "round): an NCCL all-gather, or a mailbox file in host shared memory (one node)")
+    ap.add_argument("--exchange", default="mailbox", choices=["mailbox", "nccl", "shm"],
+                    help="batched_sumcheck: mailbox = the round loop inside the library with the ranks' 64-byte shares "
+                         "going through its mailbox in POSIX shared memory; nccl / shm = the Python round loop over an NCCL "
+                         "all-gather or a mailbox file in /dev/shm")
     ap.add_argument("--hash", default="poseidon2", choices=["poseidon2", "monolith"],
                     help="Merkle hash of the basefold workload (the transcript is Poseidon2 either way); the headline "
                          "metric names Poseidon2, the reference's default cargo features select Monolith")

@@ -199,6 +199,9 @@ int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64
 int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second);
 /* the same with MMAs of N = n_cols (a multiple of 16 up to 256): what the shape of an MMA costs */
 int ajtai_tc_int8_peak_n_ffi(int groups, int n_cols, double* mac_per_second);
+/* the same with `depth` (1..7) committed groups in flight before the issuing thread waits (the two calls above use
+ * 6): with depth 1 the figure for narrow MMAs is the commit-to-wait round trip, not the pipe */
+int ajtai_tc_int8_peak_shape_ffi(int groups, int n_cols, int depth, double* mac_per_second);
 
 /* ---- batched same-point sumcheck family (sum_x eq(x) f(x) per leaf, messages at c = 0, 1, 2): ffi.rs:177-195,265-423
  * (wrapper.cu:674-707,851-1060; kernels cuda_almost_goldilocks/almost_sumcheck_prover.cuh:233-1007). Tables are Ext2

@@ -340,6 +340,22 @@ int gl_batched_state_set_alpha(void* state, uint64_t c0, uint64_t c1);
 int gl_batched_state_round_message(void* state, uint64_t* h_msg);
 int gl_batched_state_fold(void* state, uint64_t c0, uint64_t c1);
 int gl_batched_state_finals(void* state, uint64_t* h_out);
+/* The whole proof over the shards of an exchange object: round loop, recombination of the ranks' shares mod p,
+ * transcript (labels of zk-torch-4/src/fold/same_point_sumcheck.rs:58-157 as zk-torch-3's transcript absorbs them)
+ * and the last log2(world) rounds on the host, in one call per rank; no counterpart in the reference, whose
+ * sumchecks run on one GPU each. Rank r passes the slices of a_k, b_k whose top log2(world) index bits equal r:
+ * d_a, d_b = [K][2^(num_vars - log2 world)]; h_point = num_vars (c0, c1) pairs, the same on every rank; world = 1
+ * takes an mb_exchange_local_create(1) object. Per local round the ranks gather 8 words each through
+ * all_gather_host; the kernels write their share of the round polynomial straight into pinned host memory. Outputs
+ * (each may be null) are identical on every rank: h_claims [K][2], h_alpha [2], h_round_msgs [num_vars][4][2],
+ * h_challenges [num_vars][2], h_finals [2K + 1][2] (eq, a_k, b_k at the challenge point), h_final_eval [2],
+ * h_transcript_state [8]; h_round_us [3]: with MB_SHARD_TIMING set in the environment, microseconds per local round
+ * spent waiting for the kernel, in the exchange, and in recombination + transcript; -1 otherwise.
+ * -3 when num_vars - log2(world) < 1; -4 when the exchange gives up. */
+int gl_batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const uint64_t* d_b, int K, int num_vars,
+                             const uint64_t* h_point, const uint8_t* label, size_t label_len, uint64_t* h_claims,
+                             uint64_t* h_alpha, uint64_t* h_round_msgs, uint64_t* h_challenges, uint64_t* h_finals,
+                             uint64_t* h_final_eval, uint64_t* h_transcript_state, double* h_round_us);
 
 /* ---- additions: the host transcript (zk-torch-3/src/transcript.rs:174-350) ---- */
 int gl_transcript_create(const uint8_t* label, size_t label_len, void** transcript);

@@ -109,13 +109,21 @@ int launch_tc_np(const uint32_t* d_key, const uint64_t* d_M, const uint8_t* d_T,
     }
     const size_t smem = tc_ws_smem_bytes(SRC, NP);
     if (cudaFuncSetAttribute(commit_tc_ws_kernel<SRC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
-    commit_tc_ws_kernel<SRC, NP><<<grid, WS_THREADS, smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, chunk_cols);
+    commit_tc_ws_kernel<SRC, NP><<<grid, ws_threads(SRC), smem, MB_STREAM>>>(d_key, d_M, d_T, d_digits, N, p0, col_offset, partial, d_err, chunk_cols);
     return MB_OK;
 }
-// Columns per CTA: the full 512 when that already gives every SM work, otherwise narrower chunks (a multiple
-// of the four columns of an MMA stage) so that a short witness is spread over about two CTAs per SM.
+// Columns per CTA (a multiple of the four columns of an MMA stage, at most 512): one CTA runs per SM at a time
+// and a grid has three CTAs per chunk, so the chunk width is chosen to make the grid a whole number of waves:
+// as few waves as 512-column chunks allow (two at least, so that a short witness still spreads over every SM),
+// then the widest chunks that fill them. 2^18 columns: 542 chunks of 484 columns = 1626 CTAs = 10.99 waves of
+// 148 instead of 512 chunks = 10.4 waves, of which the last is two fifths full.
 inline int tc_chunk_cols(uint64_t N) {
-    const uint64_t want_chunks = ((uint64_t)sm_count() * 2 + 2) / 3;
+    const uint64_t sms = (uint64_t)sm_count();
+    const uint64_t min_chunks = (N + TC_CHUNK_COLS - 1) / TC_CHUNK_COLS;
+    uint64_t waves = (3 * min_chunks + sms - 1) / sms;
+    if (waves < 2) waves = 2;
+    uint64_t want_chunks = waves * sms / 3;
+    if (want_chunks < 1) want_chunks = 1;
     uint64_t cols = (N + want_chunks - 1) / want_chunks;
     cols = (cols + TC_STAGE_COLS - 1) / TC_STAGE_COLS * TC_STAGE_COLS;
     if (cols < TC_CHUNK_MIN) cols = TC_CHUNK_MIN;
@@ -233,7 +241,8 @@ int ajtai_commit_s8_tiled_ffi(const uint8_t* d_T, const int8_t* d_digits, uint64
 // stay in shared memory (one CTA per SM, `groups` groups of eight M = 128, N = n_cols, K = 32 MMAs each). Writes
 // multiply-accumulates per second. N = 256 (ajtai_tc_int8_peak_ffi) is the roofline denominator of the
 // tensor-core commit; smaller N shows what the shape of an MMA costs.
-int ajtai_tc_int8_peak_n_ffi(int groups, int n_cols, double* mac_per_second) {
+int ajtai_tc_int8_peak_shape_ffi(int groups, int n_cols, int depth, double* mac_per_second) {
+    if (depth < 1 || depth > PEAK_RING - 1) return MB_ERR_ARG;
     if (groups < 1 || groups > (1 << 20) || !mac_per_second || n_cols < 16 || n_cols > 256 || (n_cols & 15)) return MB_ERR_ARG;
     const size_t smem = TC_A_BYTES + 32 * (size_t)TC_SBO;
     if (cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return MB_ERR_CUDA;
@@ -246,11 +255,11 @@ int ajtai_tc_int8_peak_n_ffi(int groups, int n_cols, double* mac_per_second) {
     float ms = 0.f;
     int h_err = 0;
     if (rc == MB_OK) {
-        int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups / 8 > 0 ? groups / 8 : 1, n_cols, d_err);   // warm-up
+        int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups / 8 > 0 ? groups / 8 : 1, n_cols, depth, d_err);   // warm-up
         cudaEventRecord(a, MB_STREAM);
         {
             MB_KERNEL("int8_peak");
-            int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups, n_cols, d_err);
+            int8_peak_kernel<<<grid, 128, smem, MB_STREAM>>>(groups, n_cols, depth, d_err);
         }
         cudaEventRecord(b, MB_STREAM);
         if (cudaMemcpyAsync(&h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, MB_STREAM) != cudaSuccess) rc = MB_ERR_CUDA;
@@ -265,7 +274,8 @@ int ajtai_tc_int8_peak_n_ffi(int groups, int n_cols, double* mac_per_second) {
     *mac_per_second = (double)grid * (double)groups * 8.0 * 128.0 * (double)n_cols * 32.0 / ((double)ms * 1e-3);
     return MB_OK;
 }
-int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) { return ajtai_tc_int8_peak_n_ffi(groups, 256, mac_per_second); }
+int ajtai_tc_int8_peak_n_ffi(int groups, int n_cols, double* mac_per_second) { return ajtai_tc_int8_peak_shape_ffi(groups, n_cols, 6, mac_per_second); }
+int ajtai_tc_int8_peak_ffi(int groups, double* mac_per_second) { return ajtai_tc_int8_peak_shape_ffi(groups, 256, 6, mac_per_second); }
 
 // ---- ternary planes, sparse positions (ffi.rs:352-359,603-625,649-655; wrapper.cu:959-969,1642-1699,1741-1758) ----
 namespace {

@@ -46,6 +46,48 @@ __device__ __forceinline__ void chacha8_block(const uint32_t (&key)[8], uint32_t
     for (int i = 0; i < 16; i++) out[i] = x[i] + s[i];
 }
 
+// The first column round touches the nonce words one column at a time: columns 0, 1 and 3 of the state see only
+// the constants, the key, the block counter, the row and the high word of the column index. A thread that
+// generates the same (row, counter) for a run of matrix columns computes those three quarter rounds once.
+struct ChaChaColumns {
+    uint32_t q[12];     // state words (0, 4, 8, 12), (1, 5, 9, 13), (3, 7, 11, 15) after the first column round
+    uint32_t n2;        // the high word of the column index they were made for
+};
+__device__ __forceinline__ void chacha8_columns(const uint32_t (&key)[8], uint32_t counter, uint32_t n0, uint32_t n2,
+                                                ChaChaColumns& pre) {
+    uint32_t a0 = 0x61707865u, b0 = key[0], c0 = key[4], d0 = counter;
+    uint32_t a1 = 0x3320646eu, b1 = key[1], c1 = key[5], d1 = n0;
+    uint32_t a3 = 0x6b206574u, b3 = key[3], c3 = key[7], d3 = n2;
+    MB_AJ_QR(a0, b0, c0, d0) MB_AJ_QR(a1, b1, c1, d1) MB_AJ_QR(a3, b3, c3, d3)
+    pre.q[0] = a0; pre.q[1] = b0; pre.q[2] = c0; pre.q[3] = d0;
+    pre.q[4] = a1; pre.q[5] = b1; pre.q[6] = c1; pre.q[7] = d1;
+    pre.q[8] = a3; pre.q[9] = b3; pre.q[10] = c3; pre.q[11] = d3;
+    pre.n2 = n2;
+}
+// chacha8_block(key, counter, n0, n1, pre.n2) with the three quarter rounds taken from `pre`.
+__device__ __forceinline__ void chacha8_block_pre(const uint32_t (&key)[8], const ChaChaColumns& pre, uint32_t counter,
+                                                  uint32_t n0, uint32_t n1, uint32_t (&out)[16]) {
+    uint32_t x[16];
+    x[0] = pre.q[0]; x[4] = pre.q[1]; x[8] = pre.q[2]; x[12] = pre.q[3];
+    x[1] = pre.q[4]; x[5] = pre.q[5]; x[9] = pre.q[6]; x[13] = pre.q[7];
+    x[3] = pre.q[8]; x[7] = pre.q[9]; x[11] = pre.q[10]; x[15] = pre.q[11];
+    x[2] = 0x79622d32u; x[6] = key[2]; x[10] = key[6]; x[14] = n1;
+    MB_AJ_QR(x[2], x[6], x[10], x[14])
+    MB_AJ_QR(x[0], x[5], x[10], x[15]) MB_AJ_QR(x[1], x[6], x[11], x[12])
+    MB_AJ_QR(x[2], x[7], x[8], x[13]) MB_AJ_QR(x[3], x[4], x[9], x[14])
+#pragma unroll
+    for (int dr = 1; dr < 4; dr++) {
+        MB_AJ_QR(x[0], x[4], x[8], x[12]) MB_AJ_QR(x[1], x[5], x[9], x[13])
+        MB_AJ_QR(x[2], x[6], x[10], x[14]) MB_AJ_QR(x[3], x[7], x[11], x[15])
+        MB_AJ_QR(x[0], x[5], x[10], x[15]) MB_AJ_QR(x[1], x[6], x[11], x[12])
+        MB_AJ_QR(x[2], x[7], x[8], x[13]) MB_AJ_QR(x[3], x[4], x[9], x[14])
+    }
+    const uint32_t s[16] = {0x61707865u, 0x3320646eu, 0x79622d32u, 0x6b206574u, key[0], key[1], key[2], key[3],
+                            key[4], key[5], key[6], key[7], counter, n0, n1, pre.n2};
+#pragma unroll
+    for (int i = 0; i < 16; i++) out[i] = x[i] + s[i];
+}
+
 // Coefficients 8*block_idx .. 8*block_idx+7 of M[row][j]: the words of blocks
 // counter = block_idx, block_idx + 8, ... that are below q, first eight kept
 // (at most 16 blocks; a word is rejected with probability about 2^-31).
@@ -80,6 +122,24 @@ __device__ __forceinline__ void prg_ring_block(const uint32_t (&key)[8], uint32_
     }
 #pragma unroll
     for (int k = 0; k < 8; k++) out[k] = tmp[k];
+}
+
+// prg_ring_block for a thread that keeps `pre` = chacha8_columns(key, block_idx, row, high word of j) across
+// columns. A coefficient is rejected only when its high word is 0xFFFFFFFE or 0xFFFFFFFF (q = 2^64 - 2^32 - 31),
+// so one comparison per coefficient decides whether the exact path has to look.
+__device__ __forceinline__ void prg_ring_block_pre(const uint32_t (&key)[8], ChaChaColumns& pre, uint32_t row, uint64_t j,
+                                                   uint32_t block_idx, uint64_t (&out)[8]) {
+    if ((uint32_t)(j >> 32) != pre.n2) chacha8_columns(key, block_idx, row, (uint32_t)(j >> 32), pre);
+    uint32_t buf[16];
+    chacha8_block_pre(key, pre, block_idx, row, (uint32_t)j, buf);
+    bool ok = true;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        out[k] = ((uint64_t)buf[2 * k + 1] << 32) | buf[2 * k];
+        ok = ok && (buf[2 * k + 1] < 0xFFFFFFFEu);
+    }
+    if (ok) return;
+    prg_ring_block(key, row, j, block_idx, out);
 }
 
 enum Kind { KIND_BITS = 0, KIND_S8 = 1, KIND_WIDE = 2 };

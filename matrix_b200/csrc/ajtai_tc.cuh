@@ -318,48 +318,58 @@ commit_tc_pipe_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __rest
 //   full[b]   (count 15)  every builder warp has finished buffer b of this stage (lane 0 arrives after a
 //                         proxy fence and a warp barrier)
 //   empty[b]  (count 1)   the MMAs that read buffer b have completed (tcgen05.commit)
-//   tma[q]    (tiled)     the 28 KB image of stage s has landed in slot q = s mod WS_A_SLOTS of the A ring
-// Work needs no other synchronisation: a (column, plane) pair's digit window is loaded, reversed and expanded
-// into its rows of B by one warp (pairs w, w + 15 of the stage go to warp w), and every matrix job (one
-// ChaCha8 block or eight coefficients -> one 8 x 8 byte tile of A) belongs to one thread.
-// B is the overlapping sliding-row image described at the top of this file (1792 bytes per pair, one MMA of
-// N = 64 per plane). The other way to lay B out, one MMA over all planes with the two K blocks of an MMA in
-// separate images so that planes can sit 1024 bytes apart, was measured too: it needs 4096 bytes of stores
-// per pair and came out 5 to 10 % slower (2.16 against 1.96 ms for four planes from byte planes in operand
-// order), so what a stage costs is the operand traffic through shared memory, not the number of MMAs issued.
+//   tma[q]    (tiled)     the 28 KB image of stage s has landed in slot q = s mod ws_a_slots(NP) of the A ring
+// Work needs no other synchronisation: a (column, plane) pair's digits are fetched (asynchronous copies into a
+// ring, three stages ahead), reversed and expanded into its rows of B by one warp (pair w of the stage, and
+// w + the number of builder warps where there are more pairs than warps), and every matrix job (one ChaCha8
+// block or eight coefficients -> one 8 x 8 byte tile of A) belongs to one thread.
+// B is the overlapping sliding-row image described at the top of this file (1792 bytes per pair), with the
+// planes of a column interleaved by core matrix: row group o / 8 of plane p sits at group (o / 8) np + p of the
+// column's image. With a row-group stride of 128 bytes and a K-block stride of 256 np bytes one descriptor then
+// walks all planes (MMA column 8 (g' np + p) + i = row 8 g' + i of plane p), so a K step is ONE MMA of
+// N = 64 np instead of np MMAs of N = 64. That matters because an i8 MMA of M = 128, K = 32 occupies the tensor
+// pipe for about 90 cycles whatever its width up to N = 128 (and 136 cycles at N = 256): per-plane MMAs cap the
+// kernel at 37 % of the pipe's rate.
 // The small B leaves room for a deeper ring of A images, which is what the copies from HBM need.
 // TILED: the A image is not touched by threads at all: thread 0 issues one bulk copy per stage into a ring of
-// WS_NB + 1 slots, one stage ahead of the builders (the copy issued at stage s reuses the slot of stage
-// s - WS_NB, whose MMAs the thread has just seen complete); rows 112..127 of the M = 128 operand are whatever follows the slot in shared
+// ws_a_slots(NP) slots, ws_a_slots(NP) - 2 stages ahead of the builders (the copy issued at stage s reuses the
+// slot of stage s - 2, whose MMAs the thread has just seen complete); rows 112..127 of the M = 128 operand are whatever follows the slot in shared
 // memory: they only feed accumulator rows that nobody reads.
 // Every wait is bounded; a warp that gives up records TC_ERR_TIMEOUT and leaves the loop, the others then run
 // out of their own waits, and all threads meet at the barrier before the epilogue.
-constexpr int WS_BUILD_WARPS = 15;
-constexpr int WS_THREADS = 512;
+// Warps: 15 builders and the issuer (512 threads) when threads generate or split the matrix (the ChaCha8 build
+// needs 120 registers). Tiled source: 16 builders (one (column, plane) pair each at four planes: with 15 the warp
+// that owned two pairs set the pace of every stage), the issuer, and a warp whose first lane issues the bulk
+// copies of the A images into their own ring, as far ahead as the ring is deep (the issuer commits every stage
+// to the B buffer's barrier and to the A slot's).
+__host__ __device__ constexpr int ws_build_warps(int src) { return src == TC_SRC_TILED ? 16 : 15; }
+__host__ __device__ constexpr int ws_threads(int src) { return src == TC_SRC_TILED ? 576 : 512; }
 constexpr int WS_NB = 3;                             // operand buffers in flight (a round trip builder -> issuer ->
                                                      // tensor pipe -> builder takes about two stage times)
-constexpr int WS_A_SLOTS = WS_NB + 1;                // tiled: ring of A images, one more than the buffers
-__host__ __device__ constexpr int ws_a_slots(int) { return WS_A_SLOTS; }
+constexpr int WS_A_SLOTS_MAX = 6;
+constexpr int WS_DIGIT_DEPTH = 4;                    // ring of digit stages: copies run three stages ahead
+__host__ __device__ constexpr int ws_nb(int src) { return src == TC_SRC_TILED ? 2 : WS_NB; }   // tiled: room for the A ring
+__host__ __device__ constexpr int ws_a_slots(int np) { return np <= 3 ? 6 : 5; }
 
 template <int SRC, int NP>
-static __global__ void __launch_bounds__(WS_THREADS, 1)
+static __global__ void __launch_bounds__(ws_threads(SRC), 1)
 commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restrict__ d_M, const uint8_t* __restrict__ d_T,
                     const int8_t* __restrict__ d_digits, uint64_t N, int p0, uint64_t col_offset, uint64_t* __restrict__ partial,
                     int* __restrict__ d_error, int chunk_cols) {
     constexpr int np = NP;
     constexpr bool TILED = SRC == TC_SRC_TILED, PREMAT = SRC == TC_SRC_COEFFS;
     constexpr int PAIRS = TC_STAGE_COLS * np;                       // (column, plane) pairs per stage
+    constexpr int WS_BUILD_WARPS = ws_build_warps(SRC), WS_THREADS = ws_threads(SRC);
     constexpr int PAIRS_PER_WARP = (PAIRS + WS_BUILD_WARPS - 1) / WS_BUILD_WARPS;
     constexpr uint32_t A_SLOT = TILED ? TCP_A_IMAGE : TC_A_BYTES;
-    constexpr int NB = WS_NB;
+    constexpr int NB = ws_nb(SRC);
     constexpr int A_SLOTS = TILED ? ws_a_slots(NP) : NB;
-    constexpr int TMA_AHEAD = A_SLOTS - NB;                         // builder stages between a bulk copy and its stage
     constexpr uint32_t B_BYTES = PAIRS * TC_B_IMAGE;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* A_base = smem;
     uint8_t* B_base = smem + A_SLOTS * A_SLOT;
-    uint8_t* V_base = B_base + NB * B_BYTES;                         // per builder warp: PAIRS_PER_WARP windows
-    __shared__ __align__(8) uint64_t bar_full[WS_NB], bar_empty[WS_NB], bar_tma[WS_A_SLOTS];
+    uint8_t* DG_base = B_base + NB * B_BYTES;                        // WS_DIGIT_DEPTH stages of digits, 64 bytes per pair
+    __shared__ __align__(8) uint64_t bar_full[WS_NB], bar_empty[WS_NB], bar_tma[WS_A_SLOTS_MAX], bar_afree[WS_A_SLOTS_MAX];
     __shared__ uint32_t tmem_base_sh;
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -380,7 +390,10 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&bar_full[b])), "r"(WS_BUILD_WARPS));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_empty[b])));
         }
-        for (int q = 0; q < WS_A_SLOTS; q++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_tma[q])));
+        for (int q = 0; q < WS_A_SLOTS_MAX; q++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_tma[q])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_afree[q])));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -394,6 +407,7 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
     const uint32_t tmem = tmem_base_sh;
     bool failed = false;
     int bad_digit = 0;
+    int copies_issued = 0;   // copy warp: stages whose bulk copy has gone out
 
     auto tma_issue = [&](int stage) {   // one thread: the A image of `stage` into its ring slot
         const uint32_t bar = smem_u32(&bar_tma[stage % A_SLOTS]);
@@ -410,18 +424,28 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
 #pragma unroll
         for (int k = 0; k < 8; k++) key[k] = SRC == TC_SRC_CHACHA ? d_key[k] : 0u;
         constexpr int JOBS = TC_STAGE_COLS * TC_ROWS * 8;   // 448 matrix jobs per stage, one per thread
-        uint32_t zreg[PAIRS_PER_WARP];
         ulonglong2 creg[4];
-        auto fetch = [&](uint64_t js) {
+        // The digits of stage `stage` go into slot stage mod WS_DIGIT_DEPTH of a ring in shared memory by
+        // asynchronous copies (16 bytes per lane, four lanes per pair), WS_DIGIT_DEPTH - 1 stages ahead of their
+        // use: a global load consumed one stage later leaves every stage waiting for a full memory latency.
+        // One group is committed per stage, empty or not, so that the group count says which stage has landed.
+        auto fetch_digits = [&](int stage) {
+            const uint64_t js = j0 + (uint64_t)stage * TC_STAGE_COLS;
+            uint8_t* slot = DG_base + (stage % WS_DIGIT_DEPTH) * (PAIRS * D);
 #pragma unroll
             for (int q = 0; q < PAIRS_PER_WARP; q++) {
                 const int cp = warp + WS_BUILD_WARPS * q;
-                zreg[q] = 0;
-                if (cp < PAIRS && lane < 16) {
+                if (cp < PAIRS && lane < 4) {
                     const int jj = cp / np, p = cp % np;
-                    if (js + jj < j1) zreg[q] = *reinterpret_cast<const uint32_t*>(d_digits + ((size_t)(p0 + p) * N + js + jj) * D + 4 * lane);
+                    const bool on = stage < n_stages && js + jj < j1;
+                    const int8_t* src = d_digits + ((size_t)(p0 + p) * N + (on ? js + jj : j0)) * D + 16 * lane;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                                 ::"r"(smem_u32(slot + cp * D + 16 * lane)), "l"(src), "r"(on ? 16 : 0) : "memory");
                 }
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        auto fetch = [&](uint64_t js) {
             if (PREMAT) {
                 const int jj = t / (TC_ROWS * 8), rem = t % (TC_ROWS * 8), il = rem >> 3, blk = rem & 7;
                 const bool on = t < JOBS && js + jj < j1;
@@ -431,11 +455,16 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
                 for (int x = 0; x < 4; x++) creg[x] = on ? __ldcs(src + x) : make_ulonglong2(0, 0);
             }
         };
-        if (TILED && t == 0) {
-            for (int st = 0; st < TMA_AHEAD && st < n_stages; st++) tma_issue(st);
-        }
         if (n_stages > 0) fetch(j0);
-        uint32_t* V_w = reinterpret_cast<uint32_t*>(V_base + warp * (PAIRS_PER_WARP * TC_V_STRIDE));
+        for (int st = 0; st < WS_DIGIT_DEPTH - 1; st++) fetch_digits(st);
+        // this thread's matrix job has the same row and block in every stage: the quarter rounds of the first
+        // column round that do not see the column index are computed once
+        ChaChaColumns cols_pre;
+        cols_pre.n2 = 0;
+        if (SRC == TC_SRC_CHACHA && t < JOBS) {
+            const int rem = t % (TC_ROWS * 8);
+            chacha8_columns(key, (uint32_t)(rem & 7), (uint32_t)(group * TC_ROWS + (rem >> 3)), (uint32_t)((col_offset + j0) >> 32), cols_pre);
+        }
         for (int sidx = 0; sidx < n_stages; sidx++) {
             const uint64_t js = j0 + (uint64_t)sidx * TC_STAGE_COLS;
             const int buf = sidx % NB, use = sidx / NB;   // buffer and how many times it has been used before
@@ -448,22 +477,10 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { failed = true; break; }
             }
-            // the copy for stage sidx + TMA_AHEAD reuses the slot of stage sidx - NB, whose MMAs are done
-            if (TILED && t == 0 && sidx + TMA_AHEAD < n_stages) tma_issue(sidx + TMA_AHEAD);
-            // windows of this warp's pairs: word zi of the digits is window word 15 - zi reversed, and word
-            // 31 - zi reversed and negated
-#pragma unroll
-            for (int q = 0; q < PAIRS_PER_WARP; q++) {
-                if (warp + WS_BUILD_WARPS * q < PAIRS && lane < 16) {
-                    const uint32_t z = zreg[q];
-                    if (((z & 0xffu) == 0x80u) | ((z & 0xff00u) == 0x8000u) | ((z & 0xff0000u) == 0x800000u) | ((z >> 24) == 0x80u))
-                        bad_digit = 1;
-                    uint32_t* win = V_w + q * (TC_V_STRIDE / 4);
-                    const uint32_t rev = __byte_perm(z, 0, 0x0123);
-                    win[15 - lane] = rev;
-                    win[31 - lane] = __vneg4(rev);
-                }
-            }
+            // the copies of stage sidx + WS_DIGIT_DEPTH - 1 go out (their slot held stage sidx - 1, which this warp
+            // read before its last barrier); all but the newest WS_DIGIT_DEPTH - 1 groups have then landed
+            fetch_digits(sidx + WS_DIGIT_DEPTH - 1);
+            asm volatile("cp.async.wait_group %0;" ::"n"(WS_DIGIT_DEPTH - 1) : "memory");
             __syncwarp();
             // A: byte planes of this thread's eight coefficients
             if (!TILED && t < JOBS) {
@@ -476,7 +493,7 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
                         c[2 * x + 1] = creg[x].y;
                     }
                 } else {
-                    prg_ring_block(key, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
+                    prg_ring_block_pre(key, cols_pre, (uint32_t)(group * TC_ROWS + il), col_offset + js + jj, (uint32_t)blk, c);
                 }
                 const uint32_t kk = (uint32_t)(jj * D + 8 * blk);
                 uint8_t* dst = A_sh + il * TC_SBO + (kk >> 4) * TC_CORE + (kk & 15);
@@ -493,19 +510,37 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
                     *reinterpret_cast<uint2*>(dst + bp * 16) = make_uint2(lo, hi);
                 }
             }
-            // B: the 112 sliding rows of this warp's pairs (the windows above were written by this warp)
+            // B: the 112 sliding rows of this warp's pairs, straight from the digits. The reversed, sign-wrapped
+            // window of a pair has words W[i] = reverse(Z[15 - i]) for i < 16 and -reverse(Z[31 - i]) for i >= 16
+            // (Z the 16 digit words); lane l < 28 reads W[l .. l + 4] and forms rows 4 l .. 4 l + 3 (byte offsets
+            // 0 .. 3 into the same five words). The four stores of a lane go out rotated by l / 2, so that the
+            // lanes of one store instruction cover eight different 16-byte slots of the banks.
 #pragma unroll
             for (int q = 0; q < PAIRS_PER_WARP; q++) {
                 const int cp = warp + WS_BUILD_WARPS * q;
-                if (cp < PAIRS) {
-                    const uint32_t* win = V_w + q * (TC_V_STRIDE / 4);
-                    for (int o = lane; o < TC_B_ROWS; o += 32) {
-                        const uint32_t* W = win + (o >> 2);
-                        const int sh = 8 * (o & 3);
-                        const uint32_t w0 = W[0], w1 = W[1], w2 = W[2], w3 = W[3], w4 = W[4];
-                        *reinterpret_cast<uint4*>(B_sh + (size_t)cp * TC_B_IMAGE + 16 * o) =
-                            make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
-                                       __funnelshift_r(w3, w4, sh));
+                if (cp < PAIRS && lane < 28) {
+                    const uint32_t* Z = reinterpret_cast<const uint32_t*>(DG_base + (sidx % WS_DIGIT_DEPTH) * (PAIRS * D) + cp * D);
+                    uint32_t w[5];
+#pragma unroll
+                    for (int x = 0; x < 5; x++) {
+                        const int i = lane + x;
+                        const uint32_t z = Z[i < 16 ? 15 - i : 31 - i];
+                        if (x == 0 && lane < 16 &&
+                            (((z & 0xffu) == 0x80u) | ((z & 0xff00u) == 0x8000u) | ((z & 0xff0000u) == 0x800000u) | ((z >> 24) == 0x80u)))
+                            bad_digit = 1;
+                        const uint32_t rev = __byte_perm(z, 0, 0x0123);
+                        w[x] = i < 16 ? rev : __vneg4(rev);
+                    }
+                    // row o of plane p goes to row group (o / 8) * np + p of the column's image: the planes are
+                    // interleaved by core matrix, so that one descriptor walks all of them
+                    const int jj = cp / np, p = cp - jj * np;
+                    uint8_t* dst = B_sh + (size_t)jj * (np * TC_B_IMAGE) + p * TC_CORE + (lane >> 1) * (np * TC_CORE) + (lane & 1) * 64;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int kk = (k + (lane >> 1)) & 3, sh = 8 * kk;
+                        *reinterpret_cast<uint4*>(dst + 16 * kk) =
+                            make_uint4(__funnelshift_r(w[0], w[1], sh), __funnelshift_r(w[1], w[2], sh), __funnelshift_r(w[2], w[3], sh),
+                                       __funnelshift_r(w[3], w[4], sh));
                     }
                 }
             }
@@ -515,9 +550,20 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_full[buf])) : "memory");
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this warp is still in flight when it leaves
+    } else if (warp == WS_BUILD_WARPS + 1) {
+        // ================= copies of the A images (tiled source) =================
+        if (TILED && lane == 0) {
+            for (int st = 0; st < n_stages; st++) {
+                // the slot held stage st - A_SLOTS; its MMAs are done when the issuer's commit to the slot's barrier lands
+                if (st >= A_SLOTS && !mbar_wait(smem_u32(&bar_afree[st % A_SLOTS]), (uint32_t)((st / A_SLOTS - 1) & 1))) { failed = true; break; }
+                tma_issue(st);
+                copies_issued = st + 1;
+            }
+        }
     } else if (lane == 0) {
         // ================= issuer =================
-        const uint32_t idesc = umma_idesc_i8(64);   // one plane per MMA
+        const uint32_t idesc = umma_idesc_i8(64 * np);   // all planes in one MMA
         for (int sidx = 0; sidx < n_stages; sidx++) {
             const int buf = sidx % NB;
             if (!mbar_wait(smem_u32(&bar_full[buf]), (uint32_t)((sidx / NB) & 1))) { failed = true; break; }
@@ -527,21 +573,22 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
             const uint32_t b_addr = smem_u32(B_base + buf * B_BYTES);
             // the descriptors advance by adding to their address field (bytes / 16, no carry out of its 14 bits)
             const uint64_t da0 = umma_desc(a_addr, TC_CORE, TC_SBO);
-            // B: K blocks 256 bytes apart, row groups 128 bytes apart (overlapping core matrices, see the header)
-            const uint64_t db0 = umma_desc(b_addr, 2 * TC_CORE, TC_CORE);
+            // B: MMA column n = 8 g + i is row 8 g' + i of plane p with g = g' np + p; row groups 128 bytes apart,
+            // K blocks 256 np bytes apart: core matrix (g, c) of the K step at 512 np s is group g' + 2 c + 4 s of plane p
+            const uint64_t db0 = umma_desc(b_addr, 2 * TC_CORE * np, TC_CORE);
 #pragma unroll
             for (int ks = 0; ks < TC_STAGE_K / 32; ks++) {
                 const uint64_t da = da0 + (uint64_t)(ks * 2 * TC_CORE / 16);
                 const int jj = ks >> 1, h = ks & 1;   // column of the stage, half of its 64 coefficients
-#pragma unroll
-                for (int p = 0; p < np; p++) {
-                    const uint64_t db = db0 + (uint64_t)(((jj * np + p) * TC_B_IMAGE + h * 4 * TC_CORE) / 16);
-                    const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
-                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                                 ::"r"(tmem + (uint32_t)(64 * p)), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
-                }
+                const uint64_t db = db0 + (uint64_t)((jj * np * TC_B_IMAGE + h * 4 * TC_CORE * np) / 16);
+                const uint32_t acc = (sidx == 0 && ks == 0) ? 0u : 1u;
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                             ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bar_empty[buf])) : "memory");
+            if (TILED)
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                             ::"r"(smem_u32(&bar_afree[sidx % A_SLOTS])) : "memory");
         }
         // the last commit covers every MMA issued before it
         if (!failed && n_stages > 0) {
@@ -550,12 +597,25 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
         }
     }
     if (__syncthreads_or(failed)) failed = true;
+    if (TILED && failed && warp == WS_BUILD_WARPS + 1 && lane == 0) {
+        // a wait gave up somewhere: no copy of this CTA may still be in flight when it leaves (bounded waits again;
+        // a landed copy's phase is complete whether or not the issuer consumed it)
+        for (int st = copies_issued > A_SLOTS ? copies_issued - A_SLOTS : 0; st < copies_issued; st++)
+            mbar_wait(smem_u32(&bar_tma[st % A_SLOTS]), (uint32_t)((st / A_SLOTS) & 1));
+    }
     asm volatile("tcgen05.fence::after_thread_sync;");
 
-    if (!failed && n_stages > 0) {
+    if (!failed && n_stages > 0 && warp < 16) {
+        // Accumulator row m = 8 il + b holds byte plane b of matrix row il; a warp reads 32 rows (four values of
+        // il) and a sixteenth of the columns at a time. c = sum_b 2^(8 b) D[(il, b)] exceeds 64 bits, so planes
+        // 0..3 are summed into L and planes 4..7 into H as plain 64-bit integers (|.| < 2^57) and c = L + 2^32 H
+        // is reduced once. The eight lanes of an il share the work: each shuffle round halves the columns a lane
+        // keeps (a lane sends the half its partner keeps), so after three rounds every lane owns one of the
+        // eight columns, summed over the planes.
         const int q = warp & 3, part = warp >> 2;   // four warps per quarter of the columns
         const int m = 32 * q + lane, b = m & 7, il = m >> 3;
-        const uint64_t scale = 1ULL << (8 * b);
+        const bool b0 = b & 1, b1 = b & 2, b2 = b & 4;
+        const int sh = 8 * (b & 3), e_own = 4 * (b & 1) + (b & 2) + (b >> 2);
         const int c_lo = part * (n_cols / 4), c_hi = c_lo + n_cols / 4;
         for (int c0 = c_lo; c0 < c_hi; c0 += 8) {
             uint32_t v[8];
@@ -564,17 +624,25 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
                          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                          : "r"(taddr));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            long long u[4], w2[2];
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const int32_t sv = (int32_t)v[e];
-                uint64_t f = sv >= 0 ? (uint64_t)sv : agl::P - (uint64_t)(-(int64_t)sv);
-                f = agl::mul(f, scale);
+            for (int i = 0; i < 4; i++) {
+                const long long lo = (long long)(int32_t)v[i] << sh, hi = (long long)(int32_t)v[i + 4] << sh;
+                u[i] = (b0 ? hi : lo) + __shfl_xor_sync(0xffffffffu, b0 ? lo : hi, 1);       // column 4 b0 + i
+            }
 #pragma unroll
-                for (int off = 1; off < 8; off <<= 1) f = agl::add(f, __shfl_xor_sync(0xffffffffu, f, off));
-                if (b == 0 && il < TC_ROWS) {
-                    const int n = c0 + e, p = n >> 6, r = 63 - (n & 63);   // the rows of B run in reverse
-                    partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
-                }
+            for (int i = 0; i < 2; i++)
+                w2[i] = (b1 ? u[i + 2] : u[i]) + __shfl_xor_sync(0xffffffffu, b1 ? u[i] : u[i + 2], 2);   // column 4 b0 + 2 b1 + i
+            const long long mine = b2 ? w2[1] : w2[0];
+            const long long other = __shfl_xor_sync(0xffffffffu, b2 ? w2[0] : w2[1], 4);
+            const long long L = b2 ? other : mine, H = b2 ? mine : other;
+            const uint64_t fl = L >= 0 ? (uint64_t)L : agl::P - (uint64_t)(-L);
+            const uint64_t fh = H >= 0 ? (uint64_t)H : agl::P - (uint64_t)(-H);
+            const uint64_t f = agl::add(fl, agl::reduce128(fh << 32, fh >> 32));
+            if (il < TC_ROWS) {
+                // column c0 + e: row group g = c0 / 8 = g' np + p, row 8 g' + e of plane p; the rows of B run in reverse
+                const int g = c0 >> 3, gp = g / np, p = g - gp * np, r = 63 - (8 * gp + e_own);
+                partial[(((size_t)blockIdx.x * 3 + group) * np + p) * (TC_ROWS * D) + il * D + r] = agl::canon(f);
             }
         }
     }
@@ -588,21 +656,24 @@ commit_tc_ws_kernel(const uint32_t* __restrict__ d_key, const uint64_t* __restri
 inline size_t tc_ws_smem_bytes(int src, int np) {
     const size_t pairs = (size_t)TC_STAGE_COLS * np;
     const size_t a = src == TC_SRC_TILED ? (size_t)ws_a_slots(np) * TCP_A_IMAGE : (size_t)WS_NB * TC_A_BYTES;
-    const size_t per_warp = (pairs + WS_BUILD_WARPS - 1) / WS_BUILD_WARPS;
+    const size_t nb = (size_t)ws_nb(src);
     // the tiled ring's last slot is read 4 KB past its image (rows 112..127 of the operand): B follows it
-    return a + (size_t)WS_NB * pairs * TC_B_IMAGE + (size_t)WS_BUILD_WARPS * per_warp * TC_V_STRIDE + 4096;
+    return a + nb * pairs * TC_B_IMAGE + (size_t)WS_DIGIT_DEPTH * pairs * D + 4096;
 }
 
 // ---- sustained int8 rate of the tensor pipe, measured with this file's own issue loop -------------------
 // One CTA per SM; the operands (A: 128 rows, B: 256 columns, K = 256 bytes, pseudo-random bytes, ordinary
 // non-overlapping core-matrix layout) stay in shared memory; one thread issues `groups` times eight K = 32 MMAs
-// of M = 128, N = 256 into the same accumulators, committing every group to one of two mbarriers and waiting
-// (bounded) for the group before the last one, so that the pipe always has work queued. No operand is built
-// and nothing is read back: this is the ceiling the commit kernel is compared with.
+// of M = 128, N = n_cols into the same accumulators, committing every group to one of a ring of mbarriers and
+// waiting (bounded) for the group `depth` groups back, so that the pipe always has work queued. A commit's
+// arrival is seen well over a thousand cycles after its MMAs were issued: with depth 1 narrow MMAs measure that
+// round trip, not the pipe (16 MMAs in flight: about 89 cycles per MMA whatever the width); depth 6 keeps 56 in
+// flight. No operand is built and nothing is read back: this is the ceiling the commit kernel is compared with.
+constexpr int PEAK_RING = 8;
 static __global__ void __launch_bounds__(128, 1)
-int8_peak_kernel(int groups, int n_cols, int* __restrict__ d_error) {
+int8_peak_kernel(int groups, int n_cols, int depth, int* __restrict__ d_error) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t mbar[2];
+    __shared__ __align__(8) uint64_t mbar[PEAK_RING];
     __shared__ uint32_t tmem_base_sh;
     const int t = threadIdx.x, warp = t >> 5;
     const uint32_t b_bytes = 32 * TC_SBO;   // 256 columns
@@ -612,8 +683,7 @@ int8_peak_kernel(int groups, int n_cols, int* __restrict__ d_error) {
         reinterpret_cast<uint32_t*>(smem)[x] = h;
     }
     if (t == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[1])));
+        for (int q = 0; q < PEAK_RING; q++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[q])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     const uint32_t tmem_cols = 256u;
@@ -628,6 +698,8 @@ int8_peak_kernel(int groups, int n_cols, int* __restrict__ d_error) {
     const uint32_t tmem = tmem_base_sh;
     bool failed = false;
     if (t == 0) {
+        if (depth < 1) depth = 1;
+        if (depth > PEAK_RING - 1) depth = PEAK_RING - 1;
         const uint32_t idesc = umma_idesc_i8(n_cols);
         const uint64_t da0 = umma_desc(smem_u32(smem), TC_CORE, TC_SBO), db0 = umma_desc(smem_u32(smem + TC_A_BYTES), TC_CORE, TC_SBO);
         for (int gidx = 0; gidx < groups && !failed; gidx++) {
@@ -638,15 +710,17 @@ int8_peak_kernel(int groups, int n_cols, int* __restrict__ d_error) {
                 asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                              ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mbar[gidx & 1])) : "memory");
-            if (gidx >= 1) {
-                const int prev = gidx - 1;
-                if (!mbar_wait(smem_u32(&mbar[prev & 1]), (uint32_t)((prev >> 1) & 1))) failed = true;
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         ::"r"(smem_u32(&mbar[gidx % PEAK_RING])) : "memory");
+            if (gidx >= depth) {
+                const int prev = gidx - depth;
+                if (!mbar_wait(smem_u32(&mbar[prev % PEAK_RING]), (uint32_t)((prev / PEAK_RING) & 1))) failed = true;
             }
         }
+        // the commits complete in order: the last one covers every group
         if (!failed && groups > 0) {
             const int last = groups - 1;
-            if (!mbar_wait(smem_u32(&mbar[last & 1]), (uint32_t)((last >> 1) & 1))) failed = true;
+            if (!mbar_wait(smem_u32(&mbar[last % PEAK_RING]), (uint32_t)((last / PEAK_RING) & 1))) failed = true;
         }
         if (failed) atomicMax(d_error, (int)TC_ERR_TIMEOUT);
     }

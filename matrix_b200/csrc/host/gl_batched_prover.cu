@@ -10,10 +10,13 @@
 // challenge. With one shard it is the whole prover. The C-ABI below also exposes
 // the host transcript (zk-torch-3/src/transcript.rs:174-350) so that callers in
 // any language run the same Fiat-Shamir.
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 #include "../batched_kernels.cuh"
 #include "../eq_kernels.cuh"
+#include "exchange.hpp"
 #include "gl_transcript.hpp"
 
 using namespace mb;
@@ -159,10 +162,16 @@ public:
             return MB_OK;
         }
         if (!have_msg_) return MB_ERR_ARG;
-        uint64_t* h = pinned_scratch();   // the calling thread's landing zone, not the creating thread's
-        if (!h) return MB_ERR_CUDA;
-        MB_CUDA(cudaMemcpyAsync(h, msg_dev_, 16 * bt::NC, cudaMemcpyDeviceToHost, MB_STREAM));
-        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        uint64_t* h = landing_;
+        if (h) {
+            // the fold kernel's last block wrote the six words straight into pinned host memory
+            MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        } else {
+            h = pinned_scratch();   // the calling thread's landing zone, not the creating thread's
+            if (!h) return MB_ERR_CUDA;
+            MB_CUDA(cudaMemcpyAsync(h, msg_dev_, 16 * bt::NC, cudaMemcpyDeviceToHost, MB_STREAM));
+            MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        }
         gl::E2 m[4];
         expand_message(h, round_, m);
         for (int c = 0; c < 4; c++) {
@@ -197,12 +206,13 @@ public:
                 MB_CUDA(cudaStreamSynchronize(MB_STREAM));  // wt leaves scope
             }
             MB_KERNEL("batched_fold_message");
+            uint64_t* msg_out = landing_ ? landing_ : msg_dev_;
             if (first)
                 bt::fold_message_kernel<true><<<grid, 256, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, b0_, ab_out, wtab_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+                    eq_in, eq_out, ab_in, b0_, ab_out, wtab_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_out);
             else
                 bt::fold_message_kernel<false><<<grid, 256, 0, MB_STREAM>>>(
-                    eq_in, eq_out, ab_in, b0_, ab_out, wtab_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_dev_);
+                    eq_in, eq_out, ab_in, b0_, ab_out, wtab_dev_, r, K_, stride_in, stride_out, quarter, partial_, counter_, msg_out);
             have_msg_ = true;
         } else {
             MB_KERNEL("batched_final_fold");
@@ -222,6 +232,11 @@ public:
         round_++;
         return MB_OK;
     }
+
+    // Round messages land in `pinned` (six words of page-locked host memory of the calling thread) instead of
+    // being copied back: a round is then one launch and one stream synchronisation. Used by the whole-proof loop,
+    // which stays on one thread; the per-round C-ABI keeps the copy because its callers may change threads.
+    void set_landing(uint64_t* pinned) { landing_ = pinned; }
 
     // After n_loc folds: eq, then alpha^k a_k, b_k for every k: (2K + 1) extension elements.
     int finals(uint64_t* h_out) {
@@ -252,7 +267,186 @@ private:
     uint64_t *eq0_ = nullptr, *eq_a_ = nullptr, *eq_b_ = nullptr, *ab_a_ = nullptr, *ab_b_ = nullptr;
     uint64_t *partial_ = nullptr, *small_ = nullptr, *msg_dev_ = nullptr, *alpha_dev_ = nullptr, *eq_cur_ = nullptr, *ab_cur_ = nullptr;
     unsigned int* counter_ = nullptr;
+    uint64_t* landing_ = nullptr;
 };
+
+}  // namespace mbhost
+
+
+// ---- one proof over `world` shards: round loop, recombination, transcript and the last log2(world) rounds ----
+namespace {
+
+using gl::E2;
+inline E2 e2c(E2 a) { return gl::e2_canon(a); }
+inline E2 e2_load(const uint64_t* w) { return E2{gl::canon(w[0]), gl::canon(w[1])}; }
+
+// Sum over the ranks of `width` extension elements each (rank-major words).
+void sum_shares(const uint64_t* all, int world, int width, E2* out) {
+    for (int i = 0; i < width; i++) {
+        E2 t{0, 0};
+        for (int g = 0; g < world; g++) t = gl::e2_add(t, e2_load(all + ((size_t)g * width + i) * 2));
+        out[i] = e2c(t);
+    }
+}
+
+struct RoundClock {
+    bool on = std::getenv("MB_SHARD_TIMING") != nullptr;
+    std::chrono::steady_clock::time_point t0;
+    double kernel = 0, gather = 0, host = 0;
+    void start() { if (on) t0 = std::chrono::steady_clock::now(); }
+    void stop(double& acc) {
+        if (!on) return;
+        auto t1 = std::chrono::steady_clock::now();
+        acc += std::chrono::duration<double, std::micro>(t1 - t0).count();
+        t0 = t1;
+    }
+};
+
+}  // namespace
+
+namespace mbhost {
+
+// Every rank passes its slices; all outputs are identical on every rank.
+int batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const uint64_t* d_b, int K, int num_vars,
+                          const uint64_t* h_point, const uint8_t* label, size_t label_len, uint64_t* h_claims,
+                          uint64_t* h_alpha, uint64_t* h_round_msgs, uint64_t* h_challenges, uint64_t* h_finals,
+                          uint64_t* h_final_eval, uint64_t* h_transcript_state, double* h_round_us) {
+    if (!ex || !d_a || !d_b || !h_point || (!label && label_len) || K < 1 || K > bt::MAX_K) return MB_ERR_ARG;
+    const int world = ex->world, rank = ex->rank;
+    int g_bits = 0;
+    while ((1 << g_bits) < world) g_bits++;
+    if (world < 1 || (1 << g_bits) != world || rank < 0 || rank >= world) return MB_ERR_ARG;
+    const int n_loc = num_vars - g_bits;
+    if (n_loc < 1 || n_loc > 34) return MB_ERR_UNSUPPORTED;
+
+    // eq(t_top, rank): bit i of the rank pairs with coordinate n_loc + i
+    E2 scale{1, 0};
+    for (int i = 0; i < g_bits; i++) {
+        const E2 t = e2_load(h_point + 2 * (size_t)(n_loc + i));
+        scale = e2c(gl::e2_mul(scale, (rank >> i) & 1 ? t : gl::e2_sub(E2{1, 0}, t)));
+    }
+    const uint64_t scale_w[2] = {scale.c0, scale.c1};
+    uint64_t* pin = pinned_scratch();
+    if (!pin) return MB_ERR_CUDA;
+
+    BatchedEqAbState st;
+    int rc = st.init(d_a, d_b, h_point, scale_w, K, n_loc);
+    if (rc != MB_OK) return rc;
+    st.set_landing(pin);
+
+    const int T = 2 * K + 1;
+    std::vector<uint64_t> mine((size_t)2 * (T > 4 ? T : 4)), all((size_t)world * mine.size());
+    std::vector<E2> claims(K);
+    Transcript tr(label, label_len);
+    tr.append_u64("sp_num_var", (uint64_t)num_vars);
+    tr.append_u64("sp_num_inst", (uint64_t)K);
+    rc = st.claims(mine.data());
+    if (rc != MB_OK) return rc;
+    rc = ex->all_gather_host(ex->ctx, mine.data(), 2 * (size_t)K, all.data());
+    if (rc != MB_OK) return rc;
+    sum_shares(all.data(), world, K, claims.data());
+    for (int k = 0; k < K; k++) {
+        tr.append_ext2("sp_y_i", Ext2{claims[k].c0, claims[k].c1});
+        if (h_claims) { h_claims[2 * k] = claims[k].c0; h_claims[2 * k + 1] = claims[k].c1; }
+    }
+    const Ext2 alpha = tr.challenge_ext2("sp_alpha");
+    if (h_alpha) { h_alpha[0] = alpha.c0; h_alpha[1] = alpha.c1; }
+    rc = st.set_alpha(alpha);
+    if (rc != MB_OK) return rc;
+
+    RoundClock clock;
+    int round = 0;
+    auto publish = [&](const E2* msg) {
+        for (int c = 0; c < 4; c++) {
+            tr.append_ext2("sp_round_msg", Ext2{msg[c].c0, msg[c].c1});
+            if (h_round_msgs) {
+                h_round_msgs[(size_t)round * 8 + 2 * c] = msg[c].c0;
+                h_round_msgs[(size_t)round * 8 + 2 * c + 1] = msg[c].c1;
+            }
+        }
+        const Ext2 r = tr.challenge_ext2("sp_round_challenge");
+        if (h_challenges) { h_challenges[2 * (size_t)round] = r.c0; h_challenges[2 * (size_t)round + 1] = r.c1; }
+        round++;
+        return r;
+    };
+    for (int i = 0; i < n_loc; i++) {
+        clock.start();
+        rc = st.round_message(mine.data());
+        if (rc != MB_OK) return rc;
+        clock.stop(clock.kernel);
+        E2 msg[4];
+        if (world > 1) {
+            rc = ex->all_gather_host(ex->ctx, mine.data(), 8, all.data());
+            if (rc != MB_OK) return rc;
+            clock.stop(clock.gather);
+            sum_shares(all.data(), world, 4, msg);
+        } else {
+            for (int c = 0; c < 4; c++) msg[c] = e2_load(mine.data() + 2 * c);
+        }
+        const Ext2 r = publish(msg);
+        clock.stop(clock.host);
+        rc = st.fold(r);
+        if (rc != MB_OK) return rc;
+    }
+    // one value per table and rank: eq, alpha^k a_k, b_k; the top variables are finished on the host
+    clock.start();
+    rc = st.finals(mine.data());
+    if (rc != MB_OK) return rc;
+    clock.stop(clock.kernel);
+    rc = ex->all_gather_host(ex->ctx, mine.data(), 2 * (size_t)T, all.data());
+    if (rc != MB_OK) return rc;
+    clock.stop(clock.gather);
+    std::vector<std::vector<E2>> tab(T, std::vector<E2>(world));
+    for (int g = 0; g < world; g++)
+        for (int i = 0; i < T; i++) tab[i][g] = e2_load(all.data() + ((size_t)g * T + i) * 2);
+    for (int size = world; size > 1; size /= 2) {
+        const int half = size / 2;
+        E2 msg[4];
+        for (int c = 0; c < 4; c++) {
+            const E2 cc{(uint64_t)c, 0};
+            E2 tot{0, 0};
+            for (int y = 0; y < half; y++) {
+                auto at = [&](const std::vector<E2>& t) {
+                    return e2c(gl::e2_add(t[2 * y], gl::e2_mul(cc, gl::e2_sub(t[2 * y + 1], t[2 * y]))));
+                };
+                E2 inner{0, 0};
+                for (int k = 0; k < K; k++) inner = gl::e2_add(inner, gl::e2_mul(at(tab[1 + k]), at(tab[1 + K + k])));
+                tot = gl::e2_add(tot, gl::e2_mul(at(tab[0]), e2c(inner)));
+            }
+            msg[c] = e2c(tot);
+        }
+        const Ext2 rr = publish(msg);
+        const E2 r{rr.c0, rr.c1};
+        for (auto& t : tab)
+            for (int y = 0; y < half; y++) t[y] = e2c(gl::e2_add(t[2 * y], gl::e2_mul(r, gl::e2_sub(t[2 * y + 1], t[2 * y]))));
+    }
+    // a_k(R) is reported without the alpha^k factor the shards carry
+    std::vector<E2> fin(T);
+    fin[0] = tab[0][0];
+    E2 pw{1, 0}, acc{0, 0};
+    const E2 al{alpha.c0, alpha.c1};
+    for (int k = 0; k < K; k++) {
+        fin[1 + k] = e2c(gl::e2_mul(tab[1 + k][0], gl::e2_inv(pw)));
+        acc = gl::e2_add(acc, gl::e2_mul(tab[1 + k][0], tab[1 + K + k][0]));
+        pw = e2c(gl::e2_mul(pw, al));
+        fin[1 + K + k] = tab[1 + K + k][0];
+    }
+    for (int i = 0; i < T; i++) {
+        tr.append_ext2("sp_f_eval", Ext2{fin[i].c0, fin[i].c1});
+        if (h_finals) { h_finals[2 * i] = fin[i].c0; h_finals[2 * i + 1] = fin[i].c1; }
+    }
+    const E2 fe = e2c(gl::e2_mul(tab[0][0], e2c(acc)));
+    if (h_final_eval) { h_final_eval[0] = fe.c0; h_final_eval[1] = fe.c1; }
+    if (h_transcript_state) std::memcpy(h_transcript_state, tr.state(), 64);
+    clock.stop(clock.host);
+    if (h_round_us) {
+        // what the local rounds cost besides their kernels, per round: exchange, recombination and transcript
+        h_round_us[0] = clock.on ? clock.kernel / (n_loc + 1) : -1.0;
+        h_round_us[1] = clock.on ? clock.gather / (n_loc + 1) : -1.0;
+        h_round_us[2] = clock.on ? clock.host / (n_loc + 1) : -1.0;
+    }
+    return MB_OK;
+}
 
 }  // namespace mbhost
 
@@ -281,6 +475,20 @@ int gl_batched_state_set_alpha(void* state, uint64_t c0, uint64_t c1) { return s
 int gl_batched_state_round_message(void* state, uint64_t* h_msg) { return static_cast<BatchedEqAbState*>(state)->round_message(h_msg); }
 int gl_batched_state_fold(void* state, uint64_t c0, uint64_t c1) { return static_cast<BatchedEqAbState*>(state)->fold(Ext2{c0, c1}); }
 int gl_batched_state_finals(void* state, uint64_t* h_out) { return static_cast<BatchedEqAbState*>(state)->finals(h_out); }
+
+// ---- the whole proof over the shards of an exchange (world = 1: an mb_exchange_local_create(1) object) ----
+// d_a, d_b: this rank's slices [K][2^(num_vars - log2 world)]; h_point: num_vars (c0, c1) pairs, the same on every
+// rank. Outputs (each may be null), identical on every rank: claims [K][2], alpha [2], round messages
+// [num_vars][4][2], challenges [num_vars][2], finals [2K + 1][2] (eq, a_k, b_k at the challenge point), final
+// evaluation [2], transcript state [8]; h_round_us [3]: with MB_SHARD_TIMING set, microseconds per local round spent
+// waiting for the kernel, in the exchange, and on the host (recombination and transcript); -1 otherwise.
+int gl_batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const uint64_t* d_b, int K, int num_vars,
+                             const uint64_t* h_point, const uint8_t* label, size_t label_len, uint64_t* h_claims,
+                             uint64_t* h_alpha, uint64_t* h_round_msgs, uint64_t* h_challenges, uint64_t* h_finals,
+                             uint64_t* h_final_eval, uint64_t* h_transcript_state, double* h_round_us) {
+    return mbhost::batched_prove_sharded(ex, d_a, d_b, K, num_vars, h_point, label, label_len, h_claims, h_alpha, h_round_msgs,
+                                         h_challenges, h_finals, h_final_eval, h_transcript_state, h_round_us);
+}
 
 // ---- host transcript ----
 int gl_transcript_create(const uint8_t* label, size_t label_len, void** transcript) {

@@ -302,6 +302,49 @@ def prove_sharded(make_shard, transcript, comm, point, K, nv, g_bits):
                 state=transcript.state())
 
 
+def prove_batched_native(lib, exchange, d_a_ptr, d_b_ptr, K, nv, point, label, timing=False):
+    """The same protocol as prove_sharded with the whole round loop inside the library
+    (gl_batched_prove_sharded): one call per rank, the ranks' shares exchanged through `exchange` (an
+    mb_exchange handle: mb_exchange_local_create for threads of one process, MailboxExchange /
+    ProcessExchange for one process per GPU). `d_a_ptr`, `d_b_ptr`: this rank's slices [K][2^(nv - log2 world)]
+    on the current device. Returns the dictionary prove_sharded returns; with `timing` (and MB_SHARD_TIMING set
+    in the environment) also `round_us` = microseconds per local round in (kernel wait, exchange, host)."""
+    pt = np.array([c for t in point for c in t], dtype=np.uint64)
+    out = dict(claims=np.zeros((K, 2), dtype=np.uint64), alpha=np.zeros(2, dtype=np.uint64),
+               round_msgs=np.zeros((nv, 4, 2), dtype=np.uint64), challenges=np.zeros((nv, 2), dtype=np.uint64),
+               finals=np.zeros((2 * K + 1, 2), dtype=np.uint64), final_eval=np.zeros(2, dtype=np.uint64),
+               state=np.zeros(8, dtype=np.uint64))
+    us = np.zeros(3, dtype=np.float64)
+    rc = lib.gl_batched_prove_sharded(exchange, d_a_ptr, d_b_ptr, K, nv, pt.ctypes.data, label, len(label),
+                                      out["claims"].ctypes.data, out["alpha"].ctypes.data, out["round_msgs"].ctypes.data,
+                                      out["challenges"].ctypes.data, out["finals"].ctypes.data, out["final_eval"].ctypes.data,
+                                      out["state"].ctypes.data, us.ctypes.data)
+    if rc != 0:
+        raise RuntimeError("gl_batched_prove_sharded: %d" % rc)
+    if timing:
+        out["round_us"] = us
+    return out
+
+
+class MailboxExchange:
+    """An mb_exchange for one process per GPU on one machine whose provers exchange host words only (the batched
+    sumcheck): the library's mailbox in POSIX shared memory, no device all-to-all. `name` must be the same on
+    every rank and unused by any other run."""
+
+    def __init__(self, lib, name, rank, world, slot_words=1024):
+        self.lib = lib
+        h = ctypes.c_void_p()
+        rc = lib.mb_exchange_shm_create(name.encode(), rank, world, slot_words, None, None, ctypes.byref(h))
+        if rc != 0:
+            raise RuntimeError("mb_exchange_shm_create: %d" % rc)
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            self.lib.mb_exchange_destroy(self.handle)
+            self.handle = None
+
+
 # ---- Ajtai commitment sharded by column ranges -------------------------------------------------
 AGL_Q = 0xFFFFFFFEFFFFFFE1
 

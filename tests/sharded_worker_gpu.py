@@ -1,5 +1,7 @@
 """One rank of the multi-GPU test: the sharded batched sumcheck with a GPU shard
-per rank and NCCL for the per-round exchange. Started by test_multigpu.py."""
+per rank, first under the Python round loop with NCCL for the per-round exchange,
+then with the whole loop inside the library over its shared-memory mailbox.
+Started by test_multigpu.py."""
 import os
 import sys
 
@@ -12,7 +14,8 @@ import torch.distributed as dist  # noqa: E402
 
 from matrix_b200 import load_gl  # noqa: E402
 from matrix_b200.ffi import DeviceBuffer  # noqa: E402
-from matrix_b200.sharded import GpuShard, LibTranscript, TorchComm, prove_sharded  # noqa: E402
+from matrix_b200.sharded import (GpuShard, LibTranscript, MailboxExchange, TorchComm, prove_batched_native,  # noqa: E402
+                                 prove_sharded)
 from oracle import pyoracle  # noqa: E402
 from tests.sharded_helpers import assert_same_proof, inputs, shard_slices  # noqa: E402
 
@@ -39,6 +42,15 @@ def main():
     got = prove_sharded(make_shard, LibTranscript(lib, b"bench"), comm, point, K, nv, g_bits)
     exp = pyoracle.batched_prove(a, b, np.array([c for t in point for c in t], dtype=np.uint64), K, nv)
     assert_same_proof(got, exp)
+    # the same proof with the round loop in the library
+    ex = MailboxExchange(lib, "/mb_test_batched_%s" % os.environ.get("MASTER_PORT", "0"), comm.rank, comm.world)
+    dist.barrier()
+    sa, sb = shard_slices(a, b, K, nv, g_bits, comm.rank)
+    d_a, d_b = DeviceBuffer.from_numpy(lib, sa), DeviceBuffer.from_numpy(lib, sb)
+    native = prove_batched_native(lib, ex.handle, d_a.ptr, d_b.ptr, K, nv, point, b"bench")
+    assert_same_proof(native, exp)
+    dist.barrier()
+    ex.close()
     with open("%s.%d" % (out_path, comm.rank), "w") as f:
         f.write("ok")
     dist.destroy_process_group()
