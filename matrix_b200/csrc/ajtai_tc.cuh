@@ -12,14 +12,13 @@
 // columns (K = 32768) stays below 255 * 127 * 32768 < 2^31, so the accumulators
 // are drained every 512 columns.
 //
-// One CTA (512 threads) owns a chunk of 512 columns and one of three groups of 14 matrix rows, so no ChaCha8
-// block is generated twice. It works in stages of four columns (K = 256) with two operand buffers: while one
-// thread's eight K = 32 MMAs of stage s run (committed to the buffer's mbarrier), all threads build stage s + 1,
-// and what a stage reads from global memory is loaded into registers one stage ahead. Operands use the
-// no-swizzle K-major core-matrix layout (8 rows x 16 bytes, cores contiguous along K). Barrier b = s & 1 is
-// committed by stage s; a buffer is rewritten at stage s only after the commit of stage s - 2 has completed
-// (its (s >> 1)-th completion, parity ((s >> 1) - 1) & 1). Every wait is bounded and reports through an error
-// word instead of spinning forever.
+// One CTA owns a chunk of at most 512 columns and one of three groups of 14 matrix rows, so no ChaCha8 block
+// is generated twice. It works in stages of four columns (K = 256): eight K = 32 MMAs per stage, committed to
+// the mbarrier of the stage's operand buffer; a buffer is rewritten only after that commit has landed. Operands
+// use the no-swizzle K-major core-matrix layout (8 rows x 16 bytes, cores contiguous along K). Every wait is
+// bounded and reports through an error word instead of spinning forever. Two kernels follow: commit_tc_pipe
+// (all threads build a stage, one of them issues it; kept for the mode that writes the matrix images out) and
+// commit_tc_ws (builder warps and an issuing warp, the commit path).
 //
 // B (the Toeplitz expansion) is never written out as 64 x 64 bytes per (column, plane). With the rows taken in
 // reverse (MMA column n = 63 - r) entry (n, k) is w[n + k], w the reversed, sign-wrapped digit window of the
@@ -27,9 +26,9 @@
 // w[8 (g + 2 c) + i .. + 15], i = 0..7: it depends on g + 2 c only. The operand is therefore stored as 112
 // consecutive 16-byte rows, row o = w[o .. o + 15] (1792 bytes instead of 4096), and addressed with a stride of
 // 128 bytes between row groups and 256 bytes between K blocks, so that the core matrices of the descriptor
-// overlap in shared memory. A thread forms one row with four funnel shifts and one 16-byte store. Planes cannot
-// share one descriptor (their row groups would overlap each other), so every plane is an MMA of N = 64 with its
-// own 64 columns of tensor memory.
+// overlap in shared memory. In commit_tc_pipe every plane has its own image and its own MMA of N = 64;
+// commit_tc_ws interleaves the planes of a column by core matrix (strides 128 and 256 x planes), which puts all
+// planes behind one descriptor and one MMA of N = 64 x planes.
 //
 // Where the matrix comes from (TcSource): the ChaCha8 stream; d_M[j][i][k] as 64-bit coefficients (split into
 // byte planes here); or d_T, the byte planes already in operand order: per stage of four columns and row group
