@@ -877,6 +877,125 @@ def prof_report(lib):
     return kernels
 
 
+def run_same_point(args):
+    """The batched same-point sumcheck of zk-torch-4's fold tree (fold/same_point_sumcheck.rs) at the shape the
+    reference publishes (zk-torch-4/PROVER_PERFORMANCE.md:466-493: arity 22, 42 leaves): binary packed witnesses,
+    one claim point per leaf, whole protocol through agl_same_point_prove_device_ffi (eq tables built on the device,
+    22 rounds, host Monolith transcript). Single GPU."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    from matrix_b200 import load_agl
+    from matrix_b200.ffi import DeviceBuffer
+    from matrix_b200.inputs import AGL_Q, splitmix64
+    lib = load_agl()
+    assert lib.cuda_set_device(local) == 0 and lib.almost_goldilocks_cuda_init() == 0
+    arity = args.num_vars if args.num_vars != 24 else 22
+    M = args.instances if args.instances != 16 else 42
+    n = 1 << arity
+    words = max(1, n >> 6)
+    packed = splitmix64(11, M * words)
+    if n < 64:
+        packed &= np.uint64((1 << n) - 1)
+    pts = splitmix64(12, 2 * arity * M) % np.uint64(AGL_Q)
+    h_packed = ctypes.c_void_p()
+    assert lib.mb_host_alloc(ctypes.byref(h_packed), packed.nbytes) == 0
+    ctypes.memmove(h_packed.value, packed.ctypes.data, packed.nbytes)
+    d_w = DeviceBuffer.from_numpy(lib, packed)
+    vals = np.zeros((M, 2), dtype=np.uint64)
+    assert lib.agl_same_point_claims_device_ffi(M, arity, pts.ctypes.data, 0, d_w.ptr, None, vals.ctypes.data) == 0   # the claims: untimed
+    msgs, ch = np.zeros((arity, 3, 2), dtype=np.uint64), np.zeros((arity, 2), dtype=np.uint64)
+    fe, fin = np.zeros((M, 2), dtype=np.uint64), np.zeros(2, dtype=np.uint64)
+
+    def step():
+        t = ctypes.c_void_p()
+        assert lib.agl_transcript_create(LABEL, len(LABEL), ctypes.byref(t)) == 0
+        rc = lib.agl_same_point_prove_device_ffi(M, arity, pts.ctypes.data, vals.ctypes.data, 0, d_w.ptr, None, t, msgs.ctypes.data,
+                                                 ch.ctypes.data, fe.ctypes.data, fin.ctypes.data)
+        lib.agl_transcript_destroy(t)
+        return rc
+
+    def step_e2e():
+        assert lib.mb_memcpy_htod_async(d_w.ptr, h_packed, packed.nbytes) == 0
+        assert step() == 0
+
+    timed = _event_timer(lib)
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(max(args.warmup, 1)):
+        assert step() == 0
+    lib.mb_prof_enable(0)
+    launches0 = lib.mb_launch_count()
+    lib.cuda_device_synchronize()
+    sampler.mark_begin()
+    ms = timed(step, args.steps)
+    sampler.mark_end()
+    launches = lib.mb_launch_count() - launches0
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    psteps = min(args.steps, 3)
+    lib.mb_prof_reset(); lib.mb_prof_enable(1)
+    for _ in range(psteps):
+        step()
+    lib.mb_prof_enable(0)
+    clocks = sampler.stop()
+    kernels = prof_report(lib)
+    # the proof must verify (host verifier of the library)
+    ok = ctypes.c_int(0)
+    t = ctypes.c_void_p()
+    lib.agl_transcript_create(LABEL, len(LABEL), ctypes.byref(t))
+    ar = np.full(M, arity, dtype=np.int32)
+    assert lib.agl_same_point_verify_ffi(M, arity, ar.ctypes.data, pts.ctypes.data, vals.ctypes.data, msgs.ctypes.data, fe.ctypes.data,
+                                         fin.ctypes.data, t, None, ctypes.byref(ok)) == 0
+    lib.agl_transcript_destroy(t)
+    peak, peak_kind = measured_peaks()
+    per = ms / args.steps
+    # bytes the proof must move (extension elements of 16 B): the eq tables are written once and read by the first
+    # message and by the first fold (with the packed bits), which writes the half-size eq and f tables; every later
+    # round is one pass that reads its eq and f tables and writes their halves
+    alg = M * n * 16.0 * 3 + M * (n // 2) * 32.0 + sum(M * (n >> r) * 32.0 * 1.5 for r in range(1, arity))
+    kernel_ms = sum(x for _, x in kernels.values()) / psteps
+    ach = alg / (kernel_ms * 1e-3) / 1e9
+    elems = M * n
+    line = {"metric": "field-elems/s: batched same-point sumcheck (eq x f, degree 2), %d leaves of arity %d, almost-Goldilocks" % (M, arity),
+            "value": elems * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": per, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": {"workload": "same_point arity=%d leaves=%d binary" % (arity, M),
+                       "l2": "tables larger than L2" if M * n * 32 > (256 << 20) else "tables fit L2",
+                       "published": "26-27 ms for the 22 rounds on an A100 (zk-torch-4/PROVER_PERFORMANCE.md:466-493); "
+                                    "ms_per_step here includes the eq tables and the reveals"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "peak_kind": peak_kind,
+                         "timed_in": "a separate pass of %d steps with CUDA events around every launch" % psteps,
+                         "note": "all kernels of a proof against the bytes its passes must move (one pass per round: fold and next "
+                                 "message fused); the passes are bound by the integer pipe (extension products), not by HBM"},
+            "kernel_times_ms": {k: {"launches": c, "ms": round(x, 4)} for k, (c, x) in sorted(kernels.items())},
+            "kernel_times_steps": psteps,
+            "per_step": {"kernel_ms": kernel_ms, "other_ms": per - kernel_ms},
+            "e2e": {"value": elems * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(packed.nbytes), "d2h_bytes_per_step": int(msgs.nbytes + fe.nbytes + 6 * M * 8 * arity)},
+            "gpu_launches": int(launches), "clocks": clocks, "verified": bool(ok.value),
+            "final_eval": [int(x) for x in fin]}
+    if not args.no_cpu_baseline:
+        from oracle import pyoracle
+        sa = min(arity, 16)
+        insts = []
+        sw = max(1, (1 << sa) >> 6)
+        for i in range(M):
+            w = packed[i * words:i * words + sw].copy()
+            pt = pts[2 * arity * i:2 * arity * i + 2 * sa].reshape(sa, 2)
+            insts.append(dict(arity=sa, kind=0, witness=w, point=pt, value=pyoracle.agl_witness_eval(0, w, sa, pt)))
+        pyoracle.load().oracle_set_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        pyoracle.agl_same_point_prove(insts, sa, LABEL)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": M * (1 << sa) / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                                "sample": "CPU oracle (restatement of prove_same_point's dense path, OpenMP over the leaves) on "
+                                          "%d leaves of arity %d, %.2f s; the cost is linear in 2^arity" % (M, sa, dt)}
+    print(json.dumps(line))
+    lib.mb_host_free(h_packed)
+
+
 def part_sumcheck(lib, args, peak, peak_kind):
     """The linear sumcheck of f * g over 2^24 points (base-field tables, extension challenges): whole proof through
     gl_sumcheck_prove_device_ffi (tables resident) and gl_sumcheck_prove_host_ffi (host tables, copy inside)."""
@@ -1259,7 +1378,7 @@ def main():
     ap.add_argument("--num-vars", type=int, default=24)
     ap.add_argument("--ref-num-vars", type=int, default=20, help="sample size of the CPU arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit", "link", "llama_layer", "peval"],
+    ap.add_argument("--workload", default="basefold", choices=["basefold", "batched_sumcheck", "sumcheck", "ajtai", "mcommit", "link", "llama_layer", "peval", "same_point"],
                     help="basefold: the headline (commit + open, 2^24); batched_sumcheck: 16 instances of "
                          "eq*a*b over 2^26 points sharded on the top variables (strong scaling)")
     ap.add_argument("--instances", type=int, default=16)
@@ -1292,6 +1411,9 @@ def main():
         return
     if args.workload == "peval":
         run_peval(args)
+        return
+    if args.workload == "same_point":
+        run_same_point(args)
         return
 
     if args.impl == "reference":

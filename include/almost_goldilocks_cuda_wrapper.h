@@ -219,6 +219,13 @@ int aext2_sumcheck_batched_round0_binary_msg_ffi(const uint64_t* d_polys, const 
 int aext2_sumcheck_batched_round0_binary_fold_ffi(const uint64_t* d_polys, const uint64_t* d_packed, uint64_t* d_output,
                                                   uint64_t challenge_c0, uint64_t challenge_c1, size_t original_size, size_t half,
                                                   int num_leaves, size_t packed_size_u64);
+/* additions (no reference counterpart): the fold on the challenge and the message of the NEXT round in one pass over
+ * the tables; `half` is the half of the input tables and must be even; d_partial as for the message kernels */
+int aext2_sumcheck_batched_fold_message_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0, uint64_t challenge_c1,
+                                            size_t original_size, size_t half, int num_leaves, int num_blocks_x, uint64_t* d_partial);
+int aext2_sumcheck_batched_round0_binary_fold_message_ffi(const uint64_t* d_polys, const uint64_t* d_packed, uint64_t* d_output,
+                                                          uint64_t challenge_c0, uint64_t challenge_c1, size_t original_size, size_t half,
+                                                          int num_leaves, int num_blocks_x, size_t packed_size_u64, uint64_t* d_partial);
 /* shared eq: eq tables of the distinct points in d_eq, f tables in d_f, leaf -> point map */
 int aext2_sharedeq_msg_ffi(const uint64_t* d_eq, const uint64_t* d_f, const int* d_leaf_to_unique, uint64_t* d_partial,
                            size_t original_size, size_t half, int num_leaves, int num_blocks_x);
@@ -370,6 +377,29 @@ int agl_transcript_challenge_scalar(void* transcript, const uint8_t* label, size
 /* n = 2 is challenge_ext2 (c0 then c1) */
 int agl_transcript_challenge_vector(void* transcript, const uint8_t* label, size_t label_len, uint64_t* out, size_t n);
 int agl_transcript_state(const void* transcript, uint64_t* out12);
+
+/* ---- addition: the same-point sumcheck as a whole protocol (the host loop the reference keeps in Rust:
+ * zk-torch-4/src/fold/same_point_sumcheck.rs:58-157 prover and labels, :1334-1553 device path over the batched
+ * kernels above, :161-219 verifier). num_leaves instances of one arity, each with its own claim point and claim
+ * y_i = f_i(r_i); the proof reduces them to one point R. h_claim_pts[num_leaves][arity][2],
+ * h_claim_vals[num_leaves][2]; witness on the device: kind 0 binary packed (d_w0[num_leaves][words], words =
+ * max(1, 2^(arity - 6)), bit j of word j / 64), 1 ternary single chunk (d_w0 = +1 masks, d_w1 = -1 masks), 2
+ * extension tables (d_w0[num_leaves][2^arity][2]). `transcript` is a handle from agl_transcript_create and is
+ * advanced exactly as the reference's prover advances it. Host outputs: round_msgs[arity][3][2] (degree 2),
+ * challenges[arity][2] (may be null), f_evals[num_leaves][2] = f_i(R), final_eval[2]. Device memory: 2 x num_leaves x
+ * 2^arity x 32 bytes. Instances of different arities stay on the CPU path, as in the reference. */
+int agl_same_point_prove_device_ffi(int num_leaves, int arity, const uint64_t* h_claim_pts, const uint64_t* h_claim_vals, int kind,
+                                    const uint64_t* d_w0, const uint64_t* d_w1, void* transcript, uint64_t* h_round_msgs,
+                                    uint64_t* h_challenges, uint64_t* h_f_evals, uint64_t* h_final_eval);
+/* the claims y_i = f_i(r_i) the protocol starts from (FoldData::evaluate_at_ext2, zk-torch-4/src/fold/mod.rs:107-110),
+ * on the device with the kernels of the proof: h_claim_vals[num_leaves][2] */
+int agl_same_point_claims_device_ffi(int num_leaves, int arity, const uint64_t* h_claim_pts, int kind, const uint64_t* d_w0,
+                                     const uint64_t* d_w1, uint64_t* h_claim_vals);
+/* verify_same_point on the host; arity[i] <= num_vars may differ per instance (h_claim_pts: arity[i] pairs each, back
+ * to back). *ok = 1 when the proof is accepted; challenges (num_vars pairs) are written when not null. */
+int agl_same_point_verify_ffi(int num_instances, int num_vars, const int* arity, const uint64_t* h_claim_pts,
+                              const uint64_t* h_claim_vals, const uint64_t* round_msgs, const uint64_t* f_evals,
+                              const uint64_t* final_eval, void* transcript, uint64_t* challenges, int* ok);
 
 /* ---- host layer: the whole linear sumcheck (the reference keeps these loops in Rust) ----
  * GpuLinearSumcheckProver::new + prove / prove_ext2 / prove_gpu_resident

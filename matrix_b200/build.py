@@ -56,6 +56,7 @@ LIBRARIES = {
         "agl_stubs.cu",
         "host/agl_transcript.cu",
         "host/agl_sumcheck_prover.cu",
+        "host/agl_same_point_prover.cu",
     ],
 }
 

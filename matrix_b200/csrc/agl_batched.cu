@@ -39,7 +39,38 @@ __device__ __forceinline__ void store_block_sums(E2 (&acc)[NV], uint64_t* partia
     block_sum_store<2 * NV>(v, partial + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * 2 * NV, AglAdd(), AglCanon());
 }
 
+// Exact sum of extension products: c0 = s00 + 3 s11, c1 = s01 (X^2 = 3), every s an unreduced 160-bit sum of
+// 64 x 64 products of canonical words (room for 2^32 of them); one reduction per thread at the end.
+struct ProdSum {
+    gl::Acc s00, s11, s01;
+};
+__device__ __forceinline__ ProdSum prod_zero() { return ProdSum{gl::acc_zero(), gl::acc_zero(), gl::acc_zero()}; }
+__device__ __forceinline__ void prod_add(ProdSum& s, E2 a, E2 b) {
+    gl::acc_mul(s.s00, a.c0, b.c0);
+    gl::acc_mul(s.s11, a.c1, b.c1);
+    gl::acc_mul(s.s01, a.c0, b.c1);
+    gl::acc_mul(s.s01, a.c1, b.c0);
+}
+__device__ __forceinline__ E2 prod_reduce(const ProdSum& s) {
+    // acc_reduce_wide: a thread may add thousands of products, the top limb is not small
+    return E2{agl::add(agl::acc_reduce_wide(s.s00), agl::mul_small(agl::acc_reduce_wide(s.s11), 3)), agl::acc_reduce_wide(s.s01)};
+}
+// Exact sum of extension elements (128-bit integer sums of canonical words).
+struct ElemSum {
+    gl::Acc c0, c1;
+};
+__device__ __forceinline__ void elem_add(ElemSum& s, E2 a) {
+    gl::acc_add(s.c0, a.c0);
+    gl::acc_add(s.c1, a.c1);
+}
+__device__ __forceinline__ E2 elem_reduce(const ElemSum& s) { return E2{agl::acc_reduce_wide(s.c0), agl::acc_reduce_wide(s.c1)}; }
+
 // m(0), m(1), m(2) of sum_y eq f over pairs (2y, 2y + 1). F_MODE 0: f is an Ext2 table; 1: packed bits.
+// With d_e = e1 - e0, d_f = f1 - f0: m(2) = 2 m(1) - m(0) + 2 sum d_e d_f, so a pair costs three products that
+// are accumulated without reduction (twelve 64 x 64 multiply-accumulates and two extension subtractions; the
+// term-by-term form reduced every product and every partial sum). With a binary f the sums are selections:
+// m(0) = sum of e0 over f0 = 1, m(1) = sum of e1 over f1 = 1, sum d_e d_f = sum of d_e over f1 > f0 minus the
+// sum over f1 < f0, all exact integer sums.
 template <int F_MODE>
 __global__ void __launch_bounds__(BLK)
 eqf_message_kernel(const uint64_t* __restrict__ eq_base, size_t eq_stride, const int* __restrict__ eq_map,
@@ -47,27 +78,90 @@ eqf_message_kernel(const uint64_t* __restrict__ eq_base, size_t eq_stride, const
     const int leaf = blockIdx.y;
     const uint64_t* eq = eq_base + (size_t)(eq_map ? eq_map[leaf] : leaf) * eq_stride;
     const uint64_t* f = f_base + (size_t)leaf * f_stride;
-    E2 acc[3] = {{0, 0}, {0, 0}, {0, 0}};
+    E2 acc[3];
     const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
-        const E2 e0 = ld(eq + 4 * y), e1 = ld(eq + 4 * y + 2);
-        const E2 e2 = agl::e2_sub(agl::e2_add(e1, e1), e0);
-        if (F_MODE == 0) {
-            const E2 f0 = ld(f + 4 * y), f1 = ld(f + 4 * y + 2);
-            acc[0] = agl::e2_add(acc[0], agl::e2_mul_lazy(e0, f0));
-            acc[1] = agl::e2_add(acc[1], agl::e2_mul_lazy(e1, f1));
-            acc[2] = agl::e2_add(acc[2], agl::e2_mul_lazy(e2, agl::e2_sub(agl::e2_add(f1, f1), f0)));
-        } else {
+    if (F_MODE == 0) {
+        ProdSum p0 = prod_zero(), p1 = prod_zero(), pd = prod_zero();
+        for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
+            // any representative below 2^64 will do: the products are exact integers
+            const E2 e0 = ld(eq + 4 * y), e1 = ld(eq + 4 * y + 2), f0 = ld(f + 4 * y), f1 = ld(f + 4 * y + 2);
+            prod_add(p0, e0, f0);
+            prod_add(p1, e1, f1);
+            prod_add(pd, agl::e2_sub(e1, e0), agl::e2_sub(f1, f0));
+        }
+        acc[0] = prod_reduce(p0);
+        acc[1] = prod_reduce(p1);
+        const E2 d = prod_reduce(pd);
+        acc[2] = agl::e2_add(agl::e2_sub(agl::e2_add(acc[1], acc[1]), acc[0]), agl::e2_add(d, d));
+    } else {
+        ElemSum s0{gl::acc_zero(), gl::acc_zero()}, s1 = s0, up = s0, down = s0;
+        for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < half; y += step) {
             const uint64_t word = f[(2 * y) >> 6];
             const int f0 = (int)((word >> ((2 * y) & 63)) & 1), f1 = (int)((word >> ((2 * y + 1) & 63)) & 1);
-            if (f0) acc[0] = agl::e2_add(acc[0], e0);
-            if (f1) acc[1] = agl::e2_add(acc[1], e1);
-            const int f2 = 2 * f1 - f0;  // f at c = 2
-            if (f2 == 1) acc[2] = agl::e2_add(acc[2], e2);
-            else if (f2 == 2) acc[2] = agl::e2_add(acc[2], agl::e2_add(e2, e2));
-            else if (f2 == -1) acc[2] = agl::e2_sub(acc[2], e2);
+            if (!(f0 | f1)) continue;
+            const E2 e0 = ld(eq + 4 * y), e1 = ld(eq + 4 * y + 2);
+            if (f0) elem_add(s0, e0);
+            if (f1) elem_add(s1, e1);
+            if (f0 != f1) {
+                const E2 de = agl::e2_sub(e1, e0);
+                if (f1) elem_add(up, de);
+                else elem_add(down, de);
+            }
         }
+        acc[0] = elem_reduce(s0);
+        acc[1] = elem_reduce(s1);
+        const E2 d = agl::e2_sub(elem_reduce(up), elem_reduce(down));
+        acc[2] = agl::e2_add(agl::e2_sub(agl::e2_add(acc[1], acc[1]), acc[0]), agl::e2_add(d, d));
     }
+    store_block_sums<3>(acc, partial);
+}
+
+// Fold on r and the next round's message in one pass over the tables (an addition: the reference folds, then reads
+// the folded tables again for the message). Thread per pair y of the FOLDED tables: it reads elements 4y .. 4y + 3 of
+// eq and f (f from packed bits when F_MODE is 1: f' in {0, 1 - r, r, 1}), writes elements 2y, 2y + 1 of the folded
+// tables and adds the pair to the exact sums of the message of the next round.
+template <int F_MODE>
+__global__ void __launch_bounds__(BLK)
+eqf_fold_message_kernel(const uint64_t* __restrict__ in, const uint64_t* __restrict__ packed, size_t packed_words,
+                        uint64_t* __restrict__ out, E2 r, size_t n, size_t quarter, uint64_t* __restrict__ partial) {
+    const int leaf = blockIdx.y;
+    const uint64_t* eq = in + (size_t)leaf * 4 * n;
+    const uint64_t* f = eq + 2 * n;
+    const uint64_t* bits = packed + (size_t)leaf * packed_words;
+    uint64_t* oe = out + (size_t)leaf * 4 * n;
+    uint64_t* of = oe + 2 * n;
+    const agl::E2Pre pr = agl::e2_pre(r);
+    const E2 one{1, 0}, rc = agl::e2_canon(r), omr = agl::e2_canon(agl::e2_sub(one, r));
+    ProdSum p0 = prod_zero(), p1 = prod_zero(), pd = prod_zero();
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t y = (size_t)blockIdx.x * blockDim.x + threadIdx.x; y < quarter; y += step) {
+        const E2 a0 = ld(eq + 8 * y), a1 = ld(eq + 8 * y + 2), a2 = ld(eq + 8 * y + 4), a3 = ld(eq + 8 * y + 6);
+        const E2 e0 = agl::e2_canon(agl::e2_fma_pre(pr, agl::e2_sub(a1, a0), a0));
+        const E2 e1 = agl::e2_canon(agl::e2_fma_pre(pr, agl::e2_sub(a3, a2), a2));
+        E2 f0, f1;
+        if (F_MODE == 0) {
+            const E2 b0 = ld(f + 8 * y), b1 = ld(f + 8 * y + 2), b2 = ld(f + 8 * y + 4), b3 = ld(f + 8 * y + 6);
+            f0 = agl::e2_canon(agl::e2_fma_pre(pr, agl::e2_sub(b1, b0), b0));
+            f1 = agl::e2_canon(agl::e2_fma_pre(pr, agl::e2_sub(b3, b2), b2));
+        } else {
+            const unsigned nib = (unsigned)((bits[(4 * y) >> 6] >> ((4 * y) & 63)) & 15);   // four bits of one word
+            const unsigned lo = nib & 3, hi = nib >> 2;
+            f0 = lo == 3 ? one : lo == 2 ? rc : lo == 1 ? omr : E2{0, 0};
+            f1 = hi == 3 ? one : hi == 2 ? rc : hi == 1 ? omr : E2{0, 0};
+        }
+        agl::e2_store(oe + 4 * y, e0);
+        agl::e2_store(oe + 4 * y + 2, e1);
+        agl::e2_store(of + 4 * y, f0);
+        agl::e2_store(of + 4 * y + 2, f1);
+        prod_add(p0, e0, f0);
+        prod_add(p1, e1, f1);
+        prod_add(pd, agl::e2_sub(e1, e0), agl::e2_sub(f1, f0));
+    }
+    E2 acc[3];
+    acc[0] = prod_reduce(p0);
+    acc[1] = prod_reduce(p1);
+    const E2 d = prod_reduce(pd);
+    acc[2] = agl::e2_add(agl::e2_sub(agl::e2_add(acc[1], acc[1]), acc[0]), agl::e2_add(d, d));
     store_block_sums<3>(acc, partial);
 }
 
@@ -243,6 +337,31 @@ int aext2_sumcheck_batched_round0_binary_fold_ffi(const uint64_t* d_polys, const
     dim3 grid(gx(half), num_leaves);
     binary_fold_kernel<<<grid, BLK, 0, MB_STREAM>>>(d_polys, d_packed, d_output, E2{challenge_c0, challenge_c1}, original_size, half,
                                                     packed_size_u64);
+    return finish_async();
+}
+
+// Additions: the fold on the challenge and the message of the next round in one pass. `half` is the half of the
+// INPUT tables (as for the fold); it must be even. d_partial[block][leaf][c][2] of the round after the fold.
+int aext2_sumcheck_batched_fold_message_ffi(const uint64_t* d_input, uint64_t* d_output, uint64_t challenge_c0, uint64_t challenge_c1,
+                                            size_t original_size, size_t half, int num_leaves, int num_blocks_x, uint64_t* d_partial) {
+    if (!d_input || !d_output || !d_partial || num_leaves < 1 || num_blocks_x < 1 || half < 2 || (half & 1) || half > original_size / 2)
+        return MB_ERR_ARG;
+    MB_KERNEL("aext2_batched_fold_message");
+    dim3 grid(num_blocks_x, num_leaves);
+    eqf_fold_message_kernel<0><<<grid, BLK, 0, MB_STREAM>>>(d_input, d_input, 0, d_output, E2{challenge_c0, challenge_c1}, original_size,
+                                                              half / 2, d_partial);
+    return finish_async();
+}
+int aext2_sumcheck_batched_round0_binary_fold_message_ffi(const uint64_t* d_polys, const uint64_t* d_packed, uint64_t* d_output,
+                                                          uint64_t challenge_c0, uint64_t challenge_c1, size_t original_size, size_t half,
+                                                          int num_leaves, int num_blocks_x, size_t packed_size_u64, uint64_t* d_partial) {
+    if (!d_polys || !d_packed || !d_output || !d_partial || num_leaves < 1 || num_blocks_x < 1 || half < 2 || (half & 1) ||
+        half > original_size / 2)
+        return MB_ERR_ARG;
+    MB_KERNEL("aext2_batched_binary_fold_message");
+    dim3 grid(num_blocks_x, num_leaves);
+    eqf_fold_message_kernel<1><<<grid, BLK, 0, MB_STREAM>>>(d_polys, d_packed, packed_size_u64, d_output, E2{challenge_c0, challenge_c1},
+                                                              original_size, half / 2, d_partial);
     return finish_async();
 }
 

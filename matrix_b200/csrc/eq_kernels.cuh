@@ -85,5 +85,78 @@ inline int build(const uint64_t* d_r, uint64_t* d_out, uint64_t* d_scratch, int 
     return finish_async();
 }
 
+// `count` tables of 2^log_n elements at once: table t from the point at d_r + t * r_stride words into
+// d_out + t * out_stride words. d_scratch needs count * (2^(log_n/2) + 2^(log_n - log_n/2)) elements when
+// log_n > 12. Two launches for all tables instead of two per table (a small-tables launch keeps two blocks busy).
+template <class F>
+__global__ void small_tables_batched_kernel(const uint64_t* __restrict__ r_all, size_t r_stride, int nbits0, int nbits1,
+                                            uint64_t* scratch_all, size_t scratch_stride) {
+    using T = typename F::T;
+    const size_t t = blockIdx.x >> 1;
+    const int which = blockIdx.x & 1;
+    const uint64_t* r = r_all + t * r_stride;
+    const int var_lo = which == 0 ? 0 : nbits0;
+    const int nbits = which == 0 ? nbits0 : nbits1;
+    uint64_t* out = scratch_all + t * scratch_stride + (which == 0 ? 0 : ((size_t)F::NW << nbits0));
+    if (threadIdx.x == 0) {
+        const uint64_t one[2] = {1, 0};
+        for (int w = 0; w < F::NW; w++) out[w] = one[w];
+    }
+    __syncthreads();
+    for (int i = 0; i < nbits; i++) {
+        T ri = F::load(r, var_lo + i);
+        const size_t half = (size_t)1 << i;
+        for (size_t j = threadIdx.x; j < half; j += blockDim.x) {
+            T a = F::load(out, j);
+            T ar = F::mul(a, ri);
+            F::store(out, j, F::sub(a, ar));
+            F::store(out, j + half, ar);
+        }
+        __syncthreads();
+    }
+}
+template <class F>
+__global__ void __launch_bounds__(256)
+outer_product_batched_kernel(const uint64_t* __restrict__ scratch_all, size_t scratch_stride, int n_lo, uint64_t* __restrict__ out_all,
+                             size_t out_stride, size_t n) {
+    const uint64_t* lo = scratch_all + (size_t)blockIdx.y * scratch_stride;
+    const uint64_t* hi = lo + ((size_t)F::NW << n_lo);
+    uint64_t* out = out_all + (size_t)blockIdx.y * out_stride;
+    const size_t lo_size = (size_t)1 << n_lo, rows = n >> n_lo;
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const typename F::Pre h = F::pre(F::load(hi, row));
+        for (size_t j = threadIdx.x; j < lo_size; j += blockDim.x)
+            F::store(out, row * lo_size + j, F::mul_pre(h, F::load(lo, j)));
+    }
+}
+template <class F>
+inline int build_batched(const uint64_t* d_r, size_t r_stride, uint64_t* d_out, size_t out_stride, uint64_t* d_scratch, int log_n,
+                         int count, cudaStream_t st) {
+    if (count < 1 || count > 65535) return MB_ERR_ARG;
+    if (log_n <= 12) {
+        for (int t = 0; t < count; t++) {
+            int rc = build<F>(d_r + (size_t)t * r_stride, d_out + (size_t)t * out_stride, nullptr, log_n, st);
+            if (rc != MB_OK) return rc;
+        }
+        return MB_OK;
+    }
+    if (!d_scratch || !d_r || !d_out) return MB_ERR_ARG;
+    const int n_lo = log_n / 2, n_hi = log_n - n_lo;
+    const size_t scratch_stride = ((size_t)F::NW << n_lo) + ((size_t)F::NW << n_hi);
+    const size_t n = (size_t)1 << log_n;
+    {
+        MB_KERNEL_ON("small_tables", st);
+        small_tables_batched_kernel<F><<<2 * count, 1024, 0, st>>>(d_r, r_stride, n_lo, n_hi, d_scratch, scratch_stride);
+    }
+    {
+        MB_KERNEL_ON("outer_product", st);
+        int per_leaf = grid_for((n >> n_lo) * 256, 256, 8) / count;
+        if (per_leaf < 8) per_leaf = 8;
+        dim3 grid(per_leaf, count);
+        outer_product_batched_kernel<F><<<grid, 256, 0, st>>>(d_scratch, scratch_stride, n_lo, d_out, out_stride, n);
+    }
+    return finish_async();
+}
+
 }  // namespace eq
 }  // namespace mb

@@ -217,7 +217,9 @@ _AGL = None
 _MEM = ["cuda_malloc", "cuda_free", "mb_alloc_cache_flush", "mb_alloc_cache_bytes", "cuda_memcpy_htod", "cuda_memcpy_dtoh", "cuda_memcpy_dtod", "cuda_device_synchronize",
         "cuda_get_last_error", "cuda_peek_at_last_error", "cuda_mem_get_info", "cuda_set_device", "cuda_get_device",
         "cuda_get_device_count", "mb_event_create", "mb_event_record", "mb_event_sync", "mb_event_elapsed_ms",
-        "mb_event_destroy", "mb_stream_sync", "mb_launch_count", "mb_fill_splitmix"]
+        "mb_event_destroy", "mb_stream_sync", "mb_launch_count", "mb_fill_splitmix", "mb_host_alloc", "mb_host_free",
+        "mb_memcpy_htod_async", "mb_memcpy_dtoh_async", "mb_prof_enable", "mb_prof_reset", "mb_prof_report", "gl_memset_zero",
+        "cuda_get_device_name"]
 _AGL_SIGNATURES = {
     "almost_goldilocks_cuda_init": (c_int, []),
     "agl_batch_add_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
@@ -356,6 +358,14 @@ _AGL_SIGNATURES = {
     "agl_transcript_challenge_scalar": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, ctypes.POINTER(ctypes.c_uint64)]),
     "agl_transcript_challenge_vector": (c_int, [c_void_p, ctypes.c_char_p, c_size_t, c_void_p, c_size_t]),
     "agl_transcript_state": (c_int, [c_void_p, c_void_p]),
+    "agl_same_point_prove_device_ffi": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_void_p, c_void_p]),
+    "aext2_sumcheck_batched_fold_message_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t, c_int, c_int, c_void_p]),
+    "aext2_sumcheck_batched_round0_binary_fold_message_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t,
+                                                                      c_int, c_int, c_size_t, c_void_p]),
+    "agl_same_point_claims_device_ffi": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "agl_same_point_verify_ffi": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, ctypes.POINTER(c_int)]),
     "agl_sumcheck_prove_device_ffi": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "agl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "agl_sumcheck_verify_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(c_int)]),

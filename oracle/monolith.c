@@ -399,3 +399,211 @@ int oracle_agl_sumcheck_verify(const uint64_t *round_msgs, const uint64_t *final
     }
     return current.c0 == final_eval[0] % AGL_Q && current.c1 == final_eval[1] % AGL_Q;
 }
+
+/* ------------------------------------------------------------------ */
+/* Same-point sumcheck over the almost-Goldilocks extension             */
+/* (zk-torch-4/src/fold/same_point_sumcheck.rs)                         */
+/* ------------------------------------------------------------------ */
+/* Witness kinds of an instance (FoldData, zk-torch-4/src/fold/mod.rs:107-160):
+ *   0  binary, packed: bit j of word j / 64 is f[j]
+ *   1  ternary, one chunk: `words` words of +1 masks, then `words` words of -1 masks (words = max(1, 2^(arity-6)))
+ *   2  dense base-field table of 2^arity words
+ * The dense CPU prover lifts every kind to an extension table first (same_point_sumcheck.rs:924-1030); the
+ * small-alphabet round-0 paths of the reference compute the same field elements. */
+static void sp_lift(int kind, const uint64_t *w, int arity, aext2_t *out) {
+    size_t n = (size_t)1 << arity, words = arity >= 6 ? n >> 6 : 1;
+    for (size_t j = 0; j < n; j++) {
+        if (kind == 0) out[j] = ae2((w[j >> 6] >> (j & 63)) & 1, 0);
+        else if (kind == 1) {
+            uint64_t p = (w[j >> 6] >> (j & 63)) & 1, m = (w[words + (j >> 6)] >> (j & 63)) & 1;
+            out[j] = ae2(agl_sub(p, m), 0);
+        } else out[j] = ae2(w[j] % AGL_Q, 0);
+    }
+}
+static void sp_eq_table(const uint64_t *pt, int arity, aext2_t *out) { /* poly/mod.rs:86-120: variable 0 = bit 0 */
+    out[0] = ae2(1, 0);
+    for (int i = 0; i < arity; i++) {
+        aext2_t ri = ae2(pt[2 * i] % AGL_Q, pt[2 * i + 1] % AGL_Q);
+        size_t half = (size_t)1 << i;
+        for (size_t j = 0; j < half; j++) {
+            aext2_t a = out[j], ar = ae2_mul(a, ri);
+            out[j] = ae2_sub(a, ar);
+            out[j + half] = ar;
+        }
+    }
+}
+/* FoldData::evaluate_at_ext2 (fold/mod.rs:107-110): the multilinear extension of the witness at `pt`. */
+void oracle_agl_witness_eval(int kind, const uint64_t *w, int arity, const uint64_t *pt, uint64_t *out2) {
+    size_t n = (size_t)1 << arity;
+    aext2_t *eq = malloc(sizeof(aext2_t) * n), *f = malloc(sizeof(aext2_t) * n);
+    sp_eq_table(pt, arity, eq);
+    sp_lift(kind, w, arity, f);
+    aext2_t acc = ae2(0, 0);
+    for (size_t j = 0; j < n; j++) acc = ae2_add(acc, ae2_mul(eq[j], f[j]));
+    out2[0] = acc.c0; out2[1] = acc.c1;
+    free(eq); free(f);
+}
+static aext2_t sp_eq_eval(const uint64_t *a, const aext2_t *b, int n) { /* same_point_sumcheck.rs:907-921 */
+    aext2_t acc = ae2(1, 0), one = ae2(1, 0);
+    for (int i = 0; i < n; i++) {
+        aext2_t ai = ae2(a[2 * i] % AGL_Q, a[2 * i + 1] % AGL_Q);
+        acc = ae2_mul(acc, ae2_add(ae2_mul(ai, b[i]), ae2_mul(ae2_sub(one, ai), ae2_sub(one, b[i]))));
+    }
+    return acc;
+}
+static void sp_header(agl_transcript_t *t, int M, int N, const int *arity, const uint64_t *pts, const size_t *pt_off,
+                      const uint64_t *vals) { /* same_point_sumcheck.rs:78-87 */
+    agl_append_u64(t, "sp_num_var", (uint64_t)N);
+    agl_append_u64(t, "sp_num_inst", (uint64_t)M);
+    for (int i = 0; i < M; i++) {
+        agl_append_u64(t, "sp_arity_i", (uint64_t)arity[i]);
+        for (int k = 0; k < arity[i]; k++) agl_append_ext2(t, "sp_r_i", ae2(pts[pt_off[i] + 2 * k], pts[pt_off[i] + 2 * k + 1]));
+        agl_append_ext2(t, "sp_y_i", ae2(vals[2 * i], vals[2 * i + 1]));
+    }
+}
+
+/* prove_same_point (same_point_sumcheck.rs:58-157) with the dense per-instance state (:270-470) and
+ * compute_round_message (:826-883). M instances; instance i has arity[i] <= N variables (>= 1), claim point
+ * pts[pt_off[i] ..] (arity[i] pairs), claim value vals[2 i ..], witness kind[i] at wit + wit_off[i] (words).
+ * The transcript starts as Transcript::new(label). Outputs: round_msgs[N][3][2], challenges[N][2], f_evals[M][2],
+ * final_eval[2], state12 (sponge after the proof; may be NULL). */
+int oracle_agl_same_point_prove(int M, int N, const int *arity, const uint64_t *pts, const size_t *pt_off, const uint64_t *vals,
+                                const int *kind, const uint64_t *wit, const size_t *wit_off, const uint8_t *label,
+                                size_t label_len, uint64_t *round_msgs, uint64_t *challenges, uint64_t *f_evals,
+                                uint64_t *final_eval, uint64_t *state12) {
+    if (M < 1 || N < 1) return -2;
+    for (int i = 0; i < M; i++) if (arity[i] < 1 || arity[i] > N) return -2;
+    agl_transcript_t t;
+    agl_transcript_init(&t, label, label_len);
+    sp_header(&t, M, N, arity, pts, pt_off, vals);
+    aext2_t alpha = agl_challenge_ext2(&t, "sp_alpha");
+    aext2_t *alphas = malloc(sizeof(aext2_t) * M), **eq = malloc(sizeof(void *) * M), **f = malloc(sizeof(void *) * M);
+    aext2_t *constant = malloc(sizeof(aext2_t) * M), *R = malloc(sizeof(aext2_t) * N);
+    size_t *len = malloc(sizeof(size_t) * M);
+    aext2_t *contrib = malloc(sizeof(aext2_t) * 3 * M);
+    aext2_t pw = ae2(1, 0);
+    for (int i = 0; i < M; i++) {
+        alphas[i] = pw;
+        pw = ae2_mul(pw, alpha);
+        len[i] = (size_t)1 << arity[i];
+    }
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < M; i++) {
+        eq[i] = malloc(sizeof(aext2_t) * len[i]);
+        f[i] = malloc(sizeof(aext2_t) * len[i]);
+        sp_eq_table(pts + pt_off[i], arity[i], eq[i]);
+        sp_lift(kind[i], wit + wit_off[i], arity[i], f[i]);
+    }
+    const aext2_t two = ae2(2, 0);
+    for (int round = 0; round < N; round++) {
+        aext2_t msg[3] = { ae2(0, 0), ae2(0, 0), ae2(0, 0) };
+        const aext2_t pow_remaining = ae2((uint64_t)1 << (N - round - 1), 0);
+        /* instances in parallel (the reference uses rayon over leaves); field sums do not depend on the order */
+#pragma omp parallel for schedule(dynamic, 1)
+        for (int i = 0; i < M; i++) {
+            aext2_t *out = contrib + 3 * (size_t)i;
+            if (round >= arity[i]) { /* constant mode: alpha^i 2^(N - round - 1) eq_i(R) f_i(R) at all three points */
+                aext2_t w = ae2_mul(alphas[i], ae2_mul(pow_remaining, constant[i]));
+                out[0] = out[1] = out[2] = w;
+                continue;
+            }
+            size_t half = len[i] / 2;
+            aext2_t s0 = ae2(0, 0), s1 = ae2(0, 0), s2 = ae2(0, 0);
+            for (size_t j = 0; j < half; j++) {
+                aext2_t e0 = eq[i][2 * j], e1 = eq[i][2 * j + 1], f0 = f[i][2 * j], f1 = f[i][2 * j + 1];
+                aext2_t e2v = ae2_sub(ae2_mul(two, e1), e0), f2v = ae2_sub(ae2_mul(two, f1), f0);
+                s0 = ae2_add(s0, ae2_mul(e0, f0));
+                s1 = ae2_add(s1, ae2_mul(e1, f1));
+                s2 = ae2_add(s2, ae2_mul(e2v, f2v));
+            }
+            aext2_t scale = ae2_mul(alphas[i], ae2((uint64_t)1 << (N - arity[i]), 0));
+            out[0] = ae2_mul(scale, s0);
+            out[1] = ae2_mul(scale, s1);
+            out[2] = ae2_mul(scale, s2);
+        }
+        for (int i = 0; i < M; i++)
+            for (int c = 0; c < 3; c++) msg[c] = ae2_add(msg[c], contrib[3 * (size_t)i + c]);
+        for (int c = 0; c < 3; c++) {
+            agl_append_ext2(&t, "sp_round_msg", msg[c]);
+            round_msgs[((size_t)round * 3 + c) * 2] = msg[c].c0;
+            round_msgs[((size_t)round * 3 + c) * 2 + 1] = msg[c].c1;
+        }
+        aext2_t r = agl_challenge_ext2(&t, "sp_round_challenge");
+        challenges[2 * round] = r.c0;
+        challenges[2 * round + 1] = r.c1;
+        R[round] = r;
+#pragma omp parallel for schedule(dynamic, 1)
+        for (int i = 0; i < M; i++) {
+            if (round >= arity[i]) continue;
+            size_t half = len[i] / 2;
+            for (size_t j = 0; j < half; j++) {
+                aext2_t a = eq[i][2 * j], b = eq[i][2 * j + 1];
+                eq[i][j] = ae2_add(a, ae2_mul(r, ae2_sub(b, a)));
+                a = f[i][2 * j]; b = f[i][2 * j + 1];
+                f[i][j] = ae2_add(a, ae2_mul(r, ae2_sub(b, a)));
+            }
+            len[i] = half;
+            if (round + 1 == arity[i]) constant[i] = ae2_mul(eq[i][0], f[i][0]);
+        }
+    }
+    aext2_t fin = ae2(0, 0);
+    for (int i = 0; i < M; i++) {
+        f_evals[2 * i] = f[i][0].c0;
+        f_evals[2 * i + 1] = f[i][0].c1;
+        agl_append_ext2(&t, "sp_f_eval", f[i][0]);
+    }
+    for (int i = 0; i < M; i++) {
+        aext2_t eq_i = sp_eq_eval(pts + pt_off[i], R, arity[i]);
+        fin = ae2_add(fin, ae2_mul(alphas[i], ae2_mul(eq_i, f[i][0])));
+    }
+    final_eval[0] = fin.c0;
+    final_eval[1] = fin.c1;
+    if (state12) memcpy(state12, t.sponge, sizeof(t.sponge));
+    for (int i = 0; i < M; i++) { free(eq[i]); free(f[i]); }
+    free(alphas); free(eq); free(f); free(constant); free(R); free(len); free(contrib);
+    return 0;
+}
+
+/* verify_same_point (same_point_sumcheck.rs:161-219). Returns 1 and writes the challenges when the proof is
+ * accepted, 0 otherwise. */
+int oracle_agl_same_point_verify(int M, int N, const int *arity, const uint64_t *pts, const size_t *pt_off, const uint64_t *vals,
+                                 const uint64_t *round_msgs, const uint64_t *f_evals, const uint64_t *final_eval,
+                                 const uint8_t *label, size_t label_len, uint64_t *challenges) {
+    if (M < 1) return 0;
+    agl_transcript_t t;
+    agl_transcript_init(&t, label, label_len);
+    sp_header(&t, M, N, arity, pts, pt_off, vals);
+    aext2_t alpha = agl_challenge_ext2(&t, "sp_alpha");
+    aext2_t *alphas = malloc(sizeof(aext2_t) * M), *R = malloc(sizeof(aext2_t) * N);
+    aext2_t pw = ae2(1, 0), current = ae2(0, 0);
+    for (int i = 0; i < M; i++) {
+        alphas[i] = pw;
+        pw = ae2_mul(pw, alpha);
+        aext2_t y = ae2(vals[2 * i] % AGL_Q, vals[2 * i + 1] % AGL_Q);
+        current = ae2_add(current, ae2_mul(alphas[i], ae2_mul(y, ae2((uint64_t)1 << (N - arity[i]), 0))));
+    }
+    int ok = 1;
+    for (int round = 0; round < N && ok; round++) {
+        aext2_t m[3];
+        for (int c = 0; c < 3; c++) m[c] = ae2(round_msgs[((size_t)round * 3 + c) * 2] % AGL_Q, round_msgs[((size_t)round * 3 + c) * 2 + 1] % AGL_Q);
+        aext2_t sum = ae2_add(m[0], m[1]);
+        if (sum.c0 != current.c0 || sum.c1 != current.c1) { ok = 0; break; }
+        for (int c = 0; c < 3; c++) agl_append_ext2(&t, "sp_round_msg", m[c]);
+        aext2_t r = agl_challenge_ext2(&t, "sp_round_challenge");
+        R[round] = r;
+        if (challenges) { challenges[2 * round] = r.c0; challenges[2 * round + 1] = r.c1; }
+        current = agl_interpolate(m, 3, r);
+    }
+    if (ok) {
+        aext2_t expected = ae2(0, 0);
+        for (int i = 0; i < M; i++) agl_append_ext2(&t, "sp_f_eval", ae2(f_evals[2 * i], f_evals[2 * i + 1]));
+        for (int i = 0; i < M; i++) {
+            aext2_t fe = ae2(f_evals[2 * i] % AGL_Q, f_evals[2 * i + 1] % AGL_Q);
+            expected = ae2_add(expected, ae2_mul(alphas[i], ae2_mul(sp_eq_eval(pts + pt_off[i], R, arity[i]), fe)));
+        }
+        if (current.c0 != expected.c0 || current.c1 != expected.c1) ok = 0;
+        if (final_eval[0] % AGL_Q != expected.c0 || final_eval[1] % AGL_Q != expected.c1) ok = 0;
+    }
+    free(alphas); free(R);
+    return ok;
+}

@@ -246,6 +246,76 @@ def agl_sumcheck_verify(msgs, final_eval, claimed, d, num_var, label=b"bench"):
     return bool(ok), ch[:2 * num_var]
 
 
+_SIGS.update({
+    "oracle_agl_witness_eval": (None, [ci, vp, ci, vp, vp]),
+    "oracle_agl_same_point_prove": (ci, [ci, ci, vp, vp, vp, vp, vp, vp, vp, ctypes.c_char_p, sz, vp, vp, vp, vp, vp]),
+    "oracle_agl_same_point_verify": (ci, [ci, ci, vp, vp, vp, vp, vp, vp, vp, ctypes.c_char_p, sz, vp]),
+})
+
+
+def _sp_pack(instances):
+    """Flattens same-point instances: each is a dict with arity, point (arity x 2 words), kind (0 binary packed,
+    1 ternary single chunk: pos words then neg words, 2 dense base-field table) and witness (uint64 words)."""
+    import numpy as np
+    arity = np.array([i["arity"] for i in instances], dtype=np.int32)
+    kind = np.array([i["kind"] for i in instances], dtype=np.int32)
+    pts = [np.ascontiguousarray(i["point"], dtype=np.uint64).reshape(-1) for i in instances]
+    wit = [np.ascontiguousarray(i["witness"], dtype=np.uint64).reshape(-1) for i in instances]
+    pt_off = np.cumsum([0] + [len(x) for x in pts[:-1]]).astype(np.uint64)
+    wit_off = np.cumsum([0] + [len(x) for x in wit[:-1]]).astype(np.uint64)
+    return arity, kind, np.concatenate(pts), pt_off, np.concatenate(wit), wit_off
+
+
+def agl_witness_eval(kind, witness, arity, point):
+    """FoldData::evaluate_at_ext2: the multilinear extension of a same-point witness at `point` -> (c0, c1)."""
+    import numpy as np
+    lib = load()
+    w = np.ascontiguousarray(witness, dtype=np.uint64)
+    pt = np.ascontiguousarray(point, dtype=np.uint64).reshape(-1)
+    out = np.zeros(2, dtype=np.uint64)
+    lib.oracle_agl_witness_eval(int(kind), w.ctypes.data, int(arity), pt.ctypes.data, out.ctypes.data)
+    return out
+
+
+def agl_same_point_prove(instances, num_vars, label):
+    """zk-torch-4's prove_same_point (dense CPU states, Monolith transcript). `instances`: see _sp_pack, plus
+    "value" (2 words) per instance. Returns a dict of numpy arrays: round_msgs [N][3][2], challenges [N][2],
+    f_evals [M][2], final_eval [2], state [12]."""
+    import numpy as np
+    lib = load()
+    M = len(instances)
+    arity, kind, pts, pt_off, wit, wit_off = _sp_pack(instances)
+    vals = np.ascontiguousarray([i["value"] for i in instances], dtype=np.uint64).reshape(-1)
+    out = dict(round_msgs=np.zeros((num_vars, 3, 2), dtype=np.uint64), challenges=np.zeros((num_vars, 2), dtype=np.uint64),
+               f_evals=np.zeros((M, 2), dtype=np.uint64), final_eval=np.zeros(2, dtype=np.uint64),
+               state=np.zeros(12, dtype=np.uint64))
+    rc = lib.oracle_agl_same_point_prove(M, num_vars, arity.ctypes.data, pts.ctypes.data, pt_off.ctypes.data, vals.ctypes.data,
+                                         kind.ctypes.data, wit.ctypes.data, wit_off.ctypes.data, label, len(label),
+                                         out["round_msgs"].ctypes.data, out["challenges"].ctypes.data,
+                                         out["f_evals"].ctypes.data, out["final_eval"].ctypes.data, out["state"].ctypes.data)
+    assert rc == 0, rc
+    return out
+
+
+def agl_same_point_verify(instances, num_vars, proof, label):
+    """zk-torch-4's verify_same_point on (arity, point, value) of every instance; returns (accepted, challenges)."""
+    import numpy as np
+    lib = load()
+    M = len(instances)
+    arity = np.array([i["arity"] for i in instances], dtype=np.int32)
+    pts = [np.ascontiguousarray(i["point"], dtype=np.uint64).reshape(-1) for i in instances]
+    pt_off = np.cumsum([0] + [len(x) for x in pts[:-1]]).astype(np.uint64)
+    pts = np.concatenate(pts)
+    vals = np.ascontiguousarray([i["value"] for i in instances], dtype=np.uint64).reshape(-1)
+    msgs = np.ascontiguousarray(proof["round_msgs"], dtype=np.uint64)
+    fe = np.ascontiguousarray(proof["f_evals"], dtype=np.uint64)
+    fin = np.ascontiguousarray(proof["final_eval"], dtype=np.uint64)
+    ch = np.zeros((num_vars, 2), dtype=np.uint64)
+    ok = lib.oracle_agl_same_point_verify(M, num_vars, arity.ctypes.data, pts.ctypes.data, pt_off.ctypes.data, vals.ctypes.data,
+                                          msgs.ctypes.data, fe.ctypes.data, fin.ctypes.data, label, len(label), ch.ctypes.data)
+    return bool(ok), ch
+
+
 def e5_op(name, a, b=None, e=None):
     """One Ext5 operation of the oracle on lists of five words: name in mul / frobenius / inv / pow."""
     lib = load()
