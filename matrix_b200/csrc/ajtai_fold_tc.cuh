@@ -74,8 +74,27 @@ multifold_tc_kernel(const uint64_t* __restrict__ zbin, const uint64_t* __restric
     uint32_t phase = 0;
     bool failed = false, pending = false;
     const uint64_t tiles = (N + 127) / 128;
+    // The masks of a stage (eight instances of this thread's ring element) are loaded one stage ahead, while the
+    // MMAs of the stage before run: consumed at once, their latency was what the kernel waited for.
+    uint64_t pm[MF_INST], mm[MF_INST];
+    auto load_masks = [&](uint64_t tile_idx, int s) {
+        const uint64_t j = tile_idx * 128 + t;
+#pragma unroll
+        for (int ii = 0; ii < MF_INST; ii++) {
+            const int i = s * MF_INST + ii;
+            pm[ii] = 0;
+            mm[ii] = 0;
+            if (tile_idx < tiles && j < N && i < total) {
+                if (i < num_binary) pm[ii] = __ldcs(zbin + (uint64_t)i * N + j);
+                else {
+                    pm[ii] = __ldcs(pos + (uint64_t)(i - num_binary) * N + j);
+                    mm[ii] = __ldcs(neg + (uint64_t)(i - num_binary) * N + j);
+                }
+            }
+        }
+    };
+    if (blockIdx.x < tiles && stages > 0) load_masks(blockIdx.x, 0);
     for (uint64_t tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x) {
-        const uint64_t j = tile * 128 + t;
         for (int s = 0; s < stages && !failed; s++) {
             // the previous stage's MMAs must have read A and B before they are overwritten
             if (pending) {
@@ -85,17 +104,9 @@ multifold_tc_kernel(const uint64_t* __restrict__ zbin, const uint64_t* __restric
                 if (__syncthreads_or(failed)) { failed = true; break; }
             }
             // ---- A: this thread's ring element, eight instances, 64 bytes each ----
-#pragma unroll 2
+#pragma unroll
             for (int ii = 0; ii < MF_INST; ii++) {
-                const int i = s * MF_INST + ii;
-                uint64_t p = 0, m = 0;
-                if (j < N && i < total) {
-                    if (i < num_binary) p = zbin[(uint64_t)i * N + j];
-                    else {
-                        p = pos[(uint64_t)(i - num_binary) * N + j];
-                        m = neg[(uint64_t)(i - num_binary) * N + j];
-                    }
-                }
+                const uint64_t p = pm[ii], m = mm[ii];
                 uint8_t* dst = A_sh + (t >> 3) * MF_SBO + (ii * 4) * TC_CORE + (t & 7) * 16;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
@@ -109,6 +120,9 @@ multifold_tc_kernel(const uint64_t* __restrict__ zbin, const uint64_t* __restric
                         make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
                 }
             }
+            // the next stage's masks (of this tile, or the first of this CTA's next tile) go out now
+            if (s + 1 < stages) load_masks(tile, s + 1);
+            else load_masks(tile + gridDim.x, 0);
             // ---- B: the stage's slice of T, already in layout ----
             {
                 const uint4* src = reinterpret_cast<const uint4*>(Bg + (size_t)s * MF_B_BYTES);
