@@ -225,7 +225,9 @@ def run_batched(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))   # timing barrier and max over ranks
         if native:
-            exch = MailboxExchange(lib, "/mb_batched_%s" % os.environ.get("MASTER_PORT", "0"), rank, world)
+            token = [os.urandom(6).hex() if rank == 0 else None]   # a fresh name: a mailbox left by a killed run is never reused
+            dist.broadcast_object_list(token, src=0)
+            exch = MailboxExchange(lib, "/mb_batched_%s" % token[0], rank, world)
             handle = exch.handle
             dist.barrier()
         else:

@@ -43,7 +43,9 @@ def main():
     exp = pyoracle.batched_prove(a, b, np.array([c for t in point for c in t], dtype=np.uint64), K, nv)
     assert_same_proof(got, exp)
     # the same proof with the round loop in the library
-    ex = MailboxExchange(lib, "/mb_test_batched_%s" % os.environ.get("MASTER_PORT", "0"), comm.rank, comm.world)
+    token = [os.urandom(6).hex() if comm.rank == 0 else None]
+    dist.broadcast_object_list(token, src=0)
+    ex = MailboxExchange(lib, "/mb_test_batched_%s" % token[0], comm.rank, comm.world)
     dist.barrier()
     sa, sb = shard_slices(a, b, K, nv, g_bits, comm.rank)
     d_a, d_b = DeviceBuffer.from_numpy(lib, sa), DeviceBuffer.from_numpy(lib, sb)
