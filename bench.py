@@ -744,11 +744,16 @@ def run_llama_layer(args):
     d_o = DeviceBuffer(lib, L * 42 * 64 * 8)
     finals = []
 
-    def step(commit=True):
+    from matrix_b200.layer_trace import prove_einsum_native
+
+    def step(commit=True, native=True):
         h = ctypes.c_void_p()
         lib.agl_transcript_create(b"llama-layer", 11, ctypes.byref(h))
         for eq, dims, bufs, point, n_out in work:
-            finals.append(prover.prove_einsum(eq, dims, [b.ptr for b in bufs], point, h)[3])
+            if native:   # the whole device sequence of the block in one library call
+                finals.append(prove_einsum_native(prover, eq, dims, [b.ptr for b in bufs], point, h)[3])
+            else:        # the same sequence issued call by call, as the reference's Rust issues it
+                finals.append(prover.prove_einsum(eq, dims, [b.ptr for b in bufs], point, h)[3])
             if commit and n_out >= 6:   # the digit planes of a smaller tensor start at its own plane stride
                 assert lib.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, 1 << (n_out - 6), L, 0, d_o.ptr) == 0
         lib.agl_transcript_destroy(h)
@@ -770,6 +775,10 @@ def run_llama_layer(args):
     kernels = {l.split()[0]: round(float(l.split()[2]) / args.steps, 4) for l in buf.value.decode().splitlines() if len(l.split()) == 3}
     lib.mb_prof_enable(0)
     ms_prove = timed(lambda: step(False), args.steps)
+    native_final = [int(x) for x in finals[-1]]
+    step(True, False)
+    ms_calls = timed(lambda: step(True, False), args.steps)
+    same = native_final == [int(x) for x in finals[-1]]
     t_end = time.perf_counter() + 2.0
     while not sampler.lines and time.perf_counter() < t_end:
         step()
@@ -787,6 +796,10 @@ def run_llama_layer(args):
                        "operand_elems": int(n_in), "committed_elems": int(n_out_total),
                        "l2": "2.2 GB of distinct operands per step, larger than L2"},
             "prove_only_ms_per_step": ms_prove / args.steps, "kernel_ms_per_step": kernels,
+            "kernel_ms_total": sum(kernels.values()),
+            "call_by_call_ms_per_step": ms_calls / args.steps,
+            "call_by_call_note": "the same sequence issued one synchronising C-ABI call at a time (how the reference's Rust "
+                                 "drives it); ms_per_step is one library call per einsum block; last final evaluation equal: %s" % same,
             "e2e": {"value": ms / args.steps, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "weights and activations are resident in the reference's prover too (device weight cache); "
                             "per proof only challenges go up and round messages come back, inside the timed step"},

@@ -378,6 +378,28 @@ int agl_transcript_challenge_scalar(void* transcript, const uint8_t* label, size
 int agl_transcript_challenge_vector(void* transcript, const uint8_t* label, size_t label_len, uint64_t* out, size_t n);
 int agl_transcript_state(const void* transcript, uint64_t* out12);
 
+/* ---- addition: the device sequence of one einsum block's proof in one call (Einsum::prove_gpu,
+ * zk-torch-4/src/basicblock/einsum.rs:1168-1310, which issues these steps from Rust one synchronising FFI call each):
+ * per operand the partial evaluation at the output point's coordinates that belong to it alone (plain when those are its
+ * low variables: d_lut_lo null; fused with the bit permutation of partial_eval.rs:283-321 otherwise), the eq table of the
+ * output variables two operands share (a table of ones when num_shared = 0), the tables tiled over the variables an
+ * operand does not depend on, then agl_sumcheck_prove_device_ffi over the num_operands + 1 tables of 2^rounds
+ * elements on `transcript`. An operand's table variables are the lowest n - m of the block's. h_point: the output
+ * point, (c0, c1) per variable; fixed_idx (per operand m entries from fixed_off) and shared_idx index its variables.
+ * Host outputs as agl_sumcheck_prove_device_ffi with d = num_operands + 1. */
+typedef struct mb_einsum_operand {
+    const uint64_t* d_src;      /* 2^n base-field words */
+    const uint32_t* d_lut_lo;   /* split index tables of the permutation, or null for the identity */
+    const uint32_t* d_lut_hi;
+    int n;                      /* variables of the operand */
+    int m;                      /* of which fixed to coordinates of the point (the first m of the new order) */
+    int fixed_off;              /* offset of this operand's m indices in fixed_idx */
+    int reserved;
+} mb_einsum_operand;
+int agl_einsum_prove_device_ffi(int num_operands, const mb_einsum_operand* ops, const int* fixed_idx, int rounds, int num_shared,
+                                const int* shared_idx, const uint64_t* h_point, int point_vars, void* transcript,
+                                uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_evals, uint64_t* final_eval);
+
 /* ---- addition: the same-point sumcheck as a whole protocol (the host loop the reference keeps in Rust:
  * zk-torch-4/src/fold/same_point_sumcheck.rs:58-157 prover and labels, :1334-1553 device path over the batched
  * kernels above, :161-219 verifier). num_leaves instances of one arity, each with its own claim point and claim

@@ -57,6 +57,7 @@ LIBRARIES = {
         "host/agl_transcript.cu",
         "host/agl_sumcheck_prover.cu",
         "host/agl_same_point_prover.cu",
+        "host/agl_einsum_prover.cu",
     ],
 }
 

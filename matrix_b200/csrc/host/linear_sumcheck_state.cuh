@@ -14,8 +14,13 @@
 //    after a fold only reads (d+1) extension elements back.
 // Base / Ext are the field traits of sumcheck_kernels.cuh (GlBase, GlExt2) or
 // agl_traits.cuh (AglBase, AglExt2).
+//  * once a table is down to HOST_TAIL elements the live tables are read back and the remaining rounds run on
+//    the host: a round on the device costs a launch and a synchronisation (about 27 us) whatever its size, the
+//    same round on 128 elements takes a host core a few microseconds. The field arithmetic is exact, so the
+//    messages are the same words.
 #pragma once
 #include <vector>
+#include "../agl_field.cuh"
 #include "../gl_sumcheck_launch.cuh"
 #include "ext2_words.hpp"
 
@@ -23,6 +28,23 @@ namespace mbhost {
 
 using namespace mb;
 using namespace mb::sc;
+
+// Host-side extension arithmetic for the tail rounds, by element type.
+template <class T> struct HostExt;
+template <> struct HostExt<gl::E2> {
+    static gl::E2 add(gl::E2 a, gl::E2 b) { return gl::e2_add(a, b); }
+    static gl::E2 sub(gl::E2 a, gl::E2 b) { return gl::e2_sub(a, b); }
+    static gl::E2 mul(gl::E2 a, gl::E2 b) { return gl::e2_mul(a, b); }
+    static gl::E2 canon(gl::E2 a) { return gl::e2_canon(a); }
+};
+template <> struct HostExt<agl::E2> {
+    static agl::E2 add(agl::E2 a, agl::E2 b) { return agl::e2_add(a, b); }
+    static agl::E2 sub(agl::E2 a, agl::E2 b) { return agl::e2_sub(a, b); }
+    static agl::E2 mul(agl::E2 a, agl::E2 b) { return agl::e2_mul(a, b); }
+    static agl::E2 canon(agl::E2 a) { return agl::e2_canon(a); }
+};
+
+constexpr size_t HOST_TAIL = 128;   // live elements per table at which the rounds move to the host
 
 template <class Base, class Ext>
 class LinearSumcheckState {
@@ -41,6 +63,7 @@ public:
         src_ = d_tables;
         round_ = 0;
         cur_ = nullptr;
+        host_mode_ = false;
         size_t cap_a = n_ >= 2 ? n_ / 2 : 1, cap_b = n_ >= 4 ? n_ / 4 : 1;
         stride_a_ = cap_a;
         stride_b_ = cap_b;
@@ -64,6 +87,7 @@ public:
     int compute_round_message(std::vector<Ext2>& out) {
         if (round_ >= num_vars_) return MB_ERR_ARG;
         size_t live = n_ >> round_, half = live / 2;
+        if (host_mode_) return host_message(out, half);
         if (!have_msg_) {
             // Only round 0 gets here: every fold leaves the next message behind.
             int grid = prover_grid(half);
@@ -96,6 +120,19 @@ public:
         size_t live = n_ >> round_, half = live / 2, quarter = live / 4;
         const typename Ext::WordCanon canon;
         typename Ext::T r{canon(challenge.c0), canon(challenge.c1)};
+        if (!host_mode_ && round_ >= 1 && live <= HOST_TAIL) {
+            int rc = to_host(live);
+            if (rc != MB_OK) return rc;
+        }
+        if (host_mode_) {
+            using H = HostExt<typename Ext::T>;
+            for (int i = 0; i < d_; i++) {
+                typename Ext::T* t = host_tab_.data() + (size_t)i * host_stride_;
+                for (size_t j = 0; j < half; j++) t[j] = H::canon(H::add(t[2 * j], H::mul(r, H::sub(t[2 * j + 1], t[2 * j]))));
+            }
+            round_++;
+            return MB_OK;
+        }
         const uint64_t* in = round_ == 0 ? src_ : cur_;
         size_t stride_in = round_ == 0 ? n_ : cur_stride_;
         bool to_a = (round_ == 0) || (cur_ == buf_b_);
@@ -133,6 +170,14 @@ public:
     int final_evaluations(std::vector<Ext2>& out) {
         if (round_ != num_vars_) return MB_ERR_ARG;
         out.resize(d_);
+        if (host_mode_) {
+            for (int i = 0; i < d_; i++) {
+                const typename Ext::T v = host_tab_[(size_t)i * host_stride_];
+                out[i].c0 = v.c0;
+                out[i].c1 = v.c1;
+            }
+            return MB_OK;
+        }
         for (int i = 0; i < d_; i++) {
             uint64_t w[2] = {0, 0};
             if (num_vars_ == 0) {
@@ -154,6 +199,48 @@ public:
     int current_round() const { return round_; }
 
 private:
+    // The live elements of the (extension) tables come to the host; the rounds continue there.
+    int to_host(size_t live) {
+        host_stride_ = live;
+        host_tab_.resize((size_t)d_ * live);
+        for (int i = 0; i < d_; i++)
+            MB_CUDA(cudaMemcpyAsync(host_tab_.data() + (size_t)i * live, cur_ + 2 * (size_t)i * cur_stride_, 16 * live,
+                                    cudaMemcpyDeviceToHost, MB_STREAM));
+        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        const typename Ext::WordCanon canon;
+        for (auto& v : host_tab_) v = typename Ext::T{canon(v.c0), canon(v.c1)};
+        host_mode_ = true;
+        have_msg_ = false;
+        return MB_OK;
+    }
+    // P(c) = sum_j prod_i (t_i[2j] + c (t_i[2j+1] - t_i[2j])), c = 0..d, on the host tables.
+    int host_message(std::vector<Ext2>& out, size_t half) {
+        using H = HostExt<typename Ext::T>;
+        using T = typename Ext::T;
+        std::vector<T> acc(d_ + 1, T{0, 0});
+        T val[MAX_D], diff[MAX_D];
+        for (size_t j = 0; j < half; j++) {
+            for (int i = 0; i < d_; i++) {
+                const T* t = host_tab_.data() + (size_t)i * host_stride_;
+                val[i] = t[2 * j];
+                diff[i] = H::sub(t[2 * j + 1], t[2 * j]);
+            }
+            for (int c = 0; c <= d_; c++) {
+                T p = val[0];
+                for (int i = 1; i < d_; i++) p = H::mul(p, val[i]);
+                acc[c] = H::add(acc[c], p);
+                for (int i = 0; i < d_; i++) val[i] = H::add(val[i], diff[i]);
+            }
+        }
+        out.resize(d_ + 1);
+        for (int c = 0; c <= d_; c++) {
+            const T v = H::canon(acc[c]);
+            out[c].c0 = v.c0;
+            out[c].c1 = v.c1;
+        }
+        return MB_OK;
+    }
+
     void release() {
         pool_free(buf_a_);
         pool_free(buf_b_);
@@ -171,6 +258,9 @@ private:
     uint64_t *buf_a_ = nullptr, *buf_b_ = nullptr, *cur_ = nullptr, *partial_ = nullptr, *msg_dev_ = nullptr;
     unsigned int* counter_ = nullptr;
     uint64_t* msg_host_ = nullptr;
+    bool host_mode_ = false;
+    size_t host_stride_ = 0;
+    std::vector<typename Ext::T> host_tab_;
 };
 
 }  // namespace mbhost

@@ -363,6 +363,8 @@ _AGL_SIGNATURES = {
     "aext2_sumcheck_batched_fold_message_ffi": (c_int, [c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t, c_int, c_int, c_void_p]),
     "aext2_sumcheck_batched_round0_binary_fold_message_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_u64, c_u64, c_size_t, c_size_t,
                                                                       c_int, c_int, c_size_t, c_void_p]),
+    "agl_einsum_prove_device_ffi": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_void_p]),
     "agl_same_point_claims_device_ffi": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "agl_same_point_verify_ffi": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_void_p, ctypes.POINTER(c_int)]),

@@ -190,6 +190,53 @@ class LayerProver:
         return msgs[:rounds * (d + 1) * 2], ch[:2 * rounds], fe, fin
 
 
+class _EinsumOperand(ctypes.Structure):
+    """mb_einsum_operand of include/almost_goldilocks_cuda_wrapper.h."""
+    _fields_ = [("d_src", ctypes.c_void_p), ("d_lut_lo", ctypes.c_void_p), ("d_lut_hi", ctypes.c_void_p),
+                ("n", ctypes.c_int), ("m", ctypes.c_int), ("fixed_off", ctypes.c_int), ("reserved", ctypes.c_int)]
+
+
+def _native_plan(prover, equation, dims):
+    """The flat form of a plan that agl_einsum_prove_device_ffi takes: operand records (sources filled per call),
+    the indices of every operand's fixed output variables and of the shared ones. Cached on the plan."""
+    pl = prover.plan(equation, dims)
+    if getattr(pl, "native", None) is None:
+        out_bits = _bits(pl.out, pl.dims)
+        ops = (_EinsumOperand * len(pl.inputs))()
+        fixed = []
+        for k in range(len(pl.inputs)):
+            order, nmine = pl.operand_order(k)
+            if pl.table_vars[:nmine] != [v for v in pl.table_vars if v in _bits(pl.inputs[k], pl.dims)]:
+                raise ValueError("operand lacks an inner table variable: " + equation)
+            ops[k].n, ops[k].m, ops[k].fixed_off = len(order), len(pl.fixed[k]), len(fixed)
+            if pl.luts[k] is not None:
+                ops[k].d_lut_lo, ops[k].d_lut_hi = pl.luts[k][0].ptr, pl.luts[k][1].ptr
+            fixed += [out_bits.index(v) for v in pl.fixed[k]]
+        pl.native = (ops, (ctypes.c_int * max(len(fixed), 1))(*fixed),
+                     (ctypes.c_int * max(len(pl.shared), 1))(*[out_bits.index(v) for v in pl.shared]), len(out_bits))
+    return pl
+
+
+def prove_einsum_native(prover, equation, dims, operands, point, transcript):
+    """LayerProver.prove_einsum with the whole device sequence inside the library (agl_einsum_prove_device_ffi):
+    one call per einsum block, nothing synchronises before the sumcheck's first message. Same outputs."""
+    lib = prover.lib
+    pl = _native_plan(prover, equation, dims)
+    ops, fixed, shared, nvars = pl.native
+    for k, src in enumerate(operands):
+        ops[k].d_src = src
+    point = np.ascontiguousarray(point, dtype=np.uint64).reshape(nvars, 2)
+    rounds, d = pl.rounds, len(pl.inputs) + 1
+    msgs = np.zeros(max(rounds, 1) * (d + 1) * 2, dtype=np.uint64)
+    ch = np.zeros(max(rounds, 1) * 2, dtype=np.uint64)
+    fe, fin = np.zeros(2 * d, dtype=np.uint64), np.zeros(2, dtype=np.uint64)
+    rc = lib.agl_einsum_prove_device_ffi(len(pl.inputs), ops, fixed, rounds, len(pl.shared), shared, point.ctypes.data, nvars,
+                                         transcript, msgs.ctypes.data, ch.ctypes.data, fe.ctypes.data, fin.ctypes.data)
+    if rc != 0:
+        raise RuntimeError("agl_einsum_prove_device_ffi of %s failed: %d" % (equation, rc))
+    return msgs[:rounds * (d + 1) * 2], ch[:2 * rounds], fe, fin
+
+
 def synthetic_operand(seed, n_log):
     """2^n_log fixed-point values in [-2^15, 2^15) as canonical field elements (negatives as q - |v|)."""
     v = (splitmix64(seed, 1 << n_log) & np.uint64(0xFFFF)).astype(np.int64) - (1 << 15)

@@ -93,3 +93,37 @@ def test_einsum_proof_verifies_against_direct_claim(equation, dims):
     for i in range(d):
         prod = _mul(prod, (int(fe[2 * i]), int(fe[2 * i + 1])))
     assert (int(fin[0]), int(fin[1])) == prod
+
+
+NATIVE_CASES = CASES + [("si,ij->sj", dict(s=4, i=7, j=6)), ("hsd,htd->hst", dict(h=2, s=3, t=3, d=4)),
+                        ("hst,htd->hsd", dict(h=2, s=3, t=4, d=3)), ("si,si->si", dict(s=5, i=8))]
+
+
+@pytest.mark.parametrize("equation,dims", NATIVE_CASES, ids=[c[0] + str(i) for i, c in enumerate(NATIVE_CASES)])
+def test_one_call_per_einsum_equals_the_step_by_step_sequence(equation, dims):
+    """agl_einsum_prove_device_ffi (the whole device sequence inside the library) against the same sequence issued
+    call by call from Python, bit for bit, on two einsums sharing one transcript."""
+    from matrix_b200.layer_trace import prove_einsum_native
+    lib = load_agl()
+    prover = LayerProver(lib)
+    pl = EinsumPlan(equation, dims)
+    ops = [synthetic_operand(140 + k, sum(dims[c] for c in t)) for k, t in enumerate(pl.inputs)]
+    bufs = [DeviceBuffer.from_numpy(lib, o) for o in ops]
+    n_out = sum(dims[c] for c in pl.out)
+    results = []
+    for fn in (lambda *a: prover.prove_einsum(*a), lambda *a: prove_einsum_native(prover, *a)):
+        h = ctypes.c_void_p()
+        assert lib.agl_transcript_create(b"layer", 5, ctypes.byref(h)) == 0
+        outs = []
+        for seed in (77, 78):
+            point = field_elems(seed, 2 * max(n_out, 1), Q)[:2 * n_out].reshape(n_out, 2)
+            outs.append(fn(equation, dims, [b.ptr for b in bufs], point, h))
+        st = np.zeros(12, dtype=np.uint64)
+        assert lib.agl_transcript_state(h, st.ctypes.data) == 0
+        lib.agl_transcript_destroy(h)
+        results.append((outs, st))
+    (a_outs, a_st), (b_outs, b_st) = results
+    assert np.array_equal(a_st, b_st)
+    for x, y in zip(a_outs, b_outs):
+        for u, v in zip(x, y):
+            assert np.array_equal(u, v)
