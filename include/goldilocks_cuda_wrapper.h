@@ -286,6 +286,16 @@ int basefold_open_ext2(const void* commitment, const uint64_t* h_point, const vo
 int basefold_prove_host(const uint64_t* h_evals, int num_vars, int log_rate, const uint64_t* h_point,
                         const void* table, const uint8_t* label, size_t label_len, int num_queries, uint64_t* h_root,
                         uint64_t* h_proof);
+/* Verifier of an opening (BasefoldProver::verify_ext2, goldilocks-cuda-rs/src/basefold.rs:1759-1925, query checks
+ * :2222-2402), on the host: transcript replay, the inner sumcheck's oracle chain, and per query the commitment path,
+ * the fold consistency at every round, the folded trees' paths and the final codeword. The table's (point, weight)
+ * pairs at the queried positions come from the device table in one gather. merkle_hash: 0 Poseidon2, 1 Monolith,
+ * negative = the current basefold_set_merkle_hash setting. *result = 0 accepted; -1 claimed value, -(10+i) oracle
+ * chain at round i, -100 query index, -101 commitment path, -(200+i) fold at round i, -(300+i) folded-tree path at
+ * round i, -400 final codeword. The return value reports only argument / CUDA errors. */
+int basefold_verify_host(const uint64_t* h_root, int num_vars, int log_rate, const uint64_t* h_point, const void* table,
+                         const uint8_t* label, size_t label_len, int num_queries, int merkle_hash,
+                         const uint64_t* h_proof, int* result);
 
 /* ---- additions: one commitment + opening shared by several GPUs ----
  * No counterpart in the reference, which runs one whole prover per device

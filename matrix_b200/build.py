@@ -38,6 +38,7 @@ LIBRARIES = {
         "host/gl_sumcheck_prover.cu",
         "host/gl_basefold_prover.cu",
         "host/gl_basefold_sharded.cu",
+        "host/gl_basefold_verifier.cu",
         "host/exchange.cu",
         "host/gl_batched_prover.cu",
     ],
