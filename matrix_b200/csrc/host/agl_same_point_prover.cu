@@ -256,6 +256,7 @@ int same_point_prove(int M, int arity, const uint64_t* h_pts, const uint64_t* h_
     for (int i = 0; i < M; i++) { alphas[i] = pw; pw = e2c(agl::e2_mul(pw, alpha)); }
 
     std::vector<E2> R(arity);
+    bool label_absorbed = false;
     uint64_t* cur = buf.a;
     uint64_t* other = buf.b;
     for (int round = 0; round < arity; round++) {
@@ -268,7 +269,8 @@ int same_point_prove(int M, int arity, const uint64_t* h_pts, const uint64_t* h_
             for (int c = 0; c < 3; c++) msg[c] = agl::e2_add(msg[c], agl::e2_mul(alphas[i], ld(h_sums + (size_t)i * 6 + 2 * c)));
         for (int c = 0; c < 3; c++) {
             msg[c] = e2c(msg[c]);
-            t.append_ext2(SP_LABEL(L_MSG), msg[c].c0, msg[c].c1);
+            if (c > 0 || !label_absorbed) t.begin_append(SP_LABEL(L_MSG));
+            t.finish_append_ext2(msg[c].c0, msg[c].c1);
             h_round_msgs[((size_t)round * 3 + c) * 2] = msg[c].c0;
             h_round_msgs[((size_t)round * 3 + c) * 2 + 1] = msg[c].c1;
         }
@@ -281,6 +283,9 @@ int same_point_prove(int M, int arity, const uint64_t* h_pts, const uint64_t* h_
             rc = bits ? aext2_sumcheck_batched_round0_binary_fold_ffi(cur, d_w0, other, r.c0, r.c1, n, half, M, words)
                       : aext2_sumcheck_batched_fold_ffi(cur, other, r.c0, r.c1, n, half, M);
         if (rc != MB_OK) return rc;
+        // the next message's first label is absorbed while the fold runs
+        label_absorbed = round + 1 < arity;
+        if (label_absorbed) t.begin_append(SP_LABEL(L_MSG));
         uint64_t* tmp = cur; cur = other; other = tmp;
     }
     // reveals f_i(R): element 0 of every leaf's f table

@@ -55,11 +55,13 @@ static int prove_linear(const uint64_t* d_tables, int d, int num_var, bool base_
     int rc = st.init_device(d_tables, d, num_var, base_field);
     if (rc != MB_OK) return rc;
     std::vector<Ext2> msg;
+    bool label_absorbed = false;   // the first label of a round goes in while the round's kernel runs
     for (int round = 0; round < num_var; round++) {
         rc = st.compute_round_message(msg);
         if (rc != MB_OK) return rc;
         for (int c = 0; c <= d; c++) {
-            t.append_ext2(L_MSG, sizeof(L_MSG) - 1, msg[c].c0, msg[c].c1);
+            if (c > 0 || !label_absorbed) t.begin_append(L_MSG, sizeof(L_MSG) - 1);
+            t.finish_append_ext2(msg[c].c0, msg[c].c1);
             round_msgs[((size_t)round * (d + 1) + c) * 2] = msg[c].c0;
             round_msgs[((size_t)round * (d + 1) + c) * 2 + 1] = msg[c].c1;
         }
@@ -70,6 +72,8 @@ static int prove_linear(const uint64_t* d_tables, int d, int num_var, bool base_
         }
         rc = st.fold(r);
         if (rc != MB_OK) return rc;
+        label_absorbed = round + 1 < num_var;
+        if (label_absorbed) t.begin_append(L_MSG, sizeof(L_MSG) - 1);
     }
     std::vector<Ext2> fe;
     rc = st.final_evaluations(fe);

@@ -57,32 +57,56 @@ inline uint64_t bar(uint64_t x) {
     return ((t & 0x8080808080808080ULL) >> 7) | ((t & 0x7F7F7F7F7F7F7F7FULL) << 1);
 }
 
-// Circulant MDS (first row 7 23 8 26 13 10 9 7 6 22 21 8) on 32-bit halves: both
-// limb sums stay below 161 * 2^32 < 2^40 and each output is reduced once.
+// Host arithmetic of the permutation. A round loop's host side is a chain of these permutations between two kernel
+// launches, so this is written for a host core (64 x 64 -> 128 multiplier, 128-bit sums, no unpredictable branches)
+// rather than shared with the device's 32-bit limb forms.
+typedef unsigned __int128 u128;
+
+// lo + hi c for a high word below 2^31, loose result: one carry repair (the wrapped sum is below hi c).
+inline uint64_t reduce_small(u128 x) {
+    const uint64_t lo = (uint64_t)x, t = (uint64_t)(x >> 64) * agl::C;
+    uint64_t r = lo + t;
+    r += (0 - (uint64_t)(r < t)) & agl::C;
+    return r;
+}
+// Any 128-bit value: two folds of the high word (2^64 = c) bring it below 2^34 and then below 8.
+inline uint64_t reduce_wide(u128 x) {
+    x = (u128)(uint64_t)(x >> 64) * agl::C + (uint64_t)x;
+    x = (u128)(uint64_t)(x >> 64) * agl::C + (uint64_t)x;
+    return reduce_small(x);
+}
+
+// Row I of the circulant MDS (first row 7 23 8 26 13 10 9 7 6 22 21 8) plus the round constant: a 128-bit sum
+// below 161 * 2^64, reduced once.
+template <int I>
+inline uint64_t concrete_row(const uint64_t* s, uint64_t rc) {
+    constexpr uint32_t C2[2 * WIDTH] = {7, 23, 8, 26, 13, 10, 9, 7, 6, 22, 21, 8, 7, 23, 8, 26, 13, 10, 9, 7, 6, 22, 21, 8};
+    u128 acc = rc;
+    for (int j = 0; j < WIDTH; j++) acc += (u128)s[j] * C2[j - I + WIDTH];
+    return reduce_small(acc);
+}
 inline void concrete(uint64_t* s, const uint64_t* rc) {
-    static const uint32_t C[WIDTH] = {7, 23, 8, 26, 13, 10, 9, 7, 6, 22, 21, 8};
-    uint64_t out[WIDTH];
-    for (int i = 0; i < WIDTH; i++) {
-        uint64_t L = agl::lo32(rc[i]), H = agl::hi32(rc[i]);
-        for (int j = 0; j < WIDTH; j++) {
-            const uint32_t m = C[(j - i + WIDTH) % WIDTH];
-            L += (uint64_t)agl::lo32(s[j]) * m;
-            H += (uint64_t)agl::hi32(s[j]) * m;
-        }
-        out[i] = agl::canon(agl::reduce_limb_sums(L, H));
-    }
-    std::memcpy(s, out, sizeof(out));
+    uint64_t o[WIDTH];
+    o[0] = concrete_row<0>(s, rc[0]);   o[1] = concrete_row<1>(s, rc[1]);   o[2] = concrete_row<2>(s, rc[2]);
+    o[3] = concrete_row<3>(s, rc[3]);   o[4] = concrete_row<4>(s, rc[4]);   o[5] = concrete_row<5>(s, rc[5]);
+    o[6] = concrete_row<6>(s, rc[6]);   o[7] = concrete_row<7>(s, rc[7]);   o[8] = concrete_row<8>(s, rc[8]);
+    o[9] = concrete_row<9>(s, rc[9]);   o[10] = concrete_row<10>(s, rc[10]); o[11] = concrete_row<11>(s, rc[11]);
+    std::memcpy(s, o, sizeof(o));
 }
 
 // In place; any 64-bit words in, canonical residues out (crypto/monolith.rs:201-208).
 inline void permute(uint64_t* s) {
-    const uint64_t(*rc)[WIDTH] = round_constants();
+    static const uint64_t(*const rc)[WIDTH] = round_constants();
     concrete(s, rc[0]);
     for (int r = 1; r <= N_ROUNDS; r++) {
-        for (int i = 0; i < 4; i++) s[i] = bar(s[i]);
-        for (int i = WIDTH - 1; i >= 1; i--) s[i] = agl::add(s[i], agl::sqr(s[i - 1]));
+        for (int i = 0; i < 4; i++) s[i] = bar(s[i] >= agl::P ? s[i] - agl::P : s[i]);   // bars act on the canonical word
+        // bricks: s_i += s_{i-1}^2 on the values before the layer
+        uint64_t sq[WIDTH];
+        for (int i = 1; i < WIDTH; i++) sq[i] = reduce_wide((u128)s[i - 1] * s[i - 1]);
+        for (int i = 1; i < WIDTH; i++) s[i] = reduce_small((u128)s[i] + sq[i]);
         concrete(s, rc[r]);
     }
+    for (int i = 0; i < WIDTH; i++) s[i] = s[i] >= agl::P ? s[i] - agl::P : s[i];
 }
 
 class Transcript {
@@ -103,6 +127,10 @@ public:
         absorb(agl::canon(c0));
         absorb(agl::canon(c1));
     }
+    // append_ext2 in two halves, for a caller that knows the label before the value exists (a round loop absorbs
+    // the next message's label while the kernel that computes the message runs).
+    void begin_append(const uint8_t* l, size_t n) { absorb_label(l, n); }
+    void finish_append_ext2(uint64_t c0, uint64_t c1) { absorb(agl::canon(c0)); absorb(agl::canon(c1)); }
     uint64_t challenge_scalar(const uint8_t* l, size_t n) { absorb_label(l, n); return squeeze(); }
     void challenge_vector(const uint8_t* l, size_t n, uint64_t* out, size_t count) {
         absorb_label(l, n);

@@ -180,7 +180,7 @@ struct Digest {
 Digest host_compress(int hash, const Digest& l, const Digest& r) {
     uint64_t s[12] = {l.w[0], l.w[1], l.w[2], l.w[3], r.w[0], r.w[1], r.w[2], r.w[3], 0, 0, 0, 0};
     if (hash) gl::monolith_permute(s);
-    else gl::poseidon2_permute(s);
+    else p2host::permute(s);
     Digest d;
     for (int i = 0; i < 4; i++) d.w[i] = gl::canon(s[i]);
     return d;

@@ -24,7 +24,7 @@ struct Dg {
 };
 inline void permute(int hash, uint64_t* s) {
     if (hash) gl::monolith_permute(s);
-    else gl::poseidon2_permute(s);
+    else p2host::permute(s);
 }
 inline Dg digest_of(int hash, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {   // leaf of two elements (base: c = d = 0)
     uint64_t s[12] = {a, b, c, d, 0, 0, 0, 0, 0, 0, 0, 0};

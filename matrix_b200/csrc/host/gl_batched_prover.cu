@@ -356,9 +356,11 @@ int batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const uint
 
     RoundClock clock;
     int round = 0;
+    bool label_absorbed = false;   // the first label of a round goes in while the round's kernel runs
     auto publish = [&](const E2* msg) {
         for (int c = 0; c < 4; c++) {
-            tr.append_ext2("sp_round_msg", Ext2{msg[c].c0, msg[c].c1});
+            if (c > 0 || !label_absorbed) tr.begin_append("sp_round_msg");
+            tr.finish_append_ext2(Ext2{msg[c].c0, msg[c].c1});
             if (h_round_msgs) {
                 h_round_msgs[(size_t)round * 8 + 2 * c] = msg[c].c0;
                 h_round_msgs[(size_t)round * 8 + 2 * c + 1] = msg[c].c1;
@@ -367,6 +369,7 @@ int batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const uint
         const Ext2 r = tr.challenge_ext2("sp_round_challenge");
         if (h_challenges) { h_challenges[2 * (size_t)round] = r.c0; h_challenges[2 * (size_t)round + 1] = r.c1; }
         round++;
+        label_absorbed = false;
         return r;
     };
     for (int i = 0; i < n_loc; i++) {
@@ -387,6 +390,10 @@ int batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const uint
         clock.stop(clock.host);
         rc = st.fold(r);
         if (rc != MB_OK) return rc;
+        if (round < num_vars) {
+            tr.begin_append("sp_round_msg");
+            label_absorbed = true;
+        }
     }
     // one value per table and rank: eq, alpha^k a_k, b_k; the top variables are finished on the host
     clock.start();

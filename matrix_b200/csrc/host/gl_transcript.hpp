@@ -10,7 +10,7 @@
 #include <cstdint>
 #include <cstring>
 #include <string>
-#include "../gl_poseidon2.cuh"
+#include "gl_poseidon2_host.hpp"
 #include "ext2_words.hpp"
 
 namespace mbhost {
@@ -26,6 +26,10 @@ public:
     void append_scalar(const char* label, uint64_t v) { absorb_label(label); absorb(v); }
     void append_u64(const char* label, uint64_t v) { absorb_label(label); absorb(v); }
     void append_ext2(const char* label, Ext2 v) { absorb_label(label); absorb(v.c0); absorb(v.c1); }
+    // append_ext2 in two halves, for a caller that knows the label before the value exists (a round loop absorbs
+    // the next message's label while the kernel that computes the message runs).
+    void begin_append(const char* label) { absorb_label(label); }
+    void finish_append_ext2(Ext2 v) { absorb(v.c0); absorb(v.c1); }
     uint64_t challenge_scalar(const char* label) { absorb_label(label); return squeeze(); }
     Ext2 challenge_ext2(const char* label) {
         absorb_label(label);
@@ -71,8 +75,7 @@ private:
         for (int i = 0; i < in_count_; i++) sponge_[i] = in_buf_[i];
         for (int i = in_count_; i < 4; i++) sponge_[i] = 0;
         in_count_ = 0;
-        gl::poseidon2_permute(sponge_);
-        for (int i = 0; i < 8; i++) sponge_[i] = gl::canon(sponge_[i]);
+        p2host::permute(sponge_);   // canonical out
         perms_++;
         for (int i = 0; i < 4; i++) out_buf_[3 - i] = sponge_[i];
         out_count_ = 4;

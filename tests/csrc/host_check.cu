@@ -58,6 +58,11 @@ void hc_mcm_key_block(const uint32_t* seed, uint32_t kind, uint32_t row, uint64_
     mcm::key_block8(seed, kind, row, col, b, vals);
 }
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
+// the host-side form (transcripts, tree tops) and the reductions underneath both host permutations
+void hc_poseidon2_host(uint64_t* s) { mbhost::p2host::permute(s); }
+uint64_t hc_p2host_red(uint64_t lo, uint64_t hi) { return mbhost::p2host::red(((unsigned __int128)hi << 64) | lo); }
+uint64_t hc_aglm_reduce_wide(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_wide(((unsigned __int128)hi << 64) | lo); }
+uint64_t hc_aglm_reduce_small(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_small(((unsigned __int128)hi << 64) | lo); }
 // sum_i x[i] * y[i] + c through the lazy accumulator
 uint64_t hc_gl_dot(const uint64_t* x, const uint64_t* y, int n, uint64_t c) {
     gl::Acc s = gl::acc_from(c);

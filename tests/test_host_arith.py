@@ -94,6 +94,34 @@ def test_poseidon2_matches_oracle(hostcheck, oracle):
         assert [x % P for x in a] == list(b)
 
 
+def test_host_form_of_poseidon2_and_its_reductions(hostcheck, oracle):
+    """Transcripts and tree tops run a permutation written for a host core (128-bit products); it must be the
+    same function as the device form and the oracle on canonical, loose and extreme words."""
+    AGL_P = 2**64 - 2**32 - 31
+    rnd = random.Random(19)
+    edge = [0, 1, P - 1, P, P + 1, 2**64 - 1, 2**64 - 2**32, 2**32 - 1, 2**32, 2**63]
+    cases = [[e] * 8 for e in edge] + [[rnd.choice(edge) for _ in range(8)] for _ in range(40)]
+    cases += [[rnd.randrange(2**64) for _ in range(8)] for _ in range(200)]
+    for inp in cases:
+        a, b, c = (u64 * 8)(*inp), (u64 * 8)(*inp), (u64 * 8)(*[x % P for x in inp])
+        hostcheck.hc_poseidon2_host(a)
+        hostcheck.hc_poseidon2(b)
+        oracle.gl_poseidon2_permute(c)
+        assert list(a) == [x % P for x in b] == list(c)
+    for f in (hostcheck.hc_p2host_red, hostcheck.hc_aglm_reduce_wide, hostcheck.hc_aglm_reduce_small):
+        f.restype, f.argtypes = u64, [u64, u64]
+    words = edge + [AGL_P - 1, AGL_P, AGL_P + 1, 2**64 - 32, 2**64 - 31]
+    pairs = [(lo, hi) for lo in words for hi in words] + [(rnd.randrange(2**64), rnd.randrange(2**64)) for _ in range(2000)]
+    for lo, hi in pairs:
+        x = lo + (hi << 64)
+        assert hostcheck.hc_p2host_red(lo, hi) % P == x % P
+        assert hostcheck.hc_aglm_reduce_wide(lo, hi) % AGL_P == x % AGL_P
+    # sums of up to 161 words (one row of the MDS layer plus a constant): high word below 2^31
+    for lo in words:
+        for hi in (0, 1, 160, 161, 2**20, 2**31 - 1):
+            assert hostcheck.hc_aglm_reduce_small(lo, hi) % AGL_P == (lo + (hi << 64)) % AGL_P
+
+
 def test_transcript_matches_oracle(hostcheck, oracle):
     # Random scripts of absorbs and squeezes against the oracle's transcript.
     class T(ctypes.Structure):
