@@ -669,14 +669,17 @@ def run_link(args):
     timed = _event_timer(lib)
     for _ in range(max(args.warmup, 3)):
         assert step() == 0
-    lib.mb_prof_enable(1)
-    lib.mb_prof_reset()
     sampler = ClockSampler(local)
     launches0 = lib.mb_launch_count()
     sampler.start()
     lib.cuda_device_synchronize()
-    ms = timed(step, args.steps)
+    ms = timed(step, args.steps)   # the timed region: no per-launch events
     launches = lib.mb_launch_count() - launches0
+    lib.mb_prof_enable(1)          # per-kernel times: a separate pass
+    lib.mb_prof_reset()
+    for _ in range(args.steps):
+        step()
+    lib.cuda_device_synchronize()
     buf = ctypes.create_string_buffer(1 << 16)
     lib.mb_prof_report(buf, len(buf))
     kernels = {l.split()[0]: float(l.split()[2]) / args.steps for l in buf.value.decode().splitlines() if len(l.split()) == 3}
@@ -762,22 +765,26 @@ def run_llama_layer(args):
     timed = _event_timer(lib)
     for _ in range(max(args.warmup, 3)):
         step()
-    lib.mb_prof_enable(1)
-    lib.mb_prof_reset()
     sampler = ClockSampler(local)
     launches0 = lib.mb_launch_count()
     sampler.start()
     lib.cuda_device_synchronize()
-    ms = timed(step, args.steps)
+    ms = timed(lambda: step(), args.steps)   # the timed region: no per-launch events
     launches = lib.mb_launch_count() - launches0
-    buf = ctypes.create_string_buffer(1 << 16)
-    lib.mb_prof_report(buf, len(buf))
-    kernels = {l.split()[0]: round(float(l.split()[2]) / args.steps, 4) for l in buf.value.decode().splitlines() if len(l.split()) == 3}
-    lib.mb_prof_enable(0)
     ms_prove = timed(lambda: step(False), args.steps)
     native_final = [int(x) for x in finals[-1]]
     step(True, False)
     ms_calls = timed(lambda: step(True, False), args.steps)
+    # per-kernel times: a separate pass with events around every launch
+    lib.mb_prof_enable(1)
+    lib.mb_prof_reset()
+    for _ in range(args.steps):
+        step()
+    lib.cuda_device_synchronize()
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.mb_prof_report(buf, len(buf))
+    kernels = {l.split()[0]: round(float(l.split()[2]) / args.steps, 4) for l in buf.value.decode().splitlines() if len(l.split()) == 3}
+    lib.mb_prof_enable(0)
     same = native_final == [int(x) for x in finals[-1]]
     t_end = time.perf_counter() + 2.0
     while not sampler.lines and time.perf_counter() < t_end:

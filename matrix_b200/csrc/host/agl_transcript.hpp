@@ -13,6 +13,7 @@
 #include <mutex>
 #include "../agl_field.cuh"
 #include "sha256.hpp"
+#include "host_field.hpp"
 
 namespace mbhost {
 namespace aglm {
@@ -60,21 +61,9 @@ inline uint64_t bar(uint64_t x) {
 // Host arithmetic of the permutation. A round loop's host side is a chain of these permutations between two kernel
 // launches, so this is written for a host core (64 x 64 -> 128 multiplier, 128-bit sums, no unpredictable branches)
 // rather than shared with the device's 32-bit limb forms.
-typedef unsigned __int128 u128;
-
-// lo + hi c for a high word below 2^31, loose result: one carry repair (the wrapped sum is below hi c).
-inline uint64_t reduce_small(u128 x) {
-    const uint64_t lo = (uint64_t)x, t = (uint64_t)(x >> 64) * agl::C;
-    uint64_t r = lo + t;
-    r += (0 - (uint64_t)(r < t)) & agl::C;
-    return r;
-}
-// Any 128-bit value: two folds of the high word (2^64 = c) bring it below 2^34 and then below 8.
-inline uint64_t reduce_wide(u128 x) {
-    x = (u128)(uint64_t)(x >> 64) * agl::C + (uint64_t)x;
-    x = (u128)(uint64_t)(x >> 64) * agl::C + (uint64_t)x;
-    return reduce_small(x);
-}
+using hf::u128;
+inline uint64_t reduce_small(u128 x) { return hf::agl_red_small(x); }   // high word below 2^31
+inline uint64_t reduce_wide(u128 x) { return hf::agl_red(x); }          // any 128-bit value
 
 // Row I of the circulant MDS (first row 7 23 8 26 13 10 9 7 6 22 21 8) plus the round constant: a 128-bit sum
 // below 161 * 2^64, reduced once.

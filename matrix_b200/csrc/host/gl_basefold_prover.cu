@@ -53,8 +53,9 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
     if (rc != MB_OK) return rc;
     unsigned int* counter = reinterpret_cast<unsigned int*>(small.p + 8);
     MB_CUDA(cudaMemsetAsync(small.p, 0, 16 * sizeof(uint64_t), MB_STREAM));
-    uint64_t* h_small = pinned_scratch();  // landing zone: 6 oracle words + 4 root words
-    if (!h_small) return MB_ERR_CUDA;
+    uint64_t* h_small = pinned_scratch();  // landing zone: 6 oracle words, then (from word 8) the tree's last device layer
+    uint64_t* top_staging = pinned_arena(4 * (HOST_TOP - 1) * (size_t)nv);   // host-hashed tree tops on their way up
+    if (!h_small || !top_staging) return MB_ERR_CUDA;
 
     MB_CUDA(cudaMemcpyAsync(d_point.p, point, sizeof(uint64_t) * 2 * nv, cudaMemcpyHostToDevice, MB_STREAM));
     // eq table; bh_a doubles as scratch for the two small tables (free until round 0 writes it)
@@ -148,13 +149,17 @@ int open_ext2(const BasefoldCommitment& cm, const uint64_t* point, const Basefol
             }
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        rc = cm.hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 8)
-                     : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 8);
+        // the device stops at the layer of HOST_TOP digests; the host hashes the levels above it
+        const size_t leaves = cw_pairs / 2;
+        rc = cm.hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, leaves, MB_STREAM, h_small + 8, HOST_TOP)
+                     : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, leaves, MB_STREAM, h_small + 8, HOST_TOP);
         if (rc != MB_OK) return rc;
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
         uint64_t* po = p_oracles + 6 * (size_t)(round + 1);
         std::memcpy(po, h_small, 48);
-        std::memcpy(p_roots + 4 * (size_t)round, h_small + 8, 32);
+        rc = host_finish_top(cm.hash, h_small + 8, leaves < HOST_TOP ? leaves : HOST_TOP, top_staging + 4 * (HOST_TOP - 1) * (size_t)round,
+                             ftree[round]->p, leaves, p_roots + 4 * (size_t)round, MB_STREAM);
+        if (rc != MB_OK) return rc;
         for (int k = 0; k < 3; k++) t.observe_ext2(Ext2{po[2 * k], po[2 * k + 1]});
         t.observe_hash(p_roots + 4 * (size_t)round);
 

@@ -173,19 +173,6 @@ struct PhaseClock {
     }
 };
 
-struct Digest {
-    uint64_t w[4];
-};
-
-Digest host_compress(int hash, const Digest& l, const Digest& r) {
-    uint64_t s[12] = {l.w[0], l.w[1], l.w[2], l.w[3], r.w[0], r.w[1], r.w[2], r.w[3], 0, 0, 0, 0};
-    if (hash) gl::monolith_permute(s);
-    else p2host::permute(s);
-    Digest d;
-    for (int i = 0; i < 4; i++) d.w[i] = gl::canon(s[i]);
-    return d;
-}
-
 // levels[0] = the given digests, levels[k + 1][j] = compress(levels[k][2j], levels[k][2j+1]).
 std::vector<std::vector<Digest>> host_top_tree(int hash, std::vector<Digest> leaves) {
     std::vector<std::vector<Digest>> levels;
@@ -235,8 +222,9 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
     uint64_t* p_queries = p_final + ((size_t)2 << lr);
 
     std::vector<uint64_t> h_mine, h_all;
-    uint64_t* h_small = pinned_scratch();
-    if (!h_small) return MB_ERR_CUDA;
+    uint64_t* h_small = pinned_scratch();   // words 0..5 oracle, 6..9 subtree root, 16..47 the subtree's last device layer
+    uint64_t* top_staging = pinned_arena(4 * (HOST_TOP - 1) * (size_t)nv);
+    if (!h_small || !top_staging) return MB_ERR_CUDA;
 
     PhaseClock pc;
     // ---- commit ---------------------------------------------------------------------------------
@@ -439,10 +427,15 @@ int prove_sharded(const uint64_t* d_evals, int nv, int lr, const uint64_t* point
             bf::fold_ext2_kernel<<<gf, 256, 0, MB_STREAM>>>(cw_prev, level, r, fcw[round]->p, cw_pairs);
         }
         if (cudaGetLastError() != cudaSuccess) return MB_ERR_CUDA;
-        rc = hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 6)
-                  : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, cw_pairs / 2, MB_STREAM, h_small + 6);
+        // the device stops at the layer of HOST_TOP digests of this rank's (sub)tree; the host hashes the levels above
+        const size_t leaves = cw_pairs / 2;
+        rc = hash ? mk::build_tree<mk::HashMonolith, true>(fcw[round]->p, ftree[round]->p, leaves, MB_STREAM, h_small + 16, HOST_TOP)
+                  : mk::build_tree<mk::HashPoseidon2, true>(fcw[round]->p, ftree[round]->p, leaves, MB_STREAM, h_small + 16, HOST_TOP);
         if (rc != MB_OK) return rc;
         MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+        rc = host_finish_top(hash, h_small + 16, leaves < HOST_TOP ? leaves : HOST_TOP, top_staging + 4 * (HOST_TOP - 1) * (size_t)round,
+                             ftree[round]->p, leaves, h_small + 6, MB_STREAM);
+        if (rc != MB_OK) return rc;
         uint64_t* po = p_oracles + 6 * (size_t)(round + 1);
         uint64_t* pr = p_roots + 4 * (size_t)round;
         if (distributed) {

@@ -7,8 +7,6 @@
 // gather kernel after the query indices are known.
 #include <cstring>
 #include <vector>
-#include "../gl_monolith.cuh"
-#include "../gl_poseidon2.cuh"
 #include "gl_basefold_common.cuh"
 #include "gl_transcript.hpp"
 
@@ -19,28 +17,12 @@ namespace {
 
 using gl::E2;
 
-struct Dg {
-    uint64_t w[4];
-};
-inline void permute(int hash, uint64_t* s) {
-    if (hash) gl::monolith_permute(s);
-    else p2host::permute(s);
+inline Digest digest_of(int hash, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {   // leaf of two elements (base: c = d = 0)
+    const uint64_t l[4] = {a, b, c, d}, z[4] = {0, 0, 0, 0};
+    return host_compress(hash, l, z);
 }
-inline Dg digest_of(int hash, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {   // leaf of two elements (base: c = d = 0)
-    uint64_t s[12] = {a, b, c, d, 0, 0, 0, 0, 0, 0, 0, 0};
-    permute(hash, s);
-    Dg r;
-    for (int i = 0; i < 4; i++) r.w[i] = gl::canon(s[i]);
-    return r;
-}
-inline Dg compress(int hash, const uint64_t* l, const uint64_t* r) {
-    uint64_t s[12] = {l[0], l[1], l[2], l[3], r[0], r[1], r[2], r[3], 0, 0, 0, 0};
-    permute(hash, s);
-    Dg d;
-    for (int i = 0; i < 4; i++) d.w[i] = gl::canon(s[i]);
-    return d;
-}
-bool path_ok(int hash, Dg cur, const uint64_t* path, size_t len, size_t idx, const uint64_t* root) {
+inline Digest compress(int hash, const uint64_t* l, const uint64_t* r) { return host_compress(hash, l, r); }
+bool path_ok(int hash, Digest cur, const uint64_t* path, size_t len, size_t idx, const uint64_t* root) {
     for (size_t k = 0; k < len; k++) {
         cur = (idx & 1) == 0 ? compress(hash, cur.w, path + 4 * k) : compress(hash, path + 4 * k, cur.w);
         idx >>= 1;

@@ -8,25 +8,14 @@
 #pragma once
 #include <cstdint>
 #include "../gl_poseidon2.cuh"
+#include "host_field.hpp"
 
 namespace mbhost {
 namespace p2host {
 
-typedef unsigned __int128 u128;
-constexpr uint64_t EPS = 0xFFFFFFFFULL;
-
-// x mod p as a loose 64-bit residue, for any 128-bit x: with 2^64 = 2^32 - 1 and 2^96 = -1 (mod p),
-// x = lo - hi_hi + hi_lo (2^32 - 1). A borrow is repaired by - EPS (the wrapped value is above 2^64 - 2^32), a
-// carry by + EPS (the wrapped value is below hi_lo EPS < 2^64 - 2^33).
-static inline uint64_t red(u128 x) {
-    const uint64_t lo = (uint64_t)x, hi = (uint64_t)(x >> 64);
-    const uint64_t hh = hi >> 32, hl = hi & EPS, t1 = (hl << 32) - hl;
-    uint64_t t0 = lo - hh;
-    t0 -= (0 - (uint64_t)(lo < hh)) & EPS;           // branch-free: these carries are coin flips
-    uint64_t r = t0 + t1;
-    r += (0 - (uint64_t)(r < t1)) & EPS;
-    return r;
-}
+using hf::u128;
+constexpr uint64_t EPS = hf::GL_EPS;
+static inline uint64_t red(u128 x) { return hf::gl_red(x); }   // any 128-bit value, loose result
 static inline uint64_t mul(uint64_t a, uint64_t b) { return red((u128)a * b); }
 static inline uint64_t sbox7(uint64_t x) {
     const uint64_t x2 = mul(x, x), x4 = mul(x2, x2), x3 = mul(x2, x);

@@ -14,37 +14,41 @@
 //    after a fold only reads (d+1) extension elements back.
 // Base / Ext are the field traits of sumcheck_kernels.cuh (GlBase, GlExt2) or
 // agl_traits.cuh (AglBase, AglExt2).
-//  * once a table is down to HOST_TAIL elements the live tables are read back and the remaining rounds run on
-//    the host: a round on the device costs a launch and a synchronisation (about 27 us) whatever its size, the
-//    same round on 128 elements takes a host core a few microseconds. The field arithmetic is exact, so the
-//    messages are the same words.
+//  * once a table is down to host_tail(d) elements the live tables are read back and the remaining rounds run on
+//    the host: a round on the device costs a launch and a synchronisation (about 20 us) whatever its size, the
+//    same round on a few hundred elements takes a host core less (about 7 ns per extension product). The field
+//    arithmetic is exact, so the messages are the same words.
 #pragma once
 #include <vector>
 #include "../agl_field.cuh"
 #include "../gl_sumcheck_launch.cuh"
 #include "ext2_words.hpp"
+#include "host_field.hpp"
 
 namespace mbhost {
 
 using namespace mb;
 using namespace mb::sc;
 
-// Host-side extension arithmetic for the tail rounds, by element type.
+// Host-side extension arithmetic for the tail rounds, by element type: canonical words in and out (the tables are
+// made canonical when they come to the host), through the host forms of host_field.hpp.
 template <class T> struct HostExt;
-template <> struct HostExt<gl::E2> {
-    static gl::E2 add(gl::E2 a, gl::E2 b) { return gl::e2_add(a, b); }
-    static gl::E2 sub(gl::E2 a, gl::E2 b) { return gl::e2_sub(a, b); }
-    static gl::E2 mul(gl::E2 a, gl::E2 b) { return gl::e2_mul(a, b); }
-    static gl::E2 canon(gl::E2 a) { return gl::e2_canon(a); }
+template <class T, class F> struct HostExtOps {
+    static T add(T a, T b) { return T{F::add(a.c0, b.c0), F::add(a.c1, b.c1)}; }
+    static T sub(T a, T b) { return T{F::sub(a.c0, b.c0), F::sub(a.c1, b.c1)}; }
+    static T mul(T a, T b) {
+        T r;
+        hf::e2_mul<F>(a.c0, a.c1, b.c0, b.c1, r.c0, r.c1);
+        return r;
+    }
+    static T canon(T a) { return T{F::canon(a.c0), F::canon(a.c1)}; }
 };
-template <> struct HostExt<agl::E2> {
-    static agl::E2 add(agl::E2 a, agl::E2 b) { return agl::e2_add(a, b); }
-    static agl::E2 sub(agl::E2 a, agl::E2 b) { return agl::e2_sub(a, b); }
-    static agl::E2 mul(agl::E2 a, agl::E2 b) { return agl::e2_mul(a, b); }
-    static agl::E2 canon(agl::E2 a) { return agl::e2_canon(a); }
-};
+template <> struct HostExt<gl::E2> : HostExtOps<gl::E2, hf::GlE2Ops> {};
+template <> struct HostExt<agl::E2> : HostExtOps<agl::E2, hf::AglE2Ops> {};
 
-constexpr size_t HOST_TAIL = 128;   // live elements per table at which the rounds move to the host
+// Live elements per table at which the rounds move to the host: a host round costs live / 2 x (d^2 - 1 + d)
+// extension products, about 9 us at 512 elements of two tables and 10 us at 256 elements of three.
+inline size_t host_tail(int d) { return d <= 2 ? 512 : 256; }
 
 template <class Base, class Ext>
 class LinearSumcheckState {
@@ -120,7 +124,7 @@ public:
         size_t live = n_ >> round_, half = live / 2, quarter = live / 4;
         const typename Ext::WordCanon canon;
         typename Ext::T r{canon(challenge.c0), canon(challenge.c1)};
-        if (!host_mode_ && round_ >= 1 && live <= HOST_TAIL) {
+        if (!host_mode_ && round_ >= 1 && live <= host_tail(d_)) {
             int rc = to_host(live);
             if (rc != MB_OK) return rc;
         }

@@ -113,8 +113,8 @@ compress_pairs_kernel(const uint64_t* __restrict__ left, const uint64_t* __restr
 // one permutation per thread (hashes without an 8-lane variant).
 template <class H>
 __global__ void __launch_bounds__(TAIL_NODES / 2)
-tree_tail_kernel(uint64_t* layer, size_t size, uint64_t* root_out) {
-    while (size > 1) {
+tree_tail_kernel(uint64_t* layer, size_t size, uint64_t* root_out, size_t stop) {
+    while (size > stop) {
         uint64_t* next = layer + 4 * size;
         const size_t half = size / 2;
         if (threadIdx.x < half) compress_node<H>(layer + 8 * threadIdx.x, next + 4 * threadIdx.x);
@@ -122,7 +122,7 @@ tree_tail_kernel(uint64_t* layer, size_t size, uint64_t* root_out) {
         layer = next;
         size = half;
     }
-    if (root_out != nullptr && threadIdx.x < 4) root_out[threadIdx.x] = layer[threadIdx.x];
+    if (root_out != nullptr && threadIdx.x < 4 * size) root_out[threadIdx.x] = layer[threadIdx.x];
 }
 
 // Full Monolith permutation of n width-12 states, canonical outputs.
@@ -173,16 +173,16 @@ hash_leaves_coop_kernel(const uint64_t* __restrict__ cw, uint64_t* __restrict__ 
 }
 
 // One block (256 threads = 32 permutations at a time) walks every remaining
-// layer above `layer` (of `size` <= 64 nodes) up to the root. root_out (may be null) receives a copy of the
-// root: pinned host memory there saves the caller a copy command per tree.
+// layer above `layer` (of `size` <= 64 nodes) up to the layer of `stop` nodes (1: the root). root_out (may be null)
+// receives a copy of that last layer: pinned host memory there saves the caller a copy command per tree.
 static __global__ void __launch_bounds__(256)
-tree_tail_coop_kernel(uint64_t* layer, size_t size, uint64_t* root_out) {
+tree_tail_coop_kernel(uint64_t* layer, size_t size, uint64_t* root_out, size_t stop) {
     __shared__ uint64_t node[64 * 4];    // the current layer, kept on chip between levels (also written to the tree)
     const int l = threadIdx.x & 7;
     const size_t g = threadIdx.x >> 3;   // 32 groups: a layer of at most 64 nodes is one pass
     if (threadIdx.x < 4 * size) node[threadIdx.x] = layer[threadIdx.x];
     __syncthreads();
-    while (size > 1) {
+    while (size > stop) {
         uint64_t* next = layer + 4 * size;
         const size_t half = size / 2;
         const bool live = g < half;
@@ -200,7 +200,7 @@ tree_tail_coop_kernel(uint64_t* layer, size_t size, uint64_t* root_out) {
         layer = next;
         size = half;
     }
-    if (root_out != nullptr && threadIdx.x < 4) root_out[threadIdx.x] = node[threadIdx.x];
+    if (root_out != nullptr && threadIdx.x < 4 * size) root_out[threadIdx.x] = node[threadIdx.x];
 }
 
 // Five levels in one launch: block b (four warps) takes nodes [32 b, 32 b + 32) of `layer` (size nodes, a
@@ -291,17 +291,19 @@ inline void launch_hash_leaves(const uint64_t* cw, uint64_t* digests, size_t n, 
 }
 
 template <class H>
-inline void launch_tree_tail(uint64_t* layer, size_t size, cudaStream_t st, uint64_t* root_out = nullptr) {
+inline void launch_tree_tail(uint64_t* layer, size_t size, cudaStream_t st, uint64_t* root_out = nullptr, size_t stop = 1) {
     MB_KERNEL_ON("tree_tail", st);
-    if constexpr (H::COOP) tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size, root_out);
-    else tree_tail_kernel<H><<<1, TAIL_NODES / 2, 0, st>>>(layer, size, root_out);
+    if constexpr (H::COOP) tree_tail_coop_kernel<<<1, 256, 0, st>>>(layer, size, root_out, stop);
+    else tree_tail_kernel<H><<<1, TAIL_NODES / 2, 0, st>>>(layer, size, root_out, stop);
 }
 
-// Every layer above `layer` (`size` nodes) up to the root. Layers of more than COOP_NODES nodes take one launch
-// each; with an 8-lane permutation the rest goes five levels per launch, then one block for what is left
-// (at most 16 nodes).
+// Every layer above `layer` (`size` nodes) up to the layer of `stop` nodes (1: the root; a power of two up to 32
+// otherwise, for a caller that hashes the last levels on the host: a level there is bound by the latency of one
+// permutation, which a host core beats). root_out (may be null; device or pinned host memory) receives that last
+// layer: min(size, stop) digests. Layers of more than COOP_NODES nodes take one launch each; with an 8-lane
+// permutation the rest goes five levels per launch, then one block for what is left.
 template <class H>
-inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st, uint64_t* root_out = nullptr) {
+inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st, uint64_t* root_out = nullptr, size_t stop = 1) {
     if constexpr (H::COOP) {
         while (size > COOP_NODES) {
             size_t half = size / 2;
@@ -309,7 +311,8 @@ inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st, uint64_
             layer += 4 * size;
             size = half;
         }
-        while (size >= 64) {   // leaves 2 .. 32 nodes for the last block, which also hands out the root
+        const size_t keep = stop > 2 ? stop : 2;   // the last block hands out the result: leave it at least two nodes
+        while (size >= 32 * keep) {
             {
                 MB_KERNEL_ON("tree_up5", st);
                 tree_up5_coop_kernel<<<(unsigned)(size / 32), 128, 0, st>>>(layer, size);
@@ -317,32 +320,32 @@ inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st, uint64_
             layer += 4 * (2 * size - size / 16);   // size + size/2 + size/4 + size/8 + size/16 nodes
             size /= 32;
         }
-    } else {
-        while (size > (size_t)TAIL_NODES) {
-            size_t half = size / 2;
-            launch_compress_layer<H>(layer, layer + 4 * size, half, st);
-            layer += 4 * size;
-            size = half;
-        }
     }
-    if (size > 1) launch_tree_tail<H>(layer, size, st, root_out);
+    while (size > (size_t)TAIL_NODES) {
+        size_t half = size / 2;
+        launch_compress_layer<H>(layer, layer + 4 * size, half, st);
+        layer += 4 * size;
+        size = half;
+    }
+    if (size > 1 || stop > 1) launch_tree_tail<H>(layer, size, st, root_out, stop);
     else if (root_out != nullptr) cudaMemcpyAsync(root_out, layer, 32, cudaMemcpyDefault, st);   // a single leaf
 }
 
 // Layers above the digests already present in tree[0 .. 4*num_leaves). root_out (may be null; device or pinned
 // host memory) receives a copy of the root.
 template <class H>
-inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st, uint64_t* root_out = nullptr) {
-    finish_layers<H>(d_tree, num_leaves, st, root_out);
+inline int build_layers(uint64_t* d_tree, size_t num_leaves, cudaStream_t st, uint64_t* root_out = nullptr, size_t stop = 1) {
+    finish_layers<H>(d_tree, num_leaves, st, root_out, stop);
     return finish_async();
 }
 
+// stop > 1: the layers above the one of `stop` nodes are left to the caller (finish_layers).
 template <class H, bool EXT2>
 inline int build_tree(const uint64_t* d_codeword, uint64_t* d_tree, size_t num_leaves, cudaStream_t st,
-                      uint64_t* root_out = nullptr) {
+                      uint64_t* root_out = nullptr, size_t stop = 1) {
     if (!d_codeword || !d_tree || num_leaves < 1 || (num_leaves & (num_leaves - 1))) return MB_ERR_ARG;
     launch_hash_leaves<H, EXT2>(d_codeword, d_tree, num_leaves, st);
-    return build_layers<H>(d_tree, num_leaves, st, root_out);
+    return build_layers<H>(d_tree, num_leaves, st, root_out, stop);
 }
 
 // dst[c * words + i] = src[i] for c = 1 .. copies-1 (dst = src: in-place replication of a prefix).

@@ -6,6 +6,7 @@
 #include "gl_poseidon2.cuh"
 #include "agl_field.cuh"
 #include "host/gl_transcript.hpp"
+#include "host/host_field.hpp"
 #include "gl_monolith.cuh"
 #include "host/agl_transcript.hpp"
 #include "agl_mcommit.cuh"
@@ -60,6 +61,19 @@ void hc_mcm_key_block(const uint32_t* seed, uint32_t kind, uint32_t row, uint64_
 void hc_poseidon2(uint64_t* s) { gl::poseidon2_permute(s); }
 // the host-side form (transcripts, tree tops) and the reductions underneath both host permutations
 void hc_poseidon2_host(uint64_t* s) { mbhost::p2host::permute(s); }
+// host-form extension arithmetic (the last rounds of a sumcheck): o = a * b, a + b, a - b on canonical words
+void hc_hf_e2(int agl_field, const uint64_t* a, const uint64_t* b, uint64_t* o) {
+    using namespace mbhost::hf;
+    if (agl_field) {
+        e2_mul<AglE2Ops>(a[0], a[1], b[0], b[1], o[0], o[1]);
+        o[2] = agl_add(a[0], b[0]); o[3] = agl_add(a[1], b[1]);
+        o[4] = agl_sub(a[0], b[0]); o[5] = agl_sub(a[1], b[1]);
+    } else {
+        e2_mul<GlE2Ops>(a[0], a[1], b[0], b[1], o[0], o[1]);
+        o[2] = gl_add(a[0], b[0]); o[3] = gl_add(a[1], b[1]);
+        o[4] = gl_sub(a[0], b[0]); o[5] = gl_sub(a[1], b[1]);
+    }
+}
 uint64_t hc_p2host_red(uint64_t lo, uint64_t hi) { return mbhost::p2host::red(((unsigned __int128)hi << 64) | lo); }
 uint64_t hc_aglm_reduce_wide(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_wide(((unsigned __int128)hi << 64) | lo); }
 uint64_t hc_aglm_reduce_small(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_small(((unsigned __int128)hi << 64) | lo); }

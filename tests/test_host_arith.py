@@ -122,6 +122,22 @@ def test_host_form_of_poseidon2_and_its_reductions(hostcheck, oracle):
             assert hostcheck.hc_aglm_reduce_small(lo, hi) % AGL_P == (lo + (hi << 64)) % AGL_P
 
 
+def test_host_form_extension_arithmetic(hostcheck):
+    """The host rounds of a sumcheck multiply in F[X]/(X^2 - 7) over Goldilocks and F[X]/(X^2 - 3) over
+    almost-Goldilocks through 128-bit products; canonical words in, canonical words out."""
+    rnd = random.Random(23)
+    for agl_field, q, w in ((0, P, 7), (1, 2**64 - 2**32 - 31, 3)):
+        edge = [0, 1, 2, q - 1, q - 2, 2**32 - 1, 2**32, 2**63, q // 2]
+        cases = [(x, y, z, t) for x in edge for y in edge[:5] for z in edge[:5] for t in edge[:4]]
+        cases += [tuple(rnd.randrange(q) for _ in range(4)) for _ in range(3000)]
+        for a0, a1, b0, b1 in cases:
+            o = (u64 * 6)()
+            hostcheck.hc_hf_e2(agl_field, (u64 * 2)(a0, a1), (u64 * 2)(b0, b1), o)
+            assert o[0] == (a0 * b0 + w * a1 * b1) % q and o[1] == (a0 * b1 + a1 * b0) % q
+            assert (o[2], o[3]) == ((a0 + b0) % q, (a1 + b1) % q)
+            assert (o[4], o[5]) == ((a0 - b0) % q, (a1 - b1) % q)
+
+
 def test_transcript_matches_oracle(hostcheck, oracle):
     # Random scripts of absorbs and squeezes against the oracle's transcript.
     class T(ctypes.Structure):
