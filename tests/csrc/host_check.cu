@@ -74,6 +74,7 @@ void hc_hf_e2(int agl_field, const uint64_t* a, const uint64_t* b, uint64_t* o) 
         o[4] = gl_sub(a[0], b[0]); o[5] = gl_sub(a[1], b[1]);
     }
 }
+void hc_aglm_circulant12(const int64_t* x, int64_t* out) { mbhost::aglm::circulant12(x, out); }
 uint64_t hc_p2host_red(uint64_t lo, uint64_t hi) { return mbhost::p2host::red(((unsigned __int128)hi << 64) | lo); }
 uint64_t hc_aglm_reduce_wide(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_wide(((unsigned __int128)hi << 64) | lo); }
 uint64_t hc_aglm_reduce_small(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_small(((unsigned __int128)hi << 64) | lo); }

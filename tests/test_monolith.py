@@ -65,6 +65,24 @@ def test_host_monolith_matches_oracle(oracle, hostcheck):
         assert _perm(hostcheck.hc_agl_monolith, c) == _perm(oracle.oracle_agl_monolith_permute, c)
 
 
+def test_host_mds_layer_as_split_convolution(hostcheck):
+    """The host form of the MDS layer computes the circulant (first row 7 23 8 26 13 10 9 7 6 22 21 8,
+    zk-torch-4/src/crypto/monolith.rs) on 32-bit halves through a split cyclic convolution; it must equal the
+    direct sum as integers, extreme halves included."""
+    import random
+    row = [7, 23, 8, 26, 13, 10, 9, 7, 6, 22, 21, 8]
+    rnd = random.Random(31)
+    top = 2**32 - 1
+    cases = [[0] * 12, [top] * 12, [top if j % 2 else 0 for j in range(12)], [top if j < 6 else 0 for j in range(12)],
+             [0 if j < 6 else top for j in range(12)]]
+    cases += [[rnd.choice([0, 1, top, top - 1, rnd.randrange(2**32)]) for _ in range(12)] for _ in range(2000)]
+    i64 = ctypes.c_int64 * 12
+    for x in cases:
+        out = i64()
+        hostcheck.hc_aglm_circulant12(i64(*x), out)
+        assert list(out) == [sum(row[(j - i) % 12] * x[j] for j in range(12)) for i in range(12)]
+
+
 def test_agl_reduce_limb_sums(hostcheck):
     hostcheck.hc_agl_reduce_limb_sums.restype = ctypes.c_uint64
     hostcheck.hc_agl_reduce_limb_sums.argtypes = [ctypes.c_uint64, ctypes.c_uint64]
