@@ -203,25 +203,28 @@ tree_tail_coop_kernel(uint64_t* layer, size_t size, uint64_t* root_out, size_t s
     if (root_out != nullptr && threadIdx.x < 4 * size) root_out[threadIdx.x] = node[threadIdx.x];
 }
 
-// Five levels in one launch: block b (four warps) takes nodes [32 b, 32 b + 32) of `layer` (size nodes, a
-// multiple of 32) and writes its 16, 8, 4, 2, 1 nodes of the five layers above, so that the layer five levels up
-// (size / 32 nodes) is complete when the grid ends. What a small layer costs is not the dependent chain of a
+// Up to five levels in one launch: block b takes nodes [2^levels b, 2^levels (b + 1)) of `layer` (size nodes, a
+// multiple of 2^levels) and writes its 2^(levels-1), ..., 1 nodes of the layers above, so that the layer `levels`
+// up (size >> levels nodes) is complete when the grid ends; last_out (may be null; device or pinned host memory)
+// also receives that layer, one digest per block. What a small layer costs is not the dependent chain of a
 // permutation but issue slots: eight warps of 8-lane permutations on one SM take about 8 us per level, one warp
-// per scheduler about half of that. So a block holds only 16 permutations (one warp per scheduler) and a layer of
-// 4096 nodes is spread over 128 SMs; the old form (one launch per layer of 256-thread blocks, then one block for
-// the last six levels) cost 136 us for the twelve top levels of every tree, this one about half.
+// per scheduler about half of that. So a block holds at most 16 permutations (one warp per scheduler) and a layer
+// of 4096 nodes is spread over 128 SMs; the old form (one launch per layer of 256-thread blocks, then one block for
+// the last six levels) cost 136 us for the twelve top levels of every tree, this one about half. Blocks are whole
+// warps (the 8-lane permutation shuffles with the full mask): threads beyond the block's groups compute on zeros
+// and store nothing.
 static __global__ void __launch_bounds__(128)
-tree_up5_coop_kernel(uint64_t* layer, size_t size) {
+tree_up_coop_kernel(uint64_t* layer, size_t size, int levels, uint64_t* last_out) {
     __shared__ uint64_t node[32 * 4];    // this block's nodes of the current layer (also written to the tree)
     const int l = threadIdx.x & 7;
-    const size_t g = threadIdx.x >> 3;   // 16 groups of 8 lanes
-    node[threadIdx.x] = layer[4 * ((size_t)blockIdx.x * 32) + threadIdx.x];
+    const size_t g = threadIdx.x >> 3;   // up to 16 groups of 8 lanes
+    size_t in_nodes = (size_t)1 << levels;   // nodes of this block in the current layer
+    if (threadIdx.x < 4 * in_nodes) node[threadIdx.x] = layer[4 * ((size_t)blockIdx.x * in_nodes) + threadIdx.x];
     __syncthreads();
-    size_t in_nodes = 32;                // nodes of this block in the current layer
     size_t layer_size = size;
     uint64_t* cur = layer;
 #pragma unroll 1
-    for (int t = 0; t < 5; t++) {
+    for (int t = 0; t < levels; t++) {
         uint64_t* next = cur + 4 * layer_size;
         const size_t half = in_nodes / 2;
         uint64_t* dst = next + 4 * ((size_t)blockIdx.x * half);
@@ -241,6 +244,7 @@ tree_up5_coop_kernel(uint64_t* layer, size_t size) {
         layer_size /= 2;
         in_nodes = half;
     }
+    if (last_out != nullptr && threadIdx.x < 4) last_out[4 * (size_t)blockIdx.x + threadIdx.x] = node[threadIdx.x];
 }
 
 // Full permutation of n width-8 states (poseidon2_hash_batch_ffi).
@@ -311,14 +315,20 @@ inline void finish_layers(uint64_t* layer, size_t size, cudaStream_t st, uint64_
             layer += 4 * size;
             size = half;
         }
-        const size_t keep = stop > 2 ? stop : 2;   // the last block hands out the result: leave it at least two nodes
-        while (size >= 32 * keep) {
+        // five levels per launch (fewer in the last one), down to the layer of `stop` nodes, which the last launch
+        // also copies to root_out
+        while (size > stop) {
+            int levels = 0;
+            while (levels < 5 && (size >> levels) > stop) levels++;
+            const size_t out_nodes = size >> levels;
+            const unsigned threads = (unsigned)(4u << levels) < 32u ? 32u : (unsigned)(4u << levels);
             {
-                MB_KERNEL_ON("tree_up5", st);
-                tree_up5_coop_kernel<<<(unsigned)(size / 32), 128, 0, st>>>(layer, size);
+                MB_KERNEL_ON("tree_up", st);
+                tree_up_coop_kernel<<<(unsigned)out_nodes, threads, 0, st>>>(layer, size, levels, out_nodes == stop ? root_out : nullptr);
             }
-            layer += 4 * (2 * size - size / 16);   // size + size/2 + size/4 + size/8 + size/16 nodes
-            size /= 32;
+            layer += 4 * (2 * size - 2 * out_nodes);   // size + size/2 + ... + 2 out_nodes nodes
+            size = out_nodes;
+            if (size == stop) return;
         }
     }
     while (size > (size_t)TAIL_NODES) {
