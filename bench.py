@@ -52,6 +52,14 @@ NUM_QUERIES = 100
 LABEL = b"bench"
 
 
+def pinned_copy(lib, arr):
+    """The array's bytes in page-locked host memory (what a step's inputs are copied from in the end-to-end legs)."""
+    p = ctypes.c_void_p()
+    assert lib.mb_host_alloc(ctypes.byref(p), arr.nbytes) == 0
+    ctypes.memmove(p.value, arr.ctypes.data, arr.nbytes)
+    return p.value
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -423,7 +431,11 @@ def run_simple(args):
         fes, fe = np.zeros((d, 2), dtype=np.uint64), np.zeros(2, dtype=np.uint64)
         step = lambda: lib.gl_sumcheck_prove_device_ffi(d_t.ptr, d, nv, 1, LABEL, len(LABEL), rm.ctypes.data, ch.ctypes.data,
                                                         fes.ctypes.data, fe.ctypes.data, None)
-        step_e2e = lambda: lib.gl_sumcheck_prove_host_ffi(polys.ctypes.data, d, nv, 1, LABEL, len(LABEL), rm.ctypes.data,
+        # end to end: the tables start in page-locked host memory
+        h_polys = ctypes.c_void_p()
+        assert lib.mb_host_alloc(ctypes.byref(h_polys), polys.nbytes) == 0
+        ctypes.memmove(h_polys.value, polys.ctypes.data, polys.nbytes)
+        step_e2e = lambda: lib.gl_sumcheck_prove_host_ffi(h_polys.value, d, nv, 1, LABEL, len(LABEL), rm.ctypes.data,
                                                           ch.ctypes.data, fes.ctypes.data, fe.ctypes.data, None)
         units, metric = d * n, "field-elems/s: sumcheck of f*g over 2^%d points, Goldilocks" % nv
         workload = "sumcheck nv=%d d=2" % nv
@@ -468,8 +480,10 @@ def run_simple(args):
             module_commit_sharded(local_commit, comm, ncols, 1, rows)
             return 0
 
+        h_x = pinned_copy(lib, x)
+
         def step_e2e():
-            lib.cuda_memcpy_htod(d_x.ptr, x.ctypes.data, x.nbytes)
+            lib.cuda_memcpy_htod(d_x.ptr, h_x, x.nbytes)
             if world == 1:
                 device_commit()
                 lib.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
@@ -529,8 +543,10 @@ def run_simple(args):
             commit_sharded(local_commit, comm, n_ring, L)
             return 0
 
+        h_dig = pinned_copy(lib, dig)
+
         def step_e2e():
-            lib.cuda_memcpy_htod(d_z.ptr, dig.ctypes.data, dig.nbytes)
+            lib.cuda_memcpy_htod(d_z.ptr, h_dig, dig.nbytes)
             if world == 1:
                 commit_all()
                 lib.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
@@ -662,8 +678,10 @@ def run_link(args):
         rc |= lib.link_fold_ffi(d_w.ptr, d_om.ptr, half, n, half // 2, nc, 11, 13)
         return rc
 
+    h_words = pinned_copy(lib, words)
+
     def step_e2e():
-        lib.cuda_memcpy_htod(d_bits.ptr, words.ctypes.data, words.nbytes)
+        lib.cuda_memcpy_htod(d_bits.ptr, h_words, words.nbytes)
         step()
         lib.cuda_memcpy_dtoh(msg.ctypes.data, d_out.ptr, msg.nbytes)
     timed = _event_timer(lib)
@@ -1131,8 +1149,10 @@ def part_ajtai(args, local):
     def step():
         assert agl.ajtai_commit_s8_ffi(d_k.ptr, d_z.ptr, n_ring, L, 0, d_o.ptr) == 0
 
+    h_dig = pinned_copy(agl, dig)
+
     def step_e2e():
-        agl.cuda_memcpy_htod(d_z.ptr, dig.ctypes.data, dig.nbytes)
+        agl.cuda_memcpy_htod(d_z.ptr, h_dig, dig.nbytes)
         step()
         agl.cuda_memcpy_dtoh(out.ctypes.data, d_o.ptr, out.nbytes)
 
