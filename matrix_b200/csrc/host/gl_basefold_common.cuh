@@ -12,7 +12,7 @@
 #include "../basefold_kernels.cuh"
 #include "../eq_kernels.cuh"
 #include "../merkle_kernels.cuh"
-#include "../gl_monolith.cuh"
+#include "gl_monolith_host.hpp"
 #include "gl_transcript.hpp"
 
 namespace mb {
@@ -293,7 +293,7 @@ struct Digest {
 // compress(l, r): the first four words of the permutation of (l, r, 0 ...), canonical.
 inline Digest host_compress(int hash, const uint64_t* l, const uint64_t* r) {
     uint64_t s[12] = {l[0], l[1], l[2], l[3], r[0], r[1], r[2], r[3], 0, 0, 0, 0};
-    if (hash) gl::monolith_permute(s);
+    if (hash) monohost::permute(s);
     else p2host::permute(s);
     Digest d;
     for (int i = 0; i < 4; i++) d.w[i] = gl::canon(s[i]);

@@ -90,5 +90,45 @@ static inline void e2_mul(uint64_t a0, uint64_t a1, uint64_t b0, uint64_t b1, ui
     c1 = F::canon(F::red((u128)a0 * b1 + t10));
 }
 
+// ---- the circulant MDS layer of Monolith, width 12 --------------------------------------
+// The MDS layer of both Monolith instances (Goldilocks and almost-Goldilocks, width 12) is the circulant with first row C = 7 23 8 26 13 10 9 7 6 22 21 8: out_i = sum_j C[(j - i) mod 12] s_j,
+// a cyclic convolution of s with c'_k = C[-k mod 12]. On 32-bit halves of the state words the sums are exact
+// integers below 161 * 2^32, and the convolution splits by x^12 - 1 = (x^6 - 1)(x^6 + 1) and x^6 - 1 =
+// (x^3 - 1)(x^3 + 1): sums and differences of the halves, a cyclic and a negacyclic product of length 3 (9 + 9
+// multiply-adds), a negacyclic product of length 6 (36) and two exact halvings, 54 multiply-adds by small
+// constants instead of 144.
+namespace mds {
+constexpr int C[12] = {7, 23, 8, 26, 13, 10, 9, 7, 6, 22, 21, 8};
+constexpr int cp(int k) { return C[(12 - k) % 12]; }     // out = cp (*) s, cyclic of length 12
+constexpr int cpq(int k) { return cp(k) + cp(k + 6); }         // mod x^6 - 1
+constexpr int cmq(int k) { return cp(k) - cp(k + 6); }         // mod x^6 + 1
+constexpr int cpp(int k) { return cpq(k) + cpq(k + 3); }       // mod x^3 - 1
+constexpr int cpm(int k) { return cpq(k) - cpq(k + 3); }       // mod x^3 + 1
+}  // namespace mds
+
+// out_i = sum_j C[(j - i) mod 12] x_j for twelve values below 2^32, as exact integers.
+inline void circulant12(const int64_t* x, int64_t* out) {
+    using namespace mds;
+    int64_t sp[6], sm[6], spp[3], spm[3];
+    for (int k = 0; k < 6; k++) { sp[k] = x[k] + x[k + 6]; sm[k] = x[k] - x[k + 6]; }
+    for (int k = 0; k < 3; k++) { spp[k] = sp[k] + sp[k + 3]; spm[k] = sp[k] - sp[k + 3]; }
+    const int64_t opp0 = cpp(0) * spp[0] + cpp(2) * spp[1] + cpp(1) * spp[2];
+    const int64_t opp1 = cpp(1) * spp[0] + cpp(0) * spp[1] + cpp(2) * spp[2];
+    const int64_t opp2 = cpp(2) * spp[0] + cpp(1) * spp[1] + cpp(0) * spp[2];
+    const int64_t opm0 = cpm(0) * spm[0] - cpm(2) * spm[1] - cpm(1) * spm[2];
+    const int64_t opm1 = cpm(1) * spm[0] + cpm(0) * spm[1] - cpm(2) * spm[2];
+    const int64_t opm2 = cpm(2) * spm[0] + cpm(1) * spm[1] + cpm(0) * spm[2];
+    const int64_t op[6] = {(opp0 + opm0) >> 1, (opp1 + opm1) >> 1, (opp2 + opm2) >> 1,
+                           (opp0 - opm0) >> 1, (opp1 - opm1) >> 1, (opp2 - opm2) >> 1};
+    int64_t om[6];
+    om[0] = cmq(0) * sm[0] - cmq(5) * sm[1] - cmq(4) * sm[2] - cmq(3) * sm[3] - cmq(2) * sm[4] - cmq(1) * sm[5];
+    om[1] = cmq(1) * sm[0] + cmq(0) * sm[1] - cmq(5) * sm[2] - cmq(4) * sm[3] - cmq(3) * sm[4] - cmq(2) * sm[5];
+    om[2] = cmq(2) * sm[0] + cmq(1) * sm[1] + cmq(0) * sm[2] - cmq(5) * sm[3] - cmq(4) * sm[4] - cmq(3) * sm[5];
+    om[3] = cmq(3) * sm[0] + cmq(2) * sm[1] + cmq(1) * sm[2] + cmq(0) * sm[3] - cmq(5) * sm[4] - cmq(4) * sm[5];
+    om[4] = cmq(4) * sm[0] + cmq(3) * sm[1] + cmq(2) * sm[2] + cmq(1) * sm[3] + cmq(0) * sm[4] - cmq(5) * sm[5];
+    om[5] = cmq(5) * sm[0] + cmq(4) * sm[1] + cmq(3) * sm[2] + cmq(2) * sm[3] + cmq(1) * sm[4] + cmq(0) * sm[5];
+    for (int k = 0; k < 6; k++) { out[k] = (op[k] + om[k]) >> 1; out[k + 6] = (op[k] - om[k]) >> 1; }
+}
+
 }  // namespace hf
 }  // namespace mbhost

@@ -9,6 +9,7 @@
 #include "host/host_field.hpp"
 #include "gl_monolith.cuh"
 #include "host/agl_transcript.hpp"
+#include "host/gl_monolith_host.hpp"
 #include "agl_mcommit.cuh"
 
 extern "C" {
@@ -74,7 +75,7 @@ void hc_hf_e2(int agl_field, const uint64_t* a, const uint64_t* b, uint64_t* o) 
         o[4] = gl_sub(a[0], b[0]); o[5] = gl_sub(a[1], b[1]);
     }
 }
-void hc_aglm_circulant12(const int64_t* x, int64_t* out) { mbhost::aglm::circulant12(x, out); }
+void hc_aglm_circulant12(const int64_t* x, int64_t* out) { mbhost::hf::circulant12(x, out); }
 uint64_t hc_p2host_red(uint64_t lo, uint64_t hi) { return mbhost::p2host::red(((unsigned __int128)hi << 64) | lo); }
 uint64_t hc_aglm_reduce_wide(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_wide(((unsigned __int128)hi << 64) | lo); }
 uint64_t hc_aglm_reduce_small(uint64_t lo, uint64_t hi) { return mbhost::aglm::reduce_small(((unsigned __int128)hi << 64) | lo); }
@@ -101,6 +102,7 @@ void hc_gl_monolith(uint64_t* s) {
     gl::monolith_permute(s);
     for (int i = 0; i < 12; i++) s[i] = gl::canon(s[i]);
 }
+void hc_gl_monolith_host(uint64_t* s) { mbhost::monohost::permute(s); }
 void hc_agl_monolith(uint64_t* s) { mbhost::aglm::permute(s); }
 uint64_t hc_agl_reduce_limb_sums(uint64_t L, uint64_t H) { return agl::reduce_limb_sums(L, H); }
 

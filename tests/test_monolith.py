@@ -51,6 +51,7 @@ def test_oracle_agl_transcript_golden(oracle):
 
 def test_host_monolith_kats(hostcheck):
     assert _perm(hostcheck.hc_gl_monolith, range(12)) == GL_KAT
+    assert _perm(hostcheck.hc_gl_monolith_host, range(12)) == GL_KAT
     assert _perm(hostcheck.hc_agl_monolith, range(12)) == AGL_KAT
 
 
@@ -62,6 +63,7 @@ def test_host_monolith_matches_oracle(oracle, hostcheck):
     cases += [list(map(int, r)) for r in raw]
     for c in cases:
         assert _perm(hostcheck.hc_gl_monolith, c) == _perm(oracle.oracle_gl_monolith_permute, c)
+        assert _perm(hostcheck.hc_gl_monolith_host, c) == _perm(oracle.oracle_gl_monolith_permute, c)   # tree tops
         assert _perm(hostcheck.hc_agl_monolith, c) == _perm(oracle.oracle_agl_monolith_permute, c)
 
 
