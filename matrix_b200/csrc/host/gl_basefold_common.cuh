@@ -12,7 +12,7 @@
 #include "../basefold_kernels.cuh"
 #include "../eq_kernels.cuh"
 #include "../merkle_kernels.cuh"
-#include "gl_monolith_host.hpp"
+#include "host_tree_top.hpp"
 #include "gl_transcript.hpp"
 
 namespace mb {
@@ -286,48 +286,15 @@ public:
     DevBuf d_codeword, d_bh_evals, d_tree;
 };
 
-// ---- host hashing of tree tops -----------------------------------------------------------
-struct Digest {
-    uint64_t w[4];
-};
-// compress(l, r): the first four words of the permutation of (l, r, 0 ...), canonical.
-inline Digest host_compress(int hash, const uint64_t* l, const uint64_t* r) {
-    uint64_t s[12] = {l[0], l[1], l[2], l[3], r[0], r[1], r[2], r[3], 0, 0, 0, 0};
-    if (hash) monohost::permute(s);
-    else p2host::permute(s);
-    Digest d;
-    for (int i = 0; i < 4; i++) d.w[i] = gl::canon(s[i]);
-    return d;
-}
-inline Digest host_compress(int hash, const Digest& l, const Digest& r) { return host_compress(hash, l.w, r.w); }
-
-// The last levels of a tree are bound by the latency of one permutation per level on the device (about 10 us);
-// a host core runs a permutation in about 1 us. So a round's tree stops on the device at a layer of HOST_TOP
-// digests (mk::build_tree's `stop`), which the kernel leaves in pinned memory, and the host hashes the three
-// levels above: seven permutations, then one small upload puts them into the device tree for the query phase.
-constexpr size_t HOST_TOP = 8;
-
+// ---- host hashing of tree tops: host_tree_top.hpp -------------------------------------------
 // nodes: the layer of `count` digests (a power of two, at most HOST_TOP) the device left; upper: pinned staging for
 // count - 1 digests that stays untouched until the stream has run the upload; d_tree: the tree of num_leaves
 // leaves (2 num_leaves - 1 digests, layers back to back). root receives the root.
 inline int host_finish_top(int hash, const uint64_t* nodes, size_t count, uint64_t* upper, uint64_t* d_tree, size_t num_leaves,
                            uint64_t* root, cudaStream_t st) {
-    if (count <= 1) {
-        std::memcpy(root, nodes, 32);
-        return MB_OK;
-    }
-    const uint64_t* cur = nodes;
-    uint64_t* out = upper;
-    for (size_t size = count; size > 1; size /= 2) {
-        for (size_t j = 0; j < size / 2; j++) {
-            const Digest d = host_compress(hash, cur + 8 * j, cur + 8 * j + 4);
-            std::memcpy(out + 4 * j, d.w, 32);
-        }
-        cur = out;
-        out += 4 * (size / 2);
-    }
-    std::memcpy(root, cur, 32);
-    MB_CUDA(cudaMemcpyAsync(d_tree + 4 * (2 * num_leaves - count), upper, 32 * (count - 1), cudaMemcpyHostToDevice, st));
+    host_hash_top(hash, nodes, count, upper, root);
+    if (count > 1)
+        MB_CUDA(cudaMemcpyAsync(d_tree + 4 * (2 * num_leaves - count), upper, 32 * (count - 1), cudaMemcpyHostToDevice, st));
     return MB_OK;
 }
 

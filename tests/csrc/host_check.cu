@@ -10,6 +10,7 @@
 #include "gl_monolith.cuh"
 #include "host/agl_transcript.hpp"
 #include "host/gl_monolith_host.hpp"
+#include "host/host_tree_top.hpp"
 #include "agl_mcommit.cuh"
 
 extern "C" {
@@ -101,6 +102,10 @@ void hc_e2_dot(const uint64_t* a, const uint64_t* b, int n, uint64_t* o) {
 void hc_gl_monolith(uint64_t* s) {
     gl::monolith_permute(s);
     for (int i = 0; i < 12; i++) s[i] = gl::canon(s[i]);
+}
+// the host-hashed top of a Merkle tree: upper layers and root above a layer of `count` digests
+void hc_tree_top(int hash, const uint64_t* nodes, size_t count, uint64_t* upper, uint64_t* root) {
+    mbhost::host_hash_top(hash, nodes, count, upper, root);
 }
 void hc_gl_monolith_host(uint64_t* s) { mbhost::monohost::permute(s); }
 void hc_agl_monolith(uint64_t* s) { mbhost::aglm::permute(s); }

@@ -1,5 +1,7 @@
 """CPU tests of the Basefold oracle: table, commit structure, prover -> verifier
 round trip, tamper rejection, evaluation claim against direct MLE evaluation."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -88,3 +90,28 @@ def test_open_verifies_and_claims_mle_value(nv, lr, nq):
         bad = proof.copy()
         bad[pos] ^= np.uint64(1)
         assert pyoracle.bf_verify(root, nv, lr, point, table, nq, bad) != 0, "flip at %d accepted" % pos
+
+
+@pytest.mark.parametrize("hash_id", [0, 1])
+def test_host_hashed_tree_top_matches_oracle_tree(hostcheck, hash_id):
+    """The provers stop a round's tree on the device at a layer of eight digests and hash the levels above on the
+    host (matrix_b200/csrc/host/host_tree_top.hpp). Those host levels must be the oracle tree's own top, with both
+    Merkle hashes and for layers of 8, 4, 2 and 1 digests."""
+    from oracle import pyoracle
+    lib = pyoracle.load()
+    u64 = ctypes.c_uint64
+    with pyoracle.merkle_hash(hash_id):
+        for leaves, ext2 in ((32, 0), (16, 1), (8, 1), (4, 0), (2, 1), (1, 0)):
+            cw = field_elems(700 + leaves, leaves * (4 if ext2 else 2))
+            tree = np.zeros(4 * (2 * leaves - 1), dtype=np.uint64)
+            lib.oracle_bf_merkle_tree(cw.ctypes.data, leaves, ext2, tree.ctypes.data)
+            count = min(leaves, 8)
+            start = 4 * (2 * leaves - 2 * count)          # the layer of `count` digests
+            nodes = np.ascontiguousarray(tree[start:start + 4 * count])
+            upper = np.zeros(4 * max(count - 1, 1), dtype=np.uint64)
+            root = np.zeros(4, dtype=np.uint64)
+            hostcheck.hc_tree_top(hash_id, nodes.ctypes.data_as(ctypes.POINTER(u64)), ctypes.c_size_t(count),
+                                  upper.ctypes.data_as(ctypes.POINTER(u64)), root.ctypes.data_as(ctypes.POINTER(u64)))
+            assert np.array_equal(root, tree[-4:])
+            if count > 1:
+                assert np.array_equal(upper[:4 * (count - 1)], tree[start + 4 * count:])
