@@ -296,6 +296,11 @@ int basefold_prove_host(const uint64_t* h_evals, int num_vars, int log_rate, con
 int basefold_verify_host(const uint64_t* h_root, int num_vars, int log_rate, const uint64_t* h_point, const void* table,
                          const uint8_t* label, size_t label_len, int num_queries, int merkle_hash,
                          const uint64_t* h_proof, int* result);
+/* The same verifier with the folding table in host memory (h_table: the (point, weight) pairs as
+ * basefold_table_download writes them): no device call, for a verifier on a machine without a GPU. */
+int basefold_verify_with_table_host(const uint64_t* h_root, int num_vars, int log_rate, const uint64_t* h_point,
+                                    const uint64_t* h_table, const uint8_t* label, size_t label_len, int num_queries,
+                                    int merkle_hash, const uint64_t* h_proof, int* result);
 
 /* ---- additions: one commitment + opening shared by several GPUs ----
  * No counterpart in the reference, which runs one whole prover per device

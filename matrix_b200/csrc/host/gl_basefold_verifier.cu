@@ -52,16 +52,39 @@ __global__ void table_gather_kernel(const uint64_t* __restrict__ entries, const 
     }
 }
 
+// The pairs at `want` of a table that lives on the device: one gather kernel and one copy back.
+int fetch_from_device_table(const BasefoldTable& table, const uint64_t* want, size_t count, uint64_t* got) {
+    DevBuf d_want, d_got;
+    int rc = d_want.alloc(count);
+    if (rc == MB_OK) rc = d_got.alloc(2 * count);
+    if (rc != MB_OK) return rc;
+    MB_CUDA(cudaMemcpyAsync(d_want.p, want, sizeof(uint64_t) * count, cudaMemcpyHostToDevice, MB_STREAM));
+    {
+        MB_KERNEL_ON("table_gather", MB_STREAM);
+        table_gather_kernel<<<(unsigned)((count + 127) / 128), 128, 0, MB_STREAM>>>(table.d_entries.p, d_want.p, count, d_got.p);
+    }
+    MB_CUDA(cudaMemcpyAsync(got, d_got.p, sizeof(uint64_t) * 2 * count, cudaMemcpyDeviceToHost, MB_STREAM));
+    MB_CUDA(cudaStreamSynchronize(MB_STREAM));
+    return MB_OK;
+}
+
 }  // namespace
 
 // *result = 0 when the opening is accepted, otherwise a negative code naming the first failed check:
 // -1 claimed value against the first oracle, -(10 + i) oracle chain at round i, -100 query index, -101 commitment
 // path, -(200 + i) fold consistency at round i, -(300 + i) folded-tree path at round i, -400 final codeword.
-int basefold_verify(const uint64_t* root, int nv, int lr, const uint64_t* point, const BasefoldTable& table, Transcript& t,
+// fetch(want, count, got): got[2k], got[2k+1] = the (point, weight) pair at entry want[k] of the folding table (levels
+// back to back, level i of 2^(nv + lr - i - 1) entries); returns MB_OK or an error.
+template <class Fetch>
+int basefold_verify(const uint64_t* root, int nv, int lr, const uint64_t* point, Fetch fetch, Transcript& t,
                     int num_queries, int hash, const uint64_t* proof, int* result) {
-    if (nv < 1 || lr < 0 || nv + lr > 34 || num_queries < 0 || table.num_vars != nv || table.log_rate != lr || table.rounds < nv)
-        return MB_ERR_ARG;
+    if (nv < 1 || lr < 0 || nv + lr > 34 || num_queries < 0) return MB_ERR_ARG;
     if (hash < 0) hash = g_merkle_hash.load();
+    std::vector<size_t> level_offsets(nv);
+    {
+        size_t total = 0;
+        for (int i = 0; i < nv; i++) { level_offsets[i] = total; total += (size_t)1 << (nv + lr - i - 1); }
+    }
     const uint64_t *p_eval = proof, *p_oracles = proof + 2, *p_roots = p_oracles + (size_t)nv * 6;
     const uint64_t *p_final = p_roots + (size_t)(nv - 1) * 4, *p_queries = p_final + ((size_t)2 << lr);
     const size_t qw = query_words(nv, lr);
@@ -94,20 +117,11 @@ int basefold_verify(const uint64_t* root, int nv, int lr, const uint64_t* point,
     std::vector<uint64_t> index(num_queries), want((size_t)num_queries * nv), got((size_t)num_queries * nv * 2);
     for (int q = 0; q < num_queries; q++) {
         index[q] = t.sample_challenge() % (uint64_t)(cw_len / 2);
-        for (int i = 0; i < nv; i++) want[(size_t)q * nv + i] = table.level_offsets[i] + (index[q] >> i);
+        for (int i = 0; i < nv; i++) want[(size_t)q * nv + i] = level_offsets[i] + (index[q] >> i);
     }
     {
-        DevBuf d_want, d_got;
-        int rc = d_want.alloc(want.size());
-        if (rc == MB_OK) rc = d_got.alloc(got.size());
+        const int rc = fetch(want.data(), want.size(), got.data());
         if (rc != MB_OK) return rc;
-        MB_CUDA(cudaMemcpyAsync(d_want.p, want.data(), sizeof(uint64_t) * want.size(), cudaMemcpyHostToDevice, MB_STREAM));
-        {
-            MB_KERNEL_ON("table_gather", MB_STREAM);
-            table_gather_kernel<<<(unsigned)((want.size() + 127) / 128), 128, 0, MB_STREAM>>>(table.d_entries.p, d_want.p, want.size(), d_got.p);
-        }
-        MB_CUDA(cudaMemcpyAsync(got.data(), d_got.p, sizeof(uint64_t) * got.size(), cudaMemcpyDeviceToHost, MB_STREAM));
-        MB_CUDA(cudaStreamSynchronize(MB_STREAM));
     }
     for (int q = 0; q < num_queries; q++) {
         const uint64_t* pq = p_queries + (size_t)q * qw;
@@ -162,9 +176,33 @@ int basefold_verify_host(const uint64_t* h_root, int num_vars, int log_rate, con
                          const uint8_t* label, size_t label_len, int num_queries, int merkle_hash, const uint64_t* h_proof,
                          int* result) {
     if (!h_root || !h_point || !table || !h_proof || !result || (!label && label_len)) return MB_ERR_ARG;
+    const mbhost::BasefoldTable& tb = *static_cast<const mbhost::BasefoldTable*>(table);
+    if (tb.num_vars != num_vars || tb.log_rate != log_rate || tb.rounds < num_vars) return MB_ERR_ARG;
     mbhost::Transcript t(label, label_len);
-    return mbhost::basefold_verify(h_root, num_vars, log_rate, h_point, *static_cast<const mbhost::BasefoldTable*>(table), t,
-                                   num_queries, merkle_hash > 1 ? 1 : merkle_hash, h_proof, result);
+    auto fetch = [&tb](const uint64_t* want, size_t count, uint64_t* got) {
+        return mbhost::fetch_from_device_table(tb, want, count, got);
+    };
+    return mbhost::basefold_verify(h_root, num_vars, log_rate, h_point, fetch, t, num_queries, merkle_hash > 1 ? 1 : merkle_hash,
+                                   h_proof, result);
+}
+
+// The same verifier with the folding table in host memory (h_table: (point, weight) pairs, levels back to back, as
+// basefold_table_download writes them): no device call at all, for a verifier on a machine without a GPU, which is
+// where the reference's verifier runs (basefold.rs:1759-1925 is CPU code).
+int basefold_verify_with_table_host(const uint64_t* h_root, int num_vars, int log_rate, const uint64_t* h_point,
+                                    const uint64_t* h_table, const uint8_t* label, size_t label_len, int num_queries,
+                                    int merkle_hash, const uint64_t* h_proof, int* result) {
+    if (!h_root || !h_point || !h_table || !h_proof || !result || (!label && label_len)) return MB_ERR_ARG;
+    mbhost::Transcript t(label, label_len);
+    auto fetch = [h_table](const uint64_t* want, size_t count, uint64_t* got) {
+        for (size_t k = 0; k < count; k++) {
+            got[2 * k] = h_table[2 * want[k]];
+            got[2 * k + 1] = h_table[2 * want[k] + 1];
+        }
+        return MB_OK;
+    };
+    return mbhost::basefold_verify(h_root, num_vars, log_rate, h_point, fetch, t, num_queries, merkle_hash > 1 ? 1 : merkle_hash,
+                                   h_proof, result);
 }
 
 }  // extern "C"

@@ -170,6 +170,8 @@ _GL_SIGNATURES = {
                                     c_void_p, c_void_p]),
     "basefold_verify_host": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int, c_int,
                                      c_void_p, ctypes.POINTER(c_int)]),
+    "basefold_verify_with_table_host": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_char_p, c_size_t, c_int,
+                                                c_int, c_void_p, ctypes.POINTER(c_int)]),
     "mb_exchange_local_create": (c_int, [c_int, ctypes.POINTER(c_void_p)]),
     "mb_exchange_shm_create": (c_int, [ctypes.c_char_p, c_int, c_int, c_size_t, c_void_p, c_void_p, ctypes.POINTER(c_void_p)]),
     "mb_exchange_destroy": (c_int, [c_void_p]),

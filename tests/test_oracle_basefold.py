@@ -115,3 +115,51 @@ def test_host_hashed_tree_top_matches_oracle_tree(hostcheck, hash_id):
             assert np.array_equal(root, tree[-4:])
             if count > 1:
                 assert np.array_equal(upper[:4 * (count - 1)], tree[start + 4 * count:])
+
+
+@pytest.mark.parametrize("nv,lr,nq,hash_id", [(2, 1, 3, 0), (3, 0, 4, 0), (4, 3, 7, 1), (6, 1, 10, 0), (8, 2, 12, 1), (11, 1, 30, 0)])
+def test_library_verifier_with_host_table_agrees_with_oracle_verifier(nv, lr, nq, hash_id):
+    """basefold_verify_with_table_host (the library's verifier with the folding table in host memory: no device call,
+    so it runs here) on proofs written by the oracle prover: it accepts them, and on every flipped proof word it
+    stops at the same check as the oracle's restatement of the reference verifier
+    (goldilocks-cuda-rs/src/basefold.rs:1759-1925)."""
+    from matrix_b200.ffi import load_gl
+    from oracle import pyoracle
+    lib = load_gl()
+    evals = field_elems(40 + nv, 1 << nv)
+    point = field_elems(50 + nv, 2 * nv)
+    table = pyoracle.bf_table(nv, lr)
+    with pyoracle.merkle_hash(hash_id):
+        cw, bh, tree = pyoracle.bf_commit(evals, nv, lr)
+        proof, _ = pyoracle.bf_open(cw, bh, tree, nv, lr, point, table, nq)
+    root = np.ascontiguousarray(tree[-4:])
+
+    def ours(pr, rt=root, pt=point, label=b"bench", h=hash_id):
+        res = ctypes.c_int(777)
+        rc = lib.basefold_verify_with_table_host(rt.ctypes.data, nv, lr, pt.ctypes.data, table.ctypes.data, label, len(label), nq, h,
+                                                 pr.ctypes.data, ctypes.byref(res))
+        assert rc == 0
+        return res.value
+
+    def theirs(pr, rt=root, pt=point, label=b"bench"):
+        with pyoracle.merkle_hash(hash_id):
+            return pyoracle.bf_verify(rt, nv, lr, pt, table, nq, pr, label=label)
+
+    assert theirs(proof) == 0 and ours(proof) == 0
+    assert ours(proof, h=1 - hash_id) == -101            # the other hash: the first commitment path fails
+    words = len(proof)
+    positions = range(words) if words <= 600 else sorted(set(int(x) for x in np.random.default_rng(nv).integers(0, words, 300)))
+    for pos in positions:
+        bad = proof.copy()
+        bad[pos] ^= np.uint64(1)
+        assert ours(bad) == theirs(bad), "word %d flipped" % pos
+    bad_root = root.copy()
+    bad_root[0] ^= np.uint64(1)
+    assert ours(proof, rt=bad_root) == theirs(proof, rt=bad_root) != 0
+    bad_point = point.copy()
+    bad_point[1] ^= np.uint64(1)
+    assert ours(proof, pt=bad_point) == theirs(proof, pt=bad_point) != 0
+    assert ours(proof, label=b"other") == theirs(proof, label=b"other") != 0
+    res = ctypes.c_int(0)
+    assert lib.basefold_verify_with_table_host(root.ctypes.data, 0, lr, point.ctypes.data, table.ctypes.data, b"bench", 5, nq, 0,
+                                               proof.ctypes.data, ctypes.byref(res)) != 0
