@@ -70,3 +70,48 @@ def test_random_tables_against_python_integers():
     for t in tabs:
         pr = _mul(pr, t[0])
     assert [int(fin[0]), int(fin[1])] == list(pr)
+
+
+def test_library_verifier_agrees_with_oracle_verifier():
+    """agl_sumcheck_verify_ffi (SumcheckVerifier::verify, zk-torch-4/src/sumcheck/verifier.rs:14-113; host code of the
+    CUDA library, no device call) on proofs written by the oracle prover: accepts them with the same challenges, and
+    gives the oracle verifier's verdict on every tampered word, a wrong claim and a wrong label."""
+    import ctypes
+    from matrix_b200.ffi import load_agl
+    lib = load_agl()
+
+    def ours(msgs, fin, claim, d, nv, label):
+        msgs, fin = np.ascontiguousarray(msgs, dtype=np.uint64), np.ascontiguousarray(fin, dtype=np.uint64)
+        cl, ch = np.array(claim, dtype=np.uint64), np.zeros(max(nv, 1) * 2, dtype=np.uint64)
+        h, ok = ctypes.c_void_p(), ctypes.c_int(-1)
+        assert lib.agl_transcript_create(label, len(label), ctypes.byref(h)) == 0
+        rc = lib.agl_sumcheck_verify_ffi(msgs.ctypes.data, fin.ctypes.data, cl.ctypes.data, d, nv, h, ch.ctypes.data, ctypes.byref(ok))
+        lib.agl_transcript_destroy(h)
+        assert rc == 0
+        return bool(ok.value), ch[:2 * nv]
+
+    cases = [(label, nv, lifted(tables), len(tables), [claim, 0]) for label, nv, tables, claim in CASES]
+    for seed, (nv, d) in enumerate([(1, 1), (4, 2), (6, 3), (5, 4), (3, 6)]):
+        n = 1 << nv
+        raw = splitmix64(200 + seed, 2 * n * d) % np.uint64(Q)
+        tabs = [[(int(raw[2 * (i * n + j)]), int(raw[2 * (i * n + j) + 1])) for j in range(n)] for i in range(d)]
+        claim = [0, 0]
+        for j in range(n):
+            pr = (1, 0)
+            for i in range(d):
+                pr = _mul(pr, tabs[i][j])
+            claim = [(claim[0] + pr[0]) % Q, (claim[1] + pr[1]) % Q]
+        cases.append((b"lib-%d" % seed, nv, raw, d, claim))
+    for label, nv, polys, d, claim in cases:
+        msgs, ch, _, fin, _ = pyoracle.agl_sumcheck_prove(polys, d, nv, False, label)
+        ok, vch = ours(msgs, fin, claim, d, nv, label)
+        assert ok and list(vch) == list(ch)
+        for pos in range(len(msgs)):
+            bad = msgs.copy()
+            bad[pos] ^= np.uint64(1)
+            assert ours(bad, fin, claim, d, nv, label)[0] == pyoracle.agl_sumcheck_verify(bad, fin, claim, d, nv, label)[0] is False
+        bad_fin = fin.copy()
+        bad_fin[1] ^= np.uint64(1)
+        assert not ours(msgs, bad_fin, claim, d, nv, label)[0]
+        assert not ours(msgs, fin, [(claim[0] + 1) % Q, claim[1]], d, nv, label)[0]
+        assert not ours(msgs, fin, claim, d, nv, label + b"x")[0]

@@ -101,3 +101,52 @@ def test_claim_sum_identity():
         f = int(inst["witness"][j])
         acc = ((acc[0] + e[0] * f) % q, (acc[1] + e[1] * f) % q)
     assert [int(x) for x in inst["value"]] == list(acc)
+
+
+def _library_verify(lib, instances, n, proof, label):
+    """agl_same_point_verify_ffi (host code of the CUDA library; no device call) on a proof in the oracle's layout."""
+    import ctypes
+    arity = np.array([i["arity"] for i in instances], dtype=np.int32)
+    pts = np.concatenate([np.ascontiguousarray(i["point"], dtype=np.uint64).reshape(-1) for i in instances])
+    vals = np.ascontiguousarray([i["value"] for i in instances], dtype=np.uint64).reshape(-1)
+    msgs = np.ascontiguousarray(proof["round_msgs"], dtype=np.uint64)
+    fe = np.ascontiguousarray(proof["f_evals"], dtype=np.uint64)
+    fin = np.ascontiguousarray(proof["final_eval"], dtype=np.uint64)
+    ch = np.zeros((n, 2), dtype=np.uint64)
+    h, ok = ctypes.c_void_p(), ctypes.c_int(-1)
+    assert lib.agl_transcript_create(label, len(label), ctypes.byref(h)) == 0
+    rc = lib.agl_same_point_verify_ffi(len(instances), n, arity.ctypes.data, pts.ctypes.data, vals.ctypes.data, msgs.ctypes.data,
+                                       fe.ctypes.data, fin.ctypes.data, h, ch.ctypes.data, ctypes.byref(ok))
+    lib.agl_transcript_destroy(h)
+    assert rc == 0
+    return bool(ok.value), ch
+
+
+@pytest.mark.parametrize("kinds,arities,n", [((0,), (4,), 4), ((0, 0), (2, 4), 4), ((0, 1, 2), (3, 9, 6), 9), ((2, 2), (5, 5), 7),
+                                               ((1, 0, 2, 0), (6, 1, 6, 3), 6)])
+def test_library_verifier_agrees_with_oracle_verifier(kinds, arities, n):
+    """The library's host verifier (same_point_sumcheck.rs:161-219) against the oracle's on proofs written by the
+    oracle prover, instances of different arities included (the case only the verifier has to handle): both accept,
+    return the same challenges, and reject the same tampered proofs."""
+    from matrix_b200.ffi import load_agl
+    lib = load_agl()
+    instances = [random_instance(900 + 10 * k, kind, a) for k, (kind, a) in enumerate(zip(kinds, arities))]
+    label = b"sp-lib"
+    proof = pyoracle.agl_same_point_prove(instances, n, label)
+    ok, ch = _library_verify(lib, instances, n, proof, label)
+    ok_o, ch_o = pyoracle.agl_same_point_verify(instances, n, proof, label)
+    assert ok and ok_o and np.array_equal(ch, ch_o) and np.array_equal(ch, proof["challenges"])
+    rng = np.random.default_rng(n)
+    for key in ("round_msgs", "f_evals", "final_eval"):
+        flat = proof[key].reshape(-1)
+        for pos in sorted(set(int(x) for x in rng.integers(0, len(flat), 12))):
+            bad = {k: v.copy() for k, v in proof.items()}
+            bad[key].reshape(-1)[pos] ^= np.uint64(1)
+            got = _library_verify(lib, instances, n, bad, label)[0]
+            assert got == pyoracle.agl_same_point_verify(instances, n, bad, label)[0], "%s word %d" % (key, pos)
+            assert not got
+    # a wrong claim and a wrong label
+    wrong = [dict(i) for i in instances]
+    wrong[0]["value"] = np.array([(int(wrong[0]["value"][0]) + 1) % AGL_Q, int(wrong[0]["value"][1])], dtype=np.uint64)
+    assert not _library_verify(lib, wrong, n, proof, label)[0]
+    assert not _library_verify(lib, instances, n, proof, b"other")[0]
