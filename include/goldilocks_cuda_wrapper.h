@@ -162,6 +162,11 @@ int gl_sumcheck_prove_host_ffi(const uint64_t* h_tables, int d, int num_var, int
                                const uint8_t* label, size_t label_len, uint64_t* round_msgs,
                                uint64_t* challenges, uint64_t* final_evals, uint64_t* final_eval,
                                uint64_t* transcript_state);
+/* The verifier of the same protocol on the host (zk-torch-3/src/sumcheck/verifier.rs): *ok = 1 when every round's
+ * P(0) + P(1) equals the running claim and the last claim equals final_eval. round_msgs[num_var][d+1][2],
+ * claimed_sum[2], final_eval[2]; challenges[num_var][2] may be NULL. No device call. */
+int gl_sumcheck_verify_ffi(const uint64_t* round_msgs, const uint64_t* final_eval, const uint64_t* claimed_sum, int d,
+                           int num_var, const uint8_t* label, size_t label_len, uint64_t* challenges, int* ok);
 
 /* ---- Poseidon2: ffi.rs:287-300 (wrapper.cu:863-964) ----
  * hash_batch permutes n width-8 states (8 words in, 8 out); compress_batch and

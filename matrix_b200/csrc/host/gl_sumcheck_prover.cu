@@ -65,9 +65,64 @@ static int prove_linear(const uint64_t* d_tables, int d, int num_var, bool base_
     return MB_OK;
 }
 
+// Lagrange interpolation through x = 0..n-1, evaluated at x (zk-torch-3/src/sumcheck/verifier.rs: the next claim is
+// P_round(r)).
+static Ext2 interpolate_and_evaluate(const Ext2* evals, int n, Ext2 x) {
+    gl::E2 result{0, 0};
+    const gl::E2 xx{x.c0, x.c1};
+    for (int i = 0; i < n; i++) {
+        gl::E2 num{1, 0};
+        uint64_t den = 1;
+        for (int j = 0; j < n; j++) {
+            if (j == i) continue;
+            num = gl::e2_canon(gl::e2_mul(num, gl::e2_sub(xx, gl::E2{(uint64_t)j, 0})));
+            den = gl::mul(den, gl::sub((uint64_t)i, (uint64_t)j));
+        }
+        const uint64_t inv = gl::canon(gl::inv(den));
+        const gl::E2 basis{gl::mul(num.c0, inv), gl::mul(num.c1, inv)};
+        result = gl::e2_add(result, gl::e2_mul(gl::E2{evals[i].c0, evals[i].c1}, basis));
+    }
+    result = gl::e2_canon(result);
+    return Ext2{result.c0, result.c1};
+}
+
 }  // namespace mbhost
 
 extern "C" {
+
+// The verifier of the same protocol on the host (zk-torch-3/src/sumcheck/verifier.rs): *ok = 1 when every round's
+// P(0) + P(1) equals the running claim and the last claim equals final_eval; the challenges (num_var pairs) are
+// written when `challenges` is not NULL. The transcript starts as Transcript::new(label) and is advanced exactly as
+// the prover's, up to the round that fails. No device call.
+int gl_sumcheck_verify_ffi(const uint64_t* round_msgs, const uint64_t* final_eval, const uint64_t* claimed_sum, int d, int num_var,
+                           const uint8_t* label, size_t label_len, uint64_t* challenges, int* ok) {
+    using namespace mbhost;
+    if (!ok || !final_eval || !claimed_sum || d < 1 || d > MAX_D || num_var < 0 || (num_var && !round_msgs) || (!label && label_len))
+        return MB_ERR_ARG;
+    *ok = 0;
+    Transcript t(label, label_len);
+    t.append_u64("num_var", (uint64_t)num_var);
+    t.append_u64("num_poly", (uint64_t)d);
+    Ext2 current{gl::canon(claimed_sum[0]), gl::canon(claimed_sum[1])};
+    std::vector<Ext2> msg(d + 1);
+    for (int round = 0; round < num_var; round++) {
+        for (int c = 0; c <= d; c++) {
+            const uint64_t* w = round_msgs + ((size_t)round * (d + 1) + c) * 2;
+            msg[c] = Ext2{gl::canon(w[0]), gl::canon(w[1])};
+        }
+        const gl::E2 sum = gl::e2_canon(gl::e2_add(gl::E2{msg[0].c0, msg[0].c1}, gl::E2{msg[1].c0, msg[1].c1}));
+        if (sum.c0 != current.c0 || sum.c1 != current.c1) return MB_OK;
+        for (int c = 0; c <= d; c++) t.append_ext2("round_message", msg[c]);
+        const Ext2 r = t.challenge_ext2("challenge");
+        if (challenges) {
+            challenges[2 * round] = r.c0;
+            challenges[2 * round + 1] = r.c1;
+        }
+        current = interpolate_and_evaluate(msg.data(), d + 1, r);
+    }
+    *ok = current.c0 == gl::canon(final_eval[0]) && current.c1 == gl::canon(final_eval[1]);
+    return MB_OK;
+}
 
 // Whole sumcheck proof for d tables of 2^num_var elements that are already on
 // the device (poly-major). base_field != 0: u64 tables; else (c0, c1) tables.

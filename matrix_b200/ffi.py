@@ -201,6 +201,8 @@ _GL_SIGNATURES = {
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gl_sumcheck_prove_host_ffi": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.c_char_p, c_size_t,
                                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "gl_sumcheck_verify_ffi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_char_p, c_size_t, c_void_p,
+                                       ctypes.POINTER(c_int)]),
 }
 
 

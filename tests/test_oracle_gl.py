@@ -104,3 +104,47 @@ def test_sumcheck_random_prover_verifier_roundtrip(oracle):
         rc = oracle.oracle_gl_sumcheck_verify(d, nv, b"bench", 5, claim.ctypes.data, res["round_msgs"].ctypes.data,
                                               res["final_eval"].ctypes.data)
         assert rc == 0
+
+
+def test_library_sumcheck_verifier_agrees_with_oracle_verifier(oracle):
+    """gl_sumcheck_verify_ffi (host code of the CUDA library, no device call; zk-torch-3/src/sumcheck/verifier.rs) on
+    proofs written by the oracle prover: accepts them with the prover's challenges, and gives the oracle verifier's
+    verdict on every flipped word of the messages, a wrong final value, a wrong claim and a wrong label."""
+    import ctypes
+    from matrix_b200.ffi import load_gl
+    from oracle import pyoracle
+    lib = load_gl()
+
+    def ours(msgs, fin, claim, d, nv, label):
+        msgs = np.ascontiguousarray(msgs, dtype=np.uint64)
+        ch, ok = np.zeros((max(nv, 1), 2), dtype=np.uint64), ctypes.c_int(-1)
+        assert lib.gl_sumcheck_verify_ffi(msgs.ctypes.data, fin.ctypes.data, claim.ctypes.data, d, nv, label, len(label),
+                                          ch.ctypes.data, ctypes.byref(ok)) == 0
+        return bool(ok.value), ch[:nv]
+
+    def theirs(msgs, fin, claim, d, nv, label):
+        msgs = np.ascontiguousarray(msgs, dtype=np.uint64)
+        return oracle.oracle_gl_sumcheck_verify(d, nv, label, len(label), claim.ctypes.data, msgs.ctypes.data, fin.ctypes.data) == 0
+
+    cases = [(2, 2, True, np.array([1, 2, 3, 4, 5, 6, 7, 8], dtype=np.uint64), b"test")]
+    for nv, d, base in ((1, 1, True), (3, 2, True), (5, 3, False), (6, 2, False), (4, 4, True), (3, 6, False)):
+        cases.append((nv, d, base, field_elems(300 + nv, (1 << nv) * d * (1 if base else 2)), b"bench"))
+    for nv, d, base, polys, label in cases:
+        res = pyoracle.sumcheck_prove(polys, d, nv, base, label)
+        msgs, fin = res["round_msgs"], res["final_eval"]
+        m0 = msgs[0]
+        claim = np.array([(int(m0[0][0]) + int(m0[1][0])) % P, (int(m0[0][1]) + int(m0[1][1])) % P], dtype=np.uint64)
+        ok, ch = ours(msgs, fin, claim, d, nv, label)
+        assert ok and theirs(msgs, fin, claim, d, nv, label) and np.array_equal(ch, res["challenges"])
+        flat_len = msgs.size
+        for pos in range(flat_len):
+            bad = msgs.copy()
+            bad.reshape(-1)[pos] ^= np.uint64(1)
+            assert ours(bad, fin, claim, d, nv, label)[0] == theirs(bad, fin, claim, d, nv, label) is False, "word %d" % pos
+        bad_fin = fin.copy()
+        bad_fin[0] ^= np.uint64(1)
+        assert not ours(msgs, bad_fin, claim, d, nv, label)[0] and not theirs(msgs, bad_fin, claim, d, nv, label)
+        bad_claim = claim.copy()
+        bad_claim[1] ^= np.uint64(1)
+        assert not ours(msgs, fin, bad_claim, d, nv, label)[0]
+        assert not ours(msgs, fin, claim, d, nv, label + b"x")[0]
