@@ -376,6 +376,13 @@ int gl_batched_prove_sharded(const mb_exchange* ex, const uint64_t* d_a, const u
                              const uint64_t* h_point, const uint8_t* label, size_t label_len, uint64_t* h_claims,
                              uint64_t* h_alpha, uint64_t* h_round_msgs, uint64_t* h_challenges, uint64_t* h_finals,
                              uint64_t* h_final_eval, uint64_t* h_transcript_state, double* h_round_us);
+/* Verifier of that proof on the host (no device call): transcript replay, P(0) + P(1) against the running claim in
+ * every round (first claim sum_k alpha^k y_k), P(r) by interpolation on 0..3, and at the end the last claim against
+ * eq(R) sum_k alpha^k a_k(R) b_k(R), with eq(R) recomputed from h_point and the challenges (round i binds variable
+ * i). h_challenges [num_vars][2] may be null. *ok = 1 when accepted. */
+int gl_batched_verify_host(int K, int num_vars, const uint64_t* h_point, const uint8_t* label, size_t label_len,
+                           const uint64_t* h_claims, const uint64_t* h_round_msgs, const uint64_t* h_finals,
+                           uint64_t* h_challenges, int* ok);
 
 /* ---- additions: the host transcript (zk-torch-3/src/transcript.rs:174-350) ---- */
 int gl_transcript_create(const uint8_t* label, size_t label_len, void** transcript);

@@ -517,4 +517,72 @@ int gl_transcript_challenge_ext2(void* t, const char* label, uint64_t* out2) {
 }
 int gl_transcript_state(const void* t, uint64_t* out8) { std::memcpy(out8, static_cast<const Transcript*>(t)->state(), 64); return MB_OK; }
 
+// Verifier of the batched eq * a * b proof on the host (no device call): replays the transcript of
+// gl_batched_prove_sharded, checks P(0) + P(1) against the running claim in every round (the first claim is
+// sum_k alpha^k y_k), takes P(r) by interpolation on 0..3 as the next claim, and at the end checks that the last
+// claim equals eq(R) sum_k alpha^k a_k(R) b_k(R) and that the revealed eq(R) is the eq polynomial of h_point at the
+// challenges (round i binds variable i). The revealed a_k(R), b_k(R) are the openings the caller checks against its
+// commitments. h_claims [K][2], h_round_msgs [num_vars][4][2], h_finals [2K + 1][2]; h_challenges [num_vars][2]
+// (may be null) receives the challenges. *ok = 1 when accepted.
+int gl_batched_verify_host(int K, int num_vars, const uint64_t* h_point, const uint8_t* label, size_t label_len,
+                           const uint64_t* h_claims, const uint64_t* h_round_msgs, const uint64_t* h_finals,
+                           uint64_t* h_challenges, int* ok) {
+    using namespace mbhost;
+    if (K < 1 || num_vars < 1 || num_vars > 40 || !h_point || !h_claims || !h_round_msgs || !h_finals || !ok || (!label && label_len))
+        return MB_ERR_ARG;
+    *ok = 0;
+    Transcript tr(label, label_len);
+    tr.append_u64("sp_num_var", (uint64_t)num_vars);
+    tr.append_u64("sp_num_inst", (uint64_t)K);
+    for (int k = 0; k < K; k++) tr.append_ext2("sp_y_i", Ext2{gl::canon(h_claims[2 * k]), gl::canon(h_claims[2 * k + 1])});
+    const Ext2 a = tr.challenge_ext2("sp_alpha");
+    const E2 alpha{a.c0, a.c1};
+    E2 claim{0, 0}, pw{1, 0};
+    for (int k = 0; k < K; k++) {
+        claim = e2c(gl::e2_add(claim, gl::e2_mul(pw, e2_load(h_claims + 2 * k))));
+        pw = e2c(gl::e2_mul(pw, alpha));
+    }
+    // 1 / ((c - 0)(c - 1)...(c - 3)) without the factor c - c, for c = 0..3: -1/6, 1/2, -1/2, 1/6
+    const uint64_t inv2 = gl::canon(gl::inv(2)), inv6 = gl::canon(gl::inv(6));
+    const uint64_t wgt[4] = {gl::canon(gl::sub(0, inv6)), inv2, gl::canon(gl::sub(0, inv2)), inv6};
+    E2 eq_at_r{1, 0};
+    for (int round = 0; round < num_vars; round++) {
+        E2 msg[4];
+        for (int c = 0; c < 4; c++) msg[c] = e2_load(h_round_msgs + (size_t)round * 8 + 2 * c);
+        const E2 sum = e2c(gl::e2_add(msg[0], msg[1]));
+        if (sum.c0 != claim.c0 || sum.c1 != claim.c1) return MB_OK;
+        for (int c = 0; c < 4; c++) tr.append_ext2("sp_round_msg", Ext2{msg[c].c0, msg[c].c1});
+        const Ext2 rr = tr.challenge_ext2("sp_round_challenge");
+        const E2 r{rr.c0, rr.c1};
+        if (h_challenges) { h_challenges[2 * round] = r.c0; h_challenges[2 * round + 1] = r.c1; }
+        // P(r) = sum_c P(c) w_c prod_{k != c} (r - k)
+        E2 next{0, 0};
+        for (int c = 0; c < 4; c++) {
+            E2 num{wgt[c], 0};
+            for (int k = 0; k < 4; k++)
+                if (k != c) num = e2c(gl::e2_mul(num, gl::e2_sub(r, E2{(uint64_t)k, 0})));
+            next = gl::e2_add(next, gl::e2_mul(msg[c], num));
+        }
+        claim = e2c(next);
+        // eq factor of variable `round`: p r + (1 - p)(1 - r)
+        const E2 p = e2_load(h_point + 2 * round), one{1, 0};
+        const E2 f = gl::e2_add(gl::e2_mul(p, r), gl::e2_mul(gl::e2_sub(one, p), gl::e2_sub(one, r)));
+        eq_at_r = e2c(gl::e2_mul(eq_at_r, e2c(f)));
+    }
+    const int T = 2 * K + 1;
+    for (int i = 0; i < T; i++) tr.append_ext2("sp_f_eval", Ext2{gl::canon(h_finals[2 * i]), gl::canon(h_finals[2 * i + 1])});
+    const E2 eq_rev = e2_load(h_finals);
+    if (eq_rev.c0 != eq_at_r.c0 || eq_rev.c1 != eq_at_r.c1) return MB_OK;
+    E2 acc{0, 0};
+    pw = E2{1, 0};
+    for (int k = 0; k < K; k++) {
+        acc = e2c(gl::e2_add(acc, gl::e2_mul(pw, e2c(gl::e2_mul(e2_load(h_finals + 2 * (1 + k)), e2_load(h_finals + 2 * (1 + K + k)))))));
+        pw = e2c(gl::e2_mul(pw, alpha));
+    }
+    const E2 last = e2c(gl::e2_mul(eq_rev, acc));
+    *ok = last.c0 == claim.c0 && last.c1 == claim.c1;
+    return MB_OK;
+}
+
+
 }  // extern "C"

@@ -191,6 +191,8 @@ _GL_SIGNATURES = {
     "gl_batched_state_finals": (c_int, [c_void_p, c_void_p]),
     "gl_batched_prove_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, ctypes.c_char_p, c_size_t,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "gl_batched_verify_host": (c_int, [c_int, c_int, c_void_p, ctypes.c_char_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       ctypes.POINTER(c_int)]),
     "gl_transcript_create": (c_int, [ctypes.c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
     "gl_transcript_destroy": (c_int, [c_void_p]),
     "gl_transcript_append_u64": (c_int, [c_void_p, ctypes.c_char_p, c_u64]),

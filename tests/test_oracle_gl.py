@@ -7,6 +7,7 @@ import os
 import random
 
 import numpy as np
+import pytest
 
 from .conftest import GL_P, ROOT, field_elems
 
@@ -148,3 +149,56 @@ def test_library_sumcheck_verifier_agrees_with_oracle_verifier(oracle):
         bad_claim[1] ^= np.uint64(1)
         assert not ours(msgs, fin, bad_claim, d, nv, label)[0]
         assert not ours(msgs, fin, claim, d, nv, label + b"x")[0]
+
+
+@pytest.mark.parametrize("K,nv", [(1, 1), (1, 4), (3, 5), (16, 6), (5, 9)])
+def test_library_batched_verifier_accepts_oracle_proofs_and_rejects_tampering(K, nv):
+    """gl_batched_verify_host (host code of the CUDA library, no device call) on the batched eq * a * b proofs the
+    oracle prover writes: the round sums chain from sum_k alpha^k y_k down to eq(R) sum_k alpha^k a_k(R) b_k(R), the
+    revealed eq(R) is the eq polynomial of the point at the challenges, the challenges are the prover's, and the
+    claims are the sums over the cube computed with Python integers. Every flipped word of the claims, the messages
+    and the reveals, a wrong point and a wrong label are rejected."""
+    import ctypes
+    from matrix_b200.ffi import load_gl
+    from oracle import pyoracle
+    lib = load_gl()
+    n = 1 << nv
+    a, b = field_elems(400 + K, K * n), field_elems(500 + nv, K * n)
+    point = field_elems(600 + K + nv, 2 * nv)
+    res = pyoracle.batched_prove(a, b, point, K, nv, b"cfg4")
+
+    def verify(claims, msgs, finals, pt=point, label=b"cfg4"):
+        claims, msgs, finals = (np.ascontiguousarray(x, dtype=np.uint64) for x in (claims, msgs, finals))
+        ch, ok = np.zeros((nv, 2), dtype=np.uint64), ctypes.c_int(-1)
+        assert lib.gl_batched_verify_host(K, nv, pt.ctypes.data, label, len(label), claims.ctypes.data, msgs.ctypes.data,
+                                          finals.ctypes.data, ch.ctypes.data, ctypes.byref(ok)) == 0
+        return bool(ok.value), ch
+
+    ok, ch = verify(res["claims"], res["round_msgs"], res["finals"])
+    assert ok and np.array_equal(ch, res["challenges"])
+    # the claims are what they say: y_k = sum_x eq(point, x) a_k(x) b_k(x), here for a small case with Python integers
+    if nv <= 5:
+        def mul(x, y):
+            return ((x[0] * y[0] + 7 * x[1] * y[1]) % P, (x[0] * y[1] + x[1] * y[0]) % P)
+        pt = [(int(point[2 * i]), int(point[2 * i + 1])) for i in range(nv)]
+        for k in range(K):
+            y = (0, 0)
+            for x in range(n):
+                e = (1, 0)
+                for i in range(nv):
+                    e = mul(e, pt[i] if (x >> i) & 1 else ((1 - pt[i][0]) % P, (-pt[i][1]) % P))
+                t = mul(e, (int(a[k * n + x]) * int(b[k * n + x]) % P, 0))
+                y = ((y[0] + t[0]) % P, (y[1] + t[1]) % P)
+            assert (int(res["claims"][k][0]), int(res["claims"][k][1])) == y
+    rng = np.random.default_rng(K * 100 + nv)
+    for key in ("claims", "round_msgs", "finals"):
+        size = res[key].size
+        positions = range(size) if size <= 64 else sorted(set(int(x) for x in rng.integers(0, size, 48)) | {0, size - 1})
+        for pos in positions:
+            parts = {k: res[k].copy() for k in ("claims", "round_msgs", "finals")}
+            parts[key].reshape(-1)[pos] ^= np.uint64(1)
+            assert not verify(parts["claims"], parts["round_msgs"], parts["finals"])[0], "%s word %d accepted" % (key, pos)
+    bad_point = point.copy()
+    bad_point[2 * (nv - 1)] ^= np.uint64(1)
+    assert not verify(res["claims"], res["round_msgs"], res["finals"], pt=bad_point)[0]
+    assert not verify(res["claims"], res["round_msgs"], res["finals"], label=b"cfg5")[0]
