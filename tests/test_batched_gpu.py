@@ -69,6 +69,13 @@ def test_whole_proof_inside_the_library(K, nv, g_bits):
     exp = pyoracle.batched_prove(a, b, np.array([c for t in point for c in t], dtype=np.uint64), K, nv)
     for g in range(world):
         assert_same_proof(got[g], exp)
+    # and the library's own verifier of the protocol accepts what the ranks wrote
+    pt = np.array([c for t in point for c in t], dtype=np.uint64)
+    ch, ok = np.zeros((nv, 2), dtype=np.uint64), ctypes.c_int(-1)
+    assert lib.gl_batched_verify_host(K, nv, pt.ctypes.data, b"bench", 5, got[0]["claims"].ctypes.data,
+                                      got[0]["round_msgs"].ctypes.data, got[0]["finals"].ctypes.data, ch.ctypes.data,
+                                      ctypes.byref(ok)) == 0
+    assert ok.value == 1 and np.array_equal(ch, got[0]["challenges"])
 
 
 def test_whole_proof_refuses_a_world_larger_than_the_hypercube():
